@@ -1,0 +1,297 @@
+/*
+ * pxe.h -- C ABI of the B200 (sm_100a) epilogue kernels for PixieNN.
+ *
+ * Every entry point replaces one step that PixieNN's CUDA layers run between
+ * convolutions.  The comment above each declaration names the reference call
+ * site(s) it stands in for, by path inside the trieck/pixienn tree.
+ *
+ * Conventions
+ *  - All tensors are fp32, NCHW.  A "batch stride" is the distance in ELEMENTS
+ *    between consecutive images of a tensor; 0 means "densely packed"
+ *    (channels*height*width).  A non-dense stride lets a kernel read from or
+ *    write into a channel slot of a wider concat buffer, which is how route
+ *    (concat) layers are eliminated.
+ *  - The caller owns every buffer.  No entry point allocates or frees device
+ *    memory, and none synchronises: work is enqueued on `stream` (0 = the
+ *    legacy default stream the reference uses everywhere).
+ *  - Every entry point returns PXE_OK (0) or an error code, validates its
+ *    arguments before launching anything, never throws and never aborts.
+ *    pxe_last_error_string() returns the message of the calling thread's most
+ *    recent failure.
+ *  - Functions are re-entrant; there is no global mutable state apart from a
+ *    per-device cache of immutable device properties.
+ */
+#ifndef PXE_H
+#define PXE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define PXE_API
+#else
+#define PXE_API __attribute__((visibility("default")))
+#endif
+
+typedef void* pxe_stream_t;   /* a cudaStream_t */
+
+enum pxe_status {
+    PXE_OK = 0,
+    PXE_ERR_BAD_ARG = 1,       /* null pointer, non-positive size, misaligned or overlapping buffer */
+    PXE_ERR_UNSUPPORTED = 2,   /* valid request this build has no kernel for */
+    PXE_ERR_CUDA = 3,          /* a CUDA runtime call failed; see pxe_last_error_string() */
+    PXE_ERR_WORKSPACE = 4      /* caller-provided workspace is too small */
+};
+
+/* Same values as the reference's ActivationType (include/ActivationTypes.h:19-30). */
+enum pxe_activation {
+    PXE_ACT_LEAKY = 0,      /* x > 0 ? x : 0.1 x   (slope fixed, include/Activation.h:45) */
+    PXE_ACT_LINEAR = 1,
+    PXE_ACT_LOGGY = 2,
+    PXE_ACT_LOGISTIC = 3,
+    PXE_ACT_MISH = 4,
+    PXE_ACT_RELU = 5,
+    PXE_ACT_SOFTPLUS = 6,
+    PXE_ACT_SWISH = 7,      /* beta fixed to 1, include/Activation.h:195 */
+    PXE_ACT_TANH = 8,
+    /* Not a reference activation: the YOLO head's per-entry rule (logistic on x, y,
+     * objectness and class entries, identity on w, h) so that bias add and
+     * yoloActivateGpu run as one pass.  Needs pxe_epilogue_desc.yolo_classes. */
+    PXE_ACT_YOLO_HEAD = 100
+};
+
+/* How epsilon enters the batch-norm denominator. */
+enum pxe_bn_eps_mode {
+    PXE_BN_EPS_CUDNN = 0,   /* sqrt(var + eps): cudnnBatchNormalizationForwardInference, the CUDA path */
+    PXE_BN_EPS_CPU = 1      /* sqrt(var) + eps: normalizeCpu, src/CpuUtil.cpp:288 */
+};
+
+/* One detection, the fields of px::Detection (include/Detection.h:23-40) plus the emitting slot. */
+typedef struct pxe_detection {
+    float x, y, w, h;       /* cv::Rect2f: left, top, width, height */
+    float prob;
+    int32_t class_id;
+    int32_t batch_id;
+    int32_t source;         /* YOLO: cell*masks + mask slot; CenterNet: (class*H + y)*W + x;
+                               Region: cell*num + n; Softmax: class */
+} pxe_detection;
+
+PXE_API int pxe_version(void);
+PXE_API const char* pxe_last_error_string(void);
+PXE_API const char* pxe_status_string(int status);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused convolution epilogue.
+ *
+ * Replaces, in one pass over the conv output, the sequence in
+ * ConvLayer<Device::CUDA>::forward (include/cuda/ConvLayer.h:284-307):
+ *   cudnnBatchNormalizationForwardInference (eps 1e-5)  OR  addBiasGpu (src/BiasKernels.cu:86-93),
+ *   the preActivation_ device copy (skipped: inference never reads it),
+ *   activation_->apply == px::activate (src/Activation.cu:126-133),
+ * and, when requested, the layers that follow it in the graph:
+ *   ShortcutLayer<CUDA>::forward (include/cuda/ShortcutLayer.h:23-34): residual add + activation,
+ *   MaxPoolLayer<CUDA>::forward  (include/cuda/MaxPoolLayer.h:36-42) for kernel 2 / stride 2,
+ *   RouteLayer<CUDA>::forward    (include/cuda/RouteLayer.h:21-44): the result is stored straight
+ *                                into its slot of the concat buffer (y or y2 with a batch stride),
+ *   yoloActivateGpu              (src/YoloKernels.cu:216-221) via PXE_ACT_YOLO_HEAD.
+ *
+ * v = x; if gamma: v = gamma*(v-mean)/denom(var,eps) + beta; if bias: v += bias; v = act(v);
+ * if residual: v = res_act(res_alpha*v + res_beta*residual);
+ * y (and y2) receive v; y_pool receives the 2x2/stride-2 max of v (window origin
+ * -pool_padding/2 == 0, out-of-range taps skipped, first maximum wins).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pxe_epilogue_desc {
+    const float* x;             /* conv output [batch, channels, height, width] */
+    long long x_batch_stride;
+    float* y;                   /* destination; may equal x (in place).  May be NULL only when y_pool is set */
+    long long y_batch_stride;
+    float* y2;                  /* optional second destination (e.g. a concat slot), or NULL */
+    long long y2_batch_stride;
+    int batch, channels, height, width;
+
+    const float* gamma;         /* scales_;      NULL = no batch norm */
+    const float* beta;          /* biases_ (BN shift) */
+    const float* mean;          /* rollingMean_ */
+    const float* var;           /* rollingVar_ */
+    float eps;                  /* the reference passes 1e-5 */
+    int eps_mode;               /* enum pxe_bn_eps_mode */
+    const float* bias;          /* per-channel bias added after BN, or the conv bias when gamma is NULL; may be NULL */
+    int act;                    /* enum pxe_activation */
+    int yolo_classes;           /* PXE_ACT_YOLO_HEAD only: channels % (yolo_classes + 5) must be 0 */
+
+    const float* residual;      /* from_->output() of a following shortcut layer, or NULL */
+    long long residual_batch_stride;
+    float res_alpha, res_beta;  /* ShortcutLayer alpha_, beta_ (include/ShortcutLayer.h:51-52) */
+    int res_act;                /* the shortcut layer's activation */
+
+    int pool_kernel;            /* 0 = no pooling; otherwise must be 2 */
+    int pool_stride;            /* must be 2 */
+    int pool_padding;           /* 0 or 1 (the MaxPoolLayer default is kernel-1 = 1) */
+    float* y_pool;              /* [batch, channels, OH, OW], OH = (height + pad - 2)/2 + 1 */
+    long long y_pool_batch_stride;
+} pxe_epilogue_desc;
+
+PXE_API int pxe_conv_epilogue(pxe_stream_t stream, const pxe_epilogue_desc* desc);
+
+/* px::activate(type, x, n), include/Activation.cuh:26 / src/Activation.cu:126-133: in-place activation. */
+PXE_API int pxe_activate(pxe_stream_t stream, int act, float* x, size_t n);
+
+/* px::addBiasGpu, include/BiasKernels.cuh:21 / src/BiasKernels.cu:86-93: out[b, j, :] += bias[j]. */
+PXE_API int pxe_add_bias(pxe_stream_t stream, float* out, const float* bias, int batch, int n, int size);
+
+/* ------------------------------------------------------------------------------------------
+ * Max pooling: px::maxPoolForwardGpu (include/MaxPoolKernels.cuh:5, src/MaxPoolKernels.cu:10-59).
+ * Output extent (in + padding - kernel)/stride + 1 (include/MaxPoolLayer.h:61-62), window origin
+ * -padding/2 with C truncation, out-of-range taps skipped, first maximum wins.  `indexes`
+ * (int32 flat index into a DENSE input tensor, -1 for an empty window) may be NULL.
+ * ------------------------------------------------------------------------------------------ */
+PXE_API int pxe_maxpool(pxe_stream_t stream, const float* x, long long x_batch_stride, float* y,
+                        long long y_batch_stride, int* indexes, int batch, int channels, int height,
+                        int width, int kernel, int stride, int padding);
+PXE_API int pxe_maxpool_out_dim(int in, int kernel, int stride, int padding);
+
+/* SPP block: several stride-1 max pools of the SAME input (e.g. kernels 5, 9, 13 with the default
+ * padding kernel-1), each written to its own destination, in one launch that reads the input once.
+ * Stands in for consecutive MaxPoolLayer<CUDA>::forward calls joined by route layers. */
+PXE_API int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_stride, int batch, int channels,
+                    int height, int width, int n_pools, const int* kernels, float* const* ys,
+                    const long long* y_batch_strides);
+
+/* px::upsampleGpu forward (include/UpsampleKernels.cuh:21, src/UpsampleKernels.cu:25-63):
+ * nearest-neighbour x stride, y = scale * x (assigned, as the CPU layer does). */
+PXE_API int pxe_upsample(pxe_stream_t stream, const float* x, long long x_batch_stride, float* y,
+                         long long y_batch_stride, int batch, int channels, int height, int width,
+                         int stride, float scale);
+
+/* ShortcutLayer<CUDA>::forward (include/cuda/ShortcutLayer.h:23-34) for equal shapes:
+ * y = act(alpha * x + beta * from).  y may alias x. */
+PXE_API int pxe_shortcut(pxe_stream_t stream, const float* x, long long x_batch_stride, const float* from,
+                         long long from_batch_stride, float* y, long long y_batch_stride, float* y2,
+                         long long y2_batch_stride, int batch, int channels, int height, int width,
+                         float alpha, float beta, int act);
+
+/* px::shortcutGpu (include/ShortcutKernel.cuh:21, src/ShortcutKernel.cu:25-66), any shapes:
+ * out = s1 * out + s2 * add with the reference's stride/sample index rule. */
+PXE_API int pxe_shortcut_general(pxe_stream_t stream, int batch, int w1, int h1, int c1, const float* add,
+                                 int w2, int h2, int c2, float s1, float s2, float* out);
+
+/* RouteLayer<CUDA>::forward (include/cuda/RouteLayer.h:21-44) as one launch instead of
+ * batch x fan-in blocking copies.  Source s is [batch, src_channels[s], height, width] with its own
+ * batch stride; it lands at channel offset sum(src_channels[0..s)) of y.  n_src <= 8. */
+PXE_API int pxe_concat(pxe_stream_t stream, int n_src, const float* const* srcs,
+                       const long long* src_batch_strides, const int* src_channels, float* y,
+                       long long y_batch_stride, int batch, int height, int width);
+
+/* ------------------------------------------------------------------------------------------
+ * YOLO head
+ * ------------------------------------------------------------------------------------------ */
+/* px::yoloActivateGpu (include/YoloKernels.cuh:7, src/YoloKernels.cu:63-71, 216-221). */
+PXE_API int pxe_yolo_activate(pxe_stream_t stream, const float* in, float* out, int batch, int masks,
+                              int classes, int area);
+
+typedef struct pxe_yolo_decode_desc {
+    const float* head;          /* [batch, masks*(5+classes), height, width] */
+    long long head_batch_stride;
+    int head_is_raw;            /* 0: already activated (YoloLayer output_); 1: raw conv output,
+                                   the decode applies `bias` and the head's logistic rule itself */
+    const float* bias;          /* per-channel conv bias for head_is_raw, or NULL */
+    int batch, height, width;
+    int classes;
+    int n_masks;                /* <= 16 */
+    int mask[16];               /* YoloLayer mask_ */
+    int n_anchor_values;        /* 2*num, <= 64 */
+    int anchors[64];            /* YoloLayer anchors_, ints as the reference parses them (include/YoloLayer.h:93) */
+    int net_width, net_height;  /* model().width(), model().height() */
+    int image_width, image_height;  /* > 0: scaledYoloBox (letterbox-corrected integer pixel boxes,
+                                       include/YoloLayer.h:601-635); 0: normalised yoloBox().rect() */
+    float threshold;
+    int batch_id_offset;        /* added to batch_id (batch-sharded multi-GPU runs) */
+} pxe_yolo_decode_desc;
+
+/* Bytes of device workspace pxe_yolo_decode needs for this head. */
+PXE_API size_t pxe_yolo_decode_workspace_bytes(int batch, int height, int width);
+
+/*
+ * YoloLayer<CUDA>::addDetects (include/cuda/YoloLayer.h:168-188 -> include/YoloLayer.h:659-698):
+ * threshold on objectness, box decode, per-class probability, on the device instead of a
+ * full-tensor device-to-host copy and a host loop.  Records are appended to `dets` starting at
+ * position *count (a device counter the caller zeroes once per forward) in exactly the
+ * reference's emission order (image, cell, mask slot, class), so chaining the heads in layer order
+ * reproduces Model::detections().  *count keeps counting past `capacity`; records beyond it are
+ * dropped, so count > capacity tells the caller to retry with more room.
+ */
+PXE_API int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* desc, pxe_detection* dets,
+                            long long capacity, long long* count, void* workspace,
+                            size_t workspace_bytes);
+
+/* ------------------------------------------------------------------------------------------
+ * CenterNet head
+ * ------------------------------------------------------------------------------------------ */
+/* px::centerNetActivateGpu (include/CenterNetKernels.cuh:5, src/CenterNetKernels.cu:9-18, 110-118). */
+PXE_API int pxe_centernet_activate(pxe_stream_t stream, const float* in, float* out, int batch, int classes,
+                                   int area, float heatmap_bias);
+
+typedef struct pxe_centernet_decode_desc {
+    const float* heat;          /* [batch, classes, height, width] heatmap */
+    long long heat_batch_stride;
+    const float* size;          /* [batch, 2, height, width]: box width, height in cells */
+    long long size_batch_stride;
+    const float* offset;        /* [batch, 2, height, width]: centre offset x, y */
+    long long offset_batch_stride;
+    int heat_is_logit;          /* 1: heat holds logits, sigmoid(heat + heatmap_bias) is applied here;
+                                   0: heat is already activated (CenterNetLayer output_) */
+    float heatmap_bias;
+    int batch, classes, height, width;
+    int image_width, image_height;   /* <= 0 means 1 (normalised boxes) */
+    float threshold;
+    int max_detections;         /* CenterNetLayer max_detections (default 100), <= 1024 */
+    int batch_id_offset;
+} pxe_centernet_decode_desc;
+
+PXE_API size_t pxe_centernet_decode_workspace_bytes(int batch, int classes, int height, int width,
+                                                    int max_detections);
+
+/*
+ * CenterNetLayer<CUDA>::addDetects (include/cuda/CenterNetLayer.h:89-106 ->
+ * include/CenterNetLayer.h:181-247): 3x3 strict local-maximum test on the activated scores,
+ * threshold, validity of size/offset, box rebuild, and the max_detections best per image ordered
+ * by score descending with ties to the lower flat index (class*H + y)*W + x.
+ * dets holds batch*max_detections records (image b at dets + b*max_detections); counts[b]
+ * receives the number of valid records of image b.
+ */
+PXE_API int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_decode_desc* desc,
+                                 pxe_detection* dets, int* counts, void* workspace,
+                                 size_t workspace_bytes);
+
+/* ------------------------------------------------------------------------------------------
+ * Softmax and Region heads
+ * ------------------------------------------------------------------------------------------ */
+/* SoftmaxLayer forward.  CPU semantics (include/SoftmaxLayer.h:86-99, src/Math.cpp:77-108):
+ * each image's `inputs` values are split into `groups` contiguous groups, softmax with
+ * temperature inside each.  The CUDA layer's cudnnSoftmaxForward(MODE_CHANNEL)
+ * (include/cuda/SoftmaxLayer.h:67-85) equals groups = 1, temperature = 1 when height*width == 1. */
+PXE_API int pxe_softmax(pxe_stream_t stream, const float* in, float* out, int batch, int inputs, int groups,
+                        float temperature);
+
+/* RegionLayer forward, inference part (include/RegionLayer.h:271-300), replacing the
+ * device->host->device round trip of include/cuda/RegionLayer.h:39-54: NCHW ->
+ * [cell*num + n][coords+1+classes] transpose (flatten, src/CpuUtil.cpp:364-384), logistic on the
+ * objectness entry, optional softmax over each box's classes.  in != out. */
+PXE_API int pxe_region_forward(pxe_stream_t stream, const float* in, float* out, int batch, int width,
+                               int height, int num, int coords, int classes, int softmax);
+
+/* ------------------------------------------------------------------------------------------
+ * Post-processing on the host: px::nms (src/Box.cpp:56-145), same ordering, same 0.9 IoU
+ * cross-class duplicate rule, same 1024-candidate cap per (image, class) group.
+ * `out` must have room for n records; returns the number kept (or a negative pxe_status).
+ * ------------------------------------------------------------------------------------------ */
+PXE_API long long pxe_nms_host(const pxe_detection* dets, long long n, float threshold, pxe_detection* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PXE_H */

@@ -1,0 +1,138 @@
+"""ctypes declarations for ``libpxe.so`` (the C ABI in ``include/pxe.h``).
+
+This module only loads the library and declares prototypes.  It fails loudly when the library
+has not been built: there is no CPU or PyTorch fallback for any entry point.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libpxe.so")
+
+PXE_OK, PXE_ERR_BAD_ARG, PXE_ERR_UNSUPPORTED, PXE_ERR_CUDA, PXE_ERR_WORKSPACE = range(5)
+
+ACT = {"leaky": 0, "linear": 1, "loggy": 2, "logistic": 3, "mish": 4, "relu": 5, "softplus": 6,
+       "swish": 7, "tanh": 8, "yolo_head": 100}
+EPS_CUDNN, EPS_CPU = 0, 1
+
+
+class PxeError(RuntimeError):
+    """A C-ABI call returned a non-zero status (the counterpart of px::Error / px::CudaError)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"pxe status {status}: {message}")
+        self.status = status
+
+
+class Detection(C.Structure):
+    _fields_ = [("x", C.c_float), ("y", C.c_float), ("w", C.c_float), ("h", C.c_float),
+                ("prob", C.c_float), ("class_id", C.c_int32), ("batch_id", C.c_int32),
+                ("source", C.c_int32)]
+
+
+class EpilogueDesc(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("x_batch_stride", C.c_longlong),
+        ("y", C.c_void_p), ("y_batch_stride", C.c_longlong),
+        ("y2", C.c_void_p), ("y2_batch_stride", C.c_longlong),
+        ("batch", C.c_int), ("channels", C.c_int), ("height", C.c_int), ("width", C.c_int),
+        ("gamma", C.c_void_p), ("beta", C.c_void_p), ("mean", C.c_void_p), ("var", C.c_void_p),
+        ("eps", C.c_float), ("eps_mode", C.c_int),
+        ("bias", C.c_void_p), ("act", C.c_int), ("yolo_classes", C.c_int),
+        ("residual", C.c_void_p), ("residual_batch_stride", C.c_longlong),
+        ("res_alpha", C.c_float), ("res_beta", C.c_float), ("res_act", C.c_int),
+        ("pool_kernel", C.c_int), ("pool_stride", C.c_int), ("pool_padding", C.c_int),
+        ("y_pool", C.c_void_p), ("y_pool_batch_stride", C.c_longlong),
+    ]
+
+
+class YoloDecodeDesc(C.Structure):
+    _fields_ = [
+        ("head", C.c_void_p), ("head_batch_stride", C.c_longlong),
+        ("head_is_raw", C.c_int), ("bias", C.c_void_p),
+        ("batch", C.c_int), ("height", C.c_int), ("width", C.c_int), ("classes", C.c_int),
+        ("n_masks", C.c_int), ("mask", C.c_int * 16),
+        ("n_anchor_values", C.c_int), ("anchors", C.c_int * 64),
+        ("net_width", C.c_int), ("net_height", C.c_int),
+        ("image_width", C.c_int), ("image_height", C.c_int),
+        ("threshold", C.c_float), ("batch_id_offset", C.c_int),
+    ]
+
+
+class CenterNetDecodeDesc(C.Structure):
+    _fields_ = [
+        ("heat", C.c_void_p), ("heat_batch_stride", C.c_longlong),
+        ("size", C.c_void_p), ("size_batch_stride", C.c_longlong),
+        ("offset", C.c_void_p), ("offset_batch_stride", C.c_longlong),
+        ("heat_is_logit", C.c_int), ("heatmap_bias", C.c_float),
+        ("batch", C.c_int), ("classes", C.c_int), ("height", C.c_int), ("width", C.c_int),
+        ("image_width", C.c_int), ("image_height", C.c_int),
+        ("threshold", C.c_float), ("max_detections", C.c_int), ("batch_id_offset", C.c_int),
+    ]
+
+
+# name -> (restype, argtypes); every name here must be declared in include/pxe.h
+_vp, _ll, _i, _f, _sz = C.c_void_p, C.c_longlong, C.c_int, C.c_float, C.c_size_t
+PROTOTYPES = {
+    "pxe_version": (_i, []),
+    "pxe_last_error_string": (C.c_char_p, []),
+    "pxe_status_string": (C.c_char_p, [_i]),
+    "pxe_conv_epilogue": (_i, [_vp, C.POINTER(EpilogueDesc)]),
+    "pxe_activate": (_i, [_vp, _i, _vp, _sz]),
+    "pxe_add_bias": (_i, [_vp, _vp, _vp, _i, _i, _i]),
+    "pxe_maxpool": (_i, [_vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "pxe_maxpool_out_dim": (_i, [_i, _i, _i, _i]),
+    "pxe_spp": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_vp), C.POINTER(_ll)]),
+    "pxe_upsample": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i, _f]),
+    "pxe_shortcut": (_i, [_vp, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _f, _f, _i]),
+    "pxe_shortcut_general": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),
+    "pxe_concat": (_i, [_vp, _i, C.POINTER(_vp), C.POINTER(_ll), C.POINTER(_i), _vp, _ll, _i, _i, _i]),
+    "pxe_yolo_activate": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
+    "pxe_yolo_decode_workspace_bytes": (_sz, [_i, _i, _i]),
+    "pxe_yolo_decode": (_i, [_vp, C.POINTER(YoloDecodeDesc), _vp, _ll, _vp, _vp, _sz]),
+    "pxe_centernet_activate": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
+    "pxe_centernet_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "pxe_centernet_decode": (_i, [_vp, C.POINTER(CenterNetDecodeDesc), _vp, _vp, _vp, _sz]),
+    "pxe_softmax": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
+    "pxe_region_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "pxe_nms_host": (_ll, [_vp, _ll, _f, _vp]),
+}
+
+# mangled names of the link-compatible tier (include/pxe_compat.hpp)
+COMPAT_SYMBOLS = [
+    "_ZN2px8activateE14ActivationTypePfm",
+    "_ZN2px10addBiasGpuEPfPKfiii",
+    "_ZN2px17maxPoolForwardGpuEPKfPfPiiiiiiiiii",
+    "_ZN2px11upsampleGpuEPKfiiiiiifPfS2_",
+    "_ZN2px11shortcutGpuEiiiiPKfiiiffPf",
+    "_ZN2px15yoloActivateGpuEPKfPfiiii",
+    "_ZN2px20centerNetActivateGpuEPKfPfiiif",
+    "_ZN2px7fillGpuEPfmf",
+    "_ZN2px7fillGpuEPimi",
+]
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built (run ``python -m pixienn_b200._build``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m pixienn_b200._build` "
+                "(needs nvcc); there is no fallback implementation")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != PXE_OK:
+        raise PxeError(status, lib().pxe_last_error_string().decode(errors="replace"))

@@ -1,0 +1,665 @@
+// Fused convolution epilogue: batch-norm inference (folded to one multiply-add per element),
+// bias, activation, and optionally the residual add of a following shortcut layer, the 2x2
+// stride-2 max pool of a following maxpool layer, and a store into a concat slot -- one pass
+// over the conv output instead of the reference's separate full-tensor passes
+// (include/cuda/ConvLayer.h:284-307, include/cuda/ShortcutLayer.h:23-34,
+// include/cuda/MaxPoolLayer.h:36-42, include/cuda/RouteLayer.h:21-44).
+//
+// Memory-bound by design: 4 bytes read + 4 bytes written per element (12 with a residual,
+// 4 + 1 with pooled-only output).  No tensor cores: nothing here is a contraction.
+//
+// Work split.  The element space [batch*channels planes][H*W] is cut into contiguous chunks,
+// one per thread block.  A block first writes, for every plane its chunk touches, the folded
+// batch-norm coefficients and the plane's image / channel numbers into shared memory; the
+// streaming loop then needs one shared-memory read and one exact division per 128-bit vector.
+#include "pxe_common.cuh"
+
+namespace pxe {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kMaxPlanesPerBlock = 3000;   // 16 B each -> 48 KB of shared memory at most
+
+struct PlaneEntry {
+    float a, b;          // y = a*x + b
+    int image;           // batch index of the plane
+    int chan;            // channel; bit 30 set = "identity entry" for PXE_ACT_YOLO_HEAD
+};
+
+struct EpiParams {
+    const float* x; float* y; float* y2; const float* res; float* ypool;
+    long long xbs, ybs, y2bs, rbs, pbs;
+    const float *gamma, *beta, *mean, *var, *bias;
+    float eps; int eps_mode;
+    int C, H, W, HW;
+    int yolo_entries;
+    float ralpha, rbeta; int res_act;
+    // streaming kernels: `units` of work (vectors or elements), `chunk` per block
+    uint32_t units, chunk;
+    FastDiv div_plane;   // units per plane (vector path) or HW (scalar / straddle path)
+    FastDiv div_c;
+    // pool kernels
+    int OH, OW, OWV;
+    FastDiv div_owv, div_ohowv;
+};
+
+// Folded coefficients and image / channel numbers of plane `pl` (= image*C + channel).
+__device__ __forceinline__ PlaneEntry make_entry(const EpiParams& p, uint32_t pl)
+{
+    const uint32_t img = p.div_c.div(pl);
+    const uint32_t c = pl - img * (uint32_t)p.C;
+    float a = 1.0f, b = 0.0f;
+    if (p.gamma) {
+        const float v = p.var[c];
+        const float denom = p.eps_mode == PXE_BN_EPS_CPU ? (sqrtf(v) + p.eps) : sqrtf(v + p.eps);
+        a = p.gamma[c] / denom;
+        b = p.beta[c] - p.mean[c] * a;
+    }
+    if (p.bias) b += p.bias[c];
+    int chan = (int)c;
+    if (p.yolo_entries > 0) {
+        const uint32_t e = c % (uint32_t)p.yolo_entries;
+        if (e == 2 || e == 3) chan |= (1 << 30);
+    }
+    PlaneEntry t;
+    t.a = a; t.b = b; t.image = (int)img; t.chan = chan;
+    return t;
+}
+
+__device__ __forceinline__ void build_table(const EpiParams& p, PlaneEntry* tab, uint32_t plane_lo,
+                                            uint32_t plane_hi)
+{
+    for (uint32_t pl = plane_lo + threadIdx.x; pl <= plane_hi; pl += blockDim.x)
+        tab[pl - plane_lo] = make_entry(p, pl);
+}
+
+template <int ACT, bool AFFINE>
+__device__ __forceinline__ float apply_one(float v, const PlaneEntry& t)
+{
+    if (AFFINE) v = fmaf(t.a, v, t.b);
+    if (ACT == PXE_ACT_YOLO_HEAD) return (t.chan & (1 << 30)) ? v : act_logistic(v);
+    return activate<ACT>(v);
+}
+
+__device__ __forceinline__ float residual_one(float v, float r, const EpiParams& p)
+{
+    // alpha*v + beta*r as the reference's CUDA kernel evaluates it (src/ShortcutKernel.cu:41,
+    // contracted to one fused multiply-add by nvcc's default -fmad=true)
+    return activate_dyn(p.res_act, fmaf(p.ralpha, v, p.rbeta * r));
+}
+
+// ---------------------------------------------------------------------------------------------
+// MODE 0: plane-aligned vectors.  HW % 4 == 0 and every base pointer / batch stride keeps
+//         16-byte alignment, so a float4 never crosses a plane.
+// MODE 1: dense straddling vectors.  x, y (y2, res) are densely packed and 16-byte aligned but
+//         HW % 4 != 0 (13x13, 19x19 ...): a float4 may span two planes; HW >= 4.
+// MODE 2: scalar, anything goes.
+// ---------------------------------------------------------------------------------------------
+template <int ACT, bool AFFINE, bool RES, int MODE>
+__global__ void __launch_bounds__(kThreads)
+epilogue_kernel(const EpiParams p)
+{
+    extern __shared__ PlaneEntry tab[];
+    const uint32_t lo = blockIdx.x * p.chunk;
+    if (lo >= p.units) return;
+    uint32_t hi = lo + p.chunk;
+    if (hi > p.units) hi = p.units;
+
+    constexpr int VW = (MODE == 2) ? 1 : 4;
+    // element index of a unit = unit * VW; plane of an element = elem / HW
+    uint32_t plane_lo, plane_hi;
+    if (MODE == 0) {
+        plane_lo = p.div_plane.div(lo);
+        plane_hi = p.div_plane.div(hi - 1);
+    } else {
+        plane_lo = p.div_plane.div(lo * VW);
+        plane_hi = p.div_plane.div((hi - 1) * VW + (VW - 1));
+    }
+    build_table(p, tab, plane_lo, plane_hi);
+    __syncthreads();
+
+    const uint32_t step = kThreads * kUnroll;
+    for (uint32_t base = lo + threadIdx.x; base < hi; base += step) {
+        if (MODE == 0) {
+            float4 v[kUnroll];
+            float4 r[kUnroll];
+            long long off[kUnroll];
+            uint32_t pl[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                uint32_t u = base + k * kThreads;
+                if (u < hi) {
+                    uint32_t q, rem;
+                    p.div_plane.divmod(u, q, rem);
+                    pl[k] = q - plane_lo;
+                    const PlaneEntry t = tab[pl[k]];
+                    long long in_img = (long long)(t.chan & 0xFFFFFF) * p.HW + (long long)rem * 4;
+                    off[k] = in_img;
+                    v[k] = *reinterpret_cast<const float4*>(p.x + (long long)t.image * p.xbs + in_img);
+                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (long long)t.image * p.rbs + in_img);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                uint32_t u = base + k * kThreads;
+                if (u < hi) {
+                    const PlaneEntry t = tab[pl[k]];
+                    float4 o;
+                    o.x = apply_one<ACT, AFFINE>(v[k].x, t);
+                    o.y = apply_one<ACT, AFFINE>(v[k].y, t);
+                    o.z = apply_one<ACT, AFFINE>(v[k].z, t);
+                    o.w = apply_one<ACT, AFFINE>(v[k].w, t);
+                    if (RES) {
+                        o.x = residual_one(o.x, r[k].x, p);
+                        o.y = residual_one(o.y, r[k].y, p);
+                        o.z = residual_one(o.z, r[k].z, p);
+                        o.w = residual_one(o.w, r[k].w, p);
+                    }
+                    if (p.y) *reinterpret_cast<float4*>(p.y + (long long)t.image * p.ybs + off[k]) = o;
+                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (long long)t.image * p.y2bs + off[k]) = o;
+                }
+            }
+        } else if (MODE == 1) {
+            // dense tensors: offset == element index
+            float4 v[kUnroll];
+            float4 r[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                uint32_t u = base + k * kThreads;
+                if (u < hi) {
+                    v[k] = *reinterpret_cast<const float4*>(p.x + (size_t)u * 4);
+                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (size_t)u * 4);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                uint32_t u = base + k * kThreads;
+                if (u < hi) {
+                    uint32_t q, rem;
+                    p.div_plane.divmod(u * 4, q, rem);
+                    const uint32_t room = (uint32_t)p.HW - rem;      // elements left in plane q
+                    const PlaneEntry t0 = tab[q - plane_lo];
+                    const PlaneEntry t1 = (room < 4) ? tab[q - plane_lo + 1] : t0;
+                    float4 o;
+                    o.x = apply_one<ACT, AFFINE>(v[k].x, t0);
+                    o.y = apply_one<ACT, AFFINE>(v[k].y, room > 1 ? t0 : t1);
+                    o.z = apply_one<ACT, AFFINE>(v[k].z, room > 2 ? t0 : t1);
+                    o.w = apply_one<ACT, AFFINE>(v[k].w, room > 3 ? t0 : t1);
+                    if (RES) {
+                        o.x = residual_one(o.x, r[k].x, p);
+                        o.y = residual_one(o.y, r[k].y, p);
+                        o.z = residual_one(o.z, r[k].z, p);
+                        o.w = residual_one(o.w, r[k].w, p);
+                    }
+                    if (p.y) *reinterpret_cast<float4*>(p.y + (size_t)u * 4) = o;
+                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (size_t)u * 4) = o;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                uint32_t u = base + k * kThreads;
+                if (u < hi) {
+                    uint32_t q, rem;
+                    p.div_plane.divmod(u, q, rem);
+                    const PlaneEntry t = tab[q - plane_lo];
+                    long long in_img = (long long)(t.chan & 0xFFFFFF) * p.HW + rem;
+                    float o = apply_one<ACT, AFFINE>(p.x[(long long)t.image * p.xbs + in_img], t);
+                    if (RES) o = residual_one(o, p.res[(long long)t.image * p.rbs + in_img], p);
+                    if (p.y) p.y[(long long)t.image * p.ybs + in_img] = o;
+                    if (p.y2) p.y2[(long long)t.image * p.y2bs + in_img] = o;
+                }
+            }
+        }
+    }
+}
+
+// Tail of MODE 1: the last (n % 4) elements of a dense tensor, one thread each.
+template <int ACT, bool AFFINE, bool RES>
+__global__ void epilogue_tail_kernel(const EpiParams p, uint32_t first, uint32_t count)
+{
+    if (threadIdx.x >= count) return;
+    const uint32_t e = first + threadIdx.x;
+    const PlaneEntry t = make_entry(p, p.div_plane.div(e));
+    float o = apply_one<ACT, AFFINE>(p.x[e], t);
+    if (RES) o = residual_one(o, p.res[e], p);
+    if (p.y) p.y[e] = o;
+    if (p.y2) p.y2[e] = o;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Epilogue + 2x2 stride-2 max pool.  One thread produces VO pooled outputs from a 2 x (2*VO)
+// input patch (VO = 4, 2, 1 by row alignment); VO = 0 is the scalar form for odd widths, one
+// pooled output per thread with bounds-checked taps.  Window origin is (2*oh, 2*ow); taps past
+// the edge are skipped; the first maximum in (ky, kx) scan order wins, as in
+// src/MaxPoolKernels.cu:26-40.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float pick(float m, float v) { return v > m ? v : m; }
+
+template <int ACT, bool AFFINE, int VO>
+__global__ void __launch_bounds__(kThreads)
+epilogue_pool_kernel(const EpiParams p)
+{
+    extern __shared__ PlaneEntry tab[];
+    const uint32_t lo = blockIdx.x * p.chunk;
+    if (lo >= p.units) return;
+    uint32_t hi = lo + p.chunk;
+    if (hi > p.units) hi = p.units;
+    const uint32_t plane_lo = p.div_ohowv.div(lo);
+    const uint32_t plane_hi = p.div_ohowv.div(hi - 1);
+    build_table(p, tab, plane_lo, plane_hi);
+    __syncthreads();
+
+    constexpr int NV = VO == 0 ? 1 : VO;       // pooled outputs per thread
+    constexpr int NI = 2 * NV;                 // input columns per row
+    for (uint32_t u = lo + threadIdx.x; u < hi; u += kThreads) {
+        uint32_t q, rem, oh, owv;
+        p.div_ohowv.divmod(u, q, rem);
+        p.div_owv.divmod(rem, oh, owv);
+        const PlaneEntry t = tab[q - plane_lo];
+        const int c = t.chan & 0xFFFFFF;
+        const int ih = 2 * (int)oh;
+        const int iw = NI * (int)owv;
+        const bool row1 = ih + 1 < p.H;
+        const long long in0 = (long long)c * p.HW + (long long)ih * p.W + iw;
+        const float* x0 = p.x + (long long)t.image * p.xbs + in0;
+        float r0[NI], r1[NI];
+        if (VO == 4) {
+            float4 a0 = *reinterpret_cast<const float4*>(x0);
+            float4 a1 = *reinterpret_cast<const float4*>(x0 + 4);
+            r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
+            r0[4] = a1.x; r0[5] = a1.y; r0[6] = a1.z; r0[7] = a1.w;
+            if (row1) {
+                float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
+                float4 b1 = *reinterpret_cast<const float4*>(x0 + p.W + 4);
+                r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
+                r1[4] = b1.x; r1[5] = b1.y; r1[6] = b1.z; r1[7] = b1.w;
+            }
+        } else if (VO == 2) {
+            float4 a0 = *reinterpret_cast<const float4*>(x0);
+            r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
+            if (row1) {
+                float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
+                r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
+            }
+        } else if (VO == 1) {
+            float2 a0 = *reinterpret_cast<const float2*>(x0);
+            r0[0] = a0.x; r0[1] = a0.y;
+            if (row1) {
+                float2 b0 = *reinterpret_cast<const float2*>(x0 + p.W);
+                r1[0] = b0.x; r1[1] = b0.y;
+            }
+        } else {
+            const bool col1 = iw + 1 < p.W;
+            r0[0] = x0[0];
+            r0[1] = col1 ? x0[1] : 0.0f;
+            if (row1) {
+                r1[0] = x0[p.W];
+                r1[1] = col1 ? x0[p.W + 1] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NI; ++k) {
+            r0[k] = apply_one<ACT, AFFINE>(r0[k], t);
+            r1[k] = row1 ? apply_one<ACT, AFFINE>(r1[k], t) : 0.0f;
+        }
+        const bool col1 = (VO != 0) || (iw + 1 < p.W);
+        float m[NV];
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            float best = r0[2 * k];
+            if (col1) best = pick(best, r0[2 * k + 1]);
+            if (row1) {
+                best = pick(best, r1[2 * k]);
+                if (col1) best = pick(best, r1[2 * k + 1]);
+            }
+            m[k] = best;
+        }
+        float* yp = p.ypool + (long long)t.image * p.pbs + (long long)c * p.OH * p.OW
+                    + (long long)oh * p.OW + (long long)NV * owv;
+        if (VO == 4) *reinterpret_cast<float4*>(yp) = make_float4(m[0], m[1], m[2], m[3]);
+        else if (VO == 2) *reinterpret_cast<float2*>(yp) = make_float2(m[0], m[1]);
+        else yp[0] = m[0];
+
+        if (p.y) {
+            float* y0 = p.y + (long long)t.image * p.ybs + in0;
+            if (VO == 4) {
+                *reinterpret_cast<float4*>(y0) = make_float4(r0[0], r0[1], r0[2], r0[3]);
+                *reinterpret_cast<float4*>(y0 + 4) = make_float4(r0[4], r0[5], r0[6], r0[7]);
+                if (row1) {
+                    *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[0], r1[1], r1[2], r1[3]);
+                    *reinterpret_cast<float4*>(y0 + p.W + 4) = make_float4(r1[4], r1[5], r1[6], r1[7]);
+                }
+            } else if (VO == 2) {
+                *reinterpret_cast<float4*>(y0) = make_float4(r0[0], r0[1], r0[2], r0[3]);
+                if (row1) *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[0], r1[1], r1[2], r1[3]);
+            } else if (VO == 1) {
+                *reinterpret_cast<float2*>(y0) = make_float2(r0[0], r0[1]);
+                if (row1) *reinterpret_cast<float2*>(y0 + p.W) = make_float2(r1[0], r1[1]);
+            } else {
+                y0[0] = r0[0];
+                if (col1) y0[1] = r0[1];
+                if (row1) {
+                    y0[p.W] = r1[0];
+                    if (col1) y0[p.W + 1] = r1[1];
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------- launch helpers
+int waves_setting()
+{
+    static int waves = [] {
+        const char* s = getenv("PXE_WAVES");
+        int w = s ? atoi(s) : 4;
+        return w < 1 ? 1 : w;
+    }();
+    return waves;
+}
+
+// Splits `units` into per-block chunks: a multiple of `granule`, at most `max_chunk`, aiming at
+// sm_count * blocks_per_sm * waves blocks.
+void plan_chunks(uint32_t units, uint32_t granule, uint32_t max_chunk, int sm_count, int blocks_per_sm,
+                 uint32_t* chunk, unsigned* grid)
+{
+    long long target_blocks = (long long)sm_count * blocks_per_sm * waves_setting();
+    long long c = (units + target_blocks - 1) / target_blocks;
+    c = ((c + granule - 1) / granule) * granule;
+    if (max_chunk >= granule && c > (long long)(max_chunk / granule) * granule) c = (long long)(max_chunk / granule) * granule;
+    if (c < granule) c = granule;
+    *chunk = (uint32_t)c;
+    *grid = (unsigned)((units + c - 1) / c);
+}
+
+template <int ACT, bool AFFINE, bool RES, int MODE>
+int launch_stream_kernel(cudaStream_t s, EpiParams& p, const DeviceInfo& di)
+{
+    const int vw = MODE == 2 ? 1 : 4;
+    // planes touched by a chunk of `chunk` units: chunk*vw/HW + 2  <= kMaxPlanesPerBlock
+    long long max_chunk_ll = (long long)(kMaxPlanesPerBlock - 2) * p.HW / vw;
+    uint32_t max_chunk = max_chunk_ll > 0x7fffffffLL ? 0x7fffffffu : (uint32_t)max_chunk_ll;
+    uint32_t granule = kThreads * kUnroll;
+    if (max_chunk < granule) { granule = kThreads; }
+    if (max_chunk < granule) { max_chunk = granule; }   // tiny HW: checked below
+    unsigned grid;
+    plan_chunks(p.units, granule, max_chunk, di.sm_count, 4, &p.chunk, &grid);
+    long long planes = (long long)p.chunk * vw / p.HW + 2;
+    size_t smem = (size_t)planes * sizeof(PlaneEntry);
+    if (smem > 48 * 1024) {
+        if (smem > (size_t)di.max_smem_optin)
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue: plane table of %zu bytes does not fit shared memory", smem);
+        PXE_CUDA_OK(cudaFuncSetAttribute(epilogue_kernel<ACT, AFFINE, RES, MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    epilogue_kernel<ACT, AFFINE, RES, MODE><<<grid, kThreads, smem, s>>>(p);
+    PXE_LAUNCH_OK("epilogue_kernel");
+    return PXE_OK;
+}
+
+template <int ACT, bool AFFINE, bool RES>
+int dispatch_mode(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int mode, long long n_elems)
+{
+    if (mode == 0) {
+        p.units = (uint32_t)(n_elems / 4);
+        p.div_plane = FastDiv((uint32_t)(p.HW / 4));
+        return launch_stream_kernel<ACT, AFFINE, RES, 0>(s, p, di);
+    }
+    if (mode == 1) {
+        p.units = (uint32_t)(n_elems / 4);
+        p.div_plane = FastDiv((uint32_t)p.HW);
+        int rc = PXE_OK;
+        if (p.units) rc = launch_stream_kernel<ACT, AFFINE, RES, 1>(s, p, di);
+        if (rc != PXE_OK) return rc;
+        uint32_t tail = (uint32_t)(n_elems % 4);
+        if (tail) {
+            epilogue_tail_kernel<ACT, AFFINE, RES><<<1, 32, 0, s>>>(p, (uint32_t)(n_elems - tail), tail);
+            PXE_LAUNCH_OK("epilogue_tail_kernel");
+        }
+        return PXE_OK;
+    }
+    p.units = (uint32_t)n_elems;
+    p.div_plane = FastDiv((uint32_t)p.HW);
+    return launch_stream_kernel<ACT, AFFINE, RES, 2>(s, p, di);
+}
+
+template <int ACT>
+int dispatch_flags(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int mode, long long n, bool affine)
+{
+    const bool res = p.res != nullptr;
+    if (affine) {
+        return res ? dispatch_mode<ACT, true, true>(s, p, di, mode, n)
+                   : dispatch_mode<ACT, true, false>(s, p, di, mode, n);
+    }
+    return res ? dispatch_mode<ACT, false, true>(s, p, di, mode, n)
+               : dispatch_mode<ACT, false, false>(s, p, di, mode, n);
+}
+
+template <int ACT, bool AFFINE>
+int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
+{
+    const int nv = vo == 0 ? 1 : vo;
+    p.OWV = p.OW / nv;
+    p.div_owv = FastDiv((uint32_t)p.OWV);
+    p.div_ohowv = FastDiv((uint32_t)(p.OH * p.OWV));
+    const uint32_t per_plane = (uint32_t)(p.OH * p.OWV);
+    long long max_chunk_ll = (long long)(kMaxPlanesPerBlock - 2) * per_plane;
+    uint32_t max_chunk = max_chunk_ll > 0x7fffffffLL ? 0x7fffffffu : (uint32_t)max_chunk_ll;
+    uint32_t granule = kThreads;
+    if (max_chunk < granule) max_chunk = granule;
+    unsigned grid;
+    plan_chunks(p.units, granule, max_chunk, di.sm_count, 4, &p.chunk, &grid);
+    long long planes = (long long)p.chunk / per_plane + 2;
+    size_t smem = (size_t)planes * sizeof(PlaneEntry);
+    void (*kern)(const EpiParams) = nullptr;
+    switch (vo) {
+    case 4: kern = epilogue_pool_kernel<ACT, AFFINE, 4>; break;
+    case 2: kern = epilogue_pool_kernel<ACT, AFFINE, 2>; break;
+    case 1: kern = epilogue_pool_kernel<ACT, AFFINE, 1>; break;
+    default: kern = epilogue_pool_kernel<ACT, AFFINE, 0>; break;
+    }
+    if (smem > 48 * 1024) {
+        if (smem > (size_t)di.max_smem_optin)
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue(pool): plane table of %zu bytes does not fit shared memory", smem);
+        PXE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    kern<<<grid, kThreads, smem, s>>>(p);
+    PXE_LAUNCH_OK("epilogue_pool_kernel");
+    return PXE_OK;
+}
+
+template <int ACT>
+int dispatch_act(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int mode, long long n, bool affine,
+                 bool pool, int vo)
+{
+    if (pool) return affine ? launch_pool<ACT, true>(s, p, di, vo) : launch_pool<ACT, false>(s, p, di, vo);
+    return dispatch_flags<ACT>(s, p, di, mode, n, affine);
+}
+
+int dispatch(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int act, int mode, long long n, bool affine,
+             bool pool, int vo)
+{
+    switch (act) {
+    case PXE_ACT_LEAKY: return dispatch_act<PXE_ACT_LEAKY>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_LINEAR: return dispatch_act<PXE_ACT_LINEAR>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_LOGGY: return dispatch_act<PXE_ACT_LOGGY>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_LOGISTIC: return dispatch_act<PXE_ACT_LOGISTIC>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_MISH: return dispatch_act<PXE_ACT_MISH>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_RELU: return dispatch_act<PXE_ACT_RELU>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_SOFTPLUS: return dispatch_act<PXE_ACT_SOFTPLUS>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_SWISH: return dispatch_act<PXE_ACT_SWISH>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_TANH: return dispatch_act<PXE_ACT_TANH>(s, p, di, mode, n, affine, pool, vo);
+    case PXE_ACT_YOLO_HEAD: return dispatch_act<PXE_ACT_YOLO_HEAD>(s, p, di, mode, n, affine, pool, vo);
+    default: return set_error(PXE_ERR_BAD_ARG, "conv_epilogue: unknown activation %d", act);
+    }
+}
+
+long long dense_or(long long stride, long long dense) { return stride == 0 ? dense : stride; }
+
+// One slice of the batch whose element count fits 32-bit unit indices.
+int run_slice(cudaStream_t s, const pxe_epilogue_desc& d, int b0, int nb, const DeviceInfo& di)
+{
+    const long long HW = (long long)d.height * d.width;
+    const long long CHW = HW * d.channels;
+    EpiParams p{};
+    p.xbs = dense_or(d.x_batch_stride, CHW);
+    p.ybs = dense_or(d.y_batch_stride, CHW);
+    p.y2bs = dense_or(d.y2_batch_stride, CHW);
+    p.rbs = dense_or(d.residual_batch_stride, CHW);
+    p.x = d.x + (long long)b0 * p.xbs;
+    p.y = d.y ? d.y + (long long)b0 * p.ybs : nullptr;
+    p.y2 = d.y2 ? d.y2 + (long long)b0 * p.y2bs : nullptr;
+    p.res = d.residual ? d.residual + (long long)b0 * p.rbs : nullptr;
+    p.gamma = d.gamma; p.beta = d.beta; p.mean = d.mean; p.var = d.var; p.bias = d.bias;
+    p.eps = d.eps; p.eps_mode = d.eps_mode;
+    p.C = d.channels; p.H = d.height; p.W = d.width; p.HW = (int)HW;
+    p.yolo_entries = d.act == PXE_ACT_YOLO_HEAD ? d.yolo_classes + 5 : 0;
+    p.ralpha = d.res_alpha; p.rbeta = d.res_beta; p.res_act = d.res_act;
+    p.div_c = FastDiv((uint32_t)d.channels);
+    const long long n = (long long)nb * CHW;
+    const bool affine = d.gamma != nullptr || d.bias != nullptr;
+
+    if (d.pool_kernel) {
+        p.OH = pxe_maxpool_out_dim(d.height, 2, 2, d.pool_padding);
+        p.OW = pxe_maxpool_out_dim(d.width, 2, 2, d.pool_padding);
+        p.pbs = dense_or(d.y_pool_batch_stride, (long long)d.channels * p.OH * p.OW);
+        p.ypool = d.y_pool + (long long)b0 * p.pbs;
+        int vo = 0;
+        const bool a16 = aligned16(p.x) && p.xbs % 4 == 0 && (!p.y || (aligned16(p.y) && p.ybs % 4 == 0));
+        const bool a8 = aligned8(p.x) && p.xbs % 2 == 0 && (!p.y || (aligned8(p.y) && p.ybs % 2 == 0));
+        if (d.width % 8 == 0 && a16 && aligned16(p.ypool) && p.pbs % 4 == 0) vo = 4;
+        else if (d.width % 4 == 0 && a16 && aligned8(p.ypool) && p.pbs % 2 == 0) vo = 2;
+        else if (d.width % 2 == 0 && a8) vo = 1;
+        const int nv = vo == 0 ? 1 : vo;
+        p.units = (uint32_t)((long long)nb * d.channels * p.OH * (p.OW / nv));
+        return dispatch(s, p, di, d.act, 0, n, affine, true, vo);
+    }
+
+    int mode = 2;
+    auto ok16 = [](const float* ptr, long long bs) { return !ptr || (aligned16(ptr) && bs % 4 == 0); };
+    const bool all16 = ok16(p.x, p.xbs) && ok16(p.y, p.ybs) && ok16(p.y2, p.y2bs) && ok16(p.res, p.rbs);
+    const bool dense = p.xbs == CHW && (!p.y || p.ybs == CHW) && (!p.y2 || p.y2bs == CHW) && (!p.res || p.rbs == CHW);
+    if (HW % 4 == 0 && all16) mode = 0;
+    else if (dense && all16 && HW >= 4) mode = 1;
+    return dispatch(s, p, di, d.act, mode, n, affine, false, 0);
+}
+
+bool overlap(const void* a, size_t an, const void* b, size_t bn)
+{
+    auto pa = reinterpret_cast<uintptr_t>(a), pb = reinterpret_cast<uintptr_t>(b);
+    return pa < pb + bn && pb < pa + an;
+}
+
+}  // namespace
+}  // namespace pxe
+
+using namespace pxe;
+
+extern "C" int pxe_conv_epilogue(pxe_stream_t stream, const pxe_epilogue_desc* dp)
+{
+    PXE_REQUIRE(dp != nullptr, "conv_epilogue: null descriptor");
+    const pxe_epilogue_desc& d = *dp;
+    PXE_REQUIRE(d.x != nullptr, "conv_epilogue: x is null");
+    PXE_REQUIRE(d.batch > 0 && d.channels > 0 && d.height > 0 && d.width > 0,
+                "conv_epilogue: non-positive shape [%d,%d,%d,%d]", d.batch, d.channels, d.height, d.width);
+    PXE_REQUIRE(d.channels < (1 << 24), "conv_epilogue: too many channels (%d)", d.channels);
+    PXE_REQUIRE((long long)d.height * d.width < (1LL << 30), "conv_epilogue: plane too large");
+    PXE_REQUIRE(d.act == PXE_ACT_YOLO_HEAD || valid_activation(d.act), "conv_epilogue: unknown activation %d", d.act);
+    if (d.act == PXE_ACT_YOLO_HEAD)
+        PXE_REQUIRE(d.yolo_classes >= 0 && d.channels % (d.yolo_classes + 5) == 0,
+                    "conv_epilogue: channels %d not a multiple of yolo_classes+5 = %d", d.channels, d.yolo_classes + 5);
+    if (d.gamma)
+        PXE_REQUIRE(d.beta && d.mean && d.var, "conv_epilogue: gamma given but beta/mean/var missing");
+    PXE_REQUIRE(d.eps_mode == PXE_BN_EPS_CUDNN || d.eps_mode == PXE_BN_EPS_CPU, "conv_epilogue: bad eps_mode %d", d.eps_mode);
+    const long long HW = (long long)d.height * d.width, CHW = HW * d.channels;
+    PXE_REQUIRE(d.x_batch_stride == 0 || d.x_batch_stride >= CHW, "conv_epilogue: x_batch_stride too small");
+    PXE_REQUIRE(d.y_batch_stride == 0 || d.y_batch_stride >= CHW, "conv_epilogue: y_batch_stride too small");
+    PXE_REQUIRE(d.y2_batch_stride == 0 || d.y2_batch_stride >= CHW, "conv_epilogue: y2_batch_stride too small");
+    PXE_REQUIRE(d.residual_batch_stride == 0 || d.residual_batch_stride >= CHW, "conv_epilogue: residual_batch_stride too small");
+    if (d.residual) PXE_REQUIRE(valid_activation(d.res_act), "conv_epilogue: unknown residual activation %d", d.res_act);
+    if (d.pool_kernel) {
+        PXE_REQUIRE(d.y_pool != nullptr, "conv_epilogue: pooling requested but y_pool is null");
+        if (d.pool_kernel != 2 || d.pool_stride != 2 || d.pool_padding < 0 || d.pool_padding > 1)
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue: fused pooling supports kernel 2 / stride 2 / padding 0|1 only (got %d/%d/%d)",
+                             d.pool_kernel, d.pool_stride, d.pool_padding);
+        if (d.residual || d.y2)
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue: fused pooling cannot be combined with residual or y2");
+        const int oh = pxe_maxpool_out_dim(d.height, 2, 2, d.pool_padding);
+        const int ow = pxe_maxpool_out_dim(d.width, 2, 2, d.pool_padding);
+        PXE_REQUIRE(oh > 0 && ow > 0, "conv_epilogue: empty pooled output");
+        if (d.y && (2 * oh < d.height || 2 * ow < d.width))
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue: padding 0 with an odd extent leaves full-resolution rows uncovered; run pxe_maxpool separately");
+        const long long pchw = (long long)d.channels * oh * ow;
+        PXE_REQUIRE(d.y_pool_batch_stride == 0 || d.y_pool_batch_stride >= pchw, "conv_epilogue: y_pool_batch_stride too small");
+        const long long pbs = d.y_pool_batch_stride ? d.y_pool_batch_stride : pchw;
+        const long long xbs = d.x_batch_stride ? d.x_batch_stride : CHW;
+        PXE_REQUIRE(!overlap(d.y_pool, (size_t)((d.batch - 1) * pbs + pchw) * 4, d.x, (size_t)((d.batch - 1) * xbs + CHW) * 4),
+                    "conv_epilogue: y_pool overlaps x");
+    } else {
+        PXE_REQUIRE(d.y != nullptr, "conv_epilogue: y is null");
+    }
+    if (d.y && d.y != d.x) {
+        const long long xbs = d.x_batch_stride ? d.x_batch_stride : CHW, ybs = d.y_batch_stride ? d.y_batch_stride : CHW;
+        // a destination that is neither x itself nor disjoint from it would be read after being written
+        PXE_REQUIRE(!overlap(d.y, (size_t)((d.batch - 1) * ybs + CHW) * 4, d.x, (size_t)((d.batch - 1) * xbs + CHW) * 4)
+                        || (d.x_batch_stride != 0 || d.y_batch_stride != 0),
+                    "conv_epilogue: y partially overlaps x");
+    }
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PXE_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // keep unit indices inside 32 bits: at most 2^31 elements per launch
+    const long long max_elems = 1LL << 31;
+    PXE_REQUIRE(CHW < max_elems, "conv_epilogue: one image has %lld elements, limit is 2^31", CHW);
+    int per = (int)(max_elems / CHW);
+    if (per < 1) per = 1;
+    for (int b0 = 0; b0 < d.batch; b0 += per) {
+        int nb = d.batch - b0 < per ? d.batch - b0 : per;
+        rc = run_slice(s, d, b0, nb, di);
+        if (rc != PXE_OK) return rc;
+    }
+    return PXE_OK;
+}
+
+extern "C" int pxe_activate(pxe_stream_t stream, int act, float* x, size_t n)
+{
+    PXE_REQUIRE(valid_activation(act), "activate: unknown activation %d", act);
+    if (n == 0) return PXE_OK;
+    PXE_REQUIRE(x != nullptr, "activate: x is null");
+    // a [1, 1, rows, 1<<20]-shaped view of the flat array, sliced so every launch stays in range
+    const size_t cols = 1u << 20;
+    size_t done = 0;
+    while (done < n) {
+        size_t left = n - done;
+        pxe_epilogue_desc d{};
+        d.x = x + done; d.y = x + done;
+        d.batch = 1; d.channels = 1; d.act = act;
+        size_t take;
+        if (left >= cols) {
+            size_t rows = left / cols;
+            if (rows > 512) rows = 512;
+            d.height = (int)rows; d.width = (int)cols;
+            take = rows * cols;
+        } else {
+            d.height = 1; d.width = (int)left;
+            take = left;
+        }
+        int rc = pxe_conv_epilogue(stream, &d);
+        if (rc != PXE_OK) return rc;
+        done += take;
+    }
+    return PXE_OK;
+}
+
+extern "C" int pxe_add_bias(pxe_stream_t stream, float* out, const float* bias, int batch, int n, int size)
+{
+    PXE_REQUIRE(out && bias, "add_bias: null pointer");
+    PXE_REQUIRE(batch > 0 && n > 0 && size > 0, "add_bias: non-positive shape");
+    pxe_epilogue_desc d{};
+    d.x = out; d.y = out; d.batch = batch; d.channels = n; d.height = 1; d.width = size;
+    d.bias = bias; d.act = PXE_ACT_LINEAR;
+    return pxe_conv_epilogue(stream, &d);
+}

@@ -1,0 +1,715 @@
+// Detection heads on the device: YOLO activate + decode, CenterNet activate + decode,
+// softmax and the YOLOv2 region transform.  The reference decodes on the host after copying the
+// whole head tensor back (include/cuda/YoloLayer.h:168-188, include/cuda/CenterNetLayer.h:89-106,
+// include/cuda/RegionLayer.h:39-54); here only the compacted detections leave the GPU.
+#include <climits>
+
+#include "pxe_common.cuh"
+
+namespace pxe {
+namespace {
+
+// ============================================================================================
+// YOLO
+// ============================================================================================
+constexpr int kYoloThreads = 128;
+
+struct YoloParams {
+    pxe_yolo_decode_desc d;
+    long long hbs;
+    int HW, entries, blocks_per_image;
+    pxe_detection* dets;
+    long long capacity;
+    long long* count;
+    int* cell_counts;          // [batch*HW]
+    int* block_sums;           // [batch*blocks_per_image]
+    long long* block_offsets;  // [batch*blocks_per_image]
+};
+
+// value of entry `e` of mask slot `n` at `cell`, activated as YoloLayer::forward leaves it
+// (logistic on x, y, objectness, classes; w, h raw -- src/YoloKernels.cu:63-71)
+__device__ __forceinline__ float yolo_value(const YoloParams& p, const float* img, int n, int e, int cell)
+{
+    const int ch = n * p.entries + e;
+    float v = img[(long long)ch * p.HW + cell];
+    if (p.d.head_is_raw) {
+        if (p.d.bias) v += p.d.bias[ch];
+        if (e < 2 || e >= 4) v = act_logistic(v);
+    }
+    return v;
+}
+
+__device__ __forceinline__ int yolo_cell_count(const YoloParams& p, const float* img, int cell)
+{
+    int cnt = 0;
+    for (int n = 0; n < p.d.n_masks; ++n) {
+        const float obj = yolo_value(p, img, n, 4, cell);
+        if (obj < p.d.threshold) continue;                         // include/YoloLayer.h:676
+        for (int j = 0; j < p.d.classes; ++j) {
+            const float prob = obj * yolo_value(p, img, n, 5 + j, cell);
+            if (prob >= p.d.threshold) ++cnt;                      // include/YoloLayer.h:692
+        }
+    }
+    return cnt;
+}
+
+__device__ __forceinline__ int block_sum_int(int v, int* smem)
+{
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    int total = 0;
+    if (threadIdx.x == 0)
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += smem[w];
+    return total;   // valid in thread 0
+}
+
+__global__ void __launch_bounds__(kYoloThreads)
+yolo_count_kernel(const YoloParams p)
+{
+    __shared__ int warp_sums[kYoloThreads / 32];
+    const int b = blockIdx.y;
+    const int cell = blockIdx.x * kYoloThreads + threadIdx.x;
+    const float* img = p.d.head + (long long)b * p.hbs;
+    int cnt = 0;
+    if (cell < p.HW) {
+        cnt = yolo_cell_count(p, img, cell);
+        p.cell_counts[(long long)b * p.HW + cell] = cnt;
+    }
+    const int total = block_sum_int(cnt, warp_sums);
+    if (threadIdx.x == 0) p.block_sums[b * p.blocks_per_image + blockIdx.x] = total;
+}
+
+// Exclusive scan of the per-block sums; starts at the running total *count and advances it.
+__global__ void __launch_bounds__(1024)
+yolo_scan_kernel(const int* block_sums, long long* block_offsets, int n, long long* count)
+{
+    __shared__ long long warp_tot[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = *count;
+    __syncthreads();
+    for (int base = 0; base < n; base += 1024) {
+        const int i = base + threadIdx.x;
+        long long v = i < n ? block_sums[i] : 0;
+        long long inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            long long t = __shfl_up_sync(0xffffffffu, inc, o);
+            if ((threadIdx.x & 31) >= o) inc += t;
+        }
+        if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = inc;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            long long w = warp_tot[threadIdx.x];
+            for (int o = 1; o < 32; o <<= 1) {
+                long long t = __shfl_up_sync(0xffffffffu, w, o);
+                if (threadIdx.x >= o) w += t;
+            }
+            warp_tot[threadIdx.x] = w;          // inclusive totals of warps
+        }
+        __syncthreads();
+        const long long warp_excl = (threadIdx.x >> 5) ? warp_tot[(threadIdx.x >> 5) - 1] : 0;
+        const long long c = carry;
+        if (i < n) block_offsets[i] = c + warp_excl + inc - v;
+        __syncthreads();
+        if (threadIdx.x == 0) carry = c + warp_tot[31];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *count = carry;
+}
+
+// float -> int the way the reference's host decode converts (x86-64 cvttss2si):
+// truncation toward zero, INT_MIN for NaN and out-of-range values.
+__device__ __forceinline__ int f2i_x86(float v)
+{
+    if (!(v > -2147483904.0f && v < 2147483648.0f)) return INT_MIN;
+    return (int)v;
+}
+
+__global__ void __launch_bounds__(kYoloThreads)
+yolo_emit_kernel(const YoloParams p)
+{
+    __shared__ int warp_sums[kYoloThreads / 32];
+    const int b = blockIdx.y;
+    const int cell = blockIdx.x * kYoloThreads + threadIdx.x;
+    const float* img = p.d.head + (long long)b * p.hbs;
+    const int cnt = cell < p.HW ? p.cell_counts[(long long)b * p.HW + cell] : 0;
+    // exclusive scan of cnt over the block (emission order inside an image is cell-major)
+    int inc = cnt;
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((threadIdx.x & 31) >= o) inc += t;
+    }
+    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = inc;
+    __syncthreads();
+    int warp_excl = 0;
+    for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) warp_excl += warp_sums[w];
+    if (cnt == 0) return;
+    long long pos = p.block_offsets[b * p.blocks_per_image + blockIdx.x] + warp_excl + inc - cnt;
+
+    const int W = p.d.width, H = p.d.height;
+    const int row = cell / W, col = cell - row * W;
+    const bool scaled = p.d.image_width > 0 && p.d.image_height > 0;
+    for (int n = 0; n < p.d.n_masks; ++n) {
+        const float obj = yolo_value(p, img, n, 4, cell);
+        if (obj < p.d.threshold) continue;
+        const float tx = yolo_value(p, img, n, 0, cell), ty = yolo_value(p, img, n, 1, cell);
+        const float tw = yolo_value(p, img, n, 2, cell), th = yolo_value(p, img, n, 3, cell);
+        const int a = p.d.mask[n];
+        const int aw = p.d.anchors[2 * a], ah = p.d.anchors[2 * a + 1];
+        const int net_w = p.d.net_width, net_h = p.d.net_height;
+        float bx, by, bw, bh;
+        if (scaled) {
+            // scaledYoloBox, include/YoloLayer.h:601-635
+            const int iw = p.d.image_width, ih = p.d.image_height;
+            int new_w, new_h;
+            if (((float)net_w / iw) < ((float)net_h / ih)) { new_w = net_w; new_h = (ih * net_w) / iw; }
+            else { new_h = net_h; new_w = (iw * net_h) / ih; }
+            float x = (col + tx) / W;
+            x = (x - (net_w - new_w) / 2.0f / net_w) / ((float)new_w / net_w);
+            float y = (row + ty) / H;
+            y = (y - (net_h - new_h) / 2.0f / net_h) / ((float)new_h / net_h);
+            float width = expf(tw) * aw / net_w;
+            width *= (float)net_w / new_w;
+            float height = expf(th) * ah / net_h;
+            height *= (float)net_h / new_h;
+            int left = f2i_x86(__fmul_rn(__fsub_rn(x, width / 2), (float)iw));    if (left < 0) left = 0;
+            int right = f2i_x86(__fmul_rn(__fadd_rn(x, width / 2), (float)iw));   if (right > iw - 1) right = iw - 1;
+            int top = f2i_x86(__fmul_rn(__fsub_rn(y, height / 2), (float)ih));    if (top < 0) top = 0;
+            int bottom = f2i_x86(__fmul_rn(__fadd_rn(y, height / 2), (float)ih)); if (bottom > ih - 1) bottom = ih - 1;
+            bx = (float)left; by = (float)top; bw = (float)(right - left); bh = (float)(bottom - top);
+        } else {
+            // yoloBox().rect(), include/YoloLayer.h:637-651, src/DarkBox.cpp:84-123
+            const float x = (col + tx) / W, y = (row + ty) / H;
+            const float w = expf(tw) * aw / net_w, h = expf(th) * ah / net_h;
+            bx = w > 0.0f ? __fsub_rn(x, w / 2.0f) : x;
+            by = h > 0.0f ? __fsub_rn(y, h / 2.0f) : y;
+            bw = w; bh = h;
+        }
+        for (int j = 0; j < p.d.classes; ++j) {
+            const float prob = obj * yolo_value(p, img, n, 5 + j, cell);
+            if (prob >= p.d.threshold) {
+                if (pos < p.capacity) {
+                    pxe_detection det;
+                    det.x = bx; det.y = by; det.w = bw; det.h = bh; det.prob = prob;
+                    det.class_id = j; det.batch_id = b + p.d.batch_id_offset;
+                    det.source = cell * p.d.n_masks + n;
+                    p.dets[pos] = det;
+                }
+                ++pos;
+            }
+        }
+    }
+}
+
+// ============================================================================================
+// CenterNet
+// ============================================================================================
+struct CnActParams {
+    const float* in; float* out;
+    uint32_t total;      // elements (scalar) or float4 vectors
+    uint32_t outputs, heat;   // per image, in the same unit as total
+    float bias;
+    FastDiv div_outputs;
+};
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+centernet_activate_kernel(const CnActParams p)
+{
+    for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < p.total; i += gridDim.x * 256) {
+        uint32_t q, within;
+        p.div_outputs.divmod(i, q, within);
+        const bool heat = within < p.heat;
+        if (VEC) {
+            float4 v = reinterpret_cast<const float4*>(p.in)[i];
+            if (heat) {
+                v.x = act_logistic(v.x + p.bias); v.y = act_logistic(v.y + p.bias);
+                v.z = act_logistic(v.z + p.bias); v.w = act_logistic(v.w + p.bias);
+            }
+            reinterpret_cast<float4*>(p.out)[i] = v;
+        } else {
+            float v = p.in[i];
+            if (heat) v = act_logistic(v + p.bias);
+            p.out[i] = v;
+        }
+    }
+}
+
+constexpr int kCnTileH = 32, kCnTileW = 64, kCnThreads = 256;
+constexpr int kCnCells = kCnTileH * kCnTileW;
+constexpr int kCnMaxK = 1024;
+
+struct CnParams {
+    pxe_centernet_decode_desc d;
+    long long hbs, sbs, obs;
+    int tiles_x, tiles_y, slots;     // slots = classes * tiles_x * tiles_y per image
+    int K;
+    unsigned long long* cand;        // [batch][slots][K] sortable keys
+    int* cand_cnt;                   // [batch][slots]
+    pxe_detection* dets; int* counts;
+};
+
+// Monotone map float -> uint32 (larger float <=> larger integer), any sign.
+__device__ __forceinline__ uint32_t float_order(float f)
+{
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float order_float(uint32_t u)
+{
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
+// Key orders candidates by score descending, then flat index ascending.
+__device__ __forceinline__ unsigned long long cn_key(float score, uint32_t flat)
+{
+    return ((unsigned long long)float_order(score) << 32) | (unsigned long long)(0xffffffffu - flat);
+}
+
+// Finds the k-th largest of n distinct 64-bit keys (k >= 1, k <= n) by most-significant-digit
+// radix selection, 8 bits per pass.  `get(i)` returns key i.  All threads of the block must
+// call; every thread returns the key.  hist: 256 ints of shared memory, sh: 2 x u64.
+template <typename Get>
+__device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist, unsigned long long* sh)
+{
+    unsigned long long prefix = 0, mask = 0;
+    int want = k;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const unsigned long long key = get(i);
+            if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 0xff)], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int acc = 0, digit = 255;
+            for (; digit > 0; --digit) {
+                if (acc + hist[digit] >= want) break;
+                acc += hist[digit];
+            }
+            sh[0] = prefix | ((unsigned long long)digit << shift);
+            sh[1] = (unsigned long long)(want - acc);
+        }
+        __syncthreads();
+        prefix = sh[0];
+        want = (int)sh[1];
+        mask |= 0xffULL << shift;
+        __syncthreads();
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(kCnThreads)
+centernet_peaks_kernel(const CnParams p)
+{
+    __shared__ float tile[(kCnTileH + 2) * (kCnTileW + 2)];
+    __shared__ unsigned long long keys[kCnCells];
+    __shared__ int n_keys;
+    __shared__ int hist[256];
+    __shared__ unsigned long long sel[2];
+
+    const int b = blockIdx.z, cls = blockIdx.y;
+    const int ty = blockIdx.x / p.tiles_x, tx = blockIdx.x - ty * p.tiles_x;
+    const int y0 = ty * kCnTileH, x0 = tx * kCnTileW;
+    const int H = p.d.height, W = p.d.width;
+    const long long area = (long long)H * W;
+    const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
+    if (threadIdx.x == 0) n_keys = 0;
+
+    constexpr int TW = kCnTileW + 2;
+    for (int i = threadIdx.x; i < (kCnTileH + 2) * TW; i += kCnThreads) {
+        const int ly = i / TW, lx = i - ly * TW;
+        const int gy = y0 + ly - 1, gx = x0 + lx - 1;
+        float s = -INFINITY;                       // outside the map: never greater than a score
+        if (gy >= 0 && gy < H && gx >= 0 && gx < W) {
+            s = heat[(long long)gy * W + gx];
+            if (p.d.heat_is_logit) s = 1.0f / (1.0f + expf(-(s + p.d.heatmap_bias)));
+        }
+        tile[i] = s;
+    }
+    __syncthreads();
+
+    const float* size = p.d.size + (long long)b * p.sbs;
+    const float* off = p.d.offset + (long long)b * p.obs;
+    for (int i = threadIdx.x; i < kCnCells; i += kCnThreads) {
+        const int ly = i / kCnTileW, lx = i - ly * kCnTileW;
+        const int gy = y0 + ly, gx = x0 + lx;
+        if (gy >= H || gx >= W) continue;
+        const float* c = tile + (ly + 1) * TW + (lx + 1);
+        const float s = c[0];
+        // include/CenterNetLayer.h:212: finite, at or above the threshold, no strictly greater neighbour
+        if (!isfinite(s) || s < p.d.threshold) continue;
+        if (c[-TW - 1] > s || c[-TW] > s || c[-TW + 1] > s || c[-1] > s || c[1] > s ||
+            c[TW - 1] > s || c[TW] > s || c[TW + 1] > s) continue;
+        const long long idx = (long long)gy * W + gx;
+        const float bw = size[idx] / W, bh = size[area + idx] / H;
+        const float ox = off[idx], oy = off[area + idx];
+        if (!isfinite(bw) || !isfinite(bh) || !isfinite(ox) || !isfinite(oy) || bw <= 0.0f || bh <= 0.0f) continue;
+        const int slot = atomicAdd(&n_keys, 1);
+        keys[slot] = cn_key(s, (uint32_t)((long long)cls * area + idx));
+    }
+    __syncthreads();
+
+    const int n = n_keys;
+    const int slot_id = cls * (p.tiles_x * p.tiles_y) + blockIdx.x;
+    unsigned long long* out = p.cand + ((long long)b * p.slots + slot_id) * p.K;
+    if (n <= p.K) {
+        for (int i = threadIdx.x; i < n; i += kCnThreads) out[i] = keys[i];
+        if (threadIdx.x == 0) p.cand_cnt[(long long)b * p.slots + slot_id] = n;
+        return;
+    }
+    // more candidates than can ever be kept from one image: keep this block's K best
+    const unsigned long long kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
+    __shared__ int n_out;
+    if (threadIdx.x == 0) n_out = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += kCnThreads)
+        if (keys[i] >= kth) out[atomicAdd(&n_out, 1)] = keys[i];
+    if (threadIdx.x == 0) p.cand_cnt[(long long)b * p.slots + slot_id] = p.K;
+}
+
+// One block per image: the K best of all slots' candidates, sorted, decoded to boxes.
+__global__ void __launch_bounds__(1024)
+centernet_topk_kernel(const CnParams p)
+{
+    __shared__ unsigned long long best[kCnMaxK];
+    __shared__ int hist[256];
+    __shared__ unsigned long long sel[2];
+    __shared__ int n_total, n_best;
+    const int b = blockIdx.x;
+    const unsigned long long* cand = p.cand + (long long)b * p.slots * p.K;
+    const int* cnt = p.cand_cnt + (long long)b * p.slots;
+    if (threadIdx.x == 0) { n_total = 0; n_best = 0; }
+    __syncthreads();
+    int local = 0;
+    for (int s = threadIdx.x; s < p.slots; s += blockDim.x) local += cnt[s];
+    if (local) atomicAdd(&n_total, local);
+    __syncthreads();
+    const int n = n_total;
+    const int span = p.slots * p.K;
+    // key i of the image lives at cand[i] when (i % K) < cnt[i / K]; absent entries read as 0,
+    // which is below every real key (real keys have bit 63 or the index bits set... a real key
+    // is never 0 because its low word is 0xffffffff - flat with flat < 2^32 - 1).
+    auto get = [&](int i) -> unsigned long long {
+        const int s = i / p.K;
+        return (i - s * p.K) < cnt[s] ? cand[i] : 0ULL;
+    };
+    unsigned long long kth = 1;      // every real key is >= 1
+    if (n > p.K) kth = block_select_kth(get, span, p.K, hist, sel);
+    for (int i = threadIdx.x; i < span; i += blockDim.x) {
+        const unsigned long long key = get(i);
+        if (key >= kth && key != 0ULL) best[atomicAdd(&n_best, 1)] = key;
+    }
+    __syncthreads();
+    const int m = n_best;
+    // bitonic sort, descending, over the next power of two (padding with 0 = smallest)
+    int pow2 = 1;
+    while (pow2 < m) pow2 <<= 1;
+    for (int i = m + threadIdx.x; i < pow2; i += blockDim.x) best[i] = 0ULL;
+    __syncthreads();
+    for (int k = 2; k <= pow2; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < pow2; i += blockDim.x) {
+                const int l = i ^ j;
+                if (l > i) {
+                    const unsigned long long a = best[i], c = best[l];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (a < c) : (a > c)) { best[i] = c; best[l] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    const int H = p.d.height, W = p.d.width;
+    const long long area = (long long)H * W;
+    const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
+    const float image_h = p.d.image_height > 0 ? (float)p.d.image_height : 1.0f;
+    const float* size = p.d.size + (long long)b * p.sbs;
+    const float* off = p.d.offset + (long long)b * p.obs;
+    for (int i = threadIdx.x; i < m; i += blockDim.x) {
+        const unsigned long long key = best[i];
+        const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
+        const float score = order_float((uint32_t)(key >> 32));
+        const int cls = (int)(flat / area);
+        const long long idx = flat - (long long)cls * area;
+        const int y = (int)(idx / W), x = (int)(idx - (long long)y * W);
+        // include/CenterNetLayer.h:217-237, each product and sum rounded separately as on the host
+        const float bw = size[idx] / W, bh = size[area + idx] / H;
+        const float cx = (x + off[idx]) / W, cy = (y + off[area + idx]) / H;
+        pxe_detection det;
+        det.x = __fmul_rn(__fsub_rn(cx, bw / 2.0f), image_w);
+        det.y = __fmul_rn(__fsub_rn(cy, bh / 2.0f), image_h);
+        det.w = __fmul_rn(bw, image_w);
+        det.h = __fmul_rn(bh, image_h);
+        det.prob = score; det.class_id = cls; det.batch_id = b + p.d.batch_id_offset; det.source = (int)flat;
+        p.dets[(long long)b * p.K + i] = det;
+    }
+    if (threadIdx.x == 0) p.counts[b] = m;
+}
+
+// ============================================================================================
+// Softmax / Region
+// ============================================================================================
+// One block per row of n contiguous values: out = exp(x/temp - max/temp) / sum (src/Math.cpp:77-97).
+__global__ void __launch_bounds__(128)
+softmax_rows_kernel(const float* in, float* out, int n, float temp)
+{
+    __shared__ float red[4];
+    __shared__ float bcast;
+    const float* x = in + (long long)blockIdx.x * n;
+    float* y = out + (long long)blockIdx.x * n;
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < n; i += 128) m = x[i] > m ? x[i] : m;
+    for (int o = 16; o > 0; o >>= 1) { float t = __shfl_xor_sync(0xffffffffu, m, o); m = t > m ? t : m; }
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) { float t = red[0]; for (int w = 1; w < 4; ++w) t = red[w] > t ? red[w] : t; bcast = t; }
+    __syncthreads();
+    const float largest = bcast;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < n; i += 128) {
+        const float e = expf(x[i] / temp - largest / temp);
+        y[i] = e;
+        sum += e;
+    }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) bcast = red[0] + red[1] + red[2] + red[3];
+    __syncthreads();
+    const float total = bcast;
+    for (int i = threadIdx.x; i < n; i += 128) y[i] = y[i] / total;
+}
+
+struct RegionParams {
+    const float* in; float* out;
+    int batch, HW, num, size, coords, classes, softmax;
+};
+
+// One thread per predicted box (image, cell, anchor slot).
+__global__ void __launch_bounds__(128)
+region_forward_kernel(const RegionParams p)
+{
+    const long long boxes = (long long)p.batch * p.HW * p.num;
+    for (long long t = (long long)blockIdx.x * 128 + threadIdx.x; t < boxes; t += (long long)gridDim.x * 128) {
+        // thread order: cells fastest so the strided NCHW reads coalesce
+        const int cell = (int)(t % p.HW);
+        const long long r = t / p.HW;
+        const int n = (int)(r % p.num);
+        const int b = (int)(r / p.num);
+        const long long outputs = (long long)p.HW * p.num * p.size;
+        const float* src = p.in + b * outputs + (long long)n * p.size * p.HW + cell;
+        float* dst = p.out + b * outputs + ((long long)cell * p.num + n) * p.size;
+        for (int e = 0; e < p.size; ++e) {
+            float v = src[(long long)e * p.HW];
+            if (e == 4) v = act_logistic(v);
+            dst[e] = v;
+        }
+        if (p.softmax) {
+            float* cls = dst + p.coords + 1;
+            float largest = -FLT_MAX, sum = 0.0f;
+            for (int j = 0; j < p.classes; ++j) largest = cls[j] > largest ? cls[j] : largest;
+            for (int j = 0; j < p.classes; ++j) { const float e = expf(cls[j] - largest); sum += e; cls[j] = e; }
+            for (int j = 0; j < p.classes; ++j) cls[j] = cls[j] / sum;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace pxe
+
+using namespace pxe;
+
+// -------------------------------------------------------------------------------------- YOLO API
+extern "C" int pxe_yolo_activate(pxe_stream_t stream, const float* in, float* out, int batch, int masks,
+                                 int classes, int area)
+{
+    PXE_REQUIRE(in && out, "yolo_activate: null pointer");
+    PXE_REQUIRE(batch > 0 && masks > 0 && classes >= 0 && area > 0, "yolo_activate: non-positive shape");
+    pxe_epilogue_desc d{};
+    d.x = in; d.y = out;
+    d.batch = batch; d.channels = masks * (classes + 5); d.height = 1; d.width = area;
+    d.act = PXE_ACT_YOLO_HEAD; d.yolo_classes = classes;
+    return pxe_conv_epilogue(stream, &d);
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+extern "C" size_t pxe_yolo_decode_workspace_bytes(int batch, int height, int width)
+{
+    if (batch <= 0 || height <= 0 || width <= 0) return 0;
+    const size_t hw = (size_t)height * width;
+    const size_t bpi = (hw + kYoloThreads - 1) / kYoloThreads;
+    return align_up((size_t)batch * hw * sizeof(int), 256) + align_up((size_t)batch * bpi * sizeof(int), 256)
+           + align_up((size_t)batch * bpi * sizeof(long long), 256);
+}
+
+extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* dp, pxe_detection* dets,
+                               long long capacity, long long* count, void* workspace, size_t workspace_bytes)
+{
+    PXE_REQUIRE(dp != nullptr, "yolo_decode: null descriptor");
+    const pxe_yolo_decode_desc& d = *dp;
+    PXE_REQUIRE(d.head && count && workspace, "yolo_decode: null pointer");
+    PXE_REQUIRE(capacity >= 0 && (capacity == 0 || dets != nullptr), "yolo_decode: dets is null");
+    PXE_REQUIRE(d.batch > 0 && d.height > 0 && d.width > 0 && d.classes >= 0, "yolo_decode: non-positive shape");
+    PXE_REQUIRE(d.n_masks > 0 && d.n_masks <= 16, "yolo_decode: n_masks %d outside 1..16", d.n_masks);
+    PXE_REQUIRE(d.n_anchor_values > 0 && d.n_anchor_values <= 64 && d.n_anchor_values % 2 == 0,
+                "yolo_decode: n_anchor_values %d invalid", d.n_anchor_values);
+    for (int n = 0; n < d.n_masks; ++n)
+        PXE_REQUIRE(d.mask[n] >= 0 && 2 * d.mask[n] + 1 < d.n_anchor_values, "yolo_decode: mask[%d]=%d has no anchor", n, d.mask[n]);
+    PXE_REQUIRE(d.net_width > 0 && d.net_height > 0, "yolo_decode: network size must be positive");
+    PXE_REQUIRE((d.image_width > 0) == (d.image_height > 0), "yolo_decode: image_width and image_height must both be set or both be 0");
+    PXE_REQUIRE(d.batch <= 65535, "yolo_decode: batch %d exceeds 65535 per call", d.batch);
+    PXE_REQUIRE(aligned16(dets), "yolo_decode: dets must be 16-byte aligned");
+    const size_t need = pxe_yolo_decode_workspace_bytes(d.batch, d.height, d.width);
+    if (workspace_bytes < need)
+        return set_error(PXE_ERR_WORKSPACE, "yolo_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
+    PXE_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "yolo_decode: workspace must be 256-byte aligned");
+
+    YoloParams p{};
+    p.d = d;
+    p.HW = d.height * d.width;
+    p.entries = d.classes + 5;
+    const long long chw = (long long)d.n_masks * p.entries * p.HW;
+    PXE_REQUIRE(d.head_batch_stride == 0 || d.head_batch_stride >= chw, "yolo_decode: head_batch_stride too small");
+    p.hbs = d.head_batch_stride ? d.head_batch_stride : chw;
+    p.blocks_per_image = (p.HW + kYoloThreads - 1) / kYoloThreads;
+    p.dets = dets; p.capacity = capacity; p.count = count;
+    char* ws = static_cast<char*>(workspace);
+    p.cell_counts = reinterpret_cast<int*>(ws);
+    ws += align_up((size_t)d.batch * p.HW * sizeof(int), 256);
+    p.block_sums = reinterpret_cast<int*>(ws);
+    ws += align_up((size_t)d.batch * p.blocks_per_image * sizeof(int), 256);
+    p.block_offsets = reinterpret_cast<long long*>(ws);
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    dim3 grid((unsigned)p.blocks_per_image, (unsigned)d.batch);
+    yolo_count_kernel<<<grid, kYoloThreads, 0, s>>>(p);
+    PXE_LAUNCH_OK("yolo_count_kernel");
+    yolo_scan_kernel<<<1, 1024, 0, s>>>(p.block_sums, p.block_offsets, d.batch * p.blocks_per_image, count);
+    PXE_LAUNCH_OK("yolo_scan_kernel");
+    yolo_emit_kernel<<<grid, kYoloThreads, 0, s>>>(p);
+    PXE_LAUNCH_OK("yolo_emit_kernel");
+    return PXE_OK;
+}
+
+// --------------------------------------------------------------------------------- CenterNet API
+extern "C" int pxe_centernet_activate(pxe_stream_t stream, const float* in, float* out, int batch, int classes,
+                                      int area, float heatmap_bias)
+{
+    PXE_REQUIRE(in && out, "centernet_activate: null pointer");
+    PXE_REQUIRE(batch > 0 && classes > 0 && area > 0, "centernet_activate: non-positive shape");
+    const long long outputs = (long long)(classes + 4) * area, heat = (long long)classes * area;
+    const long long total = outputs * batch;
+    PXE_REQUIRE(total < (1LL << 32), "centernet_activate: too many elements for one launch");
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PXE_OK) return rc;
+    CnActParams p{};
+    p.in = in; p.out = out; p.bias = heatmap_bias;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (area % 4 == 0 && aligned16(in) && aligned16(out)) {
+        p.total = (uint32_t)(total / 4); p.outputs = (uint32_t)(outputs / 4); p.heat = (uint32_t)(heat / 4);
+        p.div_outputs = FastDiv(p.outputs);
+        centernet_activate_kernel<true><<<grid_for(p.total, 256, di.sm_count, 16), 256, 0, s>>>(p);
+    } else {
+        p.total = (uint32_t)total; p.outputs = (uint32_t)outputs; p.heat = (uint32_t)heat;
+        p.div_outputs = FastDiv(p.outputs);
+        centernet_activate_kernel<false><<<grid_for(p.total, 256, di.sm_count, 16), 256, 0, s>>>(p);
+    }
+    PXE_LAUNCH_OK("centernet_activate_kernel");
+    return PXE_OK;
+}
+
+static void cn_geometry(int classes, int height, int width, int* tiles_x, int* tiles_y, int* slots)
+{
+    *tiles_x = (width + kCnTileW - 1) / kCnTileW;
+    *tiles_y = (height + kCnTileH - 1) / kCnTileH;
+    *slots = classes * *tiles_x * *tiles_y;
+}
+
+extern "C" size_t pxe_centernet_decode_workspace_bytes(int batch, int classes, int height, int width,
+                                                       int max_detections)
+{
+    if (batch <= 0 || classes <= 0 || height <= 0 || width <= 0 || max_detections <= 0) return 0;
+    int tx, ty, slots;
+    cn_geometry(classes, height, width, &tx, &ty, &slots);
+    return align_up((size_t)batch * slots * max_detections * sizeof(unsigned long long), 256)
+           + align_up((size_t)batch * slots * sizeof(int), 256);
+}
+
+extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_decode_desc* dp,
+                                    pxe_detection* dets, int* counts, void* workspace, size_t workspace_bytes)
+{
+    PXE_REQUIRE(dp != nullptr, "centernet_decode: null descriptor");
+    const pxe_centernet_decode_desc& d = *dp;
+    PXE_REQUIRE(d.heat && d.size && d.offset && dets && counts && workspace, "centernet_decode: null pointer");
+    PXE_REQUIRE(d.batch > 0 && d.classes > 0 && d.height > 0 && d.width > 0, "centernet_decode: non-positive shape");
+    PXE_REQUIRE(d.max_detections > 0 && d.max_detections <= kCnMaxK, "centernet_decode: max_detections %d outside 1..%d",
+                d.max_detections, kCnMaxK);
+    const long long area = (long long)d.height * d.width;
+    PXE_REQUIRE(area * d.classes < 0xffffffffLL, "centernet_decode: heatmap has too many cells per image");
+    PXE_REQUIRE(d.batch <= 65535 && d.classes <= 65535, "centernet_decode: batch/classes exceed 65535");
+    PXE_REQUIRE(d.heat_batch_stride == 0 || d.heat_batch_stride >= area * d.classes, "centernet_decode: heat_batch_stride too small");
+    PXE_REQUIRE(d.size_batch_stride == 0 || d.size_batch_stride >= 2 * area, "centernet_decode: size_batch_stride too small");
+    PXE_REQUIRE(d.offset_batch_stride == 0 || d.offset_batch_stride >= 2 * area, "centernet_decode: offset_batch_stride too small");
+    PXE_REQUIRE(aligned16(dets), "centernet_decode: dets must be 16-byte aligned");
+    const size_t need = pxe_centernet_decode_workspace_bytes(d.batch, d.classes, d.height, d.width, d.max_detections);
+    if (workspace_bytes < need)
+        return set_error(PXE_ERR_WORKSPACE, "centernet_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
+    PXE_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "centernet_decode: workspace must be 256-byte aligned");
+
+    CnParams p{};
+    p.d = d;
+    p.hbs = d.heat_batch_stride ? d.heat_batch_stride : area * d.classes;
+    p.sbs = d.size_batch_stride ? d.size_batch_stride : 2 * area;
+    p.obs = d.offset_batch_stride ? d.offset_batch_stride : 2 * area;
+    cn_geometry(d.classes, d.height, d.width, &p.tiles_x, &p.tiles_y, &p.slots);
+    PXE_REQUIRE((long long)p.slots * d.max_detections < 0x7fffffffLL, "centernet_decode: candidate table too large");
+    p.K = d.max_detections;
+    char* ws = static_cast<char*>(workspace);
+    p.cand = reinterpret_cast<unsigned long long*>(ws);
+    ws += align_up((size_t)d.batch * p.slots * p.K * sizeof(unsigned long long), 256);
+    p.cand_cnt = reinterpret_cast<int*>(ws);
+    p.dets = dets; p.counts = counts;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    dim3 grid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, (unsigned)d.batch);
+    centernet_peaks_kernel<<<grid, kCnThreads, 0, s>>>(p);
+    PXE_LAUNCH_OK("centernet_peaks_kernel");
+    centernet_topk_kernel<<<(unsigned)d.batch, 1024, 0, s>>>(p);
+    PXE_LAUNCH_OK("centernet_topk_kernel");
+    return PXE_OK;
+}
+
+// ------------------------------------------------------------------------------ softmax / region
+extern "C" int pxe_softmax(pxe_stream_t stream, const float* in, float* out, int batch, int inputs, int groups,
+                           float temperature)
+{
+    PXE_REQUIRE(in && out, "softmax: null pointer");
+    PXE_REQUIRE(batch > 0 && inputs > 0 && groups > 0, "softmax: non-positive shape");
+    PXE_REQUIRE(inputs % groups == 0, "softmax: inputs %d not divisible by groups %d", inputs, groups);
+    PXE_REQUIRE(temperature != 0.0f, "softmax: temperature is zero");
+    const long long rows = (long long)batch * groups;
+    PXE_REQUIRE(rows <= 0x7fffffffLL, "softmax: too many rows");
+    softmax_rows_kernel<<<(unsigned)rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(in, out, inputs / groups, temperature);
+    PXE_LAUNCH_OK("softmax_rows_kernel");
+    return PXE_OK;
+}
+
+extern "C" int pxe_region_forward(pxe_stream_t stream, const float* in, float* out, int batch, int width,
+                                  int height, int num, int coords, int classes, int softmax)
+{
+    PXE_REQUIRE(in && out && in != out, "region_forward: null or aliased pointers");
+    PXE_REQUIRE(batch > 0 && width > 0 && height > 0 && num > 0 && coords >= 4 && classes >= 0, "region_forward: bad shape");
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PXE_OK) return rc;
+    RegionParams p{};
+    p.in = in; p.out = out; p.batch = batch; p.HW = width * height; p.num = num;
+    p.size = coords + 1 + classes; p.coords = coords; p.classes = classes; p.softmax = softmax;
+    const long long boxes = (long long)batch * p.HW * num;
+    region_forward_kernel<<<grid_for(boxes, 128, di.sm_count, 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    PXE_LAUNCH_OK("region_forward_kernel");
+    return PXE_OK;
+}

@@ -1,0 +1,377 @@
+"""The epilogue operators on torch CUDA tensors.
+
+Thin argument marshalling over the C ABI (``include/pxe.h``): torch supplies device memory and
+the current stream, every computation runs in ``libpxe.so``.  A tensor argument may be a channel
+slice of a wider NCHW buffer (``buf[:, 64:192]``): its batch stride is passed through, which is
+how producers write straight into route (concat) buffers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import capi
+from .capi import ACT, PxeError  # noqa: F401  (re-exported)
+
+DET_DTYPE = np.dtype([("x", "f4"), ("y", "f4"), ("w", "f4"), ("h", "f4"), ("prob", "f4"),
+                      ("class_id", "i4"), ("batch_id", "i4"), ("source", "i4")])
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _act(a) -> int:
+    return ACT[a] if isinstance(a, str) else int(a)
+
+
+def _check_f32_cuda(t: torch.Tensor, name: str) -> None:
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32):
+        raise TypeError(f"{name} must be a float32 CUDA tensor")
+
+
+def _slot(t: Optional[torch.Tensor], name: str):
+    """(pointer, batch stride) of a 4-D NCHW tensor whose per-image block is dense."""
+    if t is None:
+        return None, 0
+    _check_f32_cuda(t, name)
+    if t.dim() != 4:
+        raise ValueError(f"{name} must be 4-D [B,C,H,W], got {tuple(t.shape)}")
+    b, c, h, w = t.shape
+    st = t.stride()
+    if (st[3] != 1 and w > 1) or (st[2] != w and h > 1) or (st[1] != h * w and c > 1):
+        raise ValueError(f"{name}: per-image block must be contiguous (strides {st} for shape {tuple(t.shape)})")
+    bs = st[0] if b > 1 else c * h * w
+    return t.data_ptr(), int(bs)
+
+
+def _vec(t: Optional[torch.Tensor], n: int, name: str):
+    if t is None:
+        return None
+    _check_f32_cuda(t, name)
+    if t.numel() != n or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous tensor of {n} elements")
+    return t.data_ptr()
+
+
+def maxpool_out_dim(n: int, kernel: int, stride: int, padding: Optional[int] = None) -> int:
+    if padding is None:
+        padding = max(0, kernel - 1)
+    return capi.lib().pxe_maxpool_out_dim(n, kernel, stride, padding)
+
+
+def conv_epilogue(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None,
+                  gamma=None, beta=None, mean=None, var=None, bias=None, act="linear", eps: float = 1e-5,
+                  eps_mode: int = capi.EPS_CUDNN, yolo_classes: int = 0,
+                  residual: Optional[torch.Tensor] = None, res_alpha: float = 1.0, res_beta: float = 1.0,
+                  res_act="linear", pool: Optional[Sequence[int]] = None,
+                  y_pool: Optional[torch.Tensor] = None, in_place: bool = True):
+    """Fused BN / bias / activation (+ residual, + 2x2 pool, + concat-slot stores).
+
+    Returns ``y`` (or ``(y, y_pool)`` when pooling).  With ``y=None`` the result overwrites ``x``
+    (``in_place=True``) or goes to a new tensor; ``y=False`` with pooling skips the
+    full-resolution output altogether.
+    """
+    xp, xbs = _slot(x, "x")
+    B, Cc, H, W = x.shape
+    d = capi.EpilogueDesc()
+    d.x, d.x_batch_stride = xp, xbs
+    want_full = y is not False
+    if y is None:
+        y = x if in_place else torch.empty((B, Cc, H, W), device=x.device, dtype=torch.float32)
+    if want_full:
+        yp, ybs = _slot(y, "y")
+        if tuple(y.shape) != (B, Cc, H, W):
+            raise ValueError("y shape mismatch")
+        d.y, d.y_batch_stride = yp, ybs
+    else:
+        y = None
+    if y2 is not None:
+        if tuple(y2.shape) != (B, Cc, H, W):
+            raise ValueError("y2 shape mismatch")
+        d.y2, d.y2_batch_stride = _slot(y2, "y2")
+    d.batch, d.channels, d.height, d.width = B, Cc, H, W
+    if gamma is not None:
+        d.gamma, d.beta = _vec(gamma, Cc, "gamma"), _vec(beta, Cc, "beta")
+        d.mean, d.var = _vec(mean, Cc, "mean"), _vec(var, Cc, "var")
+    d.eps, d.eps_mode = eps, eps_mode
+    d.bias = _vec(bias, Cc, "bias")
+    d.act, d.yolo_classes = _act(act), yolo_classes
+    if residual is not None:
+        if tuple(residual.shape) != (B, Cc, H, W):
+            raise ValueError("residual shape mismatch")
+        d.residual, d.residual_batch_stride = _slot(residual, "residual")
+        d.res_alpha, d.res_beta, d.res_act = res_alpha, res_beta, _act(res_act)
+    if pool is not None:
+        k, s, pad = pool
+        d.pool_kernel, d.pool_stride, d.pool_padding = k, s, pad
+        oh, ow = maxpool_out_dim(H, k, s, pad), maxpool_out_dim(W, k, s, pad)
+        if y_pool is None:
+            y_pool = torch.empty((B, Cc, oh, ow), device=x.device, dtype=torch.float32)
+        if tuple(y_pool.shape) != (B, Cc, oh, ow):
+            raise ValueError(f"y_pool must be {(B, Cc, oh, ow)}, got {tuple(y_pool.shape)}")
+        d.y_pool, d.y_pool_batch_stride = _slot(y_pool, "y_pool")
+    capi.check(capi.lib().pxe_conv_epilogue(_stream(), C.byref(d)))
+    return (y, y_pool) if pool is not None else y
+
+
+def activate(kind, x: torch.Tensor) -> torch.Tensor:
+    """In-place activation of a contiguous tensor: px::activate (src/Activation.cu:126-133)."""
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    capi.check(capi.lib().pxe_activate(_stream(), _act(kind), x.data_ptr(), x.numel()))
+    return x
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """out[b, j, ...] += bias[j] in place: px::addBiasGpu (src/BiasKernels.cu:86-93)."""
+    _check_f32_cuda(out, "out")
+    if not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+    B, n = out.shape[0], out.shape[1]
+    size = out.numel() // (B * n)
+    capi.check(capi.lib().pxe_add_bias(_stream(), out.data_ptr(), _vec(bias, n, "bias"), B, n, size))
+    return out
+
+
+def maxpool(x: torch.Tensor, kernel: int, stride: int, padding: Optional[int] = None,
+            out: Optional[torch.Tensor] = None, with_indexes: bool = False):
+    """MaxPoolLayer forward.  Returns ``out`` or ``(out, indexes)``."""
+    if padding is None:
+        padding = max(0, kernel - 1)                       # include/MaxPoolLayer.h:56
+    xp, xbs = _slot(x, "x")
+    B, Cc, H, W = x.shape
+    oh, ow = maxpool_out_dim(H, kernel, stride, padding), maxpool_out_dim(W, kernel, stride, padding)
+    if oh <= 0 or ow <= 0:
+        raise PxeError(capi.PXE_ERR_BAD_ARG, f"maxpool: empty output {oh}x{ow}")
+    if out is None:
+        out = torch.empty((B, Cc, oh, ow), device=x.device, dtype=torch.float32)
+    if tuple(out.shape) != (B, Cc, oh, ow):
+        raise ValueError(f"out must be {(B, Cc, oh, ow)}")
+    yp, ybs = _slot(out, "out")
+    idx = torch.empty((B, Cc, oh, ow), device=x.device, dtype=torch.int32) if with_indexes else None
+    if with_indexes and xbs != Cc * H * W:
+        raise ValueError("indexes need a densely packed input")
+    capi.check(capi.lib().pxe_maxpool(_stream(), xp, xbs, yp, ybs, idx.data_ptr() if idx is not None else None,
+                                      B, Cc, H, W, kernel, stride, padding))
+    return (out, idx) if with_indexes else out
+
+
+def spp(x: torch.Tensor, kernels: Sequence[int], outs: Sequence[torch.Tensor]) -> Sequence[torch.Tensor]:
+    """Stride-1 max pools of one input (default padding kernel-1), one output per kernel size."""
+    xp, xbs = _slot(x, "x")
+    B, Cc, H, W = x.shape
+    n = len(kernels)
+    if len(outs) != n:
+        raise ValueError("one output per kernel size")
+    ptrs, strides = (C.c_void_p * n)(), (C.c_longlong * n)()
+    for i, o in enumerate(outs):
+        if tuple(o.shape) != (B, Cc, H, W):
+            raise ValueError("spp outputs have the input's shape")
+        ptrs[i], strides[i] = _slot(o, f"outs[{i}]")
+    ks = (C.c_int * n)(*[int(k) for k in kernels])
+    capi.check(capi.lib().pxe_spp(_stream(), xp, xbs, B, Cc, H, W, n, ks, ptrs, strides))
+    return outs
+
+
+def upsample(x: torch.Tensor, stride: int = 2, scale: float = 1.0, out: Optional[torch.Tensor] = None):
+    xp, xbs = _slot(x, "x")
+    B, Cc, H, W = x.shape
+    if out is None:
+        out = torch.empty((B, Cc, H * stride, W * stride), device=x.device, dtype=torch.float32)
+    if tuple(out.shape) != (B, Cc, H * stride, W * stride):
+        raise ValueError("out shape mismatch")
+    yp, ybs = _slot(out, "out")
+    capi.check(capi.lib().pxe_upsample(_stream(), xp, xbs, yp, ybs, B, Cc, H, W, stride, scale))
+    return out
+
+
+def shortcut(x: torch.Tensor, frm: torch.Tensor, alpha: float = 1.0, beta: float = 1.0, act="linear",
+             out: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None):
+    """out = act(alpha*x + beta*from) for equal shapes (ShortcutLayer forward)."""
+    xp, xbs = _slot(x, "x")
+    fp, fbs = _slot(frm, "from")
+    B, Cc, H, W = x.shape
+    if tuple(frm.shape) != (B, Cc, H, W):
+        raise ValueError("from shape mismatch")
+    if out is None:
+        out = torch.empty((B, Cc, H, W), device=x.device, dtype=torch.float32)
+    yp, ybs = _slot(out, "out")
+    y2p, y2bs = _slot(out2, "out2")
+    capi.check(capi.lib().pxe_shortcut(_stream(), xp, xbs, fp, fbs, yp, ybs, y2p, y2bs, B, Cc, H, W,
+                                       alpha, beta, _act(act)))
+    return out
+
+
+def shortcut_general(batch, w1, h1, c1, add: torch.Tensor, w2, h2, c2, s1, s2, out: torch.Tensor):
+    """px::shortcutGpu for unequal shapes: out = s1*out + s2*add, in place."""
+    _check_f32_cuda(add, "add")
+    _check_f32_cuda(out, "out")
+    capi.check(capi.lib().pxe_shortcut_general(_stream(), batch, w1, h1, c1, add.data_ptr(), w2, h2, c2,
+                                               s1, s2, out.data_ptr()))
+    return out
+
+
+def concat(srcs: Sequence[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RouteLayer forward as one launch."""
+    n = len(srcs)
+    B, _, H, W = srcs[0].shape
+    ch = [int(s.shape[1]) for s in srcs]
+    if out is None:
+        out = torch.empty((B, sum(ch), H, W), device=srcs[0].device, dtype=torch.float32)
+    ptrs, strides = (C.c_void_p * n)(), (C.c_longlong * n)()
+    for i, s in enumerate(srcs):
+        if s.shape[0] != B or s.shape[2] != H or s.shape[3] != W:
+            raise ValueError("route sources must share batch and spatial size")
+        ptrs[i], strides[i] = _slot(s, f"srcs[{i}]")
+    yp, ybs = _slot(out, "out")
+    capi.check(capi.lib().pxe_concat(_stream(), n, ptrs, strides, (C.c_int * n)(*ch), yp, ybs, B, H, W))
+    return out
+
+
+def yolo_activate(x: torch.Tensor, masks: int, classes: int, out: Optional[torch.Tensor] = None):
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    B = x.shape[0]
+    area = x.shape[2] * x.shape[3]
+    if out is None:
+        out = torch.empty_like(x)
+    capi.check(capi.lib().pxe_yolo_activate(_stream(), x.data_ptr(), out.data_ptr(), B, masks, classes, area))
+    return out
+
+
+class DetectionBuffer:
+    """Device buffer of detections plus the device-side running count the YOLO decode appends to."""
+
+    def __init__(self, capacity: int, device):
+        self.capacity = int(capacity)
+        self.dets = torch.empty((self.capacity, 8), device=device, dtype=torch.int32)   # 32-byte records
+        self.count = torch.zeros(1, device=device, dtype=torch.int64)
+        self._workspace = None
+
+    def reset(self):
+        self.count.zero_()
+
+    def workspace(self, nbytes: int) -> torch.Tensor:
+        if self._workspace is None or self._workspace.numel() < nbytes:
+            self._workspace = torch.empty(max(nbytes, 256), device=self.dets.device, dtype=torch.uint8)
+        return self._workspace
+
+    def to_host(self):
+        """(structured numpy array of the stored records, total count incl. dropped ones)."""
+        total = int(self.count.item())
+        n = min(total, self.capacity)
+        host = self.dets[:n].cpu().numpy().view(DET_DTYPE).reshape(-1)
+        return host, total
+
+
+def yolo_decode(head: torch.Tensor, mask, anchors, classes: int, net_w: int, net_h: int, threshold: float,
+                buf: DetectionBuffer, *, img_w: int = 0, img_h: int = 0, raw: bool = False,
+                bias: Optional[torch.Tensor] = None, batch_id_offset: int = 0) -> None:
+    """Appends one head's detections to ``buf`` in the reference's emission order."""
+    hp, hbs = _slot(head, "head")
+    B, Cc, H, W = head.shape
+    d = capi.YoloDecodeDesc()
+    d.head, d.head_batch_stride = hp, hbs
+    d.head_is_raw = int(raw)
+    d.bias = _vec(bias, Cc, "bias")
+    d.batch, d.height, d.width, d.classes = B, H, W, classes
+    d.n_masks = len(mask)
+    for i, m in enumerate(mask):
+        d.mask[i] = int(m)
+    d.n_anchor_values = len(anchors)
+    for i, a in enumerate(anchors):
+        d.anchors[i] = int(a)
+    d.net_width, d.net_height = net_w, net_h
+    d.image_width, d.image_height = img_w, img_h
+    d.threshold, d.batch_id_offset = threshold, batch_id_offset
+    if Cc != len(mask) * (classes + 5):
+        raise ValueError("head channels must equal masks*(classes+5)")
+    need = capi.lib().pxe_yolo_decode_workspace_bytes(B, H, W)
+    ws = buf.workspace(need)
+    capi.check(capi.lib().pxe_yolo_decode(_stream(), C.byref(d), buf.dets.data_ptr(), buf.capacity,
+                                          buf.count.data_ptr(), ws.data_ptr(), ws.numel()))
+
+
+def centernet_activate(x: torch.Tensor, classes: int, heatmap_bias: float, out: Optional[torch.Tensor] = None):
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    B = x.shape[0]
+    area = x.shape[2] * x.shape[3]
+    if out is None:
+        out = torch.empty_like(x)
+    capi.check(capi.lib().pxe_centernet_activate(_stream(), x.data_ptr(), out.data_ptr(), B, classes, area,
+                                                 heatmap_bias))
+    return out
+
+
+def centernet_decode(heat: torch.Tensor, size: torch.Tensor, offset: torch.Tensor, threshold: float,
+                     max_detections: int = 100, *, logits: bool = False, heatmap_bias: float = 0.0,
+                     img_w: int = 0, img_h: int = 0, batch_id_offset: int = 0, workspace=None):
+    """Returns (dets [B, K, 8] int32 view of 32-byte records, counts [B] int32), both on the device."""
+    hp, hbs = _slot(heat, "heat")
+    sp, sbs = _slot(size, "size")
+    op, obs = _slot(offset, "offset")
+    B, classes, H, W = heat.shape
+    d = capi.CenterNetDecodeDesc()
+    d.heat, d.heat_batch_stride = hp, hbs
+    d.size, d.size_batch_stride = sp, sbs
+    d.offset, d.offset_batch_stride = op, obs
+    d.heat_is_logit, d.heatmap_bias = int(logits), heatmap_bias
+    d.batch, d.classes, d.height, d.width = B, classes, H, W
+    d.image_width, d.image_height = img_w, img_h
+    d.threshold, d.max_detections, d.batch_id_offset = threshold, max_detections, batch_id_offset
+    need = capi.lib().pxe_centernet_decode_workspace_bytes(B, classes, H, W, max_detections)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(max(need, 256), device=heat.device, dtype=torch.uint8)
+    dets = torch.empty((B, max_detections, 8), device=heat.device, dtype=torch.int32)
+    counts = torch.empty(B, device=heat.device, dtype=torch.int32)
+    capi.check(capi.lib().pxe_centernet_decode(_stream(), C.byref(d), dets.data_ptr(), counts.data_ptr(),
+                                               workspace.data_ptr(), workspace.numel()))
+    return dets, counts
+
+
+def centernet_to_host(dets: torch.Tensor, counts: torch.Tensor):
+    """List of per-image structured arrays."""
+    h = dets.cpu().numpy()
+    c = counts.cpu().numpy()
+    return [h[b, :c[b]].copy().view(DET_DTYPE).reshape(-1) for b in range(h.shape[0])]
+
+
+def softmax(x: torch.Tensor, groups: int = 1, temperature: float = 1.0, out: Optional[torch.Tensor] = None):
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    B = x.shape[0]
+    inputs = x.numel() // B
+    if out is None:
+        out = torch.empty_like(x)
+    capi.check(capi.lib().pxe_softmax(_stream(), x.data_ptr(), out.data_ptr(), B, inputs, groups, temperature))
+    return out
+
+
+def region_forward(x: torch.Tensor, num: int, coords: int, classes: int, use_softmax: bool = True):
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    B, _, H, W = x.shape
+    out = torch.empty_like(x)
+    capi.check(capi.lib().pxe_region_forward(_stream(), x.data_ptr(), out.data_ptr(), B, W, H, num, coords,
+                                             classes, int(use_softmax)))
+    return out
+
+
+def nms(dets: np.ndarray, threshold: float) -> np.ndarray:
+    """px::nms on host records (structured array of DET_DTYPE)."""
+    dets = np.ascontiguousarray(dets, DET_DTYPE)
+    out = np.zeros(len(dets), DET_DTYPE)
+    n = capi.lib().pxe_nms_host(dets.ctypes.data, len(dets), threshold, out.ctypes.data)
+    if n < 0:
+        raise PxeError(-n, "pxe_nms_host failed")
+    return out[:n].copy()

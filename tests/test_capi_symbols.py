@@ -1,0 +1,55 @@
+"""The C-ABI library loads and exports every symbol include/pxe.h declares (no compute calls)."""
+import os
+import re
+
+from pixienn_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_in_header():
+    text = open(os.path.join(ROOT, "include", "pxe.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"PXE_API\s+[\w\s\*]+?\b(pxe_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = declared_in_header()
+    assert len(names) >= 20
+    L = capi.lib()
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in pxe.h but not exported by libpxe.so"
+        assert n in capi.PROTOTYPES, f"{n} has no ctypes prototype"
+    assert sorted(capi.PROTOTYPES) == names, "ctypes prototypes and header declarations differ"
+
+
+def test_compat_tier_symbols_exported():
+    L = capi.lib()
+    for n in capi.COMPAT_SYMBOLS:
+        assert hasattr(L, n), n
+
+
+def test_version_and_status_strings():
+    L = capi.lib()
+    assert L.pxe_version() >= 100
+    assert L.pxe_status_string(capi.PXE_OK) == b"ok"
+    assert L.pxe_status_string(capi.PXE_ERR_WORKSPACE) == b"workspace too small"
+
+
+def test_struct_layouts_match_header_sizes():
+    import ctypes as C
+    assert C.sizeof(capi.Detection) == 32
+    # pointers 8, long long 8, ints/floats 4, natural alignment: same rule the C compiler applies
+    assert C.sizeof(capi.EpilogueDesc) % 8 == 0
+    assert capi.YoloDecodeDesc.mask.offset % 4 == 0 and capi.YoloDecodeDesc.anchors.size == 256
+
+
+def test_host_only_entry_points():
+    """Argument validation and pure-host helpers can run without a GPU."""
+    L = capi.lib()
+    assert L.pxe_maxpool_out_dim(416, 2, 2, 1) == 208
+    assert L.pxe_maxpool_out_dim(13, 2, 2, 1) == 7
+    assert L.pxe_yolo_decode_workspace_bytes(2, 13, 13) > 0
+    assert L.pxe_centernet_decode_workspace_bytes(1, 20, 128, 128, 100) >= 20 * 8 * 100 * 8
+    assert L.pxe_conv_epilogue(None, None) == capi.PXE_ERR_BAD_ARG
+    assert L.pxe_nms_host(None, 0, 0.5, None) == 0

