@@ -1,0 +1,438 @@
+#!/usr/bin/env python
+"""Benchmark of the per-layer epilogue path on B200.
+
+  python bench.py --gpus N --steps K --warmup W            the new kernels (one rank per GPU)
+  python bench.py --impl reference ...                      the reference's CPU path on the host cores
+
+Workload (default): YOLOv3 on a Darknet-53 backbone, 608x608, 64 images per GPU, fp32, random-init
+weights from a seed, inference.  One step = one forward pass of the hot path over one batch:
+every convolution on cuDNN (through torch, as the reference keeps it on cuDNN) and everything
+between the convolutions -- BN, bias, activation, shortcut, upsample, route, YOLO decode -- on the
+kernels of libpxe.so.  `value` is images/s with the input batch resident in HBM; `e2e` is the same
+through Runner.predict with a pinned HOST batch in and host detections out.  The batch is sharded
+by image across ranks; there is no collective on the data path.
+
+Other workloads (not run by default): --workload sweep (the isolated fused-epilogue sweep),
+--workload centernet (the CenterNet head decode), --workload yolov3-tiny | yolov7.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+SEED = 1234
+CONF = 0.2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi samples of one GPU while the timed region runs (read-only queries)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.file = gpu_index, None, None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        name = self.file.name
+        self.file.close()
+        os.unlink(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def make_doc(workload: str):
+    from pixienn_b200 import presets
+    if workload == "yolov3-608":
+        return presets.yolov3(608, 608), "YOLOv3 (Darknet-53) 608x608"
+    if workload == "yolov3-tiny":
+        return presets.yolov3_tiny(416, 416), "YOLOv3-tiny 416x416"
+    if workload == "yolov7":
+        return presets.yolov7(640, 640), "YOLOv7 640x640"
+    raise SystemExit(f"unknown workload {workload}")
+
+
+def host_batch(model, batch, first_image):
+    from pixienn_b200 import synth
+    return np.stack([synth.uniform(SEED, f"input/{first_image + b}", (model.channels, model.height, model.width))
+                     for b in range(batch)])
+
+
+# ------------------------------------------------------------------------------------- our arm
+def run_model(args):
+    import torch
+    import torch.distributed as dist
+    from pixienn_b200 import capi, graph
+    from pixienn_b200.runner import Runner, synth_weights
+
+    rank, local_rank, world = dist_env()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    capi.lib()                                     # no library, no benchmark: there is no fallback path
+    torch.backends.cudnn.benchmark = True          # the reference picks its conv algorithm with cudnnFind*
+
+    doc, label = make_doc(args.workload)
+    model = graph.parse_model(doc)
+    B = args.batch
+    weights = synth_weights(model, SEED)
+    runner = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF,
+                    batch_id_offset=rank * B)
+    xh = torch.from_numpy(host_batch(model, B, rank * B)).pin_memory()
+    x = xh.to(dev)
+    pinned_dets = torch.empty((args.det_capacity, 8), dtype=torch.int32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        runner.forward(x)
+    barrier()
+
+    # ---- timed region: K steps, inputs resident in HBM
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    runner.timer.enabled = True
+    runner.timer.clear()
+    launches = 0
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        runner.forward(x)
+        launches += runner.launches
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    ops_summary = runner.timer.summary()
+    runner.timer.enabled = False
+    n_dets = int(runner.dets.count.item())
+
+    # ---- end to end: pinned host batch in, detections on the host out
+    def e2e_step():
+        x2 = xh.to(dev, non_blocking=True)
+        runner.forward(x2)
+        n = min(int(runner.dets.count.item()), runner.dets.capacity)
+        pinned_dets[:n].copy_(runner.dets.dets[:n], non_blocking=True)
+        torch.cuda.synchronize()
+        return n
+    e2e_step()
+    barrier()
+    w0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        n_host = e2e_step()
+    e1.record()
+    barrier()
+    wall_ms = (time.perf_counter() - w0) * 1e3       # the step ends with a host wait, so wall >= device time
+    e2e_ms = torch.tensor([max(e0.elapsed_time(e1), wall_ms)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_total_ms = float(e2e_ms.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    images = B * world * args.steps
+    value = images / (total_ms / 1e3)
+    peak, peak_src = measured_peaks()
+    mine = {k: v for k, v in ops_summary.items() if k != "conv(cudnn)"}
+    dom = max(mine, key=lambda k: mine[k]["ms"])
+    d = mine[dom]
+    achieved = d["bytes"] / (d["ms"] / 1e3) / 1e9
+    breakdown = {k: {"launches_per_step": v["launches"] // args.steps, "ms_per_step": round(v["ms"] / args.steps, 4),
+                     "GBps": (round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["bytes"] and v["ms"] > 0 else None)}
+                 for k, v in ops_summary.items()}
+    epi_ms = sum(v["ms"] for v in mine.values()) / args.steps
+    epi_bytes = sum(v["bytes"] for v in mine.values()) / args.steps
+
+    line = {
+        "metric": "YOLOv3 608x608 inference throughput" if args.workload == "yolov3-608" else f"{label} inference throughput",
+        "value": round(value, 2), "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(total_ms / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{label}, {B} images per GPU, global batch {B * world}, fp32 NCHW, random-init weights "
+                               f"(seed {SEED}), conf {CONF}; conv on cuDNN (TF32 allowed, cuDNN's default math mode), "
+                               "epilogue/shortcut/upsample/route/decode on libpxe.so",
+                   "per_gpu_batch": B, "global_batch": B * world, "sharding": "by image, no collectives",
+                   "l2": "inputs larger than L2: every timed tensor is 24 MB-3 GB and is produced/consumed once per step",
+                   "detections_per_step_per_gpu": n_dets, "plan": runner.plan.stats},
+        "clocks": clocks,
+        "e2e": {"value": round(images / (e2e_total_ms / 1e3), 2), "unit": "images/s",
+                "h2d_bytes_per_step": int(xh.numel() * 4), "d2h_bytes_per_step": int(n_host * 32 + 8),
+                "api": "pixienn_b200.runner.Runner.predict path: pinned host batch -> device, forward, detections -> pinned host"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / 8000.0, 4),
+                     "peak_source": peak_src, "traffic": None,
+                     "launches_timed": d["launches"], "avg_launch_ms": round(d["ms"] / d["launches"], 4),
+                     "algorithmic_bytes_per_step": int(d["bytes"] / args.steps)},
+        "epilogue": {"ms_per_step": round(epi_ms, 3), "algorithmic_GB_per_step": round(epi_bytes / 1e9, 3),
+                     "GBps": round(epi_bytes / (epi_ms / 1e3) / 1e9, 1), "images_per_s_epilogue_only": round(B / (epi_ms / 1e3), 1)},
+        "breakdown": breakdown,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_reference(args, steps=1, warmup=0)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------- reference arm
+def cpu_reference(args, steps: int, warmup: int):
+    """The reference's CPU path for the same model on the host cores: a bounded sample of
+    `args.cpu_images` image(s) per step."""
+    from oracle import pxoracle as po
+    from oracle.pxmodel import CpuModel
+    from pixienn_b200 import graph
+    from pixienn_b200.runner import synth_weights
+    doc, label = make_doc(args.workload)
+    model = graph.parse_model(doc)
+    weights = synth_weights(model, SEED)
+    ref = po.ref_cpu()
+    cores = os.cpu_count() or 1
+    if ref is not None:
+        cores = ref.set_threads(cores)
+    cpu = CpuModel(doc, weights, eps_mode=1, keep_outputs=False)
+    x = host_batch(model, args.cpu_images, 0)
+    for _ in range(warmup):
+        cpu.forward(x)
+    t = time.perf_counter()
+    for _ in range(steps):
+        cpu.forward(x)
+        cpu.detections(CONF)
+    sec = time.perf_counter() - t
+    return {"value": round(args.cpu_images * steps / sec, 4), "unit": "images/s", "cores": cores,
+            "kind": "reference" if ref is not None else "port",
+            "sample": f"{args.cpu_images} image(s) of the {label} batch per step, {steps} step(s): conv (im2col + OpenBLAS "
+                      "sgemm), BN, bias, activation in the reference's own compiled CpuUtil.cpp / BatchNorm.cpp / "
+                      "Activation.h" + ("" if ref is not None else " (not available: C restatement used)")
+                      + "; maxpool / upsample / shortcut / route / YOLO decode loops restated in C (oracle/px_oracle.c)",
+            "ms_per_image": round(sec / (args.cpu_images * steps) * 1e3, 1)}
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    base = cpu_reference(args, steps=args.steps, warmup=min(args.warmup, 1))
+    doc, label = make_doc(args.workload)
+    line = {
+        "impl": "reference",
+        "metric": "YOLOv3 608x608 inference throughput" if args.workload == "yolov3-608" else f"{label} inference throughput",
+        "value": base["value"], "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": round(args.cpu_images / base["value"] * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{label}, reference CPU forward path (OpenBLAS) on the host cores, "
+                               f"{args.cpu_images} image(s) per step of the {args.batch}-image batch",
+                   "per_gpu_batch": args.batch, "global_batch": args.batch * world},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ other workloads
+def run_sweep(args):
+    """Isolated fused-epilogue sweep: [64,C,H,W] x {leaky, mish, swish, logistic} x {no pool, 2x2/2 pool}."""
+    import torch
+    from pixienn_b200 import ops, synth
+    dev = torch.device("cuda", 0)
+    peak, peak_src = measured_peaks()
+    shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
+    if args.sweep_shapes:
+        shapes = shapes[:args.sweep_shapes]
+    rows = []
+    for (C, H, W) in shapes:
+        B = args.batch
+        n = B * C * H * W
+        sets = max(3, int(400e6 // (n * 4)) + 1)          # rotate so that no iteration finds its data in L2
+        g, b, m, v = (torch.from_numpy(t).to(dev) for t in synth.bn_params(SEED, f"sweep{C}", C))
+        bias = torch.from_numpy(synth.normal(SEED, f"sweepb{C}", C, 0, 0.1)).to(dev)
+        base = torch.randn((B, C, H, W), device=dev, generator=torch.Generator(dev).manual_seed(SEED))
+        xs = [base.clone() for _ in range(sets)]
+        for act in ["leaky", "mish", "swish", "logistic"]:
+            for pool in (False, True):
+                oh = ops.maxpool_out_dim(H, 2, 2, 1)
+                yp = torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) if pool else None
+
+                def call(i):
+                    if pool:
+                        ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
+                                          pool=(2, 2, 1), y_pool=yp)
+                    else:
+                        ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act)
+                for i in range(args.warmup):
+                    call(i)
+                ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+                torch.cuda.synchronize()
+                for i, (a, z) in enumerate(ev):
+                    a.record(); call(i); z.record()
+                torch.cuda.synchronize()
+                ts = sorted(a.elapsed_time(z) for a, z in ev)
+                med = ts[len(ts) // 2]
+                nbytes = (4 * n + 4 * yp.numel()) if pool else 8 * n
+                rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "MB": round(nbytes / 1e6, 1),
+                             "us_median": round(med * 1e3, 2), "us_min": round(ts[0] * 1e3, 2),
+                             "GBps": round(nbytes / med / 1e6, 1), "frac_measured": round(nbytes / med / 1e6 / peak, 3),
+                             "frac_8000": round(nbytes / med / 1e6 / 8000, 3)})
+                if pool:          # x was not modified; nothing to restore.  In-place runs keep re-activating x: refresh
+                    pass
+        del xs
+    for r in rows:
+        print(json.dumps(r), file=sys.stderr)
+    fr = [r["frac_measured"] for r in rows]
+    print(json.dumps({"metric": "fused-epilogue HBM bandwidth, isolated sweep", "value": round(statistics.median(r["GBps"] for r in rows), 1),
+                      "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic", "peak": peak, "peak_source": peak_src,
+                      "frac_min": min(fr), "frac_median": statistics.median(fr), "frac_max": max(fr),
+                      "config": {"workload": "isolated fused epilogue sweep", "l2": "rotating input sets > 400 MB"},
+                      "cells": rows}), flush=True)
+
+
+def run_centernet(args):
+    """CenterNet head decode: [B,20,128,128] heat logits N(-4,2) + Gaussian peaks, K = 100."""
+    import torch
+    from pixienn_b200 import ops, synth
+    dev = torch.device("cuda", 0)
+    peak, peak_src = measured_peaks()
+    B, classes, H, W, K = args.batch, 20, 128, 128, 100
+    rng = np.random.default_rng(SEED)
+    heat = synth.normal(SEED, "c4/heat", (B, classes, H, W), -4.0, 2.0)
+    yy, xx = np.mgrid[0:H, 0:W]
+    for bi in range(B):
+        for _ in range(int(rng.integers(1, 31))):
+            c, y, x = int(rng.integers(classes)), int(rng.integers(H)), int(rng.integers(W))
+            y0, y1, x0, x1 = max(0, y - 6), min(H, y + 7), max(0, x - 6), min(W, x + 7)
+            heat[bi, c, y0:y1, x0:x1] += (8.0 * np.exp(-((yy[y0:y1, x0:x1] - y) ** 2 + (xx[y0:y1, x0:x1] - x) ** 2) / 4.5)).astype(np.float32)
+    sets = 3
+    hs = [torch.from_numpy(heat).to(dev) for _ in range(sets)]
+    size = torch.from_numpy(synth.uniform(SEED, "c4/wh", (B, 2, H, W))).to(dev)
+    off = torch.from_numpy(synth.uniform(SEED, "c4/off", (B, 2, H, W))).to(dev)
+    need = ops.capi.lib().pxe_centernet_decode_workspace_bytes(B, classes, H, W, K)
+    ws = torch.empty(need, device=dev, dtype=torch.uint8)
+    for i in range(args.warmup):
+        ops.centernet_decode(hs[i % sets], size, off, CONF, K, logits=True, heatmap_bias=0.0, workspace=ws)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    for i, (a, z) in enumerate(ev):
+        a.record()
+        d, c = ops.centernet_decode(hs[i % sets], size, off, CONF, K, logits=True, heatmap_bias=0.0, workspace=ws)
+        z.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(z) for a, z in ev)
+    med = ts[len(ts) // 2]
+    nbytes = 4 * B * classes * H * W
+    print(json.dumps({"metric": "CenterNet head decode", "value": round(B / (med / 1e3), 1), "unit": "images/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(med, 4), "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"CenterNet decode B={B}, 20x128x128 heat + 2x wh + 2x offset, K=100, thr {CONF}",
+                                 "l2": "3 rotating 335 MB heatmaps", "kept_per_image_mean": float(c.float().mean().item())},
+                      "roofline": {"bound": "hbm", "achieved": round(nbytes / med / 1e6, 1), "peak": peak, "unit": "GB/s",
+                                   "frac": round(nbytes / med / 1e6 / peak, 4), "peak_source": peak_src, "traffic": None}}),
+          flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="yolov3-608")
+    ap.add_argument("--batch", type=int, default=None, help="images per GPU (default 64; 256 for --workload centernet)")
+    ap.add_argument("--cpu-images", type=int, default=2, help="images per step of the CPU reference sample")
+    ap.add_argument("--det-capacity", type=int, default=24 * (1 << 20))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep-shapes", type=int, default=0)
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.batch is None:
+        args.batch = 256 if args.workload == "centernet" else 64
+    _, _, world = dist_env()
+    if args.gpus != world and world == 1 and args.gpus > 1 and args.impl == "ours":
+        raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nnodes=1 --nproc-per-node N "
+                         "--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...")
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.workload == "sweep":
+        return run_sweep(args)
+    if args.workload == "centernet":
+        return run_centernet(args)
+    return run_model(args)
+
+
+if __name__ == "__main__":
+    main()

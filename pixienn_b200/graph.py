@@ -335,7 +335,9 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
         elif l.type == "route":
             if fuse:
                 # every source already stored into this route's buffer
-                steps.append(Step("alias", i, [], produces=[i]))
+                # (if this route is itself a source of a later route, its buffer is copied into that slot)
+                steps.append(Step("alias", i, [], [Dest("slot", r, off) for (r, off) in slots.get(i, [])],
+                                  produces=[i]))
                 stats["routes_eliminated"] += 1
             else:
                 steps.append(Step("concat", i, list(l.sources), [Dest("dense")], produces=[i]))

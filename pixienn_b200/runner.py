@@ -1,0 +1,332 @@
+"""Runs a planned PixieNN graph on one GPU: convolutions on cuDNN (through torch, as the reference
+keeps them on its cuDNN call), everything between them on the kernels of ``libpxe.so``.
+
+This is the host-side mirror of ``Model<Device::CUDA>::forward`` + ``Model::detections``
+(include/Model.h:1740-1759, 1062-1109): layers in index order on one stream, detections gathered
+from the detector layers in layer order.  Unlike the reference it holds no per-layer output /
+delta / preActivation buffers: tensors live from their producer to their last reader.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import graph, ops, synth
+
+
+def synth_weights(model: graph.Model, seed: int = 1234, head_bias: float = 0.0) -> Dict[int, Dict[str, np.ndarray]]:
+    """Seeded random-init weights: conv N(0, sqrt(2/fan_in)) with fan_in = k*k*C_in/groups
+    (include/ConvLayer.h:111-115); BN gamma U(0.5,1.5), beta N(0,0.1), running mean N(0,0.1),
+    running var U(0.5,1.5); non-BN conv bias 0.  ``head_bias`` is added to the objectness bias of
+    convolutions feeding a YOLO layer (0 keeps the plain init)."""
+    out: Dict[int, Dict[str, np.ndarray]] = {}
+    for l in model.layers:
+        if l.type != "conv":
+            continue
+        cin = l.in_shape[0]
+        fan_in = l.kernel * l.kernel * cin // l.groups
+        w = synth.normal(seed, f"L{l.index}/w", (l.filters, cin // l.groups, l.kernel, l.kernel), 0.0,
+                         math.sqrt(2.0 / fan_in))
+        d = {"weights": w}
+        if l.batch_norm:
+            g, b, m, v = synth.bn_params(seed, f"L{l.index}/bn", l.filters)
+            d.update(scales=g, biases=b, rolling_mean=m, rolling_var=v)
+        else:
+            bias = np.zeros(l.filters, np.float32)
+            nxt = model.layers[l.index + 1] if l.index + 1 < len(model.layers) else None
+            if head_bias != 0.0 and nxt is not None and nxt.type == "yolo":
+                entries = l.filters // len(nxt.params["mask"])
+                bias[4::entries] = head_bias
+            d["biases"] = bias
+        out[l.index] = d
+    return out
+
+
+class OpTimer:
+    """Collects CUDA-event pairs around launches; resolved after a synchronise."""
+
+    def __init__(self):
+        self.records = []          # (kind, algorithmic bytes, start event, end event)
+        self.enabled = False
+
+    def begin(self):
+        if not self.enabled:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def end(self, start, kind: str, nbytes: int):
+        if start is None:
+            return
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.records.append((kind, nbytes, start, e))
+
+    def summary(self) -> Dict[str, Dict[str, float]]:
+        out: Dict[str, Dict[str, float]] = {}
+        for kind, nbytes, s, e in self.records:
+            d = out.setdefault(kind, {"launches": 0, "ms": 0.0, "bytes": 0})
+            d["launches"] += 1
+            d["ms"] += s.elapsed_time(e)
+            d["bytes"] += nbytes
+        return out
+
+    def clear(self):
+        self.records = []
+
+
+class Runner:
+    def __init__(self, model: graph.Model, weights: Dict[int, Dict[str, np.ndarray]], batch: int, device,
+                 fuse: bool = True, raw_heads: bool = True, det_capacity: int = 1 << 20,
+                 threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0):
+        self.model, self.batch, self.device = model, batch, device
+        self.eps_mode = eps_mode        # 0: cuDNN form sqrt(var+eps) (the CUDA path), 1: the CPU path's sqrt(var)+eps
+        self.plan = graph.plan(model, fuse=fuse, raw_heads=raw_heads)
+        self.threshold = threshold
+        self.batch_id_offset = batch_id_offset
+        self.w: Dict[int, Dict[str, torch.Tensor]] = {
+            i: {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in d.items()}
+            for i, d in weights.items()}
+        self.dets = ops.DetectionBuffer(det_capacity, device)
+        self.centernet_out = []        # (dets, counts) per centernet layer of the last forward
+        self.outputs: Dict[int, torch.Tensor] = {}     # softmax / region outputs of the last forward
+        self.timer = OpTimer()
+        self.launches = 0              # kernels of libpxe.so launched by the last forward
+        self.contiguous_copies = 0     # hidden torch copies of strided conv inputs (should stay 0)
+        self.keep: Optional[set] = None  # layer indices whose tensors to retain in self.kept
+        self.kept: Dict[int, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ helpers
+    def _view(self, bufs, route: int, offset: int, layer: graph.Layer) -> torch.Tensor:
+        c, h, w = layer.out_shape
+        if route not in bufs:
+            bufs[route] = torch.empty((self.batch, self.plan.concat_channels[route], h, w), device=self.device)
+        return bufs[route][:, offset:offset + c]
+
+    def _dest_tensors(self, bufs, dests: List[graph.Dest], layer: graph.Layer, dense: Optional[torch.Tensor] = None):
+        out = []
+        for d in dests:
+            if d.kind == "dense":
+                if dense is None:
+                    dense = torch.empty((self.batch,) + layer.out_shape, device=self.device)
+                out.append(dense)
+            else:
+                out.append(self._view(bufs, d.route, d.offset, layer))
+        return out
+
+    def _extra_copies(self, src: torch.Tensor, extra: List[torch.Tensor]):
+        for t in extra:
+            s = self.timer.begin()
+            ops.concat([src], out=t)
+            self.launches += 1
+            self.timer.end(s, "concat", 8 * src.numel())
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> None:
+        """Enqueues one forward pass of the whole graph for the batch ``x`` [B,C,H,W] (on the device)."""
+        L = self.model.layers
+        T: Dict[int, torch.Tensor] = {-1: x}
+        bufs: Dict[int, torch.Tensor] = {}
+        self.dets.reset()
+        self.centernet_out, self.outputs, self.kept = [], {}, {}
+        self.launches = 0
+        tm = self.timer
+        for si, st in enumerate(self.plan.steps):
+            l = L[st.layer]
+            if st.op == "conv":
+                self._conv(st, l, T, bufs)
+            elif st.op == "alias":
+                if st.inputs:
+                    T[st.layer] = T[st.inputs[0]]
+                else:
+                    T[st.layer] = bufs[st.layer]
+                    self._extra_copies(T[st.layer], self._dest_tensors(bufs, st.dests, l))
+            elif st.op == "maxpool":
+                dests = self._dest_tensors(bufs, st.dests, l)
+                s = tm.begin()
+                ops.maxpool(T[st.inputs[0]], l.kernel, l.stride, l.padding, out=dests[0])
+                self.launches += 1
+                tm.end(s, "maxpool", 4 * (T[st.inputs[0]].numel() + dests[0].numel()))
+                self._extra_copies(dests[0], dests[1:])
+                T[st.layer] = dests[0]
+            elif st.op == "spp":
+                xin = T[st.inputs[0]]
+                firsts, rest = [], []
+                for g, ds in zip(st.spp_layers, st.spp_dests):
+                    ts = self._dest_tensors(bufs, ds, L[g])
+                    firsts.append(ts[0])
+                    rest.append(ts[1:])
+                    T[g] = ts[0]
+                s = tm.begin()
+                ops.spp(xin, [L[g].kernel for g in st.spp_layers], firsts)
+                self.launches += 1
+                tm.end(s, "spp", 4 * xin.numel() * (1 + len(firsts)))
+                for f, r in zip(firsts, rest):
+                    self._extra_copies(f, r)
+            elif st.op == "upsample":
+                dests = self._dest_tensors(bufs, st.dests, l)
+                s = tm.begin()
+                ops.upsample(T[st.inputs[0]], l.stride, l.alpha, out=dests[0])
+                self.launches += 1
+                tm.end(s, "upsample", 4 * (T[st.inputs[0]].numel() + dests[0].numel()))
+                self._extra_copies(dests[0], dests[1:])
+                T[st.layer] = dests[0]
+            elif st.op == "shortcut":
+                dests = self._dest_tensors(bufs, st.dests, l)
+                s = tm.begin()
+                ops.shortcut(T[st.inputs[0]], T[st.inputs[1]], l.alpha, l.beta, l.activation, out=dests[0],
+                             out2=dests[1] if len(dests) > 1 else None)
+                self.launches += 1
+                tm.end(s, "shortcut", 4 * dests[0].numel() * (2 + min(len(dests), 2)))
+                self._extra_copies(dests[0], dests[2:])
+                T[st.layer] = dests[0]
+            elif st.op == "concat":
+                s = tm.begin()
+                T[st.layer] = ops.concat([T[i] for i in st.inputs])
+                self.launches += 1
+                tm.end(s, "concat", 8 * T[st.layer].numel())
+            elif st.op == "yolo":
+                self._yolo(st, l, T)
+            elif st.op == "centernet":
+                xin = T[st.inputs[0]]
+                cls = l.in_shape[0] - 4
+                s = tm.begin()
+                out = ops.centernet_decode(xin[:, :cls], xin[:, cls:cls + 2], xin[:, cls + 2:], self.threshold,
+                                           int(l.params.get("max_detections", 100)), logits=True,
+                                           heatmap_bias=float(l.params.get("heatmap_bias", -2.19)),
+                                           batch_id_offset=self.batch_id_offset)
+                self.launches += 2
+                tm.end(s, "centernet_decode", 4 * self.batch * cls * l.in_shape[1] * l.in_shape[2])
+                self.centernet_out.append(out)
+                T[st.layer] = xin
+            elif st.op == "softmax":
+                xin = T[st.inputs[0]].contiguous()
+                s = tm.begin()
+                T[st.layer] = ops.softmax(xin, max(1, int(l.params.get("groups", 1))),
+                                          float(l.params.get("temperature", 1.0)))
+                self.launches += 1
+                tm.end(s, "softmax", 8 * xin.numel())
+                self.outputs[st.layer] = T[st.layer]
+            elif st.op == "region":
+                xin = T[st.inputs[0]].contiguous()
+                s = tm.begin()
+                T[st.layer] = ops.region_forward(xin, int(l.params.get("num", 1)), int(l.params.get("coords", 4)),
+                                                 int(l.params.get("classes", self.model.classes or 20)),
+                                                 bool(l.params.get("softmax", False)))
+                self.launches += 1
+                tm.end(s, "region", 8 * xin.numel())
+                self.outputs[st.layer] = T[st.layer]
+            elif st.op == "avgpool":
+                T[st.layer] = T[st.inputs[0]].mean(dim=(2, 3), keepdim=True)      # not on the epilogue path
+            elif st.op == "dropout":
+                T[st.layer] = T[st.inputs[0]]
+            else:
+                raise NotImplementedError(st.op)
+            if self.keep:
+                for p in st.produces:
+                    if p in self.keep and p in T:
+                        self.kept[p] = T[p]
+            # release tensors nobody reads any more
+            for t in st.inputs:
+                if self.plan.last_use.get(t) == si and t in T and t != -1:
+                    del T[t]
+                    bufs.pop(t, None)
+
+    def _conv(self, st: graph.Step, l: graph.Layer, T, bufs) -> None:
+        w = self.w[l.index]
+        xin = T[st.inputs[0]]
+        if not xin.is_contiguous():
+            self.contiguous_copies += 1
+        tm = self.timer
+        s = tm.begin()
+        raw = F.conv2d(xin, w["weights"], None, l.stride, l.padding, l.dilation, l.groups)
+        tm.end(s, "conv(cudnn)", 0)
+        if st.head_raw:
+            T[l.index] = raw                 # bias + activation are applied inside the YOLO decode
+            return
+        n = raw.numel()
+        bn = dict(gamma=w["scales"], beta=w["biases"], mean=w["rolling_mean"], var=w["rolling_var"],
+                  eps_mode=self.eps_mode) if l.batch_norm else dict(bias=w["biases"])
+        if st.fused_pool is not None:
+            pl = self.model.layers[st.fused_pool]
+            pd = self._dest_tensors(bufs, st.pool_dests, pl)
+            full = self._dest_tensors(bufs, st.dests, l, dense=raw) if st.keep_full else []
+            s = tm.begin()
+            ops.conv_epilogue(raw, y=full[0] if full else False, act=l.activation, pool=(2, 2, pl.padding),
+                              y_pool=pd[0], **bn)
+            self.launches += 1
+            tm.end(s, "epilogue+pool", 4 * n + 4 * pd[0].numel() + (4 * n if full else 0))
+            self._extra_copies(pd[0], pd[1:])
+            T[st.fused_pool] = pd[0]
+            if full:
+                self._extra_copies(full[0], full[1:])
+                T[l.index] = full[0]
+            return
+        out_layer = self.model.layers[st.fused_shortcut] if st.fused_shortcut is not None else l
+        dests = self._dest_tensors(bufs, st.dests, out_layer, dense=raw)
+        kw = {}
+        if st.fused_shortcut is not None:
+            kw = dict(residual=T[st.inputs[1]], res_alpha=out_layer.alpha, res_beta=out_layer.beta,
+                      res_act=out_layer.activation)
+        s = tm.begin()
+        ops.conv_epilogue(raw, y=dests[0], y2=dests[1] if len(dests) > 1 else None, act=l.activation, **bn, **kw)
+        self.launches += 1
+        nb = 4 * n * (1 + min(len(dests), 2) + (1 if kw else 0))
+        tm.end(s, "epilogue+shortcut" if kw else "epilogue", nb)
+        self._extra_copies(dests[0], dests[2:])
+        T[out_layer.index] = dests[0]
+
+    def _yolo(self, st: graph.Step, l: graph.Layer, T) -> None:
+        xin = T[st.inputs[0]]
+        mask = [int(m) for m in l.params["mask"]]
+        anchors = [int(a) for a in l.params["anchors"]]
+        classes = l.in_shape[0] // len(mask) - 5
+        tm = self.timer
+        if st.head_raw:
+            conv = self.model.layers[st.inputs[0]]
+            s = tm.begin()
+            ops.yolo_decode(xin, mask, anchors, classes, self.model.width, self.model.height, self.threshold,
+                            self.dets, raw=True, bias=self.w[conv.index]["biases"],
+                            batch_id_offset=self.batch_id_offset)
+            self.launches += 3
+            tm.end(s, "yolo_decode", 4 * xin.numel())
+            T[st.layer] = xin
+            return
+        s = tm.begin()
+        act = ops.yolo_activate(xin.contiguous(), len(mask), classes)
+        self.launches += 1
+        tm.end(s, "yolo_activate", 8 * xin.numel())
+        s = tm.begin()
+        ops.yolo_decode(act, mask, anchors, classes, self.model.width, self.model.height, self.threshold, self.dets,
+                        batch_id_offset=self.batch_id_offset)
+        self.launches += 3
+        tm.end(s, "yolo_decode", 4 * xin.numel())
+        T[st.layer] = act
+
+    # ------------------------------------------------------------------ results
+    def detections(self):
+        """Detections of the last forward in the reference's order (Model::detections):
+        (structured array, total count including records dropped for lack of capacity)."""
+        recs, total = self.dets.to_host()
+        parts = [recs]
+        for d, c in self.centernet_out:
+            per_image = ops.centernet_to_host(d, c)
+            parts.extend(per_image)
+            total += sum(len(p) for p in per_image)
+        return (np.concatenate(parts) if len(parts) > 1 else recs), total
+
+    def predict(self, host_batch: torch.Tensor, nms_threshold: Optional[float] = None):
+        """The call a user makes: host images in (pinned memory), detections out.  Mirrors
+        Model::predictBatchImageList (include/Model.h:951-1060) from the H2D copy on."""
+        x = host_batch.to(self.device, non_blocking=True)
+        self.forward(x)
+        recs, total = self.detections()
+        if nms_threshold is not None:
+            recs = ops.nms(recs, nms_threshold)
+        return recs, total
