@@ -128,7 +128,7 @@ def run_model(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     capi.lib()                                     # no library, no benchmark: there is no fallback path
-    torch.backends.cudnn.benchmark = True          # the reference picks its conv algorithm with cudnnFind*
+    torch.backends.cudnn.benchmark = not args.no_cudnn_benchmark   # the reference picks its conv algorithm with cudnnFind*
 
     doc, label = make_doc(args.workload)
     model = graph.parse_model(doc)
@@ -322,8 +322,11 @@ def run_sweep(args):
         bias = torch.from_numpy(synth.normal(SEED, f"sweepb{C}", C, 0, 0.1)).to(dev)
         base = torch.randn((B, C, H, W), device=dev, generator=torch.Generator(dev).manual_seed(SEED))
         xs = [base.clone() for _ in range(sets)]
-        for act in ["leaky", "mish", "swish", "logistic"]:
-            for pool in (False, True):
+        frm = base.clone() if args.sweep_residual else None
+        for act in args.sweep_acts.split(","):
+            for pool in {"none": (False,), "pool": (True,), "both": (False, True)}[args.sweep_pool]:
+                if pool and frm is not None:
+                    continue
                 oh = ops.maxpool_out_dim(H, 2, 2, 1)
                 yp = torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) if pool else None
 
@@ -331,24 +334,33 @@ def run_sweep(args):
                     if pool:
                         ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
                                           pool=(2, 2, 1), y_pool=yp)
+                    elif frm is not None:      # conv epilogue + the shortcut layer that follows it: 12 B / element
+                        ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
+                                          residual=frm, res_act="linear")
                     else:
                         ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act)
-                for i in range(args.warmup):
+                for i in range(max(args.warmup, sets)):
                     call(i)
+                torch.cuda.synchronize()
+                # one CUDA graph = one launch on each rotating input set; replays are timed with events, so the
+                # figure is device time per launch without the Python / ctypes launch cost in between
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for i in range(sets):
+                        call(i)
+                g.replay()
                 ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
                 torch.cuda.synchronize()
-                for i, (a, z) in enumerate(ev):
-                    a.record(); call(i); z.record()
+                for a, z in ev:
+                    a.record(); g.replay(); z.record()
                 torch.cuda.synchronize()
-                ts = sorted(a.elapsed_time(z) for a, z in ev)
+                ts = sorted(a.elapsed_time(z) / sets for a, z in ev)
                 med = ts[len(ts) // 2]
-                nbytes = (4 * n + 4 * yp.numel()) if pool else 8 * n
-                rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "MB": round(nbytes / 1e6, 1),
+                nbytes = (4 * n + 4 * yp.numel()) if pool else (12 * n if frm is not None else 8 * n)
+                rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "residual": frm is not None, "MB": round(nbytes / 1e6, 1),
                              "us_median": round(med * 1e3, 2), "us_min": round(ts[0] * 1e3, 2),
                              "GBps": round(nbytes / med / 1e6, 1), "frac_measured": round(nbytes / med / 1e6 / peak, 3),
                              "frac_8000": round(nbytes / med / 1e6 / 8000, 3)})
-                if pool:          # x was not modified; nothing to restore.  In-place runs keep re-activating x: refresh
-                    pass
         del xs
     for r in rows:
         print(json.dumps(r), file=sys.stderr)
@@ -357,7 +369,7 @@ def run_sweep(args):
                       "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
                       "dtype": "f32", "data": "synthetic", "peak": peak, "peak_source": peak_src,
                       "frac_min": min(fr), "frac_median": statistics.median(fr), "frac_max": max(fr),
-                      "config": {"workload": "isolated fused epilogue sweep", "l2": "rotating input sets > 400 MB"},
+                      "config": {"workload": "isolated fused epilogue sweep", "l2": "rotating input sets > 400 MB", "timing": "CUDA events around a CUDA-graph replay of one launch per input set"},
                       "cells": rows}), flush=True)
 
 
@@ -415,7 +427,11 @@ def main():
     ap.add_argument("--cpu-images", type=int, default=2, help="images per step of the CPU reference sample")
     ap.add_argument("--det-capacity", type=int, default=24 * (1 << 20))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep-shapes", type=int, default=0)
+    ap.add_argument("--sweep-shapes", type=int, default=0, help="only the first N shapes of the sweep")
+    ap.add_argument("--sweep-acts", default="leaky,mish,swish,logistic")
+    ap.add_argument("--sweep-pool", default="both", choices=["none", "pool", "both"])
+    ap.add_argument("--sweep-residual", action="store_true", help="sweep the epilogue fused with a shortcut add")
+    ap.add_argument("--no-cudnn-benchmark", action="store_true", help="skip cuDNN's algorithm search (profiling runs)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -441,3 +441,55 @@ def conv_forward(x, weights, filters, kernel, stride, pad, dilation=1):
                          dilation, _fp(col))
         out[b] = (wm @ col).reshape(filters, oh, ow)
     return out
+
+
+# -------------------------------------------------- reference CUDA library
+
+class RefCuda:
+    """The reference's own CUDA epilogue kernels compiled for sm_100a (``_ref/libpxref_cuda.so``).
+    Arguments are raw device pointers (``tensor.data_ptr()``); everything runs on the legacy
+    default stream, as in the reference."""
+
+    def __init__(self):
+        if not os.path.exists(REF_CUDA_SO):
+            raise FileNotFoundError(REF_CUDA_SO)
+        L = C.CDLL(REF_CUDA_SO)
+        vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+        protos = {
+            "pxrefcu_activate": [i, vp, sz],
+            "pxrefcu_add_bias": [vp, vp, i, i, i],
+            "pxrefcu_maxpool": [vp, vp, vp] + [i] * 9,
+            "pxrefcu_upsample": [vp, i, i, i, i, i, f, vp],
+            "pxrefcu_shortcut": [i, i, i, i, vp, i, i, i, f, f, vp],
+            "pxrefcu_yolo_activate": [vp, vp, i, i, i, i],
+            "pxrefcu_centernet_activate": [vp, vp, i, i, i, f],
+            "pxrefcu_fill": [vp, sz, f],
+            "pxrefcu_batchnorm_inference": [vp, vp, vp, vp, vp, i, i, i, i],
+            "pxrefcu_conv_epilogue_replay": [vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, i],
+            "pxrefcu_maxpool_replay": [vp, vp, vp, vp] + [i] * 9,
+            "pxrefcu_upsample_replay": [vp, vp, vp, i, i, i, i, i, f],
+            "pxrefcu_shortcut_replay": [vp, vp, vp, vp, i, i, i, i, f, f, i],
+            "pxrefcu_route_replay": [i, C.POINTER(vp), _i, vp, vp, i],
+            "pxrefcu_yolo_replay": [vp, vp, vp, vp, i, i, i, i],
+        }
+        for name, args in protos.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+        self.L = L
+
+    def call(self, name, *args):
+        rc = getattr(self.L, "pxrefcu_" + name)(*args)
+        if rc != 0:
+            raise RuntimeError(f"reference CUDA call {name} failed with {rc}")
+
+
+_ref_cuda = None
+
+
+def ref_cuda():
+    """The loaded reference CUDA library, or None when it was not built."""
+    global _ref_cuda
+    if _ref_cuda is None and os.path.exists(REF_CUDA_SO):
+        _ref_cuda = RefCuda()
+    return _ref_cuda

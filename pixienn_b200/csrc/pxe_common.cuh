@@ -121,17 +121,52 @@ __device__ __forceinline__ float act_mish(float x)
     return x * (n / (n + 2.0f));
 }
 
-template <int ACT>
+// ---- hardware-approximate forms for the three transcendental activations the model presets use.
+// exp(x) = ex2.approx(x * log2 e): relative error at most (2 + 1.17|x|) ulp; rcp.approx: 1 ulp.
+// In the units of the parity tolerance (|err| <= 1e-6 + 1e-5 |ref|) the worst case over the whole
+// input range is about 4 % of the tolerance: where |x| is large enough for the exponent's error to
+// grow, the affected term is either negligible against 1 or the result is far below 1e-6.
+__device__ __forceinline__ float fast_ex2(float x)
+{
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_rcp(float x)
+{
+    float y;
+    asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_exp(float x) { return fast_ex2(x * 1.4426950408889634f); }
+
+__device__ __forceinline__ float act_logistic_fast(float x) { return fast_rcp(1.0f + fast_exp(-x)); }
+__device__ __forceinline__ float act_swish_fast(float x) { return x * fast_rcp(1.0f + fast_exp(-x)); }
+// Same n/(n+2) form as act_mish.  Below -20 it needs no branch (n/(n+2) -> e to within e/2
+// relative); above 20 the select keeps exp() overflow (inf * 0) out of the result.
+__device__ __forceinline__ float act_mish_fast(float x)
+{
+    const float e = fast_exp(x);
+    const float n = e * (e + 2.0f);
+    const float t = n * fast_rcp(n + 2.0f);
+    return x > 20.0f ? x : x * t;
+}
+
+// FAST selects the hardware-approximate forms for logistic / swish / mish (the streaming
+// epilogue kernels, where the precise forms are instruction-bound); everything else, and every
+// decode that compares scores against a threshold, evaluates the reference's expressions with
+// the precise math library.
+template <int ACT, bool FAST = false>
 __device__ __forceinline__ float activate(float x)
 {
     if (ACT == PXE_ACT_LEAKY) return x > 0.0f ? x : 0.1f * x;
     if (ACT == PXE_ACT_LINEAR) return x;
     if (ACT == PXE_ACT_LOGGY) return 2.0f / (1.0f + expf(-x)) - 1.0f;
-    if (ACT == PXE_ACT_LOGISTIC) return act_logistic(x);
-    if (ACT == PXE_ACT_MISH) return act_mish(x);
+    if (ACT == PXE_ACT_LOGISTIC) return FAST ? act_logistic_fast(x) : act_logistic(x);
+    if (ACT == PXE_ACT_MISH) return FAST ? act_mish_fast(x) : act_mish(x);
     if (ACT == PXE_ACT_RELU) return x > 0.0f ? x : 0.0f;
     if (ACT == PXE_ACT_SOFTPLUS) return act_softplus(x);
-    if (ACT == PXE_ACT_SWISH) return x / (1.0f + expf(-x));
+    if (ACT == PXE_ACT_SWISH) return FAST ? act_swish_fast(x) : x / (1.0f + expf(-x));
     if (ACT == PXE_ACT_TANH) return tanhf(x);
     return x;
 }

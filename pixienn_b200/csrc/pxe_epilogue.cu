@@ -79,7 +79,7 @@ __device__ __forceinline__ float apply_one(float v, const PlaneEntry& t)
 {
     if (AFFINE) v = fmaf(t.a, v, t.b);
     if (ACT == PXE_ACT_YOLO_HEAD) return (t.chan & (1 << 30)) ? v : act_logistic(v);
-    return activate<ACT>(v);
+    return activate<ACT, true>(v);
 }
 
 __device__ __forceinline__ float residual_one(float v, float r, const EpiParams& p)

@@ -238,14 +238,17 @@ centernet_activate_kernel(const CnActParams p)
 constexpr int kCnTileH = 32, kCnTileW = 64, kCnThreads = 256;
 constexpr int kCnCells = kCnTileH * kCnTileW;
 constexpr int kCnMaxK = 1024;
+constexpr int kCnSortKeys = 8192;      // candidates per image the final kernel sorts in shared memory
 
 struct CnParams {
     pxe_centernet_decode_desc d;
     long long hbs, sbs, obs;
-    int tiles_x, tiles_y, slots;     // slots = classes * tiles_x * tiles_y per image
+    int tiles_x, tiles_y;
     int K;
-    unsigned long long* cand;        // [batch][slots][K] sortable keys
-    int* cand_cnt;                   // [batch][slots]
+    int cap;                         // candidate slots per image = blocks per image * K
+    float lo;                        // pre-filter: a cell with (value >= lo) false cannot reach the threshold
+    unsigned long long* cand;        // [batch][cap] sortable keys, unordered
+    int* cand_cnt;                   // [batch], zeroed before the launch
     pxe_detection* dets; int* counts;
 };
 
@@ -259,15 +262,15 @@ __device__ __forceinline__ float order_float(uint32_t u)
 {
     return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
-// Key orders candidates by score descending, then flat index ascending.
+// Key orders candidates by score descending, then flat index ascending.  Never 0.
 __device__ __forceinline__ unsigned long long cn_key(float score, uint32_t flat)
 {
     return ((unsigned long long)float_order(score) << 32) | (unsigned long long)(0xffffffffu - flat);
 }
 
-// Finds the k-th largest of n distinct 64-bit keys (k >= 1, k <= n) by most-significant-digit
-// radix selection, 8 bits per pass.  `get(i)` returns key i.  All threads of the block must
-// call; every thread returns the key.  hist: 256 ints of shared memory, sh: 2 x u64.
+// Finds the k-th largest of n distinct 64-bit keys (1 <= k <= n) by most-significant-digit radix
+// selection, 8 bits per pass.  `get(i)` returns key i.  All threads of the block must call; every
+// thread returns the key.  hist: 256 ints of shared memory, sh: 2 x u64.
 template <typename Get>
 __device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist, unsigned long long* sh)
 {
@@ -281,14 +284,27 @@ __device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist,
             if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 0xff)], 1);
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int acc = 0, digit = 255;
-            for (; digit > 0; --digit) {
-                if (acc + hist[digit] >= want) break;
-                acc += hist[digit];
+        if (threadIdx.x < 32) {
+            // lane L owns digits 255-8L .. 248-8L; find the digit where the running count from the
+            // top first reaches `want`
+            const int top = 255 - 8 * (int)threadIdx.x;
+            int mine = 0;
+            for (int j = 0; j < 8; ++j) mine += hist[top - j];
+            int incl = mine;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)threadIdx.x >= o) incl += t;
             }
-            sh[0] = prefix | ((unsigned long long)digit << shift);
-            sh[1] = (unsigned long long)(want - acc);
+            const int before = incl - mine;
+            if (before < want && incl >= want) {
+                int acc = before, digit = top;
+                for (int j = 0; j < 8; ++j) {
+                    if (acc + hist[top - j] >= want) { digit = top - j; break; }
+                    acc += hist[top - j];
+                }
+                sh[0] = prefix | ((unsigned long long)digit << shift);
+                sh[1] = (unsigned long long)(want - acc);
+            }
         }
         __syncthreads();
         prefix = sh[0];
@@ -299,12 +315,41 @@ __device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist,
     return prefix;
 }
 
+// Descending bitonic sort of keys[0..pow2) in shared memory.
+__device__ __forceinline__ void block_bitonic_desc(unsigned long long* keys, int pow2)
+{
+    for (int k = 2; k <= pow2; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < pow2; i += blockDim.x) {
+                const int l = i ^ j;
+                if (l > i) {
+                    const unsigned long long a = keys[i], c = keys[l];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (a < c) : (a > c)) { keys[i] = c; keys[l] = a; }
+                }
+            }
+            __syncthreads();
+        }
+}
+
+__device__ __forceinline__ float cn_score(const CnParams& p, float v)
+{
+    // the reference's activation expression (src/CenterNetKernels.cu:17), precise math: scores and
+    // therefore the kept indices are bit-identical to the reference's CUDA path
+    return p.d.heat_is_logit ? 1.0f / (1.0f + expf(-v)) : v;
+}
+
+// One block per (tile, class, image).  Shared memory holds the tile's pre-activation values
+// (logit + bias) with a one-cell halo.  The sigmoid is evaluated only where it can matter: for
+// cells that can reach the threshold, and for those of their neighbours whose pre-activation value
+// is not clearly smaller (the activation is non-decreasing, so a clearly smaller neighbour cannot
+// have a greater score; "clearly" leaves room for rounding in exp()).
 __global__ void __launch_bounds__(kCnThreads)
 centernet_peaks_kernel(const CnParams p)
 {
     __shared__ float tile[(kCnTileH + 2) * (kCnTileW + 2)];
     __shared__ unsigned long long keys[kCnCells];
-    __shared__ int n_keys;
+    __shared__ int n_keys, n_out, base;
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
 
@@ -314,33 +359,46 @@ centernet_peaks_kernel(const CnParams p)
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
     const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
-    if (threadIdx.x == 0) n_keys = 0;
+    if (threadIdx.x == 0) { n_keys = 0; n_out = 0; }
 
     constexpr int TW = kCnTileW + 2;
+    const float bias = p.d.heat_is_logit ? p.d.heatmap_bias : 0.0f;
     for (int i = threadIdx.x; i < (kCnTileH + 2) * TW; i += kCnThreads) {
         const int ly = i / TW, lx = i - ly * TW;
         const int gy = y0 + ly - 1, gx = x0 + lx - 1;
-        float s = -INFINITY;                       // outside the map: never greater than a score
+        float v = -INFINITY;                       // outside the map: never greater than a score
         if (gy >= 0 && gy < H && gx >= 0 && gx < W) {
-            s = heat[(long long)gy * W + gx];
-            if (p.d.heat_is_logit) s = 1.0f / (1.0f + expf(-(s + p.d.heatmap_bias)));
+            v = heat[(long long)gy * W + gx];
+            if (p.d.heat_is_logit) v += bias;      // same sum the reference forms before its sigmoid
         }
-        tile[i] = s;
+        tile[i] = v;
     }
     __syncthreads();
 
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
+    const bool logit = p.d.heat_is_logit != 0;
     for (int i = threadIdx.x; i < kCnCells; i += kCnThreads) {
         const int ly = i / kCnTileW, lx = i - ly * kCnTileW;
         const int gy = y0 + ly, gx = x0 + lx;
         if (gy >= H || gx >= W) continue;
         const float* c = tile + (ly + 1) * TW + (lx + 1);
-        const float s = c[0];
+        const float v = c[0];
+        if (!(v >= p.lo)) continue;
+        const float s = cn_score(p, v);
         // include/CenterNetLayer.h:212: finite, at or above the threshold, no strictly greater neighbour
         if (!isfinite(s) || s < p.d.threshold) continue;
-        if (c[-TW - 1] > s || c[-TW] > s || c[-TW + 1] > s || c[-1] > s || c[1] > s ||
-            c[TW - 1] > s || c[TW] > s || c[TW + 1] > s) continue;
+        const float near = logit ? v - 1e-4f * fmaxf(1.0f, fabsf(v)) : v;
+        bool peak = true;
+#pragma unroll
+        for (int dy = -1; dy <= 1; ++dy)
+#pragma unroll
+            for (int dx = -1; dx <= 1; ++dx) {
+                if (dy == 0 && dx == 0) continue;
+                const float u = c[dy * TW + dx];
+                if (u > near && cn_score(p, u) > s) peak = false;
+            }
+        if (!peak) continue;
         const long long idx = (long long)gy * W + gx;
         const float bw = size[idx] / W, bh = size[area + idx] / H;
         const float ox = off[idx], oy = off[area + idx];
@@ -351,74 +409,56 @@ centernet_peaks_kernel(const CnParams p)
     __syncthreads();
 
     const int n = n_keys;
-    const int slot_id = cls * (p.tiles_x * p.tiles_y) + blockIdx.x;
-    unsigned long long* out = p.cand + ((long long)b * p.slots + slot_id) * p.K;
+    if (n == 0) return;
+    unsigned long long* out = p.cand + (long long)b * p.cap;
     if (n <= p.K) {
-        for (int i = threadIdx.x; i < n; i += kCnThreads) out[i] = keys[i];
-        if (threadIdx.x == 0) p.cand_cnt[(long long)b * p.slots + slot_id] = n;
+        if (threadIdx.x == 0) base = atomicAdd(&p.cand_cnt[b], n);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += kCnThreads) out[base + i] = keys[i];
         return;
     }
-    // more candidates than can ever be kept from one image: keep this block's K best
+    // more candidates than can ever be kept from one image: pass on only this block's K best
     const unsigned long long kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
-    __shared__ int n_out;
-    if (threadIdx.x == 0) n_out = 0;
+    if (threadIdx.x == 0) base = atomicAdd(&p.cand_cnt[b], p.K);
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += kCnThreads)
-        if (keys[i] >= kth) out[atomicAdd(&n_out, 1)] = keys[i];
-    if (threadIdx.x == 0) p.cand_cnt[(long long)b * p.slots + slot_id] = p.K;
+        if (keys[i] >= kth) out[base + atomicAdd(&n_out, 1)] = keys[i];
 }
 
-// One block per image: the K best of all slots' candidates, sorted, decoded to boxes.
+// One block per image: the K best of the image's candidates, sorted, decoded to boxes.
 __global__ void __launch_bounds__(1024)
 centernet_topk_kernel(const CnParams p)
 {
-    __shared__ unsigned long long best[kCnMaxK];
+    extern __shared__ unsigned long long sorted[];       // kCnSortKeys entries
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
-    __shared__ int n_total, n_best;
+    __shared__ int n_best;
     const int b = blockIdx.x;
-    const unsigned long long* cand = p.cand + (long long)b * p.slots * p.K;
-    const int* cnt = p.cand_cnt + (long long)b * p.slots;
-    if (threadIdx.x == 0) { n_total = 0; n_best = 0; }
-    __syncthreads();
-    int local = 0;
-    for (int s = threadIdx.x; s < p.slots; s += blockDim.x) local += cnt[s];
-    if (local) atomicAdd(&n_total, local);
-    __syncthreads();
-    const int n = n_total;
-    const int span = p.slots * p.K;
-    // key i of the image lives at cand[i] when (i % K) < cnt[i / K]; absent entries read as 0,
-    // which is below every real key (real keys have bit 63 or the index bits set... a real key
-    // is never 0 because its low word is 0xffffffff - flat with flat < 2^32 - 1).
-    auto get = [&](int i) -> unsigned long long {
-        const int s = i / p.K;
-        return (i - s * p.K) < cnt[s] ? cand[i] : 0ULL;
-    };
-    unsigned long long kth = 1;      // every real key is >= 1
-    if (n > p.K) kth = block_select_kth(get, span, p.K, hist, sel);
-    for (int i = threadIdx.x; i < span; i += blockDim.x) {
-        const unsigned long long key = get(i);
-        if (key >= kth && key != 0ULL) best[atomicAdd(&n_best, 1)] = key;
-    }
-    __syncthreads();
-    const int m = n_best;
-    // bitonic sort, descending, over the next power of two (padding with 0 = smallest)
-    int pow2 = 1;
-    while (pow2 < m) pow2 <<= 1;
-    for (int i = m + threadIdx.x; i < pow2; i += blockDim.x) best[i] = 0ULL;
-    __syncthreads();
-    for (int k = 2; k <= pow2; k <<= 1)
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int i = threadIdx.x; i < pow2; i += blockDim.x) {
-                const int l = i ^ j;
-                if (l > i) {
-                    const unsigned long long a = best[i], c = best[l];
-                    const bool desc = (i & k) == 0;
-                    if (desc ? (a < c) : (a > c)) { best[i] = c; best[l] = a; }
-                }
-            }
-            __syncthreads();
+    const unsigned long long* cand = p.cand + (long long)b * p.cap;
+    const int n = p.cand_cnt[b];
+    int m;
+    if (n <= kCnSortKeys) {
+        int pow2 = 1;
+        while (pow2 < n) pow2 <<= 1;
+        for (int i = threadIdx.x; i < pow2; i += blockDim.x) sorted[i] = i < n ? cand[i] : 0ULL;
+        __syncthreads();
+        block_bitonic_desc(sorted, pow2);
+        m = n < p.K ? n : p.K;
+    } else {
+        if (threadIdx.x == 0) n_best = 0;
+        const unsigned long long kth = block_select_kth([&](int i) { return cand[i]; }, n, p.K, hist, sel);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const unsigned long long key = cand[i];
+            if (key >= kth) sorted[atomicAdd(&n_best, 1)] = key;
         }
+        __syncthreads();
+        m = n_best;                                      // == K: keys are distinct
+        int pow2 = 1;
+        while (pow2 < m) pow2 <<= 1;
+        for (int i = m + threadIdx.x; i < pow2; i += blockDim.x) sorted[i] = 0ULL;
+        __syncthreads();
+        block_bitonic_desc(sorted, pow2);
+    }
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
     const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
@@ -426,7 +466,7 @@ centernet_topk_kernel(const CnParams p)
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
     for (int i = threadIdx.x; i < m; i += blockDim.x) {
-        const unsigned long long key = best[i];
+        const unsigned long long key = sorted[i];
         const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
         const float score = order_float((uint32_t)(key >> 32));
         const int cls = (int)(flat / area);
@@ -621,21 +661,34 @@ extern "C" int pxe_centernet_activate(pxe_stream_t stream, const float* in, floa
     return PXE_OK;
 }
 
-static void cn_geometry(int classes, int height, int width, int* tiles_x, int* tiles_y, int* slots)
+static void cn_geometry(int classes, int height, int width, int* tiles_x, int* tiles_y, long long* blocks_per_image)
 {
     *tiles_x = (width + kCnTileW - 1) / kCnTileW;
     *tiles_y = (height + kCnTileH - 1) / kCnTileH;
-    *slots = classes * *tiles_x * *tiles_y;
+    *blocks_per_image = (long long)classes * *tiles_x * *tiles_y;
 }
 
 extern "C" size_t pxe_centernet_decode_workspace_bytes(int batch, int classes, int height, int width,
                                                        int max_detections)
 {
     if (batch <= 0 || classes <= 0 || height <= 0 || width <= 0 || max_detections <= 0) return 0;
-    int tx, ty, slots;
-    cn_geometry(classes, height, width, &tx, &ty, &slots);
-    return align_up((size_t)batch * slots * max_detections * sizeof(unsigned long long), 256)
-           + align_up((size_t)batch * slots * sizeof(int), 256);
+    int tx, ty;
+    long long bpi;
+    cn_geometry(classes, height, width, &tx, &ty, &bpi);
+    return align_up((size_t)batch * bpi * max_detections * sizeof(unsigned long long), 256)
+           + align_up((size_t)batch * sizeof(int), 256);
+}
+
+// Pre-activation value below which sigmoid(v) < threshold for certain (with a margin far wider
+// than any rounding in exp()).
+static float centernet_prefilter(const pxe_centernet_decode_desc& d)
+{
+    if (!d.heat_is_logit) return d.threshold;                 // "(v >= thr) false" is exactly "v < thr or NaN"
+    if (!(d.threshold > 0.0f)) return -INFINITY;
+    if (d.threshold >= 1.0f) return 15.0f;                    // sigmoid(v) rounds to 1 only for v > 16.6
+    const double t = (double)d.threshold;
+    const double logit = log(t / (1.0 - t));
+    return (float)(logit - 1e-3 - 1e-3 * fabs(logit));
 }
 
 extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_decode_desc* dp,
@@ -664,20 +717,30 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     p.hbs = d.heat_batch_stride ? d.heat_batch_stride : area * d.classes;
     p.sbs = d.size_batch_stride ? d.size_batch_stride : 2 * area;
     p.obs = d.offset_batch_stride ? d.offset_batch_stride : 2 * area;
-    cn_geometry(d.classes, d.height, d.width, &p.tiles_x, &p.tiles_y, &p.slots);
-    PXE_REQUIRE((long long)p.slots * d.max_detections < 0x7fffffffLL, "centernet_decode: candidate table too large");
+    long long bpi;
+    cn_geometry(d.classes, d.height, d.width, &p.tiles_x, &p.tiles_y, &bpi);
+    PXE_REQUIRE(bpi * d.max_detections < 0x7fffffffLL, "centernet_decode: candidate table too large");
     p.K = d.max_detections;
+    p.cap = (int)(bpi * d.max_detections);
+    p.lo = centernet_prefilter(d);
     char* ws = static_cast<char*>(workspace);
     p.cand = reinterpret_cast<unsigned long long*>(ws);
-    ws += align_up((size_t)d.batch * p.slots * p.K * sizeof(unsigned long long), 256);
+    ws += align_up((size_t)d.batch * p.cap * sizeof(unsigned long long), 256);
     p.cand_cnt = reinterpret_cast<int*>(ws);
     p.dets = dets; p.counts = counts;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    static const int smem_ready = [] {
+        return (int)cudaFuncSetAttribute(centernet_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(kCnSortKeys * sizeof(unsigned long long)));
+    }();
+    if (smem_ready != (int)cudaSuccess)
+        return set_error(PXE_ERR_CUDA, "centernet_decode: cannot reserve %zu bytes of shared memory", kCnSortKeys * sizeof(unsigned long long));
+    PXE_CUDA_OK(cudaMemsetAsync(p.cand_cnt, 0, (size_t)d.batch * sizeof(int), s));
     dim3 grid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, (unsigned)d.batch);
     centernet_peaks_kernel<<<grid, kCnThreads, 0, s>>>(p);
     PXE_LAUNCH_OK("centernet_peaks_kernel");
-    centernet_topk_kernel<<<(unsigned)d.batch, 1024, 0, s>>>(p);
+    centernet_topk_kernel<<<(unsigned)d.batch, 1024, kCnSortKeys * sizeof(unsigned long long), s>>>(p);
     PXE_LAUNCH_OK("centernet_topk_kernel");
     return PXE_OK;
 }
