@@ -344,15 +344,15 @@ def run_sweep(args):
                 torch.cuda.synchronize()
                 # one CUDA graph = one launch on each rotating input set; replays are timed with events, so the
                 # figure is device time per launch without the Python / ctypes launch cost in between
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg):
                     for i in range(sets):
                         call(i)
-                g.replay()
+                cg.replay()
                 ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
                 torch.cuda.synchronize()
                 for a, z in ev:
-                    a.record(); g.replay(); z.record()
+                    a.record(); cg.replay(); z.record()
                 torch.cuda.synchronize()
                 ts = sorted(a.elapsed_time(z) / sets for a, z in ev)
                 med = ts[len(ts) // 2]

@@ -238,7 +238,6 @@ centernet_activate_kernel(const CnActParams p)
 constexpr int kCnTileH = 32, kCnTileW = 64, kCnThreads = 256;
 constexpr int kCnCells = kCnTileH * kCnTileW;
 constexpr int kCnMaxK = 1024;
-constexpr int kCnSortKeys = 8192;      // candidates per image the final kernel sorts in shared memory
 
 struct CnParams {
     pxe_centernet_decode_desc d;
@@ -349,7 +348,8 @@ centernet_peaks_kernel(const CnParams p)
 {
     __shared__ float tile[(kCnTileH + 2) * (kCnTileW + 2)];
     __shared__ unsigned long long keys[kCnCells];
-    __shared__ int n_keys, n_out, base;
+    __shared__ unsigned short work[kCnCells];
+    __shared__ int n_keys, n_out, n_work, base;
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
 
@@ -359,7 +359,7 @@ centernet_peaks_kernel(const CnParams p)
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
     const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
-    if (threadIdx.x == 0) { n_keys = 0; n_out = 0; }
+    if (threadIdx.x == 0) { n_keys = 0; n_out = 0; n_work = 0; }
 
     constexpr int TW = kCnTileW + 2;
     const float bias = p.d.heat_is_logit ? p.d.heatmap_bias : 0.0f;
@@ -375,16 +375,25 @@ centernet_peaks_kernel(const CnParams p)
     }
     __syncthreads();
 
+    // pass A: cells that can reach the threshold at all (about one in ten for a typical heatmap) go on a
+    // work list, so that pass B runs the expensive tests with every lane busy
+    for (int i = threadIdx.x; i < kCnCells; i += kCnThreads) {
+        const int ly = i / kCnTileW, lx = i - ly * kCnTileW;
+        if (y0 + ly >= H || x0 + lx >= W) continue;
+        if (tile[(ly + 1) * TW + (lx + 1)] >= p.lo) work[atomicAdd(&n_work, 1)] = (unsigned short)i;
+    }
+    __syncthreads();
+
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
     const bool logit = p.d.heat_is_logit != 0;
-    for (int i = threadIdx.x; i < kCnCells; i += kCnThreads) {
+    const int todo = n_work;
+    for (int wi = threadIdx.x; wi < todo; wi += kCnThreads) {
+        const int i = work[wi];
         const int ly = i / kCnTileW, lx = i - ly * kCnTileW;
         const int gy = y0 + ly, gx = x0 + lx;
-        if (gy >= H || gx >= W) continue;
         const float* c = tile + (ly + 1) * TW + (lx + 1);
         const float v = c[0];
-        if (!(v >= p.lo)) continue;
         const float s = cn_score(p, v);
         // include/CenterNetLayer.h:212: finite, at or above the threshold, no strictly greater neighbour
         if (!isfinite(s) || s < p.d.threshold) continue;
@@ -426,10 +435,14 @@ centernet_peaks_kernel(const CnParams p)
 }
 
 // One block per image: the K best of the image's candidates, sorted, decoded to boxes.
-__global__ void __launch_bounds__(1024)
+// Few candidates are sorted outright; otherwise the K-th largest key is found by radix selection
+// (8 passes over the list, which sits in L2) and only the K winners are sorted.
+constexpr int kCnTopkThreads = 256;
+
+__global__ void __launch_bounds__(kCnTopkThreads)
 centernet_topk_kernel(const CnParams p)
 {
-    extern __shared__ unsigned long long sorted[];       // kCnSortKeys entries
+    __shared__ unsigned long long sorted[kCnMaxK];
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
     __shared__ int n_best;
@@ -437,7 +450,7 @@ centernet_topk_kernel(const CnParams p)
     const unsigned long long* cand = p.cand + (long long)b * p.cap;
     const int n = p.cand_cnt[b];
     int m;
-    if (n <= kCnSortKeys) {
+    if (n <= p.K || n <= 256) {
         int pow2 = 1;
         while (pow2 < n) pow2 <<= 1;
         for (int i = threadIdx.x; i < pow2; i += blockDim.x) sorted[i] = i < n ? cand[i] : 0ULL;
@@ -730,17 +743,11 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     p.dets = dets; p.counts = counts;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    static const int smem_ready = [] {
-        return (int)cudaFuncSetAttribute(centernet_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(kCnSortKeys * sizeof(unsigned long long)));
-    }();
-    if (smem_ready != (int)cudaSuccess)
-        return set_error(PXE_ERR_CUDA, "centernet_decode: cannot reserve %zu bytes of shared memory", kCnSortKeys * sizeof(unsigned long long));
     PXE_CUDA_OK(cudaMemsetAsync(p.cand_cnt, 0, (size_t)d.batch * sizeof(int), s));
     dim3 grid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, (unsigned)d.batch);
     centernet_peaks_kernel<<<grid, kCnThreads, 0, s>>>(p);
     PXE_LAUNCH_OK("centernet_peaks_kernel");
-    centernet_topk_kernel<<<(unsigned)d.batch, 1024, kCnSortKeys * sizeof(unsigned long long), s>>>(p);
+    centernet_topk_kernel<<<(unsigned)d.batch, kCnTopkThreads, 0, s>>>(p);
     PXE_LAUNCH_OK("centernet_topk_kernel");
     return PXE_OK;
 }
