@@ -19,7 +19,8 @@
  *    pxe_last_error_string() returns the message of the calling thread's most
  *    recent failure.
  *  - Functions are re-entrant; there is no global mutable state apart from a
- *    per-device cache of immutable device properties.
+ *    per-device cache of immutable device properties (and, for
+ *    pxe_yolo_decode_static only, the shared scratch array its comment describes).
  */
 #ifndef PXE_H
 #define PXE_H
@@ -227,6 +228,31 @@ PXE_API size_t pxe_yolo_decode_workspace_bytes(int batch, int height, int width)
 PXE_API int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* desc, pxe_detection* dets,
                             long long capacity, long long* count, void* workspace,
                             size_t workspace_bytes);
+
+/*
+ * pxe_yolo_decode with no workspace argument.  This entry point has no counterpart in the
+ * reference; it exists for callers that have no way to obtain device memory at the point where
+ * they decode: PixieNN's own addDetects runs inside Model::detections(), a per-frame call on
+ * objects that are not meant to grow there, and a host application that handed the engine a fixed
+ * memory budget at start-up (or forbids allocation once its real-time loop runs, since cudaMalloc
+ * stalls the whole device) cannot satisfy a "bring a scratch buffer" contract either.
+ *
+ * The scratch lives in a fixed array inside the library (PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES,
+ * resident on every GPU that loads the library for the life of the process).  A head whose
+ * pxe_yolo_decode_workspace_bytes() exceeds that size is refused with PXE_ERR_WORKSPACE; 4 MiB
+ * covers 64 images of a 76x76 head (1.5 MB).  Nothing is allocated or freed, by this function or
+ * by anything it calls.
+ *
+ * - The first call on each device looks up the array's device address (that device must be
+ *   current); make that first call before starting any stream capture.
+ * - All calls on a device share the one array.  The decode overwrites every scratch word it later
+ *   reads, so leftovers of an earlier call are harmless, but two decodes that may run at the same
+ *   time on the GPU (different streams) would corrupt each other: serialise them, or give the
+ *   concurrent ones their own workspace through pxe_yolo_decode.
+ */
+#define PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+PXE_API int pxe_yolo_decode_static(pxe_stream_t stream, const pxe_yolo_decode_desc* desc, pxe_detection* dets,
+                                   long long capacity, long long* count);
 
 /* ------------------------------------------------------------------------------------------
  * CenterNet head

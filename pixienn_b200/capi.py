@@ -92,6 +92,7 @@ PROTOTYPES = {
     "pxe_yolo_activate": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "pxe_yolo_decode_workspace_bytes": (_sz, [_i, _i, _i]),
     "pxe_yolo_decode": (_i, [_vp, C.POINTER(YoloDecodeDesc), _vp, _ll, _vp, _vp, _sz]),
+    "pxe_yolo_decode_static": (_i, [_vp, C.POINTER(YoloDecodeDesc), _vp, _ll, _vp]),
     "pxe_centernet_activate": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
     "pxe_centernet_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "pxe_centernet_decode": (_i, [_vp, C.POINTER(CenterNetDecodeDesc), _vp, _vp, _vp, _sz]),

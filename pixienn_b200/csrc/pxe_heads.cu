@@ -3,6 +3,7 @@
 // whole head tensor back (include/cuda/YoloLayer.h:168-188, include/cuda/CenterNetLayer.h:89-106,
 // include/cuda/RegionLayer.h:39-54); here only the compacted detections leave the GPU.
 #include <climits>
+#include <mutex>
 
 #include "pxe_common.cuh"
 
@@ -644,6 +645,45 @@ extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* 
     yolo_emit_kernel<<<grid, kYoloThreads, 0, s>>>(p);
     PXE_LAUNCH_OK("yolo_emit_kernel");
     return PXE_OK;
+}
+
+// ------------------------------------------------------------- YOLO decode without a caller workspace
+// The scratch of pxe_yolo_decode (per-cell counts, per-block sums and offsets) held in the library's
+// own device image instead of a buffer the caller allocates.  Every GPU that loads the library
+// carries these bytes until the process exits, so the size is kept modest.
+static __device__ __align__(256) unsigned char g_yolo_static_scratch[PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[64];      // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int pxe_yolo_decode_static(pxe_stream_t stream, const pxe_yolo_decode_desc* dp, pxe_detection* dets,
+                                      long long capacity, long long* count)
+{
+    PXE_REQUIRE(dp != nullptr, "yolo_decode_static: null descriptor");
+    PXE_REQUIRE(dp->batch > 0 && dp->height > 0 && dp->width > 0, "yolo_decode_static: non-positive shape");
+    const size_t need = pxe_yolo_decode_workspace_bytes(dp->batch, dp->height, dp->width);
+    if (need > (size_t)PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES)
+        return set_error(PXE_ERR_WORKSPACE,
+                         "yolo_decode_static: a %d x %d x %d head needs %zu bytes of scratch, the built-in array holds %zu; "
+                         "use pxe_yolo_decode with a workspace of your own",
+                         dp->batch, dp->height, dp->width, need, (size_t)PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES);
+    int dev = 0;
+    PXE_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(PXE_ERR_UNSUPPORTED, "yolo_decode_static: device ordinal %d out of range", dev);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (g_static_scratch_ptr[dev] == nullptr) {
+            // In host code the array's name is only a handle; kernels need its address on the current device.
+            void* p = nullptr;
+            PXE_CUDA_OK(cudaGetSymbolAddress(&p, g_yolo_static_scratch));
+            g_static_scratch_ptr[dev] = p;
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    return pxe_yolo_decode(stream, dp, dets, capacity, count, scratch, (size_t)PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES);
 }
 
 // --------------------------------------------------------------------------------- CenterNet API
