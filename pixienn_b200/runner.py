@@ -93,6 +93,7 @@ class Runner:
             i: {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in d.items()}
             for i, d in weights.items()}
         self.dets = ops.DetectionBuffer(det_capacity, device)
+        self.head_marks = []           # device copies of the running detection count after each YOLO head
         self.centernet_out = []        # (dets, counts) per centernet layer of the last forward
         self.outputs: Dict[int, torch.Tensor] = {}     # softmax / region outputs of the last forward
         self.timer = OpTimer()
@@ -134,7 +135,7 @@ class Runner:
         T: Dict[int, torch.Tensor] = {-1: x}
         bufs: Dict[int, torch.Tensor] = {}
         self.dets.reset()
-        self.centernet_out, self.outputs, self.kept = [], {}, {}
+        self.centernet_out, self.outputs, self.kept, self.head_marks = [], {}, {}, []
         self.launches = 0
         tm = self.timer
         for si, st in enumerate(self.plan.steps):
@@ -296,6 +297,7 @@ class Runner:
                             batch_id_offset=self.batch_id_offset)
             self.launches += 3
             tm.end(s, "yolo_decode", 4 * xin.numel())
+            self.head_marks.append(self.dets.count.clone())
             T[st.layer] = xin
             return
         s = tm.begin()
@@ -307,6 +309,7 @@ class Runner:
                         batch_id_offset=self.batch_id_offset)
         self.launches += 3
         tm.end(s, "yolo_decode", 4 * xin.numel())
+        self.head_marks.append(self.dets.count.clone())
         T[st.layer] = act
 
     # ------------------------------------------------------------------ results
@@ -320,6 +323,16 @@ class Runner:
             parts.extend(per_image)
             total += sum(len(p) for p in per_image)
         return (np.concatenate(parts) if len(parts) > 1 else recs), total
+
+    def detections_by_head(self):
+        """Per-head record arrays of the last forward (input to sharding.merge_shards)."""
+        from . import sharding
+        recs, _ = self.dets.to_host()
+        ends = [min(int(m.item()), len(recs)) for m in self.head_marks]
+        heads = sharding.split_heads(recs, ends)
+        for d, c in self.centernet_out:
+            heads.append(np.concatenate(ops.centernet_to_host(d, c)))
+        return heads
 
     def predict(self, host_batch: torch.Tensor, nms_threshold: Optional[float] = None):
         """The call a user makes: host images in (pinned memory), detections out.  Mirrors

@@ -107,23 +107,18 @@ def test_tiny416_matches_cpu_reference_path(cuda, oracle):
 
 def test_batch_sharding_gives_identical_detections(cuda):
     """Every op is per-image: running images [0,2) and [2,4) as two shards (batch_id_offset marks the
-    global image number) reproduces the 4-image run record for record."""
+    global image number) and merging per head reproduces the 4-image run record for record."""
+    from pixienn_b200 import sharding
     model = graph.parse_model(presets.yolov3_tiny(160, 160))
     weights = synth_weights(model, 5, head_bias=-3.0)
     x = make_input(6, 4, model)
     whole, n = run(model, weights, x, cuda).detections()
-    parts = []
+    shards = []
     for s in range(2):
-        r = Runner(model, weights, 2, cuda, batch_id_offset=2 * s)
-        r.forward(dev(x[2 * s:2 * s + 2], cuda))
-        parts.append(r.detections()[0])
-    merged = np.concatenate(parts)
-    # the host-side gather only has to regroup records by head; compare as sorted multisets
-    fields = ["batch_id", "source", "class_id", "prob", "x", "y", "w", "h"]
-    assert n == len(whole) == len(merged)
-    assert np.sort(merged, order=fields).tobytes() == np.sort(whole, order=fields).tobytes()
-    # and inside one head the shard order is already the global order
-    first_head = whole[:np.argmax(np.diff(whole["batch_id"]) < 0) + 1] if (np.diff(whole["batch_id"]) < 0).any() else whole
-    got_first = np.concatenate([p[:np.argmax(np.diff(p["batch_id"]) < 0) + 1] if (np.diff(p["batch_id"]) < 0).any() else p
-                                for p in parts])
-    assert got_first.tobytes() == first_head.tobytes()
+        first, last = sharding.shard_range(4, s, 2)
+        r = Runner(model, weights, last - first, cuda, batch_id_offset=first)
+        r.forward(dev(x[first:last], cuda))
+        shards.append(r.detections_by_head())
+    merged = sharding.merge_shards(shards)
+    assert n == len(whole) == len(merged) and n > 0
+    assert merged.tobytes() == whole.tobytes()
