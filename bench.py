@@ -18,6 +18,7 @@ Other workloads (not run by default): --workload sweep (the isolated fused-epilo
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
 import statistics
@@ -416,6 +417,137 @@ def run_centernet(args):
           flush=True)
 
 
+def run_epilogue_compare(args):
+    """Epilogue path only (no convolutions), layer by layer over the model graph, on scratch buffers of
+    each layer's shape: the reference's own CUDA call sequences (its src/*.cu compiled for sm_100a in
+    oracle/_ref/libpxref_cuda.so: fills, cuDNN BN inference, preActivation copy, thrust activation, per-image
+    route copies, shortcut copy + kernel + activation, YOLO activate + full device-to-host copy) against
+    this library's planned launches.  Reports milliseconds per batch for both and the ratio."""
+    import torch
+    from oracle import pxoracle as po
+    from pixienn_b200 import graph, ops
+    from pixienn_b200.runner import synth_weights
+    dev = torch.device("cuda", 0)
+    doc, label = make_doc(args.model)
+    model = graph.parse_model(doc)
+    B = args.batch
+    L = model.layers
+    ref = po.ref_cuda()
+    weights = synth_weights(model, SEED)
+    wd = {i: {k: torch.from_numpy(v).to(dev) for k, v in d.items() if k != "weights"} for i, d in weights.items()}
+    # the same scratch data is transformed in place by every layer and every repetition: neutral BN statistics keep
+    # it bounded, and a negative head bias keeps the decode at the few-detections regime of a trained network
+    for i, d in wd.items():
+        if "scales" in d:
+            d["scales"].fill_(1.0); d["biases"].zero_(); d["rolling_mean"].zero_(); d["rolling_var"].fill_(1.0)
+        else:
+            d["biases"].fill_(-6.0)
+    biggest = max(l.out_elems for l in L) * B
+    big = [torch.empty(biggest, device=dev) for _ in range(5)]       # out, delta, preact, scratch, other
+    for t in big:
+        t.normal_()
+    host = torch.empty(max(l.out_elems for l in L if l.type == "yolo") * B).pin_memory()
+    idx = torch.empty(biggest // 4 + 1, device=dev, dtype=torch.int32)
+    ptr = lambda t: t.data_ptr()
+
+    def reference_pass():
+        for l in L:
+            c, h, w = l.out_shape
+            n = B * c * h * w
+            if l.type == "conv":
+                p = wd[l.index]
+                if l.batch_norm:
+                    ref.call("conv_epilogue_replay", ptr(big[0]), ptr(big[1]), ptr(big[2]), ptr(big[3]), B, c, h, w,
+                             ptr(p["scales"]), ptr(p["biases"]), ptr(p["rolling_mean"]), ptr(p["rolling_var"]), None,
+                             po.ACT[l.activation])
+                else:
+                    ref.call("conv_epilogue_replay", ptr(big[0]), ptr(big[1]), ptr(big[2]), ptr(big[3]), B, c, h, w,
+                             None, None, None, None, ptr(p["biases"]), po.ACT[l.activation])
+            elif l.type == "shortcut":
+                ref.call("shortcut_replay", ptr(big[0]), ptr(big[4]), ptr(big[2]), ptr(big[1]), B, c, h, w, l.alpha, l.beta,
+                         po.ACT[l.activation])
+            elif l.type == "upsample":
+                ic, ih, iw = l.in_shape
+                ref.call("upsample_replay", ptr(big[0]), ptr(big[2]), ptr(big[1]), B, ic, ih, iw, l.stride, l.alpha)
+            elif l.type == "maxpool":
+                ic, ih, iw = l.in_shape
+                ref.call("maxpool_replay", ptr(big[0]), ptr(big[2]), ptr(big[1]), ptr(idx), B, ic, ih, iw, h, w, l.kernel,
+                         l.stride, l.padding)
+            elif l.type == "route":
+                srcs = (C.c_void_p * len(l.sources))(*[ptr(big[0]) for _ in l.sources])
+                outs = (C.c_int * len(l.sources))(*[L[s].out_elems for s in l.sources])
+                ref.call("route_replay", len(l.sources), srcs, outs, ptr(big[2]), ptr(big[1]), B)
+            elif l.type == "yolo":
+                masks = len(l.params["mask"])
+                ref.call("yolo_replay", ptr(big[0]), ptr(big[2]), ptr(big[1]), ptr(host), B, masks, c // masks - 5, h * w)
+
+    plan = graph.plan(model)
+    dets = ops.DetectionBuffer(args.det_capacity, dev)
+
+    def view(i, layer):
+        c, h, w = layer.out_shape
+        return big[i][:B * c * h * w].view(B, c, h, w)
+
+    def our_pass():
+        dets.reset()
+        for st in plan.steps:
+            l = L[st.layer]
+            if st.op == "conv":
+                p = wd[l.index]
+                x = view(0, l)
+                if st.head_raw:
+                    continue
+                bn = dict(gamma=p["scales"], beta=p["biases"], mean=p["rolling_mean"], var=p["rolling_var"]) if l.batch_norm \
+                    else dict(bias=p["biases"])
+                if st.fused_pool is not None:
+                    ops.conv_epilogue(x, y=x if st.keep_full else False, act=l.activation, pool=(2, 2, L[st.fused_pool].padding),
+                                      y_pool=view(2, L[st.fused_pool]), **bn)
+                elif st.fused_shortcut is not None:
+                    ops.conv_epilogue(x, y2=view(2, l) if len(st.dests) > 1 else None, act=l.activation, residual=view(4, l), **bn)
+                else:
+                    ops.conv_epilogue(x, y2=view(2, l) if len(st.dests) > 1 else None, act=l.activation, **bn)
+            elif st.op == "shortcut":
+                ops.shortcut(view(0, l), view(4, l), l.alpha, l.beta, l.activation, out=view(2, l))
+            elif st.op == "upsample":
+                src = big[0][:B * l.in_shape[0] * l.in_shape[1] * l.in_shape[2]].view(B, *l.in_shape)
+                ops.upsample(src, l.stride, l.alpha, out=view(2, l))
+            elif st.op == "maxpool":
+                src = big[0][:B * l.in_shape[0] * l.in_shape[1] * l.in_shape[2]].view(B, *l.in_shape)
+                ops.maxpool(src, l.kernel, l.stride, l.padding, out=view(2, l))
+            elif st.op == "spp":
+                src = big[0][:B * l.in_shape[0] * l.in_shape[1] * l.in_shape[2]].view(B, *l.in_shape)
+                outs = [big[2][k * src.numel():(k + 1) * src.numel()].view_as(src) for k in range(len(st.spp_layers))]
+                ops.spp(src, [L[g].kernel for g in st.spp_layers], outs)
+            elif st.op == "yolo":
+                conv = L[st.inputs[0]]
+                ops.yolo_decode(view(0, l), l.params["mask"], l.params["anchors"], l.in_shape[0] // len(l.params["mask"]) - 5,
+                                model.width, model.height, CONF, dets, raw=True, bias=wd[conv.index]["biases"])
+
+    def timed(fn):
+        for _ in range(max(1, args.warmup // 2)):
+            fn()
+        torch.cuda.synchronize()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        z.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(z) / args.steps
+
+    ours = timed(our_pass)
+    refms = timed(reference_pass) if ref is not None else None
+    print(json.dumps({"metric": f"{label} epilogue path only, ms per {B}-image batch", "value": round(ours, 3), "unit": "ms",
+                      "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "f32",
+                      "data": "synthetic", "reference_cuda_ms": round(refms, 3) if refms else None,
+                      "speedup_vs_reference_cuda": round(refms / ours, 2) if refms else None,
+                      "images_per_s": round(B / ours * 1e3, 1),
+                      "reference_cuda_images_per_s": round(B / refms * 1e3, 1) if refms else None,
+                      "config": {"workload": f"{label}, {B} images, epilogue launches only (no convolution), scratch buffers of each "
+                                             "layer's shape; reference = its own src/*.cu for sm_100a replaying Layer<CUDA>::forward",
+                                 "plan": plan.stats}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -431,6 +563,7 @@ def main():
     ap.add_argument("--sweep-acts", default="leaky,mish,swish,logistic")
     ap.add_argument("--sweep-pool", default="both", choices=["none", "pool", "both"])
     ap.add_argument("--sweep-residual", action="store_true", help="sweep the epilogue fused with a shortcut add")
+    ap.add_argument("--model", default="yolov3-608", help="model graph for --workload epilogue-compare")
     ap.add_argument("--no-cudnn-benchmark", action="store_true", help="skip cuDNN's algorithm search (profiling runs)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
@@ -447,6 +580,8 @@ def main():
         return run_sweep(args)
     if args.workload == "centernet":
         return run_centernet(args)
+    if args.workload == "epilogue-compare":
+        return run_epilogue_compare(args)
     return run_model(args)
 
 

@@ -239,9 +239,9 @@ PXE_API int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* des
  *
  * The scratch lives in a fixed array inside the library (PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES,
  * resident on every GPU that loads the library for the life of the process).  A head whose
- * pxe_yolo_decode_workspace_bytes() exceeds that size is refused with PXE_ERR_WORKSPACE; 4 MiB
- * covers 64 images of a 76x76 head (1.5 MB).  Nothing is allocated or freed, by this function or
- * by anything it calls.
+ * pxe_yolo_decode_workspace_bytes() exceeds that size is refused with PXE_ERR_WORKSPACE; the
+ * decode needs 12 bytes per 32 cells per image, so 4 MiB covers e.g. 64 images of a 76x76 head
+ * (140 KB) many times over.  Nothing is allocated or freed, by this function or by anything it calls.
  *
  * - The first call on each device looks up the array's device address (that device must be
  *   current); make that first call before starting any stream capture.

@@ -27,6 +27,10 @@ struct PlaneEntry {
     int chan;            // channel; bit 30 set = "identity entry" for PXE_ACT_YOLO_HEAD
 };
 
+// image / channel numbers of a plane without the table (used to issue the first loads of a block
+// before its table exists)
+struct PlaneId { uint32_t image, chan; };
+
 struct EpiParams {
     const float* x; float* y; float* y2; const float* res; float* ypool;
     long long xbs, ybs, y2bs, rbs, pbs;
@@ -97,7 +101,7 @@ __device__ __forceinline__ float residual_one(float v, float r, const EpiParams&
 // MODE 2: scalar, anything goes.
 // ---------------------------------------------------------------------------------------------
 template <int ACT, bool AFFINE, bool RES, int MODE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, RES ? 4 : 5)
 epilogue_kernel(const EpiParams p)
 {
     extern __shared__ PlaneEntry tab[];
@@ -116,33 +120,39 @@ epilogue_kernel(const EpiParams p)
         plane_lo = p.div_plane.div(lo * VW);
         plane_hi = p.div_plane.div((hi - 1) * VW + (VW - 1));
     }
-    build_table(p, tab, plane_lo, plane_hi);
-    __syncthreads();
 
+    // Every thread runs the same number of rounds (the barrier below sits inside the loop).  The
+    // first round issues its global loads BEFORE the coefficient table is built, so the table's own
+    // parameter loads and the square roots overlap the first wave of data instead of preceding it.
     const uint32_t step = kThreads * kUnroll;
-    for (uint32_t base = lo + threadIdx.x; base < hi; base += step) {
+    const uint32_t rounds = (hi - lo + step - 1) / step;
+    for (uint32_t rd = 0; rd < rounds; ++rd) {
+        const uint32_t base = lo + rd * step + threadIdx.x;
         if (MODE == 0) {
             float4 v[kUnroll];
             float4 r[kUnroll];
-            long long off[kUnroll];
-            uint32_t pl[kUnroll];
+            uint32_t off[kUnroll];          // offset inside one image: C*H*W < 2^31
+            uint32_t pl[kUnroll], img[kUnroll];
 #pragma unroll
             for (int k = 0; k < kUnroll; ++k) {
-                uint32_t u = base + k * kThreads;
+                const uint32_t u = base + k * kThreads;
                 if (u < hi) {
-                    uint32_t q, rem;
+                    uint32_t q, rem, c;
                     p.div_plane.divmod(u, q, rem);
+                    p.div_c.divmod(q, img[k], c);
                     pl[k] = q - plane_lo;
-                    const PlaneEntry t = tab[pl[k]];
-                    long long in_img = (long long)(t.chan & 0xFFFFFF) * p.HW + (long long)rem * 4;
-                    off[k] = in_img;
-                    v[k] = *reinterpret_cast<const float4*>(p.x + (long long)t.image * p.xbs + in_img);
-                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (long long)t.image * p.rbs + in_img);
+                    off[k] = c * (uint32_t)p.HW + rem * 4;
+                    v[k] = *reinterpret_cast<const float4*>(p.x + (long long)img[k] * p.xbs + off[k]);
+                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (long long)img[k] * p.rbs + off[k]);
                 }
+            }
+            if (rd == 0) {
+                build_table(p, tab, plane_lo, plane_hi);
+                __syncthreads();
             }
 #pragma unroll
             for (int k = 0; k < kUnroll; ++k) {
-                uint32_t u = base + k * kThreads;
+                const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     const PlaneEntry t = tab[pl[k]];
                     float4 o;
@@ -156,8 +166,8 @@ epilogue_kernel(const EpiParams p)
                         o.z = residual_one(o.z, r[k].z, p);
                         o.w = residual_one(o.w, r[k].w, p);
                     }
-                    if (p.y) *reinterpret_cast<float4*>(p.y + (long long)t.image * p.ybs + off[k]) = o;
-                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (long long)t.image * p.y2bs + off[k]) = o;
+                    if (p.y) *reinterpret_cast<float4*>(p.y + (long long)img[k] * p.ybs + off[k]) = o;
+                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (long long)img[k] * p.y2bs + off[k]) = o;
                 }
             }
         } else if (MODE == 1) {
@@ -166,15 +176,19 @@ epilogue_kernel(const EpiParams p)
             float4 r[kUnroll];
 #pragma unroll
             for (int k = 0; k < kUnroll; ++k) {
-                uint32_t u = base + k * kThreads;
+                const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     v[k] = *reinterpret_cast<const float4*>(p.x + (size_t)u * 4);
                     if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (size_t)u * 4);
                 }
             }
+            if (rd == 0) {
+                build_table(p, tab, plane_lo, plane_hi);
+                __syncthreads();
+            }
 #pragma unroll
             for (int k = 0; k < kUnroll; ++k) {
-                uint32_t u = base + k * kThreads;
+                const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     uint32_t q, rem;
                     p.div_plane.divmod(u * 4, q, rem);
@@ -197,18 +211,34 @@ epilogue_kernel(const EpiParams p)
                 }
             }
         } else {
+            float v[kUnroll], r[kUnroll];
+            uint32_t off[kUnroll];
+            uint32_t pl[kUnroll], img[kUnroll];
 #pragma unroll
             for (int k = 0; k < kUnroll; ++k) {
-                uint32_t u = base + k * kThreads;
+                const uint32_t u = base + k * kThreads;
                 if (u < hi) {
-                    uint32_t q, rem;
+                    uint32_t q, rem, c;
                     p.div_plane.divmod(u, q, rem);
-                    const PlaneEntry t = tab[q - plane_lo];
-                    long long in_img = (long long)(t.chan & 0xFFFFFF) * p.HW + rem;
-                    float o = apply_one<ACT, AFFINE>(p.x[(long long)t.image * p.xbs + in_img], t);
-                    if (RES) o = residual_one(o, p.res[(long long)t.image * p.rbs + in_img], p);
-                    if (p.y) p.y[(long long)t.image * p.ybs + in_img] = o;
-                    if (p.y2) p.y2[(long long)t.image * p.y2bs + in_img] = o;
+                    p.div_c.divmod(q, img[k], c);
+                    pl[k] = q - plane_lo;
+                    off[k] = c * (uint32_t)p.HW + rem;
+                    v[k] = p.x[(long long)img[k] * p.xbs + off[k]];
+                    if (RES) r[k] = p.res[(long long)img[k] * p.rbs + off[k]];
+                }
+            }
+            if (rd == 0) {
+                build_table(p, tab, plane_lo, plane_hi);
+                __syncthreads();
+            }
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                const uint32_t u = base + k * kThreads;
+                if (u < hi) {
+                    float o = apply_one<ACT, AFFINE>(v[k], tab[pl[k]]);
+                    if (RES) o = residual_one(o, r[k], p);
+                    if (p.y) p.y[(long long)img[k] * p.ybs + off[k]] = o;
+                    if (p.y2) p.y2[(long long)img[k] * p.y2bs + off[k]] = o;
                 }
             }
         }
@@ -238,7 +268,7 @@ __global__ void epilogue_tail_kernel(const EpiParams p, uint32_t first, uint32_t
 __device__ __forceinline__ float pick(float m, float v) { return v > m ? v : m; }
 
 template <int ACT, bool AFFINE, int VO>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, VO == 4 ? 6 : 4)
 epilogue_pool_kernel(const EpiParams p)
 {
     extern __shared__ PlaneEntry tab[];
@@ -248,101 +278,120 @@ epilogue_pool_kernel(const EpiParams p)
     if (hi > p.units) hi = p.units;
     const uint32_t plane_lo = p.div_ohowv.div(lo);
     const uint32_t plane_hi = p.div_ohowv.div(hi - 1);
-    build_table(p, tab, plane_lo, plane_hi);
-    __syncthreads();
 
-    constexpr int NV = VO == 0 ? 1 : VO;       // pooled outputs per thread
-    constexpr int NI = 2 * NV;                 // input columns per row
-    for (uint32_t u = lo + threadIdx.x; u < hi; u += kThreads) {
-        uint32_t q, rem, oh, owv;
-        p.div_ohowv.divmod(u, q, rem);
-        p.div_owv.divmod(rem, oh, owv);
-        const PlaneEntry t = tab[q - plane_lo];
-        const int c = t.chan & 0xFFFFFF;
-        const int ih = 2 * (int)oh;
-        const int iw = NI * (int)owv;
-        const bool row1 = ih + 1 < p.H;
-        const long long in0 = (long long)c * p.HW + (long long)ih * p.W + iw;
-        const float* x0 = p.x + (long long)t.image * p.xbs + in0;
-        float r0[NI], r1[NI];
-        if (VO == 4) {
-            float4 a0 = *reinterpret_cast<const float4*>(x0);
-            float4 a1 = *reinterpret_cast<const float4*>(x0 + 4);
-            r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
-            r0[4] = a1.x; r0[5] = a1.y; r0[6] = a1.z; r0[7] = a1.w;
-            if (row1) {
-                float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
-                float4 b1 = *reinterpret_cast<const float4*>(x0 + p.W + 4);
-                r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
-                r1[4] = b1.x; r1[5] = b1.y; r1[6] = b1.z; r1[7] = b1.w;
-            }
-        } else if (VO == 2) {
-            float4 a0 = *reinterpret_cast<const float4*>(x0);
-            r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
-            if (row1) {
-                float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
-                r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
-            }
-        } else if (VO == 1) {
-            float2 a0 = *reinterpret_cast<const float2*>(x0);
-            r0[0] = a0.x; r0[1] = a0.y;
-            if (row1) {
-                float2 b0 = *reinterpret_cast<const float2*>(x0 + p.W);
-                r1[0] = b0.x; r1[1] = b0.y;
-            }
-        } else {
-            const bool col1 = iw + 1 < p.W;
-            r0[0] = x0[0];
-            r0[1] = col1 ? x0[1] : 0.0f;
-            if (row1) {
-                r1[0] = x0[p.W];
-                r1[1] = col1 ? x0[p.W + 1] : 0.0f;
-            }
-        }
+    constexpr int NV = VO == 0 ? 1 : VO;       // pooled outputs per patch
+    constexpr int NI = 2 * NV;                 // input columns per patch row
+    constexpr int U = 16 / (2 * NI);           // patches per thread per round: 16 input floats in flight
+    const uint32_t step = kThreads * U;
+    const uint32_t rounds = (hi - lo + step - 1) / step;
+    for (uint32_t rd = 0; rd < rounds; ++rd) {
+        const uint32_t base = lo + rd * step + threadIdx.x;
+        float r0[U][NI], r1[U][NI];
+        uint32_t pl[U], img[U], in0[U], oh_[U], owv_[U];
+        bool row1[U], col1[U];
 #pragma unroll
-        for (int k = 0; k < NI; ++k) {
-            r0[k] = apply_one<ACT, AFFINE>(r0[k], t);
-            r1[k] = row1 ? apply_one<ACT, AFFINE>(r1[k], t) : 0.0f;
-        }
-        const bool col1 = (VO != 0) || (iw + 1 < p.W);
-        float m[NV];
-#pragma unroll
-        for (int k = 0; k < NV; ++k) {
-            float best = r0[2 * k];
-            if (col1) best = pick(best, r0[2 * k + 1]);
-            if (row1) {
-                best = pick(best, r1[2 * k]);
-                if (col1) best = pick(best, r1[2 * k + 1]);
-            }
-            m[k] = best;
-        }
-        float* yp = p.ypool + (long long)t.image * p.pbs + (long long)c * p.OH * p.OW
-                    + (long long)oh * p.OW + (long long)NV * owv;
-        if (VO == 4) *reinterpret_cast<float4*>(yp) = make_float4(m[0], m[1], m[2], m[3]);
-        else if (VO == 2) *reinterpret_cast<float2*>(yp) = make_float2(m[0], m[1]);
-        else yp[0] = m[0];
-
-        if (p.y) {
-            float* y0 = p.y + (long long)t.image * p.ybs + in0;
-            if (VO == 4) {
-                *reinterpret_cast<float4*>(y0) = make_float4(r0[0], r0[1], r0[2], r0[3]);
-                *reinterpret_cast<float4*>(y0 + 4) = make_float4(r0[4], r0[5], r0[6], r0[7]);
-                if (row1) {
-                    *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[0], r1[1], r1[2], r1[3]);
-                    *reinterpret_cast<float4*>(y0 + p.W + 4) = make_float4(r1[4], r1[5], r1[6], r1[7]);
+        for (int k = 0; k < U; ++k) {
+            const uint32_t u = base + k * kThreads;
+            if (u < hi) {
+                uint32_t q, rem, oh, owv, c;
+                p.div_ohowv.divmod(u, q, rem);
+                p.div_owv.divmod(rem, oh, owv);
+                p.div_c.divmod(q, img[k], c);
+                pl[k] = q - plane_lo; oh_[k] = oh; owv_[k] = owv;
+                const int ih = 2 * (int)oh, iw = NI * (int)owv;
+                row1[k] = ih + 1 < p.H;
+                col1[k] = (VO != 0) || (iw + 1 < p.W);
+                in0[k] = c * (uint32_t)p.HW + (uint32_t)ih * (uint32_t)p.W + (uint32_t)iw;
+                const float* x0 = p.x + (long long)img[k] * p.xbs + in0[k];
+                if (VO == 4) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
+                    const float4 a1 = *reinterpret_cast<const float4*>(x0 + 4);
+                    r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
+                    r0[k][4] = a1.x; r0[k][5] = a1.y; r0[k][6] = a1.z; r0[k][7] = a1.w;
+                    if (row1[k]) {
+                        const float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
+                        const float4 b1 = *reinterpret_cast<const float4*>(x0 + p.W + 4);
+                        r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
+                        r1[k][4] = b1.x; r1[k][5] = b1.y; r1[k][6] = b1.z; r1[k][7] = b1.w;
+                    }
+                } else if (VO == 2) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
+                    r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
+                    if (row1[k]) {
+                        const float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
+                        r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
+                    }
+                } else if (VO == 1) {
+                    const float2 a0 = *reinterpret_cast<const float2*>(x0);
+                    r0[k][0] = a0.x; r0[k][1] = a0.y;
+                    if (row1[k]) {
+                        const float2 b0 = *reinterpret_cast<const float2*>(x0 + p.W);
+                        r1[k][0] = b0.x; r1[k][1] = b0.y;
+                    }
+                } else {
+                    r0[k][0] = x0[0];
+                    r0[k][1] = col1[k] ? x0[1] : 0.0f;
+                    if (row1[k]) {
+                        r1[k][0] = x0[p.W];
+                        r1[k][1] = col1[k] ? x0[p.W + 1] : 0.0f;
+                    }
                 }
-            } else if (VO == 2) {
-                *reinterpret_cast<float4*>(y0) = make_float4(r0[0], r0[1], r0[2], r0[3]);
-                if (row1) *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[0], r1[1], r1[2], r1[3]);
-            } else if (VO == 1) {
-                *reinterpret_cast<float2*>(y0) = make_float2(r0[0], r0[1]);
-                if (row1) *reinterpret_cast<float2*>(y0 + p.W) = make_float2(r1[0], r1[1]);
-            } else {
-                y0[0] = r0[0];
-                if (col1) y0[1] = r0[1];
-                if (row1) {
-                    y0[p.W] = r1[0];
-                    if (col1) y0[p.W + 1] = r1[1];
+            }
+        }
+        if (rd == 0) {
+            build_table(p, tab, plane_lo, plane_hi);
+            __syncthreads();
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const uint32_t u = base + k * kThreads;
+            if (u >= hi) continue;
+            const PlaneEntry t = tab[pl[k]];
+            const uint32_t c = (uint32_t)(t.chan & 0xFFFFFF);
+#pragma unroll
+            for (int j = 0; j < NI; ++j) {
+                r0[k][j] = apply_one<ACT, AFFINE>(r0[k][j], t);
+                r1[k][j] = row1[k] ? apply_one<ACT, AFFINE>(r1[k][j], t) : 0.0f;
+            }
+            float m[NV];
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                float best = r0[k][2 * j];
+                if (col1[k]) best = pick(best, r0[k][2 * j + 1]);
+                if (row1[k]) {
+                    best = pick(best, r1[k][2 * j]);
+                    if (col1[k]) best = pick(best, r1[k][2 * j + 1]);
+                }
+                m[j] = best;
+            }
+            float* yp = p.ypool + (long long)img[k] * p.pbs + (long long)c * p.OH * p.OW
+                        + (long long)oh_[k] * p.OW + (long long)NV * owv_[k];
+            if (VO == 4) *reinterpret_cast<float4*>(yp) = make_float4(m[0], m[1], m[2], m[3]);
+            else if (VO == 2) *reinterpret_cast<float2*>(yp) = make_float2(m[0], m[1]);
+            else yp[0] = m[0];
+
+            if (p.y) {
+                float* y0 = p.y + (long long)img[k] * p.ybs + in0[k];
+                if (VO == 4) {
+                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
+                    *reinterpret_cast<float4*>(y0 + 4) = make_float4(r0[k][4], r0[k][5], r0[k][6], r0[k][7]);
+                    if (row1[k]) {
+                        *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
+                        *reinterpret_cast<float4*>(y0 + p.W + 4) = make_float4(r1[k][4], r1[k][5], r1[k][6], r1[k][7]);
+                    }
+                } else if (VO == 2) {
+                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
+                    if (row1[k]) *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
+                } else if (VO == 1) {
+                    *reinterpret_cast<float2*>(y0) = make_float2(r0[k][0], r0[k][1]);
+                    if (row1[k]) *reinterpret_cast<float2*>(y0 + p.W) = make_float2(r1[k][0], r1[k][1]);
+                } else {
+                    y0[0] = r0[k][0];
+                    if (col1[k]) y0[1] = r0[k][1];
+                    if (row1[k]) {
+                        y0[p.W] = r1[k][0];
+                        if (col1[k]) y0[p.W + 1] = r1[k][1];
+                    }
                 }
             }
         }
@@ -350,24 +399,20 @@ epilogue_pool_kernel(const EpiParams p)
 }
 
 // ------------------------------------------------------------------------------- launch helpers
-int waves_setting()
+// Rounds of the per-thread loop one block runs (a round = one batch of loads per thread).  Measured
+// on B200: short blocks (2 rounds, 32 KB of input each for the streaming kernel) in many waves give
+// the best HBM throughput at every tensor size; the environment variables exist for experiments.
+int rounds_setting(const char* name, int fallback)
 {
-    static int waves = [] {
-        const char* s = getenv("PXE_WAVES");
-        int w = s ? atoi(s) : 4;
-        return w < 1 ? 1 : w;
-    }();
-    return waves;
+    const char* s = getenv(name);
+    int r = s ? atoi(s) : fallback;
+    return r < 1 ? 1 : r;
 }
 
-// Splits `units` into per-block chunks: a multiple of `granule`, at most `max_chunk`, aiming at
-// sm_count * blocks_per_sm * waves blocks.
-void plan_chunks(uint32_t units, uint32_t granule, uint32_t max_chunk, int sm_count, int blocks_per_sm,
-                 uint32_t* chunk, unsigned* grid)
+// Splits `units` into per-block chunks of `rounds` granules, at most `max_chunk`.
+void plan_chunks(uint32_t units, uint32_t granule, uint32_t max_chunk, int rounds, uint32_t* chunk, unsigned* grid)
 {
-    long long target_blocks = (long long)sm_count * blocks_per_sm * waves_setting();
-    long long c = (units + target_blocks - 1) / target_blocks;
-    c = ((c + granule - 1) / granule) * granule;
+    long long c = (long long)granule * rounds;
     if (max_chunk >= granule && c > (long long)(max_chunk / granule) * granule) c = (long long)(max_chunk / granule) * granule;
     if (c < granule) c = granule;
     *chunk = (uint32_t)c;
@@ -385,7 +430,8 @@ int launch_stream_kernel(cudaStream_t s, EpiParams& p, const DeviceInfo& di)
     if (max_chunk < granule) { granule = kThreads; }
     if (max_chunk < granule) { max_chunk = granule; }   // tiny HW: checked below
     unsigned grid;
-    plan_chunks(p.units, granule, max_chunk, di.sm_count, 4, &p.chunk, &grid);
+    static const int rounds = rounds_setting("PXE_CHUNK_ROUNDS", 2);
+    plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk * vw / p.HW + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
     if (smem > 48 * 1024) {
@@ -447,10 +493,12 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
     const uint32_t per_plane = (uint32_t)(p.OH * p.OWV);
     long long max_chunk_ll = (long long)(kMaxPlanesPerBlock - 2) * per_plane;
     uint32_t max_chunk = max_chunk_ll > 0x7fffffffLL ? 0x7fffffffu : (uint32_t)max_chunk_ll;
-    uint32_t granule = kThreads;
+    uint32_t granule = kThreads * (vo == 4 ? 1 : (vo == 2 ? 2 : 4));     // patches per thread per round, see the kernel
+    if (max_chunk < granule) granule = kThreads;
     if (max_chunk < granule) max_chunk = granule;
     unsigned grid;
-    plan_chunks(p.units, granule, max_chunk, di.sm_count, 4, &p.chunk, &grid);
+    static const int rounds = rounds_setting("PXE_POOL_CHUNK_ROUNDS", 2);
+    plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk / per_plane + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
     void (*kern)(const EpiParams) = nullptr;

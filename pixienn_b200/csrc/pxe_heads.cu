@@ -13,16 +13,24 @@ namespace {
 // ============================================================================================
 // YOLO
 // ============================================================================================
-constexpr int kYoloThreads = 128;
+// Work decomposition.  A block covers 32 consecutive cells of one image.  Warp w of the block handles
+// mask slot (w / chunks) and class chunk (w % chunks) for those 32 cells, lane = cell, so every
+// global load is one coalesced 128-byte row segment of a head plane.  A chunk is at most
+// kYoloChunk classes, whose probabilities a thread keeps in registers between counting and emitting.
+// The reference emits cell-major, then mask slot, then class (include/YoloLayer.h:668-697); in
+// that order thread (lane, w) has rank lane * warps + w inside its block.
+constexpr int kYoloCells = 32;
+constexpr int kYoloChunk = 16;
+constexpr int kYoloMaxWarps = 32;
 
 struct YoloParams {
     pxe_yolo_decode_desc d;
     long long hbs;
     int HW, entries, blocks_per_image;
+    int chunks, chunk_len, warps;     // class chunks per mask slot, classes per chunk, warps per block
     pxe_detection* dets;
     long long capacity;
     long long* count;
-    int* cell_counts;          // [batch*HW]
     int* block_sums;           // [batch*blocks_per_image]
     long long* block_offsets;  // [batch*blocks_per_image]
 };
@@ -40,45 +48,55 @@ __device__ __forceinline__ float yolo_value(const YoloParams& p, const float* im
     return v;
 }
 
-__device__ __forceinline__ int yolo_cell_count(const YoloParams& p, const float* img, int cell)
+// Probabilities of this thread's class chunk that reach the threshold; returns their number and
+// leaves them in prob[] (negative = not emitted).  obj < threshold skips the slot entirely
+// (include/YoloLayer.h:676); a class is emitted when obj * cls >= threshold (:692).
+__device__ __forceinline__ int yolo_chunk(const YoloParams& p, const float* img, int n, int chunk, int cell,
+                                          float (&prob)[kYoloChunk], float* obj_out)
 {
+    const float obj = yolo_value(p, img, n, 4, cell);
+    *obj_out = obj;
+    if (obj < p.d.threshold) return 0;
     int cnt = 0;
-    for (int n = 0; n < p.d.n_masks; ++n) {
-        const float obj = yolo_value(p, img, n, 4, cell);
-        if (obj < p.d.threshold) continue;                         // include/YoloLayer.h:676
-        for (int j = 0; j < p.d.classes; ++j) {
-            const float prob = obj * yolo_value(p, img, n, 5 + j, cell);
-            if (prob >= p.d.threshold) ++cnt;                      // include/YoloLayer.h:692
+    const int c0 = chunk * p.chunk_len;
+    const int cend = min(c0 + p.chunk_len, p.d.classes);
+#pragma unroll
+    for (int j = 0; j < kYoloChunk; ++j) {
+        prob[j] = -1.0f;
+        const int cls = c0 + j;
+        if (cls < cend) {
+            const float pr = obj * yolo_value(p, img, n, 5 + cls, cell);
+            if (pr >= p.d.threshold) { prob[j] = pr; ++cnt; }
         }
     }
+    // chunks longer than the register window (very many classes): the rest is only counted here and
+    // recomputed when emitting
+    for (int cls = c0 + kYoloChunk; cls < cend; ++cls)
+        if (obj * yolo_value(p, img, n, 5 + cls, cell) >= p.d.threshold) ++cnt;
     return cnt;
 }
 
-__device__ __forceinline__ int block_sum_int(int v, int* smem)
-{
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
-    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
-    __syncthreads();
-    int total = 0;
-    if (threadIdx.x == 0)
-        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += smem[w];
-    return total;   // valid in thread 0
-}
-
-__global__ void __launch_bounds__(kYoloThreads)
+__global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
 yolo_count_kernel(const YoloParams p)
 {
-    __shared__ int warp_sums[kYoloThreads / 32];
+    __shared__ int warp_sums[kYoloMaxWarps];
     const int b = blockIdx.y;
-    const int cell = blockIdx.x * kYoloThreads + threadIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int cell = blockIdx.x * kYoloCells + lane;
     const float* img = p.d.head + (long long)b * p.hbs;
     int cnt = 0;
     if (cell < p.HW) {
-        cnt = yolo_cell_count(p, img, cell);
-        p.cell_counts[(long long)b * p.HW + cell] = cnt;
+        float prob[kYoloChunk], obj;
+        cnt = yolo_chunk(p, img, w / p.chunks, w % p.chunks, cell, prob, &obj);
     }
-    const int total = block_sum_int(cnt, warp_sums);
-    if (threadIdx.x == 0) p.block_sums[b * p.blocks_per_image + blockIdx.x] = total;
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
+    if (lane == 0) warp_sums[w] = cnt;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int i = 0; i < p.warps; ++i) total += warp_sums[i];
+        p.block_sums[b * p.blocks_per_image + blockIdx.x] = total;
+    }
 }
 
 // Exclusive scan of the per-block sums; starts at the running total *count and advances it.
@@ -126,78 +144,103 @@ __device__ __forceinline__ int f2i_x86(float v)
     return (int)v;
 }
 
-__global__ void __launch_bounds__(kYoloThreads)
+__global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
 yolo_emit_kernel(const YoloParams p)
 {
-    __shared__ int warp_sums[kYoloThreads / 32];
+    __shared__ int ranked[kYoloCells * (kYoloMaxWarps + 1)];   // counts, then exclusive prefixes, in emission order
+    __shared__ int warp_tot[kYoloMaxWarps];
     const int b = blockIdx.y;
-    const int cell = blockIdx.x * kYoloThreads + threadIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int cell = blockIdx.x * kYoloCells + lane;
     const float* img = p.d.head + (long long)b * p.hbs;
-    const int cnt = cell < p.HW ? p.cell_counts[(long long)b * p.HW + cell] : 0;
-    // exclusive scan of cnt over the block (emission order inside an image is cell-major)
-    int inc = cnt;
-    for (int o = 1; o < 32; o <<= 1) {
-        int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if ((threadIdx.x & 31) >= o) inc += t;
-    }
-    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = inc;
+    const int n = w / p.chunks, chunk = w % p.chunks;
+    float prob[kYoloChunk], obj = 0.0f;
+    int cnt = 0;
+    if (cell < p.HW) cnt = yolo_chunk(p, img, n, chunk, cell, prob, &obj);
+    // exclusive scan over the block in emission order: rank = lane * warps + w
+    const int nthreads = kYoloCells * p.warps;
+    ranked[lane * p.warps + w] = cnt;
     __syncthreads();
-    int warp_excl = 0;
-    for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) warp_excl += warp_sums[w];
+    {
+        const int v = ranked[threadIdx.x];            // thread t now owns rank t
+        int inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) warp_tot[w] = inc;
+        __syncthreads();
+        int before = 0;
+        for (int i = 0; i < w; ++i) before += warp_tot[i];
+        ranked[threadIdx.x] = before + inc - v;
+        (void)nthreads;
+    }
+    __syncthreads();
     if (cnt == 0) return;
-    long long pos = p.block_offsets[b * p.blocks_per_image + blockIdx.x] + warp_excl + inc - cnt;
+    long long pos = p.block_offsets[b * p.blocks_per_image + blockIdx.x] + ranked[lane * p.warps + w];
 
     const int W = p.d.width, H = p.d.height;
     const int row = cell / W, col = cell - row * W;
     const bool scaled = p.d.image_width > 0 && p.d.image_height > 0;
-    for (int n = 0; n < p.d.n_masks; ++n) {
-        const float obj = yolo_value(p, img, n, 4, cell);
-        if (obj < p.d.threshold) continue;
-        const float tx = yolo_value(p, img, n, 0, cell), ty = yolo_value(p, img, n, 1, cell);
-        const float tw = yolo_value(p, img, n, 2, cell), th = yolo_value(p, img, n, 3, cell);
-        const int a = p.d.mask[n];
-        const int aw = p.d.anchors[2 * a], ah = p.d.anchors[2 * a + 1];
-        const int net_w = p.d.net_width, net_h = p.d.net_height;
-        float bx, by, bw, bh;
-        if (scaled) {
-            // scaledYoloBox, include/YoloLayer.h:601-635
-            const int iw = p.d.image_width, ih = p.d.image_height;
-            int new_w, new_h;
-            if (((float)net_w / iw) < ((float)net_h / ih)) { new_w = net_w; new_h = (ih * net_w) / iw; }
-            else { new_h = net_h; new_w = (iw * net_h) / ih; }
-            float x = (col + tx) / W;
-            x = (x - (net_w - new_w) / 2.0f / net_w) / ((float)new_w / net_w);
-            float y = (row + ty) / H;
-            y = (y - (net_h - new_h) / 2.0f / net_h) / ((float)new_h / net_h);
-            float width = expf(tw) * aw / net_w;
-            width *= (float)net_w / new_w;
-            float height = expf(th) * ah / net_h;
-            height *= (float)net_h / new_h;
-            int left = f2i_x86(__fmul_rn(__fsub_rn(x, width / 2), (float)iw));    if (left < 0) left = 0;
-            int right = f2i_x86(__fmul_rn(__fadd_rn(x, width / 2), (float)iw));   if (right > iw - 1) right = iw - 1;
-            int top = f2i_x86(__fmul_rn(__fsub_rn(y, height / 2), (float)ih));    if (top < 0) top = 0;
-            int bottom = f2i_x86(__fmul_rn(__fadd_rn(y, height / 2), (float)ih)); if (bottom > ih - 1) bottom = ih - 1;
-            bx = (float)left; by = (float)top; bw = (float)(right - left); bh = (float)(bottom - top);
-        } else {
-            // yoloBox().rect(), include/YoloLayer.h:637-651, src/DarkBox.cpp:84-123
-            const float x = (col + tx) / W, y = (row + ty) / H;
-            const float w = expf(tw) * aw / net_w, h = expf(th) * ah / net_h;
-            bx = w > 0.0f ? __fsub_rn(x, w / 2.0f) : x;
-            by = h > 0.0f ? __fsub_rn(y, h / 2.0f) : y;
-            bw = w; bh = h;
-        }
-        for (int j = 0; j < p.d.classes; ++j) {
-            const float prob = obj * yolo_value(p, img, n, 5 + j, cell);
-            if (prob >= p.d.threshold) {
-                if (pos < p.capacity) {
-                    pxe_detection det;
-                    det.x = bx; det.y = by; det.w = bw; det.h = bh; det.prob = prob;
-                    det.class_id = j; det.batch_id = b + p.d.batch_id_offset;
-                    det.source = cell * p.d.n_masks + n;
-                    p.dets[pos] = det;
-                }
-                ++pos;
+    const float tx = yolo_value(p, img, n, 0, cell), ty = yolo_value(p, img, n, 1, cell);
+    const float tw = yolo_value(p, img, n, 2, cell), th = yolo_value(p, img, n, 3, cell);
+    const int a = p.d.mask[n];
+    const int aw = p.d.anchors[2 * a], ah = p.d.anchors[2 * a + 1];
+    const int net_w = p.d.net_width, net_h = p.d.net_height;
+    float bx, by, bw, bh;
+    if (scaled) {
+        // scaledYoloBox, include/YoloLayer.h:601-635
+        const int iw = p.d.image_width, ih = p.d.image_height;
+        int new_w, new_h;
+        if (((float)net_w / iw) < ((float)net_h / ih)) { new_w = net_w; new_h = (ih * net_w) / iw; }
+        else { new_h = net_h; new_w = (iw * net_h) / ih; }
+        float x = (col + tx) / W;
+        x = (x - (net_w - new_w) / 2.0f / net_w) / ((float)new_w / net_w);
+        float y = (row + ty) / H;
+        y = (y - (net_h - new_h) / 2.0f / net_h) / ((float)new_h / net_h);
+        float width = expf(tw) * aw / net_w;
+        width *= (float)net_w / new_w;
+        float height = expf(th) * ah / net_h;
+        height *= (float)net_h / new_h;
+        int left = f2i_x86(__fmul_rn(__fsub_rn(x, width / 2), (float)iw));    if (left < 0) left = 0;
+        int right = f2i_x86(__fmul_rn(__fadd_rn(x, width / 2), (float)iw));   if (right > iw - 1) right = iw - 1;
+        int top = f2i_x86(__fmul_rn(__fsub_rn(y, height / 2), (float)ih));    if (top < 0) top = 0;
+        int bottom = f2i_x86(__fmul_rn(__fadd_rn(y, height / 2), (float)ih)); if (bottom > ih - 1) bottom = ih - 1;
+        bx = (float)left; by = (float)top; bw = (float)(right - left); bh = (float)(bottom - top);
+    } else {
+        // yoloBox().rect(), include/YoloLayer.h:637-651, src/DarkBox.cpp:84-123
+        const float x = (col + tx) / W, y = (row + ty) / H;
+        const float wd = expf(tw) * aw / net_w, ht = expf(th) * ah / net_h;
+        bx = wd > 0.0f ? __fsub_rn(x, wd / 2.0f) : x;
+        by = ht > 0.0f ? __fsub_rn(y, ht / 2.0f) : y;
+        bw = wd; bh = ht;
+    }
+    const int c0 = chunk * p.chunk_len;
+#pragma unroll
+    for (int j = 0; j < kYoloChunk; ++j) {
+        if (prob[j] >= 0.0f) {
+            if (pos < p.capacity) {
+                pxe_detection det;
+                det.x = bx; det.y = by; det.w = bw; det.h = bh; det.prob = prob[j];
+                det.class_id = c0 + j; det.batch_id = b + p.d.batch_id_offset;
+                det.source = cell * p.d.n_masks + n;
+                p.dets[pos] = det;
             }
+            ++pos;
+        }
+    }
+    const int cend = min(c0 + p.chunk_len, p.d.classes);
+    for (int cls = c0 + kYoloChunk; cls < cend; ++cls) {
+        const float pr = obj * yolo_value(p, img, n, 5 + cls, cell);
+        if (pr >= p.d.threshold) {
+            if (pos < p.capacity) {
+                pxe_detection det;
+                det.x = bx; det.y = by; det.w = bw; det.h = bh; det.prob = pr;
+                det.class_id = cls; det.batch_id = b + p.d.batch_id_offset;
+                det.source = cell * p.d.n_masks + n;
+                p.dets[pos] = det;
+            }
+            ++pos;
         }
     }
 }
@@ -247,6 +290,7 @@ struct CnParams {
     int K;
     int cap;                         // candidate slots per image = blocks per image * K
     float lo;                        // pre-filter: a cell with (value >= lo) false cannot reach the threshold
+    float lo_list;                   // work-list bound, a margin below lo (see centernet_peaks_kernel)
     unsigned long long* cand;        // [batch][cap] sortable keys, unordered
     int* cand_cnt;                   // [batch], zeroed before the launch
     pxe_detection* dets; int* counts;
@@ -339,17 +383,28 @@ __device__ __forceinline__ float cn_score(const CnParams& p, float v)
     return p.d.heat_is_logit ? 1.0f / (1.0f + expf(-v)) : v;
 }
 
-// One block per (tile, class, image).  Shared memory holds the tile's pre-activation values
-// (logit + bias) with a one-cell halo.  The sigmoid is evaluated only where it can matter: for
-// cells that can reach the threshold, and for those of their neighbours whose pre-activation value
-// is not clearly smaller (the activation is non-decreasing, so a clearly smaller neighbour cannot
-// have a greater score; "clearly" leaves room for rounding in exp()).
+// One block per (32x64 tile, class, image).
+//  load   the tile's pre-activation values (logit + bias) with a one-cell halo go to shared memory,
+//         128 bits at a time where the row alignment allows; every value that is not clearly below the
+//         threshold (in pre-activation space) is put on a work list on the way.  For a typical heatmap
+//         that is about one cell in ten.
+//  score  the activation (the reference's precise sigmoid) is evaluated once per work-list entry.
+//  peak   interior entries at or above the threshold are compared with their 8 neighbours' scores.
+//         A neighbour that is not on the work list is clearly below the threshold in pre-activation
+//         space; the activation is non-decreasing, so its score cannot exceed that of a cell which
+//         reached the threshold ("clearly" = a margin far wider than any rounding in exp()).
+//  select a tile with more than K surviving candidates passes on only its K best.
+constexpr int kCnRowStride = 72;                      // floats per shared-memory row; interior starts at column 4
+constexpr int kCnSmemCells = (kCnTileH + 2) * kCnRowStride;
+
+template <bool VEC>
 __global__ void __launch_bounds__(kCnThreads)
 centernet_peaks_kernel(const CnParams p)
 {
-    __shared__ float tile[(kCnTileH + 2) * (kCnTileW + 2)];
+    __shared__ __align__(16) float tile[kCnSmemCells];
+    __shared__ __align__(16) float score[kCnSmemCells];
+    __shared__ unsigned short work[(kCnTileH + 2) * (kCnTileW + 2)];
     __shared__ unsigned long long keys[kCnCells];
-    __shared__ unsigned short work[kCnCells];
     __shared__ int n_keys, n_out, n_work, base;
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
@@ -361,54 +416,87 @@ centernet_peaks_kernel(const CnParams p)
     const long long area = (long long)H * W;
     const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
     if (threadIdx.x == 0) { n_keys = 0; n_out = 0; n_work = 0; }
-
-    constexpr int TW = kCnTileW + 2;
-    const float bias = p.d.heat_is_logit ? p.d.heatmap_bias : 0.0f;
-    for (int i = threadIdx.x; i < (kCnTileH + 2) * TW; i += kCnThreads) {
-        const int ly = i / TW, lx = i - ly * TW;
-        const int gy = y0 + ly - 1, gx = x0 + lx - 1;
-        float v = -INFINITY;                       // outside the map: never greater than a score
-        if (gy >= 0 && gy < H && gx >= 0 && gx < W) {
-            v = heat[(long long)gy * W + gx];
-            if (p.d.heat_is_logit) v += bias;      // same sum the reference forms before its sigmoid
-        }
-        tile[i] = v;
-    }
     __syncthreads();
 
-    // pass A: cells that can reach the threshold at all (about one in ten for a typical heatmap) go on a
-    // work list, so that pass B runs the expensive tests with every lane busy
-    for (int i = threadIdx.x; i < kCnCells; i += kCnThreads) {
-        const int ly = i / kCnTileW, lx = i - ly * kCnTileW;
-        if (y0 + ly >= H || x0 + lx >= W) continue;
-        if (tile[(ly + 1) * TW + (lx + 1)] >= p.lo) work[atomicAdd(&n_work, 1)] = (unsigned short)i;
-    }
-    __syncthreads();
-
-    const float* size = p.d.size + (long long)b * p.sbs;
-    const float* off = p.d.offset + (long long)b * p.obs;
     const bool logit = p.d.heat_is_logit != 0;
+    const float bias = logit ? p.d.heatmap_bias : 0.0f;
+    const float lo_list = p.lo_list;
+    constexpr float NEG = -INFINITY;                  // outside the map: never greater than a score
+
+    // ---- load + work list
+    if (VEC) {
+        // interior: 34 rows x 16 float4
+        for (int i = threadIdx.x; i < (kCnTileH + 2) * (kCnTileW / 4); i += kCnThreads) {
+            const int row = i / (kCnTileW / 4), vx = i - row * (kCnTileW / 4);
+            const int gy = y0 + row - 1, gx = x0 + 4 * vx;
+            float4 v = make_float4(NEG, NEG, NEG, NEG);
+            if (gy >= 0 && gy < H && gx < W) {
+                const float* src = heat + (long long)gy * W + gx;
+                if (gx + 3 < W) {
+                    v = *reinterpret_cast<const float4*>(src);
+                    v.x += bias; v.y += bias; v.z += bias; v.w += bias;
+                } else {
+                    v.x = src[0] + bias;
+                    if (gx + 1 < W) v.y = src[1] + bias;
+                    if (gx + 2 < W) v.z = src[2] + bias;
+                }
+            }
+            const int si = row * kCnRowStride + 4 + 4 * vx;
+            *reinterpret_cast<float4*>(tile + si) = v;
+            *reinterpret_cast<float4*>(score + si) = make_float4(NEG, NEG, NEG, NEG);
+            if (v.x >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)si;
+            if (v.y >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)(si + 1);
+            if (v.z >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)(si + 2);
+            if (v.w >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)(si + 3);
+        }
+        // halo columns: 34 rows x {left, right}
+        for (int i = threadIdx.x; i < (kCnTileH + 2) * 2; i += kCnThreads) {
+            const int row = i >> 1, side = i & 1;
+            const int gy = y0 + row - 1, gx = side ? x0 + kCnTileW : x0 - 1;
+            float v = NEG;
+            if (gy >= 0 && gy < H && gx >= 0 && gx < W) v = heat[(long long)gy * W + gx] + bias;
+            const int si = row * kCnRowStride + (side ? 4 + kCnTileW : 3);
+            tile[si] = v;
+            score[si] = NEG;
+            if (v >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)si;
+        }
+    } else {
+        for (int i = threadIdx.x; i < (kCnTileH + 2) * (kCnTileW + 2); i += kCnThreads) {
+            const int row = i / (kCnTileW + 2), lx = i - row * (kCnTileW + 2);
+            const int gy = y0 + row - 1, gx = x0 + lx - 1;
+            float v = NEG;
+            if (gy >= 0 && gy < H && gx >= 0 && gx < W) v = heat[(long long)gy * W + gx] + bias;
+            const int si = row * kCnRowStride + 3 + lx;
+            tile[si] = v;
+            score[si] = NEG;
+            if (v >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)si;
+        }
+    }
+    __syncthreads();
+
+    // ---- score: the reference's activation expression, once per listed cell
     const int todo = n_work;
     for (int wi = threadIdx.x; wi < todo; wi += kCnThreads) {
-        const int i = work[wi];
-        const int ly = i / kCnTileW, lx = i - ly * kCnTileW;
-        const int gy = y0 + ly, gx = x0 + lx;
-        const float* c = tile + (ly + 1) * TW + (lx + 1);
-        const float v = c[0];
-        const float s = cn_score(p, v);
+        const int si = work[wi];
+        score[si] = cn_score(p, tile[si]);
+    }
+    __syncthreads();
+
+    // ---- peak test, validity, key
+    const float* size = p.d.size + (long long)b * p.sbs;
+    const float* off = p.d.offset + (long long)b * p.obs;
+    for (int wi = threadIdx.x; wi < todo; wi += kCnThreads) {
+        const int si = work[wi];
+        const int row = si / kCnRowStride, col = si - row * kCnRowStride - 4;
+        if (row < 1 || row > kCnTileH || col < 0 || col >= kCnTileW) continue;      // halo cell
+        const int gy = y0 + row - 1, gx = x0 + col;
+        if (gy >= H || gx >= W) continue;
+        const float s = score[si];
         // include/CenterNetLayer.h:212: finite, at or above the threshold, no strictly greater neighbour
-        if (!isfinite(s) || s < p.d.threshold) continue;
-        const float near = logit ? v - 1e-4f * fmaxf(1.0f, fabsf(v)) : v;
-        bool peak = true;
-#pragma unroll
-        for (int dy = -1; dy <= 1; ++dy)
-#pragma unroll
-            for (int dx = -1; dx <= 1; ++dx) {
-                if (dy == 0 && dx == 0) continue;
-                const float u = c[dy * TW + dx];
-                if (u > near && cn_score(p, u) > s) peak = false;
-            }
-        if (!peak) continue;
+        if (!(tile[si] >= p.lo) || !isfinite(s) || s < p.d.threshold) continue;
+        const float* c = score + si;
+        if (c[-kCnRowStride - 1] > s || c[-kCnRowStride] > s || c[-kCnRowStride + 1] > s || c[-1] > s || c[1] > s ||
+            c[kCnRowStride - 1] > s || c[kCnRowStride] > s || c[kCnRowStride + 1] > s) continue;
         const long long idx = (long long)gy * W + gx;
         const float bw = size[idx] / W, bh = size[area + idx] / H;
         const float ox = off[idx], oy = off[area + idx];
@@ -439,11 +527,13 @@ centernet_peaks_kernel(const CnParams p)
 // Few candidates are sorted outright; otherwise the K-th largest key is found by radix selection
 // (8 passes over the list, which sits in L2) and only the K winners are sorted.
 constexpr int kCnTopkThreads = 256;
+constexpr int kCnStageKeys = 4096;     // candidates per image staged in shared memory (32 KB)
 
 __global__ void __launch_bounds__(kCnTopkThreads)
 centernet_topk_kernel(const CnParams p)
 {
     __shared__ unsigned long long sorted[kCnMaxK];
+    __shared__ unsigned long long stage[kCnStageKeys];
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
     __shared__ int n_best;
@@ -460,9 +550,16 @@ centernet_topk_kernel(const CnParams p)
         m = n < p.K ? n : p.K;
     } else {
         if (threadIdx.x == 0) n_best = 0;
-        const unsigned long long kth = block_select_kth([&](int i) { return cand[i]; }, n, p.K, hist, sel);
+        // the selection makes 8 passes over the list: stage it in shared memory when it fits
+        const bool staged = n <= kCnStageKeys;
+        if (staged) {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) stage[i] = cand[i];
+            __syncthreads();
+        }
+        const unsigned long long* src = staged ? stage : cand;
+        const unsigned long long kth = block_select_kth([&](int i) { return src[i]; }, n, p.K, hist, sel);
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const unsigned long long key = cand[i];
+            const unsigned long long key = src[i];
             if (key >= kth) sorted[atomicAdd(&n_best, 1)] = key;
         }
         __syncthreads();
@@ -593,9 +690,8 @@ extern "C" size_t pxe_yolo_decode_workspace_bytes(int batch, int height, int wid
 {
     if (batch <= 0 || height <= 0 || width <= 0) return 0;
     const size_t hw = (size_t)height * width;
-    const size_t bpi = (hw + kYoloThreads - 1) / kYoloThreads;
-    return align_up((size_t)batch * hw * sizeof(int), 256) + align_up((size_t)batch * bpi * sizeof(int), 256)
-           + align_up((size_t)batch * bpi * sizeof(long long), 256);
+    const size_t bpi = (hw + kYoloCells - 1) / kYoloCells;
+    return align_up((size_t)batch * bpi * sizeof(int), 256) + align_up((size_t)batch * bpi * sizeof(long long), 256);
 }
 
 extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* dp, pxe_detection* dets,
@@ -627,28 +723,33 @@ extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* 
     const long long chw = (long long)d.n_masks * p.entries * p.HW;
     PXE_REQUIRE(d.head_batch_stride == 0 || d.head_batch_stride >= chw, "yolo_decode: head_batch_stride too small");
     p.hbs = d.head_batch_stride ? d.head_batch_stride : chw;
-    p.blocks_per_image = (p.HW + kYoloThreads - 1) / kYoloThreads;
+    p.blocks_per_image = (p.HW + kYoloCells - 1) / kYoloCells;
+    // class chunks of kYoloChunk classes, as many as fit 32 warps per block; with more classes than that
+    // the chunks grow beyond the register window (handled in the kernels)
+    p.chunks = d.classes > 0 ? (d.classes + kYoloChunk - 1) / kYoloChunk : 1;
+    if (p.chunks > kYoloMaxWarps / d.n_masks) p.chunks = kYoloMaxWarps / d.n_masks;
+    p.chunk_len = d.classes > 0 ? (d.classes + p.chunks - 1) / p.chunks : 1;
+    p.warps = d.n_masks * p.chunks;
     p.dets = dets; p.capacity = capacity; p.count = count;
     char* ws = static_cast<char*>(workspace);
-    p.cell_counts = reinterpret_cast<int*>(ws);
-    ws += align_up((size_t)d.batch * p.HW * sizeof(int), 256);
     p.block_sums = reinterpret_cast<int*>(ws);
     ws += align_up((size_t)d.batch * p.blocks_per_image * sizeof(int), 256);
     p.block_offsets = reinterpret_cast<long long*>(ws);
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     dim3 grid((unsigned)p.blocks_per_image, (unsigned)d.batch);
-    yolo_count_kernel<<<grid, kYoloThreads, 0, s>>>(p);
+    const unsigned threads = (unsigned)(kYoloCells * p.warps);
+    yolo_count_kernel<<<grid, threads, 0, s>>>(p);
     PXE_LAUNCH_OK("yolo_count_kernel");
     yolo_scan_kernel<<<1, 1024, 0, s>>>(p.block_sums, p.block_offsets, d.batch * p.blocks_per_image, count);
     PXE_LAUNCH_OK("yolo_scan_kernel");
-    yolo_emit_kernel<<<grid, kYoloThreads, 0, s>>>(p);
+    yolo_emit_kernel<<<grid, threads, 0, s>>>(p);
     PXE_LAUNCH_OK("yolo_emit_kernel");
     return PXE_OK;
 }
 
 // ------------------------------------------------------------- YOLO decode without a caller workspace
-// The scratch of pxe_yolo_decode (per-cell counts, per-block sums and offsets) held in the library's
+// The scratch of pxe_yolo_decode (per-block sums and offsets) held in the library's
 // own device image instead of a buffer the caller allocates.  Every GPU that loads the library
 // carries these bytes until the process exits, so the size is kept modest.
 static __device__ __align__(256) unsigned char g_yolo_static_scratch[PXE_YOLO_DECODE_STATIC_SCRATCH_BYTES];
@@ -776,6 +877,7 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     p.K = d.max_detections;
     p.cap = (int)(bpi * d.max_detections);
     p.lo = centernet_prefilter(d);
+    p.lo_list = d.heat_is_logit ? p.lo - 2e-4f * fmaxf(1.0f, fabsf(p.lo)) : p.lo;
     char* ws = static_cast<char*>(workspace);
     p.cand = reinterpret_cast<unsigned long long*>(ws);
     ws += align_up((size_t)d.batch * p.cap * sizeof(unsigned long long), 256);
@@ -785,7 +887,10 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     PXE_CUDA_OK(cudaMemsetAsync(p.cand_cnt, 0, (size_t)d.batch * sizeof(int), s));
     dim3 grid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, (unsigned)d.batch);
-    centernet_peaks_kernel<<<grid, kCnThreads, 0, s>>>(p);
+    // 128-bit tile loads need every row segment of a tile to start on a 16-byte boundary
+    const bool vec = d.width % 4 == 0 && aligned16(d.heat) && p.hbs % 4 == 0;
+    if (vec) centernet_peaks_kernel<true><<<grid, kCnThreads, 0, s>>>(p);
+    else centernet_peaks_kernel<false><<<grid, kCnThreads, 0, s>>>(p);
     PXE_LAUNCH_OK("centernet_peaks_kernel");
     centernet_topk_kernel<<<(unsigned)d.batch, kCnTopkThreads, 0, s>>>(p);
     PXE_LAUNCH_OK("centernet_topk_kernel");

@@ -36,7 +36,8 @@ def yolo_case(seed, B, classes, H, W, obj_shift=-2.0):
     return x
 
 
-@pytest.mark.parametrize("B,classes,H,W", [(1, 1, 1, 1), (2, 4, 13, 13), (3, 80, 19, 19), (2, 20, 26, 26), (1, 3, 7, 31)])
+@pytest.mark.parametrize("B,classes,H,W", [(1, 1, 1, 1), (2, 4, 13, 13), (3, 80, 19, 19), (2, 20, 26, 26), (1, 3, 7, 31),
+                                           (1, 365, 9, 9), (2, 17, 5, 40), (1, 161, 4, 4)])
 @pytest.mark.parametrize("scaled", [False, True])
 def test_yolo_decode_order_and_values(cuda, oracle, B, classes, H, W, scaled):
     """Decode of an ACTIVATED head: same records, same order as YoloLayer::addDetects.  The head

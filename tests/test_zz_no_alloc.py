@@ -74,7 +74,7 @@ def test_static_scratch_decode_equals_workspace_decode_twice(cuda):
 
 def test_static_scratch_refuses_heads_beyond_its_size(cuda):
     L = capi.lib()
-    B, hw = 64, 152                                           # 64 x 152 x 152 cells need about 5.9 MB > 4 MiB
+    B, hw = 2048, 152                                         # 2048 x 152 x 152 cells need about 17 MB > 4 MiB
     assert L.pxe_yolo_decode_workspace_bytes(B, hw, hw) > (4 << 20)
     d = capi.YoloDecodeDesc()
     d.batch, d.height, d.width, d.classes = B, hw, hw, 1
