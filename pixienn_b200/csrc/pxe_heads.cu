@@ -136,6 +136,15 @@ yolo_scan_kernel(const int* block_sums, long long* block_offsets, int n, long lo
     if (threadIdx.x == 0) *count = carry;
 }
 
+// One 32-byte record as two 128-bit stores (records are 16-byte aligned).
+__device__ __forceinline__ void store_detection(pxe_detection* dst, float x, float y, float w, float h, float prob,
+                                                int class_id, int batch_id, int source)
+{
+    float4* q = reinterpret_cast<float4*>(dst);
+    q[0] = make_float4(x, y, w, h);
+    q[1] = make_float4(prob, __int_as_float(class_id), __int_as_float(batch_id), __int_as_float(source));
+}
+
 // float -> int the way the reference's host decode converts (x86-64 cvttss2si):
 // truncation toward zero, INT_MIN for NaN and out-of-range values.
 __device__ __forceinline__ int f2i_x86(float v)
@@ -219,13 +228,9 @@ yolo_emit_kernel(const YoloParams p)
 #pragma unroll
     for (int j = 0; j < kYoloChunk; ++j) {
         if (prob[j] >= 0.0f) {
-            if (pos < p.capacity) {
-                pxe_detection det;
-                det.x = bx; det.y = by; det.w = bw; det.h = bh; det.prob = prob[j];
-                det.class_id = c0 + j; det.batch_id = b + p.d.batch_id_offset;
-                det.source = cell * p.d.n_masks + n;
-                p.dets[pos] = det;
-            }
+            if (pos < p.capacity)
+                store_detection(p.dets + pos, bx, by, bw, bh, prob[j], c0 + j, b + p.d.batch_id_offset,
+                                cell * p.d.n_masks + n);
             ++pos;
         }
     }
@@ -233,13 +238,8 @@ yolo_emit_kernel(const YoloParams p)
     for (int cls = c0 + kYoloChunk; cls < cend; ++cls) {
         const float pr = obj * yolo_value(p, img, n, 5 + cls, cell);
         if (pr >= p.d.threshold) {
-            if (pos < p.capacity) {
-                pxe_detection det;
-                det.x = bx; det.y = by; det.w = bw; det.h = bh; det.prob = pr;
-                det.class_id = cls; det.batch_id = b + p.d.batch_id_offset;
-                det.source = cell * p.d.n_masks + n;
-                p.dets[pos] = det;
-            }
+            if (pos < p.capacity)
+                store_detection(p.dets + pos, bx, by, bw, bh, pr, cls, b + p.d.batch_id_offset, cell * p.d.n_masks + n);
             ++pos;
         }
     }
@@ -282,17 +282,20 @@ centernet_activate_kernel(const CnActParams p)
 constexpr int kCnTileH = 32, kCnTileW = 64, kCnThreads = 256;
 constexpr int kCnCells = kCnTileH * kCnTileW;
 constexpr int kCnMaxK = 1024;
+constexpr int kCnSlotCap = 256;          // keys one tile may pass on without reducing them (at least K)
 
 struct CnParams {
     pxe_centernet_decode_desc d;
     long long hbs, sbs, obs;
     int tiles_x, tiles_y;
     int K;
-    int cap;                         // candidate slots per image = blocks per image * K
+    int slots;                       // blocks per image (tiles x classes)
+    int slot_cap;                    // keys a block may pass on: block s of image b owns cand[(b*slots+s)*slot_cap ...]
     float lo;                        // pre-filter: a cell with (value >= lo) false cannot reach the threshold
     float lo_list;                   // work-list bound, a margin below lo (see centernet_peaks_kernel)
-    unsigned long long* cand;        // [batch][cap] sortable keys, unordered
-    int* cand_cnt;                   // [batch], zeroed before the launch
+    unsigned long long* cand;        // [batch][slots][K] sortable keys, unordered inside a slot
+    int* cand_cnt;                   // [batch][slots]
+    unsigned long long* list;        // [batch][slots*K] per-image compacted list, used when it exceeds shared memory
     pxe_detection* dets; int* counts;
 };
 
@@ -323,9 +326,17 @@ __device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist,
     for (int shift = 56; shift >= 0; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
         __syncthreads();
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const unsigned long long key = get(i);
-            if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 0xff)], 1);
+        // Scores of one image share their leading bits, so most keys fall into one or two bins of the
+        // early passes: lanes with equal digits are combined before touching shared memory.
+        for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+            const int i = i0 + threadIdx.x;
+            unsigned digit = 0x100u;                      // "no key": its own group, never counted
+            if (i < n) {
+                const unsigned long long key = get(i);
+                if ((key & mask) == prefix) digit = (unsigned)((key >> shift) & 0xff);
+            }
+            const unsigned same = __match_any_sync(0xffffffffu, digit);
+            if (digit < 0x100u && (threadIdx.x & 31) == (unsigned)(__ffs(same) - 1)) atomicAdd(&hist[digit], __popc(same));
         }
         __syncthreads();
         if (threadIdx.x < 32) {
@@ -381,6 +392,14 @@ __device__ __forceinline__ float cn_score(const CnParams& p, float v)
     // the reference's activation expression (src/CenterNetKernels.cu:17), precise math: scores and
     // therefore the kept indices are bit-identical to the reference's CUDA path
     return p.d.heat_is_logit ? 1.0f / (1.0f + expf(-v)) : v;
+}
+
+// include/CenterNetLayer.h:217-225: box size and centre offset must be finite and the size positive.
+__device__ __forceinline__ bool cn_valid(const float* size, const float* off, long long idx, long long area, int W, int H)
+{
+    const float bw = size[idx] / W, bh = size[area + idx] / H;
+    const float ox = off[idx], oy = off[area + idx];
+    return isfinite(bw) && isfinite(bh) && isfinite(ox) && isfinite(oy) && bw > 0.0f && bh > 0.0f;
 }
 
 // One block per (32x64 tile, class, image).
@@ -444,10 +463,15 @@ centernet_peaks_kernel(const CnParams p)
             const int si = row * kCnRowStride + 4 + 4 * vx;
             *reinterpret_cast<float4*>(tile + si) = v;
             *reinterpret_cast<float4*>(score + si) = make_float4(NEG, NEG, NEG, NEG);
-            if (v.x >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)si;
-            if (v.y >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)(si + 1);
-            if (v.z >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)(si + 2);
-            if (v.w >= lo_list) work[atomicAdd(&n_work, 1)] = (unsigned short)(si + 3);
+            const int hx = v.x >= lo_list, hy = v.y >= lo_list, hz = v.z >= lo_list, hw = v.w >= lo_list;
+            const int hits = hx + hy + hz + hw;
+            if (hits) {                                  // one reservation per thread, not per element
+                int at = atomicAdd(&n_work, hits);
+                if (hx) work[at++] = (unsigned short)si;
+                if (hy) work[at++] = (unsigned short)(si + 1);
+                if (hz) work[at++] = (unsigned short)(si + 2);
+                if (hw) work[at] = (unsigned short)(si + 3);
+            }
         }
         // halo columns: 34 rows x {left, right}
         for (int i = threadIdx.x; i < (kCnTileH + 2) * 2; i += kCnThreads) {
@@ -482,9 +506,8 @@ centernet_peaks_kernel(const CnParams p)
     }
     __syncthreads();
 
-    // ---- peak test, validity, key
-    const float* size = p.d.size + (long long)b * p.sbs;
-    const float* off = p.d.offset + (long long)b * p.obs;
+    // ---- peak test -> key.  Size / offset validity needs four gathers per candidate from global memory; the
+    // common case leaves that to the per-image kernel so that this kernel's only wait on memory is the tile load.
     for (int wi = threadIdx.x; wi < todo; wi += kCnThreads) {
         const int si = work[wi];
         const int row = si / kCnRowStride, col = si - row * kCnRowStride - 4;
@@ -497,85 +520,143 @@ centernet_peaks_kernel(const CnParams p)
         const float* c = score + si;
         if (c[-kCnRowStride - 1] > s || c[-kCnRowStride] > s || c[-kCnRowStride + 1] > s || c[-1] > s || c[1] > s ||
             c[kCnRowStride - 1] > s || c[kCnRowStride] > s || c[kCnRowStride + 1] > s) continue;
-        const long long idx = (long long)gy * W + gx;
-        const float bw = size[idx] / W, bh = size[area + idx] / H;
-        const float ox = off[idx], oy = off[area + idx];
-        if (!isfinite(bw) || !isfinite(bh) || !isfinite(ox) || !isfinite(oy) || bw <= 0.0f || bh <= 0.0f) continue;
         const int slot = atomicAdd(&n_keys, 1);
-        keys[slot] = cn_key(s, (uint32_t)((long long)cls * area + idx));
+        keys[slot] = cn_key(s, (uint32_t)((long long)cls * area + (long long)gy * W + gx));
     }
     __syncthreads();
 
-    const int n = n_keys;
-    if (n == 0) return;
-    unsigned long long* out = p.cand + (long long)b * p.cap;
-    if (n <= p.K) {
-        if (threadIdx.x == 0) base = atomicAdd(&p.cand_cnt[b], n);
-        __syncthreads();
-        for (int i = threadIdx.x; i < n; i += kCnThreads) out[base + i] = keys[i];
+    int n = n_keys;
+    const long long slot_id = (long long)b * p.slots + (long long)cls * (p.tiles_x * p.tiles_y) + blockIdx.x;
+    unsigned long long* out = p.cand + slot_id * p.slot_cap;
+    if (n <= p.slot_cap) {
+        for (int i = threadIdx.x; i < n; i += kCnThreads) out[i] = keys[i];
+        if (threadIdx.x == 0) p.cand_cnt[slot_id] = n;
         return;
     }
-    // more candidates than can ever be kept from one image: pass on only this block's K best
-    const unsigned long long kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
-    if (threadIdx.x == 0) base = atomicAdd(&p.cand_cnt[b], p.K);
+    // Rare: more candidates than the tile's slot holds (slot_cap >= K).  No image keeps more than K, so the
+    // tile's K best are enough -- but only valid candidates may compete for those places, so validity is
+    // checked here first.
+    const float* size = p.d.size + (long long)b * p.sbs;
+    const float* off = p.d.offset + (long long)b * p.obs;
+    for (int i = threadIdx.x; i < n; i += kCnThreads) {
+        const uint32_t flat = 0xffffffffu - (uint32_t)(keys[i] & 0xffffffffu);
+        if (!cn_valid(size, off, (long long)flat - (long long)cls * area, area, W, H)) keys[i] = 0ULL;   // sorts last
+    }
+    if (threadIdx.x == 0) base = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += kCnThreads)
-        if (keys[i] >= kth) out[base + atomicAdd(&n_out, 1)] = keys[i];
+        if (keys[i] != 0ULL) atomicAdd(&base, 1);
+    __syncthreads();
+    const int n_valid = base;
+    if (n_valid <= p.K) {
+        for (int i = threadIdx.x; i < n; i += kCnThreads)
+            if (keys[i] != 0ULL) out[atomicAdd(&n_out, 1)] = keys[i];
+        if (threadIdx.x == 0) p.cand_cnt[slot_id] = n_valid;
+        return;
+    }
+    const unsigned long long kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
+    for (int i = threadIdx.x; i < n; i += kCnThreads)
+        if (keys[i] >= kth) out[atomicAdd(&n_out, 1)] = keys[i];
+    if (threadIdx.x == 0) p.cand_cnt[slot_id] = p.K;
 }
 
 // One block per image: the K best of the image's candidates, sorted, decoded to boxes.
-// Few candidates are sorted outright; otherwise the K-th largest key is found by radix selection
-// (8 passes over the list, which sits in L2) and only the K winners are sorted.
-constexpr int kCnTopkThreads = 256;
-constexpr int kCnStageKeys = 4096;     // candidates per image staged in shared memory (32 KB)
+//  1. prefix sums of the slots' counts, so that candidate i of the image is found by a binary search;
+//  2. every candidate's size / offset validity (include/CenterNetLayer.h:217-225), all gathers in
+//     flight at once; valid keys are compacted into one list (shared memory when it fits);
+//  3. a list that fits shared memory is sorted outright (bitonic: no contention, unlike a radix
+//     histogram of scores that share their leading bits); a longer one goes through radix
+//     selection of the K-th key first.
+constexpr int kCnTopkThreads = 1024;
+constexpr int kCnStageKeys = 4096;     // candidates per image sorted in shared memory (32 KB)
+constexpr int kCnMaxSlots = 2048;      // slots per image whose prefix sums fit shared memory
 
 __global__ void __launch_bounds__(kCnTopkThreads)
 centernet_topk_kernel(const CnParams p)
 {
-    __shared__ unsigned long long sorted[kCnMaxK];
     __shared__ unsigned long long stage[kCnStageKeys];
+    __shared__ int prefix[kCnMaxSlots + 1];
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
-    __shared__ int n_best;
+    __shared__ int warp_tot[32];
+    __shared__ int n_best, n_valid;
     const int b = blockIdx.x;
-    const unsigned long long* cand = p.cand + (long long)b * p.cap;
-    const int n = p.cand_cnt[b];
-    int m;
-    if (n <= p.K || n <= 256) {
-        int pow2 = 1;
-        while (pow2 < n) pow2 <<= 1;
-        for (int i = threadIdx.x; i < pow2; i += blockDim.x) sorted[i] = i < n ? cand[i] : 0ULL;
-        __syncthreads();
-        block_bitonic_desc(sorted, pow2);
-        m = n < p.K ? n : p.K;
-    } else {
-        if (threadIdx.x == 0) n_best = 0;
-        // the selection makes 8 passes over the list: stage it in shared memory when it fits
-        const bool staged = n <= kCnStageKeys;
-        if (staged) {
-            for (int i = threadIdx.x; i < n; i += blockDim.x) stage[i] = cand[i];
-            __syncthreads();
-        }
-        const unsigned long long* src = staged ? stage : cand;
-        const unsigned long long kth = block_select_kth([&](int i) { return src[i]; }, n, p.K, hist, sel);
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const unsigned long long key = src[i];
-            if (key >= kth) sorted[atomicAdd(&n_best, 1)] = key;
-        }
-        __syncthreads();
-        m = n_best;                                      // == K: keys are distinct
-        int pow2 = 1;
-        while (pow2 < m) pow2 <<= 1;
-        for (int i = m + threadIdx.x; i < pow2; i += blockDim.x) sorted[i] = 0ULL;
-        __syncthreads();
-        block_bitonic_desc(sorted, pow2);
-    }
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
-    const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
-    const float image_h = p.d.image_height > 0 ? (float)p.d.image_height : 1.0f;
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
+    const unsigned long long* cand = p.cand + (long long)b * p.slots * p.slot_cap;
+    const int* cnt = p.cand_cnt + (long long)b * p.slots;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) { n_valid = 0; n_best = 0; prefix[0] = 0; }
+
+    // 1. inclusive prefix of slot counts -> prefix[s+1]
+    int carry = 0;
+    for (int base = 0; base < p.slots; base += kCnTopkThreads) {
+        const int sidx = base + threadIdx.x;
+        const int v = sidx < p.slots ? cnt[sidx] : 0;
+        int inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        __syncthreads();
+        int before = carry;
+        for (int i = 0; i < warp; ++i) before += warp_tot[i];
+        if (sidx < p.slots) prefix[sidx + 1] = before + inc;
+        int total = 0;
+        for (int i = 0; i < 32; ++i) total += warp_tot[i];
+        carry += total;
+        __syncthreads();
+    }
+    const int n_total = carry;
+
+    // 2. validity + compaction
+    const bool staged = n_total <= kCnStageKeys;
+    unsigned long long* list = staged ? stage : p.list + (long long)b * p.slots * p.slot_cap;
+    for (int i = threadIdx.x; i < n_total; i += kCnTopkThreads) {
+        int lo = 0, hi = p.slots;                    // largest s with prefix[s] <= i
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= i) lo = mid; else hi = mid;
+        }
+        const unsigned long long key = cand[(long long)lo * p.slot_cap + (i - prefix[lo])];
+        const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
+        const uint32_t cls = flat / (uint32_t)area;
+        if (cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) list[atomicAdd(&n_valid, 1)] = key;
+    }
+    __syncthreads();
+    const int n = n_valid;
+
+    // 3. order the best K
+    unsigned long long* sorted = stage;
+    int m;
+    if (staged) {
+        int pow2 = 1;
+        while (pow2 < n) pow2 <<= 1;
+        for (int i = n + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+        __syncthreads();
+        block_bitonic_desc(stage, pow2);
+        m = n < p.K ? n : p.K;
+    } else {
+        // the list is in global memory; the K winners are collected into `stage`
+        unsigned long long kth = 1ULL;               // every real key is >= 1
+        if (n > p.K) kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
+        for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
+            const unsigned long long key = list[i];
+            if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
+        }
+        __syncthreads();
+        m = n_best;
+        int pow2 = 1;
+        while (pow2 < m) pow2 <<= 1;
+        for (int i = m + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+        __syncthreads();
+        block_bitonic_desc(stage, pow2);
+    }
+    const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
+    const float image_h = p.d.image_height > 0 ? (float)p.d.image_height : 1.0f;
     for (int i = threadIdx.x; i < m; i += blockDim.x) {
         const unsigned long long key = sorted[i];
         const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
@@ -586,13 +667,9 @@ centernet_topk_kernel(const CnParams p)
         // include/CenterNetLayer.h:217-237, each product and sum rounded separately as on the host
         const float bw = size[idx] / W, bh = size[area + idx] / H;
         const float cx = (x + off[idx]) / W, cy = (y + off[area + idx]) / H;
-        pxe_detection det;
-        det.x = __fmul_rn(__fsub_rn(cx, bw / 2.0f), image_w);
-        det.y = __fmul_rn(__fsub_rn(cy, bh / 2.0f), image_h);
-        det.w = __fmul_rn(bw, image_w);
-        det.h = __fmul_rn(bh, image_h);
-        det.prob = score; det.class_id = cls; det.batch_id = b + p.d.batch_id_offset; det.source = (int)flat;
-        p.dets[(long long)b * p.K + i] = det;
+        store_detection(p.dets + (long long)b * p.K + i, __fmul_rn(__fsub_rn(cx, bw / 2.0f), image_w),
+                        __fmul_rn(__fsub_rn(cy, bh / 2.0f), image_h), __fmul_rn(bw, image_w), __fmul_rn(bh, image_h),
+                        score, cls, b + p.d.batch_id_offset, (int)flat);
     }
     if (threadIdx.x == 0) p.counts[b] = m;
 }
@@ -829,8 +906,9 @@ extern "C" size_t pxe_centernet_decode_workspace_bytes(int batch, int classes, i
     int tx, ty;
     long long bpi;
     cn_geometry(classes, height, width, &tx, &ty, &bpi);
-    return align_up((size_t)batch * bpi * max_detections * sizeof(unsigned long long), 256)
-           + align_up((size_t)batch * sizeof(int), 256);
+    const size_t slot_cap = max_detections > kCnSlotCap ? max_detections : kCnSlotCap;
+    return 2 * align_up((size_t)batch * bpi * slot_cap * sizeof(unsigned long long), 256)
+           + align_up((size_t)batch * bpi * sizeof(int), 256);
 }
 
 // Pre-activation value below which sigmoid(v) < threshold for certain (with a margin far wider
@@ -873,19 +951,24 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     p.obs = d.offset_batch_stride ? d.offset_batch_stride : 2 * area;
     long long bpi;
     cn_geometry(d.classes, d.height, d.width, &p.tiles_x, &p.tiles_y, &bpi);
-    PXE_REQUIRE(bpi * d.max_detections < 0x7fffffffLL, "centernet_decode: candidate table too large");
+    PXE_REQUIRE(bpi * (d.max_detections > kCnSlotCap ? d.max_detections : kCnSlotCap) < 0x7fffffffLL,
+                "centernet_decode: candidate table too large");
+    if (bpi > kCnMaxSlots)
+        return set_error(PXE_ERR_UNSUPPORTED, "centernet_decode: %lld tiles x classes per image exceed %d", bpi, kCnMaxSlots);
     p.K = d.max_detections;
-    p.cap = (int)(bpi * d.max_detections);
+    p.slots = (int)bpi;
+    p.slot_cap = d.max_detections > kCnSlotCap ? d.max_detections : kCnSlotCap;
     p.lo = centernet_prefilter(d);
     p.lo_list = d.heat_is_logit ? p.lo - 2e-4f * fmaxf(1.0f, fabsf(p.lo)) : p.lo;
     char* ws = static_cast<char*>(workspace);
     p.cand = reinterpret_cast<unsigned long long*>(ws);
-    ws += align_up((size_t)d.batch * p.cap * sizeof(unsigned long long), 256);
+    ws += align_up((size_t)d.batch * bpi * p.slot_cap * sizeof(unsigned long long), 256);
+    p.list = reinterpret_cast<unsigned long long*>(ws);
+    ws += align_up((size_t)d.batch * bpi * p.slot_cap * sizeof(unsigned long long), 256);
     p.cand_cnt = reinterpret_cast<int*>(ws);
     p.dets = dets; p.counts = counts;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    PXE_CUDA_OK(cudaMemsetAsync(p.cand_cnt, 0, (size_t)d.batch * sizeof(int), s));
     dim3 grid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, (unsigned)d.batch);
     // 128-bit tile loads need every row segment of a tile to start on a 16-byte boundary
     const bool vec = d.width % 4 == 0 && aligned16(d.heat) && p.hbs % 4 == 0;

@@ -343,3 +343,87 @@ class Runner:
         if nms_threshold is not None:
             recs = ops.nms(recs, nms_threshold)
         return recs, total
+
+
+class PipelinedPredictor:
+    """Keeps the GPU busy across consecutive ``predict`` calls: while batch i runs, batch i+1 is copied to
+    the device on a second stream and the detections of batch i-1 are copied back on a third.  Two input
+    buffers, two detection buffers and two pinned result buffers alternate.  Every batch still pays its
+    own host-to-device and device-to-host copy; they merely overlap the compute of its neighbours.
+
+    Usage: ``submit(host_batch)`` for each batch, in order; each call returns the finished result of the
+    batch submitted one call earlier (``None`` for the first), ``drain()`` returns the last one.  A result
+    is ``(records, total)`` where ``records`` is a structured view of pinned memory that stays valid
+    until two more batches have been submitted.
+    """
+
+    def __init__(self, runner: Runner, batch_shape, pinned_capacity: Optional[int] = None):
+        self.r = runner
+        dev = runner.device
+        self.compute = torch.cuda.current_stream(dev)
+        self.h2d, self.d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        cap = pinned_capacity or runner.dets.capacity
+        self.x = [torch.empty(batch_shape, device=dev) for _ in range(2)]
+        self.bufs = [runner.dets, ops.DetectionBuffer(runner.dets.capacity, dev)]
+        self.pinned = [torch.empty((cap, 8), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.count_host = [torch.zeros(1, dtype=torch.int64).pin_memory() for _ in range(2)]
+        self.x_ready = [None, None]       # event: input slot filled
+        self.x_free = [None, None]        # event: the forward that read this input slot finished
+        self.out_done = [None, None]      # event: detections of this slot are on the host
+        self.pending = None               # (slot, event after forward)
+        self.n = 0
+
+    def _stage(self, host_batch, slot):
+        with torch.cuda.stream(self.h2d):
+            if self.x_free[slot] is not None:
+                self.h2d.wait_event(self.x_free[slot])
+            self.x[slot].copy_(host_batch, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.h2d)
+            self.x_ready[slot] = ev
+
+    def _retire(self):
+        slot, done = self.pending
+        self.pending = None
+        buf = self.bufs[slot]
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(done)
+            self.count_host[slot].copy_(buf.count, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.d2h)
+        ev.synchronize()                                  # the next forward is already queued behind this one
+        total = int(self.count_host[slot].item())
+        n = min(total, buf.capacity, self.pinned[slot].shape[0])
+        with torch.cuda.stream(self.d2h):
+            self.pinned[slot][:n].copy_(buf.dets[:n], non_blocking=True)
+            out = torch.cuda.Event()
+            out.record(self.d2h)
+        self.out_done[slot] = out
+        return slot, n, total
+
+    def _result(self, slot, n, total):
+        self.out_done[slot].synchronize()
+        return self.pinned[slot][:n].numpy().view(ops.DET_DTYPE).reshape(-1), total
+
+    def submit(self, host_batch: torch.Tensor):
+        slot = self.n % 2
+        self.n += 1
+        self._stage(host_batch, slot)
+        self.compute.wait_event(self.x_ready[slot])
+        if self.out_done[slot] is not None:
+            self.compute.wait_event(self.out_done[slot])  # this slot's previous detections have left the device
+        self.r.dets = self.bufs[slot]
+        self.r.forward(self.x[slot])
+        done = torch.cuda.Event()
+        done.record(self.compute)
+        self.x_free[slot] = done
+        finished = None
+        if self.pending is not None:
+            finished = self._retire()
+        self.pending = (slot, done)
+        return self._result(*finished) if finished is not None else None
+
+    def drain(self):
+        if self.pending is None:
+            return None
+        return self._result(*self._retire())

@@ -122,3 +122,23 @@ def test_batch_sharding_gives_identical_detections(cuda):
     merged = sharding.merge_shards(shards)
     assert n == len(whole) == len(merged) and n > 0
     assert merged.tobytes() == whole.tobytes()
+
+
+def test_pipelined_predictor_equals_sequential_predict(cuda):
+    """Overlapping the copies of neighbouring batches with compute changes no record."""
+    from pixienn_b200.runner import PipelinedPredictor
+    model = graph.parse_model(presets.yolov3_tiny(160, 160))
+    weights = synth_weights(model, 9, head_bias=-3.0)
+    batches = [torch.from_numpy(make_input(20 + i, 2, model)).pin_memory() for i in range(4)]
+    seq = Runner(model, weights, 2, cuda)
+    want = [seq.predict(b)[0].copy() for b in batches]
+    pipe = PipelinedPredictor(Runner(model, weights, 2, cuda), tuple(batches[0].shape))
+    got = []
+    for b in batches:
+        r = pipe.submit(b)
+        if r is not None:
+            got.append(r[0].copy())
+    got.append(pipe.drain()[0].copy())
+    assert len(got) == len(want) == 4
+    for g, w in zip(got, want):
+        assert len(w) > 0 and g.tobytes() == w.tobytes()
