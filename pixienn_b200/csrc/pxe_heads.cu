@@ -317,13 +317,15 @@ __device__ __forceinline__ unsigned long long cn_key(float score, uint32_t flat)
 
 // Finds the k-th largest of n distinct 64-bit keys (1 <= k <= n) by most-significant-digit radix
 // selection, 8 bits per pass.  `get(i)` returns key i.  All threads of the block must call; every
-// thread returns the key.  hist: 256 ints of shared memory, sh: 2 x u64.
+// thread returns the key.  hist: 256 ints of shared memory, sh: 2 x u64.  With passes < 8 only the leading
+// digits are resolved (see the end of the function).
 template <typename Get>
-__device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist, unsigned long long* sh)
+__device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist, unsigned long long* sh,
+                                               int passes = 8, int* want_out = nullptr)
 {
     unsigned long long prefix = 0, mask = 0;
     int want = k;
-    for (int shift = 56; shift >= 0; shift -= 8) {
+    for (int shift = 56; shift > 56 - 8 * passes; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
         __syncthreads();
         // Scores of one image share their leading bits, so most keys fall into one or two bins of the
@@ -367,6 +369,9 @@ __device__ unsigned long long block_select_kth(Get get, int n, int k, int* hist,
         mask |= 0xffULL << shift;
         __syncthreads();
     }
+    // after fewer than 8 passes: `prefix` holds the leading digits of the k-th key and *want_out how many
+    // keys with exactly those leading digits still belong to the k largest
+    if (want_out) *want_out = want;
     return prefix;
 }
 
@@ -640,20 +645,51 @@ centernet_topk_kernel(const CnParams p)
         block_bitonic_desc(stage, pow2);
         m = n < p.K ? n : p.K;
     } else {
-        // the list is in global memory; the K winners are collected into `stage`
-        unsigned long long kth = 1ULL;               // every real key is >= 1
-        if (n > p.K) kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
-        for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
-            const unsigned long long key = list[i];
-            if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
+        // The list is in global memory.  Two radix passes fix the leading 16 bits of the K-th key; keys above
+        // them are certain winners, keys sharing them are the only ones still undecided.  With scores spread
+        // over the second byte that is a few hundred keys, which are sorted in shared memory.  If the
+        // undecided set does not fit (e.g. a constant heatmap), the full 8-pass selection decides.
+        int m_sort = 0;
+        if (n > p.K) {
+            int want = 0;
+            const unsigned long long lead = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel, 2, &want) >> 48;
+            const int winners = p.K - want;
+            if (threadIdx.x == 0) { n_best = 0; n_valid = 0; }      // n_valid is reused as the tie counter
+            __syncthreads();
+            for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
+                const unsigned long long key = list[i];
+                const unsigned long long top = key >> 48;
+                if (top > lead) stage[atomicAdd(&n_best, 1)] = key;
+                else if (top == lead) {
+                    const int at = atomicAdd(&n_valid, 1);
+                    if (winners + at < kCnStageKeys) stage[winners + at] = key;
+                }
+            }
+            __syncthreads();
+            if (winners + n_valid <= kCnStageKeys) {
+                m_sort = winners + n_valid;
+            } else {
+                const unsigned long long kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
+                if (threadIdx.x == 0) n_best = 0;
+                __syncthreads();
+                for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
+                    const unsigned long long key = list[i];
+                    if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
+                }
+                __syncthreads();
+                m_sort = n_best;
+            }
+        } else {
+            for (int i = threadIdx.x; i < n; i += kCnTopkThreads) stage[i] = list[i];
+            m_sort = n;
         }
         __syncthreads();
-        m = n_best;
         int pow2 = 1;
-        while (pow2 < m) pow2 <<= 1;
-        for (int i = m + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+        while (pow2 < m_sort) pow2 <<= 1;
+        for (int i = m_sort + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
         __syncthreads();
         block_bitonic_desc(stage, pow2);
+        m = m_sort < p.K ? m_sort : p.K;
     }
     const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
     const float image_h = p.d.image_height > 0 ? (float)p.d.image_height : 1.0f;
