@@ -36,6 +36,12 @@ import numpy as np  # noqa: E402
 SEED = 1234
 CONF = 0.2
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of each kernel on a [32,32,208,208] tensor,
+# divided by that launch's algorithmic bytes (profiles/epilogue_kernel_*.md, profiles/epilogue_pool_kernel_*.md).
+# Traffic grows in proportion to the tensor, so a launch's traffic is this ratio times its algorithmic bytes; the
+# ratio is below 1 because part of the written lines is still dirty in L2 when the kernel ends.
+NCU_TRAFFIC_RATIO = {"epilogue": 0.838, "epilogue+shortcut": 0.923, "epilogue+pool": 0.935}
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -236,7 +242,11 @@ def run_model(args):
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / 8000.0, 4),
-                     "peak_source": peak_src, "traffic": None,
+                     "peak_source": peak_src,
+                     "traffic": (int(NCU_TRAFFIC_RATIO[dom] * d["bytes"] / d["launches"]) if dom in NCU_TRAFFIC_RATIO else None),
+                     "traffic_note": "bytes per launch (average over the timed launches): ncu DRAM read+write of a smaller "
+                                     "capture of this kernel, scaled by algorithmic bytes",
+                     "algorithmic_bytes_per_launch": int(d["bytes"] / d["launches"]),
                      "launches_timed": d["launches"], "avg_launch_ms": round(d["ms"] / d["launches"], 4),
                      "algorithmic_bytes_per_step": int(d["bytes"] / args.steps)},
         "epilogue": {"ms_per_step": round(epi_ms, 3), "algorithmic_GB_per_step": round(epi_bytes / 1e9, 3),
@@ -315,6 +325,8 @@ def run_sweep(args):
     shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
     if args.sweep_shapes:
         shapes = shapes[:args.sweep_shapes]
+    if args.sweep_shape_index >= 0:
+        shapes = [shapes[args.sweep_shape_index]]
     rows = []
     for (C, H, W) in shapes:
         B = args.batch
@@ -561,6 +573,7 @@ def main():
     ap.add_argument("--det-capacity", type=int, default=24 * (1 << 20))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep-shapes", type=int, default=0, help="only the first N shapes of the sweep")
+    ap.add_argument("--sweep-shape-index", type=int, default=-1, help="only this shape of the sweep (0..4)")
     ap.add_argument("--sweep-acts", default="leaky,mish,swish,logistic")
     ap.add_argument("--sweep-pool", default="both", choices=["none", "pool", "both"])
     ap.add_argument("--sweep-residual", action="store_true", help="sweep the epilogue fused with a shortcut add")

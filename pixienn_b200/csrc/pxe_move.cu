@@ -20,7 +20,7 @@ struct UpParams {
 };
 
 // Stride 2, VI input columns per thread (4: float4 in, two float4 per output row;
-// 2: float2 in, one float4 per output row).  out = scale * in, assigned
+// 2: float2 in, one float4 per output row; 1: scalar in, one float2 per output row).  out = scale * in, assigned
 // (include/UpsampleLayer.h:113; the CUDA kernel's "+=" lands on a zero-filled buffer).
 template <int VI>
 __global__ void __launch_bounds__(kThreads)
@@ -44,12 +44,18 @@ upsample2_vec_kernel(const UpParams p)
             *reinterpret_cast<float4*>(dst + 4) = hi;
             *reinterpret_cast<float4*>(dst + ow) = lo;
             *reinterpret_cast<float4*>(dst + ow + 4) = hi;
-        } else {
+        } else if (VI == 2) {
             float2 v = *reinterpret_cast<const float2*>(src);
             v.x *= p.scale; v.y *= p.scale;
             const float4 o = make_float4(v.x, v.x, v.y, v.y);
             *reinterpret_cast<float4*>(dst) = o;
             *reinterpret_cast<float4*>(dst + ow) = o;
+        } else {
+            // odd widths (13, 19): one input element per thread, the output rows are still 8-byte aligned
+            const float v = src[0] * p.scale;
+            const float2 o = make_float2(v, v);
+            *reinterpret_cast<float2*>(dst) = o;
+            *reinterpret_cast<float2*>(dst + ow) = o;
         }
     }
 }
@@ -160,12 +166,14 @@ extern "C" int pxe_upsample(pxe_stream_t stream, const float* x, long long x_bat
         if (width % 4 == 0 && aligned16(x) && p.xbs % 4 == 0) vi = 4;
         else if (width % 2 == 0 && aligned8(x) && p.xbs % 2 == 0) vi = 2;
     }
+    if (stride == 2 && vi == 0 && aligned8(y) && p.ybs % 2 == 0) vi = 1;
     if (vi) {
         p.total = (uint32_t)((long long)batch * chw / vi);
         p.div_w = FastDiv((uint32_t)(width / vi)); p.div_h = FastDiv((uint32_t)height); p.div_c = FastDiv((uint32_t)channels);
         unsigned grid = grid_for(p.total, kThreads, di.sm_count, 16);
         if (vi == 4) upsample2_vec_kernel<4><<<grid, kThreads, 0, s>>>(p);
-        else upsample2_vec_kernel<2><<<grid, kThreads, 0, s>>>(p);
+        else if (vi == 2) upsample2_vec_kernel<2><<<grid, kThreads, 0, s>>>(p);
+        else upsample2_vec_kernel<1><<<grid, kThreads, 0, s>>>(p);
     } else {
         p.total = (uint32_t)((long long)batch * ochw);
         p.div_w = FastDiv((uint32_t)(width * stride)); p.div_h = FastDiv((uint32_t)(height * stride));
