@@ -336,43 +336,52 @@ def run_sweep(args):
         bias = torch.from_numpy(synth.normal(SEED, f"sweepb{C}", C, 0, 0.1)).to(dev)
         base = torch.randn((B, C, H, W), device=dev, generator=torch.Generator(dev).manual_seed(SEED))
         xs = [base.clone() for _ in range(sets)]
-        frm = base.clone() if args.sweep_residual else None
+        frm = [base.clone() for _ in range(sets)] if args.sweep_residual else None
+
+        def graph_time(call):
+            """Median / min device time (ms) of one call: a CUDA graph holds one launch per rotating input set;
+            replays are timed with events, so no Python / ctypes launch cost sits between the launches."""
+            for i in range(max(args.warmup, sets)):
+                call(i)
+            torch.cuda.synchronize()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                for i in range(sets):
+                    call(i)
+            cg.replay()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+            torch.cuda.synchronize()
+            for a, z in ev:
+                a.record(); cg.replay(); z.record()
+            torch.cuda.synchronize()
+            ts = sorted(a.elapsed_time(z) / sets for a, z in ev)
+            return ts[len(ts) // 2], ts[0]
+
+        # the floor at this size: a plain device-to-device copy of the same tensor (4 B read + 4 B written per element)
+        dsts = [torch.empty_like(base) for _ in range(sets)]
+        copy_med, _ = graph_time(lambda i: dsts[i % sets].copy_(xs[i % sets]))
+        del dsts
         for act in args.sweep_acts.split(","):
             for pool in {"none": (False,), "pool": (True,), "both": (False, True)}[args.sweep_pool]:
                 if pool and frm is not None:
                     continue
                 oh = ops.maxpool_out_dim(H, 2, 2, 1)
-                yp = torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) if pool else None
+                yps = [torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) for _ in range(sets)] if pool else None
 
                 def call(i):
                     if pool:
                         ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
-                                          pool=(2, 2, 1), y_pool=yp)
+                                          pool=(2, 2, 1), y_pool=yps[i % sets])
                     elif frm is not None:      # conv epilogue + the shortcut layer that follows it: 12 B / element
                         ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
-                                          residual=frm, res_act="linear")
+                                          residual=frm[i % sets], res_act="linear")
                     else:
                         ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act)
-                for i in range(max(args.warmup, sets)):
-                    call(i)
-                torch.cuda.synchronize()
-                # one CUDA graph = one launch on each rotating input set; replays are timed with events, so the
-                # figure is device time per launch without the Python / ctypes launch cost in between
-                cg = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(cg):
-                    for i in range(sets):
-                        call(i)
-                cg.replay()
-                ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-                torch.cuda.synchronize()
-                for a, z in ev:
-                    a.record(); cg.replay(); z.record()
-                torch.cuda.synchronize()
-                ts = sorted(a.elapsed_time(z) / sets for a, z in ev)
-                med = ts[len(ts) // 2]
-                nbytes = (4 * n + 4 * yp.numel()) if pool else (12 * n if frm is not None else 8 * n)
+                med, tmin = graph_time(call)
+                nbytes = (4 * n + 4 * yps[0].numel()) if pool else (12 * n if frm is not None else 8 * n)
                 rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "residual": frm is not None, "MB": round(nbytes / 1e6, 1),
-                             "us_median": round(med * 1e3, 2), "us_min": round(ts[0] * 1e3, 2),
+                             "us_median": round(med * 1e3, 2), "us_min": round(tmin * 1e3, 2),
+                             "copy_us": round(copy_med * 1e3, 2), "copy_GBps": round(8 * n / copy_med / 1e6, 1),
                              "GBps": round(nbytes / med / 1e6, 1), "frac_measured": round(nbytes / med / 1e6 / peak, 3),
                              "frac_8000": round(nbytes / med / 1e6 / 8000, 3)})
         del xs
@@ -600,4 +609,9 @@ def main():
 
 
 if __name__ == "__main__":
+    # Native libraries (NCCL's version banner, cuDNN) write to file descriptor 1; the contract is ONE JSON line on
+    # stdout. Python's own stdout keeps the real descriptor, everything else that writes to fd 1 lands on stderr.
+    _real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(_real_stdout, "w")
     main()

@@ -162,7 +162,7 @@ __device__ __forceinline__ float act_mish_fast(float x)
 template <int ACT, bool FAST = false>
 __device__ __forceinline__ float activate(float x)
 {
-    if (ACT == PXE_ACT_LEAKY) return x > 0.0f ? x : 0.1f * x;
+    if (ACT == PXE_ACT_LEAKY) return fmaxf(x, 0.1f * x);      // == (x > 0 ? x : 0.1f * x) for every x, NaN and -0 included
     if (ACT == PXE_ACT_LINEAR) return x;
     if (ACT == PXE_ACT_LOGGY) return 2.0f / (1.0f + expf(-x)) - 1.0f;
     if (ACT == PXE_ACT_LOGISTIC) return FAST ? act_logistic_fast(x) : act_logistic(x);

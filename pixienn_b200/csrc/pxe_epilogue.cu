@@ -46,6 +46,10 @@ struct EpiParams {
     // pool kernels
     int OH, OW, OWV;
     FastDiv div_owv, div_ohowv;
+    // even pool kernel: row pairs per plane (OH), units per image, dense-output flags
+    FastDiv div_oh;
+    uint32_t units_per_image;
+    int y_dense, pool_dense;
 };
 
 // Folded coefficients and image / channel numbers of plane `pl` (= image*C + channel).
@@ -398,6 +402,117 @@ epilogue_pool_kernel(const EpiParams p)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The common case of the kernel above with the index arithmetic stripped: H even, W a multiple
+// of the patch width, x densely packed.  Row pairs then tile the whole tensor without gaps, so
+// the input offset of patch u is (u / OWV) * 2W + (u % OWV) * NI -- one division -- and no tap is
+// ever out of range.  The image number (needed only for strided destinations) comes from the
+// coefficient table.  The pooled kernels are issue-bound rather than HBM-bound once a row is
+// short, so instructions per patch are what this form saves.
+// ---------------------------------------------------------------------------------------------
+template <int ACT, bool AFFINE, int VO>
+__global__ void __launch_bounds__(kThreads, VO == 4 ? 6 : 5)
+epilogue_pool_even_kernel(const EpiParams p)
+{
+    extern __shared__ PlaneEntry tab[];
+    const uint32_t lo = blockIdx.x * p.chunk;
+    if (lo >= p.units) return;
+    uint32_t hi = lo + p.chunk;
+    if (hi > p.units) hi = p.units;
+    const uint32_t plane_lo = p.div_ohowv.div(lo);
+    const uint32_t plane_hi = p.div_ohowv.div(hi - 1);
+
+    constexpr int NV = VO;                     // pooled outputs per patch
+    constexpr int NI = 2 * NV;                 // input columns per patch row
+    constexpr int U = 16 / (2 * NI);           // patches per thread per round: 16 input floats in flight
+    const uint32_t W = (uint32_t)p.W;
+    const uint32_t step = kThreads * U;
+    const uint32_t rounds = (hi - lo + step - 1) / step;
+    for (uint32_t rd = 0; rd < rounds; ++rd) {
+        const uint32_t base = lo + rd * step + threadIdx.x;
+        float r0[U][NI], r1[U][NI];
+        uint32_t off[U], pl[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const uint32_t u = base + k * kThreads;
+            if (u < hi) {
+                uint32_t rp, owv;
+                p.div_owv.divmod(u, rp, owv);
+                off[k] = rp * (2 * W) + owv * NI;
+                pl[k] = p.div_oh.div(rp) - plane_lo;
+                const float* x0 = p.x + off[k];
+                if (VO == 4) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
+                    const float4 a1 = *reinterpret_cast<const float4*>(x0 + 4);
+                    const float4 b0 = *reinterpret_cast<const float4*>(x0 + W);
+                    const float4 b1 = *reinterpret_cast<const float4*>(x0 + W + 4);
+                    r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
+                    r0[k][4] = a1.x; r0[k][5] = a1.y; r0[k][6] = a1.z; r0[k][7] = a1.w;
+                    r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
+                    r1[k][4] = b1.x; r1[k][5] = b1.y; r1[k][6] = b1.z; r1[k][7] = b1.w;
+                } else if (VO == 2) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
+                    const float4 b0 = *reinterpret_cast<const float4*>(x0 + W);
+                    r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
+                    r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
+                } else {
+                    const float2 a0 = *reinterpret_cast<const float2*>(x0);
+                    const float2 b0 = *reinterpret_cast<const float2*>(x0 + W);
+                    r0[k][0] = a0.x; r0[k][1] = a0.y;
+                    r1[k][0] = b0.x; r1[k][1] = b0.y;
+                }
+            }
+        }
+        if (rd == 0) {
+            build_table(p, tab, plane_lo, plane_hi);
+            __syncthreads();
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const uint32_t u = base + k * kThreads;
+            if (u >= hi) continue;
+            const PlaneEntry t = tab[pl[k]];
+#pragma unroll
+            for (int j = 0; j < NI; ++j) {
+                r0[k][j] = apply_one<ACT, AFFINE>(r0[k][j], t);
+                r1[k][j] = apply_one<ACT, AFFINE>(r1[k][j], t);
+            }
+            float m[NV];
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+                m[j] = pick(pick(pick(r0[k][2 * j], r0[k][2 * j + 1]), r1[k][2 * j]), r1[k][2 * j + 1]);
+            float* yp = p.ypool + (size_t)u * NV;
+            if (!p.pool_dense) {
+                const uint32_t img = (uint32_t)t.image;
+                yp = p.ypool + (long long)img * p.pbs + (size_t)(u - img * p.units_per_image) * NV;
+            }
+            if (VO == 4) *reinterpret_cast<float4*>(yp) = make_float4(m[0], m[1], m[2], m[3]);
+            else if (VO == 2) *reinterpret_cast<float2*>(yp) = make_float2(m[0], m[1]);
+            else yp[0] = m[0];
+
+            if (p.y) {
+                float* y0 = p.y + off[k];
+                if (!p.y_dense) {
+                    const uint32_t img = (uint32_t)t.image;
+                    y0 = p.y + (long long)img * p.ybs + (off[k] - img * (uint32_t)(p.C * p.HW));
+                }
+                if (VO == 4) {
+                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
+                    *reinterpret_cast<float4*>(y0 + 4) = make_float4(r0[k][4], r0[k][5], r0[k][6], r0[k][7]);
+                    *reinterpret_cast<float4*>(y0 + W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
+                    *reinterpret_cast<float4*>(y0 + W + 4) = make_float4(r1[k][4], r1[k][5], r1[k][6], r1[k][7]);
+                } else if (VO == 2) {
+                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
+                    *reinterpret_cast<float4*>(y0 + W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
+                } else {
+                    *reinterpret_cast<float2*>(y0) = make_float2(r0[k][0], r0[k][1]);
+                    *reinterpret_cast<float2*>(y0 + W) = make_float2(r1[k][0], r1[k][1]);
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------- launch helpers
 // Rounds of the per-thread loop one block runs (a round = one batch of loads per thread).  Measured
 // on B200: short blocks (2 rounds, 32 KB of input each for the streaming kernel) in many waves give
@@ -501,12 +616,28 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
     plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk / per_plane + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
+    // stripped index arithmetic when row pairs tile the tensor: even H, dense x (W already is a multiple of the patch)
+    const char* even_env = getenv("PXE_POOL_EVEN");            // "0" forces the general kernel (tests, experiments)
+    const bool allow_even = !even_env || atoi(even_env) != 0;
+    const bool even = allow_even && vo != 0 && p.H % 2 == 0 && p.xbs == (long long)p.C * p.HW;
     void (*kern)(const EpiParams) = nullptr;
-    switch (vo) {
-    case 4: kern = epilogue_pool_kernel<ACT, AFFINE, 4>; break;
-    case 2: kern = epilogue_pool_kernel<ACT, AFFINE, 2>; break;
-    case 1: kern = epilogue_pool_kernel<ACT, AFFINE, 1>; break;
-    default: kern = epilogue_pool_kernel<ACT, AFFINE, 0>; break;
+    if (even) {
+        p.div_oh = FastDiv((uint32_t)p.OH);
+        p.units_per_image = per_plane * (uint32_t)p.C;
+        p.y_dense = p.ybs == (long long)p.C * p.HW;
+        p.pool_dense = p.pbs == (long long)p.C * p.OH * p.OW;
+        switch (vo) {
+        case 4: kern = epilogue_pool_even_kernel<ACT, AFFINE, 4>; break;
+        case 2: kern = epilogue_pool_even_kernel<ACT, AFFINE, 2>; break;
+        default: kern = epilogue_pool_even_kernel<ACT, AFFINE, 1>; break;
+        }
+    } else {
+        switch (vo) {
+        case 4: kern = epilogue_pool_kernel<ACT, AFFINE, 4>; break;
+        case 2: kern = epilogue_pool_kernel<ACT, AFFINE, 2>; break;
+        case 1: kern = epilogue_pool_kernel<ACT, AFFINE, 1>; break;
+        default: kern = epilogue_pool_kernel<ACT, AFFINE, 0>; break;
+        }
     }
     if (smem > 48 * 1024) {
         if (smem > (size_t)di.max_smem_optin)

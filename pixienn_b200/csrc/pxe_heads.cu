@@ -60,12 +60,30 @@ __device__ __forceinline__ int yolo_chunk(const YoloParams& p, const float* img,
     int cnt = 0;
     const int c0 = chunk * p.chunk_len;
     const int cend = min(c0 + p.chunk_len, p.d.classes);
+    // Raw heads: obj * sigmoid(v) >= thr needs v >= logit(thr / obj).  Values clearly below that bound (by a
+    // margin far wider than any rounding in the sigmoid or the product) are skipped without evaluating the
+    // sigmoid; everything else goes through the exact expression, so the emitted set is unchanged.
+    float skip_below = -INFINITY;
+    if (p.d.head_is_raw && p.d.threshold > 0.0f) {
+        const float ratio = p.d.threshold / obj;
+        if (ratio < 0.999f) {
+            const float l = logf(ratio / (1.0f - ratio));
+            skip_below = l - 1e-3f - 1e-3f * fabsf(l);
+        }
+    }
 #pragma unroll
     for (int j = 0; j < kYoloChunk; ++j) {
         prob[j] = -1.0f;
         const int cls = c0 + j;
         if (cls < cend) {
-            const float pr = obj * yolo_value(p, img, n, 5 + cls, cell);
+            const int ch = n * p.entries + 5 + cls;
+            float v = img[(long long)ch * p.HW + cell];
+            if (p.d.head_is_raw) {
+                if (p.d.bias) v += p.d.bias[ch];
+                if (v < skip_below) continue;
+                v = act_logistic(v);
+            }
+            const float pr = obj * v;
             if (pr >= p.d.threshold) { prob[j] = pr; ++cnt; }
         }
     }

@@ -63,12 +63,16 @@ def test_maxpool_ties_nan_and_signed_zero(cuda, oracle):
 
 
 @pytest.mark.parametrize("shape", [(2, 4, 16, 16), (2, 3, 13, 13), (1, 5, 26, 26), (2, 2, 52, 52), (1, 3, 8, 24),
-                                   (1, 2, 7, 12)])
+                                   (1, 2, 7, 12), (2, 37, 13, 13), (1, 10, 26, 26), (1, 2, 104, 104)])
 @pytest.mark.parametrize("act", ["leaky", "mish", "swish", "logistic"])
 @pytest.mark.parametrize("keep_full", [False, True])
-def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full):
+@pytest.mark.parametrize("even_kernel", [None, "0"])
+def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, even_kernel, monkeypatch):
     """BN + bias + activation + 2x2/2 maxpool in one pass == the oracle's separate layers.
-    Pooling picks among the SAME activated values, so pooled == maxpool(full) exactly."""
+    Pooling picks among the SAME activated values, so pooled == maxpool(full) exactly.
+    PXE_POOL_EVEN=0 forces the general pooled kernel where the even-height fast form would run."""
+    if even_kernel is not None:
+        monkeypatch.setenv("PXE_POOL_EVEN", even_kernel)
     B, C, H, W = shape
     x = synth.normal(31, f"x{shape}", shape)
     (g, b, m, v), dp = bn(32, f"bn{shape}", C, cuda)
@@ -89,14 +93,18 @@ def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full):
     same(yp.cpu().numpy(), oracle.maxpool(full, 2, 2, 1)[0])
 
 
-def test_folded_pool_into_concat_slot(cuda, oracle):
-    B, C, H, W = 2, 6, 16, 16
-    x = synth.normal(34, "xs", (B, C, H, W))
+@pytest.mark.parametrize("shape", [(2, 6, 16, 16), (3, 5, 12, 20), (2, 3, 10, 6)])
+def test_folded_pool_into_concat_slot(cuda, oracle, shape):
+    """Pooled output AND the full-resolution output stored into channel slots of wider buffers."""
+    B, C, H, W = shape
+    x = synth.normal(34, f"xs{shape}", (B, C, H, W))
     wide = torch.full((B, C + 5, H // 2, W // 2), 9.0, device=cuda)
-    _, yp = ops.conv_epilogue(dev(x, cuda), y=False, act="leaky", pool=(2, 2, 1), y_pool=wide[:, 5:])
-    ref = oracle.maxpool(oracle.activate("leaky", x), 2, 2, 1)[0]
-    same(wide[:, 5:].cpu().numpy(), ref)
-    assert (wide[:, :5] == 9.0).all()
+    wide_full = torch.full((B, C + 4, H, W), 7.0, device=cuda)
+    _, yp = ops.conv_epilogue(dev(x, cuda), y=wide_full[:, 4:], act="leaky", pool=(2, 2, 1), y_pool=wide[:, 5:])
+    full = oracle.activate("leaky", x)
+    same(wide[:, 5:].cpu().numpy(), oracle.maxpool(full, 2, 2, 1)[0])
+    same(wide_full[:, 4:].cpu().numpy(), full)
+    assert (wide[:, :5] == 9.0).all() and (wide_full[:, :4] == 7.0).all()
 
 
 @pytest.mark.parametrize("shape", [(2, 8, 20, 20), (1, 3, 13, 13), (2, 2, 19, 19), (1, 2, 5, 40)])
