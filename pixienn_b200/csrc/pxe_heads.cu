@@ -593,6 +593,10 @@ centernet_peaks_kernel(const CnParams p)
 constexpr int kCnTopkThreads = 1024;
 constexpr int kCnStageKeys = 4096;     // candidates per image sorted in shared memory (32 KB)
 constexpr int kCnMaxSlots = 2048;      // slots per image whose prefix sums fit shared memory
+constexpr int kCnBinShift = 51;        // a key's leading 13 bits (sign, exponent, 4 mantissa bits of the score) ...
+constexpr int kCnBins = 1 << 13;       // ... index a histogram that aliases the staging area
+static_assert(kCnBins * sizeof(int) <= kCnStageKeys * sizeof(unsigned long long), "histogram must fit the staging area");
+static_assert(kCnBins == 8 * kCnTopkThreads, "the top-down scan gives every thread 8 bins");
 
 __global__ void __launch_bounds__(kCnTopkThreads)
 centernet_topk_kernel(const CnParams p)
@@ -635,79 +639,166 @@ centernet_topk_kernel(const CnParams p)
     }
     const int n_total = carry;
 
-    // 2. validity + compaction
-    const bool staged = n_total <= kCnStageKeys;
-    unsigned long long* list = staged ? stage : p.list + (long long)b * p.slots * p.slot_cap;
-    for (int i = threadIdx.x; i < n_total; i += kCnTopkThreads) {
-        int lo = 0, hi = p.slots;                    // largest s with prefix[s] <= i
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (prefix[mid] <= i) lo = mid; else hi = mid;
-        }
-        const unsigned long long key = cand[(long long)lo * p.slot_cap + (i - prefix[lo])];
-        const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
-        const uint32_t cls = flat / (uint32_t)area;
-        if (cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) list[atomicAdd(&n_valid, 1)] = key;
-    }
-    __syncthreads();
-    const int n = n_valid;
-
-    // 3. order the best K
+    // 2. Short cut.  Far more cells pass the peak test than an image keeps (thousands against K), and the
+    // size / offset validity check costs four scattered reads per candidate.  So first find, from a histogram
+    // of the keys' leading 13 bits, the bin holding the K-th best candidate; only candidates in that bin or
+    // above (at least K, usually a few hundred) are staged and checked.  If K or more of them are valid, the K
+    // best valid candidates of the image are among them, because every candidate left out has a smaller key.
+    // Otherwise (many invalid boxes, or one bin holding thousands of equal scores) the full path below runs.
     unsigned long long* sorted = stage;
-    int m;
-    if (staged) {
-        int pow2 = 1;
-        while (pow2 < n) pow2 <<= 1;
-        for (int i = n + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+    int m = 0;
+    bool done = false;
+    {
+        int* bins = reinterpret_cast<int*>(stage);                 // kCnBins ints alias the staging area
+        for (int i = threadIdx.x; i < kCnBins; i += kCnTopkThreads) bins[i] = 0;
         __syncthreads();
-        block_bitonic_desc(stage, pow2);
-        m = n < p.K ? n : p.K;
-    } else {
-        // The list is in global memory.  Two radix passes fix the leading 16 bits of the K-th key; keys above
-        // them are certain winners, keys sharing them are the only ones still undecided.  With scores spread
-        // over the second byte that is a few hundred keys, which are sorted in shared memory.  If the
-        // undecided set does not fit (e.g. a constant heatmap), the full 8-pass selection decides.
-        int m_sort = 0;
-        if (n > p.K) {
-            int want = 0;
-            const unsigned long long lead = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel, 2, &want) >> 48;
-            const int winners = p.K - want;
-            if (threadIdx.x == 0) { n_best = 0; n_valid = 0; }      // n_valid is reused as the tie counter
-            __syncthreads();
-            for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
-                const unsigned long long key = list[i];
-                const unsigned long long top = key >> 48;
-                if (top > lead) stage[atomicAdd(&n_best, 1)] = key;
-                else if (top == lead) {
-                    const int at = atomicAdd(&n_valid, 1);
-                    if (winners + at < kCnStageKeys) stage[winners + at] = key;
+        for (int s0 = 0; s0 < p.slots; s0 += 32) {
+            const int sidx = s0 + warp;
+            if (sidx >= p.slots) continue;
+            const int c = prefix[sidx + 1] - prefix[sidx];
+            const unsigned long long* src = cand + (long long)sidx * p.slot_cap;
+#pragma unroll 8
+            for (int j = lane; j < c; j += 32) atomicAdd(&bins[(int)(src[j] >> kCnBinShift)], 1);
+        }
+        __syncthreads();
+        // thread t owns the 8 bins below kCnBins - 8t, scanned from the top
+        const int top = kCnBins - 1 - 8 * (int)threadIdx.x;
+        int mine = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mine += bins[top - j];
+        int inc = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        if (threadIdx.x == 0) sel[0] = 0ULL;                       // lead bin 0 = "take everything"
+        __syncthreads();
+        int before = inc - mine;
+        for (int i = 0; i < warp; ++i) before += warp_tot[i];
+        if (before < p.K && before + mine >= p.K) {
+            int acc = before, bin = top;
+            for (int j = 0; j < 8; ++j) {
+                if (acc + bins[top - j] >= p.K) { bin = top - j; break; }
+                acc += bins[top - j];
+            }
+            sel[0] = (unsigned long long)bin;
+        }
+        __syncthreads();
+        const int lead = (int)sel[0];
+        __syncthreads();                                           // bins are dead from here: stage is reused
+        for (int s0 = 0; s0 < p.slots; s0 += 32) {
+            const int sidx = s0 + warp;
+            if (sidx >= p.slots) continue;
+            const int c = prefix[sidx + 1] - prefix[sidx];
+            const unsigned long long* src = cand + (long long)sidx * p.slot_cap;
+#pragma unroll 8
+            for (int j = lane; j < c; j += 32) {
+                const unsigned long long key = src[j];
+                if ((int)(key >> kCnBinShift) >= lead) {
+                    const int at = atomicAdd(&n_best, 1);
+                    if (at < kCnStageKeys) stage[at] = key;
                 }
             }
+        }
+        __syncthreads();
+        const int n_c = n_best;
+        if (n_c <= kCnStageKeys) {
+            for (int i = threadIdx.x; i < n_c; i += kCnTopkThreads) {
+                const uint32_t flat = 0xffffffffu - (uint32_t)(stage[i] & 0xffffffffu);
+                const uint32_t cls = flat / (uint32_t)area;
+                if (cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) atomicAdd(&n_valid, 1);
+                else stage[i] = 0ULL;                              // sorts behind every real key
+            }
             __syncthreads();
-            if (winners + n_valid <= kCnStageKeys) {
-                m_sort = winners + n_valid;
-            } else {
-                const unsigned long long kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
-                if (threadIdx.x == 0) n_best = 0;
+            if (n_valid >= p.K || n_c == n_total) {
+                int pow2 = 1;
+                while (pow2 < n_c) pow2 <<= 1;
+                for (int i = n_c + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+                __syncthreads();
+                block_bitonic_desc(stage, pow2);
+                m = n_valid < p.K ? n_valid : p.K;
+                done = true;
+            }
+        }
+        __syncthreads();
+    }
+
+    if (!done) {
+        if (threadIdx.x == 0) { n_valid = 0; n_best = 0; }
+        __syncthreads();
+        // 2. validity + compaction
+        const bool staged = n_total <= kCnStageKeys;
+        unsigned long long* list = staged ? stage : p.list + (long long)b * p.slots * p.slot_cap;
+        for (int i = threadIdx.x; i < n_total; i += kCnTopkThreads) {
+            int lo = 0, hi = p.slots;                    // largest s with prefix[s] <= i
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (prefix[mid] <= i) lo = mid; else hi = mid;
+            }
+            const unsigned long long key = cand[(long long)lo * p.slot_cap + (i - prefix[lo])];
+            const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
+            const uint32_t cls = flat / (uint32_t)area;
+            if (cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) list[atomicAdd(&n_valid, 1)] = key;
+        }
+        __syncthreads();
+        const int n = n_valid;
+
+        // 3. order the best K
+        if (staged) {
+            int pow2 = 1;
+            while (pow2 < n) pow2 <<= 1;
+            for (int i = n + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+            __syncthreads();
+            block_bitonic_desc(stage, pow2);
+            m = n < p.K ? n : p.K;
+        } else {
+            // The list is in global memory.  Two radix passes fix the leading 16 bits of the K-th key; keys above
+            // them are certain winners, keys sharing them are the only ones still undecided.  With scores spread
+            // over the second byte that is a few hundred keys, which are sorted in shared memory.  If the
+            // undecided set does not fit (e.g. a constant heatmap), the full 8-pass selection decides.
+            int m_sort = 0;
+            if (n > p.K) {
+                int want = 0;
+                const unsigned long long lead = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel, 2, &want) >> 48;
+                const int winners = p.K - want;
+                if (threadIdx.x == 0) { n_best = 0; n_valid = 0; }      // n_valid is reused as the tie counter
                 __syncthreads();
                 for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
                     const unsigned long long key = list[i];
-                    if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
+                    const unsigned long long top = key >> 48;
+                    if (top > lead) stage[atomicAdd(&n_best, 1)] = key;
+                    else if (top == lead) {
+                        const int at = atomicAdd(&n_valid, 1);
+                        if (winners + at < kCnStageKeys) stage[winners + at] = key;
+                    }
                 }
                 __syncthreads();
-                m_sort = n_best;
+                if (winners + n_valid <= kCnStageKeys) {
+                    m_sort = winners + n_valid;
+                } else {
+                    const unsigned long long kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
+                    if (threadIdx.x == 0) n_best = 0;
+                    __syncthreads();
+                    for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
+                        const unsigned long long key = list[i];
+                        if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
+                    }
+                    __syncthreads();
+                    m_sort = n_best;
+                }
+            } else {
+                for (int i = threadIdx.x; i < n; i += kCnTopkThreads) stage[i] = list[i];
+                m_sort = n;
             }
-        } else {
-            for (int i = threadIdx.x; i < n; i += kCnTopkThreads) stage[i] = list[i];
-            m_sort = n;
+            __syncthreads();
+            int pow2 = 1;
+            while (pow2 < m_sort) pow2 <<= 1;
+            for (int i = m_sort + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+            __syncthreads();
+            block_bitonic_desc(stage, pow2);
+            m = m_sort < p.K ? m_sort : p.K;
         }
-        __syncthreads();
-        int pow2 = 1;
-        while (pow2 < m_sort) pow2 <<= 1;
-        for (int i = m_sort + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
-        __syncthreads();
-        block_bitonic_desc(stage, pow2);
-        m = m_sort < p.K ? m_sort : p.K;
     }
     const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
     const float image_h = p.d.image_height > 0 ? (float)p.d.image_height : 1.0f;
