@@ -312,6 +312,28 @@ class Runner:
         self.head_marks.append(self.dets.count.clone())
         T[st.layer] = act
 
+    # ------------------------------------------------------------------ CUDA graph
+    def capture(self, x: torch.Tensor) -> "torch.cuda.CUDAGraph":
+        """Captures one forward pass on ``x`` (a device tensor that stays allocated: later replays read whatever
+        it holds then) into a CUDA graph and returns it.  At small batches a forward is a few hundred launches of
+        a few microseconds each and the host cannot issue them fast enough; a replay issues them all at once.
+        The pass must have run at least once before (cuDNN picks its algorithms on first use).  The detection
+        buffer, head marks and CenterNet outputs that the captured pass wrote are the ones later replays
+        write; read them with the usual accessors after a replay."""
+        enabled, self.timer.enabled = self.timer.enabled, False
+        try:
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.forward(x)                      # allocations of the pass settle in the caching allocator
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.forward(x)
+        finally:
+            self.timer.enabled = enabled
+        return g
+
     # ------------------------------------------------------------------ results
     def detections(self):
         """Detections of the last forward in the reference's order (Model::detections):
@@ -357,7 +379,7 @@ class PipelinedPredictor:
     until two more batches have been submitted.
     """
 
-    def __init__(self, runner: Runner, batch_shape, pinned_capacity: Optional[int] = None):
+    def __init__(self, runner: Runner, batch_shape, pinned_capacity: Optional[int] = None, use_graphs: bool = False):
         self.r = runner
         dev = runner.device
         self.compute = torch.cuda.current_stream(dev)
@@ -372,6 +394,15 @@ class PipelinedPredictor:
         self.out_done = [None, None]      # event: detections of this slot are on the host
         self.pending = None               # (slot, event after forward)
         self.n = 0
+        # one CUDA graph per slot (its input buffer and its detection buffer are baked into the graph)
+        self.graphs = None
+        if use_graphs:
+            self.graphs = []
+            for slot in range(2):
+                runner.dets = self.bufs[slot]
+                self.x[slot].zero_()
+                self.graphs.append(runner.capture(self.x[slot]))
+            runner.dets = self.bufs[0]
 
     def _stage(self, host_batch, slot):
         with torch.cuda.stream(self.h2d):
@@ -413,7 +444,10 @@ class PipelinedPredictor:
         if self.out_done[slot] is not None:
             self.compute.wait_event(self.out_done[slot])  # this slot's previous detections have left the device
         self.r.dets = self.bufs[slot]
-        self.r.forward(self.x[slot])
+        if self.graphs is not None:
+            self.graphs[slot].replay()
+        else:
+            self.r.forward(self.x[slot])
         done = torch.cuda.Event()
         done.record(self.compute)
         self.x_free[slot] = done

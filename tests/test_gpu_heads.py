@@ -219,6 +219,56 @@ def test_centernet_ties_plateaus_and_invalid_sizes(cuda, oracle):
     assert got["source"].tolist() == list(range(100))
 
 
+@pytest.mark.parametrize("kind", ["noise", "wide", "quantised", "saturated"])
+@pytest.mark.parametrize("shape", [(2, 3, 40, 128), (1, 2, 33, 262), (2, 2, 19, 37)])
+def test_centernet_logit_decode_equals_decode_of_device_scores(cuda, kind, shape):
+    """Decoding straight from logits (peak tests done in pre-activation space wherever that is safe)
+    must keep exactly the cells, scores and order that decoding the device's own sigmoid output keeps:
+    near-ties, plateaus and saturated sigmoids (logits of 20 and 30 both score 1.0f) included."""
+    B, classes, H, W = shape
+    rng = np.random.default_rng(77)
+    if kind == "noise":
+        heat = rng.normal(-4.0, 2.0, (B, classes, H, W))
+    elif kind == "wide":
+        heat = rng.normal(0.0, 30.0, (B, classes, H, W))
+    elif kind == "quantised":
+        heat = np.round(rng.normal(-1.0, 2.0, (B, classes, H, W)) * 2) / 2
+    else:
+        heat = rng.choice(np.array([-120.0, -95.0, -3.0, 0.0, 6.0, 17.0, 20.0, 30.0, 95.0]), (B, classes, H, W))
+    heat = heat.astype(np.float32)
+    heat[0, 0, 0, 0] = np.nan
+    heat[0, 0, H - 1, W - 1] = np.inf
+    heat[0, 0, 1, 1] = -np.inf
+    size = synth.uniform(78, "lsz", (B, 2, H, W))
+    off = synth.uniform(78, "lof", (B, 2, H, W))
+    hd, sd, od = dev(heat, cuda), dev(size, cuda), dev(off, cuda)
+    for thr, K in ((0.2, 100), (0.0, 300), (0.9, 1024)):
+        d1, c1 = ops.centernet_decode(hd, sd, od, thr, K, logits=True, heatmap_bias=0.25)
+        scores = ops.centernet_activate(torch.cat([hd, sd, od], 1), classes, 0.25)[:, :classes].contiguous()
+        d2, c2 = ops.centernet_decode(scores, sd, od, thr, K)
+        g1, g2 = ops.centernet_to_host(d1, c1), ops.centernet_to_host(d2, c2)
+        for b in range(B):
+            assert len(g1[b]) == len(g2[b])
+            assert np.array_equal(g1[b]["source"], g2[b]["source"])
+            assert np.array_equal(g1[b]["prob"].view(np.uint32), g2[b]["prob"].view(np.uint32))
+
+
+def test_centernet_crowded_tiles_are_reduced_per_tile(cuda, oracle):
+    """Checkerboard-like maps put far more peaks into one tile than its slot stores."""
+    B, classes, H, W, K = 2, 2, 48, 256, 100
+    rng = np.random.default_rng(5)
+    heat = rng.random((B, classes, H, W)).astype(np.float32) * 0.5 + 0.3
+    heat[:, :, ::2, ::2] += 0.2                      # every other cell in both directions is a local maximum
+    size = synth.uniform(79, "osz", (B, 2, H, W))
+    off = synth.uniform(79, "oof", (B, 2, H, W))
+    ref, ncand = oracle.centernet_decode(heat, size, off, 0.2, K)
+    d, c = ops.centernet_decode(dev(heat, cuda), dev(size, cuda), dev(off, cuda), 0.2, K)
+    got = ops.centernet_to_host(d, c)
+    for b in range(B):
+        assert len(got[b]) == len(ref[b]) == K
+        dets_equal(got[b], ref[b])
+
+
 @pytest.mark.parametrize("shape,groups,temp", [((4, 1000, 1, 1), 1, 1.0), ((2, 30, 1, 1), 3, 0.7), ((3, 5, 2, 2), 1, 2.0),
                                                ((1, 3000, 1, 1), 1, 1.0)])
 def test_softmax(cuda, oracle, shape, groups, temp):

@@ -124,15 +124,17 @@ def test_batch_sharding_gives_identical_detections(cuda):
     assert merged.tobytes() == whole.tobytes()
 
 
-def test_pipelined_predictor_equals_sequential_predict(cuda):
-    """Overlapping the copies of neighbouring batches with compute changes no record."""
+@pytest.mark.parametrize("use_graphs", [False, True])
+def test_pipelined_predictor_equals_sequential_predict(cuda, use_graphs):
+    """Overlapping the copies of neighbouring batches with compute changes no record; neither does
+    replaying the forward pass as a CUDA graph (one graph per buffer slot)."""
     from pixienn_b200.runner import PipelinedPredictor
     model = graph.parse_model(presets.yolov3_tiny(160, 160))
     weights = synth_weights(model, 9, head_bias=-3.0)
     batches = [torch.from_numpy(make_input(20 + i, 2, model)).pin_memory() for i in range(4)]
     seq = Runner(model, weights, 2, cuda)
     want = [seq.predict(b)[0].copy() for b in batches]
-    pipe = PipelinedPredictor(Runner(model, weights, 2, cuda), tuple(batches[0].shape))
+    pipe = PipelinedPredictor(Runner(model, weights, 2, cuda), tuple(batches[0].shape), use_graphs=use_graphs)
     got = []
     for b in batches:
         r = pipe.submit(b)
@@ -142,3 +144,26 @@ def test_pipelined_predictor_equals_sequential_predict(cuda):
     assert len(got) == len(want) == 4
     for g, w in zip(got, want):
         assert len(w) > 0 and g.tobytes() == w.tobytes()
+
+
+@pytest.mark.parametrize("name", ["yolov3_tiny", "centernet_tiny"])
+def test_cuda_graph_replay_equals_eager_forward(cuda, name):
+    """Runner.capture: replays read the captured input tensor's current contents and rewrite the same
+    detection buffers; records and per-head marks equal an eager pass on the same input."""
+    builder = getattr(presets, name)
+    model = graph.parse_model(builder(128, 128))
+    weights = synth_weights(model, 11, head_bias=-3.0 if name == "yolov3_tiny" else 0.0)
+    eager = Runner(model, weights, 2, cuda)
+    captured = Runner(model, weights, 2, cuda)
+    x = dev(make_input(30, 2, model), cuda)
+    captured.forward(x)
+    g = captured.capture(x)
+    for seed in (31, 32):
+        xin = dev(make_input(seed, 2, model), cuda)
+        x.copy_(xin)
+        g.replay()
+        eager.forward(xin)
+        want, wt = eager.detections()
+        got, gt = captured.detections()
+        assert wt == gt and len(want) > 0 and got.tobytes() == want.tobytes()
+        assert [h.tobytes() for h in captured.detections_by_head()] == [h.tobytes() for h in eager.detections_by_head()]
