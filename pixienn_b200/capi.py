@@ -73,6 +73,35 @@ class CenterNetDecodeDesc(C.Structure):
     ]
 
 
+PLAN_MAX_SOURCES, PLAN_MAX_DESTS, PLAN_MAX_SPP = 16, 8, 4
+
+
+class LayerDesc(C.Structure):
+    """pxe_layer_desc of include/pxe_plan.h."""
+    _fields_ = [("type", C.c_int), ("out_channels", C.c_int), ("out_height", C.c_int), ("out_width", C.c_int),
+                ("kernel", C.c_int), ("stride", C.c_int), ("padding", C.c_int), ("batch_norm", C.c_int),
+                ("activation", C.c_int), ("n_sources", C.c_int), ("sources", C.c_int * PLAN_MAX_SOURCES)]
+
+
+class PlanDest(C.Structure):
+    _fields_ = [("kind", C.c_int), ("route", C.c_int), ("channel_offset", C.c_int)]
+
+
+class PlanStep(C.Structure):
+    """pxe_step of include/pxe_plan.h."""
+    _fields_ = [("op", C.c_int), ("layer", C.c_int), ("n_inputs", C.c_int), ("inputs", C.c_int * 2),
+                ("n_dests", C.c_int), ("dests", PlanDest * PLAN_MAX_DESTS),
+                ("fused_shortcut", C.c_int), ("fused_pool", C.c_int), ("keep_full", C.c_int),
+                ("n_pool_dests", C.c_int), ("pool_dests", PlanDest * PLAN_MAX_DESTS), ("head_raw", C.c_int),
+                ("n_spp", C.c_int), ("spp_layers", C.c_int * PLAN_MAX_SPP), ("n_spp_dests", C.c_int * PLAN_MAX_SPP),
+                ("spp_dests", (PlanDest * PLAN_MAX_DESTS) * PLAN_MAX_SPP)]
+
+
+class PlanStats(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("fused_shortcut", "fused_pool", "routes_eliminated", "routes_aliased",
+                                       "spp_blocks", "raw_heads", "concat_copies")]
+
+
 # name -> (restype, argtypes); every name here must be declared in include/pxe.h
 _vp, _ll, _i, _f, _sz = C.c_void_p, C.c_longlong, C.c_int, C.c_float, C.c_size_t
 PROTOTYPES = {
@@ -101,6 +130,18 @@ PROTOTYPES = {
     "pxe_nms_host": (_ll, [_vp, _ll, _f, _vp]),
 }
 
+# the planner of include/pxe_plan.h (host code)
+PLAN_PROTOTYPES = {
+    "pxe_plan_build": (_i, [C.POINTER(LayerDesc), _i, _i, _i, C.POINTER(_vp)]),
+    "pxe_plan_destroy": (None, [_vp]),
+    "pxe_plan_step_count": (_i, [_vp]),
+    "pxe_plan_step": (C.POINTER(PlanStep), [_vp, _i]),
+    "pxe_plan_alias": (_i, [_vp, _i]),
+    "pxe_plan_concat_channels": (_i, [_vp, _i]),
+    "pxe_plan_last_use": (_i, [_vp, _i]),
+    "pxe_plan_get_stats": (None, [_vp, C.POINTER(PlanStats)]),
+}
+
 # mangled names of the link-compatible tier (include/pxe_compat.hpp)
 COMPAT_SYMBOLS = [
     "_ZN2px8activateE14ActivationTypePfm",
@@ -126,7 +167,7 @@ def lib() -> C.CDLL:
                 f"{LIB_PATH} is missing: build it with `python -m pixienn_b200._build` "
                 "(needs nvcc); there is no fallback implementation")
         L = C.CDLL(LIB_PATH)
-        for name, (res, args) in PROTOTYPES.items():
+        for name, (res, args) in list(PROTOTYPES.items()) + list(PLAN_PROTOTYPES.items()):
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args

@@ -359,3 +359,74 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
         for t in st.inputs:
             last_use[t] = si
     return Plan(model, steps, alias, concat_channels, last_use, stats)
+
+
+# ------------------------------------------------------------------------- the library's planner
+_LAYER_TYPE = {"conv": 0, "maxpool": 1, "upsample": 2, "route": 3, "shortcut": 4, "yolo": 5, "centernet": 6,
+               "region": 7, "softmax": 8, "avgpool": 9, "dropout": 10, "connected": 11, "conn": 11}
+_STEP_OP = {0: "conv", 1: "alias", 2: "maxpool", 3: "spp", 4: "upsample", 5: "shortcut", 6: "concat"}
+
+
+def layer_descs(model: Model):
+    """The model as the array of ``pxe_layer_desc`` records that ``pxe_plan_build`` takes
+    (include/pxe_plan.h): what a C++ caller fills from its own layer objects."""
+    from . import capi
+    arr = (capi.LayerDesc * len(model.layers))()
+    for l, d in zip(model.layers, arr):
+        d.type = _LAYER_TYPE[l.type]
+        d.out_channels, d.out_height, d.out_width = l.out_shape
+        d.kernel, d.stride, d.padding = l.kernel, l.stride, l.padding
+        d.batch_norm = int(l.batch_norm)
+        d.activation = capi.ACT.get(l.activation, capi.ACT["linear"])
+        if len(l.sources) > capi.PLAN_MAX_SOURCES:
+            raise ValueError(f"layer {l.index}: {len(l.sources)} sources exceed {capi.PLAN_MAX_SOURCES}")
+        d.n_sources = len(l.sources)
+        for k, s in enumerate(l.sources):
+            d.sources[k] = s
+    return arr
+
+
+def plan_native(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
+    """The same plan as :func:`plan`, built by the library's C++ planner (``pxe_plan_build``) and
+    converted to the Python records the runner walks."""
+    import ctypes as C
+    from . import capi
+    L = capi.lib()
+    descs = layer_descs(model)
+    handle = C.c_void_p()
+    capi.check(L.pxe_plan_build(descs, len(model.layers), int(fuse), int(raw_heads), C.byref(handle)))
+    try:
+        def dests(arr, n):
+            return [Dest("slot", arr[k].route, arr[k].channel_offset) if arr[k].kind else Dest("dense") for k in range(n)]
+
+        steps: List[Step] = []
+        for si in range(L.pxe_plan_step_count(handle)):
+            s = L.pxe_plan_step(handle, si).contents
+            layer = model.layers[s.layer]
+            op = _STEP_OP.get(s.op) or ("connected" if layer.type == "conn" else layer.type)
+            st = Step(op, s.layer, [s.inputs[k] for k in range(s.n_inputs)], dests(s.dests, s.n_dests))
+            if op == "concat":
+                st.inputs = list(layer.sources)
+            st.fused_shortcut = s.fused_shortcut if s.fused_shortcut >= 0 else None
+            st.fused_pool = s.fused_pool if s.fused_pool >= 0 else None
+            st.keep_full = bool(s.keep_full)
+            st.pool_dests = dests(s.pool_dests, s.n_pool_dests)
+            st.head_raw = bool(s.head_raw)
+            st.spp_layers = [s.spp_layers[g] for g in range(s.n_spp)]
+            st.spp_dests = [dests(s.spp_dests[g], s.n_spp_dests[g]) for g in range(s.n_spp)]
+            if st.spp_layers:
+                st.produces = list(st.spp_layers)
+            elif st.fused_shortcut is not None:
+                st.produces = [st.fused_shortcut]
+            else:
+                st.produces = [s.layer] + ([st.fused_pool] if st.fused_pool is not None else [])
+            steps.append(st)
+        n = len(model.layers)
+        alias = {i: L.pxe_plan_alias(handle, i) for i in range(n) if L.pxe_plan_alias(handle, i) >= 0}
+        concat = {i: L.pxe_plan_concat_channels(handle, i) for i in range(n) if L.pxe_plan_concat_channels(handle, i) > 0}
+        last_use = {i: L.pxe_plan_last_use(handle, i) for i in range(-1, n) if L.pxe_plan_last_use(handle, i) >= 0}
+        stats = capi.PlanStats()
+        L.pxe_plan_get_stats(handle, C.byref(stats))
+        return Plan(model, steps, alias, concat, last_use, {name: getattr(stats, name) for name, _ in stats._fields_})
+    finally:
+        L.pxe_plan_destroy(handle)

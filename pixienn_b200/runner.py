@@ -86,7 +86,7 @@ class Runner:
                  threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0):
         self.model, self.batch, self.device = model, batch, device
         self.eps_mode = eps_mode        # 0: cuDNN form sqrt(var+eps) (the CUDA path), 1: the CPU path's sqrt(var)+eps
-        self.plan = graph.plan(model, fuse=fuse, raw_heads=raw_heads)
+        self.plan = graph.plan_native(model, fuse=fuse, raw_heads=raw_heads)   # the library's C++ planner (pxe_plan.h)
         self.threshold = threshold
         self.batch_id_offset = batch_id_offset
         self.w: Dict[int, Dict[str, torch.Tensor]] = {

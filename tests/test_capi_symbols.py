@@ -7,8 +7,8 @@ from pixienn_b200 import capi
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_in_header():
-    text = open(os.path.join(ROOT, "include", "pxe.h")).read()
+def declared_in_header(name="pxe.h"):
+    text = open(os.path.join(ROOT, "include", name)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"PXE_API\s+[\w\s\*]+?\b(pxe_\w+)\s*\(", text)))
 
@@ -21,6 +21,15 @@ def test_every_declared_symbol_is_exported_and_bound():
         assert hasattr(L, n), f"{n} declared in pxe.h but not exported by libpxe.so"
         assert n in capi.PROTOTYPES, f"{n} has no ctypes prototype"
     assert sorted(capi.PROTOTYPES) == names, "ctypes prototypes and header declarations differ"
+
+
+def test_planner_symbols_exported_and_bound():
+    names = declared_in_header("pxe_plan.h")
+    assert len(names) == 8
+    L = capi.lib()
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in pxe_plan.h but not exported by libpxe.so"
+    assert sorted(capi.PLAN_PROTOTYPES) == names
 
 
 def test_compat_tier_symbols_exported():
