@@ -310,12 +310,42 @@ PXE_API int pxe_softmax(pxe_stream_t stream, const float* in, float* out, int ba
 PXE_API int pxe_region_forward(pxe_stream_t stream, const float* in, float* out, int batch, int width,
                                int height, int num, int coords, int classes, int softmax);
 
+/* Global average pooling (AvgPoolLayer::forward, include/AvgPoolLayer.h:66-87; cudnnPoolingForward with an
+ * H x W average window on the CUDA path, include/cuda/AvgPoolLayer.h:66-75): y[b][c] = mean of plane (b, c).
+ * x: [batch, channels, height, width] with batch stride (0 = dense); y: [batch, channels] likewise. */
+PXE_API int pxe_avgpool(pxe_stream_t stream, const float* x, long long x_batch_stride, float* y,
+                        long long y_batch_stride, int batch, int channels, int height, int width);
+
+/* YOLOv1 detection head decode (DetectLayer::addDetects, include/DetectLayer.h:166-209; the CUDA layer copies
+ * the whole head to the host first, include/cuda/DetectLayer.h).  `pred`: per image
+ * [side*side*classes class scores][side*side*num object scales][side*side*num*coords boxes], the layer's
+ * input as the connected layer before it leaves it.  A box is emitted when its scale is finite and positive
+ * and scale * (best class score of its cell) >= threshold; its record carries that class and probability;
+ * squared != 0 squares the predicted width / height (the layer's `sqrt` option).  Records are appended to
+ * `dets` behind *count (device) in the reference's order (image, cell, box); *count advances past every
+ * emitted box even when capacity is exceeded.  width / height: the scale of the boxes (1, 1 = normalised). */
+PXE_API int pxe_detect_decode(pxe_stream_t stream, const float* pred, long long pred_batch_stride, int batch,
+                              int side, int num, int classes, int coords, int squared, float width, float height,
+                              float threshold, pxe_detection* dets, long long capacity, long long* count,
+                              int batch_id_offset);
+
 /* ------------------------------------------------------------------------------------------
  * Post-processing on the host: px::nms (src/Box.cpp:56-145), same ordering, same 0.9 IoU
  * cross-class duplicate rule, same 1024-candidate cap per (image, class) group.
  * `out` must have room for n records; returns the number kept (or a negative pxe_status).
  * ------------------------------------------------------------------------------------------ */
 PXE_API long long pxe_nms_host(const pxe_detection* dets, long long n, float threshold, pxe_detection* out);
+
+/* The same post-processing on the device: `dets` and `out` are device buffers of n records (out has room for
+ * n), *out_count (device) receives the number kept; the kept records are those pxe_nms_host keeps, in the
+ * same order, bit for bit.  Nothing is copied to the host and nothing synchronises: the O(N^2) passes of
+ * src/Box.cpp:68-139 run as one block per image / per (image, class) group.  n is the host's copy of the
+ * record count (the decodes leave it on the device; the caller reads it to size its own buffers anyway).
+ * `workspace`: pxe_nms_workspace_bytes(n) bytes, 256-byte aligned.  Records with NaN probabilities have no
+ * defined order in the reference (its comparator is `a.prob > b.prob`); here they sort first. */
+PXE_API size_t pxe_nms_workspace_bytes(long long n);
+PXE_API int pxe_nms(pxe_stream_t stream, const pxe_detection* dets, long long n, float threshold,
+                    pxe_detection* out, long long* out_count, void* workspace, size_t workspace_bytes);
 
 #ifdef __cplusplus
 }

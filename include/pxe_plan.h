@@ -44,7 +44,8 @@ enum {
     PXE_LAYER_SOFTMAX = 8,
     PXE_LAYER_AVGPOOL = 9,
     PXE_LAYER_DROPOUT = 10,
-    PXE_LAYER_CONNECTED = 11
+    PXE_LAYER_CONNECTED = 11,
+    PXE_LAYER_DETECTION = 12      /* the YOLOv1 head, `type: detection` */
 };
 
 /* step operations */
@@ -56,7 +57,7 @@ enum {
     PXE_STEP_UPSAMPLE = 4,   /* pxe_upsample */
     PXE_STEP_SHORTCUT = 5,   /* pxe_shortcut (a shortcut that could not be folded into a conv) */
     PXE_STEP_CONCAT = 6,     /* pxe_concat (unfused plans only) */
-    PXE_STEP_HEAD = 7        /* yolo / centernet / region / softmax / avgpool / dropout / connected: see layer type */
+    PXE_STEP_HEAD = 7        /* yolo / centernet / region / softmax / avgpool / dropout / connected / detection: see layer type */
 };
 
 typedef struct pxe_layer_desc {

@@ -333,6 +333,60 @@ PXO_API void pxo_yolo_decode_image(const float* pred, int b, int masks, const in
 }
 
 /* ------------------------------------------------------------------ */
+/* YOLOv1 detection head: DetectLayer::addDetects for one image,       */
+/* include/DetectLayer.h:166-209.  predictions = that image's values:  */
+/* [locations*classes scores][locations*num scales][locations*num*coords boxes]. */
+/* ------------------------------------------------------------------ */
+PXO_API void pxo_detect_decode_image(const float* predictions, int b, int side, int num, int classes,
+                                     int coords, int squared, int width, int height, float thr,
+                                     pxo_detection* dets, long long cap, long long* count)
+{
+    const int locations = side * side;
+    for (int i = 0; i < locations; ++i) {
+        int row = i / side, col = i % side;
+        for (int n = 0; n < num; ++n) {
+            int pindex = locations * classes + i * num + n;
+            float scale = predictions[pindex];
+            if (!isfinite(scale) || scale <= 0.0f) continue;
+            int bindex = locations * (classes + num) + (i * num + n) * coords;
+            float x = (predictions[bindex + 0] + col) / side * width;
+            float y = (predictions[bindex + 1] + row) / side * height;
+            float w = powf(predictions[bindex + 2], squared ? 2.0f : 1.0f) * width;
+            float h = powf(predictions[bindex + 3], squared ? 2.0f : 1.0f) * height;
+            int max_class = 0;
+            float max_prob = -FLT_MAX;
+            for (int j = 0; j < classes; ++j) {
+                float prob = scale * predictions[i * classes + j];
+                if (prob > max_prob) { max_class = j; max_prob = prob; }
+            }
+            if (max_prob >= thr) {
+                if (*count < cap) {
+                    pxo_detection* d = dets + *count;
+                    d->x = w > 0.0f ? x - w / 2.0f : x;    /* DarkBox::left,  DarkBox.cpp:84-91 */
+                    d->y = h > 0.0f ? y - h / 2.0f : y;    /* DarkBox::top,   DarkBox.cpp:102-109 */
+                    d->w = w; d->h = h; d->prob = max_prob;
+                    d->class_id = max_class; d->batch_id = b; d->source = i * num + n;
+                }
+                ++*count;
+            }
+        }
+    }
+}
+
+/* AvgPoolLayer::forward, include/AvgPoolLayer.h:66-87: running float sum in index order, then one division. */
+PXO_API void pxo_avgpool(const float* in, float* out, int batch, int channels, int area)
+{
+    if (area < 1) area = 1;
+    for (int b = 0; b < batch; ++b)
+        for (int k = 0; k < channels; ++k) {
+            int oi = k + b * channels;
+            out[oi] = 0.0f;
+            for (int i = 0; i < area; ++i) out[oi] += in[i + (size_t)area * (k + (size_t)b * channels)];
+            out[oi] /= area;
+        }
+}
+
+/* ------------------------------------------------------------------ */
 /* CenterNet head: include/CenterNetLayer.h:85-110, 181-247            */
 /* ------------------------------------------------------------------ */
 PXO_API void pxo_centernet_activate(const float* in, float* out, int batch, int classes,

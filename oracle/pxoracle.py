@@ -83,6 +83,8 @@ def lib():
         L.pxo_yolo_decode_image.argtypes = [_f, C.c_int, C.c_int, _i, _i] + [C.c_int] * 7 + [
             C.c_float, C.c_void_p, C.c_longlong, C.POINTER(C.c_longlong)]
         L.pxo_centernet_activate.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.pxo_detect_decode_image.argtypes = [_f] + [C.c_int] * 8 + [C.c_float, C.c_void_p, C.c_longlong, C.POINTER(C.c_longlong)]
+        L.pxo_avgpool.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.pxo_centernet_decode_image.restype = C.c_int
         L.pxo_centernet_decode_image.argtypes = [_f, _f, _f] + [C.c_int] * 6 + [
             C.c_float, C.c_int, C.c_void_p, _i]
@@ -212,6 +214,31 @@ def yolo_decode(pred, mask, anchors, classes, net_w, net_h, thr, img_w=0, img_h=
                                     net_w, net_h, img_w, img_h, C.c_float(thr),
                                     dets.ctypes.data, cap, C.byref(count))
     return dets[:min(count.value, cap)].copy(), count.value
+
+
+def detect_decode(pred, side, num, classes, thr, coords=4, squared=False, width=1, height=1, cap=None):
+    """YOLOv1 detection head: pred [B, side*side*(classes + num*(1+coords))] -> (detections, count)."""
+    pred = _c(pred)
+    B = pred.shape[0]
+    per = pred.size // B
+    if cap is None:
+        cap = B * side * side * num
+    dets = np.zeros(cap, DET_DTYPE)
+    count = C.c_longlong(0)
+    flat = pred.reshape(B, per)
+    for b in range(B):
+        row = np.ascontiguousarray(flat[b])
+        lib().pxo_detect_decode_image(_fp(row), b, side, num, classes, coords, int(squared), int(width), int(height),
+                                      C.c_float(thr), dets.ctypes.data, cap, C.byref(count))
+    return dets[:min(count.value, cap)].copy(), count.value
+
+
+def avgpool(x):
+    x = _c(x)
+    B, Cc, H, W = x.shape
+    out = np.empty((B, Cc, 1, 1), np.float32)
+    lib().pxo_avgpool(_fp(x), _fp(out), B, Cc, H * W)
+    return out
 
 
 def centernet_activate(x, classes, heatmap_bias):

@@ -127,7 +127,11 @@ PROTOTYPES = {
     "pxe_centernet_decode": (_i, [_vp, C.POINTER(CenterNetDecodeDesc), _vp, _vp, _vp, _sz]),
     "pxe_softmax": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
     "pxe_region_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "pxe_avgpool": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i]),
+    "pxe_detect_decode": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _ll, _vp, _i]),
     "pxe_nms_host": (_ll, [_vp, _ll, _f, _vp]),
+    "pxe_nms_workspace_bytes": (_sz, [_ll]),
+    "pxe_nms": (_i, [_vp, _vp, _ll, _f, _vp, _vp, _vp, _sz]),
 }
 
 # the planner of include/pxe_plan.h (host code)

@@ -888,6 +888,84 @@ region_forward_kernel(const RegionParams p)
     }
 }
 
+// ============================================================================================
+// YOLOv1 detection head (include/DetectLayer.h:166-209)
+// ============================================================================================
+// One image's predictions are [side*side*classes class scores][side*side*num object scales]
+// [side*side*num*coords boxes].  A box is emitted when its scale is finite and positive and
+// scale * (its cell's best class score) reaches the threshold; order: image, cell, box.
+// The head is a few thousand values, so one block walks all boxes in order with a running count.
+struct DetectParams {
+    const float* pred; long long pbs;
+    int batch, side, num, classes, coords, squared;
+    float width, height, threshold;
+    pxe_detection* dets; long long capacity; long long* count;
+    int batch_id_offset;
+};
+
+__global__ void __launch_bounds__(1024)
+detect_decode_kernel(const DetectParams p)
+{
+    __shared__ int warp_tot[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = *p.count;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int locations = p.side * p.side;
+    const int per_image = locations * p.num;
+    const long long total = (long long)p.batch * per_image;
+    for (long long base = 0; base < total; base += 1024) {
+        const long long t = base + threadIdx.x;
+        int flag = 0, best = 0;
+        float best_prob = 0.0f, bx = 0, by = 0, bw = 0, bh = 0;
+        int b = 0, slot = 0;
+        if (t < total) {
+            b = (int)(t / per_image);
+            slot = (int)(t - (long long)b * per_image);          // i * num + n
+            const int i = slot / p.num;
+            const int row = i / p.side, col = i - row * p.side;
+            const float* pred = p.pred + (long long)b * p.pbs;
+            const float scale = pred[locations * p.classes + slot];
+            if (isfinite(scale) && scale > 0.0f) {
+                const float* box = pred + (long long)locations * (p.classes + p.num) + (long long)slot * p.coords;
+                const float x = __fmul_rn((box[0] + col) / p.side, p.width);
+                const float y = __fmul_rn((box[1] + row) / p.side, p.height);
+                // std::pow(v, 2) is correctly rounded: one multiplication
+                const float w = __fmul_rn(p.squared ? __fmul_rn(box[2], box[2]) : box[2], p.width);
+                const float h = __fmul_rn(p.squared ? __fmul_rn(box[3], box[3]) : box[3], p.height);
+                best_prob = -FLT_MAX;
+                for (int j = 0; j < p.classes; ++j) {
+                    const float pr = __fmul_rn(scale, pred[i * p.classes + j]);
+                    if (pr > best_prob) { best = j; best_prob = pr; }
+                }
+                if (best_prob >= p.threshold) {
+                    flag = 1;
+                    bx = w > 0.0f ? __fsub_rn(x, w / 2.0f) : x;      // DarkBox::rect, src/DarkBox.cpp:84-123
+                    by = h > 0.0f ? __fsub_rn(y, h / 2.0f) : y;
+                    bw = w; bh = h;
+                }
+            }
+        }
+        int inc = flag;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        __syncthreads();
+        long long before = carry;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (flag) {
+            const long long pos = before + inc - 1;
+            if (pos < p.capacity) store_detection(p.dets + pos, bx, by, bw, bh, best_prob, best, b + p.batch_id_offset, slot);
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = before + inc;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *p.count = carry;
+}
+
 }  // namespace
 }  // namespace pxe
 
@@ -1154,5 +1232,27 @@ extern "C" int pxe_region_forward(pxe_stream_t stream, const float* in, float* o
     const long long boxes = (long long)batch * p.HW * num;
     region_forward_kernel<<<grid_for(boxes, 128, di.sm_count, 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
     PXE_LAUNCH_OK("region_forward_kernel");
+    return PXE_OK;
+}
+
+// ------------------------------------------------------------------------------- YOLOv1 detect
+extern "C" int pxe_detect_decode(pxe_stream_t stream, const float* pred, long long pred_batch_stride, int batch,
+                                 int side, int num, int classes, int coords, int squared, float width, float height,
+                                 float threshold, pxe_detection* dets, long long capacity, long long* count,
+                                 int batch_id_offset)
+{
+    PXE_REQUIRE(pred && dets && count, "detect_decode: null pointer");
+    PXE_REQUIRE(batch > 0 && side > 0 && num > 0 && classes > 0 && coords >= 4, "detect_decode: bad shape");
+    PXE_REQUIRE(capacity >= 0, "detect_decode: negative capacity");
+    PXE_REQUIRE(aligned16(dets), "detect_decode: dets must be 16-byte aligned");
+    const long long outputs = (long long)side * side * (classes + num * (1 + coords));
+    PXE_REQUIRE(pred_batch_stride == 0 || pred_batch_stride >= outputs, "detect_decode: pred_batch_stride too small");
+    DetectParams p{};
+    p.pred = pred; p.pbs = pred_batch_stride ? pred_batch_stride : outputs;
+    p.batch = batch; p.side = side; p.num = num; p.classes = classes; p.coords = coords; p.squared = squared;
+    p.width = width; p.height = height; p.threshold = threshold;
+    p.dets = dets; p.capacity = capacity; p.count = count; p.batch_id_offset = batch_id_offset;
+    detect_decode_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    PXE_LAUNCH_OK("detect_decode_kernel");
     return PXE_OK;
 }

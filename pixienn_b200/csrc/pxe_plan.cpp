@@ -43,6 +43,7 @@ bool reads_dense_only(int type)
     switch (type) {
     case PXE_LAYER_CONV: case PXE_LAYER_CONNECTED: case PXE_LAYER_YOLO: case PXE_LAYER_CENTERNET:
     case PXE_LAYER_REGION: case PXE_LAYER_SOFTMAX: case PXE_LAYER_AVGPOOL: case PXE_LAYER_DROPOUT:
+    case PXE_LAYER_DETECTION:
         return true;
     default:
         return false;
@@ -264,7 +265,7 @@ struct Builder {
                 break;
             }
             case PXE_LAYER_YOLO: case PXE_LAYER_CENTERNET: case PXE_LAYER_REGION: case PXE_LAYER_SOFTMAX:
-            case PXE_LAYER_AVGPOOL: case PXE_LAYER_DROPOUT: case PXE_LAYER_CONNECTED: {
+            case PXE_LAYER_AVGPOOL: case PXE_LAYER_DROPOUT: case PXE_LAYER_CONNECTED: case PXE_LAYER_DETECTION: {
                 pxe_step st = blank(PXE_STEP_HEAD, i);
                 st.n_inputs = 1; st.inputs[0] = resolve(l.sources[0]);
                 st.n_dests = 1; st.dests[0] = pxe_dest{0, -1, 0};

@@ -99,6 +99,24 @@ spp_kernel(const SppParams p)
     }
 }
 
+// Global average pool (include/AvgPoolLayer.h:66-87; cuDNN average pooling over the whole plane on the CUDA
+// path, include/cuda/AvgPoolLayer.h:35-75): one warp per (image, channel) plane, lanes stride the plane,
+// shuffle reduction, one division by max(1, H*W).  The reference's CPU loop adds the plane's values in index
+// order; the tree order here differs from it by rounding only.
+__global__ void __launch_bounds__(256)
+avgpool_kernel(const float* x, long long xbs, float* y, long long ybs, int batch, int channels, int area)
+{
+    const int lane = threadIdx.x & 31;
+    const long long plane = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (plane >= (long long)batch * channels) return;
+    const int b = (int)(plane / channels), c = (int)(plane - (long long)b * channels);
+    const float* src = x + (long long)b * xbs + (long long)c * area;
+    float sum = 0.0f;
+    for (int i = lane; i < area; i += 32) sum += src[i];
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) y[(long long)b * ybs + c] = sum / (float)(area > 1 ? area : 1);
+}
+
 }  // namespace
 }  // namespace pxe
 
@@ -191,5 +209,22 @@ extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_st
     }
     spp_kernel<<<(unsigned)(batch * channels), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
     PXE_LAUNCH_OK("spp_kernel");
+    return PXE_OK;
+}
+
+extern "C" int pxe_avgpool(pxe_stream_t stream, const float* x, long long x_batch_stride, float* y,
+                           long long y_batch_stride, int batch, int channels, int height, int width)
+{
+    PXE_REQUIRE(x && y, "avgpool: null pointer");
+    PXE_REQUIRE(batch > 0 && channels > 0 && height > 0 && width > 0, "avgpool: non-positive shape");
+    const long long area = (long long)height * width, chw = area * channels;
+    PXE_REQUIRE(area <= 0x7fffffffLL, "avgpool: plane too large");
+    PXE_REQUIRE(x_batch_stride == 0 || x_batch_stride >= chw, "avgpool: x_batch_stride too small");
+    PXE_REQUIRE(y_batch_stride == 0 || y_batch_stride >= channels, "avgpool: y_batch_stride too small");
+    const long long planes = (long long)batch * channels;
+    PXE_REQUIRE((planes + 7) / 8 <= 0x7fffffffLL, "avgpool: too many planes");
+    avgpool_kernel<<<(unsigned)((planes + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, x_batch_stride ? x_batch_stride : chw, y, y_batch_stride ? y_batch_stride : channels, batch, channels, (int)area);
+    PXE_LAUNCH_OK("avgpool_kernel");
     return PXE_OK;
 }

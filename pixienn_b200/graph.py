@@ -118,7 +118,7 @@ def parse_model(doc: dict, height: Optional[int] = None, width: Optional[int] = 
             L.sources = [i - 1, frm]
             L.activation = ld.get("activation", "linear")                     # ShortcutLayer.h:49
             L.alpha, L.beta = float(ld.get("alpha", 1.0)), float(ld.get("beta", 1.0))
-        elif t in ("yolo", "centernet", "region", "softmax", "dropout"):
+        elif t in ("yolo", "centernet", "region", "softmax", "dropout", "detection"):
             pass
         elif t == "avgpool":
             L.out_shape = (c, 1, 1)
@@ -151,6 +151,10 @@ def _infer_classes(model: Model) -> Optional[int]:
             return l.in_shape[0] - 4
         if l.type == "region":
             return int(l.params.get("classes", 20))
+        if l.type == "detection":
+            side, num = int(l.params.get("side", 7)), int(l.params.get("num", 1))
+            coords = int(l.params.get("coords", 4))
+            return l.in_shape[0] * l.in_shape[1] * l.in_shape[2] // (side * side) - num * (1 + coords)
         if l.type == "softmax":
             return l.in_shape[0] * l.in_shape[1] * l.in_shape[2]
     return None
@@ -245,7 +249,8 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
         if t not in slots:
             return True
         for r in readers:
-            if L[r].type in ("conv", "connected", "conn", "yolo", "centernet", "region", "softmax", "avgpool", "dropout"):
+            if L[r].type in ("conv", "connected", "conn", "yolo", "centernet", "region", "softmax", "avgpool", "dropout",
+                             "detection"):
                 return True
         return False
 
@@ -342,7 +347,7 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
             else:
                 steps.append(Step("concat", i, list(l.sources), [Dest("dense")], produces=[i]))
                 stats["concat_copies"] += 1
-        elif l.type in ("yolo", "centernet", "region", "softmax", "avgpool", "dropout", "connected", "conn"):
+        elif l.type in ("yolo", "centernet", "region", "softmax", "avgpool", "dropout", "connected", "conn", "detection"):
             st = Step(l.type, i, [resolve(l.sources[0])], [Dest("dense")], produces=[i])
             if l.type == "yolo" and steps and steps[-1].op == "conv" and steps[-1].head_raw:
                 st.head_raw = True
@@ -363,7 +368,7 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
 
 # ------------------------------------------------------------------------- the library's planner
 _LAYER_TYPE = {"conv": 0, "maxpool": 1, "upsample": 2, "route": 3, "shortcut": 4, "yolo": 5, "centernet": 6,
-               "region": 7, "softmax": 8, "avgpool": 9, "dropout": 10, "connected": 11, "conn": 11}
+               "region": 7, "softmax": 8, "avgpool": 9, "dropout": 10, "connected": 11, "conn": 11, "detection": 12}
 _STEP_OP = {0: "conv", 1: "alias", 2: "maxpool", 3: "spp", 4: "upsample", 5: "shortcut", 6: "concat"}
 
 

@@ -375,3 +375,51 @@ def nms(dets: np.ndarray, threshold: float) -> np.ndarray:
     if n < 0:
         raise PxeError(-n, "pxe_nms_host failed")
     return out[:n].copy()
+
+
+def nms_device(dets: torch.Tensor, n: int, threshold: float, out: Optional[torch.Tensor] = None,
+               workspace: Optional[torch.Tensor] = None):
+    """px::nms on the device.  ``dets``: int32 tensor [capacity, 8] of 32-byte records (a DetectionBuffer's
+    ``dets``), of which the first ``n`` are valid.  Returns (out [n, 8] int32, count [1] int64), both on the
+    device; the first ``count`` records of ``out`` are the survivors in the reference's order."""
+    if dets.dtype != torch.int32 or dets.dim() != 2 or dets.shape[1] != 8 or not dets.is_cuda or not dets.is_contiguous():
+        raise ValueError("dets must be a contiguous int32 CUDA tensor of shape [capacity, 8]")
+    n = int(n)
+    if n < 0 or n > dets.shape[0]:
+        raise ValueError(f"n = {n} outside 0..{dets.shape[0]}")
+    if out is None:
+        out = torch.empty((max(n, 1), 8), device=dets.device, dtype=torch.int32)
+    count = torch.zeros(1, device=dets.device, dtype=torch.int64)
+    need = capi.lib().pxe_nms_workspace_bytes(n)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(max(need, 256), device=dets.device, dtype=torch.uint8)
+    capi.check(capi.lib().pxe_nms(_stream(), dets.data_ptr(), n, float(threshold), out.data_ptr(), count.data_ptr(),
+                                  workspace.data_ptr(), workspace.numel()))
+    return out, count
+
+
+def avgpool(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Global average pool: [B, C, H, W] -> [B, C, 1, 1]."""
+    xp, xbs = _slot(x, "x")
+    B, Cc, H, W = x.shape
+    if out is None:
+        out = torch.empty((B, Cc, 1, 1), device=x.device, dtype=torch.float32)
+    capi.check(capi.lib().pxe_avgpool(_stream(), xp, xbs, out.data_ptr(), out.stride(0), B, Cc, H, W))
+    return out
+
+
+def detect_decode(pred: torch.Tensor, side: int, num: int, classes: int, threshold: float, buf: DetectionBuffer, *,
+                  coords: int = 4, squared: bool = False, width: float = 1.0, height: float = 1.0,
+                  batch_id_offset: int = 0) -> None:
+    """Appends a YOLOv1 detection head's boxes to ``buf``.  ``pred``: [B, side*side*(classes + num*(1+coords))]
+    (any trailing shape of that many values per image), contiguous."""
+    _check_f32_cuda(pred, "pred")
+    if not pred.is_contiguous():
+        raise ValueError("pred must be contiguous")
+    B = pred.shape[0]
+    per = pred.numel() // B
+    if per != side * side * (classes + num * (1 + coords)):
+        raise ValueError(f"pred has {per} values per image, expected {side * side * (classes + num * (1 + coords))}")
+    capi.check(capi.lib().pxe_detect_decode(_stream(), pred.data_ptr(), per, B, side, num, classes, coords, int(squared),
+                                            float(width), float(height), float(threshold), buf.dets.data_ptr(),
+                                            buf.capacity, buf.count.data_ptr(), batch_id_offset))

@@ -25,6 +25,17 @@ def synth_weights(model: graph.Model, seed: int = 1234, head_bias: float = 0.0) 
     convolutions feeding a YOLO layer (0 keeps the plain init)."""
     out: Dict[int, Dict[str, np.ndarray]] = {}
     for l in model.layers:
+        if l.type in ("connected", "conn"):
+            # ConnLayer: weights [outputs, inputs] (row-major, include/ConnLayer.h:184-191), same init rule
+            inputs = l.in_shape[0] * l.in_shape[1] * l.in_shape[2]
+            d = {"weights": synth.normal(seed, f"L{l.index}/w", (l.filters, inputs), 0.0, math.sqrt(2.0 / inputs))}
+            if l.batch_norm:
+                g, b, m, v = synth.bn_params(seed, f"L{l.index}/bn", l.filters)
+                d.update(scales=g, biases=b, rolling_mean=m, rolling_var=v)
+            else:
+                d["biases"] = synth.normal(seed, f"L{l.index}/b", l.filters, 0.0, 0.1)
+            out[l.index] = d
+            continue
         if l.type != "conv":
             continue
         cin = l.in_shape[0]
@@ -224,7 +235,36 @@ class Runner:
                 tm.end(s, "region", 8 * xin.numel())
                 self.outputs[st.layer] = T[st.layer]
             elif st.op == "avgpool":
-                T[st.layer] = T[st.inputs[0]].mean(dim=(2, 3), keepdim=True)      # not on the epilogue path
+                xin = T[st.inputs[0]]
+                s = tm.begin()
+                T[st.layer] = ops.avgpool(xin)
+                self.launches += 1
+                tm.end(s, "avgpool", 4 * (xin.numel() + T[st.layer].numel()))
+            elif st.op == "connected":
+                # GEMM on cuBLAS as in the reference (include/cuda/ConnLayer.h:170-183), then the conv epilogue
+                # kernel on [B, outputs, 1, 1]: BN inference or bias, activation (:185-217)
+                w = self.w[l.index]
+                xin = T[st.inputs[0]].reshape(self.batch, -1)
+                s = tm.begin()
+                raw = F.linear(xin, w["weights"]).reshape(self.batch, l.filters, 1, 1)
+                tm.end(s, "gemm(cublas)", 0)
+                bn = dict(gamma=w["scales"], beta=w["biases"], mean=w["rolling_mean"], var=w["rolling_var"],
+                          eps_mode=self.eps_mode) if l.batch_norm else dict(bias=w["biases"])
+                s = tm.begin()
+                T[st.layer] = ops.conv_epilogue(raw, act=l.activation, **bn)
+                self.launches += 1
+                tm.end(s, "epilogue", 8 * raw.numel())
+            elif st.op == "detection":
+                xin = T[st.inputs[0]].contiguous()
+                s = tm.begin()
+                ops.detect_decode(xin, int(l.params.get("side", 7)), int(l.params.get("num", 1)),
+                                  self.model.classes, self.threshold, self.dets,
+                                  coords=int(l.params.get("coords", 4)), squared=bool(l.params.get("sqrt", False)),
+                                  batch_id_offset=self.batch_id_offset)
+                self.launches += 1
+                tm.end(s, "detect_decode", 4 * xin.numel())
+                self.head_marks.append(self.dets.count.clone())
+                T[st.layer] = xin
             elif st.op == "dropout":
                 T[st.layer] = T[st.inputs[0]]
             else:

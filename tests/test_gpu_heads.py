@@ -331,3 +331,93 @@ def test_compat_symbols_run(cuda, oracle):
     fill(out.data_ptr(), out.numel(), 3.5)
     torch.cuda.synchronize()
     assert (out == 3.5).all()
+
+
+def _random_boxes(rng, n, images, classes, spread=0.8):
+    d = np.zeros(n, ops.DET_DTYPE)
+    d["x"], d["y"] = rng.random(n) * spread, rng.random(n) * spread
+    d["w"], d["h"] = rng.random(n) * 0.3 + 0.01, rng.random(n) * 0.3 + 0.01
+    d["prob"] = np.round(rng.random(n), 2)          # many ties: exercises the stable order
+    d["class_id"], d["batch_id"] = rng.integers(0, classes, n), rng.integers(0, images, n)
+    d["source"] = np.arange(n)
+    return d
+
+
+def _nms_device(d, thr, cuda):
+    t = torch.from_numpy(d.view(np.int32).reshape(-1, 8).copy()).to(cuda)
+    out, count = ops.nms_device(t, len(d), thr)
+    m = int(count.item())
+    return out[:m].cpu().numpy().view(ops.DET_DTYPE).reshape(-1)
+
+
+@pytest.mark.parametrize("n,images,classes,thr", [(3000, 2, 3, 0.4), (1, 1, 1, 0.4), (500, 7, 80, 0.45), (6000, 1, 2, 0.3),
+                                                  (4000, 3, 1, 0.6), (257, 2, 5, 0.0)])
+def test_nms_device_equals_host_nms(cuda, oracle, n, images, classes, thr):
+    """Same survivors, same order, same bits as pxe_nms_host (and the oracle's restatement of px::nms):
+    probability ties, cross-class duplicates, groups longer than the 1024-member window."""
+    d = _random_boxes(np.random.default_rng(n), n, images, classes)
+    if n >= 500:
+        dup = d[: n // 10].copy()                   # near-identical boxes of other classes: the IoU > 0.9 rule
+        dup["class_id"] = (dup["class_id"] + 1) % max(classes, 2)
+        dup["x"] += 1e-3
+        d[-len(dup):] = dup
+        d["w"][5], d["h"][6] = -0.2, 0.0            # negative / empty extents go through the same normalisation
+    want = ops.nms(d, thr)
+    got = _nms_device(d, thr, cuda)
+    assert len(got) == len(want)
+    assert got.tobytes() == want.tobytes()
+    ref = oracle.nms(d, thr)
+    assert len(ref) == len(got) and np.array_equal(ref["source"], got["source"])
+
+
+def test_nms_device_on_decoded_detections(cuda):
+    """End of the pipeline on the device: YOLO decode -> device NMS, against decode -> host copy -> host NMS."""
+    model_in = synth.normal(90, "nmshead", (2, 255, 13, 13), 0, 1.5)
+    buf = ops.DetectionBuffer(1 << 16, cuda)
+    ops.yolo_decode(ops.yolo_activate(dev(model_in, cuda), 3, 80), [3, 4, 5], [10, 14, 23, 27, 37, 58, 81, 82, 135, 169, 344, 319],
+                    80, 416, 416, 0.6, buf)
+    recs, total = buf.to_host()
+    assert 0 < total <= buf.capacity
+    out, count = ops.nms_device(buf.dets, total, 0.4)
+    got = out[: int(count.item())].cpu().numpy().view(ops.DET_DTYPE).reshape(-1)
+    want = ops.nms(recs, 0.4)
+    assert len(want) > 0 and got.tobytes() == want.tobytes()
+
+
+def test_nms_device_argument_errors(cuda):
+    t = torch.zeros((4, 8), device=cuda, dtype=torch.int32)
+    out, count = ops.nms_device(t, 0, 0.4)
+    assert int(count.item()) == 0
+    with pytest.raises(ValueError):
+        ops.nms_device(t, 5, 0.4)
+    L = ops.capi.lib()
+    assert L.pxe_nms(None, t.data_ptr(), 4, 0.4, t.data_ptr(), count.data_ptr(), t.data_ptr(), 16) == ops.capi.PXE_ERR_BAD_ARG
+    ws = torch.empty(256, device=cuda, dtype=torch.uint8)
+    o = torch.empty_like(t)
+    assert L.pxe_nms(None, t.data_ptr(), 4, 0.4, o.data_ptr(), count.data_ptr(), ws.data_ptr(), 256) == ops.capi.PXE_ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("B,side,num,classes,squared,thr", [(3, 7, 2, 20, True, 0.2), (1, 3, 1, 4, False, 0.05), (5, 11, 3, 80, True, 0.5)])
+def test_detect_decode_matches_oracle(cuda, oracle, B, side, num, classes, squared, thr):
+    """YOLOv1 head: same boxes, classes, probabilities and order as DetectLayer::addDetects; scales that are
+    zero, negative or not finite emit nothing; capacity overflow is counted, not stored."""
+    rng = np.random.default_rng(B * 100 + side)
+    per = side * side * (classes + num * 5)
+    pred = rng.random((B, per)).astype(np.float32)
+    scales = pred[:, side * side * classes: side * side * (classes + num)]
+    scales[:, ::5] = 0.0
+    scales[:, 1::7] = -0.3
+    scales[0, 2] = np.nan
+    scales[0, 3] = np.inf
+    ref, total = oracle.detect_decode(pred, side, num, classes, thr, squared=squared)
+    assert total > 0
+    buf = ops.DetectionBuffer(B * side * side * num, cuda)
+    ops.detect_decode(dev(pred, cuda), side, num, classes, thr, buf, squared=squared)
+    got, n = buf.to_host()
+    assert n == total
+    dets_equal(got, ref)
+    small = ops.DetectionBuffer(max(1, total // 2), cuda)
+    ops.detect_decode(dev(pred, cuda), side, num, classes, thr, small, squared=squared, batch_id_offset=4)
+    got, n = small.to_host()
+    assert n == total and len(got) == max(1, total // 2)
+    assert np.array_equal(got["source"], ref["source"][:len(got)]) and np.array_equal(got["batch_id"], ref["batch_id"][:len(got)] + 4)

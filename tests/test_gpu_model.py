@@ -167,3 +167,33 @@ def test_cuda_graph_replay_equals_eager_forward(cuda, name):
         got, gt = captured.detections()
         assert wt == gt and len(want) > 0 and got.tobytes() == want.tobytes()
         assert [h.tobytes() for h in captured.detections_by_head()] == [h.tobytes() for h in eager.detections_by_head()]
+
+
+def test_yolov1_style_graph_runs_connected_and_detection_layers(cuda, oracle):
+    """conv + pool -> avgpool-free YOLOv1 tail: connected layer (cuBLAS GEMM + the epilogue kernel on
+    [B, outputs, 1, 1]) and the detection head decoded on the device.  The decode is checked exactly against
+    the oracle on the head values the device produced; the connected layer against a float64 product."""
+    side, num, classes = 3, 2, 4
+    doc = {"model": {"channels": 3, "height": 24, "width": 24, "layers": [
+        {"type": "conv", "filters": 8, "kernel": 3, "stride": 1, "pad": True, "batch_normalize": True, "activation": "leaky"},
+        {"type": "maxpool", "kernel": 2, "stride": 2},
+        {"type": "conv", "filters": 16, "kernel": 3, "stride": 2, "pad": True, "batch_normalize": True, "activation": "leaky"},
+        {"type": "connected", "output": side * side * (classes + num * 5), "activation": "linear"},
+        {"type": "detection", "side": side, "num": num, "coords": 4, "sqrt": True, "softmax": False},
+    ]}}
+    model = graph.parse_model(doc)
+    assert model.classes == classes
+    weights = synth_weights(model, 13)
+    weights[3]["biases"] = weights[3]["biases"] + 0.3
+    r = Runner(model, weights, 2, cuda, threshold=0.05)
+    r.keep = {2, 3}
+    x = dev(make_input(40, 2, model), cuda)
+    with exact_fp32_convolutions():
+        r.forward(x)
+    head = r.kept[3].cpu().numpy().reshape(2, -1)
+    feat = r.kept[2].cpu().numpy().reshape(2, -1).astype(np.float64)
+    want_head = feat @ weights[3]["weights"].astype(np.float64).T + weights[3]["biases"]
+    np.testing.assert_allclose(head, want_head, rtol=2e-3, atol=2e-3)      # cuBLAS may use TF32 products
+    ref, total = oracle.detect_decode(head, side, num, classes, 0.05, squared=True)
+    got, n = r.detections()
+    assert n == total > 0 and got.tobytes() == ref.tobytes()

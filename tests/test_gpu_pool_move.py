@@ -160,3 +160,13 @@ def test_pool_and_move_argument_errors(cuda):
         ops.upsample(x, 0)
     assert capi.lib().pxe_concat(None, 0, None, None, None, None, 0, 1, 1, 1) == capi.PXE_ERR_BAD_ARG
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("shape", [(2, 512, 7, 7), (3, 5, 1, 1), (1, 3, 13, 40), (2, 1000, 2, 2)])
+def test_avgpool(cuda, oracle, shape):
+    x = synth.normal(41, f"avg{shape}", shape, 0.5, 2.0)
+    ref = oracle.avgpool(x)
+    close(ops.avgpool(dev(x, cuda)).cpu().numpy(), ref)
+    wide = torch.zeros((shape[0], shape[1] + 3, shape[2], shape[3]), device=cuda)
+    wide[:, 3:] = dev(x, cuda)
+    close(ops.avgpool(wide[:, 3:]).cpu().numpy(), ref)          # a channel slot of a wider buffer
