@@ -142,7 +142,7 @@ def run_model(args):
     B = args.batch
     weights = synth_weights(model, SEED)
     runner = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF,
-                    batch_id_offset=rank * B)
+                    batch_id_offset=rank * B, layout=args.layout)
     xh = torch.from_numpy(host_batch(model, B, rank * B)).pin_memory()
     x = xh.to(dev)
     pinned_dets = None
@@ -245,7 +245,7 @@ def run_model(args):
         "ms_per_step": round(total_ms / args.steps, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{label}, {B} images per GPU, global batch {B * world}, fp32 NCHW, random-init weights "
+        "config": {"workload": f"{label}, {B} images per GPU, global batch {B * world}, fp32 {args.layout.upper()}, random-init weights "
                                f"(seed {SEED}), conf {CONF}; conv on cuDNN (TF32 allowed, cuDNN's default math mode), "
                                "epilogue/shortcut/upsample/route/decode on libpxe.so",
                    "per_gpu_batch": B, "global_batch": B * world, "sharding": "by image, no collectives",
@@ -457,6 +457,53 @@ def run_centernet(args):
           flush=True)
 
 
+def run_nms(args):
+    """px::nms on the device (pxe_nms) against the same rule on the host (pxe_nms_host): `--batch` images with
+    `--nms-boxes` candidate boxes each over 80 classes, clustered around 12 objects per image so that
+    suppression has real work to do."""
+    import torch
+    from pixienn_b200 import ops
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(SEED)
+    B, per = args.batch, args.nms_boxes
+    n = B * per
+    d = np.zeros(n, ops.DET_DTYPE)
+    centres = rng.random((B, 12, 2)) * 0.8 + 0.1
+    sizes = rng.random((B, 12, 2)) * 0.25 + 0.05
+    obj = rng.integers(0, 12, n)
+    img = np.repeat(np.arange(B), per)
+    d["w"] = sizes[img, obj, 0] * (1 + rng.normal(0, 0.08, n))
+    d["h"] = sizes[img, obj, 1] * (1 + rng.normal(0, 0.08, n))
+    d["x"] = centres[img, obj, 0] + rng.normal(0, 0.01, n) - d["w"] / 2
+    d["y"] = centres[img, obj, 1] + rng.normal(0, 0.01, n) - d["h"] / 2
+    d["prob"] = rng.random(n).astype(np.float32) * 0.8 + 0.2
+    d["class_id"] = (obj * 5 + rng.integers(0, 2, n)) % 80
+    d["batch_id"] = img
+    d["source"] = np.arange(n)
+    t = torch.from_numpy(d.view(np.int32).reshape(-1, 8).copy()).to(dev)
+    ws = torch.empty(ops.capi.lib().pxe_nms_workspace_bytes(n), device=dev, dtype=torch.uint8)
+    out = torch.empty_like(t)
+    for _ in range(args.warmup):
+        o, c = ops.nms_device(t, n, 0.4, out=out, workspace=ws)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    for a, z in ev:
+        a.record()
+        o, c = ops.nms_device(t, n, 0.4, out=out, workspace=ws)
+        z.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(z) for a, z in ev)
+    kept = int(c.item())
+    h0 = time.perf_counter()
+    want = ops.nms(d, 0.4)
+    host_ms = (time.perf_counter() - h0) * 1e3
+    got = o[:kept].cpu().numpy().view(ops.DET_DTYPE).reshape(-1)
+    print(json.dumps({"metric": "px::nms on the device", "value": round(ts[len(ts) // 2], 4), "unit": "ms", "higher_is_better": False,
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"NMS of {B} images x {per} boxes, 80 classes, threshold 0.4", "records": n, "kept": kept},
+                      "host_ms": round(host_ms, 2), "identical_to_host": bool(got.tobytes() == want.tobytes())}), flush=True)
+
+
 def run_epilogue_compare(args):
     """Epilogue path only (no convolutions), layer by layer over the model graph, on scratch buffers of
     each layer's shape: the reference's own CUDA call sequences (its src/*.cu compiled for sm_100a in
@@ -605,7 +652,11 @@ def main():
     ap.add_argument("--sweep-pool", default="both", choices=["none", "pool", "both"])
     ap.add_argument("--sweep-residual", action="store_true", help="sweep the epilogue fused with a shortcut add")
     ap.add_argument("--model", default="yolov3-608", help="model graph for --workload epilogue-compare")
+    ap.add_argument("--nms-boxes", type=int, default=1000, help="candidate boxes per image for --workload nms")
     ap.add_argument("--no-cudnn-benchmark", action="store_true", help="skip cuDNN's algorithm search (profiling runs)")
+    ap.add_argument("--layout", default="nchw", choices=["nchw", "nhwc"],
+                    help="activation layout between layers: nchw = the reference's (BASELINE.json's configs); nhwc = "
+                         "channels-last, which lets cuDNN skip its layout conversions (the library's NHWC tier)")
     ap.add_argument("--cuda-graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the forward pass as one CUDA graph (auto: batches of 8 images or fewer, where the "
                          "host cannot issue the launches fast enough)")
@@ -624,6 +675,8 @@ def main():
         return run_sweep(args)
     if args.workload == "centernet":
         return run_centernet(args)
+    if args.workload == "nms":
+        return run_nms(args)
     if args.workload == "epilogue-compare":
         return run_epilogue_compare(args)
     return run_model(args)

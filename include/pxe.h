@@ -310,6 +310,58 @@ PXE_API int pxe_softmax(pxe_stream_t stream, const float* in, float* out, int ba
 PXE_API int pxe_region_forward(pxe_stream_t stream, const float* in, float* out, int batch, int width,
                                int height, int num, int coords, int classes, int softmax);
 
+/* ------------------------------------------------------------------------------------------
+ * Channels-last (NHWC) tier.  The reference describes every tensor to cuDNN as NCHW
+ * (include/Cudnn.h:103-108; include/cuda/ConvLayer.h:278-283), and cuDNN then converts to and from the NHWC
+ * layout of its tensor-core kernels around every convolution.  A caller that sets its descriptors to
+ * CUDNN_TENSOR_NHWC (and stores its filters that way) avoids those conversions; these entry points are the
+ * epilogue path for such tensors.  Element (image b, row r, column c, channel k) of a tensor lives at
+ * ((b*H + r)*W + c) * pixel_stride + k; pixel_stride is the channel count of the buffer the tensor lives in
+ * (0 = the tensor's own channel count), so a channel slot of a route's concat buffer is a tensor with a
+ * larger pixel stride and a pointer advanced by the slot's first channel.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Folds batch-norm inference and bias into y = a[k]*x + b[k] (include/cuda/ConvLayer.h:294-303;
+ * CPU form src/BatchNorm.cpp:61-66 with eps_mode = PXE_BN_EPS_CPU): a = gamma / denom(var, eps),
+ * b = beta - mean*a (+ bias).  gamma == NULL: a = 1, b = bias (or 0).  Run once per layer when the weights
+ * are loaded; a, b: device arrays of `channels` floats. */
+PXE_API int pxe_fold_bn(pxe_stream_t stream, const float* gamma, const float* beta, const float* mean,
+                        const float* var, const float* bias, float eps, int eps_mode, int channels, float* a,
+                        float* b);
+
+typedef struct pxe_epilogue_nhwc_desc {
+    const float* x;               /* conv output, NHWC */
+    float* y;                     /* destination (may be x) */
+    float* y2;                    /* optional second destination, e.g. a route slot */
+    const float* residual;        /* optional: the `from` tensor of a following shortcut layer */
+    long long x_pixel_stride, y_pixel_stride, y2_pixel_stride, residual_pixel_stride;   /* 0 = channels */
+    long long pixels;             /* batch * height * width */
+    int channels;
+    const float* a;               /* folded coefficients from pxe_fold_bn, or NULL (with b) for none */
+    const float* b;
+    int act;                      /* pxe_activation */
+    float res_alpha, res_beta;    /* y = res_act(res_alpha * act(a*x+b) + res_beta * residual) */
+    int res_act;
+} pxe_epilogue_nhwc_desc;
+
+/* The fused conv epilogue of pxe_conv_epilogue for NHWC tensors; with a = b = NULL and act linear it is
+ * the shortcut layer (include/cuda/ShortcutLayer.h:23-34) or a copy into a route slot. */
+PXE_API int pxe_conv_epilogue_nhwc(pxe_stream_t stream, const pxe_epilogue_nhwc_desc* desc);
+
+/* UpsampleLayer (src/UpsampleKernels.cu:25-63) and MaxPoolLayer (src/MaxPoolKernels.cu:10-43, values only)
+ * for NHWC tensors; same geometry and tie rules as pxe_upsample / pxe_maxpool. */
+PXE_API int pxe_upsample_nhwc(pxe_stream_t stream, const float* in, long long in_pixel_stride, float* out,
+                              long long out_pixel_stride, int batch, int channels, int height, int width,
+                              int stride, float scale);
+PXE_API int pxe_maxpool_nhwc(pxe_stream_t stream, const float* in, long long in_pixel_stride, float* out,
+                             long long out_pixel_stride, int batch, int channels, int height, int width,
+                             int kernel, int stride, int padding);
+
+/* NHWC -> dense NCHW (batch stride 0 = channels*height*width): hands a head to the decoders, which read the
+ * reference's [B][C][H*W] layout. */
+PXE_API int pxe_nhwc_to_nchw(pxe_stream_t stream, const float* in, long long in_pixel_stride, float* out,
+                             long long out_batch_stride, int batch, int channels, int height, int width);
+
 /* Global average pooling (AvgPoolLayer::forward, include/AvgPoolLayer.h:66-87; cudnnPoolingForward with an
  * H x W average window on the CUDA path, include/cuda/AvgPoolLayer.h:66-75): y[b][c] = mean of plane (b, c).
  * x: [batch, channels, height, width] with batch stride (0 = dense); y: [batch, channels] likewise. */
@@ -321,7 +373,8 @@ PXE_API int pxe_avgpool(pxe_stream_t stream, const float* x, long long x_batch_s
  * [side*side*classes class scores][side*side*num object scales][side*side*num*coords boxes], the layer's
  * input as the connected layer before it leaves it.  A box is emitted when its scale is finite and positive
  * and scale * (best class score of its cell) >= threshold; its record carries that class and probability;
- * squared != 0 squares the predicted width / height (the layer's `sqrt` option).  Records are appended to
+ * squared != 0 squares the predicted width / height (the layer's `sqrt` option; v*v here, powf(v, 2) on the
+ * reference's host path, which can differ in the last bit).  Records are appended to
  * `dets` behind *count (device) in the reference's order (image, cell, box); *count advances past every
  * emitted box even when capacity is exceeded.  width / height: the scale of the boxes (1, 1 = normalised). */
 PXE_API int pxe_detect_decode(pxe_stream_t stream, const float* pred, long long pred_batch_stride, int batch,

@@ -48,6 +48,15 @@ class EpilogueDesc(C.Structure):
     ]
 
 
+class EpilogueNhwcDesc(C.Structure):
+    """pxe_epilogue_nhwc_desc of include/pxe.h."""
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("y2", C.c_void_p), ("residual", C.c_void_p),
+                ("x_pixel_stride", C.c_longlong), ("y_pixel_stride", C.c_longlong), ("y2_pixel_stride", C.c_longlong),
+                ("residual_pixel_stride", C.c_longlong), ("pixels", C.c_longlong), ("channels", C.c_int),
+                ("a", C.c_void_p), ("b", C.c_void_p), ("act", C.c_int), ("res_alpha", C.c_float), ("res_beta", C.c_float),
+                ("res_act", C.c_int)]
+
+
 class YoloDecodeDesc(C.Structure):
     _fields_ = [
         ("head", C.c_void_p), ("head_batch_stride", C.c_longlong),
@@ -127,6 +136,11 @@ PROTOTYPES = {
     "pxe_centernet_decode": (_i, [_vp, C.POINTER(CenterNetDecodeDesc), _vp, _vp, _vp, _sz]),
     "pxe_softmax": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
     "pxe_region_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "pxe_fold_bn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]),
+    "pxe_conv_epilogue_nhwc": (_i, [_vp, C.POINTER(EpilogueNhwcDesc)]),
+    "pxe_upsample_nhwc": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i, _f]),
+    "pxe_maxpool_nhwc": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i, _i, _i]),
+    "pxe_nhwc_to_nchw": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i]),
     "pxe_avgpool": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i]),
     "pxe_detect_decode": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _ll, _vp, _i]),
     "pxe_nms_host": (_ll, [_vp, _ll, _f, _vp]),

@@ -119,14 +119,45 @@ __global__ void nms_segment_starts_kernel(const K* sorted, int n, int* starts, i
     if (threadIdx.x == 0) *count = carry;
 }
 
-// Step 2.  members[start..end) = input indices of one image's records in probability order.
+// Step 2.  members[start..end) = input indices of one image's records in probability order.  An image with at
+// most kImageStage records is staged in shared memory first, so that a pivot step costs a barrier and a few
+// shared-memory reads instead of a chain of dependent global loads; longer segments run from global memory.
+constexpr int kImageStage = 4096;
+constexpr size_t kImageStageBytes = (size_t)kImageStage * (sizeof(Rect) + sizeof(unsigned) + 1);
+
 __global__ void __launch_bounds__(1024)
 nms_cross_class_kernel(const int* members, const int* starts, const int* nseg, int n, const Rect* rect,
                        const unsigned* cls, unsigned char* discard)
 {
+    extern __shared__ __align__(16) unsigned char stage_raw[];
+    Rect* sbox = reinterpret_cast<Rect*>(stage_raw);
+    unsigned* scls = reinterpret_cast<unsigned*>(sbox + kImageStage);
+    unsigned char* sdead = reinterpret_cast<unsigned char*>(scls + kImageStage);
     const int segs = *nseg;
     for (int s = blockIdx.x; s < segs; s += gridDim.x) {
         const int lo = starts[s], hi = s + 1 < segs ? starts[s + 1] : n;
+        const int cnt = hi - lo;
+        if (cnt <= kImageStage) {
+            for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
+                const int j = members[lo + t];
+                sbox[t] = rect[j];
+                scls[t] = cls[j];
+                sdead[t] = 0;                              // nothing has been discarded before this step
+            }
+            __syncthreads();
+            for (int p = 0; p < cnt; ++p) {
+                if (sdead[p]) continue;                    // block-uniform: written before the last barrier
+                const Rect ri = sbox[p];
+                const unsigned ci = scls[p];
+                for (int q = p + 1 + (int)threadIdx.x; q < cnt; q += blockDim.x)
+                    if (scls[q] != ci && !sdead[q] && rect_iou(sbox[q], ri) > 0.9f) sdead[q] = 1;
+                __syncthreads();
+            }
+            for (int t = threadIdx.x; t < cnt; t += blockDim.x)
+                if (sdead[t]) discard[members[lo + t]] = 1;
+            __syncthreads();
+            continue;
+        }
         for (int p = lo; p < hi; ++p) {
             const int i = members[p];
             if (discard[i]) continue;                      // block-uniform: written before the last barrier
@@ -304,7 +335,8 @@ extern "C" int pxe_nms(pxe_stream_t stream, const pxe_detection* dets, long long
     nms_segment_starts_kernel<unsigned long long><<<1, 1024, 0, s>>>(group_b, N, starts_grp, counts + 1);
     PXE_LAUNCH_OK("nms_segment_starts_kernel");
     const unsigned seg_blocks = (unsigned)(N < 4 * di.sm_count ? N : 4 * di.sm_count);
-    nms_cross_class_kernel<<<seg_blocks, 1024, 0, s>>>(by_image, starts_img, counts + 0, N, rect, cls, discard);
+    PXE_CUDA_OK(cudaFuncSetAttribute(nms_cross_class_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kImageStageBytes));
+    nms_cross_class_kernel<<<seg_blocks, 1024, kImageStageBytes, s>>>(by_image, starts_img, counts + 0, N, rect, cls, discard);
     PXE_LAUNCH_OK("nms_cross_class_kernel");
     nms_group_kernel<<<seg_blocks, kGroupCap, 0, s>>>(by_group, starts_grp, counts + 1, N, rect, threshold, discard);
     PXE_LAUNCH_OK("nms_group_kernel");

@@ -423,3 +423,94 @@ def detect_decode(pred: torch.Tensor, side: int, num: int, classes: int, thresho
     capi.check(capi.lib().pxe_detect_decode(_stream(), pred.data_ptr(), per, B, side, num, classes, coords, int(squared),
                                             float(width), float(height), float(threshold), buf.dets.data_ptr(),
                                             buf.capacity, buf.count.data_ptr(), batch_id_offset))
+
+
+# ------------------------------------------------------------------------------ channels-last tier
+def _nhwc(t: Optional[torch.Tensor], name: str):
+    """(pointer, pixel stride) of a logical [B,C,H,W] tensor stored channels-last: a dense channels-last tensor
+    or a channel slice of one."""
+    if t is None:
+        return None, 0
+    _check_f32_cuda(t, name)
+    if t.dim() != 4:
+        raise ValueError(f"{name} must be 4-D [B,C,H,W], got {tuple(t.shape)}")
+    b, c, h, w = t.shape
+    st = t.stride()
+    ps = st[3] if w > 1 else (st[2] // max(w, 1) if h > 1 else (st[0] // max(h * w, 1) if b > 1 else c))
+    if ps < c or (c > 1 and st[1] != 1) or (h > 1 and st[2] != w * ps) or (b > 1 and st[0] != h * w * ps):
+        raise ValueError(f"{name} is not channels-last (strides {st} for shape {tuple(t.shape)})")
+    return t.data_ptr(), int(ps)
+
+
+def empty_nhwc(shape, device) -> torch.Tensor:
+    return torch.empty(tuple(shape), device=device, dtype=torch.float32, memory_format=torch.channels_last)
+
+
+def fold_bn(channels: int, device, *, gamma=None, beta=None, mean=None, var=None, bias=None, eps: float = 1e-5,
+            eps_mode: int = capi.EPS_CUDNN):
+    """Folded per-channel coefficients (a, b) of BN inference + bias, computed once per layer."""
+    a = torch.empty(channels, device=device, dtype=torch.float32)
+    b = torch.empty(channels, device=device, dtype=torch.float32)
+    capi.check(capi.lib().pxe_fold_bn(_stream(), _vec(gamma, channels, "gamma"), _vec(beta, channels, "beta"),
+                                      _vec(mean, channels, "mean"), _vec(var, channels, "var"),
+                                      _vec(bias, channels, "bias"), eps, eps_mode, channels, a.data_ptr(), b.data_ptr()))
+    return a, b
+
+
+def conv_epilogue_nhwc(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None,
+                       a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None, act="linear",
+                       residual: Optional[torch.Tensor] = None, res_alpha: float = 1.0, res_beta: float = 1.0,
+                       res_act="linear") -> torch.Tensor:
+    """Fused epilogue on channels-last tensors; ``y=None`` works in place."""
+    xp, xps = _nhwc(x, "x")
+    B, Cc, H, W = x.shape
+    if y is None:
+        y = x
+    d = capi.EpilogueNhwcDesc()
+    d.x, d.x_pixel_stride = xp, xps
+    d.y, d.y_pixel_stride = _nhwc(y, "y")
+    for t, n in ((y, "y"), (y2, "y2"), (residual, "residual")):
+        if t is not None and tuple(t.shape) != (B, Cc, H, W):
+            raise ValueError(f"{n} has shape {tuple(t.shape)}, expected {(B, Cc, H, W)}")
+    if y2 is not None:
+        d.y2, d.y2_pixel_stride = _nhwc(y2, "y2")
+    if residual is not None:
+        d.residual, d.residual_pixel_stride = _nhwc(residual, "residual")
+    d.pixels, d.channels = B * H * W, Cc
+    d.a, d.b = _vec(a, Cc, "a"), _vec(b, Cc, "b")
+    d.act, d.res_alpha, d.res_beta, d.res_act = _act(act), res_alpha, res_beta, _act(res_act)
+    capi.check(capi.lib().pxe_conv_epilogue_nhwc(_stream(), C.byref(d)))
+    return y
+
+
+def upsample_nhwc(x: torch.Tensor, stride: int, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    xp, xps = _nhwc(x, "x")
+    B, Cc, H, W = x.shape
+    if out is None:
+        out = empty_nhwc((B, Cc, H * stride, W * stride), x.device)
+    op, ops_ = _nhwc(out, "out")
+    capi.check(capi.lib().pxe_upsample_nhwc(_stream(), xp, xps, op, ops_, B, Cc, H, W, stride, scale))
+    return out
+
+
+def maxpool_nhwc(x: torch.Tensor, kernel: int, stride: int, padding: Optional[int] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    xp, xps = _nhwc(x, "x")
+    B, Cc, H, W = x.shape
+    if padding is None:
+        padding = kernel - 1
+    oh, ow = maxpool_out_dim(H, kernel, stride, padding), maxpool_out_dim(W, kernel, stride, padding)
+    if out is None:
+        out = empty_nhwc((B, Cc, oh, ow), x.device)
+    op, ops_ = _nhwc(out, "out")
+    capi.check(capi.lib().pxe_maxpool_nhwc(_stream(), xp, xps, op, ops_, B, Cc, H, W, kernel, stride, padding))
+    return out
+
+
+def nhwc_to_nchw(x: torch.Tensor) -> torch.Tensor:
+    """Dense NCHW copy of a channels-last tensor (for the decoders)."""
+    xp, xps = _nhwc(x, "x")
+    B, Cc, H, W = x.shape
+    out = torch.empty((B, Cc, H, W), device=x.device, dtype=torch.float32)
+    capi.check(capi.lib().pxe_nhwc_to_nchw(_stream(), xp, xps, out.data_ptr(), 0, B, Cc, H, W))
+    return out

@@ -94,8 +94,15 @@ class OpTimer:
 class Runner:
     def __init__(self, model: graph.Model, weights: Dict[int, Dict[str, np.ndarray]], batch: int, device,
                  fuse: bool = True, raw_heads: bool = True, det_capacity: int = 1 << 20,
-                 threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0):
+                 threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0, layout: str = "nchw"):
+        if layout not in ("nchw", "nhwc"):
+            raise ValueError("layout must be 'nchw' (the reference's) or 'nhwc' (channels-last)")
         self.model, self.batch, self.device = model, batch, device
+        # "nhwc": every activation tensor is channels-last, so cuDNN runs its tensor-core convolution kernels
+        # without converting the layout around each of them; the epilogue path uses the library's NHWC tier and
+        # heads are transposed to NCHW for the decoders.  Results equal the "nchw" run up to the convolutions'
+        # own rounding (cuDNN picks different kernels for the two layouts).
+        self.nhwc = layout == "nhwc"
         self.eps_mode = eps_mode        # 0: cuDNN form sqrt(var+eps) (the CUDA path), 1: the CPU path's sqrt(var)+eps
         self.plan = graph.plan_native(model, fuse=fuse, raw_heads=raw_heads)   # the library's C++ planner (pxe_plan.h)
         self.threshold = threshold
@@ -103,6 +110,17 @@ class Runner:
         self.w: Dict[int, Dict[str, torch.Tensor]] = {
             i: {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in d.items()}
             for i, d in weights.items()}
+        if self.nhwc:
+            for l in model.layers:
+                if l.type != "conv":
+                    continue
+                w = self.w[l.index]
+                w["weights"] = w["weights"].contiguous(memory_format=torch.channels_last)
+                if l.batch_norm:
+                    w["a"], w["b"] = ops.fold_bn(l.filters, device, gamma=w["scales"], beta=w["biases"],
+                                                 mean=w["rolling_mean"], var=w["rolling_var"], eps_mode=eps_mode)
+                else:
+                    w["a"], w["b"] = ops.fold_bn(l.filters, device, bias=w["biases"])
         self.dets = ops.DetectionBuffer(det_capacity, device)
         self.head_marks = []           # device copies of the running detection count after each YOLO head
         self.centernet_out = []        # (dets, counts) per centernet layer of the last forward
@@ -114,10 +132,22 @@ class Runner:
         self.kept: Dict[int, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ helpers
+    def _empty(self, shape) -> torch.Tensor:
+        if self.nhwc:
+            return ops.empty_nhwc(shape, self.device)
+        return torch.empty(tuple(shape), device=self.device)
+
+    def _nchw(self, t: torch.Tensor) -> torch.Tensor:
+        """Dense NCHW tensor for the decoders and the flattening layers."""
+        if self.nhwc and t.shape[1] > 1 and t.shape[2] * t.shape[3] > 1:
+            self.launches += 1
+            return ops.nhwc_to_nchw(t)
+        return t.contiguous()
+
     def _view(self, bufs, route: int, offset: int, layer: graph.Layer) -> torch.Tensor:
         c, h, w = layer.out_shape
         if route not in bufs:
-            bufs[route] = torch.empty((self.batch, self.plan.concat_channels[route], h, w), device=self.device)
+            bufs[route] = self._empty((self.batch, self.plan.concat_channels[route], h, w))
         return bufs[route][:, offset:offset + c]
 
     def _dest_tensors(self, bufs, dests: List[graph.Dest], layer: graph.Layer, dense: Optional[torch.Tensor] = None):
@@ -125,7 +155,7 @@ class Runner:
         for d in dests:
             if d.kind == "dense":
                 if dense is None:
-                    dense = torch.empty((self.batch,) + layer.out_shape, device=self.device)
+                    dense = self._empty((self.batch,) + layer.out_shape)
                 out.append(dense)
             else:
                 out.append(self._view(bufs, d.route, d.offset, layer))
@@ -134,7 +164,10 @@ class Runner:
     def _extra_copies(self, src: torch.Tensor, extra: List[torch.Tensor]):
         for t in extra:
             s = self.timer.begin()
-            ops.concat([src], out=t)
+            if self.nhwc:
+                ops.conv_epilogue_nhwc(src, y=t)
+            else:
+                ops.concat([src], out=t)
             self.launches += 1
             self.timer.end(s, "concat", 8 * src.numel())
 
@@ -143,6 +176,8 @@ class Runner:
     def forward(self, x: torch.Tensor) -> None:
         """Enqueues one forward pass of the whole graph for the batch ``x`` [B,C,H,W] (on the device)."""
         L = self.model.layers
+        if self.nhwc:
+            x = x.contiguous(memory_format=torch.channels_last)
         T: Dict[int, torch.Tensor] = {-1: x}
         bufs: Dict[int, torch.Tensor] = {}
         self.dets.reset()
@@ -162,7 +197,10 @@ class Runner:
             elif st.op == "maxpool":
                 dests = self._dest_tensors(bufs, st.dests, l)
                 s = tm.begin()
-                ops.maxpool(T[st.inputs[0]], l.kernel, l.stride, l.padding, out=dests[0])
+                if self.nhwc:
+                    ops.maxpool_nhwc(T[st.inputs[0]], l.kernel, l.stride, l.padding, out=dests[0])
+                else:
+                    ops.maxpool(T[st.inputs[0]], l.kernel, l.stride, l.padding, out=dests[0])
                 self.launches += 1
                 tm.end(s, "maxpool", 4 * (T[st.inputs[0]].numel() + dests[0].numel()))
                 self._extra_copies(dests[0], dests[1:])
@@ -176,7 +214,12 @@ class Runner:
                     rest.append(ts[1:])
                     T[g] = ts[0]
                 s = tm.begin()
-                ops.spp(xin, [L[g].kernel for g in st.spp_layers], firsts)
+                if self.nhwc:
+                    for g, f in zip(st.spp_layers, firsts):
+                        ops.maxpool_nhwc(xin, L[g].kernel, 1, L[g].kernel - 1, out=f)
+                    self.launches += len(firsts) - 1
+                else:
+                    ops.spp(xin, [L[g].kernel for g in st.spp_layers], firsts)
                 self.launches += 1
                 tm.end(s, "spp", 4 * xin.numel() * (1 + len(firsts)))
                 for f, r in zip(firsts, rest):
@@ -184,7 +227,10 @@ class Runner:
             elif st.op == "upsample":
                 dests = self._dest_tensors(bufs, st.dests, l)
                 s = tm.begin()
-                ops.upsample(T[st.inputs[0]], l.stride, l.alpha, out=dests[0])
+                if self.nhwc:
+                    ops.upsample_nhwc(T[st.inputs[0]], l.stride, l.alpha, out=dests[0])
+                else:
+                    ops.upsample(T[st.inputs[0]], l.stride, l.alpha, out=dests[0])
                 self.launches += 1
                 tm.end(s, "upsample", 4 * (T[st.inputs[0]].numel() + dests[0].numel()))
                 self._extra_copies(dests[0], dests[1:])
@@ -192,21 +238,35 @@ class Runner:
             elif st.op == "shortcut":
                 dests = self._dest_tensors(bufs, st.dests, l)
                 s = tm.begin()
-                ops.shortcut(T[st.inputs[0]], T[st.inputs[1]], l.alpha, l.beta, l.activation, out=dests[0],
-                             out2=dests[1] if len(dests) > 1 else None)
+                if self.nhwc:
+                    ops.conv_epilogue_nhwc(T[st.inputs[0]], y=dests[0], y2=dests[1] if len(dests) > 1 else None,
+                                           residual=T[st.inputs[1]], res_alpha=l.alpha, res_beta=l.beta,
+                                           res_act=l.activation)
+                else:
+                    ops.shortcut(T[st.inputs[0]], T[st.inputs[1]], l.alpha, l.beta, l.activation, out=dests[0],
+                                 out2=dests[1] if len(dests) > 1 else None)
                 self.launches += 1
                 tm.end(s, "shortcut", 4 * dests[0].numel() * (2 + min(len(dests), 2)))
                 self._extra_copies(dests[0], dests[2:])
                 T[st.layer] = dests[0]
             elif st.op == "concat":
                 s = tm.begin()
-                T[st.layer] = ops.concat([T[i] for i in st.inputs])
+                if self.nhwc:
+                    out = self._empty((self.batch,) + l.out_shape)
+                    off = 0
+                    for i in st.inputs:
+                        ops.conv_epilogue_nhwc(T[i], y=out[:, off:off + T[i].shape[1]])
+                        off += T[i].shape[1]
+                    self.launches += len(st.inputs) - 1
+                    T[st.layer] = out
+                else:
+                    T[st.layer] = ops.concat([T[i] for i in st.inputs])
                 self.launches += 1
                 tm.end(s, "concat", 8 * T[st.layer].numel())
             elif st.op == "yolo":
                 self._yolo(st, l, T)
             elif st.op == "centernet":
-                xin = T[st.inputs[0]]
+                xin = self._nchw(T[st.inputs[0]]) if self.nhwc else T[st.inputs[0]]
                 cls = l.in_shape[0] - 4
                 s = tm.begin()
                 out = ops.centernet_decode(xin[:, :cls], xin[:, cls:cls + 2], xin[:, cls + 2:], self.threshold,
@@ -218,7 +278,7 @@ class Runner:
                 self.centernet_out.append(out)
                 T[st.layer] = xin
             elif st.op == "softmax":
-                xin = T[st.inputs[0]].contiguous()
+                xin = self._nchw(T[st.inputs[0]])
                 s = tm.begin()
                 T[st.layer] = ops.softmax(xin, max(1, int(l.params.get("groups", 1))),
                                           float(l.params.get("temperature", 1.0)))
@@ -226,7 +286,7 @@ class Runner:
                 tm.end(s, "softmax", 8 * xin.numel())
                 self.outputs[st.layer] = T[st.layer]
             elif st.op == "region":
-                xin = T[st.inputs[0]].contiguous()
+                xin = self._nchw(T[st.inputs[0]])
                 s = tm.begin()
                 T[st.layer] = ops.region_forward(xin, int(l.params.get("num", 1)), int(l.params.get("coords", 4)),
                                                  int(l.params.get("classes", self.model.classes or 20)),
@@ -235,7 +295,7 @@ class Runner:
                 tm.end(s, "region", 8 * xin.numel())
                 self.outputs[st.layer] = T[st.layer]
             elif st.op == "avgpool":
-                xin = T[st.inputs[0]]
+                xin = self._nchw(T[st.inputs[0]])
                 s = tm.begin()
                 T[st.layer] = ops.avgpool(xin)
                 self.launches += 1
@@ -244,7 +304,7 @@ class Runner:
                 # GEMM on cuBLAS as in the reference (include/cuda/ConnLayer.h:170-183), then the conv epilogue
                 # kernel on [B, outputs, 1, 1]: BN inference or bias, activation (:185-217)
                 w = self.w[l.index]
-                xin = T[st.inputs[0]].reshape(self.batch, -1)
+                xin = self._nchw(T[st.inputs[0]]).reshape(self.batch, -1)
                 s = tm.begin()
                 raw = F.linear(xin, w["weights"]).reshape(self.batch, l.filters, 1, 1)
                 tm.end(s, "gemm(cublas)", 0)
@@ -255,7 +315,7 @@ class Runner:
                 self.launches += 1
                 tm.end(s, "epilogue", 8 * raw.numel())
             elif st.op == "detection":
-                xin = T[st.inputs[0]].contiguous()
+                xin = self._nchw(T[st.inputs[0]])
                 s = tm.begin()
                 ops.detect_decode(xin, int(l.params.get("side", 7)), int(l.params.get("num", 1)),
                                   self.model.classes, self.threshold, self.dets,
@@ -282,16 +342,20 @@ class Runner:
     def _conv(self, st: graph.Step, l: graph.Layer, T, bufs) -> None:
         w = self.w[l.index]
         xin = T[st.inputs[0]]
-        if not xin.is_contiguous():
+        if not xin.is_contiguous(memory_format=torch.channels_last if self.nhwc else torch.contiguous_format):
             self.contiguous_copies += 1
         tm = self.timer
         s = tm.begin()
         raw = F.conv2d(xin, w["weights"], None, l.stride, l.padding, l.dilation, l.groups)
         tm.end(s, "conv(cudnn)", 0)
+        if self.nhwc and not raw.is_contiguous(memory_format=torch.channels_last):
+            raw = raw.contiguous(memory_format=torch.channels_last)      # 1-pixel or 1-channel outputs only
         if st.head_raw:
             T[l.index] = raw                 # bias + activation are applied inside the YOLO decode
             return
         n = raw.numel()
+        if self.nhwc:
+            return self._conv_epilogue_nhwc(st, l, T, bufs, raw, w)
         bn = dict(gamma=w["scales"], beta=w["biases"], mean=w["rolling_mean"], var=w["rolling_var"],
                   eps_mode=self.eps_mode) if l.batch_norm else dict(bias=w["biases"])
         if st.fused_pool is not None:
@@ -323,8 +387,50 @@ class Runner:
         self._extra_copies(dests[0], dests[2:])
         T[out_layer.index] = dests[0]
 
+    def _conv_epilogue_nhwc(self, st: graph.Step, l: graph.Layer, T, bufs, raw: torch.Tensor, w) -> None:
+        """The conv step's epilogue on channels-last tensors.  A folded 2x2 max pool runs as its own launch
+        behind the epilogue here (the single-pass form exists for NCHW only)."""
+        tm = self.timer
+        n = raw.numel()
+        if st.fused_pool is not None:
+            pl = self.model.layers[st.fused_pool]
+            pd = self._dest_tensors(bufs, st.pool_dests, pl)
+            full = self._dest_tensors(bufs, st.dests, l, dense=raw) if st.keep_full else [raw]
+            s = tm.begin()
+            ops.conv_epilogue_nhwc(raw, y=full[0], y2=full[1] if len(full) > 1 else None, a=w["a"], b=w["b"],
+                                   act=l.activation)
+            self.launches += 1
+            tm.end(s, "epilogue", 4 * n * (1 + min(len(full), 2)))
+            s = tm.begin()
+            ops.maxpool_nhwc(full[0], 2, 2, pl.padding, out=pd[0])
+            self.launches += 1
+            tm.end(s, "maxpool", 4 * n + 4 * pd[0].numel())
+            self._extra_copies(pd[0], pd[1:])
+            T[st.fused_pool] = pd[0]
+            if st.keep_full:
+                self._extra_copies(full[0], full[2:])
+                T[l.index] = full[0]
+            return
+        out_layer = self.model.layers[st.fused_shortcut] if st.fused_shortcut is not None else l
+        dests = self._dest_tensors(bufs, st.dests, out_layer, dense=raw)
+        kw = {}
+        if st.fused_shortcut is not None:
+            kw = dict(residual=T[st.inputs[1]], res_alpha=out_layer.alpha, res_beta=out_layer.beta,
+                      res_act=out_layer.activation)
+        s = tm.begin()
+        ops.conv_epilogue_nhwc(raw, y=dests[0], y2=dests[1] if len(dests) > 1 else None, a=w["a"], b=w["b"],
+                               act=l.activation, **kw)
+        self.launches += 1
+        tm.end(s, "epilogue+shortcut" if kw else "epilogue", 4 * n * (1 + min(len(dests), 2) + (1 if kw else 0)))
+        self._extra_copies(dests[0], dests[2:])
+        T[out_layer.index] = dests[0]
+
     def _yolo(self, st: graph.Step, l: graph.Layer, T) -> None:
         xin = T[st.inputs[0]]
+        if self.nhwc:
+            s = self.timer.begin()
+            xin = self._nchw(xin)
+            self.timer.end(s, "head->nchw", 8 * xin.numel())
         mask = [int(m) for m in l.params["mask"]]
         anchors = [int(a) for a in l.params["anchors"]]
         classes = l.in_shape[0] // len(mask) - 5

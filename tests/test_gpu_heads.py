@@ -415,7 +415,10 @@ def test_detect_decode_matches_oracle(cuda, oracle, B, side, num, classes, squar
     ops.detect_decode(dev(pred, cuda), side, num, classes, thr, buf, squared=squared)
     got, n = buf.to_host()
     assert n == total
-    dets_equal(got, ref)
+    # classes, order and probabilities are exact.  With `sqrt` the host squares widths with std::pow(v, 2) =
+    # glibc's powf, which is within one ulp of v*v but not always equal to it (0.06 % of values differ in the
+    # last bit); the device multiplies.  Boxes are therefore compared to 1e-6.
+    dets_equal(got, ref, box_tol=1e-6 if squared else 0.0)
     small = ops.DetectionBuffer(max(1, total // 2), cuda)
     ops.detect_decode(dev(pred, cuda), side, num, classes, thr, small, squared=squared, batch_id_offset=4)
     got, n = small.to_host()
