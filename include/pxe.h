@@ -342,6 +342,11 @@ typedef struct pxe_epilogue_nhwc_desc {
     int act;                      /* pxe_activation */
     float res_alpha, res_beta;    /* y = res_act(res_alpha * act(a*x+b) + res_beta * residual) */
     int res_act;
+    /* optional folded 2x2 stride-2 max pool (as in pxe_epilogue_desc): needs the geometry as well */
+    int pool_kernel, pool_stride, pool_padding;   /* 0 = none; 2 / 2 / 0|1 */
+    int batch, height, width;                     /* batch * height * width == pixels */
+    float* y_pool;                                /* [batch, OH, OW, channels]; y may then be NULL */
+    long long y_pool_pixel_stride;
 } pxe_epilogue_nhwc_desc;
 
 /* The fused conv epilogue of pxe_conv_epilogue for NHWC tensors; with a = b = NULL and act linear it is

@@ -54,7 +54,9 @@ class EpilogueNhwcDesc(C.Structure):
                 ("x_pixel_stride", C.c_longlong), ("y_pixel_stride", C.c_longlong), ("y2_pixel_stride", C.c_longlong),
                 ("residual_pixel_stride", C.c_longlong), ("pixels", C.c_longlong), ("channels", C.c_int),
                 ("a", C.c_void_p), ("b", C.c_void_p), ("act", C.c_int), ("res_alpha", C.c_float), ("res_beta", C.c_float),
-                ("res_act", C.c_int)]
+                ("res_act", C.c_int), ("pool_kernel", C.c_int), ("pool_stride", C.c_int), ("pool_padding", C.c_int),
+                ("batch", C.c_int), ("height", C.c_int), ("width", C.c_int), ("y_pool", C.c_void_p),
+                ("y_pool_pixel_stride", C.c_longlong)]
 
 
 class YoloDecodeDesc(C.Structure):

@@ -160,6 +160,85 @@ int dispatch_nhwc(cudaStream_t s, NhwcParams& p, long long n, bool vec)
     return res ? launch_nhwc<ACT, false, true>(s, p, n, vec) : launch_nhwc<ACT, false, false>(s, p, n, vec);
 }
 
+// Epilogue + 2x2 stride-2 max pool, NHWC: the four taps of a window are four pixels with the same channel
+// vector, so a thread handles one channel vector of one pooled pixel -- four loads, one pooled store and
+// (when the full-resolution tensor is wanted too) four stores.  Window origin (2*oh, 2*ow), taps past the
+// edge skipped, first maximum in (ky, kx) order wins (src/MaxPoolKernels.cu:26-40).
+struct NhwcPoolParams {
+    NhwcParams e;
+    float* ypool; long long pps;
+    int H, W, OH, OW;
+    FastDiv div_ow, div_oh;
+};
+
+template <int ACT, bool AFFINE, int VW>
+__global__ void __launch_bounds__(kThreads, 4)
+epilogue_pool_nhwc_kernel(const NhwcPoolParams q)
+{
+    const NhwcParams& p = q.e;
+    for (uint32_t u = blockIdx.x * kThreads + threadIdx.x; u < p.units; u += gridDim.x * kThreads) {
+        uint32_t opix, cv, bh, ow, b, oh;
+        p.div_cv.divmod(u, opix, cv);
+        q.div_ow.divmod(opix, bh, ow);
+        q.div_oh.divmod(bh, b, oh);
+        const uint32_t c = cv * VW;
+        const int iy = 2 * (int)oh, ix = 2 * (int)ow;
+        const bool row1 = iy + 1 < q.H, col1 = ix + 1 < q.W;
+        const long long pix00 = ((long long)b * q.H + iy) * q.W + ix;
+        const long long tap[4] = {pix00, pix00 + 1, pix00 + q.W, pix00 + q.W + 1};
+        const bool on[4] = {true, col1, row1, row1 && col1};
+        float v[4][VW];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            if (!on[t]) continue;
+            const float* src = p.x + tap[t] * p.xps + c;
+            if (VW == 4) {
+                const float4 f = *reinterpret_cast<const float4*>(src);
+                v[t][0] = f.x; v[t][1] = f.y; v[t][2] = f.z; v[t][3] = f.w;
+            } else {
+                v[t][0] = src[0];
+            }
+        }
+        float ca[VW], cb[VW];
+#pragma unroll
+        for (int j = 0; j < VW; ++j) { ca[j] = AFFINE ? p.a[c + j] : 1.0f; cb[j] = AFFINE ? p.b[c + j] : 0.0f; }
+        float m[VW];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            if (!on[t]) continue;
+#pragma unroll
+            for (int j = 0; j < VW; ++j) {
+                v[t][j] = nhwc_apply<ACT, AFFINE>(v[t][j], ca[j], cb[j]);
+                m[j] = (t == 0 || v[t][j] > m[j]) ? v[t][j] : m[j];
+            }
+            if (p.y) {
+                float* dst = p.y + tap[t] * p.yps + c;
+                if (VW == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[t][0], v[t][1], v[t][2], v[t][3]);
+                else dst[0] = v[t][0];
+            }
+        }
+        float* dst = q.ypool + (long long)opix * q.pps + c;
+        if (VW == 4) *reinterpret_cast<float4*>(dst) = make_float4(m[0], m[1], m[2], m[3]);
+        else dst[0] = m[0];
+    }
+}
+
+template <int ACT>
+int launch_pool_nhwc(cudaStream_t s, NhwcPoolParams& q, bool vec, int sm_count)
+{
+    const bool affine = q.e.a != nullptr;
+    const unsigned grid = grid_for(q.e.units, kThreads, sm_count, 32);
+    if (vec) {
+        if (affine) epilogue_pool_nhwc_kernel<ACT, true, 4><<<grid, kThreads, 0, s>>>(q);
+        else epilogue_pool_nhwc_kernel<ACT, false, 4><<<grid, kThreads, 0, s>>>(q);
+    } else {
+        if (affine) epilogue_pool_nhwc_kernel<ACT, true, 1><<<grid, kThreads, 0, s>>>(q);
+        else epilogue_pool_nhwc_kernel<ACT, false, 1><<<grid, kThreads, 0, s>>>(q);
+    }
+    PXE_LAUNCH_OK("epilogue_pool_nhwc_kernel");
+    return PXE_OK;
+}
+
 // Nearest-neighbour upsample (src/UpsampleKernels.cu:25-63): thread per input vector, stride*stride stores.
 template <int VW>
 __global__ void __launch_bounds__(kThreads)
@@ -270,7 +349,7 @@ extern "C" int pxe_conv_epilogue_nhwc(pxe_stream_t stream, const pxe_epilogue_nh
 {
     PXE_REQUIRE(dp != nullptr, "conv_epilogue_nhwc: null descriptor");
     const pxe_epilogue_nhwc_desc& d = *dp;
-    PXE_REQUIRE(d.x && d.y, "conv_epilogue_nhwc: x or y is null");
+    PXE_REQUIRE(d.x && (d.y || d.pool_kernel), "conv_epilogue_nhwc: x or y is null");
     PXE_REQUIRE(d.pixels > 0 && d.channels > 0, "conv_epilogue_nhwc: non-positive shape");
     PXE_REQUIRE(valid_activation(d.act), "conv_epilogue_nhwc: unknown activation %d", d.act);
     PXE_REQUIRE((d.a == nullptr) == (d.b == nullptr), "conv_epilogue_nhwc: a and b go together");
@@ -287,6 +366,48 @@ extern "C" int pxe_conv_epilogue_nhwc(pxe_stream_t stream, const pxe_epilogue_nh
     const bool vec = C % 4 == 0 && ok16(d.x, p.xps) && ok16(d.y, p.yps) && ok16(d.y2, p.y2ps) && ok16(d.residual, p.rps)
                      && ok16(d.a, 4) && ok16(d.b, 4);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (d.pool_kernel) {
+        PXE_REQUIRE(d.y_pool != nullptr, "conv_epilogue_nhwc: pooling requested but y_pool is null");
+        if (d.pool_kernel != 2 || d.pool_stride != 2 || d.pool_padding < 0 || d.pool_padding > 1)
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue_nhwc: fused pooling supports kernel 2 / stride 2 / padding 0|1 only (got %d/%d/%d)",
+                             d.pool_kernel, d.pool_stride, d.pool_padding);
+        if (d.residual || d.y2)
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue_nhwc: fused pooling cannot be combined with residual or y2");
+        PXE_REQUIRE(d.batch > 0 && d.height > 0 && d.width > 0 && (long long)d.batch * d.height * d.width == d.pixels,
+                    "conv_epilogue_nhwc: batch * height * width must equal pixels when pooling");
+        NhwcPoolParams q{};
+        q.e = p;
+        q.e.x = d.x; q.e.y = d.y;
+        q.H = d.height; q.W = d.width;
+        q.OH = pxe_maxpool_out_dim(d.height, 2, 2, d.pool_padding);
+        q.OW = pxe_maxpool_out_dim(d.width, 2, 2, d.pool_padding);
+        PXE_REQUIRE(q.OH > 0 && q.OW > 0, "conv_epilogue_nhwc: empty pooled output");
+        if (d.y && (2 * q.OH < d.height || 2 * q.OW < d.width))
+            return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue_nhwc: padding 0 with an odd extent leaves full-resolution rows uncovered");
+        q.ypool = d.y_pool; q.pps = dense_or(d.y_pool_pixel_stride, C);
+        PXE_REQUIRE(q.pps >= C, "conv_epilogue_nhwc: y_pool pixel stride smaller than the channel count");
+        const bool pvec = vec && aligned16(d.y_pool) && q.pps % 4 == 0;
+        const int vw = pvec ? 4 : 1;
+        const long long units = (long long)d.batch * q.OH * q.OW * (C / vw);
+        PXE_REQUIRE(units < (1LL << 32), "conv_epilogue_nhwc: pooled tensor too large for one launch");
+        q.e.units = (uint32_t)units;
+        q.e.div_cv = FastDiv((uint32_t)(C / vw));
+        q.div_ow = FastDiv((uint32_t)q.OW); q.div_oh = FastDiv((uint32_t)q.OH);
+        DeviceInfo di;
+        int rc = device_info(&di);
+        if (rc != PXE_OK) return rc;
+        switch (d.act) {
+        case PXE_ACT_LEAKY: return launch_pool_nhwc<PXE_ACT_LEAKY>(s, q, pvec, di.sm_count);
+        case PXE_ACT_LINEAR: return launch_pool_nhwc<PXE_ACT_LINEAR>(s, q, pvec, di.sm_count);
+        case PXE_ACT_LOGGY: return launch_pool_nhwc<PXE_ACT_LOGGY>(s, q, pvec, di.sm_count);
+        case PXE_ACT_LOGISTIC: return launch_pool_nhwc<PXE_ACT_LOGISTIC>(s, q, pvec, di.sm_count);
+        case PXE_ACT_MISH: return launch_pool_nhwc<PXE_ACT_MISH>(s, q, pvec, di.sm_count);
+        case PXE_ACT_RELU: return launch_pool_nhwc<PXE_ACT_RELU>(s, q, pvec, di.sm_count);
+        case PXE_ACT_SOFTPLUS: return launch_pool_nhwc<PXE_ACT_SOFTPLUS>(s, q, pvec, di.sm_count);
+        case PXE_ACT_SWISH: return launch_pool_nhwc<PXE_ACT_SWISH>(s, q, pvec, di.sm_count);
+        default: return launch_pool_nhwc<PXE_ACT_TANH>(s, q, pvec, di.sm_count);
+        }
+    }
     // unit indices are 32-bit: at most 2^31 elements per launch, larger tensors go in slices of whole pixels
     const long long per = ((1LL << 31) / C) > 0 ? ((1LL << 31) / C) : 1;
     for (long long p0 = 0; p0 < d.pixels; p0 += per) {

@@ -460,15 +460,22 @@ def fold_bn(channels: int, device, *, gamma=None, beta=None, mean=None, var=None
 def conv_epilogue_nhwc(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None,
                        a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None, act="linear",
                        residual: Optional[torch.Tensor] = None, res_alpha: float = 1.0, res_beta: float = 1.0,
-                       res_act="linear") -> torch.Tensor:
-    """Fused epilogue on channels-last tensors; ``y=None`` works in place."""
+                       res_act="linear", pool: Optional[Sequence[int]] = None, y_pool: Optional[torch.Tensor] = None):
+    """Fused epilogue on channels-last tensors; ``y=None`` works in place.  With ``pool=(2, 2, padding)`` the
+    2x2 max pool is folded in: returns ``(y, y_pool)``, and ``y=False`` skips the full-resolution output."""
     xp, xps = _nhwc(x, "x")
     B, Cc, H, W = x.shape
+    want_full = y is not False
     if y is None:
         y = x
     d = capi.EpilogueNhwcDesc()
     d.x, d.x_pixel_stride = xp, xps
-    d.y, d.y_pixel_stride = _nhwc(y, "y")
+    if want_full:
+        d.y, d.y_pixel_stride = _nhwc(y, "y")
+    else:
+        if pool is None:
+            raise ValueError("y=False needs pool")
+        y = None
     for t, n in ((y, "y"), (y2, "y2"), (residual, "residual")):
         if t is not None and tuple(t.shape) != (B, Cc, H, W):
             raise ValueError(f"{n} has shape {tuple(t.shape)}, expected {(B, Cc, H, W)}")
@@ -479,8 +486,18 @@ def conv_epilogue_nhwc(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2:
     d.pixels, d.channels = B * H * W, Cc
     d.a, d.b = _vec(a, Cc, "a"), _vec(b, Cc, "b")
     d.act, d.res_alpha, d.res_beta, d.res_act = _act(act), res_alpha, res_beta, _act(res_act)
+    if pool is not None:
+        k, st, pad = pool
+        d.pool_kernel, d.pool_stride, d.pool_padding = k, st, pad
+        d.batch, d.height, d.width = B, H, W
+        oh, ow = maxpool_out_dim(H, k, st, pad), maxpool_out_dim(W, k, st, pad)
+        if y_pool is None:
+            y_pool = empty_nhwc((B, Cc, oh, ow), x.device)
+        elif tuple(y_pool.shape) != (B, Cc, oh, ow):
+            raise ValueError(f"y_pool has shape {tuple(y_pool.shape)}, expected {(B, Cc, oh, ow)}")
+        d.y_pool, d.y_pool_pixel_stride = _nhwc(y_pool, "y_pool")
     capi.check(capi.lib().pxe_conv_epilogue_nhwc(_stream(), C.byref(d)))
-    return y
+    return (y, y_pool) if pool is not None else y
 
 
 def upsample_nhwc(x: torch.Tensor, stride: int, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:

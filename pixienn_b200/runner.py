@@ -388,27 +388,22 @@ class Runner:
         T[out_layer.index] = dests[0]
 
     def _conv_epilogue_nhwc(self, st: graph.Step, l: graph.Layer, T, bufs, raw: torch.Tensor, w) -> None:
-        """The conv step's epilogue on channels-last tensors.  A folded 2x2 max pool runs as its own launch
-        behind the epilogue here (the single-pass form exists for NCHW only)."""
+        """The conv step's epilogue on channels-last tensors."""
         tm = self.timer
         n = raw.numel()
         if st.fused_pool is not None:
             pl = self.model.layers[st.fused_pool]
             pd = self._dest_tensors(bufs, st.pool_dests, pl)
-            full = self._dest_tensors(bufs, st.dests, l, dense=raw) if st.keep_full else [raw]
+            full = self._dest_tensors(bufs, st.dests, l, dense=raw) if st.keep_full else []
             s = tm.begin()
-            ops.conv_epilogue_nhwc(raw, y=full[0], y2=full[1] if len(full) > 1 else None, a=w["a"], b=w["b"],
-                                   act=l.activation)
+            ops.conv_epilogue_nhwc(raw, y=full[0] if full else False, a=w["a"], b=w["b"], act=l.activation,
+                                   pool=(2, 2, pl.padding), y_pool=pd[0])
             self.launches += 1
-            tm.end(s, "epilogue", 4 * n * (1 + min(len(full), 2)))
-            s = tm.begin()
-            ops.maxpool_nhwc(full[0], 2, 2, pl.padding, out=pd[0])
-            self.launches += 1
-            tm.end(s, "maxpool", 4 * n + 4 * pd[0].numel())
+            tm.end(s, "epilogue+pool", 4 * n + 4 * pd[0].numel() + (4 * n if full else 0))
             self._extra_copies(pd[0], pd[1:])
             T[st.fused_pool] = pd[0]
-            if st.keep_full:
-                self._extra_copies(full[0], full[2:])
+            if full:
+                self._extra_copies(full[0], full[1:])
                 T[l.index] = full[0]
             return
         out_layer = self.model.layers[st.fused_shortcut] if st.fused_shortcut is not None else l

@@ -66,6 +66,31 @@ def test_epilogue_nhwc_residual_and_slot_stores(cuda):
     same(ops.conv_epilogue_nhwc(nhwc(x3.clone()), a=a_, b=b_, act="mish"), ops.conv_epilogue(x3.clone(), bias=b3, act="mish"))
 
 
+@pytest.mark.parametrize("shape", [(2, 8, 16, 16), (2, 16, 13, 13), (1, 5, 26, 26), (1, 12, 7, 12), (2, 32, 52, 52)])
+@pytest.mark.parametrize("act", ["leaky", "mish"])
+@pytest.mark.parametrize("keep_full", [False, True])
+def test_epilogue_nhwc_with_folded_pool(cuda, shape, act, keep_full):
+    """Pooled (and full-resolution) outputs equal the NCHW fused kernel's, element for element."""
+    B, C, H, W = shape
+    x = dev(synth.normal(83, f"xp{shape}", shape), cuda)
+    (g, b, m, v), dp = bn(84, f"bnp{shape}", C, cuda)
+    kw = dict(gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3])
+    wy, wp = ops.conv_epilogue(x.clone(), y=None if keep_full else False, act=act, pool=(2, 2, 1), **kw)
+    fa, fb = ops.fold_bn(C, cuda, **kw)
+    xin = nhwc(x.clone())
+    gy, gp = ops.conv_epilogue_nhwc(xin, y=None if keep_full else False, a=fa, b=fb, act=act, pool=(2, 2, 1))
+    same(gp, wp)
+    if keep_full:
+        same(gy, wy)
+    else:
+        assert gy is None and torch.equal(xin, nhwc(x))
+    wide = ops.empty_nhwc((B, C + 4, wp.shape[2], wp.shape[3]), cuda)
+    wide.fill_(1.5)
+    ops.conv_epilogue_nhwc(nhwc(x.clone()), y=False, a=fa, b=fb, act=act, pool=(2, 2, 1), y_pool=wide[:, 4:])
+    same(wide[:, 4:], wp)
+    assert (wide[:, :4] == 1.5).all()
+
+
 @pytest.mark.parametrize("shape,stride", [((2, 8, 13, 13), 2), ((1, 6, 5, 9), 3), ((2, 256, 19, 19), 2)])
 def test_upsample_nhwc(cuda, shape, stride):
     x = dev(synth.normal(79, f"up{shape}", shape), cuda)
