@@ -381,6 +381,10 @@ def run_sweep(args):
         g, b, m, v = (torch.from_numpy(t).to(dev) for t in synth.bn_params(SEED, f"sweep{C}", C))
         bias = torch.from_numpy(synth.normal(SEED, f"sweepb{C}", C, 0, 0.1)).to(dev)
         base = torch.randn((B, C, H, W), device=dev, generator=torch.Generator(dev).manual_seed(SEED))
+        nhwc = args.layout == "nhwc"
+        if nhwc:                      # the same cells on channels-last tensors, coefficients folded once
+            base = base.contiguous(memory_format=torch.channels_last)
+            fa, fb = ops.fold_bn(C, dev, gamma=g, beta=b, mean=m, var=v, bias=bias)
         xs = [base.clone() for _ in range(sets)]
         frm = [base.clone() for _ in range(sets)] if args.sweep_residual else None
 
@@ -413,9 +417,18 @@ def run_sweep(args):
                     continue
                 oh = ops.maxpool_out_dim(H, 2, 2, 1)
                 yps = [torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) for _ in range(sets)] if pool else None
+                if nhwc and pool:
+                    yps = [t.contiguous(memory_format=torch.channels_last) for t in yps]
 
                 def call(i):
-                    if pool:
+                    if nhwc:
+                        if pool:
+                            ops.conv_epilogue_nhwc(xs[i % sets], y=False, a=fa, b=fb, act=act, pool=(2, 2, 1), y_pool=yps[i % sets])
+                        elif frm is not None:
+                            ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act, residual=frm[i % sets], res_act="linear")
+                        else:
+                            ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act)
+                    elif pool:
                         ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
                                           pool=(2, 2, 1), y_pool=yps[i % sets])
                     elif frm is not None:      # conv epilogue + the shortcut layer that follows it: 12 B / element
@@ -438,7 +451,7 @@ def run_sweep(args):
                       "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
                       "dtype": "f32", "data": "synthetic", "peak": peak, "peak_source": peak_src,
                       "frac_min": min(fr), "frac_median": statistics.median(fr), "frac_max": max(fr),
-                      "config": {"workload": "isolated fused epilogue sweep", "l2": "rotating input sets > 400 MB", "timing": "CUDA events around a CUDA-graph replay of one launch per input set"},
+                      "config": {"workload": f"isolated fused epilogue sweep, {args.layout.upper()}", "l2": "rotating input sets > 400 MB", "timing": "CUDA events around a CUDA-graph replay of one launch per input set"},
                       "cells": rows}), flush=True)
 
 
