@@ -1,0 +1,36 @@
+"""The boundary from the reference's own languages: the public headers compile as strict C99, and a C++
+program that includes them (and the px:: declarations of the link-compatible tier) links against
+libpxe.so and runs the host-only entry points."""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+from pixienn_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+INC = os.path.join(ROOT, "include")
+SRC = os.path.join(ROOT, "tests", "cpp")
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="gcc not found")
+def test_headers_compile_as_c99(tmp_path):
+    obj = tmp_path / "header_is_c.o"
+    r = subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Wextra", "-Werror", "-I", INC, "-c",
+                        os.path.join(SRC, "header_is_c.c"), "-o", str(obj)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="g++ not found")
+def test_cpp_client_links_and_runs(tmp_path):
+    capi.lib()                                            # the library exists (raises with build instructions otherwise)
+    libdir = os.path.dirname(capi.LIB_PATH)
+    exe = tmp_path / "link_client"
+    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-I", INC, os.path.join(SRC, "link_client.cpp"),
+                        "-L", libdir, "-lpxe", f"-Wl,-rpath,{libdir}", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
+    assert "steps=4 fused_pool=1 fused_shortcut=1 raw_heads=1" in run.stdout
+    assert "nms kept=2" in run.stdout and "px:: symbols resolved" in run.stdout
