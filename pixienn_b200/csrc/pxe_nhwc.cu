@@ -61,14 +61,17 @@ __device__ __forceinline__ float nhwc_apply(float v, float a, float b)
 
 // VW = 4: C % 4 == 0 and every pointer / stride keeps 16-byte alignment; VW = 1: anything.
 template <int ACT, bool AFFINE, bool RES, int VW>
-__global__ void __launch_bounds__(kThreads, RES ? 4 : 5)
+__global__ void __launch_bounds__(kThreads, 5)
 epilogue_nhwc_kernel(const NhwcParams p)
 {
     const uint32_t lo = blockIdx.x * p.chunk;
     if (lo >= p.units) return;
     uint32_t hi = lo + p.chunk;
     if (hi > p.units) hi = p.units;
-    const uint32_t step = kThreads * kUnroll;
+    // with a residual every vector holds two loads in flight: half the unroll keeps the bytes in flight per
+    // thread (64) and the register count of the plain form, so that more blocks are resident
+    constexpr int UN = RES ? kUnroll / 2 : kUnroll;
+    const uint32_t step = kThreads * UN;
     // When the vectors of one pixel divide the block size (every power-of-two channel count up to 1024), a
     // thread meets the same four channels in every vector it handles: its coefficients are loaded once.
     // p.chunk and step are multiples of kThreads, so u % cv == threadIdx.x % cv throughout.
@@ -81,10 +84,10 @@ epilogue_nhwc_kernel(const NhwcParams p)
     }
     for (uint32_t r0 = lo; r0 < hi; r0 += step) {
         if (VW == 4) {
-            float4 v[kUnroll], r[kUnroll];
-            uint32_t pix[kUnroll], ch[kUnroll];
+            float4 v[UN], r[UN];
+            uint32_t pix[UN], ch[UN];
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = r0 + threadIdx.x + k * kThreads;
                 if (u < hi) {
                     uint32_t cv;
@@ -95,7 +98,7 @@ epilogue_nhwc_kernel(const NhwcParams p)
                 }
             }
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = r0 + threadIdx.x + k * kThreads;
                 if (u < hi) {
                     float4 ca = fa, cb = fb;
@@ -121,7 +124,7 @@ epilogue_nhwc_kernel(const NhwcParams p)
             }
         } else {
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = r0 + threadIdx.x + k * kThreads;
                 if (u < hi) {
                     uint32_t pix, c;
