@@ -105,7 +105,7 @@ __device__ __forceinline__ float residual_one(float v, float r, const EpiParams&
 // MODE 2: scalar, anything goes.
 // ---------------------------------------------------------------------------------------------
 template <int ACT, bool AFFINE, bool RES, int MODE>
-__global__ void __launch_bounds__(kThreads, RES ? 4 : 5)
+__global__ void __launch_bounds__(kThreads, 5)
 epilogue_kernel(const EpiParams p)
 {
     extern __shared__ PlaneEntry tab[];
@@ -128,17 +128,20 @@ epilogue_kernel(const EpiParams p)
     // Every thread runs the same number of rounds (the barrier below sits inside the loop).  The
     // first round issues its global loads BEFORE the coefficient table is built, so the table's own
     // parameter loads and the square roots overlap the first wave of data instead of preceding it.
-    const uint32_t step = kThreads * kUnroll;
+    // With a residual every vector has two loads in flight: half the unroll keeps the bytes in flight per
+    // thread (64) and the registers of the plain form, so that five blocks stay resident per SM.
+    constexpr int UN = RES ? kUnroll / 2 : kUnroll;
+    const uint32_t step = kThreads * UN;
     const uint32_t rounds = (hi - lo + step - 1) / step;
     for (uint32_t rd = 0; rd < rounds; ++rd) {
         const uint32_t base = lo + rd * step + threadIdx.x;
         if (MODE == 0) {
-            float4 v[kUnroll];
-            float4 r[kUnroll];
-            uint32_t off[kUnroll];          // offset inside one image: C*H*W < 2^31
-            uint32_t pl[kUnroll], img[kUnroll];
+            float4 v[UN];
+            float4 r[UN];
+            uint32_t off[UN];          // offset inside one image: C*H*W < 2^31
+            uint32_t pl[UN], img[UN];
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     uint32_t q, rem, c;
@@ -155,7 +158,7 @@ epilogue_kernel(const EpiParams p)
                 __syncthreads();
             }
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     const PlaneEntry t = tab[pl[k]];
@@ -176,10 +179,10 @@ epilogue_kernel(const EpiParams p)
             }
         } else if (MODE == 1) {
             // dense tensors: offset == element index
-            float4 v[kUnroll];
-            float4 r[kUnroll];
+            float4 v[UN];
+            float4 r[UN];
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     v[k] = *reinterpret_cast<const float4*>(p.x + (size_t)u * 4);
@@ -191,7 +194,7 @@ epilogue_kernel(const EpiParams p)
                 __syncthreads();
             }
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     uint32_t q, rem;
@@ -215,11 +218,11 @@ epilogue_kernel(const EpiParams p)
                 }
             }
         } else {
-            float v[kUnroll], r[kUnroll];
-            uint32_t off[kUnroll];
-            uint32_t pl[kUnroll], img[kUnroll];
+            float v[UN], r[UN];
+            uint32_t off[UN];
+            uint32_t pl[UN], img[UN];
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     uint32_t q, rem, c;
@@ -236,7 +239,7 @@ epilogue_kernel(const EpiParams p)
                 __syncthreads();
             }
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k) {
+            for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
                     float o = apply_one<ACT, AFFINE>(v[k], tab[pl[k]]);
