@@ -206,3 +206,36 @@ def test_region_forward_layout(oracle):
             np.testing.assert_allclose(out[cell, n, 4], 1 / (1 + np.exp(-src[4])), rtol=1e-6)
             e = np.exp(src[5:] - src[5:].max())
             np.testing.assert_allclose(out[cell, n, 5:], e / e.sum(), rtol=1e-6)
+
+
+def test_avgpool_is_the_plane_mean_in_index_order(oracle):
+    """AvgPoolLayer::forward (include/AvgPoolLayer.h:66-87): running float sum over the plane, one division."""
+    x = np.arange(2 * 3 * 2 * 2, dtype=np.float32).reshape(2, 3, 2, 2)
+    out = oracle.avgpool(x)
+    assert out.shape == (2, 3, 1, 1)
+    assert np.array_equal(out.ravel(), np.array([1.5, 5.5, 9.5, 13.5, 17.5, 21.5], np.float32))
+    # order matters in float: 1e8 + 1 - 1e8 summed left to right loses the 1
+    y = np.array([1e8, 1.0, -1e8, 0.0], np.float32).reshape(1, 1, 2, 2)
+    assert oracle.avgpool(y).ravel()[0] == 0.0
+
+
+def test_yolov1_detection_decode_known_answer(oracle):
+    """DetectLayer::addDetects (include/DetectLayer.h:166-209) on a 2x2 grid, one box per cell, two classes:
+    cell 3 (row 1, col 1) has scale 0.8 and class scores (0.25, 0.5); squared sizes."""
+    side, num, classes = 2, 1, 2
+    loc = side * side
+    pred = np.zeros(loc * (classes + num * 5), np.float32)
+    pred[3 * classes + 0], pred[3 * classes + 1] = 0.25, 0.5
+    pred[loc * classes + 3] = 0.8                                  # scale of cell 3
+    pred[loc * classes + 1] = -0.5                                 # a negative scale emits nothing
+    box = loc * (classes + num) + 3 * 4
+    pred[box:box + 4] = [0.5, 0.25, 0.5, 0.4]
+    dets, n = oracle.detect_decode(pred[None], side, num, classes, 0.3, squared=True)
+    assert n == 1
+    d = dets[0]
+    assert d["class_id"] == 1 and d["batch_id"] == 0 and d["source"] == 3
+    assert abs(d["prob"] - 0.4) < 1e-7
+    w, h = 0.25, 0.16000001
+    assert abs(d["w"] - w) < 1e-6 and abs(d["h"] - h) < 1e-6
+    assert abs(d["x"] - ((0.5 + 1) / 2 - w / 2)) < 1e-6 and abs(d["y"] - ((0.25 + 1) / 2 - h / 2)) < 1e-6
+    assert oracle.detect_decode(pred[None], side, num, classes, 0.41, squared=True)[1] == 0
