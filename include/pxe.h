@@ -387,6 +387,27 @@ PXE_API int pxe_detect_decode(pxe_stream_t stream, const float* pred, long long 
                               float threshold, pxe_detection* dets, long long capacity, long long* count,
                               int batch_id_offset);
 
+/* SoftmaxLayer::addDetects (include/SoftmaxLayer.h:182-196): one record per image whose largest class
+ * probability (the first maximum, std::max_element) is >= threshold: box {0, 0, width, height}, that class and
+ * probability.  probs: the output of pxe_softmax, [batch][classes] with batch stride (0 = classes).  Records
+ * are appended behind *count (device), images in order. */
+PXE_API int pxe_softmax_decode(pxe_stream_t stream, const float* probs, long long probs_batch_stride, int batch,
+                               int classes, float width, float height, float threshold, pxe_detection* dets,
+                               long long capacity, long long* count, int batch_id_offset);
+
+/* RegionLayer::addDetects (include/RegionLayer.h:355-395, box from lightBox, src/DarkBox.cpp:191-202) on the
+ * output of pxe_region_forward: for box (cell, n) with scale = its objectness entry, every class j with
+ * scale * class_j >= threshold is one record {x - w/2, y - h/2, w, h} * image size, x = (col + logistic(tx)) / W,
+ * w = exp(tw) * anchors[2n] / W.  anchors: 2*num floats on the HOST (the layer's `anchors`, at most 32 boxes per
+ * cell).  Order: image, cell, box, class; records are appended behind *count (device) as in pxe_yolo_decode.
+ * per_image = 0 reproduces the reference exactly: it indexes the predictions without the image's offset
+ * (RegionLayer.h:363-369), so every image of a batch decodes image 0's boxes; per_image = 1 decodes each
+ * image's own. */
+PXE_API int pxe_region_decode(pxe_stream_t stream, const float* pred, int batch, int width, int height, int num,
+                              int coords, int classes, const float* anchors, int per_image, float image_width,
+                              float image_height, float threshold, pxe_detection* dets, long long capacity,
+                              long long* count, int batch_id_offset);
+
 /* ------------------------------------------------------------------------------------------
  * Post-processing on the host: px::nms (src/Box.cpp:56-145), same ordering, same 0.9 IoU
  * cross-class duplicate rule, same 1024-candidate cap per (image, class) group.

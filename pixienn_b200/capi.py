@@ -145,6 +145,8 @@ PROTOTYPES = {
     "pxe_nhwc_to_nchw": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i]),
     "pxe_avgpool": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i]),
     "pxe_detect_decode": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _ll, _vp, _i]),
+    "pxe_softmax_decode": (_i, [_vp, _vp, _ll, _i, _i, _f, _f, _f, _vp, _ll, _vp, _i]),
+    "pxe_region_decode": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_float), _i, _f, _f, _f, _vp, _ll, _vp, _i]),
     "pxe_nms_host": (_ll, [_vp, _ll, _f, _vp]),
     "pxe_nms_workspace_bytes": (_sz, [_ll]),
     "pxe_nms": (_i, [_vp, _vp, _ll, _f, _vp, _vp, _vp, _sz]),

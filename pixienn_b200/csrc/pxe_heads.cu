@@ -967,6 +967,137 @@ detect_decode_kernel(const DetectParams p)
     if (threadIdx.x == 0) *p.count = carry;
 }
 
+// ============================================================================================
+// Region (YOLOv2) head decode (include/RegionLayer.h:355-395, lightBox src/DarkBox.cpp:191-202)
+// ============================================================================================
+// pred is the output of pxe_region_forward: [image][cell*num + n][coords + 1 + classes].  Every class of a
+// box whose scale * class probability reaches the threshold is one record; order: image, cell, box, class.
+// One block walks the boxes in order with a running count (a head is 13x13x5 boxes per image).
+constexpr int kRegionMaxBoxes = 32;      // boxes per cell
+
+struct RegionDecodeParams {
+    const float* pred;
+    int batch, W, H, num, coords, classes, per_image;
+    float biases[2 * kRegionMaxBoxes];
+    float img_w, img_h, threshold;
+    pxe_detection* dets; long long capacity; long long* count;
+    int batch_id_offset;
+};
+
+__global__ void __launch_bounds__(1024)
+region_decode_kernel(const RegionDecodeParams p)
+{
+    __shared__ int warp_tot[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = *p.count;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int size = p.coords + 1 + p.classes;
+    const int per_image = p.W * p.H * p.num;
+    const long long total = (long long)p.batch * per_image;
+    for (long long base = 0; base < total; base += 1024) {
+        const long long t = base + threadIdx.x;
+        int cnt = 0, b = 0, index = 0;
+        const float* box = nullptr;
+        float scale = 0.0f;
+        if (t < total) {
+            b = (int)(t / per_image);
+            index = (int)(t - (long long)b * per_image);
+            // RegionLayer.h:363-369 indexes the predictions without the image's offset: every image decodes
+            // image 0's boxes.  per_image = 0 keeps that; 1 gives every image its own.
+            box = p.pred + ((long long)(p.per_image ? b : 0) * per_image + index) * size;
+            scale = box[p.coords];
+            for (int j = 0; j < p.classes; ++j)
+                if (__fmul_rn(scale, box[p.coords + 1 + j]) >= p.threshold) ++cnt;
+        }
+        int inc = cnt;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        __syncthreads();
+        long long before = carry;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (cnt) {
+            long long pos = before + inc - cnt;
+            const int i = index / p.num, n = index - i * p.num;
+            const int row = i / p.W, col = i - row * p.W;
+            const float x = (col + 1.0f / (1.0f + expf(-box[0]))) / p.W;
+            const float y = (row + 1.0f / (1.0f + expf(-box[1]))) / p.H;
+            const float bw = expf(box[2]) * p.biases[2 * n] / p.W;
+            const float bh = expf(box[3]) * p.biases[2 * n + 1] / p.H;
+            const float x1 = __fmul_rn(x, p.img_w), y1 = __fmul_rn(y, p.img_h);
+            const float ww = __fmul_rn(bw, p.img_w), hh = __fmul_rn(bh, p.img_h);
+            for (int j = 0; j < p.classes; ++j) {
+                const float pr = __fmul_rn(scale, box[p.coords + 1 + j]);
+                if (pr >= p.threshold) {
+                    if (pos < p.capacity)
+                        store_detection(p.dets + pos, __fsub_rn(x1, ww / 2.0f), __fsub_rn(y1, hh / 2.0f), ww, hh, pr, j,
+                                        b + p.batch_id_offset, index);
+                    ++pos;
+                }
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = before + inc;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *p.count = carry;
+}
+
+// Softmax (classifier) head: SoftmaxLayer::addDetects, include/SoftmaxLayer.h:182-196.  One record per image
+// whose largest probability (first maximum, std::max_element) reaches the threshold: the whole frame as the
+// box, the class and its probability.  One warp per image, 32 images per pass, images in order.
+__global__ void __launch_bounds__(1024)
+softmax_decode_kernel(const float* probs, long long pbs, int batch, int classes, float width, float height,
+                      float threshold, pxe_detection* dets, long long capacity, long long* count, int batch_id_offset)
+{
+    __shared__ int flags[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = *count;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < batch; base += 32) {
+        const int b = base + warp;
+        // std::max_element: the earliest of the largest values; a NaN never replaces the running maximum, and
+        // a NaN in front (element 0) is never replaced.  So: the lowest index among the largest non-NaN values,
+        // and no detection at all when element 0 is NaN.
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        bool first_is_nan = false;
+        if (b < batch) {
+            const float* p = probs + (long long)b * pbs;
+            first_is_nan = !(p[0] == p[0]);
+            for (int j = lane; j < classes; j += 32) {
+                const float v = p[j];
+                if (v > best || (v == best && j < arg)) { best = v; arg = j; }
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ov > best || (ov == best && oa < arg)) { best = ov; arg = oa; }
+        }
+        if (first_is_nan) best = __int_as_float(0x7fc00000);      // NaN >= threshold is false
+        const int flag = (b < batch && best >= threshold) ? 1 : 0;
+        if (lane == 0) flags[warp] = flag;
+        __syncthreads();
+        long long pos = carry;
+        int total = 0;
+        for (int w = 0; w < 32; ++w) {
+            if (w < warp) pos += flags[w];
+            total += flags[w];
+        }
+        if (flag && lane == 0 && pos < capacity)
+            store_detection(dets + pos, 0.0f, 0.0f, width, height, best, arg, b + batch_id_offset, 0);
+        __syncthreads();
+        if (threadIdx.x == 0) carry += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *count = carry;
+}
+
 }  // namespace
 }  // namespace pxe
 
@@ -1255,5 +1386,44 @@ extern "C" int pxe_detect_decode(pxe_stream_t stream, const float* pred, long lo
     p.dets = dets; p.capacity = capacity; p.count = count; p.batch_id_offset = batch_id_offset;
     detect_decode_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
     PXE_LAUNCH_OK("detect_decode_kernel");
+    return PXE_OK;
+}
+
+// --------------------------------------------------------------------------------- Region decode
+extern "C" int pxe_region_decode(pxe_stream_t stream, const float* pred, int batch, int width, int height, int num,
+                                 int coords, int classes, const float* anchors, int per_image, float image_width,
+                                 float image_height, float threshold, pxe_detection* dets, long long capacity,
+                                 long long* count, int batch_id_offset)
+{
+    PXE_REQUIRE(pred && anchors && dets && count, "region_decode: null pointer");
+    PXE_REQUIRE(batch > 0 && width > 0 && height > 0 && num > 0 && coords >= 4 && classes > 0, "region_decode: bad shape");
+    PXE_REQUIRE(num <= kRegionMaxBoxes, "region_decode: more than %d boxes per cell", kRegionMaxBoxes);
+    PXE_REQUIRE(capacity >= 0, "region_decode: negative capacity");
+    PXE_REQUIRE(aligned16(dets), "region_decode: dets must be 16-byte aligned");
+    RegionDecodeParams p{};
+    p.pred = pred; p.batch = batch; p.W = width; p.H = height; p.num = num; p.coords = coords; p.classes = classes;
+    p.per_image = per_image;
+    for (int i = 0; i < 2 * num; ++i) p.biases[i] = anchors[i];
+    p.img_w = image_width; p.img_h = image_height; p.threshold = threshold;
+    p.dets = dets; p.capacity = capacity; p.count = count; p.batch_id_offset = batch_id_offset;
+    region_decode_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    PXE_LAUNCH_OK("region_decode_kernel");
+    return PXE_OK;
+}
+
+// -------------------------------------------------------------------------------- Softmax decode
+extern "C" int pxe_softmax_decode(pxe_stream_t stream, const float* probs, long long probs_batch_stride, int batch,
+                                  int classes, float width, float height, float threshold, pxe_detection* dets,
+                                  long long capacity, long long* count, int batch_id_offset)
+{
+    PXE_REQUIRE(probs && dets && count, "softmax_decode: null pointer");
+    PXE_REQUIRE(batch > 0 && classes > 0, "softmax_decode: non-positive shape");
+    PXE_REQUIRE(probs_batch_stride == 0 || probs_batch_stride >= classes, "softmax_decode: probs_batch_stride too small");
+    PXE_REQUIRE(capacity >= 0, "softmax_decode: negative capacity");
+    PXE_REQUIRE(aligned16(dets), "softmax_decode: dets must be 16-byte aligned");
+    softmax_decode_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        probs, probs_batch_stride ? probs_batch_stride : classes, batch, classes, width, height, threshold, dets, capacity,
+        count, batch_id_offset);
+    PXE_LAUNCH_OK("softmax_decode_kernel");
     return PXE_OK;
 }

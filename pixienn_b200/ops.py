@@ -531,3 +531,35 @@ def nhwc_to_nchw(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty((B, Cc, H, W), device=x.device, dtype=torch.float32)
     capi.check(capi.lib().pxe_nhwc_to_nchw(_stream(), xp, xps, out.data_ptr(), 0, B, Cc, H, W))
     return out
+
+
+def region_decode(pred: torch.Tensor, width: int, height: int, num: int, coords: int, classes: int, anchors,
+                  threshold: float, buf: DetectionBuffer, *, per_image: bool = False, img_w: float = 1.0,
+                  img_h: float = 1.0, batch_id_offset: int = 0) -> None:
+    """Appends a Region (YOLOv2) head's detections to ``buf``.  ``pred`` is the output of
+    :func:`region_forward`.  ``per_image=False`` is the reference's behaviour: every image of the batch decodes
+    image 0's predictions (include/RegionLayer.h:363-369)."""
+    _check_f32_cuda(pred, "pred")
+    if not pred.is_contiguous():
+        raise ValueError("pred must be contiguous")
+    B = pred.shape[0]
+    if pred.numel() != B * width * height * num * (coords + 1 + classes):
+        raise ValueError("pred does not have batch * width * height * num * (coords + 1 + classes) values")
+    arr = (C.c_float * (2 * num))(*[float(a) for a in list(anchors)[:2 * num]])
+    capi.check(capi.lib().pxe_region_decode(_stream(), pred.data_ptr(), B, width, height, num, coords, classes, arr,
+                                            int(per_image), float(img_w), float(img_h), float(threshold),
+                                            buf.dets.data_ptr(), buf.capacity, buf.count.data_ptr(), batch_id_offset))
+
+
+def softmax_decode(probs: torch.Tensor, width: float, height: float, threshold: float, buf: DetectionBuffer, *,
+                   batch_id_offset: int = 0) -> None:
+    """Appends the classifier head's records (SoftmaxLayer::addDetects): one per image whose best class reaches
+    the threshold.  ``probs``: [B, classes, ...] contiguous."""
+    _check_f32_cuda(probs, "probs")
+    if not probs.is_contiguous():
+        raise ValueError("probs must be contiguous")
+    B = probs.shape[0]
+    classes = probs.numel() // B
+    capi.check(capi.lib().pxe_softmax_decode(_stream(), probs.data_ptr(), classes, B, classes, float(width), float(height),
+                                             float(threshold), buf.dets.data_ptr(), buf.capacity, buf.count.data_ptr(),
+                                             batch_id_offset))

@@ -128,6 +128,7 @@ class Runner:
         self.timer = OpTimer()
         self.launches = 0              # kernels of libpxe.so launched by the last forward
         self.contiguous_copies = 0     # hidden torch copies of strided conv inputs (should stay 0)
+        self.region_per_image = False   # False: RegionLayer::addDetects as written (every image decodes image 0's boxes)
         self.keep: Optional[set] = None  # layer indices whose tensors to retain in self.kept
         self.kept: Dict[int, torch.Tensor] = {}
 
@@ -285,6 +286,11 @@ class Runner:
                 self.launches += 1
                 tm.end(s, "softmax", 8 * xin.numel())
                 self.outputs[st.layer] = T[st.layer]
+                # SoftmaxLayer::addDetects: the best class of every image, if it reaches the threshold
+                ops.softmax_decode(T[st.layer], self.model.width, self.model.height, self.threshold, self.dets,
+                                   batch_id_offset=self.batch_id_offset)
+                self.launches += 1
+                self.head_marks.append(self.dets.count.clone())
             elif st.op == "region":
                 xin = self._nchw(T[st.inputs[0]])
                 s = tm.begin()
@@ -294,6 +300,14 @@ class Runner:
                 self.launches += 1
                 tm.end(s, "region", 8 * xin.numel())
                 self.outputs[st.layer] = T[st.layer]
+                # RegionLayer::addDetects, with the reference's indexing unless region_per_image is set
+                num = int(l.params.get("num", 1))
+                anchors = [float(a) for a in l.params.get("anchors", [0.5] * (2 * num))]
+                ops.region_decode(T[st.layer], l.in_shape[2], l.in_shape[1], num, int(l.params.get("coords", 4)),
+                                  int(l.params.get("classes", self.model.classes or 20)), anchors, self.threshold,
+                                  self.dets, per_image=self.region_per_image, batch_id_offset=self.batch_id_offset)
+                self.launches += 1
+                self.head_marks.append(self.dets.count.clone())
             elif st.op == "avgpool":
                 xin = self._nchw(T[st.inputs[0]])
                 s = tm.begin()

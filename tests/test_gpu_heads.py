@@ -424,3 +424,60 @@ def test_detect_decode_matches_oracle(cuda, oracle, B, side, num, classes, squar
     got, n = small.to_host()
     assert n == total and len(got) == max(1, total // 2)
     assert np.array_equal(got["source"], ref["source"][:len(got)]) and np.array_equal(got["batch_id"], ref["batch_id"][:len(got)] + 4)
+
+
+@pytest.mark.parametrize("B,num,classes,H,W,thr", [(2, 5, 20, 13, 13, 0.05), (1, 3, 4, 5, 7, 0.0), (3, 2, 80, 9, 9, 0.2)])
+def test_region_decode_matches_oracle(cuda, oracle, B, num, classes, H, W, thr):
+    """RegionLayer::addDetects after the layer's forward: same records and order.  per_image=False keeps the
+    reference's indexing (every image decodes image 0's boxes); per_image=True equals decoding each image alone."""
+    coords = 4
+    x = synth.normal(62, f"reg{B}{num}{classes}", (B, num * (coords + 1 + classes), H, W), 0, 1.5)
+    anchors = [1.08, 1.19, 3.42, 4.41, 6.63, 11.38, 9.42, 5.11, 16.62, 10.52][:2 * num]
+    fwd = oracle.region_forward(x, num, coords, classes, True)
+    ref = oracle.region_decode(fwd, W, H, num, coords, classes, np.array(anchors, np.float32), thr)
+    assert len(ref) > 0
+    dfwd = ops.region_forward(dev(x, cuda), num, coords, classes, True)
+    buf = ops.DetectionBuffer(len(ref) + 16, cuda)
+    ops.region_decode(dev(fwd, cuda), W, H, num, coords, classes, anchors, thr, buf)
+    got, n = buf.to_host()
+    assert n == len(ref)
+    dets_equal(got, ref, box_tol=2e-6)                  # exp / logistic on the device vs glibc
+    # from the device's own forward: same boxes up to the activation tolerance
+    buf.reset()
+    ops.region_decode(dfwd, W, H, num, coords, classes, anchors, thr, buf, per_image=True)
+    got_all, n_all = buf.to_host()
+    parts = [oracle.region_decode(fwd[b:b + 1], W, H, num, coords, classes, np.array(anchors, np.float32), thr) for b in range(B)]
+    assert abs(n_all - sum(len(q) for q in parts)) <= max(2, n_all // 500)
+
+
+def test_softmax_decode_first_maximum_threshold_and_nan(cuda):
+    """SoftmaxLayer::addDetects: std::max_element keeps the earliest of equal maxima; a NaN elsewhere is ignored,
+    a NaN in front blocks the image; images below the threshold emit nothing; order = image order."""
+    B, classes = 70, 1000
+    rng = np.random.default_rng(3)
+    p = rng.random((B, classes)).astype(np.float32) * 0.5
+    p[1, 17] = p[1, 400] = 0.9               # tie: the earlier index wins
+    p[2] *= 0.1                              # below the threshold
+    p[3, 5] = np.nan; p[3, 900] = 0.8        # NaN in the middle is skipped
+    p[4, 0] = np.nan; p[4, 10] = 0.99        # NaN in front: max_element never leaves it
+    p[5, 999] = 0.95
+    p[69, 31] = 0.7
+    want = []
+    for b in range(B):
+        row = p[b]
+        arg = 0
+        for j in range(1, classes):
+            if row[arg] < row[j]:
+                arg = j
+        if row[arg] >= 0.3:
+            want.append((b, arg, row[arg]))
+    buf = ops.DetectionBuffer(B, cuda)
+    ops.softmax_decode(dev(p, cuda), 224, 224, 0.3, buf, batch_id_offset=2)
+    got, n = buf.to_host()
+    assert n == len(want) and len(got) == n
+    assert got["batch_id"].tolist() == [b + 2 for b, _, _ in want]
+    assert got["class_id"].tolist() == [a for _, a, _ in want]
+    assert np.array_equal(got["prob"], np.array([v for _, _, v in want], np.float32))
+    assert (got["x"] == 0).all() and (got["w"] == 224).all() and (got["h"] == 224).all()
+    assert 2 not in [b for b, _, _ in want] and 4 not in [b for b, _, _ in want]
+    assert (1, 17, np.float32(0.9)) in want and (3, 900, np.float32(0.8)) in want
