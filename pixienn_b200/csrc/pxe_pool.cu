@@ -70,6 +70,11 @@ struct SppParams {
     long long ybs[kMaxPools];
 };
 
+// A k x k maximum is the maximum over rows of the k-wide row maxima: each pool runs as a row pass into a second
+// shared-memory plane and a column pass over it, 2k reads per output instead of k*k (54 instead of 275 for the
+// 5 / 9 / 13 block).  The reference's scan (src/MaxPoolKernels.cu:26-40: the first tap is taken as it is, a later
+// tap replaces it only when strictly greater) is reproduced exactly: both passes ignore NaNs the way "v > best"
+// does, and a window whose FIRST tap is a NaN yields that NaN, as the scan would.
 __global__ void __launch_bounds__(kThreads)
 spp_kernel(const SppParams p)
 {
@@ -77,25 +82,39 @@ spp_kernel(const SppParams p)
     const int plane = blockIdx.x;
     const int b = plane / p.C, c = plane - b * p.C;
     const int HW = p.H * p.W;
+    float* rowmax = tile + HW;
     const float* src = p.x + (long long)b * p.xbs + (long long)c * HW;
     for (int i = threadIdx.x; i < HW; i += kThreads) tile[i] = src[i];
     __syncthreads();
-    for (int i = threadIdx.x; i < HW; i += kThreads) {
-        const int oy = i / p.W, ox = i - oy * p.W;
-        for (int k = 0; k < p.n_pools; ++k) {
-            const int y0 = oy + p.offset[k], x0 = ox + p.offset[k];
-            const int ya = y0 < 0 ? 0 : y0, xa = x0 < 0 ? 0 : x0;
-            const int yb = y0 + p.kernel[k] < p.H ? y0 + p.kernel[k] : p.H;
-            const int xb = x0 + p.kernel[k] < p.W ? x0 + p.kernel[k] : p.W;
-            float best = -FLT_MAX;
-            bool first = true;
-            for (int iy = ya; iy < yb; ++iy)
-                for (int ix = xa; ix < xb; ++ix) {
-                    const float v = tile[iy * p.W + ix];
-                    if (first || v > best) { best = v; first = false; }
-                }
-            p.y[k][(long long)b * p.ybs[k] + (long long)c * HW + i] = best;
+    for (int k = 0; k < p.n_pools; ++k) {
+        const int K = p.kernel[k], off = p.offset[k];
+        for (int i = threadIdx.x; i < HW; i += kThreads) {
+            const int oy = i / p.W, ox = i - oy * p.W;
+            const int xa = ox + off < 0 ? 0 : ox + off;
+            const int xb = ox + off + K < p.W ? ox + off + K : p.W;
+            float m = -INFINITY;
+            for (int ix = xa; ix < xb; ++ix) {
+                const float v = tile[oy * p.W + ix];
+                m = v > m ? v : m;
+            }
+            rowmax[i] = m;
         }
+        __syncthreads();
+        for (int i = threadIdx.x; i < HW; i += kThreads) {
+            const int oy = i / p.W, ox = i - oy * p.W;
+            const int ya = oy + off < 0 ? 0 : oy + off;
+            const int yb = oy + off + K < p.H ? oy + off + K : p.H;
+            const int xa = ox + off < 0 ? 0 : ox + off;
+            float m = -INFINITY;
+            for (int iy = ya; iy < yb; ++iy) {
+                const float v = rowmax[iy * p.W + ox];
+                m = v > m ? v : m;
+            }
+            const float first = tile[ya * p.W + xa];
+            if (first != first) m = first;
+            p.y[k][(long long)b * p.ybs[k] + (long long)c * HW + i] = m;
+        }
+        __syncthreads();
     }
 }
 
@@ -197,7 +216,7 @@ extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_st
         p.y[k] = ys[k];
         p.ybs[k] = y_batch_strides[k] ? y_batch_strides[k] : chw;
     }
-    const size_t smem = (size_t)height * width * sizeof(float);
+    const size_t smem = 2 * (size_t)height * width * sizeof(float);      // the plane and its row maxima
     if (smem > 48 * 1024 || (long long)batch * channels > 0x7fffffffLL) {
         // plane too large to stage: one generic stride-1 pool per kernel size
         for (int k = 0; k < n_pools; ++k) {

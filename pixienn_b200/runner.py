@@ -216,8 +216,18 @@ class Runner:
                     T[g] = ts[0]
                 s = tm.begin()
                 if self.nhwc:
-                    for g, f in zip(st.spp_layers, firsts):
-                        ops.maxpool_nhwc(xin, L[g].kernel, 1, L[g].kernel - 1, out=f)
+                    # A (k+4)-wide stride-1 maximum is the 5-wide maximum of the k-wide one (taps outside the
+                    # map are skipped, i.e. -inf): pools whose sizes step by 4 (5, 9, 13) are chained, each
+                    # reading the previous result, 25 taps per output instead of 81 and 169.
+                    order = sorted(range(len(firsts)), key=lambda i: L[st.spp_layers[i]].kernel)
+                    prev_k, prev_t = None, None
+                    for i in order:
+                        k = L[st.spp_layers[i]].kernel
+                        if prev_k is not None and k == prev_k + 4:
+                            ops.maxpool_nhwc(prev_t, 5, 1, 4, out=firsts[i])
+                        else:
+                            ops.maxpool_nhwc(xin, k, 1, k - 1, out=firsts[i])
+                        prev_k, prev_t = k, firsts[i]
                     self.launches += len(firsts) - 1
                 else:
                     ops.spp(xin, [L[g].kernel for g in st.spp_layers], firsts)

@@ -120,6 +120,29 @@ def test_spp_block(cuda, oracle, shape):
     same(cat.cpu().numpy(), ref)
 
 
+def test_spp_block_nan_infinities_and_signed_zeros(cuda, oracle):
+    """The row / column form of the SPP kernel keeps the reference scan's corner cases: a NaN as the first tap of
+    a window is the result, NaNs elsewhere are ignored, -inf planes stay -inf, the first of +0 / -0 wins."""
+    B, C, H, W = 1, 6, 12, 12
+    x = synth.normal(36, "sppnan", (B, C, H, W))
+    x[0, 0, 0, 0] = np.nan                     # first tap of the windows in the top-left corner
+    x[0, 0, 5, 5] = np.nan
+    x[0, 1, 3, :] = np.nan                     # a whole row of NaNs
+    x[0, 2] = -np.inf
+    x[0, 3] = 0.0
+    x[0, 3, ::2, ::2] = -0.0
+    x[0, 4, 6, 6] = np.inf
+    x[0, 5, :, 0] = np.nan                     # first column: first tap of every window that touches it
+    outs = [torch.empty((B, C, H, W), device=cuda) for _ in range(3)]
+    ops.spp(dev(x, cuda), [13, 9, 5], outs)
+    for k, o in zip((13, 9, 5), outs):
+        ref = oracle.maxpool(x, k, 1)[0]
+        got = o.cpu().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(ref))
+        m = ~np.isnan(ref)
+        assert np.array_equal(got[m], ref[m]) and np.array_equal(np.signbit(got[m]), np.signbit(ref[m]))
+
+
 @pytest.mark.parametrize("shape", [(2, 4, 16, 16), (2, 3, 13, 13), (1, 5, 38, 38), (2, 2, 19, 19), (1, 3, 5, 7)])
 @pytest.mark.parametrize("stride,scale", [(2, 1.0), (2, 0.5), (3, 1.0)])
 def test_upsample(cuda, oracle, shape, stride, scale):
