@@ -34,3 +34,21 @@ def test_cpp_client_links_and_runs(tmp_path):
     assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
     assert "steps=4 fused_pool=1 fused_shortcut=1 raw_heads=1" in run.stdout
     assert "nms kept=2" in run.stdout and "px:: symbols resolved" in run.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(shutil.which("g++") is None, reason="g++ not found")
+def test_cpp_program_drives_the_c_abi_on_the_gpu(tmp_path):
+    """No Python and no torch between the caller and the kernels: a C++ program with the CUDA runtime fills the
+    descriptors, launches on its own stream and checks the results itself."""
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    libdir = os.path.dirname(capi.LIB_PATH)
+    exe = tmp_path / "epilogue_client"
+    r = subprocess.run(["g++", "-std=c++17", "-O1", "-I", INC, "-I", os.path.join(cuda_home, "include"),
+                        os.path.join(SRC, "epilogue_client.cpp"), "-L", libdir, "-lpxe", f"-Wl,-rpath,{libdir}",
+                        "-L", os.path.join(cuda_home, "lib64"), "-lcudart", f"-Wl,-rpath,{os.path.join(cuda_home, 'lib64')}",
+                        "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
+    assert run.stdout.startswith("ok:")
