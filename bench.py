@@ -334,7 +334,18 @@ def cpu_reference(args, steps: int, warmup: int):
         cpu.forward(x)
         cpu.detections(CONF)
     sec = time.perf_counter() - t
+    single = None
+    if ref is not None and args.cpu_single_core and cores > 1:
+        # the same path on one host thread: one image, once (about ten seconds for YOLOv3-608)
+        ref.set_threads(1)
+        x1 = x[:1]
+        t1 = time.perf_counter()
+        cpu.forward(x1)
+        cpu.detections(CONF)
+        single = round(1.0 / (time.perf_counter() - t1), 4)
+        ref.set_threads(cores)
     return {"value": round(args.cpu_images * steps / sec, 4), "unit": "images/s", "cores": cores,
+            "single_core_value": single,
             "kind": "reference" if ref is not None else "port",
             "sample": f"{args.cpu_images} image(s) of the {label} batch per step, {steps} step(s): conv (im2col + OpenBLAS "
                       "sgemm), BN, bias, activation in the reference's own compiled CpuUtil.cpp / BatchNorm.cpp / "
@@ -691,6 +702,8 @@ def main():
     ap.add_argument("--cpu-images", type=int, default=2, help="images per step of the CPU reference sample")
     ap.add_argument("--det-capacity", type=int, default=24 * (1 << 20))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-single-core", action="store_true",
+                    help="also time the CPU reference on one host thread (one image, adds about ten seconds)")
     ap.add_argument("--sweep-shapes", type=int, default=0, help="only the first N shapes of the sweep")
     ap.add_argument("--sweep-shape-index", type=int, default=-1, help="only this shape of the sweep (0..4)")
     ap.add_argument("--sweep-acts", default="leaky,mish,swish,logistic")
