@@ -521,11 +521,20 @@ class Runner:
             heads.append(np.concatenate(ops.centernet_to_host(d, c)))
         return heads
 
-    def predict(self, host_batch: torch.Tensor, nms_threshold: Optional[float] = None):
+    def predict(self, host_batch: torch.Tensor, nms_threshold: Optional[float] = None, nms_on_device: bool = False):
         """The call a user makes: host images in (pinned memory), detections out.  Mirrors
-        Model::predictBatchImageList (include/Model.h:951-1060) from the H2D copy on."""
+        Model::predictBatchImageList (include/Model.h:951-1060) from the H2D copy on.  With
+        ``nms_on_device`` px::nms runs on the device buffer the decodes filled and only the survivors are
+        copied to the host (same records, same order as the host form); CenterNet heads, whose records live
+        in their own per-image buffers, always take the host form."""
         x = host_batch.to(self.device, non_blocking=True)
         self.forward(x)
+        if nms_threshold is not None and nms_on_device and not self.centernet_out:
+            total = int(self.dets.count.item())
+            n = min(total, self.dets.capacity)
+            kept, count = ops.nms_device(self.dets.dets, n, nms_threshold)
+            m = int(count.item())
+            return kept[:m].cpu().numpy().view(ops.DET_DTYPE).reshape(-1), total
         recs, total = self.detections()
         if nms_threshold is not None:
             recs = ops.nms(recs, nms_threshold)

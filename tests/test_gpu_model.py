@@ -200,3 +200,15 @@ def test_yolov1_style_graph_runs_connected_and_detection_layers(cuda, oracle):
         assert np.array_equal(got[f], ref[f]), f
     for f in ("x", "y", "w", "h"):                   # squared widths: the host's powf(v, 2) vs v*v, one ulp apart at most
         np.testing.assert_allclose(got[f], ref[f], rtol=1e-6, atol=1e-6)
+
+
+def test_predict_with_device_nms_equals_host_nms(cuda):
+    """Runner.predict: NMS on the device buffer + a copy of the survivors == a copy of everything + host NMS."""
+    model = graph.parse_model(presets.yolov3_tiny(160, 160))
+    weights = synth_weights(model, 9, head_bias=-3.0)
+    r = Runner(model, weights, 3, cuda)
+    xb = torch.from_numpy(make_input(50, 3, model)).pin_memory()
+    want, total = r.predict(xb, nms_threshold=0.4)
+    got, total2 = r.predict(xb, nms_threshold=0.4, nms_on_device=True)
+    assert total == total2 and 0 < len(want) < total
+    assert got.tobytes() == want.tobytes()
