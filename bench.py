@@ -142,7 +142,7 @@ def run_model(args):
     B = args.batch
     weights = synth_weights(model, SEED)
     runner = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF,
-                    batch_id_offset=rank * B, layout=args.layout)
+                    batch_id_offset=rank * B, layout=args.layout, fused_stem=args.fused_stem)
     xh = torch.from_numpy(host_batch(model, B, rank * B)).pin_memory()
     x = xh.to(dev)
     pinned_dets = None
@@ -229,7 +229,7 @@ def run_model(args):
         del pipe
         torch.cuda.empty_cache()
         r2 = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B,
-                    layout="nhwc")
+                    layout="nhwc", fused_stem=args.fused_stem)
         r2.dets = runner.dets
         step2 = r2.capture(x).replay if use_graph else (lambda: r2.forward(x))
         for _ in range(args.warmup):
@@ -732,6 +732,8 @@ def main():
                     help="activation layout between layers: nchw = the reference's (BASELINE.json's configs); nhwc = "
                          "channels-last, which lets cuDNN skip its layout conversions (the library's NHWC tier)")
     ap.add_argument("--no-alt-layout", action="store_true", help="skip the extra channels-last measurement")
+    ap.add_argument("--fused-stem", action="store_true",
+                    help="first convolution + epilogue as one launch of the library (pxe_conv_stem) instead of cuDNN + epilogue")
     ap.add_argument("--cuda-graph", default="auto", choices=["auto", "on", "off"],
                     help="auto / on: the reported step is one CUDA-graph replay of the forward pass (the eager pass "
                          "with per-kernel events is still run and timed for the breakdown); off: eager only")

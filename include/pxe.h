@@ -367,6 +367,30 @@ PXE_API int pxe_maxpool_nhwc(pxe_stream_t stream, const float* in, long long in_
 PXE_API int pxe_nhwc_to_nchw(pxe_stream_t stream, const float* in, long long in_pixel_stride, float* out,
                              long long out_batch_stride, int batch, int channels, int height, int width);
 
+/* ------------------------------------------------------------------------------------------
+ * The network's first convolution fused with its epilogue (ConvLayer<CUDA>::forward in one launch,
+ * include/cuda/ConvLayer.h:278-307): 3x3, stride 1, padding 1, dilation 1, one group, 1..4 input channels,
+ * 8..64 output channels in multiples of 8.  With so few input channels the layer is bound by writing its
+ * output, the largest tensor of the network, not by arithmetic; cuDNN + a separate epilogue write it once
+ * and then read and write it again.  y = act(a[k] * conv(x, weights)[k] + b[k]) with the folded coefficients
+ * of pxe_fold_bn (NULL, NULL: no affine part).  Summation order differs from cuDNN's, so results agree with
+ * the two-launch path to fp32 rounding (a few 1e-7 relative), not bit for bit.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pxe_stem_desc {
+    const float* x;               /* [batch, in_channels, height, width], NCHW */
+    long long x_batch_stride;     /* 0 = dense */
+    const float* weights;         /* [out_channels, in_channels, 3, 3], the layer's weights_ */
+    const float* a;               /* folded coefficients [out_channels], or NULL (with b) */
+    const float* b;
+    float* y;                     /* output, same height and width */
+    int y_is_nhwc;                /* 0: [batch, out_channels, H, W]; 1: [batch, H, W, out_channels] */
+    long long y_stride;           /* NCHW: batch stride; NHWC: pixel stride; 0 = dense */
+    int batch, in_channels, out_channels, height, width;
+    int act;                      /* pxe_activation */
+} pxe_stem_desc;
+
+PXE_API int pxe_conv_stem(pxe_stream_t stream, const pxe_stem_desc* desc);
+
 /* Global average pooling (AvgPoolLayer::forward, include/AvgPoolLayer.h:66-87; cudnnPoolingForward with an
  * H x W average window on the CUDA path, include/cuda/AvgPoolLayer.h:66-75): y[b][c] = mean of plane (b, c).
  * x: [batch, channels, height, width] with batch stride (0 = dense); y: [batch, channels] likewise. */

@@ -59,6 +59,14 @@ class EpilogueNhwcDesc(C.Structure):
                 ("y_pool_pixel_stride", C.c_longlong)]
 
 
+class StemDesc(C.Structure):
+    """pxe_stem_desc of include/pxe.h."""
+    _fields_ = [("x", C.c_void_p), ("x_batch_stride", C.c_longlong), ("weights", C.c_void_p), ("a", C.c_void_p),
+                ("b", C.c_void_p), ("y", C.c_void_p), ("y_is_nhwc", C.c_int), ("y_stride", C.c_longlong),
+                ("batch", C.c_int), ("in_channels", C.c_int), ("out_channels", C.c_int), ("height", C.c_int),
+                ("width", C.c_int), ("act", C.c_int)]
+
+
 class YoloDecodeDesc(C.Structure):
     _fields_ = [
         ("head", C.c_void_p), ("head_batch_stride", C.c_longlong),
@@ -138,6 +146,7 @@ PROTOTYPES = {
     "pxe_centernet_decode": (_i, [_vp, C.POINTER(CenterNetDecodeDesc), _vp, _vp, _vp, _sz]),
     "pxe_softmax": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
     "pxe_region_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
+    "pxe_conv_stem": (_i, [_vp, C.POINTER(StemDesc)]),
     "pxe_fold_bn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]),
     "pxe_conv_epilogue_nhwc": (_i, [_vp, C.POINTER(EpilogueNhwcDesc)]),
     "pxe_upsample_nhwc": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i, _f]),

@@ -563,3 +563,28 @@ def softmax_decode(probs: torch.Tensor, width: float, height: float, threshold: 
     capi.check(capi.lib().pxe_softmax_decode(_stream(), probs.data_ptr(), classes, B, classes, float(width), float(height),
                                              float(threshold), buf.dets.data_ptr(), buf.capacity, buf.count.data_ptr(),
                                              batch_id_offset))
+
+
+def conv_stem(x: torch.Tensor, weights: torch.Tensor, *, a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None,
+              act="linear", out: Optional[torch.Tensor] = None, nhwc: bool = False) -> torch.Tensor:
+    """First-layer 3x3 / stride 1 / padding 1 convolution fused with its epilogue.  ``x``: NCHW [B, Cin<=4, H, W];
+    ``weights``: [Cout, Cin, 3, 3] contiguous; ``a``, ``b``: folded coefficients (:func:`fold_bn`).  The output is
+    NCHW, or channels-last with ``nhwc=True``; ``out`` may be a channel slot of a wider buffer of that layout."""
+    xp, xbs = _slot(x, "x")
+    B, Cin, H, W = x.shape
+    _check_f32_cuda(weights, "weights")
+    if not weights.is_contiguous() or tuple(weights.shape[1:]) != (Cin, 3, 3):
+        raise ValueError(f"weights must be a contiguous [Cout, {Cin}, 3, 3] tensor, got {tuple(weights.shape)}")
+    Cout = weights.shape[0]
+    if out is None:
+        out = empty_nhwc((B, Cout, H, W), x.device) if nhwc else torch.empty((B, Cout, H, W), device=x.device)
+    elif tuple(out.shape) != (B, Cout, H, W):
+        raise ValueError(f"out has shape {tuple(out.shape)}, expected {(B, Cout, H, W)}")
+    d = capi.StemDesc()
+    d.x, d.x_batch_stride, d.weights = xp, xbs, weights.data_ptr()
+    d.a, d.b = _vec(a, Cout, "a"), _vec(b, Cout, "b")
+    d.y, d.y_stride = _nhwc(out, "out") if nhwc else _slot(out, "out")
+    d.y_is_nhwc = int(nhwc)
+    d.batch, d.in_channels, d.out_channels, d.height, d.width, d.act = B, Cin, Cout, H, W, _act(act)
+    capi.check(capi.lib().pxe_conv_stem(_stream(), C.byref(d)))
+    return out

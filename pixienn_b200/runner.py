@@ -94,7 +94,8 @@ class OpTimer:
 class Runner:
     def __init__(self, model: graph.Model, weights: Dict[int, Dict[str, np.ndarray]], batch: int, device,
                  fuse: bool = True, raw_heads: bool = True, det_capacity: int = 1 << 20,
-                 threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0, layout: str = "nchw"):
+                 threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0, layout: str = "nchw",
+                 fused_stem: bool = False):
         if layout not in ("nchw", "nhwc"):
             raise ValueError("layout must be 'nchw' (the reference's) or 'nhwc' (channels-last)")
         self.model, self.batch, self.device = model, batch, device
@@ -121,6 +122,23 @@ class Runner:
                                                  mean=w["rolling_mean"], var=w["rolling_var"], eps_mode=eps_mode)
                 else:
                     w["a"], w["b"] = ops.fold_bn(l.filters, device, bias=w["biases"])
+        # fused_stem: the first convolution and its epilogue as one launch of the library (pxe_conv_stem) instead of
+        # the cuDNN call + epilogue, where the layer and its place in the plan allow it
+        self.stem = None
+        if fused_stem and model.layers:
+            l0, st0 = model.layers[0], self.plan.steps[0]
+            others_read_input = any(-1 in l.sources for l in model.layers[1:])
+            if (l0.type == "conv" and l0.kernel == 3 and l0.stride == 1 and l0.padding == 1 and l0.dilation == 1
+                    and l0.groups == 1 and model.channels <= 4 and 8 <= l0.filters <= 64 and l0.filters % 8 == 0
+                    and st0.op == "conv" and st0.layer == 0 and st0.fused_pool is None and st0.fused_shortcut is None
+                    and not st0.head_raw and st0.dests and not others_read_input):
+                w = self.w[0]
+                if l0.batch_norm:
+                    a, b = ops.fold_bn(l0.filters, device, gamma=w["scales"], beta=w["biases"], mean=w["rolling_mean"],
+                                       var=w["rolling_var"], eps_mode=eps_mode)
+                else:
+                    a, b = ops.fold_bn(l0.filters, device, bias=w["biases"])
+                self.stem = {"weights": w["weights"].contiguous(), "a": a, "b": b}
         self.dets = ops.DetectionBuffer(det_capacity, device)
         self.head_marks = []           # device copies of the running detection count after each YOLO head
         self.centernet_out = []        # (dets, counts) per centernet layer of the last forward
@@ -177,7 +195,7 @@ class Runner:
     def forward(self, x: torch.Tensor) -> None:
         """Enqueues one forward pass of the whole graph for the batch ``x`` [B,C,H,W] (on the device)."""
         L = self.model.layers
-        if self.nhwc:
+        if self.nhwc and self.stem is None:
             x = x.contiguous(memory_format=torch.channels_last)
         T: Dict[int, torch.Tensor] = {-1: x}
         bufs: Dict[int, torch.Tensor] = {}
@@ -366,9 +384,19 @@ class Runner:
     def _conv(self, st: graph.Step, l: graph.Layer, T, bufs) -> None:
         w = self.w[l.index]
         xin = T[st.inputs[0]]
+        tm = self.timer
+        if l.index == 0 and self.stem is not None:
+            dests = self._dest_tensors(bufs, st.dests, l)
+            s = tm.begin()
+            ops.conv_stem(xin, self.stem["weights"], a=self.stem["a"], b=self.stem["b"], act=l.activation, out=dests[0],
+                          nhwc=self.nhwc)
+            self.launches += 1
+            tm.end(s, "stem conv+epilogue", 4 * (xin.numel() + dests[0].numel()))
+            self._extra_copies(dests[0], dests[1:])
+            T[0] = dests[0]
+            return
         if not xin.is_contiguous(memory_format=torch.channels_last if self.nhwc else torch.contiguous_format):
             self.contiguous_copies += 1
-        tm = self.timer
         s = tm.begin()
         raw = F.conv2d(xin, w["weights"], None, l.stride, l.padding, l.dilation, l.groups)
         tm.end(s, "conv(cudnn)", 0)

@@ -157,3 +157,51 @@ def test_channels_last_run_agrees_with_nchw_run(cuda, exact_fp32_convolutions, n
     if head_bias != 0.0:
         key = lambda d: set(zip(d["batch_id"].tolist(), d["class_id"].tolist(), d["source"].tolist()))
         assert len(key(da) & key(db)) >= 0.9 * max(len(da), len(db))
+
+
+@pytest.mark.parametrize("shape,cout", [((2, 3, 40, 150), 32), ((1, 3, 9, 7), 16), ((2, 1, 33, 129), 8), ((1, 4, 16, 260), 64)])
+@pytest.mark.parametrize("act", ["leaky", "mish", "linear"])
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_fused_stem_convolution(cuda, exact_fp32_convolutions, shape, cout, act, layout):
+    """First-layer convolution + epilogue in one launch == cuDNN convolution (true fp32) + the epilogue kernel,
+    to fp32 rounding of a 27-term sum; both output layouts, ragged tile edges, stores into a wider buffer."""
+    import torch.nn.functional as F
+    B, Cin, H, W = shape
+    x = dev(synth.uniform(85, f"stem{shape}", shape), cuda)
+    w = dev(synth.normal(86, f"stemw{shape}{cout}", (cout, Cin, 3, 3), 0.0, 0.3), cuda)
+    (g, b, m, v), dp = bn(87, f"stembn{cout}", cout, cuda)
+    fa, fb = ops.fold_bn(cout, cuda, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3])
+    want = ops.conv_epilogue(F.conv2d(x, w, None, 1, 1), gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], act=act)
+    got = ops.conv_stem(x, w, a=fa, b=fb, act=act, nhwc=layout == "nhwc")
+    assert got.is_contiguous(memory_format=torch.channels_last if layout == "nhwc" and cout > 1 and H * W > 1 else torch.contiguous_format)
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) <= 2e-6 * scale + 1e-6
+    wide = ops.empty_nhwc((B, cout + 8, H, W), cuda) if layout == "nhwc" else torch.empty((B, cout + 8, H, W), device=cuda)
+    wide.fill_(3.0)
+    ops.conv_stem(x, w, a=fa, b=fb, act=act, out=wide[:, 8:], nhwc=layout == "nhwc")
+    assert torch.equal(wide[:, 8:].contiguous(), got.contiguous()) and bool((wide[:, :8] == 3.0).all())
+    bare = ops.conv_stem(x, w, act="linear", nhwc=layout == "nhwc")
+    ref = F.conv2d(x, w, None, 1, 1)
+    assert float((bare - ref).abs().max()) <= 2e-6 * float(ref.abs().max()) + 1e-6
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_runner_with_fused_stem_agrees_with_the_cudnn_stem(cuda, exact_fp32_convolutions, layout):
+    model = graph.parse_model(presets.PRESETS["yolov3"](128, 128))
+    weights = synth_weights(model, 7, head_bias=-3.0)
+    x = dev(np.stack([synth.uniform(8, f"input/{b}", (3, 128, 128)) for b in range(2)]), cuda)
+    runs = []
+    for fused in (False, True):
+        r = Runner(model, weights, 2, cuda, layout=layout, fused_stem=fused)
+        assert (r.stem is not None) == fused
+        r.keep = set(range(len(model.layers)))
+        r.forward(x)
+        torch.cuda.synchronize()
+        runs.append(r)
+    a, b = runs
+    assert b.launches == a.launches                       # one library launch either way: the cuDNN call is what goes
+    for i in sorted(a.kept):
+        ta, tb = a.kept[i], b.kept[i]
+        assert float((ta - tb).abs().max()) <= 2e-4 * (float(ta.abs().max()) + 1e-6), f"layer {i}"
+    na, nb = a.detections()[1], b.detections()[1]
+    assert na > 0 and abs(na - nb) <= max(2, na // 50)
