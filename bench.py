@@ -222,14 +222,12 @@ def run_model(args):
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_total_ms = float(e2e_ms.item())
 
-    # ---- the same forward with channels-last activations (the library's NHWC tier): reported beside the headline
-    # number, which stays on the reference's NCHW layout
-    alt = None
-    if args.layout == "nchw" and not args.no_alt_layout:
-        del pipe
-        torch.cuda.empty_cache()
+    # ---- the same forward with channels-last activations (the library's NHWC tier), with cuDNN for every
+    # convolution and with the first convolution fused with its epilogue (pxe_conv_stem): reported beside the
+    # headline number, which stays on the reference's NCHW layout and cuDNN calls
+    def measure_variant(layout, fused_stem, note):
         r2 = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B,
-                    layout="nhwc", fused_stem=args.fused_stem)
+                    layout=layout, fused_stem=fused_stem)
         r2.dets = runner.dets
         step2 = r2.capture(x).replay if use_graph else (lambda: r2.forward(x))
         for _ in range(args.warmup):
@@ -243,6 +241,7 @@ def run_model(args):
         alt_ms = torch.tensor([t0.elapsed_time(t1)], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(alt_ms, op=dist.ReduceOp.MAX)
+        del step2
         # ... and end to end, the same way as the headline's e2e
         pipe2 = PipelinedPredictor(r2, tuple(xh.shape), use_graphs=use_graph)
         pipe2.submit(xh)
@@ -257,13 +256,23 @@ def run_model(args):
         barrier()
         if world > 1:
             dist.all_reduce(alt_wall, op=dist.ReduceOp.MAX)
-        del pipe2
-        alt = {"layout": "nhwc", "value": round(B * world * args.steps / (float(alt_ms.item()) / 1e3), 2), "unit": "images/s",
-               "ms_per_step": round(float(alt_ms.item()) / args.steps, 3),
-               "e2e_value": round(B * world * args.steps / (float(alt_wall.item()) / 1e3), 2),
-               "note": "same graph, weights and input; activations channels-last between layers, so cuDNN converts no "
-                       "layouts around its convolutions; resident input, " + ("one CUDA graph replay per step" if use_graph else "eager launches")}
-        del r2
+        return {"layout": layout, "fused_stem": bool(r2.stem is not None),
+                "value": round(B * world * args.steps / (float(alt_ms.item()) / 1e3), 2), "unit": "images/s",
+                "ms_per_step": round(float(alt_ms.item()) / args.steps, 3),
+                "e2e_value": round(B * world * args.steps / (float(alt_wall.item()) / 1e3), 2),
+                "note": note + "; same graph, weights and input; resident input, "
+                        + ("one CUDA graph replay per step" if use_graph else "eager launches")}
+
+    alt = alt_stem = None
+    if args.layout == "nchw" and not args.no_alt_layout:
+        del pipe
+        torch.cuda.empty_cache()
+        alt = measure_variant("nhwc", False, "activations channels-last between layers, so cuDNN converts no layouts around "
+                                             "its convolutions")
+        torch.cuda.empty_cache()
+        alt_stem = measure_variant("nhwc", True, "channels-last, and the first convolution + its epilogue as one launch of "
+                                                 "this library instead of cuDNN + epilogue")
+        torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
@@ -319,6 +328,7 @@ def run_model(args):
     }
     if alt is not None:
         line["channels_last"] = alt
+        line["channels_last_fused_stem"] = alt_stem
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, steps=1, warmup=0)
     print(json.dumps(line), flush=True)
