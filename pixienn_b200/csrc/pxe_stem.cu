@@ -22,6 +22,24 @@ constexpr int kStemTH = 16, kStemTW = 128;         // output tile: 16 rows x 128
 constexpr int kStemPatchW = kStemTW + 4;           // columns x0-1 .. x0+128, padded to keep rows 16-byte multiples
 constexpr int kStemMaxCin = 4, kStemMaxCout = 64;
 
+// two floats in one 64-bit register, for fma.rn.f32x2
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c)
+{
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 struct StemParams {
     const float* x; long long xbs;                 // [B, CIN, H, W]
     const float* w;                                // [COUT, CIN, 3, 3]
@@ -78,11 +96,14 @@ stem_conv_kernel(const StemParams p)
     const int gy = y0 + row;
     if (gy >= H) break;
     for (int k0 = 0; k0 < p.cout; k0 += 8) {
-        float acc[4][8];
+        // Accumulators as pairs of output channels: fma.rn.f32x2 performs two independent IEEE fused
+        // multiply-adds per instruction (same results as two scalar ones), which halves the issue slots the
+        // 27 x 32 multiply-adds of a pixel take.
+        unsigned long long acc2[4][4];
 #pragma unroll
         for (int px = 0; px < 4; ++px)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[px][k] = 0.0f;
+            for (int q = 0; q < 4; ++q) acc2[px][q] = 0ULL;
 #pragma unroll 1
         for (int ci = 0; ci < CIN; ++ci)
 #pragma unroll 1
@@ -90,18 +111,24 @@ stem_conv_kernel(const StemParams p)
                 // six input columns of this row: one 128-bit and one 64-bit shared-memory read
                 const float4 i0 = *reinterpret_cast<const float4*>(&patch[ci][row + ky][4 * xg]);
                 const float2 i1 = *reinterpret_cast<const float2*>(&patch[ci][row + ky][4 * xg + 4]);
-                const float in[6] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y};
+                const unsigned long long in2[6] = {pack2(i0.x, i0.x), pack2(i0.y, i0.y), pack2(i0.z, i0.z),
+                                                   pack2(i0.w, i0.w), pack2(i1.x, i1.x), pack2(i1.y, i1.y)};
 #pragma unroll
                 for (int kx = 0; kx < 3; ++kx) {
-                    const float4 w0 = *reinterpret_cast<const float4*>(&wsm[ci * 9 + ky * 3 + kx][k0]);
-                    const float4 w1 = *reinterpret_cast<const float4*>(&wsm[ci * 9 + ky * 3 + kx][k0 + 4]);
-                    const float wk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    const ulonglong2 w0 = *reinterpret_cast<const ulonglong2*>(&wsm[ci * 9 + ky * 3 + kx][k0]);
+                    const ulonglong2 w1 = *reinterpret_cast<const ulonglong2*>(&wsm[ci * 9 + ky * 3 + kx][k0 + 4]);
+                    const unsigned long long wq[4] = {w0.x, w0.y, w1.x, w1.y};
 #pragma unroll
                     for (int px = 0; px < 4; ++px)
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) acc[px][k] = fmaf(in[px + kx], wk[k], acc[px][k]);
+                        for (int q = 0; q < 4; ++q) acc2[px][q] = ffma2(in2[px + kx], wq[q], acc2[px][q]);
                 }
             }
+        float acc[4][8];
+#pragma unroll
+        for (int px = 0; px < 4; ++px)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) unpack2(acc2[px][q], acc[px][2 * q], acc[px][2 * q + 1]);
         // epilogue and store
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -117,8 +144,15 @@ stem_conv_kernel(const StemParams p)
             for (int px = 0; px < 4; ++px) {
                 if (gx + px >= W) break;
                 float* dst = p.y + (((long long)b * H + gy) * W + gx + px) * p.yps + k0;
-                *reinterpret_cast<float4*>(dst) = make_float4(acc[px][0], acc[px][1], acc[px][2], acc[px][3]);
-                *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[px][4], acc[px][5], acc[px][6], acc[px][7]);
+                if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+                    // one 256-bit store: the pixel's 8 channels are exactly one 32-byte sector
+                    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                 :: "l"(dst), "f"(acc[px][0]), "f"(acc[px][1]), "f"(acc[px][2]), "f"(acc[px][3]),
+                                    "f"(acc[px][4]), "f"(acc[px][5]), "f"(acc[px][6]), "f"(acc[px][7]) : "memory");
+                } else {
+                    *reinterpret_cast<float4*>(dst) = make_float4(acc[px][0], acc[px][1], acc[px][2], acc[px][3]);
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[px][4], acc[px][5], acc[px][6], acc[px][7]);
+                }
             }
         } else {
 #pragma unroll
