@@ -263,10 +263,14 @@ def run_model(args):
                 "note": note + "; same graph, weights and input; resident input, "
                         + ("one CUDA graph replay per step" if use_graph else "eager launches")}
 
-    alt = alt_stem = None
+    alt = alt_stem = nchw_stem = None
     if args.layout == "nchw" and not args.no_alt_layout:
         del pipe
         torch.cuda.empty_cache()
+        if not args.fused_stem:
+            nchw_stem = measure_variant("nchw", True, "the reference's layout, and the first convolution + its epilogue as one "
+                                                      "launch of this library instead of cuDNN + epilogue")
+            torch.cuda.empty_cache()
         alt = measure_variant("nhwc", False, "activations channels-last between layers, so cuDNN converts no layouts around "
                                              "its convolutions")
         torch.cuda.empty_cache()
@@ -329,6 +333,8 @@ def run_model(args):
     if alt is not None:
         line["channels_last"] = alt
         line["channels_last_fused_stem"] = alt_stem
+        if nchw_stem is not None:
+            line["nchw_fused_stem"] = nchw_stem
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, steps=1, warmup=0)
     print(json.dumps(line), flush=True)
