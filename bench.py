@@ -225,10 +225,13 @@ def run_model(args):
     # ---- the same forward with channels-last activations (the library's NHWC tier), with cuDNN for every
     # convolution and with the first convolution fused with its epilogue (pxe_conv_stem): reported beside the
     # headline number, which stays on the reference's NCHW layout and cuDNN calls
-    def measure_variant(layout, fused_stem, note):
+    def measure_variant(layout, fused_stem, note, conv_fusion=False):
         r2 = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B,
-                    layout=layout, fused_stem=fused_stem)
+                    layout=layout, fused_stem=fused_stem, conv_fusion=conv_fusion)
         r2.dets = runner.dets
+        if conv_fusion:
+            r2.forward(x)            # the eager pass in which every layer shape times its fused plans once
+            torch.cuda.synchronize()
         step2 = r2.capture(x).replay if use_graph else (lambda: r2.forward(x))
         for _ in range(args.warmup):
             step2()
@@ -256,14 +259,20 @@ def run_model(args):
         barrier()
         if world > 1:
             dist.all_reduce(alt_wall, op=dist.ReduceOp.MAX)
-        return {"layout": layout, "fused_stem": bool(r2.stem is not None),
+        extra = {}
+        if conv_fusion:
+            extra = {"conv_fusion": dict(r2.fused_conv.summary(), launches_per_step=r2.fused_conv_launches,
+                                         shapes_timed=[{"x": list(k[0]), "w": list(k[1]), "stride": k[2], "shortcut": bool(k[7]),
+                                                        "choice": c, "fused_ms": f and round(f, 4), "split_ms": round(sp, 4)}
+                                                       for k, c, f, sp in r2.fused_conv.log])}
+        return {"layout": layout, "fused_stem": bool(r2.stem is not None), **extra,
                 "value": round(B * world * args.steps / (float(alt_ms.item()) / 1e3), 2), "unit": "images/s",
                 "ms_per_step": round(float(alt_ms.item()) / args.steps, 3),
                 "e2e_value": round(B * world * args.steps / (float(alt_wall.item()) / 1e3), 2),
                 "note": note + "; same graph, weights and input; resident input, "
                         + ("one CUDA graph replay per step" if use_graph else "eager launches")}
 
-    alt = alt_stem = nchw_stem = None
+    alt = alt_stem = nchw_stem = alt_fusion = None
     if args.layout == "nchw" and not args.no_alt_layout:
         del pipe
         torch.cuda.empty_cache()
@@ -277,6 +286,12 @@ def run_model(args):
         alt_stem = measure_variant("nhwc", True, "channels-last, and the first convolution + its epilogue as one launch of "
                                                  "this library instead of cuDNN + epilogue")
         torch.cuda.empty_cache()
+        if args.conv_fusion:
+            alt_fusion = measure_variant("nhwc", True, "channels-last, fused first layer, and every other convolution whose cuDNN "
+                                                       "runtime-fusion plan (conv + scale + bias + activation + shortcut in one "
+                                                       "launch) measured faster than cuDNN convolution + this library's epilogue",
+                                         conv_fusion=True)
+            torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
@@ -335,6 +350,8 @@ def run_model(args):
         line["channels_last_fused_stem"] = alt_stem
         if nchw_stem is not None:
             line["nchw_fused_stem"] = nchw_stem
+        if alt_fusion is not None:
+            line["channels_last_conv_fusion"] = alt_fusion
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, steps=1, warmup=0)
     print(json.dumps(line), flush=True)
@@ -748,6 +765,9 @@ def main():
                     help="activation layout between layers: nchw = the reference's (BASELINE.json's configs); nhwc = "
                          "channels-last, which lets cuDNN skip its layout conversions (the library's NHWC tier)")
     ap.add_argument("--no-alt-layout", action="store_true", help="skip the extra channels-last measurement")
+    ap.add_argument("--conv-fusion", action="store_true",
+                    help="also measure the channels-last forward with conv + epilogue as one cuDNN runtime-fusion launch per "
+                         "layer where that is faster (adds about a minute of plan compilation and timing)")
     ap.add_argument("--fused-stem", action="store_true",
                     help="first convolution + epilogue as one launch of the library (pxe_conv_stem) instead of cuDNN + epilogue")
     ap.add_argument("--cuda-graph", default="auto", choices=["auto", "on", "off"],

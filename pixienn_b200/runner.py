@@ -95,7 +95,7 @@ class Runner:
     def __init__(self, model: graph.Model, weights: Dict[int, Dict[str, np.ndarray]], batch: int, device,
                  fuse: bool = True, raw_heads: bool = True, det_capacity: int = 1 << 20,
                  threshold: float = 0.2, batch_id_offset: int = 0, eps_mode: int = 0, layout: str = "nchw",
-                 fused_stem: bool = False):
+                 fused_stem: bool = False, conv_fusion: bool = False):
         if layout not in ("nchw", "nhwc"):
             raise ValueError("layout must be 'nchw' (the reference's) or 'nhwc' (channels-last)")
         self.model, self.batch, self.device = model, batch, device
@@ -139,6 +139,15 @@ class Runner:
                 else:
                     a, b = ops.fold_bn(l0.filters, device, bias=w["biases"])
                 self.stem = {"weights": w["weights"].contiguous(), "a": a, "b": b}
+        # conv_fusion: a convolution and its epilogue as one cuDNN runtime-fusion launch where that measures faster
+        # than the cuDNN convolution + the library's epilogue (channels-last only; see cudnn_fused.py)
+        self.fused_conv = None
+        if conv_fusion:
+            if not self.nhwc:
+                raise ValueError("conv_fusion needs layout='nhwc'")
+            from . import cudnn_fused
+            self.fused_conv = cudnn_fused.FusedConvPlanner(device)
+        self.fused_conv_launches = 0
         self.dets = ops.DetectionBuffer(det_capacity, device)
         self.head_marks = []           # device copies of the running detection count after each YOLO head
         self.centernet_out = []        # (dets, counts) per centernet layer of the last forward
@@ -202,6 +211,7 @@ class Runner:
         self.dets.reset()
         self.centernet_out, self.outputs, self.kept, self.head_marks = [], {}, {}, []
         self.launches = 0
+        self.fused_conv_launches = 0
         tm = self.timer
         for si, st in enumerate(self.plan.steps):
             l = L[st.layer]
@@ -397,6 +407,8 @@ class Runner:
             return
         if not xin.is_contiguous(memory_format=torch.channels_last if self.nhwc else torch.contiguous_format):
             self.contiguous_copies += 1
+        if self.fused_conv is not None and self._conv_fused(st, l, T, bufs, xin, w):
+            return
         s = tm.begin()
         raw = F.conv2d(xin, w["weights"], None, l.stride, l.padding, l.dilation, l.groups)
         tm.end(s, "conv(cudnn)", 0)
@@ -438,6 +450,59 @@ class Runner:
         tm.end(s, "epilogue+shortcut" if kw else "epilogue", nb)
         self._extra_copies(dests[0], dests[2:])
         T[out_layer.index] = dests[0]
+
+    def _conv_fused(self, st: graph.Step, l: graph.Layer, T, bufs, xin, w) -> bool:
+        """Convolution + epilogue (+ shortcut) of this step as one cuDNN launch, if the layer's shape has a fused
+        plan that measured faster than the split form.  False: the caller runs the split form."""
+        if (st.head_raw or st.fused_pool is not None or len(st.dests) != 1 or l.groups != 1 or l.dilation != 1
+                or self.fused_conv is None):
+            return False
+        out_layer, residual, res_act = l, None, "linear"
+        if st.fused_shortcut is not None:
+            out_layer = self.model.layers[st.fused_shortcut]
+            if out_layer.alpha != 1.0 or out_layer.beta != 1.0:
+                return False
+            residual, res_act = T[st.inputs[1]], out_layer.activation
+        fc = self.fused_conv
+        c, h, wd = out_layer.out_shape
+        # the key needs the destination's strides, not its memory: probe with the dense shape first so that a
+        # layer that keeps the split form allocates nothing here
+        d = st.dests[0]
+        if d.kind == "dense":
+            probe_shape, ps = (self.batch, c, h, wd), c
+        else:
+            probe_shape, ps = (self.batch, c, h, wd), self.plan.concat_channels[d.route]
+        probe = torch.empty_strided(probe_shape, (h * wd * ps, 1, wd * ps, ps), device="meta")
+        key = fc.key(xin, w["weights"], l.stride, l.padding, l.activation, probe, residual, res_act)
+        if key is None:
+            return False
+        capturing = torch.cuda.is_current_stream_capturing()
+        if fc.known(key):
+            if fc.cache[key] is None:
+                return False
+        elif capturing:
+            return False
+        dest = self._dest_tensors(bufs, st.dests, out_layer)[0]
+        tm = self.timer
+        if not fc.known(key):
+            kw = {}
+            if residual is not None:
+                kw = dict(residual=residual, res_alpha=1.0, res_beta=1.0, res_act=res_act)
+
+            def split():
+                raw = F.conv2d(xin, w["weights"], None, l.stride, l.padding)
+                ops.conv_epilogue_nhwc(raw, y=dest, a=w["a"], b=w["b"], act=l.activation, **kw)
+
+            if fc.tune(key, xin, w["weights"], w["a"], w["b"], dest, residual, split) is None:
+                T[out_layer.index] = dest            # the last timed split run left the layer's output there
+                self.launches += 1
+                return True
+        s = tm.begin()
+        fc.run(key, xin, w["weights"], w["a"], w["b"], dest, residual)
+        self.fused_conv_launches += 1
+        tm.end(s, "conv+epilogue (cudnn fused)", 0)
+        T[out_layer.index] = dest
+        return True
 
     def _conv_epilogue_nhwc(self, st: graph.Step, l: graph.Layer, T, bufs, raw: torch.Tensor, w) -> None:
         """The conv step's epilogue on channels-last tensors."""

@@ -205,3 +205,40 @@ def test_runner_with_fused_stem_agrees_with_the_cudnn_stem(cuda, exact_fp32_conv
         assert float((ta - tb).abs().max()) <= 2e-4 * (float(ta.abs().max()) + 1e-6), f"layer {i}"
     na, nb = a.detections()[1], b.detections()[1]
     assert na > 0 and abs(na - nb) <= max(2, na // 50)
+
+
+@pytest.mark.parametrize("name,hw,batch", [("yolov3", 128, 2), ("yolov7", 128, 1)])
+def test_runner_with_cudnn_conv_fusion_agrees_with_the_split_form(cuda, name, hw, batch):
+    """conv + epilogue (+ shortcut) as one cuDNN runtime-fusion launch per layer == cuDNN convolution + the
+    library's epilogue, to the convolutions' own rounding (both use TF32 tensor cores with different summation
+    orders, and the difference grows through a hundred layers: 2e-3 of a tensor's range by the last ones); first
+    pass (plans are timed) and second pass (cached plans) alike."""
+    pytest.importorskip("cudnn")
+    model = graph.parse_model(presets.PRESETS[name](hw, hw))
+    weights = synth_weights(model, 7, head_bias=-3.0)
+    x = dev(np.stack([synth.uniform(8, f"input/{b}", (model.channels, hw, hw)) for b in range(batch)]), cuda)
+    ref = Runner(model, weights, batch, cuda, layout="nhwc")
+    ref.keep = set(range(len(model.layers)))
+    ref.forward(x)
+    r = Runner(model, weights, batch, cuda, layout="nhwc", conv_fusion=True)
+    r.fused_conv.prefer_fused = True          # small shapes: take a fused plan wherever cuDNN has one
+    r.keep = set(range(len(model.layers)))
+    with pytest.raises(ValueError):
+        Runner(model, weights, batch, cuda, layout="nchw", conv_fusion=True)
+    for attempt in range(2):
+        r.forward(x)
+        torch.cuda.synchronize()
+        assert set(r.kept) == set(ref.kept)
+        for i in sorted(ref.kept):
+            ta, tb = ref.kept[i], r.kept[i]
+            assert ta.shape == tb.shape, i
+            assert float((ta - tb).abs().max()) <= 1e-2 * (float(ta.abs().max()) + 1e-6), f"pass {attempt} layer {i}"
+    assert r.fused_conv_launches > 0, r.fused_conv.log
+    s = r.fused_conv.summary()
+    assert s["fused"] > 0 and s["shapes"] >= s["fused"]
+    # replayed as a CUDA graph the fused launches are part of the graph
+    g = r.capture(x)
+    g.replay()
+    torch.cuda.synchronize()
+    for i in sorted(ref.kept):
+        assert float((ref.kept[i] - r.kept[i]).abs().max()) <= 1e-2 * (float(ref.kept[i].abs().max()) + 1e-6)
