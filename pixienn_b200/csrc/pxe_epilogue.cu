@@ -516,6 +516,97 @@ epilogue_pool_even_kernel(const EpiParams p)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Odd widths with small planes (13x13 -> 7x7, 19x19 -> 10x10, where no row pair is aligned and the
+// scalar form above spends ~150 instructions of index arithmetic per pooled output).  A warp takes
+// whole planes: lane l owns pooled outputs l, l+32, ... of EVERY plane the warp visits, so its
+// window offsets, edge predicates and output offset are computed once per thread and the loop over
+// planes is loads, the epilogue, three comparisons and a store.  PU planes are in flight per warp.
+// Four resident blocks where the activation is cheap enough to fit 64 registers (measured: 11.1 against
+// 13.1 us with three at [64,512,13,13] leaky), three for the transcendental ones (which spill at 64).
+// ---------------------------------------------------------------------------------------------
+template <int ACT, bool AFFINE, int SLOTS>
+__global__ void __launch_bounds__(kThreads, (ACT == PXE_ACT_LEAKY || ACT == PXE_ACT_LINEAR || ACT == PXE_ACT_RELU) ? 4 : 3)
+epilogue_pool_smallplane_kernel(const EpiParams p, uint32_t planes, uint32_t planes_per_block)
+{
+    extern __shared__ PlaneEntry tab[];
+    constexpr int PU = SLOTS >= 8 ? 1 : 8 / SLOTS;          // planes in flight per warp: 32 loads per lane
+    const uint32_t plane_lo = blockIdx.x * planes_per_block;
+    if (plane_lo >= planes) return;
+    uint32_t plane_end = plane_lo + planes_per_block;
+    if (plane_end > planes) plane_end = planes;
+    build_table(p, tab, plane_lo, plane_end - 1);
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr uint32_t kWarps = kThreads / 32;
+    const uint32_t ohow = (uint32_t)(p.OH * p.OW);
+    uint32_t in_off[SLOTS];
+    bool valid[SLOTS], row1[SLOTS], col1[SLOTS];
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const uint32_t idx = lane + 32u * s;
+        valid[s] = idx < ohow;
+        uint32_t oh, ow;
+        p.div_owv.divmod(valid[s] ? idx : 0u, oh, ow);       // OWV == OW in this form
+        in_off[s] = 2u * oh * (uint32_t)p.W + 2u * ow;
+        row1[s] = 2 * (int)oh + 1 < p.H;
+        col1[s] = 2 * (int)ow + 1 < p.W;
+    }
+    __syncthreads();
+
+    for (uint32_t q0 = plane_lo + warp * PU; q0 < plane_end; q0 += kWarps * PU) {
+        float t00[PU][SLOTS], t01[PU][SLOTS], t10[PU][SLOTS], t11[PU][SLOTS];
+#pragma unroll
+        for (int u = 0; u < PU; ++u) {
+            const uint32_t q = q0 + u;
+            if (q < plane_end) {
+                const PlaneEntry t = tab[q - plane_lo];
+                const float* xb = p.x + (long long)t.image * p.xbs + (long long)(t.chan & 0xFFFFFF) * p.HW;
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) {
+                    if (valid[s]) {
+                        const float* x0 = xb + in_off[s];
+                        t00[u][s] = x0[0];
+                        t01[u][s] = col1[s] ? x0[1] : 0.0f;
+                        t10[u][s] = row1[s] ? x0[p.W] : 0.0f;
+                        t11[u][s] = (row1[s] && col1[s]) ? x0[p.W + 1] : 0.0f;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PU; ++u) {
+            const uint32_t q = q0 + u;
+            if (q >= plane_end) continue;
+            const PlaneEntry t = tab[q - plane_lo];
+            const uint32_t c = (uint32_t)(t.chan & 0xFFFFFF);
+            float* yp = p.ypool + (long long)t.image * p.pbs + (long long)c * ohow;
+            float* yb = p.y ? p.y + (long long)t.image * p.ybs + (long long)c * p.HW : nullptr;
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                if (!valid[s]) continue;
+                const float a00 = apply_one<ACT, AFFINE>(t00[u][s], t);
+                float best = a00, a01 = 0.0f, a10 = 0.0f, a11 = 0.0f;
+                if (col1[s]) { a01 = apply_one<ACT, AFFINE>(t01[u][s], t); best = pick(best, a01); }
+                if (row1[s]) {
+                    a10 = apply_one<ACT, AFFINE>(t10[u][s], t); best = pick(best, a10);
+                    if (col1[s]) { a11 = apply_one<ACT, AFFINE>(t11[u][s], t); best = pick(best, a11); }
+                }
+                yp[lane + 32u * s] = best;
+                if (yb) {
+                    float* y0 = yb + in_off[s];
+                    y0[0] = a00;
+                    if (col1[s]) y0[1] = a01;
+                    if (row1[s]) {
+                        y0[p.W] = a10;
+                        if (col1[s]) y0[p.W + 1] = a11;
+                    }
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------- launch helpers
 // Rounds of the per-thread loop one block runs (a round = one batch of loads per thread).  Measured
 // on B200: short blocks (2 rounds, 32 KB of input each for the streaming kernel) in many waves give
@@ -619,6 +710,25 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
     plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk / per_plane + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
+    // odd widths, small planes: a warp per plane with per-thread window geometry hoisted out of the loop
+    const char* small_env = getenv("PXE_POOL_SMALLPLANE");     // "0" forces the general kernel (tests, experiments)
+    const uint32_t ohow = (uint32_t)(p.OH * p.OW);
+    const int slots = ohow <= 64 ? 2 : 4;
+    // measured on B200: ahead of the general form with two or four output slots per lane and at least 70 % of the
+    // lane slots in use (13x13 -> 7x7, 19x19 -> 10x10); behind it with one slot (tiny planes) or eight (27x27, 31x31)
+    if (vo == 0 && ohow > 32 && ohow <= 128 && 10 * ohow >= 7 * 32 * (uint32_t)slots && (!small_env || atoi(small_env) != 0)) {
+        const uint32_t n_planes = p.units / per_plane;
+        const uint32_t pu = 8 / slots;
+        const uint32_t planes_per_block = (kThreads / 32) * pu * 2;          // two rounds per warp: short blocks
+        const unsigned blocks = (n_planes + planes_per_block - 1) / planes_per_block;
+        const size_t tab_bytes = (size_t)planes_per_block * sizeof(PlaneEntry);
+        if (slots == 2)
+            epilogue_pool_smallplane_kernel<ACT, AFFINE, 2><<<blocks, kThreads, tab_bytes, s>>>(p, n_planes, planes_per_block);
+        else
+            epilogue_pool_smallplane_kernel<ACT, AFFINE, 4><<<blocks, kThreads, tab_bytes, s>>>(p, n_planes, planes_per_block);
+        PXE_LAUNCH_OK("epilogue_pool_smallplane_kernel");
+        return PXE_OK;
+    }
     // stripped index arithmetic when row pairs tile the tensor: even H, dense x (W already is a multiple of the patch)
     const char* even_env = getenv("PXE_POOL_EVEN");            // "0" forces the general kernel (tests, experiments)
     const bool allow_even = !even_env || atoi(even_env) != 0;

@@ -93,6 +93,45 @@ def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, even_ker
     same(yp.cpu().numpy(), oracle.maxpool(full, 2, 2, 1)[0])
 
 
+@pytest.mark.parametrize("shape", [(3, 5, 7, 7), (2, 37, 13, 13), (2, 9, 19, 19), (1, 11, 27, 27), (1, 3, 33, 33),
+                                   (1, 70, 5, 9), (2, 130, 13, 13), (1, 4, 3, 31)])
+@pytest.mark.parametrize("act", ["leaky", "mish"])
+@pytest.mark.parametrize("padding", [0, 1])
+def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding, monkeypatch):
+    """Odd widths with 33 to 128 pooled outputs per plane (13x13, 19x19 here) run the warp-per-plane form (two or
+    four output slots per lane), the other shapes the general one; the former must equal the general scalar
+    form bit for bit (PXE_POOL_SMALLPLANE=0 forces that one) and the oracle's separate layers, pooled-only and with the full-resolution output, dense and into channel
+    slots of wider buffers, NaNs included."""
+    B, C, H, W = shape
+    x = synth.normal(36, f"sp{shape}", shape)
+    x[0, 0, 0, 0] = np.nan
+    x[-1, -1, -1, -1] = np.nan
+    (g, b, m, v), dp = bn(37, f"spbn{shape}", C, cuda)
+    oh, ow = (H + padding - 2) // 2 + 1, (W + padding - 2) // 2 + 1
+    covered = 2 * oh >= H and 2 * ow >= W
+    got = {}
+    for env in ("1", "0"):
+        monkeypatch.setenv("PXE_POOL_SMALLPLANE", env)
+        wide = torch.full((B, C + 3, oh, ow), 9.0, device=cuda)
+        wide_full = torch.full((B, C + 2, H, W), 7.0, device=cuda)
+        _, yp = ops.conv_epilogue(dev(x, cuda), y=False, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], act=act,
+                                  pool=(2, 2, padding))
+        # the full-resolution output is offered only where the windows cover every input element
+        ops.conv_epilogue(dev(x, cuda), y=wide_full[:, 2:] if covered else False, gamma=dp[0], beta=dp[1], mean=dp[2],
+                          var=dp[3], act=act, pool=(2, 2, padding), y_pool=wide[:, 3:])
+        assert bool((wide[:, :3] == 9.0).all()) and bool((wide_full[:, :2] == 7.0).all())
+        got[env] = (yp.cpu().numpy(), wide[:, 3:].cpu().numpy(), wide_full[:, 2:].cpu().numpy())
+    for a, c in zip(got["1"], got["0"]):
+        same(a, c)
+    yp, yp_slot, full = got["1"]
+    same(yp, yp_slot)
+    ref_full = oracle.conv_epilogue(x, g, b, m, v, None, act)
+    if covered:
+        close(full, ref_full)
+        same(yp, oracle.maxpool(full, 2, 2, padding)[0])
+    close(yp, oracle.maxpool(ref_full, 2, 2, padding)[0])
+
+
 @pytest.mark.parametrize("shape", [(2, 6, 16, 16), (3, 5, 12, 20), (2, 3, 10, 6)])
 def test_folded_pool_into_concat_slot(cuda, oracle, shape):
     """Pooled output AND the full-resolution output stored into channel slots of wider buffers."""
