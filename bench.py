@@ -286,11 +286,14 @@ def run_model(args):
         alt_stem = measure_variant("nhwc", True, "channels-last, and the first convolution + its epilogue as one launch of "
                                                  "this library instead of cuDNN + epilogue")
         torch.cuda.empty_cache()
-        if args.conv_fusion:
-            alt_fusion = measure_variant("nhwc", True, "channels-last, fused first layer, and every other convolution whose cuDNN "
-                                                       "runtime-fusion plan (conv + scale + bias + activation + shortcut in one "
-                                                       "launch) measured faster than cuDNN convolution + this library's epilogue",
-                                         conv_fusion=True)
+        if not args.no_conv_fusion:
+            try:
+                alt_fusion = measure_variant(
+                    "nhwc", True, "channels-last, fused first layer, and every other convolution whose cuDNN runtime-fusion "
+                                  "plan (conv + scale + bias + activation + shortcut in one launch) measured faster than "
+                                  "cuDNN convolution + this library's epilogue", conv_fusion=True)
+            except Exception as e:                     # e.g. an image without the cuDNN frontend: reported, not hidden
+                alt_fusion = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
             torch.cuda.empty_cache()
 
     if rank != 0:
@@ -765,9 +768,10 @@ def main():
                     help="activation layout between layers: nchw = the reference's (BASELINE.json's configs); nhwc = "
                          "channels-last, which lets cuDNN skip its layout conversions (the library's NHWC tier)")
     ap.add_argument("--no-alt-layout", action="store_true", help="skip the extra channels-last measurement")
-    ap.add_argument("--conv-fusion", action="store_true",
-                    help="also measure the channels-last forward with conv + epilogue as one cuDNN runtime-fusion launch per "
-                         "layer where that is faster (adds about a minute of plan compilation and timing)")
+    ap.add_argument("--conv-fusion", action="store_true", help="(the default; kept for older command lines)")
+    ap.add_argument("--no-conv-fusion", action="store_true",
+                    help="skip the channels-last measurement with conv + epilogue as one cuDNN runtime-fusion launch per "
+                         "layer where that is faster (it adds about a minute of plan compilation and timing)")
     ap.add_argument("--fused-stem", action="store_true",
                     help="first convolution + epilogue as one launch of the library (pxe_conv_stem) instead of cuDNN + epilogue")
     ap.add_argument("--cuda-graph", default="auto", choices=["auto", "on", "off"],
