@@ -162,6 +162,19 @@ PXE_API int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_strid
                     int height, int width, int n_pools, const int* kernels, float* const* ys,
                     const long long* y_batch_strides);
 
+/* The conv epilogue folded into the SPP block that follows it (ConvLayer<CUDA>::forward lines
+ * include/cuda/ConvLayer.h:284-307, then the MaxPoolLayer<CUDA>::forward calls of the block,
+ * include/cuda/MaxPoolLayer.h:36-42, and the route that concatenates them, include/cuda/RouteLayer.h:21-44):
+ * x is the RAW convolution output; v = act(a[c] * x + b[c]) (a, b: the table of pxe_fold_bn, or NULL for
+ * the activation alone) is computed once while the plane is staged, stored to y_identity (the block's
+ * pass-through slot; may be NULL) and pooled with every kernel size.  One read of the conv output instead of
+ * an epilogue pass plus the SPP's read.  Values equal pxe_conv_epilogue followed by pxe_spp bit for bit.
+ * PXE_ERR_UNSUPPORTED when a plane (2 * height * width floats) does not fit shared memory. */
+PXE_API int pxe_spp_epilogue(pxe_stream_t stream, const float* x, long long x_batch_stride, int batch, int channels,
+                             int height, int width, const float* a, const float* b, int act, float* y_identity,
+                             long long y_identity_batch_stride, int n_pools, const int* kernels, float* const* ys,
+                             const long long* y_batch_strides);
+
 /* px::upsampleGpu forward (include/UpsampleKernels.cuh:21, src/UpsampleKernels.cu:25-63):
  * nearest-neighbour x stride, y = scale * x (assigned, as the CPU layer does). */
 PXE_API int pxe_upsample(pxe_stream_t stream, const float* x, long long x_batch_stride, float* y,

@@ -133,6 +133,8 @@ PROTOTYPES = {
     "pxe_maxpool": (_i, [_vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "pxe_maxpool_out_dim": (_i, [_i, _i, _i, _i]),
     "pxe_spp": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(_vp), C.POINTER(_ll)]),
+    "pxe_spp_epilogue": (_i, [_vp, _vp, _ll, _i, _i, _i, _i, _vp, _vp, _i, _vp, _ll, _i, C.POINTER(_i), C.POINTER(_vp),
+                              C.POINTER(_ll)]),
     "pxe_upsample": (_i, [_vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i, _f]),
     "pxe_shortcut": (_i, [_vp, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _f, _f, _i]),
     "pxe_shortcut_general": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),

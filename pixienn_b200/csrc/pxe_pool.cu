@@ -68,7 +68,27 @@ struct SppParams {
     int offset[kMaxPools];
     float* y[kMaxPools];
     long long ybs[kMaxPools];
+    // optional conv epilogue applied while the plane is staged (pxe_spp_epilogue): v = act(a[c]*v + b[c]),
+    // also stored to yid (the identity slot of the SPP concat) when that is set
+    const float* a; const float* b; int act;
+    float* yid; long long yidbs;
 };
+
+// the activations exactly as the fused epilogue kernels evaluate them (fast-math forms)
+__device__ __forceinline__ float activate_fast_dyn(int act, float x)
+{
+    switch (act) {
+    case PXE_ACT_LEAKY: return activate<PXE_ACT_LEAKY, true>(x);
+    case PXE_ACT_LOGGY: return activate<PXE_ACT_LOGGY, true>(x);
+    case PXE_ACT_LOGISTIC: return activate<PXE_ACT_LOGISTIC, true>(x);
+    case PXE_ACT_MISH: return activate<PXE_ACT_MISH, true>(x);
+    case PXE_ACT_RELU: return activate<PXE_ACT_RELU, true>(x);
+    case PXE_ACT_SOFTPLUS: return activate<PXE_ACT_SOFTPLUS, true>(x);
+    case PXE_ACT_SWISH: return activate<PXE_ACT_SWISH, true>(x);
+    case PXE_ACT_TANH: return activate<PXE_ACT_TANH, true>(x);
+    default: return x;
+    }
+}
 
 // A k x k maximum is the maximum over rows of the k-wide row maxima: each pool runs as a row pass into a second
 // shared-memory plane and a column pass over it, 2k reads per output instead of k*k (54 instead of 275 for the
@@ -84,7 +104,19 @@ spp_kernel(const SppParams p)
     const int HW = p.H * p.W;
     float* rowmax = tile + HW;
     const float* src = p.x + (long long)b * p.xbs + (long long)c * HW;
-    for (int i = threadIdx.x; i < HW; i += kThreads) tile[i] = src[i];
+    if (p.a || p.act != PXE_ACT_LINEAR || p.yid) {
+        const float ca = p.a ? p.a[c] : 1.0f, cb = p.a ? p.b[c] : 0.0f;
+        float* yid = p.yid ? p.yid + (long long)b * p.yidbs + (long long)c * HW : nullptr;
+        for (int i = threadIdx.x; i < HW; i += kThreads) {
+            float v = src[i];
+            if (p.a) v = fmaf(ca, v, cb);
+            v = activate_fast_dyn(p.act, v);
+            tile[i] = v;
+            if (yid) yid[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < HW; i += kThreads) tile[i] = src[i];
+    }
     __syncthreads();
     for (int k = 0; k < p.n_pools; ++k) {
         const int K = p.kernel[k], off = p.offset[k];
@@ -193,9 +225,11 @@ extern "C" int pxe_maxpool(pxe_stream_t stream, const float* x, long long x_batc
     return PXE_OK;
 }
 
-extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_stride, int batch, int channels,
-                       int height, int width, int n_pools, const int* kernels, float* const* ys,
-                       const long long* y_batch_strides)
+namespace {
+int spp_launch(pxe_stream_t stream, const float* x, long long x_batch_stride, int batch, int channels,
+               int height, int width, int n_pools, const int* kernels, float* const* ys,
+               const long long* y_batch_strides, const float* a, const float* b, int act, float* y_identity,
+               long long y_identity_batch_stride, bool fused)
 {
     PXE_REQUIRE(x && kernels && ys && y_batch_strides, "spp: null pointer");
     PXE_REQUIRE(batch > 0 && channels > 0 && height > 0 && width > 0, "spp: non-positive shape");
@@ -208,6 +242,8 @@ extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_st
     SppParams p{};
     p.x = x; p.xbs = x_batch_stride ? x_batch_stride : chw;
     p.C = channels; p.H = height; p.W = width; p.n_pools = n_pools;
+    p.a = a; p.b = b; p.act = act; p.yid = y_identity;
+    p.yidbs = y_identity_batch_stride ? y_identity_batch_stride : chw;
     for (int k = 0; k < n_pools; ++k) {
         PXE_REQUIRE(kernels[k] > 0 && ys[k] != nullptr, "spp: bad pool %d", k);
         PXE_REQUIRE(y_batch_strides[k] == 0 || y_batch_strides[k] >= chw, "spp: y_batch_stride %d too small", k);
@@ -218,6 +254,9 @@ extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_st
     }
     const size_t smem = 2 * (size_t)height * width * sizeof(float);      // the plane and its row maxima
     if (smem > 48 * 1024 || (long long)batch * channels > 0x7fffffffLL) {
+        if (fused)
+            return set_error(PXE_ERR_UNSUPPORTED, "spp_epilogue: a %d x %d plane does not fit shared memory; run "
+                             "pxe_conv_epilogue and pxe_spp", height, width);
         // plane too large to stage: one generic stride-1 pool per kernel size
         for (int k = 0; k < n_pools; ++k) {
             rc = pxe_maxpool(stream, x, x_batch_stride, ys[k], y_batch_strides[k], nullptr, batch, channels,
@@ -229,6 +268,28 @@ extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_st
     spp_kernel<<<(unsigned)(batch * channels), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
     PXE_LAUNCH_OK("spp_kernel");
     return PXE_OK;
+}
+}  // namespace
+
+extern "C" int pxe_spp(pxe_stream_t stream, const float* x, long long x_batch_stride, int batch, int channels,
+                       int height, int width, int n_pools, const int* kernels, float* const* ys,
+                       const long long* y_batch_strides)
+{
+    return spp_launch(stream, x, x_batch_stride, batch, channels, height, width, n_pools, kernels, ys, y_batch_strides,
+                      nullptr, nullptr, PXE_ACT_LINEAR, nullptr, 0, false);
+}
+
+extern "C" int pxe_spp_epilogue(pxe_stream_t stream, const float* x, long long x_batch_stride, int batch, int channels,
+                                int height, int width, const float* a, const float* b, int act, float* y_identity,
+                                long long y_identity_batch_stride, int n_pools, const int* kernels, float* const* ys,
+                                const long long* y_batch_strides)
+{
+    PXE_REQUIRE((a == nullptr) == (b == nullptr), "spp_epilogue: a and b come together");
+    PXE_REQUIRE(valid_activation(act), "spp_epilogue: unknown activation %d", act);
+    const long long chw = (long long)channels * height * width;
+    PXE_REQUIRE(y_identity_batch_stride == 0 || y_identity_batch_stride >= chw, "spp_epilogue: y_identity_batch_stride too small");
+    return spp_launch(stream, x, x_batch_stride, batch, channels, height, width, n_pools, kernels, ys, y_batch_strides,
+                      a, b, act, y_identity, y_identity_batch_stride, true);
 }
 
 extern "C" int pxe_avgpool(pxe_stream_t stream, const float* x, long long x_batch_stride, float* y,

@@ -161,8 +161,11 @@ def maxpool(x: torch.Tensor, kernel: int, stride: int, padding: Optional[int] = 
     return (out, idx) if with_indexes else out
 
 
-def spp(x: torch.Tensor, kernels: Sequence[int], outs: Sequence[torch.Tensor]) -> Sequence[torch.Tensor]:
-    """Stride-1 max pools of one input (default padding kernel-1), one output per kernel size."""
+def spp(x: torch.Tensor, kernels: Sequence[int], outs: Sequence[torch.Tensor], *, a: Optional[torch.Tensor] = None,
+        b: Optional[torch.Tensor] = None, act=None, y_identity: Optional[torch.Tensor] = None) -> Sequence[torch.Tensor]:
+    """Stride-1 max pools of one input (default padding kernel-1), one output per kernel size.  With ``act``
+    (and optionally the folded coefficients ``a``, ``b`` of fold_bn) ``x`` is a raw convolution output: the
+    epilogue is applied as the planes are read, its result goes to ``y_identity`` and into every pool."""
     xp, xbs = _slot(x, "x")
     B, Cc, H, W = x.shape
     n = len(kernels)
@@ -174,7 +177,14 @@ def spp(x: torch.Tensor, kernels: Sequence[int], outs: Sequence[torch.Tensor]) -
             raise ValueError("spp outputs have the input's shape")
         ptrs[i], strides[i] = _slot(o, f"outs[{i}]")
     ks = (C.c_int * n)(*[int(k) for k in kernels])
-    capi.check(capi.lib().pxe_spp(_stream(), xp, xbs, B, Cc, H, W, n, ks, ptrs, strides))
+    if act is None and a is None and y_identity is None:
+        capi.check(capi.lib().pxe_spp(_stream(), xp, xbs, B, Cc, H, W, n, ks, ptrs, strides))
+        return outs
+    if y_identity is not None and tuple(y_identity.shape) != (B, Cc, H, W):
+        raise ValueError("y_identity has the input's shape")
+    ip, ibs = _slot(y_identity, "y_identity") if y_identity is not None else (None, 0)
+    capi.check(capi.lib().pxe_spp_epilogue(_stream(), xp, xbs, B, Cc, H, W, _vec(a, Cc, "a"), _vec(b, Cc, "b"),
+                                           _act(act if act is not None else "linear"), ip, ibs, n, ks, ptrs, strides))
     return outs
 
 

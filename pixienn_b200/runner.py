@@ -148,6 +148,8 @@ class Runner:
             from . import cudnn_fused
             self.fused_conv = cudnn_fused.FusedConvPlanner(device)
         self.fused_conv_launches = 0
+        self.fold_spp = fuse           # NCHW: a conv's epilogue runs inside the SPP block that reads it next
+        self._spp_pending = None
         self.dets = ops.DetectionBuffer(det_capacity, device)
         self.head_marks = []           # device copies of the running detection count after each YOLO head
         self.centernet_out = []        # (dets, counts) per centernet layer of the last forward
@@ -216,7 +218,8 @@ class Runner:
         for si, st in enumerate(self.plan.steps):
             l = L[st.layer]
             if st.op == "conv":
-                self._conv(st, l, T, bufs)
+                nxt = self.plan.steps[si + 1] if si + 1 < len(self.plan.steps) else None
+                self._conv(st, l, T, bufs, nxt)
             elif st.op == "alias":
                 if st.inputs:
                     T[st.layer] = T[st.inputs[0]]
@@ -257,10 +260,17 @@ class Runner:
                             ops.maxpool_nhwc(xin, k, 1, k - 1, out=firsts[i])
                         prev_k, prev_t = k, firsts[i]
                     self.launches += len(firsts) - 1
+                elif self._spp_pending is not None:
+                    raw, cd, fa, fb, act = self._spp_pending
+                    self._spp_pending = None
+                    ops.spp(raw, [L[g].kernel for g in st.spp_layers], firsts, a=fa, b=fb, act=act, y_identity=cd[0])
+                    rest.append(cd[1:])
+                    firsts.append(cd[0])
                 else:
                     ops.spp(xin, [L[g].kernel for g in st.spp_layers], firsts)
                 self.launches += 1
-                tm.end(s, "spp", 4 * xin.numel() * (1 + len(firsts)))
+                folded = len(firsts) > len(st.spp_layers)
+                tm.end(s, "epilogue+spp" if folded else "spp", 4 * xin.numel() * (1 + len(firsts)))
                 for f, r in zip(firsts, rest):
                     self._extra_copies(f, r)
             elif st.op == "upsample":
@@ -391,8 +401,9 @@ class Runner:
                     del T[t]
                     bufs.pop(t, None)
 
-    def _conv(self, st: graph.Step, l: graph.Layer, T, bufs) -> None:
+    def _conv(self, st: graph.Step, l: graph.Layer, T, bufs, nxt: Optional[graph.Step] = None) -> None:
         w = self.w[l.index]
+        self._spp_pending = None
         xin = T[st.inputs[0]]
         tm = self.timer
         if l.index == 0 and self.stem is not None:
@@ -420,6 +431,21 @@ class Runner:
         n = raw.numel()
         if self.nhwc:
             return self._conv_epilogue_nhwc(st, l, T, bufs, raw, w)
+        # an SPP block reads this conv next: its kernel applies the epilogue while it stages each plane, writes the
+        # block's pass-through slot and the pools from one read of the raw output (pxe_spp_epilogue)
+        if (self.fold_spp and nxt is not None and nxt.op == "spp" and nxt.inputs and nxt.inputs[0] == l.index
+                and st.fused_pool is None and st.fused_shortcut is None and st.dests
+                and 2 * raw.shape[2] * raw.shape[3] * 4 <= 48 * 1024):
+            if "a" not in w:
+                if l.batch_norm:
+                    w["a"], w["b"] = ops.fold_bn(l.filters, self.device, gamma=w["scales"], beta=w["biases"],
+                                                 mean=w["rolling_mean"], var=w["rolling_var"], eps_mode=self.eps_mode)
+                else:
+                    w["a"], w["b"] = ops.fold_bn(l.filters, self.device, bias=w["biases"])
+            dests = self._dest_tensors(bufs, st.dests, l)
+            self._spp_pending = (raw, dests, w["a"], w["b"], l.activation)
+            T[l.index] = dests[0]
+            return
         bn = dict(gamma=w["scales"], beta=w["biases"], mean=w["rolling_mean"], var=w["rolling_var"],
                   eps_mode=self.eps_mode) if l.batch_norm else dict(bias=w["biases"])
         if st.fused_pool is not None:

@@ -51,6 +51,30 @@ def test_fused_plan_equals_layer_by_layer(cuda, name, hw, batch, head_bias):
     assert fused.contiguous_copies == 0
 
 
+def test_spp_block_takes_the_conv_epilogue(cuda):
+    """YOLOv7's SPP block: the conv before it hands its raw output to the block, which applies the epilogue while
+    it stages each plane (one launch, "epilogue+spp"); every layer's tensor equals the run that keeps them apart."""
+    model = graph.parse_model(presets.PRESETS["yolov7"](128, 128))
+    weights = synth_weights(model, 7)
+    x = make_input(8, 2, model)
+    runs = []
+    for fold in (True, False):
+        r = Runner(model, weights, 2, cuda)
+        r.fold_spp = fold
+        r.keep = set(range(len(model.layers)))
+        r.timer.enabled = True
+        r.forward(torch.from_numpy(x).to(cuda))
+        torch.cuda.synchronize()
+        runs.append(r)
+    a, b = runs
+    assert "epilogue+spp" in a.timer.summary() and "epilogue+spp" not in b.timer.summary()
+    assert "spp" in b.timer.summary() and a.launches == b.launches - 1
+    assert set(a.kept) == set(b.kept)
+    for i in sorted(a.kept):
+        assert torch.equal(a.kept[i], b.kept[i]), f"layer {i} ({model.layers[i].type})"
+    assert a.detections()[0].tobytes() == b.detections()[0].tobytes()
+
+
 def test_tiny416_matches_cpu_reference_path(cuda, oracle):
     """Config 0: YOLOv3-tiny, batch 1, 416x416, seeded weights, against the CPU forward.
     (i)  every conv epilogue, fed the CPU path's own conv output, within 1e-5 rel / 1e-6 abs;

@@ -232,3 +232,42 @@ def test_avgpool(cuda, oracle, shape):
     wide = torch.zeros((shape[0], shape[1] + 3, shape[2], shape[3]), device=cuda)
     wide[:, 3:] = dev(x, cuda)
     close(ops.avgpool(wide[:, 3:]).cpu().numpy(), ref)          # a channel slot of a wider buffer
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 20, 20), (1, 3, 13, 13), (2, 5, 19, 19), (1, 2, 5, 40)])
+@pytest.mark.parametrize("act", ["leaky", "mish", "swish", "linear"])
+@pytest.mark.parametrize("use_bn", [True, False])
+def test_spp_block_with_folded_epilogue(cuda, oracle, shape, act, use_bn):
+    """pxe_spp_epilogue on a raw conv output == pxe_conv_epilogue followed by pxe_spp, bit for bit: the pass-through
+    slot and the three pools, all as channel slots of the SPP concat buffer; and the oracle's separate layers."""
+    B, C, H, W = shape
+    x = synth.normal(38, f"sppe{shape}", shape)
+    x[0, 0, 0, 0] = np.nan
+    (g, b, m, v), dp = bn(39, f"sppebn{shape}", C, cuda)
+    xd = dev(x, cuda)
+    if use_bn:
+        fa, fb = ops.fold_bn(C, cuda, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3])
+        full = ops.conv_epilogue(dev(x, cuda), gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], act=act)
+        ref_full = oracle.conv_epilogue(x, g, b, m, v, None, act)
+    else:
+        fa = fb = None
+        full = ops.conv_epilogue(dev(x, cuda), act=act)
+        ref_full = oracle.activate(act, x)
+    want = torch.zeros((B, 4 * C, H, W), device=cuda)
+    ops.spp(full, [13, 9, 5], [want[:, 0:C], want[:, C:2 * C], want[:, 2 * C:3 * C]])
+    want[:, 3 * C:] = full
+    got = torch.full((B, 4 * C + 2, H, W), 5.0, device=cuda)
+    ops.spp(xd, [13, 9, 5], [got[:, 0:C], got[:, C:2 * C], got[:, 2 * C:3 * C]], a=fa, b=fb, act=act,
+            y_identity=got[:, 3 * C:4 * C])
+    same(got[:, :4 * C].cpu().numpy(), want.cpu().numpy())
+    assert bool((got[:, 4 * C:] == 5.0).all())
+    assert np.array_equal(xd.cpu().numpy()[~np.isnan(x)], x[~np.isnan(x)])          # the raw input is not modified
+    close(got[:, 3 * C:4 * C].cpu().numpy(), ref_full)
+    # without an identity destination only the pools are written
+    got2 = torch.zeros((B, 3 * C, H, W), device=cuda)
+    ops.spp(xd, [13, 9, 5], [got2[:, 0:C], got2[:, C:2 * C], got2[:, 2 * C:]], a=fa, b=fb, act=act)
+    same(got2.cpu().numpy(), want[:, :3 * C].cpu().numpy())
+    # a plane that does not fit shared memory is refused, not silently run another way
+    big = torch.zeros((1, 1, 96, 96), device=cuda)
+    with pytest.raises(Exception):
+        ops.spp(big, [5], [torch.zeros_like(big)], act="leaky")
