@@ -28,9 +28,21 @@ def _act(a) -> int:
     return ACT[a] if isinstance(a, str) else int(a)
 
 
+def _check_device(index: int, name: str) -> None:
+    """The library launches on the calling thread's current device and on torch's current stream of that
+    device, so a tensor of another GPU must not reach it: without peer access the kernel would fault, with it
+    the work would silently run on the wrong GPU.  Callers select the device first (``torch.cuda.device``;
+    Runner and PipelinedPredictor do it themselves)."""
+    cur = torch.cuda.current_device()
+    if index != cur:
+        raise ValueError(f"{name} lives on cuda:{index} but the current device is cuda:{cur}; "
+                         f"wrap the call in torch.cuda.device({index})")
+
+
 def _check_f32_cuda(t: torch.Tensor, name: str) -> None:
     if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32):
         raise TypeError(f"{name} must be a float32 CUDA tensor")
+    _check_device(t.device.index, name)
 
 
 def _slot(t: Optional[torch.Tensor], name: str):
@@ -394,6 +406,7 @@ def nms_device(dets: torch.Tensor, n: int, threshold: float, out: Optional[torch
     device; the first ``count`` records of ``out`` are the survivors in the reference's order."""
     if dets.dtype != torch.int32 or dets.dim() != 2 or dets.shape[1] != 8 or not dets.is_cuda or not dets.is_contiguous():
         raise ValueError("dets must be a contiguous int32 CUDA tensor of shape [capacity, 8]")
+    _check_device(dets.device.index, "dets")
     n = int(n)
     if n < 0 or n > dets.shape[0]:
         raise ValueError(f"n = {n} outside 0..{dets.shape[0]}")

@@ -8,6 +8,7 @@ delta / preActivation buffers: tensors live from their producer to their last re
 """
 from __future__ import annotations
 
+import functools
 import math
 from typing import Dict, List, Optional
 
@@ -18,11 +19,15 @@ import torch.nn.functional as F
 from . import graph, ops, synth
 
 
-def synth_weights(model: graph.Model, seed: int = 1234, head_bias: float = 0.0) -> Dict[int, Dict[str, np.ndarray]]:
+def synth_weights(model: graph.Model, seed: int = 1234, head_bias: float = 0.0, head_gain=1.0,
+                  class_bias: float = 0.0) -> Dict[int, Dict[str, np.ndarray]]:
     """Seeded random-init weights: conv N(0, sqrt(2/fan_in)) with fan_in = k*k*C_in/groups
     (include/ConvLayer.h:111-115); BN gamma U(0.5,1.5), beta N(0,0.1), running mean N(0,0.1),
     running var U(0.5,1.5); non-BN conv bias 0.  ``head_bias`` is added to the objectness bias of
-    convolutions feeding a YOLO layer (0 keeps the plain init)."""
+    convolutions feeding a YOLO layer (0 keeps the plain init), ``class_bias`` to their class biases, and
+    ``head_gain`` (a number, or {conv layer index: number}) multiplies those convolutions' weights: with the
+    plain init a deep residual graph feeds its heads logits of magnitude 1e6 (every box either certain or
+    absent), so tests that want a realistic candidate count scale the head back to logits of order one."""
     out: Dict[int, Dict[str, np.ndarray]] = {}
     for l in model.layers:
         if l.type in ("connected", "conn"):
@@ -49,12 +54,29 @@ def synth_weights(model: graph.Model, seed: int = 1234, head_bias: float = 0.0) 
         else:
             bias = np.zeros(l.filters, np.float32)
             nxt = model.layers[l.index + 1] if l.index + 1 < len(model.layers) else None
-            if head_bias != 0.0 and nxt is not None and nxt.type == "yolo":
+            if nxt is not None and nxt.type == "yolo":
                 entries = l.filters // len(nxt.params["mask"])
-                bias[4::entries] = head_bias
+                if class_bias != 0.0:
+                    for e in range(5, entries):
+                        bias[e::entries] = class_bias
+                if head_bias != 0.0:
+                    bias[4::entries] = head_bias
+                g = head_gain.get(l.index, 1.0) if isinstance(head_gain, dict) else head_gain
+                if g != 1.0:
+                    d["weights"] = (w * np.float32(g)).astype(np.float32)
             d["biases"] = bias
         out[l.index] = d
     return out
+
+
+def _on_own_device(method):
+    """Runs a method with the object's device current: the library launches on the current device and stream,
+    whatever device the tensors live on."""
+    @functools.wraps(method)
+    def wrapper(self, *args, **kwargs):
+        with torch.cuda.device(self._device_of()):
+            return method(self, *args, **kwargs)
+    return wrapper
 
 
 class OpTimer:
@@ -98,7 +120,19 @@ class Runner:
                  fused_stem: bool = False, conv_fusion: bool = False):
         if layout not in ("nchw", "nhwc"):
             raise ValueError("layout must be 'nchw' (the reference's) or 'nhwc' (channels-last)")
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise ValueError(f"Runner needs a CUDA device, got {device}")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
         self.model, self.batch, self.device = model, batch, device
+        self._setup(weights, fuse, raw_heads, det_capacity, threshold, batch_id_offset, eps_mode, layout,
+                    fused_stem, conv_fusion)
+
+    @_on_own_device
+    def _setup(self, weights, fuse, raw_heads, det_capacity, threshold, batch_id_offset, eps_mode, layout,
+               fused_stem, conv_fusion):
+        model, batch, device = self.model, self.batch, self.device
         # "nhwc": every activation tensor is channels-last, so cuDNN runs its tensor-core convolution kernels
         # without converting the layout around each of them; the epilogue path uses the library's NHWC tier and
         # heads are transposed to NCHW for the decoders.  Results equal the "nchw" run up to the convolutions'
@@ -160,8 +194,18 @@ class Runner:
         self.region_per_image = False   # False: RegionLayer::addDetects as written (every image decodes image 0's boxes)
         self.keep: Optional[set] = None  # layer indices whose tensors to retain in self.kept
         self.kept: Dict[int, torch.Tensor] = {}
+        # probe points for whole-graph comparisons with another implementation of the same model:
+        #   conv_override(layer, raw) -> tensor   replaces a convolution's raw output (before its epilogue)
+        #   step_hook(step_index, step, T, bufs)  runs after every step, before dead tensors are released;
+        #                                         T maps layer index -> the tensor that holds its value,
+        #                                         bufs maps route layer index -> its concat buffer
+        self.conv_override = None
+        self.step_hook = None
 
     # ------------------------------------------------------------------ helpers
+    def _device_of(self):
+        return self.device
+
     def _empty(self, shape) -> torch.Tensor:
         if self.nhwc:
             return ops.empty_nhwc(shape, self.device)
@@ -202,6 +246,7 @@ class Runner:
             self.timer.end(s, "concat", 8 * src.numel())
 
     # ------------------------------------------------------------------ forward
+    @_on_own_device
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> None:
         """Enqueues one forward pass of the whole graph for the batch ``x`` [B,C,H,W] (on the device)."""
@@ -395,6 +440,8 @@ class Runner:
                 for p in st.produces:
                     if p in self.keep and p in T:
                         self.kept[p] = T[p]
+            if self.step_hook is not None:
+                self.step_hook(si, st, T, bufs)
             # release tensors nobody reads any more
             for t in st.inputs:
                 if self.plan.last_use.get(t) == si and t in T and t != -1:
@@ -423,6 +470,8 @@ class Runner:
         s = tm.begin()
         raw = F.conv2d(xin, w["weights"], None, l.stride, l.padding, l.dilation, l.groups)
         tm.end(s, "conv(cudnn)", 0)
+        if self.conv_override is not None:
+            raw = self.conv_override(l.index, raw)
         if self.nhwc and not raw.is_contiguous(memory_format=torch.channels_last):
             raw = raw.contiguous(memory_format=torch.channels_last)      # 1-pixel or 1-channel outputs only
         if st.head_raw:
@@ -597,6 +646,7 @@ class Runner:
         T[st.layer] = act
 
     # ------------------------------------------------------------------ CUDA graph
+    @_on_own_device
     def capture(self, x: torch.Tensor) -> "torch.cuda.CUDAGraph":
         """Captures one forward pass on ``x`` (a device tensor that stays allocated: later replays read whatever
         it holds then) into a CUDA graph and returns it.  At small batches a forward is a few hundred launches of
@@ -640,6 +690,7 @@ class Runner:
             heads.append(np.concatenate(ops.centernet_to_host(d, c)))
         return heads
 
+    @_on_own_device
     def predict(self, host_batch: torch.Tensor, nms_threshold: Optional[float] = None, nms_on_device: bool = False):
         """The call a user makes: host images in (pinned memory), detections out.  Mirrors
         Model::predictBatchImageList (include/Model.h:951-1060) from the H2D copy on.  With
@@ -697,6 +748,9 @@ class PipelinedPredictor:
                 self.graphs.append(runner.capture(self.x[slot]))
             runner.dets = self.bufs[0]
 
+    def _device_of(self):
+        return self.r.device
+
     def _stage(self, host_batch, slot):
         with torch.cuda.stream(self.h2d):
             if self.x_free[slot] is not None:
@@ -729,6 +783,7 @@ class PipelinedPredictor:
         self.out_done[slot].synchronize()
         return self.pinned[slot][:n].numpy().view(ops.DET_DTYPE).reshape(-1), total
 
+    @_on_own_device
     def submit(self, host_batch: torch.Tensor):
         slot = self.n % 2
         self.n += 1
@@ -750,6 +805,7 @@ class PipelinedPredictor:
         self.pending = (slot, done)
         return self._result(*finished) if finished is not None else None
 
+    @_on_own_device
     def drain(self):
         if self.pending is None:
             return None

@@ -9,9 +9,11 @@ normalisation ``scales[F]``, ``rollingMean[F]``, ``rollingVar[F]``, then
 the version (Model.h:1979); files it saves carry version 0.1, for which 4 bytes is also what it
 reads back.
 
-Only convolution blocks are handled (the layers of the graphs this package runs); a file with
-bytes left over, or too short, is an error exactly as in the reference ("Did not fully read
-weights file").
+A connected layer stores (ConnLayer::loadWeights, include/ConnLayer.h:119-135): ``biases[out]``,
+``weights[out * in]``, and with batch normalisation ``scales[out]``, ``rollingMean[out]``,
+``rollingVar[out]`` -- note the weights come before the normalisation parameters here, unlike a
+convolution.  Every other layer type this package plans carries no weights.  A file with bytes left
+over, or too short, is an error exactly as in the reference ("Did not fully read weights file").
 """
 from __future__ import annotations
 
@@ -25,6 +27,25 @@ from . import graph
 
 def _seen_bytes(major: int, minor: int) -> int:
     return 8 if (major * 10 + minor) >= 2 and major < 1000 and minor < 1000 else 4
+
+
+_NO_WEIGHTS = ("maxpool", "upsample", "route", "shortcut", "yolo", "centernet", "region", "softmax", "avgpool",
+               "dropout", "detection")
+
+
+def _block(l: graph.Layer):
+    """The arrays of one layer's block, in file order, as (name, shape) pairs."""
+    norm = [("scales", (l.filters,)), ("rolling_mean", (l.filters,)), ("rolling_var", (l.filters,))]
+    if l.type == "conv":
+        cin = l.in_shape[0] // l.groups
+        return [("biases", (l.filters,))] + (norm if l.batch_norm else []) + \
+               [("weights", (l.filters, cin, l.kernel, l.kernel))]
+    if l.type in ("connected", "conn"):
+        inputs = l.in_shape[0] * l.in_shape[1] * l.in_shape[2]
+        return [("biases", (l.filters,)), ("weights", (l.filters, inputs))] + (norm if l.batch_norm else [])
+    if l.type in _NO_WEIGHTS:
+        return []
+    raise ValueError(f"layer {l.index}: no weights-file layout known for layer type {l.type!r}")
 
 
 def load(path: str, model: graph.Model) -> Tuple[Dict[int, Dict[str, np.ndarray]], dict]:
@@ -49,16 +70,8 @@ def load(path: str, model: graph.Model) -> Tuple[Dict[int, Dict[str, np.ndarray]
         return a
 
     for l in model.layers:
-        if l.type != "conv":
-            continue
-        d = {"biases": take(l.filters)}
-        if l.batch_norm:
-            d["scales"] = take(l.filters)
-            d["rolling_mean"] = take(l.filters)
-            d["rolling_var"] = take(l.filters)
-        cin = l.in_shape[0] // l.groups
-        d["weights"] = take(l.filters * cin * l.kernel * l.kernel).reshape(l.filters, cin, l.kernel, l.kernel)
-        out[l.index] = d
+        for k, shape in _block(l):
+            out.setdefault(l.index, {})[k] = take(int(np.prod(shape))).reshape(shape)
     if pos != len(data):
         raise ValueError(f"{path}: did not fully read weights file; read {pos} bytes, file has {len(data)}")
     return out, {"major": major, "minor": minor, "revision": revision, "seen": seen}
@@ -71,13 +84,9 @@ def save(path: str, model: graph.Model, weights: Dict[int, Dict[str, np.ndarray]
     chunks = [struct.pack("<3i", major, minor, revision),
               int(seen).to_bytes(_seen_bytes(major, minor), "little")]
     for l in model.layers:
-        if l.type != "conv":
-            continue
-        d = weights[l.index]
-        order = ["biases"] + (["scales", "rolling_mean", "rolling_var"] if l.batch_norm else []) + ["weights"]
-        for k in order:
-            a = np.ascontiguousarray(d[k], "<f4")
-            want = l.filters if k != "weights" else l.filters * (l.in_shape[0] // l.groups) * l.kernel * l.kernel
+        for k, shape in _block(l):
+            a = np.ascontiguousarray(weights[l.index][k], "<f4")
+            want = int(np.prod(shape))
             if a.size != want:
                 raise ValueError(f"layer {l.index}: {k} has {a.size} values, expected {want}")
             chunks.append(a.tobytes())

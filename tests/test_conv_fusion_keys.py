@@ -1,5 +1,6 @@
 """Host logic of the optional cuDNN conv + epilogue fusion: which layers are eligible and how a destination
 that is a channel slot of a concat buffer is described to cuDNN (no GPU, no cuDNN call)."""
+import pytest
 import torch
 
 from pixienn_b200.cudnn_fused import FusedConvPlanner, _pixel_stride
@@ -34,3 +35,13 @@ def test_key_accepts_what_the_graph_can_express_and_nothing_else():
     # keys work on meta tensors: the runner asks before it allocates the destination
     probe = torch.empty_strided((2, 16, 16, 16), (16 * 16 * 24, 1, 16 * 24, 24), device="meta")
     assert FusedConvPlanner.key(x, w, 1, 1, "leaky", probe, None, "linear")[6] == 24
+
+
+def test_tensor_of_another_device_is_refused(monkeypatch):
+    """The library launches on the current device: a tensor that lives elsewhere is refused before any launch."""
+    import torch
+    from pixienn_b200 import ops
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    ops._check_device(0, "x")
+    with pytest.raises(ValueError, match="cuda:1 but the current device is cuda:0"):
+        ops._check_device(1, "x")

@@ -50,3 +50,32 @@ def test_wrong_length_is_an_error(tmp_path):
     open(path, "wb").write(blob[:-8])
     with pytest.raises(ValueError, match="file ends inside"):
         weights.load(path, model)
+
+
+def test_connected_layer_blocks(tmp_path):
+    """A connected layer's block is biases, weights, then (with batch normalisation) scales, mean, variance
+    (include/ConnLayer.h:119-135); a convolution behind it starts where the reference's reader would be."""
+    doc = {"model": {"channels": 3, "height": 8, "width": 8, "layers": [
+        {"type": "conv", "filters": 4, "kernel": 3, "stride": 2, "pad": True, "batch_normalize": True, "activation": "leaky"},
+        {"type": "connected", "output": 10, "activation": "leaky", "batch_normalize": True},
+        {"type": "connected", "output": 6, "activation": "linear"},
+        {"type": "softmax"},
+    ]}}
+    model = graph.parse_model(doc)
+    w = synth_weights(model, 6)
+    path = str(tmp_path / "conn.weights")
+    n = weights.save(path, model, w)
+    conv = 4 * 4 + 4 * 3 * 9
+    conn1 = 10 + 10 * 64 + 3 * 10
+    conn2 = 6 + 6 * 10
+    assert n == 16 + 4 * (conv + conn1 + conn2)
+    raw = open(path, "rb").read()
+    base = 16 + 4 * conv
+    assert np.array_equal(np.frombuffer(raw, "<f4", 10, base), w[1]["biases"])
+    assert np.array_equal(np.frombuffer(raw, "<f4", 640, base + 40).reshape(10, 64), w[1]["weights"])
+    assert np.array_equal(np.frombuffer(raw, "<f4", 10, base + 40 + 2560), w[1]["scales"])
+    back, _ = weights.load(path, model)
+    for i, d in w.items():
+        assert set(back[i]) == set(d)
+        for k, v in d.items():
+            assert np.array_equal(back[i][k], v), (i, k)
