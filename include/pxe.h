@@ -289,6 +289,11 @@ typedef struct pxe_centernet_decode_desc {
     float threshold;
     int max_detections;         /* CenterNetLayer max_detections (default 100), <= 1024 */
     int batch_id_offset;
+    int candidate_capacity;     /* 0 = default.  Local maxima one image may list before it is redone by the
+                                   tile-by-tile pass, which reduces every tile to its best max_detections (the
+                                   result is the same either way; a heat map with plateaus, where every cell is a
+                                   maximum, is the case that overflows).  Values below tiles x classes x
+                                   max_detections are raised to that; values above the default are refused. */
 } pxe_centernet_decode_desc;
 
 PXE_API size_t pxe_centernet_decode_workspace_bytes(int batch, int classes, int height, int width,

@@ -89,6 +89,7 @@ class CenterNetDecodeDesc(C.Structure):
         ("batch", C.c_int), ("classes", C.c_int), ("height", C.c_int), ("width", C.c_int),
         ("image_width", C.c_int), ("image_height", C.c_int),
         ("threshold", C.c_float), ("max_detections", C.c_int), ("batch_id_offset", C.c_int),
+        ("candidate_capacity", C.c_int),
     ]
 
 

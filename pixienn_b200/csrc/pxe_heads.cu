@@ -300,20 +300,35 @@ centernet_activate_kernel(const CnActParams p)
 constexpr int kCnTileH = 32, kCnTileW = 64, kCnThreads = 256;
 constexpr int kCnCells = kCnTileH * kCnTileW;
 constexpr int kCnMaxK = 1024;
-constexpr int kCnSlotCap = 256;          // keys one tile may pass on without reducing them (at least K)
+constexpr int kCnBins = 1024;            // score histogram per image (leading bits of the key above the threshold)
+constexpr int kCnListCap = 32768;        // default length of an image's candidate list
 
 struct CnParams {
     pxe_centernet_decode_desc d;
     long long hbs, sbs, obs;
-    int tiles_x, tiles_y;
     int K;
-    int slots;                       // blocks per image (tiles x classes)
-    int slot_cap;                    // keys a block may pass on: block s of image b owns cand[(b*slots+s)*slot_cap ...]
-    float lo;                        // pre-filter: a cell with (value >= lo) false cannot reach the threshold
-    float lo_list;                   // work-list bound, a margin below lo (see centernet_peaks_kernel)
-    unsigned long long* cand;        // [batch][slots][K] sortable keys, unordered inside a slot
-    int* cand_cnt;                   // [batch][slots]
-    unsigned long long* list;        // [batch][slots*K] per-image compacted list, used when it exceeds shared memory
+    // streaming filter: a group is four consecutive cells of a row; a warp walks groups_per_warp of them
+    uint32_t groups, groups_per_warp;  // per image
+    FastDiv div_row, div_h;            // by groups per row, by height
+    float lo_raw;                    // a cell whose stored value is below this cannot reach the threshold
+    float margin;                    // stored values further apart than this have scores in the same order, for certain
+    float sat_raw;                   // ... unless the centre value is at or above this (the sigmoid flattens out)
+    uint32_t bin_base; int bin_shift;  // activated head: bin = min(kCnBins-1, (score bits - bin_base) >> bin_shift)
+    float bin_lo, bin_scale, bin_width;  // logits: bin = (min(value, sat_raw) - bin_lo) * bin_scale, clamped
+    int bin_slack;                     // bins below the one holding the K-th candidate that are staged as well
+    int sample_stride, sample_want;    // the sampling pass reads every sample_stride-th row and wants this many hot cells
+    // tile pass (only for images whose list overflowed or whose raised bound left too few detections)
+    int tiles_x, tiles_y;
+    float lo;                        // activated-space pre-filter of the tile pass
+    float lo_list;                   // its work-list bound, a margin below lo (see centernet_peaks_kernel)
+    int cap;                         // keys per image list
+    unsigned long long* list;        // [batch][cap] sortable keys, in no particular order
+    unsigned long long* list2;       // [batch][cap] valid keys, compacted, when a list does not fit shared memory
+    int* count;                      // [batch] keys the streaming filter found (it stores only the first cap)
+    int* count2;                     // [batch] keys the tile pass stored for an image it redid
+    float* bound;                    // [batch] listing bound of the image: lo_raw, or higher when the sample allowed
+    int* redo;                       // images for the tile pass: [0] how many, [1 + i] which (key list overflowed, or a
+                                     // raised bound left fewer than K detections)
     pxe_detection* dets; int* counts;
 };
 
@@ -425,23 +440,383 @@ __device__ __forceinline__ bool cn_valid(const float* size, const float* off, lo
     return isfinite(bw) && isfinite(bh) && isfinite(ox) && isfinite(oy) && bw > 0.0f && bh > 0.0f;
 }
 
-// One block per (32x64 tile, class, image).
+// The decode runs as a short chain of launches.
+//
+//  centernet_sample_kernel   one block per image reads every 16th row of the heat map into a histogram of the stored
+//                            values and, when the sample holds enough cells above the threshold, raises the
+//                            image's listing bound to the histogram bin above which some K/4 sampled cells lie --
+//                            about 16 x that many cells of the whole map, several times the K an image keeps.
+//  centernet_filter_kernel   streams the heat map once, comparing stored values only (logits, when the head is not
+//                            yet activated).  Four consecutive cells none of which reaches the image's listing
+//                            bound -- 99 in 100 for a typical head -- cost a 128-bit load and a compare.  The
+//                            others are collected and looked at 32 at a time: a cell is listed when it reaches the
+//                            bound and no neighbour is larger by more than a margin; it becomes a 64-bit key
+//                            (stored value, cell index, and one bit that says whether every neighbour is smaller by
+//                            more than the margin) in its image's list.  No exponential is evaluated here.
+//  centernet_peaks_kernel    the tile-by-tile pass, which needs no bound and reduces each tile to its best K valid
+//                            candidates.  It runs after the selection, only for the images the selection put on
+//                            its list: those whose key list overflowed (a plateau makes every cell a maximum) and
+//                            those whose raised bound turned out to leave fewer than K detections.
+//  centernet_select_kernel   one block per image gives the listed keys the exact treatment -- the reference's
+//                            activation expression, the threshold test on the score, the 3x3 test on the
+//                            neighbours' exact scores where the margin did not settle it, size / offset validity --
+//                            sorts them by (score, index) and writes the K best as boxes.  Run again for the images
+//                            the tile pass redid.
+//
+// Why comparing stored values is enough for most cells.  The activation 1/(1+exp(-v)) is increasing with slope
+// s(1-s).  For a centre value v < 8 (in activated units: after the bias) the slope on [v - m, v + m] is at least
+// 3.3e-4, so two values at least m = 0.01 apart have true scores at least 3.3e-6 apart, an order of magnitude more
+// than the rounding of expf, the add and the division (a few units of 6e-8).  So "a neighbour exceeds the centre by
+// more than m" settles "its score is strictly greater", and "every neighbour is below the centre by more than m"
+// settles the opposite; only the cases in between, and centres at or above 8 (where the sigmoid flattens out and
+// different logits share a score), need the neighbours' exact scores.  The bias is added only where a score is
+// evaluated: v + bias rounds monotonically, and its rounding error (1e-6 at these magnitudes) is far inside the
+// margin.  A head that is already activated is compared exactly (margin 0).
+//
+// Why a raised bound loses nothing.  Cells below the bound are never listed.  If at least K of the listed cells
+// with a value of bound + m or more turn out to be detections, each of them has a strictly larger score than any
+// cell below the bound, so the K best of the image are all listed.  If fewer do, the image is redone by the tile
+// pass.  An image whose bound was not raised lists every cell that can reach the threshold.
+
+constexpr int kCnQueueFlush = 64;        // keys a warp collects before it reserves room in the image's list
+constexpr int kCnQueueLen = kCnQueueFlush + 32;
+
+// Key written by the filter: stored value (order-preserving bits) | (0x7fffffff - cell index) << 1 | settled bit.
+__device__ __forceinline__ unsigned long long cn_raw_key(float value, uint32_t flat, bool settled)
+{
+    return ((unsigned long long)float_order(value) << 32) | (unsigned long long)(((0x7fffffffu - flat) << 1) | (settled ? 1u : 0u));
+}
+
+// Histogram bin of a stored value: linear between bin_lo and the saturation bound for logits (bins are bin_width
+// wide in logit units), leading bits of the score for an activated head.  Non-decreasing in the value.
+__device__ __forceinline__ int cn_bin(const CnParams& p, float value)
+{
+    if (p.d.heat_is_logit) {
+        const float t = (fminf(value, p.sat_raw) - p.bin_lo) * p.bin_scale;
+        return t > 0.0f ? min((int)t, kCnBins - 1) : 0;
+    }
+    const uint32_t hi = float_order(value);
+    const uint32_t bin = hi >= p.bin_base ? (hi - p.bin_base) >> p.bin_shift : 0u;
+    return (int)(bin < (uint32_t)kCnBins ? bin : kCnBins - 1);
+}
+
+// A value that is not above any value of bin j (j >= 1).
+__device__ __forceinline__ float cn_bin_floor(const CnParams& p, int j)
+{
+    if (p.d.heat_is_logit) return p.bin_lo + (float)(j - 1) * p.bin_width;      // one bin of slack for the rounding of cn_bin
+    return order_float(p.bin_base + ((uint32_t)j << p.bin_shift));
+}
+
+constexpr int kCnSampleThreads = 512;
+
+template <bool VEC>
+__global__ void __launch_bounds__(kCnSampleThreads)
+centernet_sample_kernel(const CnParams p)
+{
+    __shared__ int hist[kCnBins];
+    __shared__ int warp_tot[kCnSampleThreads / 32];
+    __shared__ int lead_bin;
+    const int b = blockIdx.x;
+    const int H = p.d.height, W = p.d.width;
+    for (int i = threadIdx.x; i < kCnBins; i += kCnSampleThreads) hist[i] = 0;
+    if (threadIdx.x == 0) lead_bin = 0;
+    __syncthreads();
+    const int rows_per_plane = (H + p.sample_stride - 1) / p.sample_stride;
+    const int rows = p.d.classes * rows_per_plane;
+    const float* heat = p.d.heat + (long long)b * p.hbs;
+    const float lo = p.lo_raw;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kWarps = kCnSampleThreads / 32, kRows = 4;      // a warp reads kRows sampled rows at a time
+    auto count = [&](float v) { if (v >= lo) atomicAdd(&hist[cn_bin(p, v)], 1); };
+    for (int r0 = warp; r0 < rows; r0 += kRows * kWarps) {
+        const float* src[kRows];
+#pragma unroll
+        for (int j = 0; j < kRows; ++j) {
+            const int r = min(r0 + j * kWarps, rows - 1);
+            const int cls = r / rows_per_plane, gy = (r - cls * rows_per_plane) * p.sample_stride;
+            src[j] = heat + ((long long)cls * H + gy) * W;
+        }
+        if (VEC) {
+            for (int x = 4 * lane; x < W; x += 128) {
+                float4 v[kRows];
+#pragma unroll
+                for (int j = 0; j < kRows; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(src[j] + x));
+#pragma unroll
+                for (int j = 0; j < kRows; ++j)
+                    if (r0 + j * kWarps < rows) { count(v[j].x); count(v[j].y); count(v[j].z); count(v[j].w); }
+            }
+        } else {
+            for (int x = lane; x < W; x += 32) {
+                float v[kRows];
+#pragma unroll
+                for (int j = 0; j < kRows; ++j) v[j] = __ldg(src[j] + x);
+#pragma unroll
+                for (int j = 0; j < kRows; ++j)
+                    if (r0 + j * kWarps < rows) count(v[j]);
+            }
+        }
+    }
+    __syncthreads();
+    // the highest bin with sample_want sampled cells in or above it: thread t owns kCnBins / threads bins, from the top
+    constexpr int kPer = kCnBins / kCnSampleThreads;
+    const int top = kCnBins - 1 - kPer * (int)threadIdx.x;
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) mine += hist[top - j];
+    int inc = mine;
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    int before = inc - mine;
+    for (int i = 0; i < warp; ++i) before += warp_tot[i];
+    if (before < p.sample_want && before + mine >= p.sample_want) {
+        int acc = before, bin = top;
+        for (int j = 0; j < kPer; ++j) {
+            if (acc + hist[top - j] >= p.sample_want) { bin = top - j; break; }
+            acc += hist[top - j];
+        }
+        lead_bin = bin;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float bound = lo;
+        if (lead_bin >= 2) bound = fmaxf(lo, cn_bin_floor(p, lead_bin));
+        p.bound[b] = bound;
+    }
+}
+
+// Writes the first n keys of a warp's queue to the image's list: one reservation (one atomic) per call.  The
+// count keeps running past the end of the list, which is how the selection sees that the list overflowed.
+__device__ __forceinline__ void cn_flush(const unsigned long long* queue, int n, unsigned long long* list, int cap,
+                                         int* count)
+{
+    const int lane = threadIdx.x & 31;
+    int base = 0;
+    if (lane == 0) base = atomicAdd(count, n);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    for (int i = lane; i < n; i += 32)
+        if (base + i < cap) list[base + i] = queue[i];
+}
+
+constexpr int kCnFilterWarps = 8;
+constexpr int kCnLoads = 8;              // 128-bit loads a lane keeps in flight
+constexpr int kCnHotLen = 64;            // hot groups a warp collects before it looks at their neighbourhoods
+
+// The filter in two speeds.  A "group" is four consecutive cells of a row (one 128-bit load).
+//  stream   a warp walks its share of the image's groups, eight loads in flight per lane, and only asks whether
+//           any of a group's four cells reaches the image's listing bound.  For a typical head one group in a
+//           hundred does ("hot"); its index goes to the warp's queue.  Everything else costs a load and a compare.
+//  look     once 32 hot groups are queued, each lane takes one: it reads the group's 3 x 6 neighbourhood (from L2,
+//           the rows were streamed moments ago), forms the largest neighbour of each of the four cells and lists a
+//           cell when it reaches the bound and no neighbour is larger by more than the margin.  A listed cell
+//           becomes a key in the warp's key queue, which is written to the image's list 64 keys at a time.
+template <bool VEC>
+__global__ void __launch_bounds__(kCnFilterWarps * 32)
+centernet_filter_kernel(const CnParams p)
+{
+    __shared__ unsigned long long key_queues[kCnFilterWarps][kCnQueueLen];
+    __shared__ uint32_t hot_queues[kCnFilterWarps][kCnHotLen];
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const uint32_t wi = blockIdx.x * kCnFilterWarps + (threadIdx.x >> 5);
+    const uint32_t g_begin = wi * (uint32_t)p.groups_per_warp;
+    if (g_begin >= p.groups) return;
+    const uint32_t g_end = min(p.groups, g_begin + (uint32_t)p.groups_per_warp);
+    const int H = p.d.height, W = p.d.width;
+    const float* heat = p.d.heat + (long long)b * p.hbs;
+    const float lo = p.bound[b], m = p.margin, sat = p.sat_raw;
+    // outside the map: never listed (NaN >= x is false), never greater than anything (fmaxf skips NaN)
+    const float OUT = __int_as_float(0x7fffffff);
+    unsigned long long* key_queue = key_queues[threadIdx.x >> 5];
+    uint32_t* hot_queue = hot_queues[threadIdx.x >> 5];
+    unsigned long long* list = p.list + (long long)b * p.cap;
+    int qn = 0, hn = 0;                                           // keys / hot groups queued, the same in every lane
+
+    // the four cells of group g (row g / groups_per_row over all classes, columns 4 * (g % groups_per_row) ...)
+    auto load_group = [&](uint32_t g) {
+        if (VEC) return __ldg(reinterpret_cast<const float4*>(heat) + g);
+        uint32_t row, gx;
+        p.div_row.divmod(g, row, gx);
+        const int x = 4 * (int)gx;
+        const float* src = heat + (size_t)row * W + x;
+        float4 v = make_float4(OUT, OUT, OUT, OUT);
+        v.x = __ldg(src);
+        if (x + 1 < W) v.y = __ldg(src + 1);
+        if (x + 2 < W) v.z = __ldg(src + 2);
+        if (x + 3 < W) v.w = __ldg(src + 3);
+        return v;
+    };
+
+    // look at up to 32 queued hot groups, one per lane
+    auto look = [&](int n) {
+        const bool active = lane < n;
+        float4 c = make_float4(OUT, OUT, OUT, OUT);
+        float nbx = OUT, nby = OUT, nbz = OUT, nbw = OUT;
+        uint32_t flat = 0;
+        if (active) {
+            const uint32_t g = hot_queue[lane];
+            uint32_t row, gx;
+            p.div_row.divmod(g, row, gx);                          // row over all classes: class * H + y
+            const uint32_t cls = p.div_h.div(row);
+            const int gy = (int)(row - cls * (uint32_t)H), x = 4 * (int)gx;
+            flat = row * (uint32_t)W + (uint32_t)x;                // (class * H + y) * W + x
+            float4 r[3];
+            float l[3], rt[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const int ny = gy + k - 1;
+                r[k] = make_float4(OUT, OUT, OUT, OUT);
+                l[k] = OUT; rt[k] = OUT;
+                if (ny >= 0 && ny < H) {
+                    const float* src = heat + ((size_t)row + k - 1) * W + x;
+                    if (VEC) {
+                        r[k] = __ldg(reinterpret_cast<const float4*>(src));
+                    } else {
+                        r[k].x = __ldg(src);
+                        if (x + 1 < W) r[k].y = __ldg(src + 1);
+                        if (x + 2 < W) r[k].z = __ldg(src + 2);
+                        if (x + 3 < W) r[k].w = __ldg(src + 3);
+                    }
+                    if (x > 0) l[k] = __ldg(src - 1);
+                    if (x + 4 < W) rt[k] = __ldg(src + 4);
+                }
+            }
+            c = r[1];
+            const float4 u = r[0], d = r[2];
+            // largest neighbour of each of the four cells: three above, three below, two beside
+            const float ux = fmaxf(fmaxf(l[0], u.x), u.y), uy = fmaxf(fmaxf(u.x, u.y), u.z);
+            const float uz = fmaxf(fmaxf(u.y, u.z), u.w), uw = fmaxf(fmaxf(u.z, u.w), rt[0]);
+            const float dx = fmaxf(fmaxf(l[2], d.x), d.y), dy = fmaxf(fmaxf(d.x, d.y), d.z);
+            const float dz = fmaxf(fmaxf(d.y, d.z), d.w), dw = fmaxf(fmaxf(d.z, d.w), rt[2]);
+            nbx = fmaxf(fmaxf(ux, dx), fmaxf(l[1], c.y)); nby = fmaxf(fmaxf(uy, dy), fmaxf(c.x, c.z));
+            nbz = fmaxf(fmaxf(uz, dz), fmaxf(c.y, c.w)); nbw = fmaxf(fmaxf(uw, dw), fmaxf(c.z, rt[1]));
+        }
+        // listed: reaches the bound, and not (a neighbour larger by more than the margin while the centre is
+        // below the saturation bound, where a larger neighbour may still have the same score)
+        unsigned fm = (c.x >= lo && !(nbx > c.x + m && c.x < sat) ? 1u : 0u) |
+                      (c.y >= lo && !(nby > c.y + m && c.y < sat) ? 2u : 0u) |
+                      (c.z >= lo && !(nbz > c.z + m && c.z < sat) ? 4u : 0u) |
+                      (c.w >= lo && !(nbw > c.w + m && c.w < sat) ? 8u : 0u);
+        while (__any_sync(0xffffffffu, fm != 0u)) {               // one cell per lane and round
+            const bool has = fm != 0u;
+            const int col = has ? __ffs(fm) - 1 : 0;
+            const float me = col == 0 ? c.x : col == 1 ? c.y : col == 2 ? c.z : c.w;
+            const float nb = col == 0 ? nbx : col == 1 ? nby : col == 2 ? nbz : nbw;
+            const unsigned mask = __ballot_sync(0xffffffffu, has);
+            if (has) {
+                const bool settled = nb <= me - m && me < sat;     // every neighbour's score is smaller, for certain
+                key_queue[qn + __popc(mask & ((1u << lane) - 1u))] = cn_raw_key(me, flat + (uint32_t)col, settled);
+            }
+            qn += __popc(mask);
+            fm &= fm - 1u;
+            __syncwarp();
+            if (qn >= kCnQueueFlush) {
+                cn_flush(key_queue, kCnQueueFlush, list, p.cap, p.count + b);
+                const unsigned long long rest = key_queue[kCnQueueFlush + lane];   // at most 31 keys lie beyond
+                __syncwarp();
+                if (lane < qn - kCnQueueFlush) key_queue[lane] = rest;
+                __syncwarp();
+                qn -= kCnQueueFlush;
+            }
+        }
+    };
+
+    for (uint32_t g0 = g_begin; g0 < g_end; g0 += 32 * kCnLoads) {
+        float4 v[kCnLoads];
+#pragma unroll
+        for (int k = 0; k < kCnLoads; ++k) {
+            const uint32_t g = g0 + 32 * k + lane;
+            v[k] = g < g_end ? load_group(g) : make_float4(OUT, OUT, OUT, OUT);
+        }
+#pragma unroll
+        for (int k = 0; k < kCnLoads; ++k) {
+            const bool hot = v[k].x >= lo || v[k].y >= lo || v[k].z >= lo || v[k].w >= lo;
+            const unsigned mask = __ballot_sync(0xffffffffu, hot);
+            if (mask) {
+                if (hot) hot_queue[hn + __popc(mask & ((1u << lane) - 1u))] = g0 + 32 * k + lane;
+                hn += __popc(mask);
+                __syncwarp();
+                if (hn >= 32) {
+                    look(32);
+                    const uint32_t rest = hot_queue[32 + lane];    // at most 31 groups lie beyond the ones looked at
+                    __syncwarp();
+                    if (lane < hn - 32) hot_queue[lane] = rest;
+                    __syncwarp();
+                    hn -= 32;
+                }
+            }
+        }
+    }
+    if (hn > 0) look(hn);
+    if (qn > 0) cn_flush(key_queue, qn, list, p.cap, p.count + b);
+}
+
+// The exact treatment of one key of the filter: size / offset validity (include/CenterNetLayer.h:217-225), the
+// reference's activation expression (src/CenterNetKernels.cu:17), the threshold test on the score and, unless the
+// filter settled it, the 3x3 test on the neighbours' scores (include/CenterNetLayer.h:181-194, 212).  Returns the
+// final key (score, index) or 0 when the cell is not a detection.
+__device__ __forceinline__ unsigned long long cn_exact(const CnParams& p, const float* heat, const float* size,
+                                                       const float* off, unsigned long long key)
+{
+    const int H = p.d.height, W = p.d.width;
+    const uint32_t area = (uint32_t)H * (uint32_t)W;               // cells per image < 2^31
+    const uint32_t low = (uint32_t)(key & 0xffffffffu);
+    const uint32_t flat = 0x7fffffffu - (low >> 1);
+    const bool settled = (low & 1u) != 0u;
+    const float c = order_float((uint32_t)(key >> 32));
+    const uint32_t cls = flat / area;
+    const uint32_t idx = flat - cls * area;
+    if (!cn_valid(size, off, (long long)idx, (long long)area, W, H)) return 0ULL;
+    const bool logit = p.d.heat_is_logit != 0;
+    const float bias = p.d.heatmap_bias;
+    const float s = logit ? 1.0f / (1.0f + expf(-(c + bias))) : c;
+    if (!isfinite(s) || s < p.d.threshold) return 0ULL;
+    if (logit && !settled) {
+        const float m = p.margin, sat = p.sat_raw;
+        const float* plane = heat + (size_t)cls * area;
+        const int gy = (int)(idx / (uint32_t)W), gx = (int)(idx - (uint32_t)gy * (uint32_t)W);
+        const float NONE = __int_as_float(0x7fffffff);             // outside the map: compares false
+        float nv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int dy = (k < 3) ? -1 : (k < 5 ? 0 : 1);
+            const int dx = (k < 3) ? k - 1 : (k == 3 ? -1 : (k == 4 ? 1 : k - 6));
+            const int ny = gy + dy, nx = gx + dx;
+            nv[k] = (ny >= 0 && ny < H && nx >= 0 && nx < W) ? __ldg(plane + (size_t)ny * W + nx) : NONE;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            // a neighbour below the centre by more than the margin cannot have a larger score (centre < sat)
+            if (nv[k] > c - m || (!(c < sat) && nv[k] == nv[k])) {
+                const float ns = 1.0f / (1.0f + expf(-(nv[k] + bias)));
+                if (ns > s) return 0ULL;
+            }
+        }
+    }
+    return cn_key(s, flat);
+}
+
+// The tile pass, for the images on the list `todo` ([0]: how many, [1 + i]: which).  One block per (32x64 tile,
+// class) walks those images.
 //  load   the tile's pre-activation values (logit + bias) with a one-cell halo go to shared memory,
 //         128 bits at a time where the row alignment allows; every value that is not clearly below the
-//         threshold (in pre-activation space) is put on a work list on the way.  For a typical heatmap
-//         that is about one cell in ten.
+//         threshold (in pre-activation space) is put on a work list on the way.
 //  score  the activation (the reference's precise sigmoid) is evaluated once per work-list entry.
 //  peak   interior entries at or above the threshold are compared with their 8 neighbours' scores.
 //         A neighbour that is not on the work list is clearly below the threshold in pre-activation
 //         space; the activation is non-decreasing, so its score cannot exceed that of a cell which
 //         reached the threshold ("clearly" = a margin far wider than any rounding in exp()).
-//  select a tile with more than K surviving candidates passes on only its K best.
+//  select a tile with more than K surviving candidates passes on only its K best valid ones, so an image's
+//         list (at least tiles x classes x K keys long) always holds what this pass appends.
 constexpr int kCnRowStride = 72;                      // floats per shared-memory row; interior starts at column 4
 constexpr int kCnSmemCells = (kCnTileH + 2) * kCnRowStride;
 
 template <bool VEC>
 __global__ void __launch_bounds__(kCnThreads)
-centernet_peaks_kernel(const CnParams p)
+centernet_peaks_kernel(const CnParams p, const int* todo)
 {
     __shared__ __align__(16) float tile[kCnSmemCells];
     __shared__ __align__(16) float score[kCnSmemCells];
@@ -451,19 +826,23 @@ centernet_peaks_kernel(const CnParams p)
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
 
-    const int b = blockIdx.z, cls = blockIdx.y;
+    const int cls = blockIdx.y;
     const int ty = blockIdx.x / p.tiles_x, tx = blockIdx.x - ty * p.tiles_x;
     const int y0 = ty * kCnTileH, x0 = tx * kCnTileW;
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
-    const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
-    if (threadIdx.x == 0) { n_keys = 0; n_out = 0; n_work = 0; }
-    __syncthreads();
-
     const bool logit = p.d.heat_is_logit != 0;
     const float bias = logit ? p.d.heatmap_bias : 0.0f;
     const float lo_list = p.lo_list;
     constexpr float NEG = -INFINITY;                  // outside the map: never greater than a score
+    const int n_over = min(todo[0], p.d.batch);
+
+    for (int oi = blockIdx.z; oi < n_over; oi += gridDim.z) {
+    const int b = todo[1 + oi];
+    const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
+    __syncthreads();                                  // the previous image's shared state is dead
+    if (threadIdx.x == 0) { n_keys = 0; n_out = 0; n_work = 0; }
+    __syncthreads();
 
     // ---- load + work list
     if (VEC) {
@@ -529,8 +908,7 @@ centernet_peaks_kernel(const CnParams p)
     }
     __syncthreads();
 
-    // ---- peak test -> key.  Size / offset validity needs four gathers per candidate from global memory; the
-    // common case leaves that to the per-image kernel so that this kernel's only wait on memory is the tile load.
+    // ---- peak test -> key
     for (int wi = threadIdx.x; wi < todo; wi += kCnThreads) {
         const int si = work[wi];
         const int row = si / kCnRowStride, col = si - row * kCnRowStride - 4;
@@ -548,17 +926,16 @@ centernet_peaks_kernel(const CnParams p)
     }
     __syncthreads();
 
-    int n = n_keys;
-    const long long slot_id = (long long)b * p.slots + (long long)cls * (p.tiles_x * p.tiles_y) + blockIdx.x;
-    unsigned long long* out = p.cand + slot_id * p.slot_cap;
-    if (n <= p.slot_cap) {
-        for (int i = threadIdx.x; i < n; i += kCnThreads) out[i] = keys[i];
-        if (threadIdx.x == 0) p.cand_cnt[slot_id] = n;
-        return;
+    const int n = n_keys;
+    unsigned long long* out = p.list + (long long)b * p.cap;
+    if (n <= p.K) {
+        if (threadIdx.x == 0) base = n ? atomicAdd(&p.count2[b], n) : 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += kCnThreads) out[base + i] = keys[i];
+        continue;
     }
-    // Rare: more candidates than the tile's slot holds (slot_cap >= K).  No image keeps more than K, so the
-    // tile's K best are enough -- but only valid candidates may compete for those places, so validity is
-    // checked here first.
+    // More candidates than an image keeps: the tile's K best are enough -- but only valid candidates may
+    // compete for those places, so validity is checked here first.
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
     for (int i = threadIdx.x; i < n; i += kCnThreads) {
@@ -571,153 +948,163 @@ centernet_peaks_kernel(const CnParams p)
         if (keys[i] != 0ULL) atomicAdd(&base, 1);
     __syncthreads();
     const int n_valid = base;
-    if (n_valid <= p.K) {
-        for (int i = threadIdx.x; i < n; i += kCnThreads)
-            if (keys[i] != 0ULL) out[atomicAdd(&n_out, 1)] = keys[i];
-        if (threadIdx.x == 0) p.cand_cnt[slot_id] = n_valid;
-        return;
-    }
-    const unsigned long long kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
+    __syncthreads();
+    unsigned long long kth = 1ULL;                     // every valid key
+    if (n_valid > p.K) kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
+    const int n_pass = n_valid > p.K ? p.K : n_valid;
+    if (threadIdx.x == 0) base = n_pass ? atomicAdd(&p.count2[b], n_pass) : 0;
+    __syncthreads();
     for (int i = threadIdx.x; i < n; i += kCnThreads)
-        if (keys[i] >= kth) out[atomicAdd(&n_out, 1)] = keys[i];
-    if (threadIdx.x == 0) p.cand_cnt[slot_id] = p.K;
+        if (keys[i] >= kth) out[base + atomicAdd(&n_out, 1)] = keys[i];
+    }
 }
 
 // One block per image: the K best of the image's candidates, sorted, decoded to boxes.
-//  1. prefix sums of the slots' counts, so that candidate i of the image is found by a binary search;
-//  2. every candidate's size / offset validity (include/CenterNetLayer.h:217-225), all gathers in
-//     flight at once; valid keys are compacted into one list (shared memory when it fits);
-//  3. a list that fits shared memory is sorted outright (bitonic: no contention, unlike a radix
-//     histogram of scores that share their leading bits); a longer one goes through radix
-//     selection of the K-th key first.
-constexpr int kCnTopkThreads = 1024;
+//  1. a short list (up to about 2.5 K keys) is staged whole.  A longer one is counted into a histogram of the
+//     stored values first; the bin in or above which at least K + K/4 + 32 keys lie, less bin_slack bins whose
+//     scores are not separated from it for certain, bounds what is staged;
+//  2. staged keys get the exact treatment (cn_exact).  If K or more of the keys in or above the bin turn out to
+//     be detections, the K best of the list are among the staged ones, because every key left out has a strictly
+//     smaller score;
+//  3. otherwise (many invalid boxes, one bin holding thousands of equal scores, or an image the tile pass redid)
+//     every key is treated, the detections are compacted and the K-th key is found by radix selection;
+//  4. the staged keys are sorted (bitonic, shared memory) and the first K become records -- unless the image's
+//     listing bound was raised and fewer than K detections lie clear above it: then the list may be missing some
+//     of the K best, and the image goes on the list of images to redo.
+// `only` == nullptr: block b treats image b.  Otherwise the blocks walk the images listed in `only`, which the tile
+// pass has redone.
+constexpr int kCnSelThreads = 512;
 constexpr int kCnStageKeys = 4096;     // candidates per image sorted in shared memory (32 KB)
-constexpr int kCnMaxSlots = 2048;      // slots per image whose prefix sums fit shared memory
-constexpr int kCnBinShift = 51;        // a key's leading 13 bits (sign, exponent, 4 mantissa bits of the score) ...
-constexpr int kCnBins = 1 << 13;       // ... index a histogram that aliases the staging area
-static_assert(kCnBins * sizeof(int) <= kCnStageKeys * sizeof(unsigned long long), "histogram must fit the staging area");
-static_assert(kCnBins == 8 * kCnTopkThreads, "the top-down scan gives every thread 8 bins");
+constexpr int kCnRankKeys = 128;       // up to this many, keys are placed by counting instead of sorted
+static_assert(kCnBins == 2 * kCnSelThreads, "the top-down scan gives every thread 2 bins");
 
-__global__ void __launch_bounds__(kCnTopkThreads)
-centernet_topk_kernel(const CnParams p)
+__global__ void __launch_bounds__(kCnSelThreads)
+centernet_select_kernel(const CnParams p, const int* only)
 {
     __shared__ unsigned long long stage[kCnStageKeys];
-    __shared__ int prefix[kCnMaxSlots + 1];
+    __shared__ int bins[kCnBins];
     __shared__ int hist[256];
     __shared__ unsigned long long sel[2];
-    __shared__ int warp_tot[32];
-    __shared__ int n_best, n_valid;
-    const int b = blockIdx.x;
+    __shared__ int warp_tot[kCnSelThreads / 32];
+    __shared__ int n_best, n_valid, n_top, n_above, lead_bin;
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_items = only ? min(only[0], p.d.batch) : p.d.batch;
+
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int b = only ? only[1 + item] : item;
+    const float* heat = p.d.heat + (long long)b * p.hbs;
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
-    const unsigned long long* cand = p.cand + (long long)b * p.slots * p.slot_cap;
-    const int* cnt = p.cand_cnt + (long long)b * p.slots;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) { n_valid = 0; n_best = 0; prefix[0] = 0; }
-
-    // 1. inclusive prefix of slot counts -> prefix[s+1]
-    int carry = 0;
-    for (int base = 0; base < p.slots; base += kCnTopkThreads) {
-        const int sidx = base + threadIdx.x;
-        const int v = sidx < p.slots ? cnt[sidx] : 0;
-        int inc = v;
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, inc, o);
-            if (lane >= o) inc += t;
+    const unsigned long long* cand = p.list + (long long)b * p.cap;
+    const int found = p.count[b];
+    if (only == nullptr && found > p.cap) {
+        // the filter found more keys than the list holds (a plateau): the tile pass redoes this image
+        if (threadIdx.x == 0) {
+            p.redo[1 + atomicAdd(&p.redo[0], 1)] = b;
+            p.counts[b] = 0;
         }
-        if (lane == 31) warp_tot[warp] = inc;
-        __syncthreads();
-        int before = carry;
-        for (int i = 0; i < warp; ++i) before += warp_tot[i];
-        if (sidx < p.slots) prefix[sidx + 1] = before + inc;
-        int total = 0;
-        for (int i = 0; i < 32; ++i) total += warp_tot[i];
-        carry += total;
-        __syncthreads();
+        continue;
     }
-    const int n_total = carry;
+    // an image on the list was redone by the tile pass, which stored count2 final keys (at most cap)
+    const bool redone = only != nullptr;
+    const int n_total = redone ? min(p.count2[b], p.cap) : found;
+    const float bound = p.bound[b];
+    const bool raised = !redone && bound > p.lo_raw;
+    const float clear = bound + p.margin;              // a detection at or above this beats every cell below the bound
+    __syncthreads();                                   // the previous image's shared state is dead
+    if (threadIdx.x == 0) { n_valid = 0; n_best = 0; n_top = 0; n_above = 0; lead_bin = 0; }
+    __syncthreads();
 
-    // 2. Short cut.  Far more cells pass the peak test than an image keeps (thousands against K), and the
-    // size / offset validity check costs four scattered reads per candidate.  So first find, from a histogram
-    // of the keys' leading 13 bits, the bin holding the K-th best candidate; only candidates in that bin or
-    // above (at least K, usually a few hundred) are staged and checked.  If K or more of them are valid, the K
-    // best valid candidates of the image are among them, because every candidate left out has a smaller key.
-    // Otherwise (many invalid boxes, or one bin holding thousands of equal scores) the full path below runs.
     unsigned long long* sorted = stage;
     int m = 0;
     bool done = false;
-    {
-        int* bins = reinterpret_cast<int*>(stage);                 // kCnBins ints alias the staging area
-        for (int i = threadIdx.x; i < kCnBins; i += kCnTopkThreads) bins[i] = 0;
-        __syncthreads();
-        for (int s0 = 0; s0 < p.slots; s0 += 32) {
-            const int sidx = s0 + warp;
-            if (sidx >= p.slots) continue;
-            const int c = prefix[sidx + 1] - prefix[sidx];
-            const unsigned long long* src = cand + (long long)sidx * p.slot_cap;
-#pragma unroll 8
-            for (int j = lane; j < c; j += 32) atomicAdd(&bins[(int)(src[j] >> kCnBinShift)], 1);
-        }
-        __syncthreads();
-        // thread t owns the 8 bins below kCnBins - 8t, scanned from the top
-        const int top = kCnBins - 1 - 8 * (int)threadIdx.x;
-        int mine = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mine += bins[top - j];
-        int inc = mine;
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, inc, o);
-            if (lane >= o) inc += t;
-        }
-        if (lane == 31) warp_tot[warp] = inc;
-        if (threadIdx.x == 0) sel[0] = 0ULL;                       // lead bin 0 = "take everything"
-        __syncthreads();
-        int before = inc - mine;
-        for (int i = 0; i < warp; ++i) before += warp_tot[i];
-        if (before < p.K && before + mine >= p.K) {
-            int acc = before, bin = top;
-            for (int j = 0; j < 8; ++j) {
-                if (acc + bins[top - j] >= p.K) { bin = top - j; break; }
-                acc += bins[top - j];
+    if (!redone) {
+        int lead = 0, lead_staged = 0;
+        if (n_total > 2 * (p.K + p.K / 4 + 32)) {
+            // 1. histogram of the stored values; thread t owns bins kCnBins-1-2t and the one below, from the top
+            for (int i = threadIdx.x; i < kCnBins; i += kCnSelThreads) bins[i] = 0;
+            __syncthreads();
+            for (int i = threadIdx.x; i < n_total; i += kCnSelThreads)
+                atomicAdd(&bins[cn_bin(p, order_float((uint32_t)(cand[i] >> 32)))], 1);
+            __syncthreads();
+            const int want = p.K + p.K / 4 + 32;
+            const int top = kCnBins - 1 - 2 * (int)threadIdx.x;
+            const int h0 = bins[top], h1 = bins[top - 1];
+            const int mine = h0 + h1;
+            int inc = mine;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
             }
-            sel[0] = (unsigned long long)bin;
+            if (lane == 31) warp_tot[warp] = inc;
+            __syncthreads();
+            int before = inc - mine;
+            for (int i = 0; i < warp; ++i) before += warp_tot[i];
+            if (before < want && before + mine >= want) lead_bin = before + h0 >= want ? top : top - 1;
+            __syncthreads();
+            lead = lead_bin;
+            lead_staged = lead > p.bin_slack ? lead - p.bin_slack : 0;
         }
-        __syncthreads();
-        const int lead = (int)sel[0];
-        __syncthreads();                                           // bins are dead from here: stage is reused
-        for (int s0 = 0; s0 < p.slots; s0 += 32) {
-            const int sidx = s0 + warp;
-            if (sidx >= p.slots) continue;
-            const int c = prefix[sidx + 1] - prefix[sidx];
-            const unsigned long long* src = cand + (long long)sidx * p.slot_cap;
-#pragma unroll 8
-            for (int j = lane; j < c; j += 32) {
-                const unsigned long long key = src[j];
-                if ((int)(key >> kCnBinShift) >= lead) {
-                    const int at = atomicAdd(&n_best, 1);
-                    if (at < kCnStageKeys) stage[at] = key;
-                }
+
+        // 2. stage, then the exact treatment
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n_total; i += kCnSelThreads) {
+            const unsigned long long key = cand[i];
+            if (lead_staged == 0 || cn_bin(p, order_float((uint32_t)(key >> 32))) >= lead_staged) {
+                const int at = atomicAdd(&n_best, 1);
+                if (at < kCnStageKeys) stage[at] = key;
             }
         }
         __syncthreads();
         const int n_c = n_best;
         if (n_c <= kCnStageKeys) {
-            for (int i = threadIdx.x; i < n_c; i += kCnTopkThreads) {
-                const uint32_t flat = 0xffffffffu - (uint32_t)(stage[i] & 0xffffffffu);
-                const uint32_t cls = flat / (uint32_t)area;
-                if (cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) atomicAdd(&n_valid, 1);
-                else stage[i] = 0ULL;                              // sorts behind every real key
+            for (int i0 = 0; i0 < n_c; i0 += kCnSelThreads) {     // all threads of a warp take part in the votes
+                const int i = i0 + threadIdx.x;
+                bool ok = false, top = false, above = false;
+                if (i < n_c) {
+                    const unsigned long long key = stage[i];
+                    const unsigned long long fin = cn_exact(p, heat, size, off, key);
+                    stage[i] = fin;                                // 0 sorts behind every real key
+                    if (fin != 0ULL) {
+                        const float value = order_float((uint32_t)(key >> 32));
+                        ok = true;
+                        top = lead == 0 || cn_bin(p, value) >= lead;
+                        above = value >= clear;
+                    }
+                }
+                const unsigned v_ok = __ballot_sync(0xffffffffu, ok), v_top = __ballot_sync(0xffffffffu, top);
+                const unsigned v_above = __ballot_sync(0xffffffffu, above);
+                if (lane == 0 && v_ok) {
+                    atomicAdd(&n_valid, __popc(v_ok));
+                    if (v_top) atomicAdd(&n_top, __popc(v_top));
+                    if (v_above) atomicAdd(&n_above, __popc(v_above));
+                }
             }
             __syncthreads();
-            if (n_valid >= p.K || n_c == n_total) {
-                int pow2 = 1;
-                while (pow2 < n_c) pow2 <<= 1;
-                for (int i = n_c + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
-                __syncthreads();
-                block_bitonic_desc(stage, pow2);
+            if (n_top >= p.K || n_c == n_total) {
                 m = n_valid < p.K ? n_valid : p.K;
+                if (n_c <= kCnRankKeys) {
+                    // few keys: every thread finds the place of its key by counting the larger ones; the first
+                    // K places are written to the front of a second area
+                    unsigned long long* out = stage + kCnStageKeys / 2;
+                    for (int i = threadIdx.x; i < n_c; i += kCnSelThreads) {
+                        const unsigned long long mine = stage[i];
+                        if (mine == 0ULL) continue;
+                        int rank = 0;
+                        for (int j = 0; j < n_c; ++j) rank += stage[j] > mine ? 1 : 0;
+                        if (rank < m) out[rank] = mine;
+                    }
+                    sorted = out;
+                    __syncthreads();
+                } else {
+                    int pow2 = 1;
+                    while (pow2 < n_c) pow2 <<= 1;
+                    for (int i = n_c + threadIdx.x; i < pow2; i += kCnSelThreads) stage[i] = 0ULL;
+                    __syncthreads();
+                    block_bitonic_desc(stage, pow2);
+                }
                 done = true;
             }
         }
@@ -725,30 +1112,31 @@ centernet_topk_kernel(const CnParams p)
     }
 
     if (!done) {
-        if (threadIdx.x == 0) { n_valid = 0; n_best = 0; }
+        if (threadIdx.x == 0) { n_valid = 0; n_best = 0; n_above = 0; }
         __syncthreads();
-        // 2. validity + compaction
+        // 3. the exact treatment of every key + compaction
         const bool staged = n_total <= kCnStageKeys;
-        unsigned long long* list = staged ? stage : p.list + (long long)b * p.slots * p.slot_cap;
-        for (int i = threadIdx.x; i < n_total; i += kCnTopkThreads) {
-            int lo = 0, hi = p.slots;                    // largest s with prefix[s] <= i
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (prefix[mid] <= i) lo = mid; else hi = mid;
+        unsigned long long* list = staged ? stage : p.list2 + (long long)b * p.cap;
+        for (int i = threadIdx.x; i < n_total; i += kCnSelThreads) {
+            unsigned long long key = cand[i];
+            if (redone) {                                  // final keys of the tile pass: only validity is open
+                const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
+                const uint32_t cls = flat / (uint32_t)area;
+                if (!cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) key = 0ULL;
+            } else {
+                const float value = order_float((uint32_t)(key >> 32));
+                key = cn_exact(p, heat, size, off, key);
+                if (key != 0ULL && value >= clear) atomicAdd(&n_above, 1);
             }
-            const unsigned long long key = cand[(long long)lo * p.slot_cap + (i - prefix[lo])];
-            const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
-            const uint32_t cls = flat / (uint32_t)area;
-            if (cn_valid(size, off, (long long)(flat - cls * (uint32_t)area), area, W, H)) list[atomicAdd(&n_valid, 1)] = key;
+            if (key != 0ULL) list[atomicAdd(&n_valid, 1)] = key;
         }
         __syncthreads();
         const int n = n_valid;
 
-        // 3. order the best K
         if (staged) {
             int pow2 = 1;
             while (pow2 < n) pow2 <<= 1;
-            for (int i = n + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+            for (int i = n + threadIdx.x; i < pow2; i += kCnSelThreads) stage[i] = 0ULL;
             __syncthreads();
             block_bitonic_desc(stage, pow2);
             m = n < p.K ? n : p.K;
@@ -760,15 +1148,15 @@ centernet_topk_kernel(const CnParams p)
             int m_sort = 0;
             if (n > p.K) {
                 int want = 0;
-                const unsigned long long lead = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel, 2, &want) >> 48;
+                const unsigned long long lead16 = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel, 2, &want) >> 48;
                 const int winners = p.K - want;
                 if (threadIdx.x == 0) { n_best = 0; n_valid = 0; }      // n_valid is reused as the tie counter
                 __syncthreads();
-                for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
+                for (int i = threadIdx.x; i < n; i += kCnSelThreads) {
                     const unsigned long long key = list[i];
                     const unsigned long long top = key >> 48;
-                    if (top > lead) stage[atomicAdd(&n_best, 1)] = key;
-                    else if (top == lead) {
+                    if (top > lead16) stage[atomicAdd(&n_best, 1)] = key;
+                    else if (top == lead16) {
                         const int at = atomicAdd(&n_valid, 1);
                         if (winners + at < kCnStageKeys) stage[winners + at] = key;
                     }
@@ -780,7 +1168,7 @@ centernet_topk_kernel(const CnParams p)
                     const unsigned long long kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
                     if (threadIdx.x == 0) n_best = 0;
                     __syncthreads();
-                    for (int i = threadIdx.x; i < n; i += kCnTopkThreads) {
+                    for (int i = threadIdx.x; i < n; i += kCnSelThreads) {
                         const unsigned long long key = list[i];
                         if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
                     }
@@ -788,17 +1176,26 @@ centernet_topk_kernel(const CnParams p)
                     m_sort = n_best;
                 }
             } else {
-                for (int i = threadIdx.x; i < n; i += kCnTopkThreads) stage[i] = list[i];
+                for (int i = threadIdx.x; i < n; i += kCnSelThreads) stage[i] = list[i];
                 m_sort = n;
             }
             __syncthreads();
             int pow2 = 1;
             while (pow2 < m_sort) pow2 <<= 1;
-            for (int i = m_sort + threadIdx.x; i < pow2; i += kCnTopkThreads) stage[i] = 0ULL;
+            for (int i = m_sort + threadIdx.x; i < pow2; i += kCnSelThreads) stage[i] = 0ULL;
             __syncthreads();
             block_bitonic_desc(stage, pow2);
             m = m_sort < p.K ? m_sort : p.K;
         }
+    }
+    __syncthreads();
+    if (raised && n_above < p.K) {
+        // the raised bound may have kept some of the K best off the list: the tile pass redoes this image
+        if (threadIdx.x == 0) {
+            p.redo[1 + atomicAdd(&p.redo[0], 1)] = b;
+            p.counts[b] = 0;
+        }
+        continue;
     }
     const float image_w = p.d.image_width > 0 ? (float)p.d.image_width : 1.0f;
     const float image_h = p.d.image_height > 0 ? (float)p.d.image_height : 1.0f;
@@ -806,9 +1203,9 @@ centernet_topk_kernel(const CnParams p)
         const unsigned long long key = sorted[i];
         const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
         const float score = order_float((uint32_t)(key >> 32));
-        const int cls = (int)(flat / area);
-        const long long idx = flat - (long long)cls * area;
-        const int y = (int)(idx / W), x = (int)(idx - (long long)y * W);
+        const int cls = (int)(flat / (uint32_t)area);
+        const uint32_t idx = flat - (uint32_t)cls * (uint32_t)area;
+        const int y = (int)(idx / (uint32_t)W), x = (int)(idx - (uint32_t)y * (uint32_t)W);
         // include/CenterNetLayer.h:217-237, each product and sum rounded separately as on the host
         const float bw = size[idx] / W, bh = size[area + idx] / H;
         const float cx = (x + off[idx]) / W, cy = (y + off[area + idx]) / H;
@@ -817,6 +1214,7 @@ centernet_topk_kernel(const CnParams p)
                         score, cls, b + p.d.batch_id_offset, (int)flat);
     }
     if (threadIdx.x == 0) p.counts[b] = m;
+    }
 }
 
 // ============================================================================================
@@ -1254,16 +1652,34 @@ static void cn_geometry(int classes, int height, int width, int* tiles_x, int* t
     *blocks_per_image = (long long)classes * *tiles_x * *tiles_y;
 }
 
+// Keys per image list: enough for what the tile pass may append (tiles x classes x K), by default kCnListCap,
+// never more than the image has cells.
+static long long cn_list_cap(int classes, int height, int width, int max_detections, long long* floor_out)
+{
+    int tx, ty;
+    long long bpi;
+    cn_geometry(classes, height, width, &tx, &ty, &bpi);
+    const long long cells = (long long)classes * height * width;
+    long long floor_cap = bpi * max_detections;
+    if (floor_cap > cells) floor_cap = cells;
+    long long cap = floor_cap > kCnListCap ? floor_cap : kCnListCap;
+    if (cap > cells) cap = cells;
+    if (floor_out) *floor_out = floor_cap;
+    return cap;
+}
+
+static size_t cn_counter_ints(int batch)
+{
+    return 2 * (size_t)batch + (size_t)batch + 1;                // count, count2, redo list
+}
+
 extern "C" size_t pxe_centernet_decode_workspace_bytes(int batch, int classes, int height, int width,
                                                        int max_detections)
 {
     if (batch <= 0 || classes <= 0 || height <= 0 || width <= 0 || max_detections <= 0) return 0;
-    int tx, ty;
-    long long bpi;
-    cn_geometry(classes, height, width, &tx, &ty, &bpi);
-    const size_t slot_cap = max_detections > kCnSlotCap ? max_detections : kCnSlotCap;
-    return 2 * align_up((size_t)batch * bpi * slot_cap * sizeof(unsigned long long), 256)
-           + align_up((size_t)batch * bpi * sizeof(int), 256);
+    const long long cap = cn_list_cap(classes, height, width, max_detections, nullptr);
+    return 2 * align_up((size_t)batch * cap * sizeof(unsigned long long), 256)
+           + align_up(cn_counter_ints(batch) * sizeof(int), 256) + align_up((size_t)batch * sizeof(float), 256);
 }
 
 // Pre-activation value below which sigmoid(v) < threshold for certain (with a margin far wider
@@ -1278,6 +1694,13 @@ static float centernet_prefilter(const pxe_centernet_decode_desc& d)
     return (float)(logit - 1e-3 - 1e-3 * fabs(logit));
 }
 
+static uint32_t host_float_order(float f)
+{
+    uint32_t u;
+    memcpy(&u, &f, sizeof u);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_decode_desc* dp,
                                     pxe_detection* dets, int* counts, void* workspace, size_t workspace_bytes)
 {
@@ -1288,7 +1711,7 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     PXE_REQUIRE(d.max_detections > 0 && d.max_detections <= kCnMaxK, "centernet_decode: max_detections %d outside 1..%d",
                 d.max_detections, kCnMaxK);
     const long long area = (long long)d.height * d.width;
-    PXE_REQUIRE(area * d.classes < 0xffffffffLL, "centernet_decode: heatmap has too many cells per image");
+    PXE_REQUIRE(area * d.classes < 0x7fffffffLL, "centernet_decode: heatmap has too many cells per image");
     PXE_REQUIRE(d.batch <= 65535 && d.classes <= 65535, "centernet_decode: batch/classes exceed 65535");
     PXE_REQUIRE(d.heat_batch_stride == 0 || d.heat_batch_stride >= area * d.classes, "centernet_decode: heat_batch_stride too small");
     PXE_REQUIRE(d.size_batch_stride == 0 || d.size_batch_stride >= 2 * area, "centernet_decode: size_batch_stride too small");
@@ -1304,34 +1727,98 @@ extern "C" int pxe_centernet_decode(pxe_stream_t stream, const pxe_centernet_dec
     p.hbs = d.heat_batch_stride ? d.heat_batch_stride : area * d.classes;
     p.sbs = d.size_batch_stride ? d.size_batch_stride : 2 * area;
     p.obs = d.offset_batch_stride ? d.offset_batch_stride : 2 * area;
-    long long bpi;
+    long long bpi, floor_cap;
     cn_geometry(d.classes, d.height, d.width, &p.tiles_x, &p.tiles_y, &bpi);
-    PXE_REQUIRE(bpi * (d.max_detections > kCnSlotCap ? d.max_detections : kCnSlotCap) < 0x7fffffffLL,
-                "centernet_decode: candidate table too large");
-    if (bpi > kCnMaxSlots)
-        return set_error(PXE_ERR_UNSUPPORTED, "centernet_decode: %lld tiles x classes per image exceed %d", bpi, kCnMaxSlots);
+    const long long full_cap = cn_list_cap(d.classes, d.height, d.width, d.max_detections, &floor_cap);
+    PXE_REQUIRE(full_cap < 0x7fffffffLL && bpi < 0x7fffffffLL, "centernet_decode: candidate table too large");
+    PXE_REQUIRE(d.candidate_capacity >= 0 && d.candidate_capacity <= full_cap,
+                "centernet_decode: candidate_capacity %d outside 0..%lld", d.candidate_capacity, full_cap);
     p.K = d.max_detections;
-    p.slots = (int)bpi;
-    p.slot_cap = d.max_detections > kCnSlotCap ? d.max_detections : kCnSlotCap;
+    p.cap = (int)(d.candidate_capacity == 0 ? full_cap : (d.candidate_capacity < floor_cap ? floor_cap : d.candidate_capacity));
     p.lo = centernet_prefilter(d);
     p.lo_list = d.heat_is_logit ? p.lo - 2e-4f * fmaxf(1.0f, fabsf(p.lo)) : p.lo;
+    if (d.heat_is_logit) {
+        // the filter compares stored logits; the bias is added only where a score is evaluated
+        const float shifted = p.lo - d.heatmap_bias;
+        p.lo_raw = isfinite(shifted) ? shifted - 1e-3f * fmaxf(1.0f, fabsf(p.lo) + fabsf(d.heatmap_bias)) : shifted;
+        p.margin = 0.01f;
+        p.sat_raw = 8.0f - d.heatmap_bias;
+        if (!isfinite(p.sat_raw)) p.sat_raw = -INFINITY;        // a non-finite bias: every listed cell takes the exact test
+    } else {
+        p.lo_raw = d.threshold;
+        p.margin = 0.0f;
+        p.sat_raw = INFINITY;
+    }
+    // histogram bins (sampling pass; long lists in the selection).  Logits: linear from the listing bound (at
+    // most 64 below the saturation bound) to the saturation bound; bins are bin_width wide, so keys bin_slack
+    // bins apart differ by more than the margin.  Activated head: leading bits of the score between the
+    // threshold and the largest float.
+    p.bin_base = host_float_order(d.threshold);
+    const uint32_t top = host_float_order(FLT_MAX);
+    p.bin_shift = 0;
+    while (top > p.bin_base && ((top - p.bin_base) >> p.bin_shift) >= (uint32_t)kCnBins) ++p.bin_shift;
+    p.bin_lo = 0.0f; p.bin_scale = 0.0f; p.bin_width = 0.0f; p.bin_slack = 0;
+    if (d.heat_is_logit) {
+        p.bin_lo = fmaxf(p.lo_raw, p.sat_raw - 64.0f);
+        const float width = (p.sat_raw - p.bin_lo) / (float)(kCnBins - 1);
+        if (isfinite(width) && width > 0.0f) {
+            p.bin_width = width;
+            p.bin_scale = 1.0f / width;
+            p.bin_slack = (int)ceilf(p.margin / width) + 1;
+        } else {
+            p.bin_lo = 0.0f;                                     // degenerate bounds: one bin, every key staged
+            p.bin_slack = kCnBins;
+        }
+    }
+    // the sampling pass: every 16th row; it raises an image's bound when some 4K cells of the whole map lie above
+    p.sample_stride = d.height >= 32 ? 16 : 1;
+    p.sample_want = 4 * p.K / p.sample_stride + 16;
+    // groups of four cells; a warp's share is a multiple of what its lanes load at once, sized for a few waves
+    DeviceInfo di;
+    { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
+    const bool vec = d.width % 4 == 0 && aligned16(d.heat) && p.hbs % 4 == 0;   // 128-bit loads: rows start on 16 bytes
+    const uint32_t groups_per_row = (uint32_t)((d.width + 3) / 4);
+    p.groups = (uint32_t)d.classes * (uint32_t)d.height * groups_per_row;     // < 2^31
+    p.div_row = FastDiv(groups_per_row);
+    p.div_h = FastDiv((uint32_t)d.height);
+    const uint32_t step = 32 * kCnLoads;
+    uint32_t share = 8 * step;
+    while (share > step && (long long)d.batch * ((p.groups + share - 1) / share) < 4LL * 24 * di.sm_count) share >>= 1;
+    p.groups_per_warp = share;
+    const long long wpi = (p.groups + share - 1) / share;
+
     char* ws = static_cast<char*>(workspace);
-    p.cand = reinterpret_cast<unsigned long long*>(ws);
-    ws += align_up((size_t)d.batch * bpi * p.slot_cap * sizeof(unsigned long long), 256);
+    const size_t list_bytes = align_up((size_t)d.batch * full_cap * sizeof(unsigned long long), 256);
     p.list = reinterpret_cast<unsigned long long*>(ws);
-    ws += align_up((size_t)d.batch * bpi * p.slot_cap * sizeof(unsigned long long), 256);
-    p.cand_cnt = reinterpret_cast<int*>(ws);
+    p.list2 = reinterpret_cast<unsigned long long*>(ws + list_bytes);
+    int* ints = reinterpret_cast<int*>(ws + 2 * list_bytes);
+    p.count = ints;
+    p.count2 = ints + d.batch;
+    p.redo = ints + 2 * (size_t)d.batch;
+    p.bound = reinterpret_cast<float*>(ws + 2 * list_bytes + align_up(cn_counter_ints(d.batch) * sizeof(int), 256));
     p.dets = dets; p.counts = counts;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, (unsigned)d.batch);
-    // 128-bit tile loads need every row segment of a tile to start on a 16-byte boundary
-    const bool vec = d.width % 4 == 0 && aligned16(d.heat) && p.hbs % 4 == 0;
-    if (vec) centernet_peaks_kernel<true><<<grid, kCnThreads, 0, s>>>(p);
-    else centernet_peaks_kernel<false><<<grid, kCnThreads, 0, s>>>(p);
+    PXE_CUDA_OK(cudaMemsetAsync(ints, 0, cn_counter_ints(d.batch) * sizeof(int), s));
+    if (vec) centernet_sample_kernel<true><<<(unsigned)d.batch, kCnSampleThreads, 0, s>>>(p);
+    else centernet_sample_kernel<false><<<(unsigned)d.batch, kCnSampleThreads, 0, s>>>(p);
+    PXE_LAUNCH_OK("centernet_sample_kernel");
+    dim3 fgrid((unsigned)((wpi + kCnFilterWarps - 1) / kCnFilterWarps), (unsigned)d.batch);
+    if (vec) centernet_filter_kernel<true><<<fgrid, kCnFilterWarps * 32, 0, s>>>(p);
+    else centernet_filter_kernel<false><<<fgrid, kCnFilterWarps * 32, 0, s>>>(p);
+    PXE_LAUNCH_OK("centernet_filter_kernel");
+    centernet_select_kernel<<<(unsigned)d.batch, kCnSelThreads, 0, s>>>(p, nullptr);
+    PXE_LAUNCH_OK("centernet_select_kernel");
+    // The selection puts two kinds of image on a list that is empty in the normal case: those whose key list
+    // overflowed and those whose raised bound left fewer than K detections.  The tile pass redoes them (its
+    // blocks return at once when there are none) and the selection runs again for them.
+    const unsigned walkers = (unsigned)(d.batch < 2 ? d.batch : 2);
+    dim3 tgrid((unsigned)(p.tiles_x * p.tiles_y), (unsigned)d.classes, walkers);
+    if (vec) centernet_peaks_kernel<true><<<tgrid, kCnThreads, 0, s>>>(p, p.redo);
+    else centernet_peaks_kernel<false><<<tgrid, kCnThreads, 0, s>>>(p, p.redo);
     PXE_LAUNCH_OK("centernet_peaks_kernel");
-    centernet_topk_kernel<<<(unsigned)d.batch, kCnTopkThreads, 0, s>>>(p);
-    PXE_LAUNCH_OK("centernet_topk_kernel");
+    centernet_select_kernel<<<walkers, kCnSelThreads, 0, s>>>(p, p.redo);
+    PXE_LAUNCH_OK("centernet_select_kernel");
     return PXE_OK;
 }
 

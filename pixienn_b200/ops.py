@@ -335,8 +335,10 @@ def centernet_activate(x: torch.Tensor, classes: int, heatmap_bias: float, out: 
 
 def centernet_decode(heat: torch.Tensor, size: torch.Tensor, offset: torch.Tensor, threshold: float,
                      max_detections: int = 100, *, logits: bool = False, heatmap_bias: float = 0.0,
-                     img_w: int = 0, img_h: int = 0, batch_id_offset: int = 0, workspace=None):
-    """Returns (dets [B, K, 8] int32 view of 32-byte records, counts [B] int32), both on the device."""
+                     img_w: int = 0, img_h: int = 0, batch_id_offset: int = 0, workspace=None,
+                     candidate_capacity: int = 0):
+    """Returns (dets [B, K, 8] int32 view of 32-byte records, counts [B] int32), both on the device.
+    ``candidate_capacity``: see pxe_centernet_decode_desc (0 = default)."""
     hp, hbs = _slot(heat, "heat")
     sp, sbs = _slot(size, "size")
     op, obs = _slot(offset, "offset")
@@ -349,6 +351,7 @@ def centernet_decode(heat: torch.Tensor, size: torch.Tensor, offset: torch.Tenso
     d.batch, d.classes, d.height, d.width = B, classes, H, W
     d.image_width, d.image_height = img_w, img_h
     d.threshold, d.max_detections, d.batch_id_offset = threshold, max_detections, batch_id_offset
+    d.candidate_capacity = candidate_capacity
     need = capi.lib().pxe_centernet_decode_workspace_bytes(B, classes, H, W, max_detections)
     if workspace is None or workspace.numel() < need:
         workspace = torch.empty(max(need, 256), device=heat.device, dtype=torch.uint8)

@@ -269,6 +269,84 @@ def test_centernet_crowded_tiles_are_reduced_per_tile(cuda, oracle):
         dets_equal(got[b], ref[b])
 
 
+@pytest.mark.parametrize("logits", [False, True])
+def test_centernet_list_overflow_is_redone_tile_by_tile(cuda, oracle, logits):
+    """The streaming pass lists an image's local maxima up to candidate_capacity; an image with more is redone
+    by the tile pass, which keeps each tile's best K valid candidates.  Thousands of equal maxima (which no
+    listing bound can thin out) and a small capacity force that for the two crowded images of the batch; the
+    sparse one in between keeps its streamed list.  Records are identical to the run whose lists hold every
+    cell, and to the oracle."""
+    B, classes, H, W, K = 3, 2, 48, 256, 20
+    rng = np.random.default_rng(6)
+    heat = rng.random((B, classes, H, W)).astype(np.float32) * 0.5 + 0.2
+    heat[:, :, ::2, ::2] = 0.9                       # every other cell in both directions: equal local maxima
+    heat[1] = 0.05
+    heat[1, 0, 10, 10], heat[1, 1, 40, 200], heat[1, 1, 0, 255] = 0.9, 0.8, 0.7
+    size = synth.uniform(80, "osz", (B, 2, H, W))
+    size[0, :, ::4, ::4] = -1.0                      # invalid boxes among the crowded candidates
+    off = synth.uniform(80, "oof", (B, 2, H, W))
+    bias = 0.0
+    if logits:
+        heat = (np.log(heat / (1 - heat)) - 0.3).astype(np.float32)
+        bias = 0.3
+    hd, sd, od = dev(heat, cuda), dev(size, cuda), dev(off, cuda)
+    full = ops.centernet_to_host(*ops.centernet_decode(hd, sd, od, 0.2, K, logits=logits, heatmap_bias=bias))
+    small = ops.centernet_to_host(*ops.centernet_decode(hd, sd, od, 0.2, K, logits=logits, heatmap_bias=bias,
+                                                        candidate_capacity=1))
+    if logits:
+        scores = ops.centernet_activate(torch.cat([hd, sd, od], 1), classes, bias)[:, :classes].contiguous().cpu().numpy()
+    else:
+        scores = heat
+    ref, ncand = oracle.centernet_decode(scores, size, off, 0.2, K)
+    assert ncand[0] > 2000 and ncand[1] == 3 and ncand[2] > 2000
+    for b in range(B):
+        assert len(full[b]) == len(ref[b]) == min(K, ncand[b])
+        dets_equal(full[b], ref[b])
+        assert small[b].tobytes() == full[b].tobytes()
+
+
+@pytest.mark.parametrize("logits", [False, True])
+def test_centernet_raised_bound_with_too_few_valid_boxes_is_redone(cuda, oracle, logits):
+    """The sampling pass raises an image's listing bound when the map holds far more hot cells than an image
+    keeps.  If most of the boxes above the bound then turn out invalid, fewer than K detections remain above it and
+    some of the K best may lie below: the image is redone without a bound.  Image 0: almost every box invalid;
+    image 1: all valid (keeps its raised bound); image 2: nothing above the threshold."""
+    B, classes, H, W, K = 3, 4, 64, 128, 50
+    heat, size, off = centernet_case(52, B, classes, H, W)
+    heat[2] = -9.0
+    size[0] = -1.0
+    rng = np.random.default_rng(9)
+    for _ in range(70):                              # 70 valid boxes at random places of image 0
+        size[0, :, int(rng.integers(H)), int(rng.integers(W))] = 0.5
+    act = oracle.centernet_activate(np.concatenate([heat, size, off], 1), classes, 0.0)
+    scores = np.ascontiguousarray(act[:, :classes])
+    ref, ncand = oracle.centernet_decode(scores, size, off, 0.2, K)
+    src = heat if logits else scores
+    d, c = ops.centernet_decode(dev(src, cuda), dev(size, cuda), dev(off, cuda), 0.2, K, logits=logits, heatmap_bias=0.0)
+    got = ops.centernet_to_host(d, c)
+    assert 0 < ncand[0] < K and ncand[1] > 10 * K and ncand[2] == 0
+    for b in range(B):
+        assert len(got[b]) == len(ref[b]) == min(K, ncand[b])
+        assert np.array_equal(got[b]["source"], ref[b]["source"])
+        if not logits:
+            dets_equal(got[b], ref[b])
+
+
+def test_centernet_plateau_larger_than_the_default_list(cuda):
+    """An all-equal map of more cells than an image's list holds by default: every cell is a maximum, the
+    list overflows, the tile pass takes over and the K lowest indices win."""
+    flat = np.full((2, 1, 200, 200), 0.5, np.float32)
+    flat[1] = 0.1
+    flat[1, 0, 7, 9] = 0.6
+    ones = np.ones((2, 2, 200, 200), np.float32)
+    d, c = ops.centernet_decode(dev(flat, cuda), dev(ones, cuda), dev(ones, cuda), 0.2, 100)
+    got = ops.centernet_to_host(d, c)
+    assert got[0]["source"].tolist() == list(range(100))
+    assert got[1]["source"].tolist() == [7 * 200 + 9]
+    with pytest.raises(ops.PxeError):
+        ops.centernet_decode(dev(flat, cuda), dev(ones, cuda), dev(ones, cuda), 0.2, 100, candidate_capacity=1 << 20)
+
+
 @pytest.mark.parametrize("shape,groups,temp", [((4, 1000, 1, 1), 1, 1.0), ((2, 30, 1, 1), 3, 0.7), ((3, 5, 2, 2), 1, 2.0),
                                                ((1, 3000, 1, 1), 1, 1.0)])
 def test_softmax(cuda, oracle, shape, groups, temp):
