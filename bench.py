@@ -35,12 +35,42 @@ import numpy as np  # noqa: E402
 
 SEED = 1234
 CONF = 0.2
+NMS = 0.4
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of each kernel on a [32,32,208,208] tensor,
-# divided by that launch's algorithmic bytes (profiles/epilogue_kernel_*.md, profiles/epilogue_pool_kernel_*.md).
-# Traffic grows in proportion to the tensor, so a launch's traffic is this ratio times its algorithmic bytes; the
-# ratio is below 1 because part of the written lines is still dirty in L2 when the kernel ends.
-NCU_TRAFFIC_RATIO = {"epilogue": 0.838, "epilogue+shortcut": 0.923, "epilogue+pool": 0.935}
+# A head that behaves like a trained one, for the end-to-end arm that gathers final detections.  With the plain
+# seeded init a deep residual graph drives its heads to logits of magnitude 1e6: every box is certain or absent and
+# 228 k candidates per image pass the confidence threshold.  Here the head convolutions' weights are scaled back
+# to logits of order one (powers of two, so products stay exact) and the objectness / class biases lowered.
+HEAD_VARIANT = {
+    "yolov3-608": dict(head_bias=-4.0, class_bias=-1.0, head_gain={81: 2.0 ** -19, 93: 2.0 ** -19, 105: 2.0 ** -18}),
+    "yolov3-tiny": dict(head_bias=-4.0, class_bias=-1.0, head_gain=0.5),
+    "yolov7": dict(head_bias=-4.0, class_bias=-1.0, head_gain=16.0),
+}
+HEAD_VARIANT_NOTE = {
+    "yolov3-608": "head conv weights x 2^-19 / 2^-19 / 2^-18 (logits of order one), objectness bias -4, class bias -1",
+    "yolov3-tiny": "head conv weights x 0.5, objectness bias -4, class bias -1",
+    "yolov7": "head conv weights x 16, objectness bias -4, class bias -1",
+}
+
+def traffic_ratios():
+    """DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum of one capture) divided by the algorithmic
+    bytes of the captured launch, per kind of launch, read from the table in profiles/traffic_ratios.md -- which
+    names the kernel and the capture each figure comes from, so a changed kernel shows up as a stale row there
+    and not as a constant here.  Traffic grows in proportion to the tensor, so a launch's traffic is this ratio
+    times its algorithmic bytes."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "traffic_ratios.md")
+    if not os.path.exists(path):
+        return out
+    with open(path) as f:
+        for line in f:
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) >= 4 and cells[0] and not set(cells[0]) <= set("-: ") and cells[0] != "kind":
+                try:
+                    out[cells[0]] = {"ratio": float(cells[3]), "kernel": cells[1], "capture": cells[2]}
+                except ValueError:
+                    continue
+    return out
 
 
 def measured_peaks():
@@ -48,7 +78,7 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s: no MEASURED_PEAKS.json beside bench.py)"
 
 
 class ClockSampler:
@@ -226,14 +256,14 @@ def run_model(args):
     # ---- the same forward with channels-last activations (the library's NHWC tier), with cuDNN for every
     # convolution and with the first convolution fused with its epilogue (pxe_conv_stem): reported beside the
     # headline number, which stays on the reference's NCHW layout and cuDNN calls
-    def measure_variant(layout, fused_stem, note, conv_fusion=False):
-        r2 = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B,
-                    layout=layout, fused_stem=fused_stem, conv_fusion=conv_fusion)
-        r2.dets = runner.dets
-        if conv_fusion:
-            r2.forward(x)            # the eager pass in which every layer shape times its fused plans once
+    def time_runner(r2, x_dev, xh_pinned, nms_threshold=None, prepare=False):
+        """(device ms, end-to-end wall ms) for args.steps steps of runner r2, each the max over ranks: resident
+        input (one CUDA-graph replay per step unless --cuda-graph off), then host batch in / host records out
+        through PipelinedPredictor (with px::nms on the device when nms_threshold is given)."""
+        if prepare:
+            r2.forward(x_dev)            # the eager pass in which every layer shape times its fused plans once
             torch.cuda.synchronize()
-        step2 = r2.capture(x).replay if use_graph else (lambda: r2.forward(x))
+        step2 = r2.capture(x_dev).replay if use_graph else (lambda: r2.forward(x_dev))
         for _ in range(args.warmup):
             step2()
         barrier()
@@ -246,32 +276,75 @@ def run_model(args):
         if world > 1:
             dist.all_reduce(alt_ms, op=dist.ReduceOp.MAX)
         del step2
-        # ... and end to end, the same way as the headline's e2e
-        pipe2 = PipelinedPredictor(r2, tuple(xh.shape), use_graphs=use_graph)
-        pipe2.submit(xh)
+        pipe2 = PipelinedPredictor(r2, tuple(xh_pinned.shape), use_graphs=use_graph, nms_threshold=nms_threshold)
+        pipe2.submit(xh_pinned)
         pipe2.drain()
         barrier()
         w0 = time.perf_counter()
         for _ in range(args.steps):
-            pipe2.submit(xh)
-        pipe2.drain()
+            pipe2.submit(xh_pinned)
+        last = pipe2.drain()
         torch.cuda.synchronize()
         alt_wall = torch.tensor([(time.perf_counter() - w0) * 1e3], device=dev, dtype=torch.float64)
         barrier()
         if world > 1:
             dist.all_reduce(alt_wall, op=dist.ReduceOp.MAX)
+        return float(alt_ms.item()), float(alt_wall.item()), len(last[0]), int(last[1])
+
+    def measure_variant(layout, fused_stem, note, conv_fusion=False):
+        r2 = Runner(model, weights, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B,
+                    layout=layout, fused_stem=fused_stem, conv_fusion=conv_fusion)
+        r2.dets = runner.dets
+        alt_ms, alt_wall, _, _ = time_runner(r2, x, xh, prepare=conv_fusion)
         extra = {}
         if conv_fusion:
-            extra = {"conv_fusion": dict(r2.fused_conv.summary(), launches_per_step=r2.fused_conv_launches,
-                                         shapes_timed=[{"x": list(k[0]), "w": list(k[1]), "stride": k[2], "shortcut": bool(k[7]),
-                                                        "choice": c, "fused_ms": f and round(f, 4), "split_ms": round(sp, 4)}
-                                                       for k, c, f, sp in r2.fused_conv.log])}
+            extra = {"conv_fusion": dict(r2.fused_conv.summary(), launches_per_step=r2.fused_conv_launches)}
+            if args.fusion_shapes:
+                extra["conv_fusion"]["shapes_timed"] = [
+                    {"x": list(k[0]), "w": list(k[1]), "stride": k[2], "shortcut": bool(k[7]), "choice": c,
+                     "fused_ms": f and round(f, 4), "split_ms": round(sp, 4)} for k, c, f, sp in r2.fused_conv.log]
         return {"layout": layout, "fused_stem": bool(r2.stem is not None), **extra,
-                "value": round(B * world * args.steps / (float(alt_ms.item()) / 1e3), 2), "unit": "images/s",
-                "ms_per_step": round(float(alt_ms.item()) / args.steps, 3),
-                "e2e_value": round(B * world * args.steps / (float(alt_wall.item()) / 1e3), 2),
+                "value": round(B * world * args.steps / (alt_ms / 1e3), 2), "unit": "images/s",
+                "ms_per_step": round(alt_ms / args.steps, 3),
+                "e2e_value": round(B * world * args.steps / (alt_wall / 1e3), 2),
                 "note": note + "; same graph, weights and input; resident input, "
                         + ("one CUDA graph replay per step" if use_graph else "eager launches")}
+
+    # ---- the same model with a head that behaves like a trained one (see HEAD_VARIANT): candidates per image in
+    # the thousands instead of 228 k, px::nms on the device, only survivors copied to the host
+    def measure_post_nms():
+        hw = synth_weights(model, SEED, **HEAD_VARIANT[args.workload])
+        r2 = Runner(model, hw, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B)
+        ms2, wall2, kept, total = time_runner(r2, x, xh, nms_threshold=NMS)
+        return {"value": round(B * world * args.steps / (wall2 / 1e3), 2), "unit": "images/s",
+                "resident_value": round(B * world * args.steps / (ms2 / 1e3), 2),
+                "candidates_per_step_per_gpu": total, "survivors_per_step_per_gpu": kept,
+                "d2h_bytes_per_step": kept * 32 + 16,
+                "head": HEAD_VARIANT_NOTE[args.workload]}
+
+    # ---- the configured split of the same global batch over the ranks (strong scaling): B / world images per rank
+    def measure_strong():
+        per = max(1, B // world)
+        r2 = Runner(model, weights, per, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * per)
+        xs_h = torch.from_numpy(host_batch(model, per, rank * per)).pin_memory()
+        ms2, wall2, _, _ = time_runner(r2, xs_h.to(dev), xs_h)
+        return {"per_gpu_batch": per, "global_batch": per * world,
+                "value": round(per * world * args.steps / (ms2 / 1e3), 2),
+                "e2e": round(per * world * args.steps / (wall2 / 1e3), 2), "ms_per_step": round(ms2 / args.steps, 3)}
+
+    # ---- BASELINE.json's YOLOv7-640 configuration: 16 images per GPU (128 over 8 GPUs)
+    def measure_c3():
+        doc3, _ = make_doc("yolov7")
+        m3 = graph.parse_model(doc3)
+        w3 = synth_weights(m3, SEED)
+        r3 = Runner(m3, w3, 16, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * 16)
+        x3_h = torch.from_numpy(host_batch(m3, 16, rank * 16)).pin_memory()
+        x3 = x3_h.to(dev)
+        for _ in range(2):
+            r3.forward(x3)
+        ms3, wall3, _, _ = time_runner(r3, x3, x3_h)
+        return {"per_gpu_batch": 16, "global_batch": 16 * world, "value": round(16 * world * args.steps / (ms3 / 1e3), 2),
+                "e2e": round(16 * world * args.steps / (wall3 / 1e3), 2), "ms_per_step": round(ms3 / args.steps, 3)}
 
     alt = alt_stem = nchw_stem = alt_fusion = None
     if args.layout == "nchw" and not args.no_alt_layout:
@@ -297,6 +370,20 @@ def run_model(args):
                 alt_fusion = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
             torch.cuda.empty_cache()
 
+    post_nms = strong = c3 = None
+    if args.workload == "yolov3-608" and not args.no_extras:
+        try:
+            del pipe
+        except NameError:
+            pass
+        torch.cuda.empty_cache()
+        post_nms = measure_post_nms()
+        torch.cuda.empty_cache()
+        strong = measure_strong() if world > 1 else None
+        torch.cuda.empty_cache()
+        c3 = measure_c3()
+        torch.cuda.empty_cache()
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -305,6 +392,7 @@ def run_model(args):
     images = B * world * args.steps
     value = images / (total_ms / 1e3)
     peak, peak_src = measured_peaks()
+    ratios = traffic_ratios()
     mine = {k: v for k, v in ops_summary.items() if "cudnn" not in k}       # this library's kernels only
     dom = max(mine, key=lambda k: mine[k]["ms"])
     d = mine[dom]
@@ -339,9 +427,10 @@ def run_model(args):
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                      "peak_source": peak_src,
-                     "traffic": (int(NCU_TRAFFIC_RATIO[dom] * d["bytes"] / d["launches"]) if dom in NCU_TRAFFIC_RATIO else None),
-                     "traffic_note": "bytes per launch (average over the timed launches): ncu DRAM read+write of a smaller "
-                                     "capture of this kernel, scaled by algorithmic bytes",
+                     "traffic": (int(ratios[dom]["ratio"] * d["bytes"] / d["launches"]) if dom in ratios else None),
+                     "traffic_note": ("bytes per launch (average over the timed launches): ncu DRAM read+write of a smaller "
+                                      f"capture ({ratios[dom]['kernel']}, {ratios[dom]['capture']}: x{ratios[dom]['ratio']} of its "
+                                      "algorithmic bytes), scaled by algorithmic bytes") if dom in ratios else "no capture on record",
                      "algorithmic_bytes_per_launch": int(d["bytes"] / d["launches"]),
                      "launches_timed": d["launches"], "avg_launch_ms": round(d["ms"] / d["launches"], 4),
                      "algorithmic_bytes_per_step": int(d["bytes"] / args.steps)},
@@ -356,6 +445,57 @@ def run_model(args):
             line["nchw_fused_stem"] = nchw_stem
         if alt_fusion is not None:
             line["channels_last_conv_fusion"] = alt_fusion
+    if post_nms is not None:
+        line["e2e"].update(post_nms_value=post_nms["value"], post_nms_resident_value=post_nms["resident_value"],
+                           post_nms_d2h_bytes_per_step=post_nms["d2h_bytes_per_step"],
+                           post_nms_candidates_per_step_per_gpu=post_nms["candidates_per_step_per_gpu"],
+                           post_nms_survivors_per_step_per_gpu=post_nms["survivors_per_step_per_gpu"],
+                           post_nms_head=post_nms["head"],
+                           post_nms_api="PipelinedPredictor(nms_threshold=0.4): decode, px::nms on the device, survivors -> pinned host")
+        line["config"].update(
+            strong_value=strong["value"] if strong else line["value"],
+            strong_e2e=strong["e2e"] if strong else line["e2e"]["value"],
+            strong_per_gpu_batch=strong["per_gpu_batch"] if strong else B,
+            strong_global_batch=strong["global_batch"] if strong else B,
+            strong_note="the same model with the global batch of one GPU's share split over the ranks (BASELINE.json's "
+                        "64 / 32 / 16 / 8 images per GPU)",
+            c3_value=c3["value"], c3_e2e=c3["e2e"], c3_per_gpu_batch=16, c3_global_batch=c3["global_batch"],
+            c3_ms_per_step=c3["ms_per_step"], c3_note="YOLOv7 640x640, 16 images per GPU, same measurement")
+    if world == 1 and not args.no_extras and args.workload == "yolov3-608":
+        # the path's other stated targets, measured after every timed region above, on this GPU
+        del runner
+        torch.cuda.empty_cache()
+        try:
+            ours_ms, ref_ms, _, _ = epilogue_compare(args, "yolov3-608", B)
+            line["roofline"].update(epilogue_ms=round(ours_ms, 3), ref_cuda_epilogue_ms=round(ref_ms, 3) if ref_ms else None,
+                                    vs_ref_cuda=round(ref_ms / ours_ms, 2) if ref_ms else None,
+                                    ref_cuda_kind="reference-cuda: the reference's own src/*.cu for sm_100a (oracle/_ref/"
+                                                  "libpxref_cuda.so) replaying Layer<CUDA>::forward's epilogue calls on "
+                                                  f"YOLOv3-608, {B} images, beside this library's planned launches; no convolutions")
+        except Exception as e:
+            line["roofline"]["ref_cuda_error"] = f"{type(e).__name__}: {str(e)[:160]}"
+        torch.cuda.empty_cache()
+        sw_args = argparse.Namespace(**vars(args))
+        sw_args.sweep_shapes, sw_args.sweep_shape_index, sw_args.sweep_residual, sw_args.layout = 0, -1, False, "nchw"
+        sw_args.steps = max(args.steps, 10)
+        rows = sweep_rows(sw_args, [(a, k) for a in ("leaky", "mish") for k in ("plain", "pool", "shortcut")])
+        worst = min(rows, key=lambda r: r["frac_measured"])
+        vs_copy = [r["GBps"] / r["copy_GBps"] for r in rows]
+        line["roofline"].update(
+            sweep_cells=len(rows), sweep_min_frac=worst["frac_measured"],
+            sweep_median_frac=round(statistics.median(r["frac_measured"] for r in rows), 3),
+            sweep_max_frac=max(r["frac_measured"] for r in rows),
+            sweep_worst_cell=f"{'x'.join(map(str, worst['shape']))} {worst['act']} "
+                             f"{'pool' if worst['pool'] else ('shortcut' if worst['residual'] else 'plain')}",
+            sweep_worst_cell_copy_frac=round(worst["copy_GBps"] / peak, 3),
+            sweep_min_vs_copy=round(min(vs_copy), 3), sweep_median_vs_copy=round(statistics.median(vs_copy), 3),
+            sweep_note="isolated fused epilogue, [64,C,H,W] x {leaky, mish} x {plain, +2x2 pool, +shortcut}: fraction of the "
+                       "measured peak on algorithmic bytes; *_vs_copy = against a device copy of the same tensor timed the same way")
+        torch.cuda.empty_cache()
+        cn_ms, _ = centernet_time(args, 256)
+        line["roofline"].update(centernet_ms=round(cn_ms, 4), centernet_batch=256,
+                                centernet_frac=round(4 * 256 * 20 * 128 * 128 / cn_ms / 1e6 / peak, 4),
+                                centernet_note="CenterNet head decode, [256,20,128,128] logits, K=100: heat-map bytes / time / peak")
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, steps=1, warmup=0)
     print(json.dumps(line), flush=True)
@@ -430,11 +570,12 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------ other workloads
-def run_sweep(args):
-    """Isolated fused-epilogue sweep: [64,C,H,W] x {leaky, mish, swish, logistic} x {no pool, 2x2/2 pool}."""
+def sweep_rows(args, variants=None):
+    """Times the cells of the isolated fused-epilogue sweep.  ``variants``: list of (act, kind) with kind in
+    {"plain", "pool", "shortcut"}; None = the cells the command line asks for."""
     import torch
     from pixienn_b200 import ops, synth
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", torch.cuda.current_device())
     peak, peak_src = measured_peaks()
     shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
     if args.sweep_shapes:
@@ -454,7 +595,8 @@ def run_sweep(args):
             base = base.contiguous(memory_format=torch.channels_last)
             fa, fb = ops.fold_bn(C, dev, gamma=g, beta=b, mean=m, var=v, bias=bias)
         xs = [base.clone() for _ in range(sets)]
-        frm = [base.clone() for _ in range(sets)] if args.sweep_residual else None
+        want_res = args.sweep_residual or (variants is not None and any(k == "shortcut" for _, k in variants))
+        frm_sets = [base.clone() for _ in range(sets)] if want_res else None
 
         def graph_time(call):
             """Median / min device time (ms) of one call: a CUDA graph holds one launch per rotating input set;
@@ -479,39 +621,52 @@ def run_sweep(args):
         dsts = [torch.empty_like(base) for _ in range(sets)]
         copy_med, _ = graph_time(lambda i: dsts[i % sets].copy_(xs[i % sets]))
         del dsts
-        for act in args.sweep_acts.split(","):
-            for pool in {"none": (False,), "pool": (True,), "both": (False, True)}[args.sweep_pool]:
-                if pool and frm is not None:
-                    continue
-                oh = ops.maxpool_out_dim(H, 2, 2, 1)
-                yps = [torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) for _ in range(sets)] if pool else None
-                if nhwc and pool:
-                    yps = [t.contiguous(memory_format=torch.channels_last) for t in yps]
+        if variants is None:
+            cells = [(act, "pool" if pool else ("shortcut" if args.sweep_residual else "plain"))
+                     for act in args.sweep_acts.split(",")
+                     for pool in {"none": (False,), "pool": (True,), "both": (False, True)}[args.sweep_pool]
+                     if not (pool and args.sweep_residual)]
+        else:
+            cells = list(variants)
+        for act, kind in cells:
+            pool = kind == "pool"
+            frm = frm_sets if kind == "shortcut" else None
+            oh = ops.maxpool_out_dim(H, 2, 2, 1)
+            yps = [torch.empty((B, C, oh, ops.maxpool_out_dim(W, 2, 2, 1)), device=dev) for _ in range(sets)] if pool else None
+            if nhwc and pool:
+                yps = [t.contiguous(memory_format=torch.channels_last) for t in yps]
 
-                def call(i):
-                    if nhwc:
-                        if pool:
-                            ops.conv_epilogue_nhwc(xs[i % sets], y=False, a=fa, b=fb, act=act, pool=(2, 2, 1), y_pool=yps[i % sets])
-                        elif frm is not None:
-                            ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act, residual=frm[i % sets], res_act="linear")
-                        else:
-                            ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act)
-                    elif pool:
-                        ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
-                                          pool=(2, 2, 1), y_pool=yps[i % sets])
-                    elif frm is not None:      # conv epilogue + the shortcut layer that follows it: 12 B / element
-                        ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
-                                          residual=frm[i % sets], res_act="linear")
+            def call(i):
+                if nhwc:
+                    if pool:
+                        ops.conv_epilogue_nhwc(xs[i % sets], y=False, a=fa, b=fb, act=act, pool=(2, 2, 1), y_pool=yps[i % sets])
+                    elif frm is not None:
+                        ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act, residual=frm[i % sets], res_act="linear")
                     else:
-                        ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act)
-                med, tmin = graph_time(call)
-                nbytes = (4 * n + 4 * yps[0].numel()) if pool else (12 * n if frm is not None else 8 * n)
-                rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "residual": frm is not None, "MB": round(nbytes / 1e6, 1),
-                             "us_median": round(med * 1e3, 2), "us_min": round(tmin * 1e3, 2),
-                             "copy_us": round(copy_med * 1e3, 2), "copy_GBps": round(8 * n / copy_med / 1e6, 1),
-                             "GBps": round(nbytes / med / 1e6, 1), "frac_measured": round(nbytes / med / 1e6 / peak, 3),
-                             "frac_8000": round(nbytes / med / 1e6 / 8000, 3)})
-        del xs
+                        ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act)
+                elif pool:
+                    ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
+                                      pool=(2, 2, 1), y_pool=yps[i % sets])
+                elif frm is not None:      # conv epilogue + the shortcut layer that follows it: 12 B / element
+                    ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
+                                      residual=frm[i % sets], res_act="linear")
+                else:
+                    ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act)
+            med, tmin = graph_time(call)
+            nbytes = (4 * n + 4 * yps[0].numel()) if pool else (12 * n if frm is not None else 8 * n)
+            rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "residual": frm is not None, "MB": round(nbytes / 1e6, 1),
+                         "us_median": round(med * 1e3, 2), "us_min": round(tmin * 1e3, 2),
+                         "copy_us": round(copy_med * 1e3, 2), "copy_GBps": round(8 * n / copy_med / 1e6, 1),
+                         "GBps": round(nbytes / med / 1e6, 1), "frac_measured": round(nbytes / med / 1e6 / peak, 3),
+                         "frac_8000": round(nbytes / med / 1e6 / 8000, 3)})
+        del xs, frm_sets
+    return rows
+
+
+def run_sweep(args):
+    """Isolated fused-epilogue sweep: [64,C,H,W] x {leaky, mish, swish, logistic} x {no pool, 2x2/2 pool}."""
+    peak, peak_src = measured_peaks()
+    rows = sweep_rows(args)
     for r in rows:
         print(json.dumps(r), file=sys.stderr)
     fr = [r["frac_measured"] for r in rows]
@@ -523,13 +678,13 @@ def run_sweep(args):
                       "cells": rows}), flush=True)
 
 
-def run_centernet(args):
-    """CenterNet head decode: [B,20,128,128] heat logits N(-4,2) + Gaussian peaks, K = 100."""
+def centernet_time(args, B):
+    """CenterNet head decode: [B,20,128,128] heat logits N(-4,2) + Gaussian peaks, K = 100.  Returns
+    (median ms per decode, mean records kept per image)."""
     import torch
     from pixienn_b200 import ops, synth
-    dev = torch.device("cuda", 0)
-    peak, peak_src = measured_peaks()
-    B, classes, H, W, K = args.batch, 20, 128, 128, 100
+    dev = torch.device("cuda", torch.cuda.current_device())
+    classes, H, W, K = 20, 128, 128, 100
     rng = np.random.default_rng(SEED)
     heat = synth.normal(SEED, "c4/heat", (B, classes, H, W), -4.0, 2.0)
     yy, xx = np.mgrid[0:H, 0:W]
@@ -544,9 +699,10 @@ def run_centernet(args):
     off = torch.from_numpy(synth.uniform(SEED, "c4/off", (B, 2, H, W))).to(dev)
     need = ops.capi.lib().pxe_centernet_decode_workspace_bytes(B, classes, H, W, K)
     ws = torch.empty(need, device=dev, dtype=torch.uint8)
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, 3)):
         ops.centernet_decode(hs[i % sets], size, off, CONF, K, logits=True, heatmap_bias=0.0, workspace=ws)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    steps = max(args.steps, 10)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     torch.cuda.synchronize()
     for i, (a, z) in enumerate(ev):
         a.record()
@@ -554,13 +710,19 @@ def run_centernet(args):
         z.record()
     torch.cuda.synchronize()
     ts = sorted(a.elapsed_time(z) for a, z in ev)
-    med = ts[len(ts) // 2]
-    nbytes = 4 * B * classes * H * W
+    return ts[len(ts) // 2], float(c.float().mean().item())
+
+
+def run_centernet(args):
+    peak, peak_src = measured_peaks()
+    B = args.batch
+    med, kept = centernet_time(args, B)
+    nbytes = 4 * B * 20 * 128 * 128
     print(json.dumps({"metric": "CenterNet head decode", "value": round(B / (med / 1e3), 1), "unit": "images/s", "n_gpus": 1,
-                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(med, 4), "higher_is_better": True,
+                      "steps": max(args.steps, 10), "warmup": max(args.warmup, 3), "ms_per_step": round(med, 4), "higher_is_better": True,
                       "dtype": "f32", "data": "synthetic",
                       "config": {"workload": f"CenterNet decode B={B}, 20x128x128 heat + 2x wh + 2x offset, K=100, thr {CONF}",
-                                 "l2": "3 rotating 335 MB heatmaps", "kept_per_image_mean": float(c.float().mean().item())},
+                                 "l2": "3 rotating heat maps", "kept_per_image_mean": kept},
                       "roofline": {"bound": "hbm", "achieved": round(nbytes / med / 1e6, 1), "peak": peak, "unit": "GB/s",
                                    "frac": round(nbytes / med / 1e6 / peak, 4), "peak_source": peak_src, "traffic": None}}),
           flush=True)
@@ -613,20 +775,20 @@ def run_nms(args):
                       "host_ms": round(host_ms, 2), "identical_to_host": bool(got.tobytes() == want.tobytes())}), flush=True)
 
 
-def run_epilogue_compare(args):
+def epilogue_compare(args, model_name, B):
     """Epilogue path only (no convolutions), layer by layer over the model graph, on scratch buffers of
     each layer's shape: the reference's own CUDA call sequences (its src/*.cu compiled for sm_100a in
     oracle/_ref/libpxref_cuda.so: fills, cuDNN BN inference, preActivation copy, thrust activation, per-image
     route copies, shortcut copy + kernel + activation, YOLO activate + full device-to-host copy) against
-    this library's planned launches.  Reports milliseconds per batch for both and the ratio."""
+    this library's planned launches.  Returns (ms per batch here, ms per batch of the reference's kernels or None
+    when that library is not built, label, plan statistics)."""
     import torch
     from oracle import pxoracle as po
     from pixienn_b200 import graph, ops
     from pixienn_b200.runner import synth_weights
-    dev = torch.device("cuda", 0)
-    doc, label = make_doc(args.model)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    doc, label = make_doc(model_name)
     model = graph.parse_model(doc)
-    B = args.batch
     L = model.layers
     ref = po.ref_cuda()
     weights = synth_weights(model, SEED)
@@ -733,6 +895,12 @@ def run_epilogue_compare(args):
 
     ours = timed(our_pass)
     refms = timed(reference_pass) if ref is not None else None
+    return ours, refms, label, plan.stats
+
+
+def run_epilogue_compare(args):
+    B = args.batch
+    ours, refms, label, stats = epilogue_compare(args, args.model, B)
     print(json.dumps({"metric": f"{label} epilogue path only, ms per {B}-image batch", "value": round(ours, 3), "unit": "ms",
                       "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "f32",
                       "data": "synthetic", "reference_cuda_ms": round(refms, 3) if refms else None,
@@ -741,7 +909,7 @@ def run_epilogue_compare(args):
                       "reference_cuda_images_per_s": round(B / refms * 1e3, 1) if refms else None,
                       "config": {"workload": f"{label}, {B} images, epilogue launches only (no convolution), scratch buffers of each "
                                              "layer's shape; reference = its own src/*.cu for sm_100a replaying Layer<CUDA>::forward",
-                                 "plan": plan.stats}}), flush=True)
+                                 "plan": stats}}), flush=True)
 
 
 def main():
@@ -755,8 +923,12 @@ def main():
     ap.add_argument("--cpu-images", type=int, default=2, help="images per step of the CPU reference sample")
     ap.add_argument("--det-capacity", type=int, default=24 * (1 << 20))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-single-core", action="store_true",
-                    help="also time the CPU reference on one host thread (one image, adds about ten seconds)")
+    ap.add_argument("--no-cpu-single-core", dest="cpu_single_core", action="store_false",
+                    help="skip timing the CPU reference on one host thread as well (one image, a few seconds)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline: skip the post-NMS end-to-end arm, the configured split, YOLOv7 and (at one "
+                         "GPU) the reference-CUDA epilogue comparison, the compact sweep and the CenterNet decode")
+    ap.add_argument("--fusion-shapes", action="store_true", help="list every layer shape the conv-fusion variant timed")
     ap.add_argument("--sweep-shapes", type=int, default=0, help="only the first N shapes of the sweep")
     ap.add_argument("--sweep-shape-index", type=int, default=-1, help="only this shape of the sweep (0..4)")
     ap.add_argument("--sweep-acts", default="leaky,mish,swish,logistic")

@@ -723,11 +723,18 @@ class PipelinedPredictor:
     until two more batches have been submitted.
     """
 
-    def __init__(self, runner: Runner, batch_shape, pinned_capacity: Optional[int] = None, use_graphs: bool = False):
+    def __init__(self, runner: Runner, batch_shape, pinned_capacity: Optional[int] = None, use_graphs: bool = False,
+                 nms_threshold: Optional[float] = None):
+        """``nms_threshold``: run px::nms on the device (pxe_nms) on each batch's candidates and copy only the
+        survivors to the host, as Model::predict does after detections(); None copies every candidate."""
         self.r = runner
         dev = runner.device
         self.compute = torch.cuda.current_stream(dev)
         self.h2d, self.d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.nms_threshold = nms_threshold
+        self.kept = [None, None]          # per slot: device buffer of NMS survivors
+        self.kept_count_host = [torch.zeros(1, dtype=torch.int64).pin_memory() for _ in range(2)]
+        self.nms_ws = None
         cap = pinned_capacity or runner.dets.capacity
         self.x = [torch.empty(batch_shape, device=dev) for _ in range(2)]
         self.bufs = [runner.dets, ops.DetectionBuffer(runner.dets.capacity, dev)]
@@ -772,8 +779,24 @@ class PipelinedPredictor:
         ev.synchronize()                                  # the next forward is already queued behind this one
         total = int(self.count_host[slot].item())
         n = min(total, buf.capacity, self.pinned[slot].shape[0])
+        src = buf.dets
+        if self.nms_threshold is not None:
+            # NMS of this batch on the copy stream, beside the next batch's forward pass; only survivors leave the GPU
+            with torch.cuda.stream(self.d2h):
+                need = ops.capi.lib().pxe_nms_workspace_bytes(n)
+                if self.nms_ws is None or self.nms_ws.numel() < need:
+                    self.nms_ws = torch.empty(max(need, 256), device=buf.dets.device, dtype=torch.uint8)
+                if self.kept[slot] is None or self.kept[slot].shape[0] < max(n, 1):
+                    self.kept[slot] = torch.empty((max(n, 1), 8), device=buf.dets.device, dtype=torch.int32)
+                _, kept_count = ops.nms_device(buf.dets, n, self.nms_threshold, out=self.kept[slot], workspace=self.nms_ws)
+                self.kept_count_host[slot].copy_(kept_count, non_blocking=True)
+                ev2 = torch.cuda.Event()
+                ev2.record(self.d2h)
+            ev2.synchronize()
+            n = min(int(self.kept_count_host[slot].item()), self.pinned[slot].shape[0])
+            src = self.kept[slot]
         with torch.cuda.stream(self.d2h):
-            self.pinned[slot][:n].copy_(buf.dets[:n], non_blocking=True)
+            self.pinned[slot][:n].copy_(src[:n], non_blocking=True)
             out = torch.cuda.Event()
             out.record(self.d2h)
         self.out_done[slot] = out

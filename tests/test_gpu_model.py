@@ -170,6 +170,28 @@ def test_pipelined_predictor_equals_sequential_predict(cuda, use_graphs):
         assert len(w) > 0 and g.tobytes() == w.tobytes()
 
 
+def test_pipelined_predictor_with_device_nms_returns_the_survivors(cuda):
+    """nms_threshold: px::nms runs on the device beside the next batch's forward pass and only the survivors are
+    copied to the host: the same records as predict() with host NMS, batch by batch."""
+    from pixienn_b200.runner import PipelinedPredictor
+    model = graph.parse_model(presets.yolov3_tiny(160, 160))
+    weights = synth_weights(model, 9, head_bias=-3.0)
+    batches = [torch.from_numpy(make_input(60 + i, 2, model)).pin_memory() for i in range(4)]
+    seq = Runner(model, weights, 2, cuda)
+    want = [seq.predict(b, nms_threshold=0.4) for b in batches]
+    pipe = PipelinedPredictor(Runner(model, weights, 2, cuda), tuple(batches[0].shape), use_graphs=True, nms_threshold=0.4)
+    got = []
+    for b in batches:
+        r = pipe.submit(b)
+        if r is not None:
+            got.append((r[0].copy(), r[1]))
+    last = pipe.drain()
+    got.append((last[0].copy(), last[1]))
+    assert len(got) == 4
+    for (g, gt), (w, wt) in zip(got, want):
+        assert gt == wt and 0 < len(w) < wt and g.tobytes() == w.tobytes()
+
+
 @pytest.mark.parametrize("name", ["yolov3_tiny", "centernet_tiny"])
 def test_cuda_graph_replay_equals_eager_forward(cuda, name):
     """Runner.capture: replays read the captured input tensor's current contents and rewrite the same
