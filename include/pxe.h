@@ -468,6 +468,36 @@ PXE_API size_t pxe_nms_workspace_bytes(long long n);
 PXE_API int pxe_nms(pxe_stream_t stream, const pxe_detection* dets, long long n, float threshold,
                     pxe_detection* out, long long* out_count, void* workspace, size_t workspace_bytes);
 
+/* ------------------------------------------------------------------------------------------
+ * The other side of the same layers: what PixieNN's CUDA layers call on the way back through the
+ * graph and when they set weights up.  Element-wise and reduction kernels; none synchronises.
+ * ------------------------------------------------------------------------------------------ */
+/* px::gradient (include/Activation.cuh:27, src/Activation.cu:84-92, 135-143): delta[i] *= f'(x[i]) with the
+ * gradient() of the functor for `act` (include/Activation.h:54-228). */
+PXE_API int pxe_activation_gradient(pxe_stream_t stream, int act, const float* x, size_t n, float* delta);
+/* px::backwardBiasGpu (include/BiasKernels.cuh:22, src/BiasKernels.cu:39-111): bias_updates[f] += the sum of
+ * delta[b, f, 0..size) over the images; size == 1 is the connected-layer form. */
+PXE_API int pxe_backward_bias(pxe_stream_t stream, float* bias_updates, const float* delta, int batch, int n,
+                              int size);
+/* px::maxPoolBackwardGpu (include/MaxPoolKernels.cuh:7, src/MaxPoolKernels.cu:45-49, 61-65):
+ * grad[indexes[i]] += delta[i] for every output i whose window had a tap. */
+PXE_API int pxe_maxpool_backward(pxe_stream_t stream, const float* delta, const int* indexes, float* grad,
+                                 size_t size);
+/* px::upsampleGpu with forward == 0 (src/UpsampleKernels.cu:25-63): acc[b, c, y, x] += scale * the sum of the
+ * stride x stride elements of `out` ([batch, channels, height*stride, width*stride]) above that input. */
+PXE_API int pxe_upsample_backward(pxe_stream_t stream, float* acc, const float* out, int batch, int channels,
+                                  int height, int width, int stride, float scale);
+/* px::constrainGpu (src/CudaUtils.cu:122-138): x = min(alpha, max(-alpha, x)). */
+PXE_API int pxe_constrain(pxe_stream_t stream, float* x, size_t n, float alpha);
+/* px::mulGpu (src/CudaUtils.cu:140-146): y = x * y. */
+PXE_API int pxe_mul(pxe_stream_t stream, const float* x, float* y, size_t n);
+/* px::randomGpu / px::randomNormalGpu (src/CudaUtils.cu:77-120): element i is drawn from the minimal-standard
+ * generator (seed 1) advanced i steps, mapped to U[a, b) or to N(mean, stddev) by inversion.  The uniform
+ * values follow the reference's mapping; the normal values follow the same engine positions but this
+ * library's own inversion, so they agree with the reference in distribution, not digit for digit. */
+PXE_API int pxe_random_uniform(pxe_stream_t stream, float* out, size_t n, float a, float b);
+PXE_API int pxe_random_normal(pxe_stream_t stream, float* out, size_t n, float mean, float stddev);
+
 #ifdef __cplusplus
 }
 #endif

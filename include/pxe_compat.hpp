@@ -1,9 +1,14 @@
 /*
  * pxe_compat.hpp -- link-compatible tier.
  *
- * The eight free functions PixieNN's CUDA layers call between convolutions, declared with the
- * reference's exact C++ signatures (namespace px, same parameter types and order), so that the
- * reference links against libpxe.so instead of its own src/*.cu objects with no source change.
+ * The free functions of the reference's src/Activation.cu, BiasKernels.cu, MaxPoolKernels.cu,
+ * UpsampleKernels.cu, ShortcutKernel.cu and CudaUtils.cu -- forward and backward -- and the two head
+ * activations of YoloKernels.cu / CenterNetKernels.cu, declared with the reference's exact C++
+ * signatures (namespace px, same parameter types and order), so that the reference links against
+ * libpxe.so instead of those six object files with no source change.  (YoloKernels.cu and
+ * CenterNetKernels.cu also hold the loss launchers yoloLossGpu / centerNetLossGpu: a training build
+ * keeps those two files; their yoloActivateGpu / centerNetActivateGpu then take precedence over the
+ * ones here, which an inference-only build uses.)
  * Each one forwards to the C ABI in pxe.h on the legacy default stream and, like the
  * reference's PX_CUDA_CHECK_LAST, throws on failure (std::runtime_error here; the reference
  * throws px::CudaError, which also derives from std::exception).
@@ -13,6 +18,9 @@
  */
 #pragma once
 #include <cstddef>
+#include <cstdint>
+
+#include <vector_types.h>
 
 /* include/ActivationTypes.h:19-30 -- must stay value- and name-identical for the mangled
  * name of px::activate to match. */
@@ -40,7 +48,7 @@ void addBiasGpu(float* output, const float* biases, int batch, int n, int size);
 /* include/MaxPoolKernels.cuh:5 */
 void maxPoolForwardGpu(const float* input, float* output, int* indexes, int batch, int channels, int inputHeight,
                        int inputWidth, int outputHeight, int outputWidth, int kernel, int stride, int padding);
-/* include/UpsampleKernels.cuh:21 (forward != 0 only; the backward mode is training code) */
+/* include/UpsampleKernels.cuh:21 (forward != 0: out = scale * in; forward == 0: acc += scale * out, summed per input) */
 void upsampleGpu(const float* in, int w, int h, int c, int batch, int stride, int forward, float scale, float* acc,
                  float* out);
 /* include/ShortcutKernel.cuh:21 */
@@ -53,5 +61,19 @@ void centerNetActivateGpu(const float* input, float* output, int batch, int clas
 /* include/CudaUtils.cuh:29-30 */
 void fillGpu(float* ptr, std::size_t n, float value);
 void fillGpu(int* ptr, std::size_t n, int value);
+/* include/Activation.cuh:27 */
+void gradient(ActivationType type, const float* x, std::size_t n, float* delta);
+/* include/BiasKernels.cuh:22 */
+void backwardBiasGpu(float* biasUpdates, const float* delta, int batch, int n, int size);
+/* include/MaxPoolKernels.cuh:7 */
+void maxPoolBackwardGpu(const float* delta, const int* indexes, float* grad, int size);
+/* include/CudaUtils.cuh:27-33.  cudaGridsize: the launch grid for n threads in blocks of CUDA_BLOCK_SIZE = 512,
+ * folded into two dimensions beyond 65535 blocks (src/CudaUtils.cu:28-43); the reference's own kernels that
+ * stay in a build (Adam, the loss launchers) size their launches with it. */
+void constrainGpu(int n, float alpha, float* x);
+dim3 cudaGridsize(std::uint32_t n);
+void mulGpu(int n, float* x, float* y);
+void randomGpu(float* ptr, std::size_t n, float a = 0.f, float b = 1.f);
+void randomNormalGpu(float* ptr, std::size_t n, float mean = 0.f, float stddev = 1.f);
 
 }   // namespace px

@@ -73,6 +73,81 @@ PXO_API void pxo_activate(int type, float* x, size_t n)
     for (size_t i = 0; i < n; ++i) x[i] = pxo_activate_one(type, x[i]);
 }
 
+/* The gradient() members of the same functors, include/Activation.h:54-228. */
+static float softplus_gradient_ref(float x)
+{
+    if (x > 20.0f) return 1.0f;                     /* :120-129 */
+    if (x < -20.0f) return expf(x);
+    return 1.0f / (1.0f + expf(-x));
+}
+
+PXO_API float pxo_gradient_one(int type, float x)
+{
+    switch (type) {
+    case PXO_LEAKY:    return x > 0.0f ? 1.0f : 0.1f;
+    case PXO_LINEAR:   return 1.0f;
+    case PXO_LOGGY:    { float y = (x + 1.0f) / 2.0f; return 2.0f * (1 - y) * y; }
+    case PXO_LOGISTIC: { float y = 1.0f / (1.0f + expf(-x)); return y * (1.0f - y); }
+    case PXO_SOFTPLUS: return softplus_gradient_ref(x);
+    case PXO_MISH: {
+        float sp = softplus_ref(x), grad_sp = softplus_gradient_ref(x);
+        float tsp = tanhf(sp);
+        float grad_tsp = (1 - tsp * tsp) * grad_sp;
+        return x * grad_tsp + tsp;
+    }
+    case PXO_RELU:     return x > 0.0f ? 1.0f : 0.0f;
+    case PXO_SWISH:    { float val = 1 / (1 + expf(-1.0f * x)); return x * val + 1.0f * val * (1 - x * val); }
+    case PXO_TANH:     { float y = tanhf(x); return 1.0f - y * y; }
+    default:           return NAN;
+    }
+}
+
+/* Activation<U,CPU>::gradient(dbegin, dend, x), include/Activation.h:306-316: delta *= gradient(x). */
+PXO_API void pxo_gradient(int type, const float* x, size_t n, float* delta)
+{
+    for (size_t i = 0; i < n; ++i) delta[i] *= pxo_gradient_one(type, x[i]);
+}
+
+/* backwardBias, src/CpuUtil.cpp:189-196 (sumArray adds left to right, :208-215). */
+PXO_API void pxo_backward_bias(float* bias_updates, const float* delta, int batch, int n, int size)
+{
+    for (int b = 0; b < batch; ++b)
+        for (int i = 0; i < n; ++i) {
+            const float* a = delta + (size_t)size * (i + (size_t)b * n);
+            float sum = 0.0f;
+            for (int j = 0; j < size; ++j) sum += a[j];
+            bias_updates[i] += sum;
+        }
+}
+
+/* MaxPoolLayer::backward, include/MaxPoolLayer.h:138-158. */
+PXO_API void pxo_maxpool_backward(const float* delta, const int* indexes, float* grad, size_t size)
+{
+    for (size_t i = 0; i < size; ++i)
+        if (indexes[i] >= 0) grad[indexes[i]] += delta[i];
+}
+
+/* UpsampleLayer::upsample with forward == false, include/UpsampleLayer.h:97-121: acc[in] += scale * out[o],
+ * outputs visited in row-major order. */
+PXO_API void pxo_upsample_backward(float* acc, const float* out, int batch, int c, int h, int w, int stride, float scale)
+{
+    for (int b = 0; b < batch; ++b)
+        for (int k = 0; k < c; ++k)
+            for (int j = 0; j < h * stride; ++j)
+                for (int i = 0; i < w * stride; ++i) {
+                    size_t ii = (size_t)b * w * h * c + (size_t)k * w * h + (size_t)(j / stride) * w + i / stride;
+                    size_t oi = (size_t)b * w * h * c * stride * stride + (size_t)k * w * h * stride * stride
+                                + (size_t)j * w * stride + i;
+                    acc[ii] += scale * out[oi];
+                }
+}
+
+/* constrain(n, alpha, x, 1), src/CpuUtil.cpp:344-362. */
+PXO_API void pxo_constrain(float* x, size_t n, float alpha)
+{
+    for (size_t i = 0; i < n; ++i) x[i] = fminf(alpha, fmaxf(-alpha, x[i]));
+}
+
 /* ------------------------------------------------------------------ */
 /* Bias / batch-norm inference: src/CpuUtil.cpp, src/BatchNorm.cpp     */
 /* ------------------------------------------------------------------ */

@@ -44,15 +44,23 @@ def _ip(a):
     return a.ctypes.data_as(_i) if a is not None else None
 
 
+def reference_root():
+    """Root of the trieck/pixienn checkout the ref_* libraries are compiled from: $PXE_REFERENCE_ROOT, else a
+    directory ``reference`` beside this repository.  None when neither exists."""
+    cand = os.environ.get("PXE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src")) else None
+
+
 def build(ref: bool = True) -> None:
     """Compile the oracle (always) and the reference libraries (when the
     reference checkout is present and ``ref`` is true)."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    if ref and os.path.isdir(os.environ.get("PXE_REFERENCE_ROOT", "/root/reference")):
-        env = dict(os.environ)
-        root = os.environ.get("PXE_REFERENCE_ROOT", "/root/reference")
-        subprocess.run(["make", "-s", "-C", HERE, "ref_cpu", f"REF={root}"], check=True, env=env)
-        subprocess.run(["make", "-s", "-C", HERE, "ref_cuda", f"REF={root}"], check=True, env=env)
+    root = reference_root()
+    if ref and root:
+        subprocess.run(["make", "-s", "-C", HERE, "ref_cpu", f"REF={root}"], check=True)
+        subprocess.run(["make", "-s", "-C", HERE, "ref_cuda", f"REF={root}"], check=True)
+        if os.path.exists(os.path.join(os.path.dirname(HERE), "pixienn_b200", "lib", "libpxe.so")):
+            subprocess.run(["make", "-s", "-C", HERE, "ref_link", f"REF={root}"], check=True)
 
 
 _lib = None
@@ -69,6 +77,11 @@ def lib():
         L.pxo_activate_one.argtypes = [C.c_int, C.c_float]
         L.pxo_activate.argtypes = [C.c_int, _f, C.c_size_t]
         L.pxo_add_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
+        L.pxo_gradient.argtypes = [C.c_int, _f, C.c_size_t, _f]
+        L.pxo_backward_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
+        L.pxo_maxpool_backward.argtypes = [_f, _i, _f, C.c_size_t]
+        L.pxo_upsample_backward.argtypes = [_f, _f] + [C.c_int] * 5 + [C.c_float]
+        L.pxo_constrain.argtypes = [_f, C.c_size_t, C.c_float]
         L.pxo_scale_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.pxo_normalize.argtypes = [_f, _f, _f, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         L.pxo_conv_epilogue.argtypes = [_f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, C.c_float,
@@ -116,6 +129,46 @@ def _c(a, dtype=np.float32):
 def activate(kind, x):
     y = _c(x).copy()
     lib().pxo_activate(ACT[kind] if isinstance(kind, str) else int(kind), _fp(y), y.size)
+    return y
+
+
+def gradient(kind, x, delta):
+    """delta * f'(x): Activation::gradient (include/Activation.h:306-316)."""
+    d = _c(delta).copy()
+    xx = _c(x)
+    lib().pxo_gradient(ACT[kind] if isinstance(kind, str) else int(kind), _fp(xx), xx.size, _fp(d))
+    return d
+
+
+def backward_bias(bias_updates, delta):
+    """delta: [B, n, ...]; returns bias_updates + per-filter sums (src/CpuUtil.cpp:189-196)."""
+    d = _c(delta)
+    out = _c(bias_updates).copy()
+    B, n = d.shape[0], d.shape[1]
+    lib().pxo_backward_bias(_fp(out), _fp(d), B, n, d.size // (B * n))
+    return out
+
+
+def maxpool_backward(delta, indexes, grad):
+    g = _c(grad).copy()
+    d = _c(delta)
+    idx = _c(indexes, np.int32)
+    lib().pxo_maxpool_backward(_fp(d), _ip(idx), _fp(g), d.size)
+    return g
+
+
+def upsample_backward(acc, out, stride, scale=1.0):
+    """acc: [B,C,H,W] accumulated into; out: [B,C,H*stride,W*stride]."""
+    a = _c(acc).copy()
+    o = _c(out)
+    B, Cc, H, W = a.shape
+    lib().pxo_upsample_backward(_fp(a), _fp(o), B, Cc, H, W, stride, C.c_float(scale))
+    return a
+
+
+def constrain(x, alpha):
+    y = _c(x).copy()
+    lib().pxo_constrain(_fp(y), y.size, C.c_float(alpha))
     return y
 
 
@@ -348,6 +401,9 @@ class RefCpu:
         L.pxref_blas_sgemm_ptr.restype = C.c_void_p
         L.pxref_activate.argtypes = [C.c_int, _f, C.c_size_t]
         L.pxref_add_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
+        L.pxref_gradient.argtypes = [C.c_int, _f, C.c_size_t, _f]
+        L.pxref_backward_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
+        L.pxref_constrain.argtypes = [C.c_int, C.c_float, _f]
         L.pxref_scale_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.pxref_normalize.argtypes = [_f, _f, _f, C.c_int, C.c_int, C.c_int]
         L.pxref_batchnorm_inference.argtypes = [_f, _f, _f, _f, _f, C.c_int, C.c_int, C.c_int]
@@ -375,6 +431,25 @@ class RefCpu:
 
     def activate_inplace(self, kind, y):
         self.L.pxref_activate(ACT[kind], _fp(y), y.size)
+
+    def gradient(self, kind, x, delta):
+        d = _c(delta).copy()
+        xx = _c(x)
+        rc = self.L.pxref_gradient(ACT[kind] if isinstance(kind, str) else int(kind), _fp(xx), xx.size, _fp(d))
+        assert rc == 0
+        return d
+
+    def backward_bias(self, bias_updates, delta):
+        d = _c(delta)
+        out = _c(bias_updates).copy()
+        B, n = d.shape[0], d.shape[1]
+        self.L.pxref_backward_bias(_fp(out), _fp(d), B, n, d.size // (B * n))
+        return out
+
+    def constrain(self, x, alpha):
+        y = _c(x).copy()
+        self.L.pxref_constrain(y.size, C.c_float(alpha), _fp(y))
+        return y
 
     def batchnorm_inference(self, x, gamma, beta, mean, var, via_vector=False):
         y = _c(x).copy()
@@ -477,10 +552,11 @@ class RefCuda:
     Arguments are raw device pointers (``tensor.data_ptr()``); everything runs on the legacy
     default stream, as in the reference."""
 
-    def __init__(self):
-        if not os.path.exists(REF_CUDA_SO):
-            raise FileNotFoundError(REF_CUDA_SO)
-        L = C.CDLL(REF_CUDA_SO)
+    def __init__(self, path=None):
+        path = path or REF_CUDA_SO
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        L = C.CDLL(path)
         vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
         protos = {
             "pxrefcu_activate": [i, vp, sz],
@@ -498,7 +574,17 @@ class RefCuda:
             "pxrefcu_shortcut_replay": [vp, vp, vp, vp, i, i, i, i, f, f, i],
             "pxrefcu_route_replay": [i, C.POINTER(vp), _i, vp, vp, i],
             "pxrefcu_yolo_replay": [vp, vp, vp, vp, i, i, i, i],
+            "pxrefcu_gradient": [i, vp, sz, vp],
+            "pxrefcu_backward_bias": [vp, vp, i, i, i],
+            "pxrefcu_maxpool_backward": [vp, vp, vp, i],
+            "pxrefcu_upsample_backward": [i, i, i, i, i, f, vp, vp],
+            "pxrefcu_constrain": [i, f, vp],
+            "pxrefcu_mul": [i, vp, vp],
+            "pxrefcu_random": [vp, sz, f, f],
+            "pxrefcu_random_normal": [vp, sz, f, f],
         }
+        L.pxrefcu_gridsize.argtypes = [C.c_uint, C.POINTER(C.c_uint)]
+        L.pxrefcu_gridsize.restype = None
         for name, args in protos.items():
             fn = getattr(L, name)
             fn.argtypes = args
@@ -520,3 +606,16 @@ def ref_cuda():
     if _ref_cuda is None and os.path.exists(REF_CUDA_SO):
         _ref_cuda = RefCuda()
     return _ref_cuda
+
+
+REF_LINK_SO = os.path.join(HERE, "_ref", "libpxref_cuda_on_pxe.so")
+_ref_link = None
+
+
+def ref_cuda_on_pxe():
+    """The same glue (the reference's call sequences, compiled against the reference's headers) linked against
+    libpxe.so instead of the reference's .cu files: the link-compatible tier in use.  None when not built."""
+    global _ref_link
+    if _ref_link is None and os.path.exists(REF_LINK_SO):
+        _ref_link = RefCuda(REF_LINK_SO)
+    return _ref_link

@@ -40,6 +40,34 @@ API int pxref_activate(int type, float* x, std::size_t n)
 }
 
 /* addBias, src/CpuUtil.cpp:178 */
+/* Activation<U, CPU>::gradient(T* dbegin, T* dend, const T* x), include/Activation.h:306-316 */
+API int pxref_gradient(int type, const float* x, std::size_t n, float* delta)
+{
+    switch (static_cast<ActivationType>(type)) {
+    case LEAKY:    { Activation<Leaky> a;    a.gradient(delta, delta + n, x); return 0; }
+    case LINEAR:   { Activation<Linear> a;   a.gradient(delta, delta + n, x); return 0; }
+    case LOGGY:    { Activation<Loggy> a;    a.gradient(delta, delta + n, x); return 0; }
+    case LOGISTIC: { Activation<Logistic> a; a.gradient(delta, delta + n, x); return 0; }
+    case MISH:     { Activation<Mish> a;     a.gradient(delta, delta + n, x); return 0; }
+    case RELU:     { Activation<ReLU> a;     a.gradient(delta, delta + n, x); return 0; }
+    case SOFTPLUS: { Activation<Softplus> a; a.gradient(delta, delta + n, x); return 0; }
+    case SWISH:    { Activation<Swish> a;    a.gradient(delta, delta + n, x); return 0; }
+    case TANH:     { Activation<Tanh> a;     a.gradient(delta, delta + n, x); return 0; }
+    }
+    return 1;
+}
+
+/* backwardBias, src/CpuUtil.cpp:189-196; constrain, :357-362 */
+API void pxref_backward_bias(float* biasUpdates, const float* delta, int batch, int n, int size)
+{
+    backwardBias(biasUpdates, delta, batch, n, size);
+}
+
+API void pxref_constrain(int n, float alpha, float* x)
+{
+    constrain(n, alpha, x, 1);
+}
+
 API void pxref_add_bias(float* out, const float* bias, int batch, int n, int size)
 {
     addBias(out, bias, batch, n, size);

@@ -81,6 +81,52 @@ API int pxrefcu_centernet_activate(const float* in, float* out, int batch, int c
     return guarded([&] { px::centerNetActivateGpu(in, out, batch, classes, area, bias); });
 }
 
+API int pxrefcu_gradient(int type, const float* x, std::size_t n, float* delta)
+{
+    return guarded([&] { px::gradient(static_cast<ActivationType>(type), x, n, delta); });
+}
+
+API int pxrefcu_backward_bias(float* bias_updates, const float* delta, int batch, int n, int size)
+{
+    return guarded([&] { px::backwardBiasGpu(bias_updates, delta, batch, n, size); });
+}
+
+API int pxrefcu_maxpool_backward(const float* delta, const int* indexes, float* grad, int size)
+{
+    return guarded([&] { px::maxPoolBackwardGpu(delta, indexes, grad, size); });
+}
+
+API int pxrefcu_upsample_backward(int w, int h, int c, int batch, int stride, float scale, float* acc, float* out)
+{
+    return guarded([&] { px::upsampleGpu(nullptr, w, h, c, batch, stride, 0, scale, acc, out); });
+}
+
+API int pxrefcu_constrain(int n, float alpha, float* x)
+{
+    return guarded([&] { px::constrainGpu(n, alpha, x); });
+}
+
+API int pxrefcu_mul(int n, float* x, float* y)
+{
+    return guarded([&] { px::mulGpu(n, x, y); });
+}
+
+API int pxrefcu_random(float* p, std::size_t n, float a, float b)
+{
+    return guarded([&] { px::randomGpu(p, n, a, b); });
+}
+
+API int pxrefcu_random_normal(float* p, std::size_t n, float mean, float stddev)
+{
+    return guarded([&] { px::randomNormalGpu(p, n, mean, stddev); });
+}
+
+API void pxrefcu_gridsize(unsigned n, unsigned* xyz)
+{
+    const dim3 d = px::cudaGridsize(n);
+    xyz[0] = d.x; xyz[1] = d.y; xyz[2] = d.z;
+}
+
 API int pxrefcu_fill(float* p, std::size_t n, float v)
 {
     return guarded([&] { px::fillGpu(p, n, v); });

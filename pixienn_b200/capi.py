@@ -162,6 +162,14 @@ PROTOTYPES = {
     "pxe_nms_host": (_ll, [_vp, _ll, _f, _vp]),
     "pxe_nms_workspace_bytes": (_sz, [_ll]),
     "pxe_nms": (_i, [_vp, _vp, _ll, _f, _vp, _vp, _vp, _sz]),
+    "pxe_activation_gradient": (_i, [_vp, _i, _vp, _sz, _vp]),
+    "pxe_backward_bias": (_i, [_vp, _vp, _vp, _i, _i, _i]),
+    "pxe_maxpool_backward": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "pxe_upsample_backward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f]),
+    "pxe_constrain": (_i, [_vp, _vp, _sz, _f]),
+    "pxe_mul": (_i, [_vp, _vp, _vp, _sz]),
+    "pxe_random_uniform": (_i, [_vp, _vp, _sz, _f, _f]),
+    "pxe_random_normal": (_i, [_vp, _vp, _sz, _f, _f]),
 }
 
 # the planner of include/pxe_plan.h (host code)
@@ -187,6 +195,14 @@ COMPAT_SYMBOLS = [
     "_ZN2px20centerNetActivateGpuEPKfPfiiif",
     "_ZN2px7fillGpuEPfmf",
     "_ZN2px7fillGpuEPimi",
+    "_ZN2px8gradientE14ActivationTypePKfmPf",
+    "_ZN2px15backwardBiasGpuEPfPKfiii",
+    "_ZN2px18maxPoolBackwardGpuEPKfPKiPfi",
+    "_ZN2px12constrainGpuEifPf",
+    "_ZN2px12cudaGridsizeEj",
+    "_ZN2px6mulGpuEiPfS0_",
+    "_ZN2px9randomGpuEPfmff",
+    "_ZN2px15randomNormalGpuEPfmff",
 ]
 
 _lib = None

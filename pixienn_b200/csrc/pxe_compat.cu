@@ -60,8 +60,10 @@ PXE_EXPORT void maxPoolForwardGpu(const float* input, float* output, int* indexe
 PXE_EXPORT void upsampleGpu(const float* in, int w, int h, int c, int batch, int stride, int forward, float scale,
                             float* acc, float* out)
 {
-    (void)acc;
-    if (!forward) throw std::runtime_error("upsampleGpu: the backward mode is not part of the inference path");
+    if (!forward) {
+        check(pxe_upsample_backward(nullptr, acc, out, batch, c, h, w, stride, scale), "upsampleGpu");
+        return;
+    }
     check(pxe_upsample(nullptr, in, 0, out, 0, batch, c, h, w, stride, scale), "upsampleGpu");
 }
 
@@ -88,5 +90,57 @@ PXE_EXPORT void centerNetActivateGpu(const float* input, float* output, int batc
 
 PXE_EXPORT void fillGpu(float* ptr, std::size_t n, float value) { fill<float>(ptr, n, value); }
 PXE_EXPORT void fillGpu(int* ptr, std::size_t n, int value) { fill<int>(ptr, n, value); }
+
+PXE_EXPORT void gradient(ActivationType type, const float* x, std::size_t n, float* delta)
+{
+    check(pxe_activation_gradient(nullptr, (int)type, x, n, delta), "gradient");
+}
+
+PXE_EXPORT void backwardBiasGpu(float* biasUpdates, const float* delta, int batch, int n, int size)
+{
+    check(pxe_backward_bias(nullptr, biasUpdates, delta, batch, n, size), "backwardBiasGpu");
+}
+
+PXE_EXPORT void maxPoolBackwardGpu(const float* delta, const int* indexes, float* grad, int size)
+{
+    if (size < 0) throw std::runtime_error("maxPoolBackwardGpu: negative size");
+    check(pxe_maxpool_backward(nullptr, delta, indexes, grad, (std::size_t)size), "maxPoolBackwardGpu");
+}
+
+PXE_EXPORT void constrainGpu(int n, float alpha, float* x)
+{
+    if (n < 0) throw std::runtime_error("constrainGpu: negative size");
+    check(pxe_constrain(nullptr, x, (std::size_t)n, alpha), "constrainGpu");
+}
+
+PXE_EXPORT void mulGpu(int n, float* x, float* y)
+{
+    if (n < 0) throw std::runtime_error("mulGpu: negative size");
+    check(pxe_mul(nullptr, x, y, (std::size_t)n), "mulGpu");
+}
+
+PXE_EXPORT void randomGpu(float* ptr, std::size_t n, float a, float b)
+{
+    check(pxe_random_uniform(nullptr, ptr, n, a, b), "randomGpu");
+}
+
+PXE_EXPORT void randomNormalGpu(float* ptr, std::size_t n, float mean, float stddev)
+{
+    check(pxe_random_normal(nullptr, ptr, n, mean, stddev), "randomNormalGpu");
+}
+
+// Launch grid for n threads in blocks of 512: one row of blocks up to 65535, a near-square arrangement beyond
+// (src/CudaUtils.cu:28-43).  The second dimension is what keeps launches of more than 33.5 M threads legal.
+PXE_EXPORT dim3 cudaGridsize(std::uint32_t n)
+{
+    constexpr std::uint32_t kBlock = 512;
+    const std::uint32_t blocks = (n - 1) / kBlock + 1;
+    std::uint32_t x = blocks, y = 1;
+    if (x > 65535) {
+        x = (std::uint32_t)ceil(sqrt((double)blocks));
+        y = (n - 1) / (x * kBlock) + 1;
+    }
+    return dim3(x, y, 1);
+}
 
 }  // namespace px

@@ -451,6 +451,84 @@ def detect_decode(pred: torch.Tensor, side: int, num: int, classes: int, thresho
                                             buf.capacity, buf.count.data_ptr(), batch_id_offset))
 
 
+# ------------------------------------------------------------------------------ backward-side kernels
+def activation_gradient(kind, x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """delta *= f'(x) in place: px::gradient (src/Activation.cu:135-143)."""
+    _check_f32_cuda(x, "x")
+    _check_f32_cuda(delta, "delta")
+    if not (x.is_contiguous() and delta.is_contiguous()) or x.numel() != delta.numel():
+        raise ValueError("x and delta must be contiguous tensors of the same size")
+    capi.check(capi.lib().pxe_activation_gradient(_stream(), _act(kind), x.data_ptr(), x.numel(), delta.data_ptr()))
+    return delta
+
+
+def backward_bias(bias_updates: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """bias_updates[f] += sum of delta[:, f] in place: px::backwardBiasGpu (src/BiasKernels.cu:95-111)."""
+    _check_f32_cuda(delta, "delta")
+    if not delta.is_contiguous():
+        raise ValueError("delta must be contiguous")
+    B, n = delta.shape[0], delta.shape[1]
+    capi.check(capi.lib().pxe_backward_bias(_stream(), _vec(bias_updates, n, "bias_updates"), delta.data_ptr(), B, n,
+                                            delta.numel() // (B * n)))
+    return bias_updates
+
+
+def maxpool_backward(delta: torch.Tensor, indexes: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+    """grad[indexes[i]] += delta[i] in place: px::maxPoolBackwardGpu (src/MaxPoolKernels.cu:61-65)."""
+    _check_f32_cuda(delta, "delta")
+    _check_f32_cuda(grad, "grad")
+    if indexes.dtype != torch.int32 or not indexes.is_cuda or indexes.numel() != delta.numel():
+        raise ValueError("indexes must be an int32 CUDA tensor with delta's element count")
+    if not (delta.is_contiguous() and indexes.is_contiguous() and grad.is_contiguous()):
+        raise ValueError("delta, indexes and grad must be contiguous")
+    capi.check(capi.lib().pxe_maxpool_backward(_stream(), delta.data_ptr(), indexes.data_ptr(), grad.data_ptr(), delta.numel()))
+    return grad
+
+
+def upsample_backward(acc: torch.Tensor, out: torch.Tensor, stride: int, scale: float = 1.0) -> torch.Tensor:
+    """acc += scale * (sum of the stride x stride block of out above each element): px::upsampleGpu, forward == 0."""
+    _check_f32_cuda(acc, "acc")
+    _check_f32_cuda(out, "out")
+    B, Cc, H, W = acc.shape
+    if tuple(out.shape) != (B, Cc, H * stride, W * stride) or not (acc.is_contiguous() and out.is_contiguous()):
+        raise ValueError("out must be the contiguous [B, C, H*stride, W*stride] tensor for a contiguous acc [B, C, H, W]")
+    capi.check(capi.lib().pxe_upsample_backward(_stream(), acc.data_ptr(), out.data_ptr(), B, Cc, H, W, stride, scale))
+    return acc
+
+
+def constrain(x: torch.Tensor, alpha: float) -> torch.Tensor:
+    """x = clamp(x, -alpha, alpha) in place: px::constrainGpu (src/CudaUtils.cu:131-138)."""
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    capi.check(capi.lib().pxe_constrain(_stream(), x.data_ptr(), x.numel(), alpha))
+    return x
+
+
+def mul(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """y = x * y in place: px::mulGpu (src/CudaUtils.cu:140-146)."""
+    _check_f32_cuda(x, "x")
+    _check_f32_cuda(y, "y")
+    if not (x.is_contiguous() and y.is_contiguous()) or x.numel() != y.numel():
+        raise ValueError("x and y must be contiguous tensors of the same size")
+    capi.check(capi.lib().pxe_mul(_stream(), x.data_ptr(), y.data_ptr(), x.numel()))
+    return y
+
+
+def random_uniform(out: torch.Tensor, a: float = 0.0, b: float = 1.0) -> torch.Tensor:
+    """px::randomGpu (src/CudaUtils.cu:77-86)."""
+    _check_f32_cuda(out, "out")
+    capi.check(capi.lib().pxe_random_uniform(_stream(), out.data_ptr(), out.numel(), a, b))
+    return out
+
+
+def random_normal(out: torch.Tensor, mean: float = 0.0, stddev: float = 1.0) -> torch.Tensor:
+    """px::randomNormalGpu (src/CudaUtils.cu:110-120)."""
+    _check_f32_cuda(out, "out")
+    capi.check(capi.lib().pxe_random_normal(_stream(), out.data_ptr(), out.numel(), mean, stddev))
+    return out
+
+
 # ------------------------------------------------------------------------------ channels-last tier
 def _nhwc(t: Optional[torch.Tensor], name: str):
     """(pointer, pixel stride) of a logical [B,C,H,W] tensor stored channels-last: a dense channels-last tensor

@@ -27,13 +27,30 @@ def test_cpp_client_links_and_runs(tmp_path):
     capi.lib()                                            # the library exists (raises with build instructions otherwise)
     libdir = os.path.dirname(capi.LIB_PATH)
     exe = tmp_path / "link_client"
-    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-I", INC, os.path.join(SRC, "link_client.cpp"),
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")   # dim3 (px::cudaGridsize)
+    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-I", INC, "-I", cuda_inc, os.path.join(SRC, "link_client.cpp"),
                         "-L", libdir, "-lpxe", f"-Wl,-rpath,{libdir}", "-o", str(exe)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
     assert "steps=4 fused_pool=1 fused_shortcut=1 raw_heads=1" in run.stdout
     assert "nms kept=2" in run.stdout and "px:: symbols resolved" in run.stdout
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="g++ not found")
+def test_shim_fragments_compile_inside_stand_in_layers(tmp_path):
+    """include/shim/*.inl are the replacement bodies for the reference's CUDA forward / addDetects members.  They are
+    compiled here inside member functions of stand-in classes that carry the reference's member names, with the
+    entry points recorded instead of launched; the program then checks which pointers and strides the plan made the
+    conv fragment put into pxe_epilogue_desc for a folded shortcut and two concat slots."""
+    capi.lib()
+    libdir = os.path.dirname(capi.LIB_PATH)
+    exe = tmp_path / "shim_standin"
+    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-I", INC, os.path.join(SRC, "shim_standin.cpp"),
+                        "-L", libdir, "-lpxe", f"-Wl,-rpath,{libdir}", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.startswith("ok: epilogues=2 concats=0"), (run.stdout, run.stderr)
 
 
 @pytest.mark.gpu

@@ -1,6 +1,11 @@
 """Three-way agreement on the GPU: new kernels vs the reference's own CUDA kernels (its src/*.cu
 compiled unchanged for sm_100a into oracle/_ref/libpxref_cuda.so) vs the CPU oracle.
-Skipped where that library was not built (it needs a checkout of the reference at build time)."""
+Skipped where that library was not built (it needs a checkout of the reference at build time).
+
+Every test also runs a second time with the same glue -- the reference's call sequences, compiled against the
+reference's own headers -- linked against libpxe.so INSTEAD of the reference's .cu files
+(oracle/_ref/libpxref_cuda_on_pxe.so, linked with -z defs): the link-compatible tier carrying the reference's
+calls.  In that run "theirs" is this library reached through the px:: signatures."""
 import numpy as np
 import pytest
 import torch
@@ -11,11 +16,12 @@ from test_gpu_epilogue import bn, close, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def refcu(oracle):
-    r = oracle.ref_cuda()
+@pytest.fixture(scope="module", params=["reference-kernels", "glue-linked-against-libpxe"])
+def refcu(oracle, request):
+    r = oracle.ref_cuda() if request.param == "reference-kernels" else oracle.ref_cuda_on_pxe()
     if r is None:
-        pytest.skip("oracle/_ref/libpxref_cuda.so not built")
+        pytest.skip("oracle/_ref/libpxref_cuda*.so not built")
+    r.kind = request.param
     return r
 
 
@@ -136,3 +142,113 @@ def test_centernet_topk_indices_bit_exact_vs_reference_cuda_scores(cuda, oracle,
     for b in range(B):
         assert np.array_equal(got[b]["source"], ref[b]["source"])
         assert np.array_equal(got[b]["prob"], ref[b]["prob"])
+
+
+# ------------------------------------------------------------------ the backward-side functions
+@pytest.mark.parametrize("act", ["leaky", "linear", "loggy", "logistic", "mish", "relu", "softplus", "swish", "tanh"])
+def test_activation_gradient_three_way(cuda, oracle, refcu, act):
+    x = np.concatenate([synth.normal(92, "gx", 100003, 0, 6), np.linspace(-25, 25, 20001, dtype=np.float32)])
+    delta = synth.normal(92, "gd", len(x), 0, 2)
+    mine = ops.activation_gradient(act, dev(x, cuda), dev(delta, cuda))
+    theirs = dev(delta, cuda)
+    refcu.call("gradient", oracle.ACT[act], dev(x, cuda).data_ptr(), len(x), theirs.data_ptr())
+    torch.cuda.synchronize()
+    m, t = mine.cpu().numpy(), theirs.cpu().numpy()
+    close(m, t, atol=2e-6)
+    if act in ("leaky", "linear", "relu", "loggy"):      # no transcendental: bit-identical
+        assert np.array_equal(m, t)
+    close(t, oracle.gradient(act, x, delta), atol=4e-6)
+    # odd sizes and unaligned starts take the scalar path
+    xs, ds = dev(x, cuda)[1:1001], dev(delta, cuda)[1:1001].clone()
+    close(ops.activation_gradient(act, xs.contiguous(), ds).cpu().numpy(), oracle.gradient(act, x[1:1001], delta[1:1001]), atol=4e-6)
+
+
+@pytest.mark.parametrize("shape", [(4, 16, 26, 26), (2, 255, 19, 19), (3, 7, 1, 1), (5, 300, 1, 1), (2, 3, 50, 70)])
+def test_backward_bias_three_way(cuda, oracle, refcu, shape):
+    """Sums of up to tens of thousands of terms: the reference's kernel, this library's and the CPU loop add in
+    different orders; they agree to the rounding of such a sum."""
+    delta = synth.normal(93, f"bb{shape}", shape, 0, 1)
+    start = synth.normal(93, f"bs{shape}", shape[1])
+    mine = ops.backward_bias(dev(start, cuda), dev(delta, cuda))
+    again = ops.backward_bias(dev(start, cuda), dev(delta, cuda))
+    theirs = dev(start, cuda)
+    refcu.call("backward_bias", theirs.data_ptr(), dev(delta, cuda).data_ptr(), shape[0], shape[1], shape[2] * shape[3])
+    torch.cuda.synchronize()
+    assert torch.equal(mine, again)                        # fixed summation order: the same bits every time
+    terms = shape[0] * shape[2] * shape[3]
+    tol = 1e-6 * np.sqrt(terms) * 4 + 1e-6
+    want = oracle.backward_bias(start, delta)
+    assert np.abs(mine.cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+    assert np.abs(theirs.cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("k,stride", [(2, 2), (2, 1), (5, 1), (3, 2)])
+def test_maxpool_backward_three_way(cuda, oracle, refcu, k, stride):
+    B, C, H, W = 2, 5, 13, 17
+    x = synth.normal(94, "mpx", (B, C, H, W))
+    out, idx = ops.maxpool(dev(x, cuda), k, stride, with_indexes=True)
+    delta = synth.normal(94, "mpd", tuple(out.shape))
+    grad0 = synth.normal(94, "mpg", (B, C, H, W))
+    mine = ops.maxpool_backward(dev(delta, cuda), idx, dev(grad0, cuda))
+    theirs = dev(grad0, cuda)
+    refcu.call("maxpool_backward", dev(delta, cuda).data_ptr(), idx.data_ptr(), theirs.data_ptr(), delta.size)
+    torch.cuda.synchronize()
+    want = oracle.maxpool_backward(delta, idx.cpu().numpy(), grad0)
+    if stride >= k:                                        # no input is named twice: exact
+        assert np.array_equal(mine.cpu().numpy(), want) and np.array_equal(theirs.cpu().numpy(), want)
+    else:                                                  # several adds per input, in any order
+        close(mine.cpu().numpy(), want, atol=2e-6)
+        close(theirs.cpu().numpy(), want, atol=2e-6)
+
+
+@pytest.mark.parametrize("stride,scale", [(2, 1.0), (3, 0.5), (1, 2.0)])
+def test_upsample_backward_three_way(cuda, oracle, refcu, stride, scale):
+    B, C, H, W = 2, 3, 7, 9
+    out = synth.normal(95, "ubo", (B, C, H * stride, W * stride))
+    acc0 = synth.normal(95, "uba", (B, C, H, W))
+    mine = ops.upsample_backward(dev(acc0, cuda), dev(out, cuda), stride, scale)
+    theirs = dev(acc0, cuda)
+    refcu.call("upsample_backward", W, H, C, B, stride, scale, theirs.data_ptr(), dev(out, cuda).data_ptr())
+    torch.cuda.synchronize()
+    want = oracle.upsample_backward(acc0, out, stride, scale)
+    close(mine.cpu().numpy(), want, atol=2e-6)
+    close(theirs.cpu().numpy(), want, atol=2e-6)
+
+
+def test_constrain_mul_three_way(cuda, oracle, refcu):
+    x = synth.normal(96, "cx", 100001, 0, 4)
+    y = synth.normal(96, "cy", 100001, 0, 4)
+    mine = ops.constrain(dev(x, cuda), 1.5)
+    theirs = dev(x, cuda)
+    refcu.call("constrain", len(x), 1.5, theirs.data_ptr())
+    torch.cuda.synchronize()
+    assert np.array_equal(mine.cpu().numpy(), theirs.cpu().numpy())
+    assert np.array_equal(mine.cpu().numpy(), oracle.constrain(x, 1.5))
+    my = ops.mul(dev(x, cuda), dev(y, cuda))
+    ty = dev(y, cuda)
+    refcu.call("mul", len(x), dev(x, cuda).data_ptr(), ty.data_ptr())
+    torch.cuda.synchronize()
+    assert np.array_equal(my.cpu().numpy(), ty.cpu().numpy()) and np.array_equal(my.cpu().numpy(), x * y)
+
+
+def test_random_fills_follow_the_reference_engine(cuda, refcu):
+    """Element i comes from the minimal-standard generator advanced i steps: uniform values equal the reference's
+    (thrust) to the last bit or the one before; normal values have the requested moments and, value by value, sit
+    where the reference's inversion of the same engine position puts them, to the accuracy of the two erf^-1."""
+    n = 200000
+    mine = ops.random_uniform(torch.empty(n, device=cuda), -0.25, 0.75).cpu().numpy()
+    theirs = torch.empty(n, device=cuda)
+    refcu.call("random", theirs.data_ptr(), n, -0.25, 0.75)
+    torch.cuda.synchronize()
+    t = theirs.cpu().numpy()
+    assert mine.min() >= -0.25 and mine.max() < 0.75
+    assert np.abs(mine - t).max() <= 1.2e-7
+    print(f"\nuniform fill: {np.mean(mine == t) * 100:.2f} % of {n} values bit-identical to the reference ({refcu.kind})")
+    mn = ops.random_normal(torch.empty(n, device=cuda), 1.0, 2.0).cpu().numpy()
+    tn = torch.empty(n, device=cuda)
+    refcu.call("random_normal", tn.data_ptr(), n, 1.0, 2.0)
+    torch.cuda.synchronize()
+    tn = tn.cpu().numpy()
+    assert abs(mn.mean() - 1.0) < 0.02 and abs(mn.std() - 2.0) < 0.02
+    assert abs(tn.mean() - 1.0) < 0.02 and abs(tn.std() - 2.0) < 0.02
+    print(f"normal fill: max |mine - reference| = {np.abs(mn - tn).max():.3e}, correlation {np.corrcoef(mn, tn)[0, 1]:.6f}")

@@ -58,3 +58,37 @@ def test_conv_forward_im2col_matches(oracle, ref):
         import torch
         want = torch.nn.functional.conv2d(torch.from_numpy(x), torch.from_numpy(w), stride=s, padding=pad).numpy()
         np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["leaky", "linear", "loggy", "logistic", "mish", "relu", "softplus", "swish", "tanh"])
+def test_activation_gradients_bit_identical(oracle, ref, kind):
+    """Activation<U, CPU>::gradient of the reference's own header against the restatement."""
+    x = np.concatenate([synth.normal(73, "gx", 20000, 0, 8), np.linspace(-25, 25, 5001, dtype=np.float32),
+                        np.array([0, -0.0, 20, -20, 1e-40, 90, -90], np.float32)])
+    delta = synth.normal(73, "gd", len(x), 0, 3)
+    assert np.array_equal(ref.gradient(kind, x, delta), oracle.gradient(kind, x, delta))
+
+
+def test_backward_bias_and_constrain_bit_identical(oracle, ref):
+    delta = synth.normal(74, "bd", (3, 5, 7, 9), 0, 2)
+    start = synth.normal(74, "bs", 5)
+    assert np.array_equal(ref.backward_bias(start, delta), oracle.backward_bias(start, delta))
+    conn = synth.normal(74, "bc", (4, 11))
+    assert np.array_equal(ref.backward_bias(np.zeros(11, np.float32), conn), oracle.backward_bias(np.zeros(11, np.float32), conn))
+    x = synth.normal(75, "cx", 1000, 0, 5)
+    assert np.array_equal(ref.constrain(x, 2.5), oracle.constrain(x, 2.5))
+
+
+def test_launch_grid_of_the_compat_tier_equals_the_reference(oracle):
+    """px::cudaGridsize of libpxe.so against the reference's (src/CudaUtils.cu:28-43), through the same glue built
+    twice: over the reference's own sources and over libpxe.so.  Host code: no GPU is touched."""
+    import ctypes as C
+    theirs, ours = oracle.ref_cuda(), oracle.ref_cuda_on_pxe()
+    if theirs is None or ours is None:
+        pytest.skip("oracle/_ref/libpxref_cuda*.so not built")
+    a, b = (C.c_uint * 3)(), (C.c_uint * 3)()
+    for n in [1, 2, 511, 512, 513, 65535 * 512, 65535 * 512 + 1, 10 ** 8, 757 * 10 ** 6, 2 ** 31, 2 ** 32 - 1]:
+        theirs.L.pxrefcu_gridsize(n, a)
+        ours.L.pxrefcu_gridsize(n, b)
+        assert list(a) == list(b), n
+        assert a[0] * a[1] * 512 >= n
