@@ -134,7 +134,13 @@ typedef struct pxe_epilogue_desc {
     int pool_padding;           /* 0 or 1 (the MaxPoolLayer default is kernel-1 = 1) */
     float* y_pool;              /* [batch, channels, OH, OW], OH = (height + pad - 2)/2 + 1 */
     long long y_pool_batch_stride;
+    int pool_variant;           /* 0: the library picks the pooled kernel for the shape (what callers want);
+                                   PXE_POOL_GENERAL: always the general pooled kernel -- the specialised forms
+                                   (even heights, small odd planes) must equal it bit for bit, which is how
+                                   the tests hold them to it */
 } pxe_epilogue_desc;
+
+enum pxe_pool_variant { PXE_POOL_AUTO = 0, PXE_POOL_GENERAL = 1 };
 
 PXE_API int pxe_conv_epilogue(pxe_stream_t stream, const pxe_epilogue_desc* desc);
 

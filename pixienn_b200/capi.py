@@ -44,7 +44,7 @@ class EpilogueDesc(C.Structure):
         ("residual", C.c_void_p), ("residual_batch_stride", C.c_longlong),
         ("res_alpha", C.c_float), ("res_beta", C.c_float), ("res_act", C.c_int),
         ("pool_kernel", C.c_int), ("pool_stride", C.c_int), ("pool_padding", C.c_int),
-        ("y_pool", C.c_void_p), ("y_pool_batch_stride", C.c_longlong),
+        ("y_pool", C.c_void_p), ("y_pool_batch_stride", C.c_longlong), ("pool_variant", C.c_int),
     ]
 
 
@@ -93,6 +93,7 @@ class CenterNetDecodeDesc(C.Structure):
     ]
 
 
+POOL_AUTO, POOL_GENERAL = 0, 1            # enum pxe_pool_variant
 PLAN_MAX_SOURCES, PLAN_MAX_DESTS, PLAN_MAX_SPP = 16, 8, 4
 
 

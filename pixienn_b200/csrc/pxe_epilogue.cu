@@ -50,6 +50,7 @@ struct EpiParams {
     FastDiv div_oh;
     uint32_t units_per_image;
     int y_dense, pool_dense;
+    int pool_general;          // host side only: skip the specialised pooled kernels
 };
 
 // Folded coefficients and image / channel numbers of plane `pl` (= image*C + channel).
@@ -610,14 +611,7 @@ epilogue_pool_smallplane_kernel(const EpiParams p, uint32_t planes, uint32_t pla
 // ------------------------------------------------------------------------------- launch helpers
 // Rounds of the per-thread loop one block runs (a round = one batch of loads per thread).  Measured
 // on B200: short blocks (2 rounds, 32 KB of input each for the streaming kernel) in many waves give
-// the best HBM throughput at every tensor size; the environment variables exist for experiments.
-int rounds_setting(const char* name, int fallback)
-{
-    const char* s = getenv(name);
-    int r = s ? atoi(s) : fallback;
-    return r < 1 ? 1 : r;
-}
-
+// the best HBM throughput at every tensor size.
 // Splits `units` into per-block chunks of `rounds` granules, at most `max_chunk`.
 void plan_chunks(uint32_t units, uint32_t granule, uint32_t max_chunk, int rounds, uint32_t* chunk, unsigned* grid)
 {
@@ -639,7 +633,7 @@ int launch_stream_kernel(cudaStream_t s, EpiParams& p, const DeviceInfo& di)
     if (max_chunk < granule) { granule = kThreads; }
     if (max_chunk < granule) { max_chunk = granule; }   // tiny HW: checked below
     unsigned grid;
-    static const int rounds = rounds_setting("PXE_CHUNK_ROUNDS", 2);
+    constexpr int rounds = 2;
     plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk * vw / p.HW + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
@@ -695,6 +689,7 @@ int dispatch_flags(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int mode,
 template <int ACT, bool AFFINE>
 int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
 {
+    const bool general_only = p.pool_general != 0;       // the caller asked for the general kernel (pxe_epilogue_desc.pool_variant)
     const int nv = vo == 0 ? 1 : vo;
     p.OWV = p.OW / nv;
     p.div_owv = FastDiv((uint32_t)p.OWV);
@@ -706,17 +701,16 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
     if (max_chunk < granule) granule = kThreads;
     if (max_chunk < granule) max_chunk = granule;
     unsigned grid;
-    static const int rounds = rounds_setting("PXE_POOL_CHUNK_ROUNDS", 2);
+    constexpr int rounds = 2;
     plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk / per_plane + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
     // odd widths, small planes: a warp per plane with per-thread window geometry hoisted out of the loop
-    const char* small_env = getenv("PXE_POOL_SMALLPLANE");     // "0" forces the general kernel (tests, experiments)
     const uint32_t ohow = (uint32_t)(p.OH * p.OW);
     const int slots = ohow <= 64 ? 2 : 4;
     // measured on B200: ahead of the general form with two or four output slots per lane and at least 70 % of the
     // lane slots in use (13x13 -> 7x7, 19x19 -> 10x10); behind it with one slot (tiny planes) or eight (27x27, 31x31)
-    if (vo == 0 && ohow > 32 && ohow <= 128 && 10 * ohow >= 7 * 32 * (uint32_t)slots && (!small_env || atoi(small_env) != 0)) {
+    if (vo == 0 && ohow > 32 && ohow <= 128 && 10 * ohow >= 7 * 32 * (uint32_t)slots && !general_only) {
         const uint32_t n_planes = p.units / per_plane;
         const uint32_t pu = 8 / slots;
         const uint32_t planes_per_block = (kThreads / 32) * pu * 2;          // two rounds per warp: short blocks
@@ -730,9 +724,7 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
         return PXE_OK;
     }
     // stripped index arithmetic when row pairs tile the tensor: even H, dense x (W already is a multiple of the patch)
-    const char* even_env = getenv("PXE_POOL_EVEN");            // "0" forces the general kernel (tests, experiments)
-    const bool allow_even = !even_env || atoi(even_env) != 0;
-    const bool even = allow_even && vo != 0 && p.H % 2 == 0 && p.xbs == (long long)p.C * p.HW;
+    const bool even = !general_only && vo != 0 && p.H % 2 == 0 && p.xbs == (long long)p.C * p.HW;
     void (*kern)(const EpiParams) = nullptr;
     if (even) {
         p.div_oh = FastDiv((uint32_t)p.OH);
@@ -814,6 +806,8 @@ int run_slice(cudaStream_t s, const pxe_epilogue_desc& d, int b0, int nb, const 
     const bool affine = d.gamma != nullptr || d.bias != nullptr;
 
     if (d.pool_kernel) {
+        PXE_REQUIRE(d.pool_variant == PXE_POOL_AUTO || d.pool_variant == PXE_POOL_GENERAL, "conv_epilogue: unknown pool_variant %d", d.pool_variant);
+        p.pool_general = d.pool_variant == PXE_POOL_GENERAL;
         p.OH = pxe_maxpool_out_dim(d.height, 2, 2, d.pool_padding);
         p.OW = pxe_maxpool_out_dim(d.width, 2, 2, d.pool_padding);
         p.pbs = dense_or(d.y_pool_batch_stride, (long long)d.channels * p.OH * p.OW);

@@ -80,7 +80,7 @@ def conv_epilogue(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Opti
                   eps_mode: int = capi.EPS_CUDNN, yolo_classes: int = 0,
                   residual: Optional[torch.Tensor] = None, res_alpha: float = 1.0, res_beta: float = 1.0,
                   res_act="linear", pool: Optional[Sequence[int]] = None,
-                  y_pool: Optional[torch.Tensor] = None, in_place: bool = True):
+                  y_pool: Optional[torch.Tensor] = None, in_place: bool = True, pool_variant: int = 0):
     """Fused BN / bias / activation (+ residual, + 2x2 pool, + concat-slot stores).
 
     Returns ``y`` (or ``(y, y_pool)`` when pooling).  With ``y=None`` the result overwrites ``x``
@@ -126,6 +126,7 @@ def conv_epilogue(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Opti
         if tuple(y_pool.shape) != (B, Cc, oh, ow):
             raise ValueError(f"y_pool must be {(B, Cc, oh, ow)}, got {tuple(y_pool.shape)}")
         d.y_pool, d.y_pool_batch_stride = _slot(y_pool, "y_pool")
+        d.pool_variant = pool_variant        # capi.POOL_GENERAL: the general pooled kernel whatever the shape (tests)
     capi.check(capi.lib().pxe_conv_epilogue(_stream(), C.byref(d)))
     return (y, y_pool) if pool is not None else y
 

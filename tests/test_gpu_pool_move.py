@@ -66,13 +66,11 @@ def test_maxpool_ties_nan_and_signed_zero(cuda, oracle):
                                    (1, 2, 7, 12), (2, 37, 13, 13), (1, 10, 26, 26), (1, 2, 104, 104)])
 @pytest.mark.parametrize("act", ["leaky", "mish", "swish", "logistic"])
 @pytest.mark.parametrize("keep_full", [False, True])
-@pytest.mark.parametrize("even_kernel", [None, "0"])
-def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, even_kernel, monkeypatch):
+@pytest.mark.parametrize("variant", [capi.POOL_AUTO, capi.POOL_GENERAL])
+def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, variant):
     """BN + bias + activation + 2x2/2 maxpool in one pass == the oracle's separate layers.
     Pooling picks among the SAME activated values, so pooled == maxpool(full) exactly.
-    PXE_POOL_EVEN=0 forces the general pooled kernel where the even-height fast form would run."""
-    if even_kernel is not None:
-        monkeypatch.setenv("PXE_POOL_EVEN", even_kernel)
+    pool_variant = PXE_POOL_GENERAL runs the general pooled kernel where the even-height fast form would run."""
     B, C, H, W = shape
     x = synth.normal(31, f"x{shape}", shape)
     (g, b, m, v), dp = bn(32, f"bn{shape}", C, cuda)
@@ -80,7 +78,7 @@ def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, even_ker
     ref_full = oracle.conv_epilogue(x, g, b, m, v, bias, act)
     xd = dev(x, cuda)
     y, yp = ops.conv_epilogue(xd, y=None if keep_full else False, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3],
-                              bias=dev(bias, cuda), act=act, pool=(2, 2, 1))
+                              bias=dev(bias, cuda), act=act, pool=(2, 2, 1), pool_variant=variant)
     if keep_full:
         close(y.cpu().numpy(), ref_full)
         full = y.cpu().numpy()
@@ -97,10 +95,10 @@ def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, even_ker
                                    (1, 70, 5, 9), (2, 130, 13, 13), (1, 4, 3, 31)])
 @pytest.mark.parametrize("act", ["leaky", "mish"])
 @pytest.mark.parametrize("padding", [0, 1])
-def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding, monkeypatch):
+def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding):
     """Odd widths with 33 to 128 pooled outputs per plane (13x13, 19x19 here) run the warp-per-plane form (two or
     four output slots per lane), the other shapes the general one; the former must equal the general scalar
-    form bit for bit (PXE_POOL_SMALLPLANE=0 forces that one) and the oracle's separate layers, pooled-only and with the full-resolution output, dense and into channel
+    form bit for bit (pool_variant = PXE_POOL_GENERAL runs that one) and the oracle's separate layers, pooled-only and with the full-resolution output, dense and into channel
     slots of wider buffers, NaNs included."""
     B, C, H, W = shape
     x = synth.normal(36, f"sp{shape}", shape)
@@ -110,15 +108,14 @@ def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding, monkeyp
     oh, ow = (H + padding - 2) // 2 + 1, (W + padding - 2) // 2 + 1
     covered = 2 * oh >= H and 2 * ow >= W
     got = {}
-    for env in ("1", "0"):
-        monkeypatch.setenv("PXE_POOL_SMALLPLANE", env)
+    for env, variant in (("1", capi.POOL_AUTO), ("0", capi.POOL_GENERAL)):
         wide = torch.full((B, C + 3, oh, ow), 9.0, device=cuda)
         wide_full = torch.full((B, C + 2, H, W), 7.0, device=cuda)
         _, yp = ops.conv_epilogue(dev(x, cuda), y=False, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], act=act,
-                                  pool=(2, 2, padding))
+                                  pool=(2, 2, padding), pool_variant=variant)
         # the full-resolution output is offered only where the windows cover every input element
         ops.conv_epilogue(dev(x, cuda), y=wide_full[:, 2:] if covered else False, gamma=dp[0], beta=dp[1], mean=dp[2],
-                          var=dp[3], act=act, pool=(2, 2, padding), y_pool=wide[:, 3:])
+                          var=dp[3], act=act, pool=(2, 2, padding), y_pool=wide[:, 3:], pool_variant=variant)
         assert bool((wide[:, :3] == 9.0).all()) and bool((wide_full[:, :2] == 7.0).all())
         got[env] = (yp.cpu().numpy(), wide[:, 3:].cpu().numpy(), wide_full[:, 2:].cpu().numpy())
     for a, c in zip(got["1"], got["0"]):

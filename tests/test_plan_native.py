@@ -7,10 +7,11 @@ import os
 
 import pytest
 
+from oracle.pxoracle import reference_root
 from pixienn_b200 import capi, graph, presets
 
 PRESETS = [("yolov3_tiny", 416), ("yolov3", 608), ("yolov7", 640), ("centernet_tiny", 320)]
-REFERENCE_MODELS = sorted(glob.glob("/root/reference/resources/models/*.yml"))
+REFERENCE_MODELS = sorted(glob.glob(os.path.join(reference_root() or "", "resources", "models", "*.yml")))
 
 
 def same_plan(a: graph.Plan, b: graph.Plan):

@@ -4,9 +4,11 @@ import os
 import pytest
 import yaml
 
+from oracle.pxoracle import reference_root
 from pixienn_b200 import graph, presets
 
-REF_MODELS = "/root/reference/resources/models"
+# the reference's model files, where its tree is present ($PXE_REFERENCE_ROOT, or a checkout beside this repository)
+REF_MODELS = os.path.join(reference_root() or "", "resources", "models")
 KEYS = ["type", "activation", "batch_normalize", "filters", "kernel", "pad", "stride", "layers", "from", "mask",
         "anchors", "num", "padding", "dilation", "groups", "heatmap_bias", "max_detections"]
 
