@@ -316,7 +316,16 @@ def run_model(args):
         hw = synth_weights(model, SEED, **HEAD_VARIANT[args.workload])
         r2 = Runner(model, hw, B, dev, det_capacity=args.det_capacity, threshold=CONF, batch_id_offset=rank * B)
         ms2, wall2, kept, total = time_runner(r2, x, xh, nms_threshold=NMS)
-        return {"value": round(B * world * args.steps / (wall2 / 1e3), 2), "unit": "images/s",
+        # the decode's own time on this head: eager passes with events around every launch
+        r2.timer.enabled = True
+        r2.timer.clear()
+        for _ in range(3):
+            r2.forward(x)
+        torch.cuda.synchronize()
+        dec = r2.timer.summary().get("yolo_decode", {"ms": 0.0, "bytes": 0})
+        r2.timer.enabled = False
+        return {"decode_ms": round(dec["ms"] / 3, 4), "decode_head_bytes": int(dec["bytes"] / 3),
+                "value": round(B * world * args.steps / (wall2 / 1e3), 2), "unit": "images/s",
                 "resident_value": round(B * world * args.steps / (ms2 / 1e3), 2),
                 "candidates_per_step_per_gpu": total, "survivors_per_step_per_gpu": kept,
                 "d2h_bytes_per_step": kept * 32 + 16,
@@ -450,7 +459,7 @@ def run_model(args):
                            post_nms_d2h_bytes_per_step=post_nms["d2h_bytes_per_step"],
                            post_nms_candidates_per_step_per_gpu=post_nms["candidates_per_step_per_gpu"],
                            post_nms_survivors_per_step_per_gpu=post_nms["survivors_per_step_per_gpu"],
-                           post_nms_head=post_nms["head"],
+                           post_nms_head=post_nms["head"], post_nms_decode_ms=post_nms["decode_ms"],
                            post_nms_api="PipelinedPredictor(nms_threshold=0.4): decode, px::nms on the device, survivors -> pinned host")
         line["config"].update(
             strong_value=strong["value"] if strong else line["value"],
@@ -461,6 +470,17 @@ def run_model(args):
                         "64 / 32 / 16 / 8 images per GPU)",
             c3_value=c3["value"], c3_e2e=c3["e2e"], c3_per_gpu_batch=16, c3_global_batch=c3["global_batch"],
             c3_ms_per_step=c3["ms_per_step"], c3_note="YOLOv7 640x640, 16 images per GPU, same measurement")
+    if post_nms is not None and "yolo_decode" in ops_summary:
+        rd = ops_summary["yolo_decode"]
+        line["roofline"].update(
+            yolo_decode_ms=round(rd["ms"] / args.steps, 4),
+            yolo_decode_frac=round(rd["bytes"] / (rd["ms"] / 1e3) / 1e9 / peak, 4),
+            yolo_decode_trained_like_ms=post_nms["decode_ms"],
+            yolo_decode_trained_like_frac=round(post_nms["decode_head_bytes"] / (post_nms["decode_ms"] / 1e3) / 1e9 / peak, 4)
+            if post_nms["decode_ms"] > 0 else None,
+            yolo_decode_note="three heads of one step; frac = 4 bytes per head element / time / peak.  Random-init heads emit "
+                             "228 k records per image (466 MB written per step); the trained-like head (e2e.post_nms_head) "
+                             "about a thousand")
     if world == 1 and not args.no_extras and args.workload == "yolov3-608":
         # the path's other stated targets, measured after every timed region above, on this GPU
         del runner

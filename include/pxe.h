@@ -232,8 +232,12 @@ typedef struct pxe_yolo_decode_desc {
     int batch_id_offset;        /* added to batch_id (batch-sharded multi-GPU runs) */
 } pxe_yolo_decode_desc;
 
-/* Bytes of device workspace pxe_yolo_decode needs for this head. */
+/* Bytes of device workspace pxe_yolo_decode needs for this head (12 bytes per 32 cells per image). */
 PXE_API size_t pxe_yolo_decode_workspace_bytes(int batch, int height, int width);
+/* With this many bytes (about 2 KB per 32 cells per image more) the decode's first pass leaves, per box slot and
+ * class chunk, a mask of the classes that reached the threshold, and the second pass evaluates only those: one
+ * logistic per emitted value, and no second read of the head where nothing is emitted.  Same records either way. */
+PXE_API size_t pxe_yolo_decode_fast_workspace_bytes(int batch, int height, int width);
 
 /*
  * YoloLayer<CUDA>::addDetects (include/cuda/YoloLayer.h:168-188 -> include/YoloLayer.h:659-698):
@@ -503,6 +507,45 @@ PXE_API int pxe_mul(pxe_stream_t stream, const float* x, float* y, size_t n);
  * library's own inversion, so they agree with the reference in distribution, not digit for digit. */
 PXE_API int pxe_random_uniform(pxe_stream_t stream, float* out, size_t n, float a, float b);
 PXE_API int pxe_random_normal(pxe_stream_t stream, float* out, size_t n, float mean, float stddev);
+
+/* ------------------------------------------------------------------------------------------
+ * Loss kernels of the detector heads.
+ * ------------------------------------------------------------------------------------------ */
+/* px::yoloLossGpu (include/YoloKernels.cuh:10-19, src/YoloKernels.cu:73-252) as one launch.  All pointers are
+ * device memory.  `output` is the activated head [batch, mask_count*(5+classes), height, width]; `delta` has the
+ * same shape and is updated in place (entries the loss does not decide keep their value, as in the reference,
+ * which clears delta before the call); truths: [batch, max_truth, 5] = x, y, w, h, class; assigned_*: one entry
+ * per box slot (image, mask slot, cell), assigned_classes < 0 where no truth is assigned; masks: anchor index
+ * of every mask slot; anchors: [2 * anchors] floats.  stats (PXE_YOLO_STATS_SIZE floats) and cost (1 float) are
+ * added to, not cleared. */
+#define PXE_YOLO_STATS_SIZE 12
+typedef struct pxe_yolo_loss_desc {
+    const float* output;
+    float* delta;
+    const float* truths;
+    const int* truth_counts;
+    int max_truth;
+    const int* assigned_classes;
+    const int* assigned_anchors;
+    const float* assigned_boxes;
+    const int* masks;
+    const float* anchors;
+    float* stats;
+    float* cost;
+    int batch, mask_count, classes, width, height;
+    int network_width, network_height;
+    float ignore_threshold, truth_threshold, coord_scale, object_scale, no_object_scale, class_scale;
+} pxe_yolo_loss_desc;
+
+PXE_API int pxe_yolo_loss(pxe_stream_t stream, const pxe_yolo_loss_desc* desc);
+
+/* px::centerNetLossGpu (include/CenterNetKernels.cuh:8-13, src/CenterNetKernels.cu:20-139): focal loss on the
+ * heat map (costs[0]), L1 loss on size (costs[1]) and offset (costs[2]) at the cells target_mask marks; delta
+ * [batch, classes+4, area] receives normalizer * the negative gradients.  costs is added to, not cleared. */
+PXE_API int pxe_centernet_loss(pxe_stream_t stream, const float* output, float* delta, const float* target_heatmap,
+                               const float* target_size, const float* target_offset, const float* target_mask,
+                               float* costs, int batch, int classes, int area, float normalizer, float focal_alpha,
+                               float focal_beta, float size_weight);
 
 #ifdef __cplusplus
 }

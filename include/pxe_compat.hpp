@@ -2,13 +2,10 @@
  * pxe_compat.hpp -- link-compatible tier.
  *
  * The free functions of the reference's src/Activation.cu, BiasKernels.cu, MaxPoolKernels.cu,
- * UpsampleKernels.cu, ShortcutKernel.cu and CudaUtils.cu -- forward and backward -- and the two head
- * activations of YoloKernels.cu / CenterNetKernels.cu, declared with the reference's exact C++
- * signatures (namespace px, same parameter types and order), so that the reference links against
- * libpxe.so instead of those six object files with no source change.  (YoloKernels.cu and
- * CenterNetKernels.cu also hold the loss launchers yoloLossGpu / centerNetLossGpu: a training build
- * keeps those two files; their yoloActivateGpu / centerNetActivateGpu then take precedence over the
- * ones here, which an inference-only build uses.)
+ * UpsampleKernels.cu, ShortcutKernel.cu, CudaUtils.cu, YoloKernels.cu and CenterNetKernels.cu -- forward,
+ * backward and loss -- declared with the reference's exact C++ signatures (namespace px, same
+ * parameter types and order), so that the reference links against libpxe.so instead of those
+ * eight object files with no source change.
  * Each one forwards to the C ABI in pxe.h on the legacy default stream and, like the
  * reference's PX_CUDA_CHECK_LAST, throws on failure (std::runtime_error here; the reference
  * throws px::CudaError, which also derives from std::exception).
@@ -75,5 +72,15 @@ dim3 cudaGridsize(std::uint32_t n);
 void mulGpu(int n, float* x, float* y);
 void randomGpu(float* ptr, std::size_t n, float a = 0.f, float b = 1.f);
 void randomNormalGpu(float* ptr, std::size_t n, float mean = 0.f, float stddev = 1.f);
+/* include/YoloKernels.cuh:10-19 */
+void yoloLossGpu(const float* output, float* delta, const float* truths, const int* truthCounts, int maxTruth,
+                 const int* assignedClasses, const int* assignedAnchors, const float* assignedBoxes, const int* masks,
+                 const float* anchors, float* stats, float* cost, int batch, int maskCount, int anchorCount, int classes,
+                 int width, int height, int networkWidth, int networkHeight, float ignoreThreshold,
+                 float truthThreshold, float coordScale, float objectScale, float noObjectScale, float classScale);
+/* include/CenterNetKernels.cuh:8-13 */
+void centerNetLossGpu(const float* output, float* delta, const float* targetHeatmap, const float* targetSize,
+                      const float* targetOffset, const float* targetMask, float* costs, int batch, int classes, int area,
+                      float normalizer, float focalAlpha, float focalBeta, float sizeWeight);
 
 }   // namespace px

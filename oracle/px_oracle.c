@@ -831,3 +831,166 @@ PXO_API void pxo_conv_forward(pxo_sgemm_fn sgemm, const float* in, const float* 
               out + (size_t)b * m * n, n);
     }
 }
+
+
+/* ------------------------------------------------------------------ */
+/* Detector losses as the reference's CUDA path computes them:         */
+/* src/YoloKernels.cu:11-214, src/CenterNetKernels.cu:20-122.          */
+/* Sums are taken in index order, in double, so that they can serve as */
+/* the reference value for any order of float additions.               */
+/* ------------------------------------------------------------------ */
+static float loss_overlap(float x1, float w1, float x2, float w2)
+{
+    return fminf(x1 + w1 / 2.0f, x2 + w2 / 2.0f) - fmaxf(x1 - w1 / 2.0f, x2 - w2 / 2.0f);   /* :11-15 */
+}
+
+static float loss_box_iou(const float* a, const float* b)                                   /* :17-24 */
+{
+    float w = loss_overlap(a[0], a[2], b[0], b[2]);
+    float h = loss_overlap(a[1], a[3], b[1], b[3]);
+    float intersection = w > 0.0f && h > 0.0f ? w * h : 0.0f;
+    float union_area = fmaxf(0.0f, a[2] * a[3] + b[2] * b[3] - intersection);
+    return union_area > 0.0f ? intersection / union_area : 0.0f;
+}
+
+static void loss_decode_box(const float* out, float* box, int area, int x, int y, int anchor, const float* anchors,
+                            int width, int height, int net_w, int net_h)                    /* :33-46 */
+{
+    box[0] = (x + out[0]) / width;
+    box[1] = (y + out[area]) / height;
+    box[2] = expf(out[2 * area]) * anchors[2 * anchor] / net_w;
+    box[3] = expf(out[3 * area]) * anchors[2 * anchor + 1] / net_h;
+}
+
+static void loss_box_delta(const float* truth, const float* out, float* del, int area, int x, int y, int width,
+                           int height, int net_w, int net_h, const float* anchors, int anchor, float coord_scale)
+{                                                                                            /* :48-61 */
+    float scale = coord_scale * (2.0f - truth[2] * truth[3]);
+    float tx = truth[0] * width - x;
+    float ty = truth[1] * height - y;
+    float tw = logf(fmaxf(1e-9f, truth[2] * net_w / anchors[2 * anchor]));
+    float th = logf(fmaxf(1e-9f, truth[3] * net_h / anchors[2 * anchor + 1]));
+    del[0] = scale * (tx - out[0]);
+    del[area] = scale * (ty - out[area]);
+    del[2 * area] = scale * (tw - out[2 * area]);
+    del[3 * area] = scale * (th - out[3 * area]);
+}
+
+/* yoloLossGpu, src/YoloKernels.cu:223-252: the region pass, the object pass, the squared norm of delta and the
+ * loss components, in that order.  stats: 12 doubles, cost: 1 double, both added to. */
+PXO_API void pxo_yolo_loss(const float* output, float* delta, const float* truths, const int* truth_counts, int max_truth,
+                           const int* assigned_classes, const int* assigned_anchors, const float* assigned_boxes,
+                           const int* masks, const float* anchors, double* stats, double* cost, int batch, int mask_count,
+                           int classes, int width, int height, int net_w, int net_h, float ignore_thr, float truth_thr,
+                           float coord_scale, float object_scale, float no_object_scale, float class_scale)
+{
+    const int area = width * height, entries = classes + 5;
+    const int slots = batch * mask_count * area;
+    for (int slot = 0; slot < slots; ++slot) {                                              /* :73-124 */
+        int b = slot / (mask_count * area), within = slot % (mask_count * area);
+        int ms = within / area, cell = within % area;
+        int x = cell % width, y = cell / width;
+        const float* out = output + (size_t)b * mask_count * entries * area + (size_t)ms * entries * area + cell;
+        float* del = delta + (out - output);
+        float pred[4];
+        loss_decode_box(out, pred, area, x, y, masks[ms], anchors, width, height, net_w, net_h);
+        float best_iou = -FLT_MAX;
+        int best = -1;
+        for (int t = 0; t < truth_counts[b]; ++t) {
+            int ti = (b * max_truth + t) * 5;
+            float iou = loss_box_iou(pred, truths + ti);
+            if (iou > best_iou) { best_iou = iou; best = ti; }
+        }
+        float objectness = out[4 * area];
+        stats[5] += objectness;
+        if (best < 0 || best_iou < ignore_thr) del[4 * area] = -no_object_scale * objectness;
+        if (best >= 0 && best_iou > truth_thr) {
+            del[4 * area] = object_scale * (1.0f - objectness);
+            int class_id = (int)truths[best + 4];
+            for (int c = 0; c < classes; ++c)
+                del[(5 + c) * area] = class_scale * ((c == class_id ? 1.0f : 0.0f) - out[(5 + c) * area]);
+            loss_box_delta(truths + best, out, del, area, x, y, width, height, net_w, net_h, anchors, masks[ms], coord_scale);
+        }
+    }
+    for (int slot = 0; slot < slots; ++slot) {                                              /* :126-168 */
+        if (assigned_classes[slot] < 0) continue;
+        int b = slot / (mask_count * area), within = slot % (mask_count * area);
+        int ms = within / area, cell = within % area;
+        int x = cell % width, y = cell / width;
+        const float* out = output + (size_t)b * mask_count * entries * area + (size_t)ms * entries * area + cell;
+        float* del = delta + (out - output);
+        const float* truth = assigned_boxes + (size_t)slot * 4;
+        int anchor = assigned_anchors[slot];
+        float pred[4];
+        loss_decode_box(out, pred, area, x, y, anchor, anchors, width, height, net_w, net_h);
+        float iou = loss_box_iou(pred, truth);
+        loss_box_delta(truth, out, del, area, x, y, width, height, net_w, net_h, anchors, anchor, coord_scale);
+        stats[4] += out[4 * area];
+        del[4 * area] = object_scale * (1.0f - out[4 * area]);
+        int class_id = assigned_classes[slot];
+        for (int c = 0; c < classes; ++c) {
+            float truth_class = c == class_id ? 1.0f : 0.0f;
+            del[(5 + c) * area] = class_scale * (truth_class - out[(5 + c) * area]);
+            if (truth_class != 0.0f) stats[3] += fminf(1.0f, out[(5 + c) * area]);
+        }
+        stats[0] += iou;
+        if (iou > 0.5f) stats[1] += 1.0;
+        if (iou > 0.75f) stats[2] += 1.0;
+        stats[6] += 1.0;
+        stats[7] += 1.0;
+    }
+    const size_t outputs = (size_t)slots * entries;                                         /* :170-182 */
+    for (size_t i = 0; i < outputs; ++i) *cost += (double)(delta[i] * delta[i]);
+    for (int slot = 0; slot < slots; ++slot) {                                              /* :184-214 */
+        int b = slot / (mask_count * area), within = slot % (mask_count * area);
+        int ms = within / area, cell = within % area;
+        const float* del = delta + (size_t)b * mask_count * entries * area + (size_t)ms * entries * area + cell;
+        float box = 0.0f;
+        for (int k = 0; k < 4; ++k) box += del[k * area] * del[k * area];
+        stats[8] += box;
+        float object = del[4 * area];
+        stats[object >= 0.0f ? 9 : 10] += (double)(object * object);
+        float cls = 0.0f;
+        for (int c = 0; c < classes; ++c) cls += del[(5 + c) * area] * del[(5 + c) * area];
+        stats[11] += cls;
+    }
+}
+
+/* centerNetLossGpu, src/CenterNetKernels.cu:20-139.  costs: 3 doubles, added to. */
+PXO_API void pxo_centernet_loss(const float* output, float* delta, const float* target_heat, const float* target_size,
+                                const float* target_offset, const float* target_mask, double* costs, int batch,
+                                int classes, int area, float normalizer, float alpha, float beta, float size_weight)
+{
+    const size_t outputs = (size_t)(classes + 4) * area, heat = (size_t)classes * area;
+    for (size_t i = 0; i < (size_t)batch * heat; ++i) {                                     /* :20-61 */
+        size_t b = i / heat, at = b * outputs + i % heat;
+        float prediction = fminf(fmaxf(output[at], 1e-4f), 1.0f - 1e-4f);
+        float truth = target_heat[i];
+        float loss;
+        if (truth >= 1.0f - 1e-6f) {
+            float one_minus = 1.0f - prediction;
+            loss = -powf(one_minus, alpha) * logf(prediction);
+            delta[at] = normalizer * (powf(one_minus, alpha + 1.0f) - alpha * prediction * powf(one_minus, alpha) * logf(prediction));
+        } else {
+            float weight = powf(1.0f - truth, beta);
+            loss = -weight * powf(prediction, alpha) * logf(1.0f - prediction);
+            delta[at] = normalizer * weight * (alpha * powf(prediction, alpha) * (1.0f - prediction) * logf(1.0f - prediction)
+                                               - powf(prediction, alpha + 1.0f));
+        }
+        costs[0] += loss;
+    }
+    for (size_t i = 0; i < (size_t)batch * area; ++i) {                                     /* :63-122 */
+        if (target_mask[i] == 0.0f) continue;
+        size_t b = i / area, cell = i % area;
+        for (int channel = 0; channel < 2; ++channel) {
+            size_t map = (size_t)channel * area + cell;
+            size_t si = b * outputs + heat + map, oi = b * outputs + heat + 2 * (size_t)area + map;
+            float size_error = target_size[b * 2 * area + map] - output[si];
+            float offset_error = target_offset[b * 2 * area + map] - output[oi];
+            costs[1] += fabsf(size_error);
+            costs[2] += fabsf(offset_error);
+            delta[si] = size_weight * normalizer * (float)((size_error > 0.0f) - (size_error < 0.0f));
+            delta[oi] = normalizer * (float)((offset_error > 0.0f) - (offset_error < 0.0f));
+        }
+    }
+}

@@ -82,6 +82,9 @@ def lib():
         L.pxo_maxpool_backward.argtypes = [_f, _i, _f, C.c_size_t]
         L.pxo_upsample_backward.argtypes = [_f, _f] + [C.c_int] * 5 + [C.c_float]
         L.pxo_constrain.argtypes = [_f, C.c_size_t, C.c_float]
+        _d = C.POINTER(C.c_double)
+        L.pxo_yolo_loss.argtypes = [_f, _f, _f, _i, C.c_int, _i, _i, _f, _i, _f, _d, _d] + [C.c_int] * 7 + [C.c_float] * 6
+        L.pxo_centernet_loss.argtypes = [_f, _f, _f, _f, _f, _f, _d] + [C.c_int] * 3 + [C.c_float] * 4
         L.pxo_scale_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.pxo_normalize.argtypes = [_f, _f, _f, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         L.pxo_conv_epilogue.argtypes = [_f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, C.c_float,
@@ -170,6 +173,40 @@ def constrain(x, alpha):
     y = _c(x).copy()
     lib().pxo_constrain(_fp(y), y.size, C.c_float(alpha))
     return y
+
+
+def yolo_loss(output, delta, truths, truth_counts, assigned_classes, assigned_anchors, assigned_boxes, masks, anchors,
+              net_w, net_h, ignore_thr=0.5, truth_thr=1.0, coord_scale=1.0, object_scale=1.0, no_object_scale=1.0,
+              class_scale=1.0):
+    """yoloLossGpu as the reference's kernels compute it.  output, delta: [B, masks*(5+classes), H, W];
+    truths: [B, max_truth, 5].  Returns (delta, stats[12], cost) with the sums in float64."""
+    out = _c(output)
+    d = _c(delta).copy()
+    B, ch, H, W = out.shape
+    mc = len(masks)
+    classes = ch // mc - 5
+    t = _c(truths)
+    tc, ac, aa = _c(truth_counts, np.int32), _c(assigned_classes, np.int32), _c(assigned_anchors, np.int32)
+    ab, mk, an = _c(assigned_boxes), _c(masks, np.int32), _c(anchors)
+    stats, cost = np.zeros(12, np.float64), np.zeros(1, np.float64)
+    dp = C.POINTER(C.c_double)
+    lib().pxo_yolo_loss(_fp(out), _fp(d), _fp(t), _ip(tc), t.shape[1], _ip(ac), _ip(aa), _fp(ab), _ip(mk), _fp(an),
+                        stats.ctypes.data_as(dp), cost.ctypes.data_as(dp), B, mc, classes, W, H, net_w, net_h,
+                        ignore_thr, truth_thr, coord_scale, object_scale, no_object_scale, class_scale)
+    return d, stats, float(cost[0])
+
+
+def centernet_loss(output, delta, target_heat, target_size, target_offset, target_mask, normalizer, alpha=2.0, beta=4.0,
+                   size_weight=0.1):
+    """centerNetLossGpu.  output, delta: [B, classes+4, H, W].  Returns (delta, costs[3] in float64)."""
+    out = _c(output)
+    d = _c(delta).copy()
+    B, ch, H, W = out.shape
+    costs = np.zeros(3, np.float64)
+    lib().pxo_centernet_loss(_fp(out), _fp(d), _fp(_c(target_heat)), _fp(_c(target_size)), _fp(_c(target_offset)),
+                             _fp(_c(target_mask)), costs.ctypes.data_as(C.POINTER(C.c_double)), B, ch - 4, H * W,
+                             normalizer, alpha, beta, size_weight)
+    return d, costs
 
 
 def conv_epilogue(x, gamma=None, beta=None, mean=None, var=None, bias=None, act="linear",
@@ -582,6 +619,8 @@ class RefCuda:
             "pxrefcu_mul": [i, vp, vp],
             "pxrefcu_random": [vp, sz, f, f],
             "pxrefcu_random_normal": [vp, sz, f, f],
+            "pxrefcu_yolo_loss": [vp] * 12 + [i] * 9 + [f] * 6,
+            "pxrefcu_centernet_loss": [vp] * 7 + [i] * 3 + [f] * 4,
         }
         L.pxrefcu_gridsize.argtypes = [C.c_uint, C.POINTER(C.c_uint)]
         L.pxrefcu_gridsize.restype = None

@@ -121,6 +121,31 @@ API int pxrefcu_random_normal(float* p, std::size_t n, float mean, float stddev)
     return guarded([&] { px::randomNormalGpu(p, n, mean, stddev); });
 }
 
+API int pxrefcu_yolo_loss(const float* output, float* delta, const float* truths, const int* truth_counts,
+                          const int* assigned_classes, const int* assigned_anchors, const float* assigned_boxes,
+                          const int* masks, const float* anchors, float* stats, float* cost, const void* unused,
+                          int max_truth, int batch, int mask_count, int anchor_count, int classes, int width, int height,
+                          int net_w, int net_h, float ignore_thr, float truth_thr, float coord_scale, float object_scale,
+                          float no_object_scale, float class_scale)
+{
+    (void)unused;
+    return guarded([&] {
+        px::yoloLossGpu(output, delta, truths, truth_counts, max_truth, assigned_classes, assigned_anchors, assigned_boxes,
+                        masks, anchors, stats, cost, batch, mask_count, anchor_count, classes, width, height, net_w, net_h,
+                        ignore_thr, truth_thr, coord_scale, object_scale, no_object_scale, class_scale);
+    });
+}
+
+API int pxrefcu_centernet_loss(const float* output, float* delta, const float* target_heat, const float* target_size,
+                               const float* target_offset, const float* target_mask, float* costs, int batch, int classes,
+                               int area, float normalizer, float alpha, float beta, float size_weight)
+{
+    return guarded([&] {
+        px::centerNetLossGpu(output, delta, target_heat, target_size, target_offset, target_mask, costs, batch, classes,
+                             area, normalizer, alpha, beta, size_weight);
+    });
+}
+
 API void pxrefcu_gridsize(unsigned n, unsigned* xyz)
 {
     const dim3 d = px::cudaGridsize(n);

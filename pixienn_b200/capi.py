@@ -94,6 +94,17 @@ class CenterNetDecodeDesc(C.Structure):
 
 
 POOL_AUTO, POOL_GENERAL = 0, 1            # enum pxe_pool_variant
+class YoloLossDesc(C.Structure):
+    """pxe_yolo_loss_desc of include/pxe.h."""
+    _fields_ = [("output", C.c_void_p), ("delta", C.c_void_p), ("truths", C.c_void_p), ("truth_counts", C.c_void_p),
+                ("max_truth", C.c_int), ("assigned_classes", C.c_void_p), ("assigned_anchors", C.c_void_p),
+                ("assigned_boxes", C.c_void_p), ("masks", C.c_void_p), ("anchors", C.c_void_p), ("stats", C.c_void_p),
+                ("cost", C.c_void_p), ("batch", C.c_int), ("mask_count", C.c_int), ("classes", C.c_int),
+                ("width", C.c_int), ("height", C.c_int), ("network_width", C.c_int), ("network_height", C.c_int),
+                ("ignore_threshold", C.c_float), ("truth_threshold", C.c_float), ("coord_scale", C.c_float),
+                ("object_scale", C.c_float), ("no_object_scale", C.c_float), ("class_scale", C.c_float)]
+
+
 PLAN_MAX_SOURCES, PLAN_MAX_DESTS, PLAN_MAX_SPP = 16, 8, 4
 
 
@@ -143,6 +154,7 @@ PROTOTYPES = {
     "pxe_concat": (_i, [_vp, _i, C.POINTER(_vp), C.POINTER(_ll), C.POINTER(_i), _vp, _ll, _i, _i, _i]),
     "pxe_yolo_activate": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "pxe_yolo_decode_workspace_bytes": (_sz, [_i, _i, _i]),
+    "pxe_yolo_decode_fast_workspace_bytes": (_sz, [_i, _i, _i]),
     "pxe_yolo_decode": (_i, [_vp, C.POINTER(YoloDecodeDesc), _vp, _ll, _vp, _vp, _sz]),
     "pxe_yolo_decode_static": (_i, [_vp, C.POINTER(YoloDecodeDesc), _vp, _ll, _vp]),
     "pxe_centernet_activate": (_i, [_vp, _vp, _vp, _i, _i, _i, _f]),
@@ -171,6 +183,8 @@ PROTOTYPES = {
     "pxe_mul": (_i, [_vp, _vp, _vp, _sz]),
     "pxe_random_uniform": (_i, [_vp, _vp, _sz, _f, _f]),
     "pxe_random_normal": (_i, [_vp, _vp, _sz, _f, _f]),
+    "pxe_yolo_loss": (_i, [_vp, C.POINTER(YoloLossDesc)]),
+    "pxe_centernet_loss": (_i, [_vp] + [_vp] * 7 + [_i] * 3 + [_f] * 4),
 }
 
 # the planner of include/pxe_plan.h (host code)
@@ -204,6 +218,8 @@ COMPAT_SYMBOLS = [
     "_ZN2px6mulGpuEiPfS0_",
     "_ZN2px9randomGpuEPfmff",
     "_ZN2px15randomNormalGpuEPfmff",
+    "_ZN2px11yoloLossGpuEPKfPfS1_PKiiS4_S4_S1_S4_S1_S2_S2_iiiiiiiiffffff",
+    "_ZN2px16centerNetLossGpuEPKfPfS1_S1_S1_S1_S2_iiiffff",
 ]
 
 _lib = None

@@ -129,6 +129,34 @@ PXE_EXPORT void randomNormalGpu(float* ptr, std::size_t n, float mean, float std
     check(pxe_random_normal(nullptr, ptr, n, mean, stddev), "randomNormalGpu");
 }
 
+PXE_EXPORT void yoloLossGpu(const float* output, float* delta, const float* truths, const int* truthCounts, int maxTruth,
+                            const int* assignedClasses, const int* assignedAnchors, const float* assignedBoxes,
+                            const int* masks, const float* anchors, float* stats, float* cost, int batch, int maskCount,
+                            int anchorCount, int classes, int width, int height, int networkWidth, int networkHeight,
+                            float ignoreThreshold, float truthThreshold, float coordScale, float objectScale,
+                            float noObjectScale, float classScale)
+{
+    (void)anchorCount;
+    pxe_yolo_loss_desc d{};
+    d.output = output; d.delta = delta; d.truths = truths; d.truth_counts = truthCounts; d.max_truth = maxTruth;
+    d.assigned_classes = assignedClasses; d.assigned_anchors = assignedAnchors; d.assigned_boxes = assignedBoxes;
+    d.masks = masks; d.anchors = anchors; d.stats = stats; d.cost = cost;
+    d.batch = batch; d.mask_count = maskCount; d.classes = classes; d.width = width; d.height = height;
+    d.network_width = networkWidth; d.network_height = networkHeight;
+    d.ignore_threshold = ignoreThreshold; d.truth_threshold = truthThreshold; d.coord_scale = coordScale;
+    d.object_scale = objectScale; d.no_object_scale = noObjectScale; d.class_scale = classScale;
+    check(pxe_yolo_loss(nullptr, &d), "yoloLossGpu");
+}
+
+PXE_EXPORT void centerNetLossGpu(const float* output, float* delta, const float* targetHeatmap, const float* targetSize,
+                                 const float* targetOffset, const float* targetMask, float* costs, int batch,
+                                 int classes, int area, float normalizer, float focalAlpha, float focalBeta,
+                                 float sizeWeight)
+{
+    check(pxe_centernet_loss(nullptr, output, delta, targetHeatmap, targetSize, targetOffset, targetMask, costs, batch,
+                             classes, area, normalizer, focalAlpha, focalBeta, sizeWeight), "centerNetLossGpu");
+}
+
 // Launch grid for n threads in blocks of 512: one row of blocks up to 65535, a near-square arrangement beyond
 // (src/CudaUtils.cu:28-43).  The second dimension is what keeps launches of more than 33.5 M threads legal.
 PXE_EXPORT dim3 cudaGridsize(std::uint32_t n)

@@ -33,6 +33,8 @@ struct YoloParams {
     long long* count;
     int* block_sums;           // [batch*blocks_per_image]
     long long* block_offsets;  // [batch*blocks_per_image]
+    unsigned short* masks;     // [batch*blocks_per_image][threads per block]: which classes of a thread's chunk the count
+                               // pass found at or above the threshold; NULL = the emit pass finds them again itself
 };
 
 // value of entry `e` of mask slot `n` at `cell`, activated as YoloLayer::forward leaves it
@@ -103,10 +105,16 @@ yolo_count_kernel(const YoloParams p)
     const int cell = blockIdx.x * kYoloCells + lane;
     const float* img = p.d.head + (long long)b * p.hbs;
     int cnt = 0;
+    unsigned mask = 0;
     if (cell < p.HW) {
         float prob[kYoloChunk], obj;
         cnt = yolo_chunk(p, img, w / p.chunks, w % p.chunks, cell, prob, &obj);
+        if (cnt > 0) {                                 // prob[] is only filled when the slot's objectness passed
+#pragma unroll
+            for (int j = 0; j < kYoloChunk; ++j) mask |= prob[j] >= 0.0f ? 1u << j : 0u;
+        }
     }
+    if (p.masks) p.masks[((size_t)b * p.blocks_per_image + blockIdx.x) * blockDim.x + threadIdx.x] = (unsigned short)mask;
     for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
     if (lane == 0) warp_sums[w] = cnt;
     __syncthreads();
@@ -183,7 +191,21 @@ yolo_emit_kernel(const YoloParams p)
     const int n = w / p.chunks, chunk = w % p.chunks;
     float prob[kYoloChunk], obj = 0.0f;
     int cnt = 0;
-    if (cell < p.HW) cnt = yolo_chunk(p, img, n, chunk, cell, prob, &obj);
+    if (p.masks) {
+        // the count pass left the classes that reach the threshold: one activation per emitted value, none at all
+        // for the threads (most of them, on a trained head) that emit nothing
+        const unsigned mask = p.masks[((size_t)b * p.blocks_per_image + blockIdx.x) * blockDim.x + threadIdx.x];
+        cnt = __popc(mask);
+        if (cnt) {
+            obj = yolo_value(p, img, n, 4, cell);
+            const int c0 = chunk * p.chunk_len;
+#pragma unroll
+            for (int j = 0; j < kYoloChunk; ++j)
+                prob[j] = (mask >> j) & 1u ? obj * yolo_value(p, img, n, 5 + c0 + j, cell) : -1.0f;
+        }
+    } else if (cell < p.HW) {
+        cnt = yolo_chunk(p, img, n, chunk, cell, prob, &obj);
+    }
     // exclusive scan over the block in emission order: rank = lane * warps + w
     const int nthreads = kYoloCells * p.warps;
     ranked[lane * p.warps + w] = cnt;
@@ -1524,6 +1546,15 @@ extern "C" size_t pxe_yolo_decode_workspace_bytes(int batch, int height, int wid
     return align_up((size_t)batch * bpi * sizeof(int), 256) + align_up((size_t)batch * bpi * sizeof(long long), 256);
 }
 
+extern "C" size_t pxe_yolo_decode_fast_workspace_bytes(int batch, int height, int width)
+{
+    if (batch <= 0 || height <= 0 || width <= 0) return 0;
+    const size_t hw = (size_t)height * width;
+    const size_t bpi = (hw + kYoloCells - 1) / kYoloCells;
+    return pxe_yolo_decode_workspace_bytes(batch, height, width) +
+           align_up((size_t)batch * bpi * kYoloCells * kYoloMaxWarps * sizeof(unsigned short), 256);
+}
+
 extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* dp, pxe_detection* dets,
                                long long capacity, long long* count, void* workspace, size_t workspace_bytes)
 {
@@ -1565,6 +1596,12 @@ extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* 
     p.block_sums = reinterpret_cast<int*>(ws);
     ws += align_up((size_t)d.batch * p.blocks_per_image * sizeof(int), 256);
     p.block_offsets = reinterpret_cast<long long*>(ws);
+    ws += align_up((size_t)d.batch * p.blocks_per_image * sizeof(long long), 256);
+    // with room for them, the count pass leaves per-thread class masks and the emit pass evaluates only what it
+    // emits (chunks longer than the register window keep the plain form: their tail is not in the mask)
+    p.masks = nullptr;
+    if (workspace_bytes >= pxe_yolo_decode_fast_workspace_bytes(d.batch, d.height, d.width) && p.chunk_len <= kYoloChunk)
+        p.masks = reinterpret_cast<unsigned short*>(ws);
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     dim3 grid((unsigned)p.blocks_per_image, (unsigned)d.batch);

@@ -315,7 +315,7 @@ def yolo_decode(head: torch.Tensor, mask, anchors, classes: int, net_w: int, net
     d.threshold, d.batch_id_offset = threshold, batch_id_offset
     if Cc != len(mask) * (classes + 5):
         raise ValueError("head channels must equal masks*(classes+5)")
-    need = capi.lib().pxe_yolo_decode_workspace_bytes(B, H, W)
+    need = capi.lib().pxe_yolo_decode_fast_workspace_bytes(B, H, W)
     ws = buf.workspace(need)
     capi.check(capi.lib().pxe_yolo_decode(_stream(), C.byref(d), buf.dets.data_ptr(), buf.capacity,
                                           buf.count.data_ptr(), ws.data_ptr(), ws.numel()))
@@ -528,6 +528,40 @@ def random_normal(out: torch.Tensor, mean: float = 0.0, stddev: float = 1.0) -> 
     _check_f32_cuda(out, "out")
     capi.check(capi.lib().pxe_random_normal(_stream(), out.data_ptr(), out.numel(), mean, stddev))
     return out
+
+
+def yolo_loss(output: torch.Tensor, delta: torch.Tensor, truths: torch.Tensor, truth_counts: torch.Tensor,
+              assigned_classes: torch.Tensor, assigned_anchors: torch.Tensor, assigned_boxes: torch.Tensor,
+              masks: torch.Tensor, anchors: torch.Tensor, stats: torch.Tensor, cost: torch.Tensor, net_w: int, net_h: int,
+              ignore_thr: float = 0.5, truth_thr: float = 1.0, coord_scale: float = 1.0, object_scale: float = 1.0,
+              no_object_scale: float = 1.0, class_scale: float = 1.0) -> None:
+    """px::yoloLossGpu as one launch; delta, stats (12 floats) and cost (1 float) are updated in place."""
+    _check_f32_cuda(output, "output")
+    _check_f32_cuda(delta, "delta")
+    B, ch, H, W = output.shape
+    d = capi.YoloLossDesc()
+    d.output, d.delta, d.truths, d.truth_counts = output.data_ptr(), delta.data_ptr(), truths.data_ptr(), truth_counts.data_ptr()
+    d.max_truth = truths.shape[1]
+    d.assigned_classes, d.assigned_anchors = assigned_classes.data_ptr(), assigned_anchors.data_ptr()
+    d.assigned_boxes, d.masks, d.anchors = assigned_boxes.data_ptr(), masks.data_ptr(), anchors.data_ptr()
+    d.stats, d.cost = stats.data_ptr(), cost.data_ptr()
+    d.batch, d.mask_count, d.classes, d.width, d.height = B, masks.numel(), ch // masks.numel() - 5, W, H
+    d.network_width, d.network_height = net_w, net_h
+    d.ignore_threshold, d.truth_threshold, d.coord_scale = ignore_thr, truth_thr, coord_scale
+    d.object_scale, d.no_object_scale, d.class_scale = object_scale, no_object_scale, class_scale
+    capi.check(capi.lib().pxe_yolo_loss(_stream(), C.byref(d)))
+
+
+def centernet_loss(output: torch.Tensor, delta: torch.Tensor, target_heat: torch.Tensor, target_size: torch.Tensor,
+                   target_offset: torch.Tensor, target_mask: torch.Tensor, costs: torch.Tensor, normalizer: float,
+                   alpha: float = 2.0, beta: float = 4.0, size_weight: float = 0.1) -> None:
+    """px::centerNetLossGpu; delta and costs (3 floats) are updated in place."""
+    _check_f32_cuda(output, "output")
+    _check_f32_cuda(delta, "delta")
+    B, ch, H, W = output.shape
+    capi.check(capi.lib().pxe_centernet_loss(_stream(), output.data_ptr(), delta.data_ptr(), target_heat.data_ptr(),
+                                             target_size.data_ptr(), target_offset.data_ptr(), target_mask.data_ptr(),
+                                             costs.data_ptr(), B, ch - 4, H * W, normalizer, alpha, beta, size_weight))
 
 
 # ------------------------------------------------------------------------------ channels-last tier

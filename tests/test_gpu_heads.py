@@ -108,6 +108,43 @@ def test_yolo_decode_raw_head_with_bias_and_chained_heads(cuda, oracle):
         pytest.fail("device-activated decode changed the detection set")
 
 
+def test_yolo_decode_with_and_without_class_masks(cuda, oracle):
+    """With the larger workspace the first pass leaves per-thread class masks and the second evaluates only what
+    it emits; with the minimum workspace the second pass finds the classes again.  Same records, raw and
+    activated heads, 80 classes (5 chunks per slot) and 7 (one partial chunk)."""
+    import ctypes as C
+    from pixienn_b200 import capi
+    L = capi.lib()
+    for classes, hw in ((80, 19), (7, 13)):
+        B = 3
+        raw = synth.normal(44, f"ym{classes}", (B, 3 * (classes + 5), hw, hw), 0.0, 1.5)
+        bias = synth.normal(44, f"ymb{classes}", 3 * (classes + 5), 0, 0.3)
+        anchors = [10, 14, 23, 27, 37, 58, 81, 82, 135, 169, 344, 319]
+        results = []
+        for fast in (True, False):
+            buf = ops.DetectionBuffer(B * hw * hw * 3 * classes, cuda)
+            d = capi.YoloDecodeDesc()
+            head = dev(raw, cuda)
+            b = dev(bias, cuda)
+            d.head, d.head_is_raw, d.bias = head.data_ptr(), 1, b.data_ptr()
+            d.batch, d.height, d.width, d.classes, d.n_masks = B, hw, hw, classes, 3
+            for i, m in enumerate([3, 4, 5]):
+                d.mask[i] = m
+            d.n_anchor_values = len(anchors)
+            for i, a in enumerate(anchors):
+                d.anchors[i] = a
+            d.net_width = d.net_height = 416
+            d.threshold = 0.2
+            need = (L.pxe_yolo_decode_fast_workspace_bytes if fast else L.pxe_yolo_decode_workspace_bytes)(B, hw, hw)
+            ws = torch.empty(need, device=cuda, dtype=torch.uint8)
+            capi.check(L.pxe_yolo_decode(torch.cuda.current_stream().cuda_stream, C.byref(d), buf.dets.data_ptr(), buf.capacity,
+                                         buf.count.data_ptr(), ws.data_ptr(), need))
+            results.append(buf.to_host())
+        (a, na), (b2, nb) = results
+        assert na == nb > 100 and a.tobytes() == b2.tobytes()
+        assert L.pxe_yolo_decode_fast_workspace_bytes(B, hw, hw) > L.pxe_yolo_decode_workspace_bytes(B, hw, hw)
+
+
 def test_yolo_decode_capacity_overflow_and_offset(cuda, oracle):
     classes, B = 4, 2
     raw = yolo_case(44, B, classes, 13, 13, obj_shift=1.0)

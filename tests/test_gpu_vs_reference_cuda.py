@@ -252,3 +252,91 @@ def test_random_fills_follow_the_reference_engine(cuda, refcu):
     assert abs(mn.mean() - 1.0) < 0.02 and abs(mn.std() - 2.0) < 0.02
     assert abs(tn.mean() - 1.0) < 0.02 and abs(tn.std() - 2.0) < 0.02
     print(f"normal fill: max |mine - reference| = {np.abs(mn - tn).max():.3e}, correlation {np.corrcoef(mn, tn)[0, 1]:.6f}")
+
+
+# ------------------------------------------------------------------ detector losses
+def yolo_loss_case(seed, B=3, masks=(3, 4, 5), classes=5, H=13, W=13, max_truth=8):
+    rng = np.random.default_rng(seed)
+    mc = len(masks)
+    raw = synth.normal(seed, "yl", (B, mc * (classes + 5), H, W), 0, 1.0)
+    out = raw.reshape(B, mc, classes + 5, H, W).copy()
+    sig = lambda v: (1.0 / (1.0 + np.exp(-v.astype(np.float64)))).astype(np.float32)
+    out[:, :, :2] = sig(out[:, :, :2]); out[:, :, 4:] = sig(out[:, :, 4:]); out[:, :, 2:4] *= 0.3
+    out = np.ascontiguousarray(out.reshape(B, -1, H, W))
+    truths = np.zeros((B, max_truth, 5), np.float32)
+    counts = np.array([3, 0, 7][:B], np.int32)
+    for b in range(B):
+        for t in range(counts[b]):
+            truths[b, t] = [rng.uniform(0.1, 0.9), rng.uniform(0.1, 0.9), rng.uniform(0.05, 0.5), rng.uniform(0.05, 0.5),
+                            rng.integers(classes)]
+    slots = B * mc * H * W
+    a_cls = np.full(slots, -1, np.int32)
+    a_anc = np.zeros(slots, np.int32)
+    a_box = np.zeros((slots, 4), np.float32)
+    for s_ in rng.choice(slots, 25, replace=False):
+        a_cls[s_] = rng.integers(classes)
+        a_anc[s_] = rng.integers(6)
+        a_box[s_] = [rng.uniform(0.1, 0.9), rng.uniform(0.1, 0.9), rng.uniform(0.05, 0.5), rng.uniform(0.05, 0.5)]
+    anchors = np.array([10, 14, 23, 27, 37, 58, 81, 82, 135, 169, 344, 319], np.float32)
+    return out, truths, counts, a_cls, a_anc, a_box, np.array(masks, np.int32), anchors
+
+
+@pytest.mark.parametrize("prior", ["cleared", "kept"])
+def test_yolo_loss_three_way(cuda, oracle, refcu, prior):
+    """One launch here against the reference's four (region, object, squared norm, components): every delta value
+    identical, the twelve statistics and the cost equal to the rounding of their float sums.  `kept`: delta holds
+    values the loss does not decide, which must survive and count in the cost."""
+    out, truths, counts, a_cls, a_anc, a_box, masks, anchors = yolo_loss_case(97)
+    delta0 = np.zeros_like(out) if prior == "cleared" else synth.normal(97, "ylp", out.shape, 0, 0.05)
+    kw = dict(ignore_thr=0.5, truth_thr=0.3, coord_scale=1.5, object_scale=5.0, no_object_scale=0.7, class_scale=1.2)
+    want_delta, want_stats, want_cost = oracle.yolo_loss(out, delta0, truths, counts, a_cls, a_anc, a_box, masks, anchors,
+                                                         416, 416, **kw)
+    ti = lambda a: torch.from_numpy(a).to(cuda)
+    args = [ti(out), None, ti(truths), ti(counts), ti(a_cls), ti(a_anc), ti(a_box), ti(masks), ti(anchors)]
+    mine_d, mine_s, mine_c = ti(delta0), torch.zeros(12, device=cuda), torch.zeros(1, device=cuda)
+    ops.yolo_loss(args[0], mine_d, *args[2:], mine_s, mine_c, 416, 416, **kw)
+    ref_d, ref_s, ref_c = ti(delta0), torch.zeros(12, device=cuda), torch.zeros(1, device=cuda)
+    B, ch, H, W = out.shape
+    refcu.call("yolo_loss", args[0].data_ptr(), ref_d.data_ptr(), args[2].data_ptr(), args[3].data_ptr(), args[4].data_ptr(),
+               args[5].data_ptr(), args[6].data_ptr(), args[7].data_ptr(), args[8].data_ptr(), ref_s.data_ptr(),
+               ref_c.data_ptr(), None, truths.shape[1], B, len(masks), 6, ch // len(masks) - 5, W, H, 416, 416,
+               kw["ignore_thr"], kw["truth_thr"], kw["coord_scale"], kw["object_scale"], kw["no_object_scale"], kw["class_scale"])
+    torch.cuda.synchronize()
+    assert torch.equal(mine_d, ref_d)                      # the same expressions: identical deltas
+    close(mine_d.cpu().numpy(), want_delta, atol=2e-6)
+    assert np.count_nonzero(want_delta != delta0) > 500
+    for got in (mine_s.cpu().numpy(), ref_s.cpu().numpy()):
+        np.testing.assert_allclose(got, want_stats, rtol=2e-5, atol=1e-5)
+    assert want_stats[6] == 25 and want_stats[0] > 0
+    for got in (float(mine_c.item()), float(ref_c.item())):
+        assert abs(got - want_cost) <= 2e-5 * want_cost
+
+
+def test_centernet_loss_three_way(cuda, oracle, refcu):
+    B, classes, H, W = 3, 4, 16, 24
+    rng = np.random.default_rng(98)
+    out = synth.uniform(98, "clo", (B, classes + 4, H, W))
+    out[:, :classes] = np.clip(out[:, :classes], 1e-5, 1 - 1e-5)
+    heat = (synth.uniform(98, "clh", (B, classes, H, W)) ** 4).astype(np.float32)
+    mask = np.zeros((B, H, W), np.float32)
+    for _ in range(20):
+        b, c, y, x = rng.integers(B), rng.integers(classes), rng.integers(H), rng.integers(W)
+        heat[b, c, y, x] = 1.0
+        mask[b, y, x] = 1.0
+    tsize = synth.uniform(98, "cls", (B, 2, H, W)) * 5
+    toff = synth.uniform(98, "clf", (B, 2, H, W))
+    delta0 = np.zeros_like(out)
+    want_delta, want_costs = oracle.centernet_loss(out, delta0, heat, tsize, toff, mask, 1.0 / 20, 2.0, 4.0, 0.1)
+    ti = lambda a: torch.from_numpy(a).to(cuda)
+    t = [ti(a) for a in (out, heat, tsize, toff, mask)]
+    mine_d, mine_c = ti(delta0), torch.zeros(3, device=cuda)
+    ops.centernet_loss(t[0], mine_d, t[1], t[2], t[3], t[4], mine_c, 1.0 / 20, 2.0, 4.0, 0.1)
+    ref_d, ref_c = ti(delta0), torch.zeros(3, device=cuda)
+    refcu.call("centernet_loss", t[0].data_ptr(), ref_d.data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(),
+               t[4].data_ptr(), ref_c.data_ptr(), B, classes, H * W, 1.0 / 20, 2.0, 4.0, 0.1)
+    torch.cuda.synchronize()
+    assert torch.equal(mine_d, ref_d)
+    close(mine_d.cpu().numpy(), want_delta, rtol=2e-5, atol=2e-6)     # powf / logf: CUDA's and glibc's differ by ulps
+    for got in (mine_c.cpu().numpy(), ref_c.cpu().numpy()):
+        np.testing.assert_allclose(got, want_costs, rtol=2e-5)
+    assert want_costs.min() > 0
