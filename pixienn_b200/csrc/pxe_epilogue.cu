@@ -832,10 +832,34 @@ int run_slice(cudaStream_t s, const pxe_epilogue_desc& d, int b0, int nb, const 
     return dispatch(s, p, di, d.act, mode, n, affine, false, 0);
 }
 
-bool overlap(const void* a, size_t an, const void* b, size_t bn)
+// A tensor argument as the kernels see it: `batch` blocks of `n` floats, `bs` floats apart.
+struct Span {
+    const float* p;
+    long long bs, n;
+    int batch;
+};
+
+// True when some image block of `a` shares an element with some image block of `b` -- unless they are the same
+// tensor (same base, same stride), which the kernels handle: every element is read before it is written by the
+// same thread.  Channel slots of one concat buffer interleave without touching and pass.
+bool conflict(const Span& a, const Span& b)
 {
-    auto pa = reinterpret_cast<uintptr_t>(a), pb = reinterpret_cast<uintptr_t>(b);
-    return pa < pb + bn && pb < pa + an;
+    if (!a.p || !b.p) return false;
+    if (a.p == b.p && (a.bs == b.bs || (a.batch == 1 && b.batch == 1))) return false;
+    const long long base_a = (long long)(reinterpret_cast<uintptr_t>(a.p) / sizeof(float));
+    const long long base_b = (long long)(reinterpret_cast<uintptr_t>(b.p) / sizeof(float));
+    const long long sb = b.bs > 0 ? b.bs : b.n;
+    for (int i = 0; i < a.batch; ++i) {
+        const long long lo = base_a + i * a.bs, hi = lo + a.n;         // [lo, hi) in float units
+        // image j of b is [base_b + j*sb, + b.n): intersects iff base_b + j*sb < hi and base_b + j*sb + b.n > lo
+        long long j_lo = lo - base_b - b.n + 1, j_hi = hi - 1 - base_b;
+        j_lo = j_lo <= 0 ? 0 : (j_lo + sb - 1) / sb;
+        if (j_hi < 0) continue;
+        j_hi = j_hi / sb;
+        if (j_hi > b.batch - 1) j_hi = b.batch - 1;
+        if (j_lo <= j_hi) return true;
+    }
+    return false;
 }
 
 }  // namespace
@@ -879,19 +903,30 @@ extern "C" int pxe_conv_epilogue(pxe_stream_t stream, const pxe_epilogue_desc* d
             return set_error(PXE_ERR_UNSUPPORTED, "conv_epilogue: padding 0 with an odd extent leaves full-resolution rows uncovered; run pxe_maxpool separately");
         const long long pchw = (long long)d.channels * oh * ow;
         PXE_REQUIRE(d.y_pool_batch_stride == 0 || d.y_pool_batch_stride >= pchw, "conv_epilogue: y_pool_batch_stride too small");
-        const long long pbs = d.y_pool_batch_stride ? d.y_pool_batch_stride : pchw;
-        const long long xbs = d.x_batch_stride ? d.x_batch_stride : CHW;
-        PXE_REQUIRE(!overlap(d.y_pool, (size_t)((d.batch - 1) * pbs + pchw) * 4, d.x, (size_t)((d.batch - 1) * xbs + CHW) * 4),
-                    "conv_epilogue: y_pool overlaps x");
     } else {
         PXE_REQUIRE(d.y != nullptr, "conv_epilogue: y is null");
     }
-    if (d.y && d.y != d.x) {
-        const long long xbs = d.x_batch_stride ? d.x_batch_stride : CHW, ybs = d.y_batch_stride ? d.y_batch_stride : CHW;
-        // a destination that is neither x itself nor disjoint from it would be read after being written
-        PXE_REQUIRE(!overlap(d.y, (size_t)((d.batch - 1) * ybs + CHW) * 4, d.x, (size_t)((d.batch - 1) * xbs + CHW) * 4)
-                        || (d.x_batch_stride != 0 || d.y_batch_stride != 0),
-                    "conv_epilogue: y partially overlaps x");
+    {
+        // A destination that shares memory with an input (other than being that very tensor), or with another
+        // destination, would be read after being written or written twice: refuse it.  Slots of one concat buffer
+        // interleave image by image without sharing an element, so the test is per image block.
+        const Span x{d.x, d.x_batch_stride ? d.x_batch_stride : CHW, CHW, d.batch};
+        const Span y{d.y, d.y_batch_stride ? d.y_batch_stride : CHW, CHW, d.batch};
+        const Span y2{d.y2, d.y2_batch_stride ? d.y2_batch_stride : CHW, CHW, d.batch};
+        const Span res{d.residual, d.residual_batch_stride ? d.residual_batch_stride : CHW, CHW, d.batch};
+        long long pchw = 0;
+        if (d.pool_kernel) pchw = (long long)d.channels * pxe_maxpool_out_dim(d.height, 2, 2, d.pool_padding) *
+                                  pxe_maxpool_out_dim(d.width, 2, 2, d.pool_padding);
+        const Span yp{d.pool_kernel ? d.y_pool : nullptr, d.y_pool_batch_stride ? d.y_pool_batch_stride : pchw, pchw, d.batch};
+        PXE_REQUIRE(!conflict(y, x), "conv_epilogue: y partially overlaps x");
+        PXE_REQUIRE(!conflict(y2, x), "conv_epilogue: y2 partially overlaps x");
+        PXE_REQUIRE(!d.y2 || d.y2 != d.y, "conv_epilogue: y2 is y");
+        PXE_REQUIRE(!conflict(y2, y), "conv_epilogue: y2 overlaps y");
+        PXE_REQUIRE(!conflict(y, res) && !conflict(y2, res), "conv_epilogue: a destination partially overlaps the residual");
+        PXE_REQUIRE(!conflict(yp, x) && !(d.pool_kernel && d.y_pool == d.x), "conv_epilogue: y_pool overlaps x");
+        PXE_REQUIRE(!conflict(yp, y) && !conflict(yp, y2) && !conflict(yp, res) &&
+                        !(d.pool_kernel && (d.y_pool == d.y || d.y_pool == d.y2 || d.y_pool == d.residual)),
+                    "conv_epilogue: y_pool overlaps another tensor of the call");
     }
     DeviceInfo di;
     int rc = device_info(&di);

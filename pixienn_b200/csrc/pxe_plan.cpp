@@ -149,7 +149,7 @@ struct Builder {
             switch (l.type) {
             case PXE_LAYER_CONV: {
                 pxe_step st = blank(PXE_STEP_CONV, i);
-                st.n_inputs = 1; st.inputs[0] = l.sources[0];
+                st.n_inputs = 1; st.inputs[0] = resolve(l.sources[0]);
                 int out_t = i;
                 std::vector<int> readers = real_consumers(i);
                 const pxe_layer_desc* nxt = i + 1 < n ? &L[i + 1] : nullptr;
@@ -157,7 +157,7 @@ struct Builder {
                     if (nxt->type == PXE_LAYER_SHORTCUT && nxt->sources[0] == i && nxt->sources[1] >= 0
                         && same_shape(L[nxt->sources[1]], l)) {
                         st.fused_shortcut = i + 1;
-                        st.inputs[st.n_inputs++] = nxt->sources[1];
+                        st.inputs[st.n_inputs++] = resolve(nxt->sources[1]);
                         absorbed.insert(i + 1);
                         alias[i] = i + 1;            // the conv's own value is never materialised
                         out_t = i + 1;
@@ -268,7 +268,16 @@ struct Builder {
             case PXE_LAYER_AVGPOOL: case PXE_LAYER_DROPOUT: case PXE_LAYER_CONNECTED: case PXE_LAYER_DETECTION: {
                 pxe_step st = blank(PXE_STEP_HEAD, i);
                 st.n_inputs = 1; st.inputs[0] = resolve(l.sources[0]);
+                // a dense tensor of its own, plus a copy into every route buffer that concatenates it
                 st.n_dests = 1; st.dests[0] = pxe_dest{0, -1, 0};
+                {
+                    auto it = slots.find(i);
+                    if (it != slots.end())
+                        for (const Slot& sl : it->second) {
+                            if (st.n_dests == PXE_PLAN_MAX_DESTS) return too_many(i);
+                            st.dests[st.n_dests++] = pxe_dest{1, sl.route, sl.offset};
+                        }
+                }
                 if (l.type == PXE_LAYER_YOLO && !plan->steps.empty() && plan->steps.back().op == PXE_STEP_CONV
                     && plan->steps.back().head_raw)
                     st.head_raw = 1;

@@ -274,14 +274,14 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
             i += 1
             continue
         if l.type == "conv":
-            st = Step("conv", i, [l.sources[0]], produces=[i])
+            st = Step("conv", i, [resolve(l.sources[0])], produces=[i])
             out_t = i
             readers = real_consumers(i)
             nxt = L[i + 1] if i + 1 < n else None
             if fuse and nxt is not None and readers == [i + 1]:
                 if nxt.type == "shortcut" and nxt.sources[0] == i and L[nxt.sources[1]].out_shape == l.out_shape:
                     st.fused_shortcut = i + 1
-                    st.inputs.append(nxt.sources[1])
+                    st.inputs.append(resolve(nxt.sources[1]))
                     absorbed.add(i + 1)
                     alias[i] = i + 1            # the conv's own value is never materialised
                     out_t = i + 1
@@ -348,7 +348,9 @@ def plan(model: Model, fuse: bool = True, raw_heads: bool = True) -> Plan:
                 steps.append(Step("concat", i, list(l.sources), [Dest("dense")], produces=[i]))
                 stats["concat_copies"] += 1
         elif l.type in ("yolo", "centernet", "region", "softmax", "avgpool", "dropout", "connected", "conn", "detection"):
-            st = Step(l.type, i, [resolve(l.sources[0])], [Dest("dense")], produces=[i])
+            # a dense tensor of its own, plus a copy into every route buffer that concatenates it
+            st = Step(l.type, i, [resolve(l.sources[0])],
+                      [Dest("dense")] + [Dest("slot", r, off) for (r, off) in slots.get(i, [])], produces=[i])
             if l.type == "yolo" and steps and steps[-1].op == "conv" and steps[-1].head_raw:
                 st.head_raw = True
             steps.append(st)

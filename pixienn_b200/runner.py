@@ -113,6 +113,9 @@ class OpTimer:
         self.records = []
 
 
+_HEAD_OPS = ("yolo", "centernet", "softmax", "region", "avgpool", "connected", "detection", "dropout")
+
+
 class Runner:
     def __init__(self, model: graph.Model, weights: Dict[int, Dict[str, np.ndarray]], batch: int, device,
                  fuse: bool = True, raw_heads: bool = True, det_capacity: int = 1 << 20,
@@ -329,6 +332,29 @@ class Runner:
                 tm.end(s, "upsample", 4 * (T[st.inputs[0]].numel() + dests[0].numel()))
                 self._extra_copies(dests[0], dests[1:])
                 T[st.layer] = dests[0]
+            elif st.op == "shortcut" and tuple(T[st.inputs[0]].shape) != tuple(T[st.inputs[1]].shape):
+                # ShortcutLayer::forward hands shortcutGpu its OWN dimensions for `from` as well
+                # (include/cuda/ShortcutLayer.h:29-30): a `from` tensor of another shape (resnet18.yml adds across its
+                # stride-2 stages) is read as if it had this layer's shape, image b at b*C*H*W of from's buffer.
+                # Reproduced as it is, as long as those reads stay inside from's buffer.
+                xin, frm = self._nchw(T[st.inputs[0]]), self._nchw(T[st.inputs[1]])
+                if frm.numel() < xin.numel():
+                    raise ValueError(f"layer {l.index}: shortcut from a tensor of {frm.numel()} elements into one of "
+                                     f"{xin.numel()}: the reference would read past the end of `from`")
+                s = tm.begin()
+                out = xin.clone()
+                _, c, h, w = out.shape
+                ops.shortcut_general(self.batch, w, h, c, frm, w, h, c, l.alpha, l.beta, out)
+                self.launches += 1
+                if l.activation != "linear":
+                    ops.activate(l.activation, out)
+                    self.launches += 1
+                tm.end(s, "shortcut", 12 * out.numel())
+                if self.nhwc:
+                    out = out.contiguous(memory_format=torch.channels_last)
+                dests = self._dest_tensors(bufs, st.dests, l, dense=out)
+                self._extra_copies(out, [d for d in dests if d is not out])
+                T[st.layer] = out
             elif st.op == "shortcut":
                 dests = self._dest_tensors(bufs, st.dests, l)
                 s = tm.begin()
@@ -436,6 +462,9 @@ class Runner:
                 T[st.layer] = T[st.inputs[0]]
             else:
                 raise NotImplementedError(st.op)
+            if st.op in _HEAD_OPS and len(st.dests) > 1 and st.layer in T:
+                # a head-type layer that a route concatenates: its dense output is copied into the route's buffer
+                self._extra_copies(T[st.layer], self._dest_tensors(bufs, st.dests[1:], l))
             if self.keep:
                 for p in st.produces:
                     if p in self.keep and p in T:

@@ -62,3 +62,33 @@ def test_host_only_entry_points():
     assert L.pxe_centernet_decode_workspace_bytes(1, 20, 128, 128, 100) >= 20 * 8 * 100 * 8
     assert L.pxe_conv_epilogue(None, None) == capi.PXE_ERR_BAD_ARG
     assert L.pxe_nms_host(None, 0, 0.5, None) == 0
+
+
+def test_overlapping_tensors_are_refused_before_any_launch():
+    """A destination that shares elements with an input or with another destination -- other than being that very
+    tensor -- is refused, batch strides or not.  (Channel slots of one buffer interleave without sharing and are
+    accepted: the GPU suites store into them.)  Pointers here are never dereferenced: validation fails first."""
+    import ctypes as C
+    L = capi.lib()
+    base = 0x10000000
+
+    def desc(**kw):
+        d = capi.EpilogueDesc()
+        d.x, d.batch, d.channels, d.height, d.width = base, 4, 6, 10, 10          # 600 floats per image
+        d.x_batch_stride = 1000
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+    cases = [
+        desc(y=base + 4 * 300, y_batch_stride=1000),                       # y starts inside every image of x
+        desc(y=base + 4 * 1000, y_batch_stride=1000),                      # image i of y is image i+1 of x
+        desc(y=base + 4 * 5000, y2=base + 4 * 100, y2_batch_stride=1000),  # second store into x's images
+        desc(y=base + 4 * 5000, y2=base + 4 * 5200),                       # the two stores overlap each other
+        desc(y=base + 4 * 5000, residual=base + 4 * 5300),                 # y would overwrite residual values not yet read
+        desc(y=base + 4 * 5000, pool_kernel=2, pool_stride=2, pool_padding=0, y_pool=base + 4 * 5100),
+        desc(y=None, pool_kernel=2, pool_stride=2, pool_padding=0, y_pool=base, y_pool_batch_stride=1000),
+    ]
+    for d in cases:
+        assert L.pxe_conv_epilogue(None, C.byref(d)) == capi.PXE_ERR_BAD_ARG, L.pxe_last_error_string()
+        assert b"overlap" in L.pxe_last_error_string() or b"is y" in L.pxe_last_error_string()

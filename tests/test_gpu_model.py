@@ -258,3 +258,37 @@ def test_predict_with_device_nms_equals_host_nms(cuda):
     got, total2 = r.predict(xb, nms_threshold=0.4, nms_on_device=True)
     assert total == total2 and 0 < len(want) < total
     assert got.tobytes() == want.tobytes()
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_route_of_a_head_type_layer_and_shortcut_across_shapes(cuda, oracle, layout):
+    """Two graph shapes outside the presets: a route that concatenates a dropout layer's output (a head-type step,
+    whose dense output has to be copied into the route's buffer) and a shortcut whose `from` tensor has another
+    shape, which the reference reads with this layer's own dimensions (resnet18.yml does that across its stride-2
+    stages).  Every layer equals the CPU walk, which follows the same rule."""
+    from oracle.pxmodel import CpuModel
+    conv = lambda f, k, s, act="leaky": {"type": "conv", "filters": f, "kernel": k, "stride": s, "pad": True,
+                                         "batch_normalize": True, "activation": act}
+    doc = {"model": {"channels": 3, "height": 16, "width": 16, "layers": [
+        conv(8, 3, 1),                                   # 0: 8 x 16 x 16
+        conv(16, 3, 2),                                  # 1: 16 x 8 x 8
+        conv(16, 1, 1, "linear"),                        # 2
+        {"type": "shortcut", "from": 0, "activation": "leaky"},      # 3: from is 8 x 16 x 16 = the same element count, another shape
+        {"type": "dropout"},                             # 4
+        {"type": "route", "layers": [4, 1]},             # 5: 32 x 8 x 8
+        {"type": "conv", "filters": 18, "kernel": 1, "stride": 1, "pad": True, "activation": "linear"},
+        {"type": "yolo", "mask": [0, 1, 2], "anchors": [10, 14, 23, 27, 37, 58]},
+    ]}}
+    model = graph.parse_model(doc)
+    weights = synth_weights(model, 21, head_bias=-1.0)
+    x = make_input(22, 2, model)
+    cpu = CpuModel(doc, weights, eps_mode=0)
+    cpu.forward(x)
+    r = Runner(model, weights, 2, cuda, layout=layout, raw_heads=False)
+    r.keep = set(range(len(model.layers)))
+    r.forward(dev(x, cuda))
+    torch.cuda.synchronize()
+    for i in (0, 1, 3, 4, 5):
+        np.testing.assert_allclose(r.kept[i].contiguous().cpu().numpy(), cpu.outputs[i], rtol=2e-3, atol=2e-3, err_msg=f"layer {i}")
+    # the route's buffer holds the dropout output and layer 1, in that order
+    assert torch.equal(r.kept[5][:, :16].contiguous(), r.kept[4].contiguous()) and torch.equal(r.kept[5][:, 16:].contiguous(), r.kept[1].contiguous())
