@@ -598,7 +598,8 @@ class Runner:
                 ops.conv_epilogue_nhwc(raw, y=dest, a=w["a"], b=w["b"], act=l.activation, **kw)
 
             if fc.tune(key, xin, w["weights"], w["a"], w["b"], dest, residual, split) is None:
-                T[out_layer.index] = dest            # the last timed split run left the layer's output there
+                split()                              # the candidates wrote dest after the split form was timed
+                T[out_layer.index] = dest
                 self.launches += 1
                 return True
         s = tm.begin()
