@@ -51,6 +51,7 @@ struct EpiParams {
     uint32_t units_per_image;
     int y_dense, pool_dense;
     int pool_general;          // host side only: skip the specialised pooled kernels
+    int flat_ok;               // host side only: groups of four planes are whole aligned vectors (flat pooled kernel)
 };
 
 // Folded coefficients and image / channel numbers of plane `pl` (= image*C + channel).
@@ -608,6 +609,140 @@ epilogue_pool_smallplane_kernel(const EpiParams p, uint32_t planes, uint32_t pla
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Odd small planes of a tensor whose images are dense and 16-byte aligned, channels a multiple of four: four
+// consecutive planes are 4*HW floats = HW whole 128-bit vectors starting on a 16-byte boundary.  A warp loads such
+// a group as flat coalesced vectors (one sector per 32 bytes, where the scalar stride-2 taps of the form above
+// touch eight sectors per request), applies the epilogue once per element on the vector, leaves the result in
+// the warp's own staging area and takes the 2x2 taps of its pooled outputs from there.
+//
+// The kernel is bound by instruction issue and latency, not by memory, so everything that does not depend on the
+// data is tabulated once per block: for each pooled output of a group the four staging offsets of its taps (a tap
+// outside the plane repeats the window's first tap, which never changes "first maximum wins"), for each vector the
+// table offsets of the planes its components lie in (a vector may straddle two planes; which of a lane's vectors
+// can is the same for the whole warp).  The loop over groups is then loads, the epilogue, four shared-memory reads
+// and three comparisons per pooled output, and stores.  Each warp folds the coefficients of its own planes after
+// the block's one barrier, so no warp waits there for another one's loads; the loads of a warp's next group go
+// out as soon as the registers of the current one are free (its values sit in the staging by then).
+//
+// Measured on B200 at [64,512,13,13] -> 7x7 (leaky / mish, us): the warp-per-plane form above 11.1 / 13.7; this
+// kernel with geometry in registers instead of tables 12.8 / 15.2; tables, 8 warps x 2 groups 10.0 / 11.6; the
+// same with all groups requested up front by asynchronous copies into a two-group staging 11.0 / 11.7; 4 warps x 2
+// groups (1024 blocks, seven resident per SM: 56 groups on every SM) 9.5 / 10.9; 1, 3, 4 groups per warp and 2- or
+// 8-warp blocks are all behind.  A launch that only reads the tensor takes 5.1, an empty one 1.2.
+// ---------------------------------------------------------------------------------------------
+constexpr int kFlatPlanes = 4;
+constexpr int kFlatWarps = 4;             // warps per block
+constexpr int kFlatGroups = 2;            // groups per warp
+constexpr int kFlatVectors = 6;           // vectors per lane and group: planes of up to 192 elements
+constexpr int kFlatSlots = 7;             // pooled outputs per lane and group: up to 56 per plane
+
+template <int ACT, bool AFFINE, int NV, int SLOTS, int WARPS, int GPW>
+__global__ void __launch_bounds__(WARPS * 32, 7)
+epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
+{
+    extern __shared__ float4 flat_smem[];
+    constexpr uint32_t kBlock = WARPS * 32;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t HW = (uint32_t)p.HW, W = (uint32_t)p.W;
+    const uint32_t ohow = (uint32_t)(p.OH * p.OW);
+    // shared memory: staging, HW vectors per warp | the warps' plane entries | tap offsets | component planes
+    float4* stage4 = flat_smem + (size_t)warp * HW;
+    PlaneEntry* tab = reinterpret_cast<PlaneEntry*>(flat_smem + (size_t)WARPS * HW) + warp * GPW * kFlatPlanes;
+    uint2* tap_tab = reinterpret_cast<uint2*>(flat_smem + (size_t)WARPS * HW + WARPS * GPW * kFlatPlanes);
+    uint32_t* comp_tab = reinterpret_cast<uint32_t*>(tap_tab + 32 * SLOTS);
+
+    const uint32_t w0 = (blockIdx.x * WARPS + warp) * GPW;                   // the warp's first group
+    float4 d[NV];
+    auto load_group = [&](uint32_t g) {
+        if (g >= groups) return;
+        const uint32_t q0 = g * kFlatPlanes;
+        const uint32_t img = p.div_c.div(q0);
+        const float4* x4 = reinterpret_cast<const float4*>(p.x + (long long)img * p.xbs + (long long)(q0 - img * (uint32_t)p.C) * HW);
+#pragma unroll
+        for (int r = 0; r < NV; ++r)
+            if (lane + 32u * r < HW) d[r] = x4[lane + 32u * r];
+    };
+    load_group(w0);                                        // before anything else
+    for (uint32_t o = threadIdx.x; o < 32u * SLOTS; o += kBlock) {
+        // pooled output o of a group: byte offsets of its four taps in the group's staging, two per word
+        const uint32_t oo = o < kFlatPlanes * ohow ? o : 0u;
+        const uint32_t pl = (oo >= ohow) + (oo >= 2 * ohow) + (oo >= 3 * ohow);
+        uint32_t oh, ow;
+        p.div_owv.divmod(oo - pl * ohow, oh, ow);                       // OWV == OW in this form
+        const uint32_t t00 = 4u * (pl * HW + 2u * oh * W + 2u * ow);
+        const uint32_t dx = 2 * ow + 1 < W ? 4u : 0u, dy = 2 * oh + 1 < (uint32_t)p.H ? 4u * W : 0u;
+        tap_tab[o] = make_uint2(t00 | ((t00 + dx) << 16), (t00 + dy) | ((t00 + dy + dx) << 16));
+    }
+    for (uint32_t i = threadIdx.x; i < 32u * NV; i += kBlock) {
+        // vector i of a group: 16 * (plane of component j) in byte j; HW > 3, so a vector meets one boundary at most
+        const uint32_t e = 4u * i;
+        const uint32_t lo = e < kFlatPlanes * HW ? (e >= HW) + (e >= 2 * HW) + (e >= 3 * HW) : 0u;
+        const uint32_t hi = e + 3 < kFlatPlanes * HW ? (e + 3 >= HW) + (e + 3 >= 2 * HW) + (e + 3 >= 3 * HW) : lo;
+        const uint32_t edge = hi * HW;
+        const uint32_t p1 = e + 1 >= edge ? hi : lo, p2 = e + 2 >= edge ? hi : lo;
+        comp_tab[i] = (lo | (p1 << 8) | (p2 << 16) | (hi << 24)) * (uint32_t)sizeof(PlaneEntry);
+    }
+    __syncthreads();
+    if (lane < GPW * kFlatPlanes && w0 * kFlatPlanes + lane < groups * kFlatPlanes)
+        tab[lane] = make_entry(p, w0 * kFlatPlanes + lane);
+    __syncwarp();
+
+    uint32_t straddles = 0;          // bit r: some lane's vector r crosses a plane boundary (the same for every lane)
+#pragma unroll
+    for (int r = 0; r < NV; ++r) {
+        const uint32_t w = comp_tab[lane + 32 * r];
+        if (__any_sync(0xffffffffu, (w >> 24) != (w & 0xFFu))) straddles |= 1u << r;
+    }
+    const uint32_t n_out = kFlatPlanes * ohow;
+    const char* stage_bytes = reinterpret_cast<const char*>(stage4);
+
+#pragma unroll 1
+    for (int k = 0; k < GPW; ++k) {
+        const uint32_t g = w0 + k;
+        if (g >= groups) break;
+        const uint32_t q0 = g * kFlatPlanes;
+        const uint32_t img = p.div_c.div(q0);
+        const uint32_t c0 = q0 - img * (uint32_t)p.C;
+        const char* tab_bytes = reinterpret_cast<const char*>(tab + k * kFlatPlanes);
+        auto entry = [&](uint32_t off) { return *reinterpret_cast<const PlaneEntry*>(tab_bytes + off); };
+        float4* y4 = p.y ? reinterpret_cast<float4*>(p.y + (long long)img * p.ybs + (long long)c0 * HW) : nullptr;
+#pragma unroll
+        for (int r = 0; r < NV; ++r) {
+            const uint32_t v = lane + 32u * r;
+            if (v >= HW) continue;
+            const uint32_t w = comp_tab[v];
+            const PlaneEntry t0 = entry(w & 0xFFu);
+            float4 o;
+            o.x = apply_one<ACT, AFFINE>(d[r].x, t0);
+            if (!(straddles & (1u << r))) {
+                o.y = apply_one<ACT, AFFINE>(d[r].y, t0);
+                o.z = apply_one<ACT, AFFINE>(d[r].z, t0);
+                o.w = apply_one<ACT, AFFINE>(d[r].w, t0);
+            } else {
+                o.y = apply_one<ACT, AFFINE>(d[r].y, entry((w >> 8) & 0xFFu));
+                o.z = apply_one<ACT, AFFINE>(d[r].z, entry((w >> 16) & 0xFFu));
+                o.w = apply_one<ACT, AFFINE>(d[r].w, entry(w >> 24));
+            }
+            stage4[v] = o;
+            if (y4) y4[v] = o;
+        }
+        if (k + 1 < GPW) load_group(g + 1);
+        __syncwarp();
+        float* yp = p.ypool + (long long)img * p.pbs + (long long)c0 * ohow + lane;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const uint2 t = tap_tab[lane + 32 * s];
+            float best = *reinterpret_cast<const float*>(stage_bytes + (t.x & 0xFFFFu));
+            best = pick(best, *reinterpret_cast<const float*>(stage_bytes + (t.x >> 16)));
+            best = pick(best, *reinterpret_cast<const float*>(stage_bytes + (t.y & 0xFFFFu)));
+            best = pick(best, *reinterpret_cast<const float*>(stage_bytes + (t.y >> 16)));
+            if (lane + 32u * s < n_out) yp[32 * s] = best;
+        }
+        __syncwarp();
+    }
+}
+
 // ------------------------------------------------------------------------------- launch helpers
 // Rounds of the per-thread loop one block runs (a round = one batch of loads per thread).  Measured
 // on B200: short blocks (2 rounds, 32 KB of input each for the streaming kernel) in many waves give
@@ -710,6 +845,18 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
     const int slots = ohow <= 64 ? 2 : 4;
     // measured on B200: ahead of the general form with two or four output slots per lane and at least 70 % of the
     // lane slots in use (13x13 -> 7x7, 19x19 -> 10x10); behind it with one slot (tiny planes) or eight (27x27, 31x31)
+    // ahead of the warp-per-plane form wherever it applies (9.5 against 11.1 us at [64,512,13,13] leaky, 10.9 against 13.7 mish)
+    if (vo == 0 && p.flat_ok && !general_only && p.HW > 32 && p.HW <= 32 * kFlatVectors && kFlatPlanes * ohow <= 32 * kFlatSlots) {
+        const uint32_t groups = p.units / per_plane / kFlatPlanes;
+        constexpr int per_block = kFlatWarps * kFlatGroups;
+        const unsigned blocks = (groups + per_block - 1) / per_block;
+        const size_t bytes = (size_t)kFlatWarps * (p.HW * sizeof(float4) + kFlatGroups * kFlatPlanes * sizeof(PlaneEntry))
+                             + 32 * kFlatSlots * sizeof(uint2) + 32 * kFlatVectors * sizeof(uint32_t);
+        epilogue_pool_flat_kernel<ACT, AFFINE, kFlatVectors, kFlatSlots, kFlatWarps, kFlatGroups>
+            <<<blocks, kFlatWarps * 32, bytes, s>>>(p, groups);
+        PXE_LAUNCH_OK("epilogue_pool_flat_kernel");
+        return PXE_OK;
+    }
     if (vo == 0 && ohow > 32 && ohow <= 128 && 10 * ohow >= 7 * 32 * (uint32_t)slots && !general_only) {
         const uint32_t n_planes = p.units / per_plane;
         const uint32_t pu = 8 / slots;
@@ -818,6 +965,7 @@ int run_slice(cudaStream_t s, const pxe_epilogue_desc& d, int b0, int nb, const 
         if (d.width % 8 == 0 && a16 && aligned16(p.ypool) && p.pbs % 4 == 0) vo = 4;
         else if (d.width % 4 == 0 && a16 && aligned8(p.ypool) && p.pbs % 2 == 0) vo = 2;
         else if (d.width % 2 == 0 && a8) vo = 1;
+        p.flat_ok = a16 && d.channels % kFlatPlanes == 0;
         const int nv = vo == 0 ? 1 : vo;
         p.units = (uint32_t)((long long)nb * d.channels * p.OH * (p.OW / nv));
         return dispatch(s, p, di, d.act, 0, n, affine, true, vo);

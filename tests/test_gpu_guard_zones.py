@@ -33,7 +33,7 @@ class Guarded:
 
 
 SHAPES = [(2, 3, 13, 13), (1, 5, 19, 19), (3, 2, 7, 5), (1, 1, 1, 1), (2, 7, 1, 3), (1, 2, 37, 31), (2, 4, 26, 26),
-          (1, 3, 52, 52), (2, 9, 3, 129)]
+          (1, 3, 52, 52), (2, 9, 3, 129), (2, 4, 13, 13), (3, 8, 11, 13), (1, 4, 7, 5)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)

@@ -63,7 +63,8 @@ def test_maxpool_ties_nan_and_signed_zero(cuda, oracle):
 
 
 @pytest.mark.parametrize("shape", [(2, 4, 16, 16), (2, 3, 13, 13), (1, 5, 26, 26), (2, 2, 52, 52), (1, 3, 8, 24),
-                                   (1, 2, 7, 12), (2, 37, 13, 13), (1, 10, 26, 26), (1, 2, 104, 104)])
+                                   (1, 2, 7, 12), (2, 37, 13, 13), (1, 10, 26, 26), (1, 2, 104, 104),
+                                   (2, 8, 13, 13), (3, 4, 13, 13), (2, 36, 13, 13), (1, 12, 11, 11), (2, 4, 9, 13), (1, 8, 7, 7)])
 @pytest.mark.parametrize("act", ["leaky", "mish", "swish", "logistic"])
 @pytest.mark.parametrize("keep_full", [False, True])
 @pytest.mark.parametrize("variant", [capi.POOL_AUTO, capi.POOL_GENERAL])
@@ -92,12 +93,14 @@ def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, variant)
 
 
 @pytest.mark.parametrize("shape", [(3, 5, 7, 7), (2, 37, 13, 13), (2, 9, 19, 19), (1, 11, 27, 27), (1, 3, 33, 33),
-                                   (1, 70, 5, 9), (2, 130, 13, 13), (1, 4, 3, 31)])
+                                   (1, 70, 5, 9), (2, 130, 13, 13), (1, 4, 3, 31), (2, 8, 13, 13), (1, 132, 13, 13),
+                                   (3, 4, 11, 13), (2, 12, 7, 7), (1, 8, 9, 5)])
 @pytest.mark.parametrize("act", ["leaky", "mish"])
 @pytest.mark.parametrize("padding", [0, 1])
 def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding):
     """Odd widths with 33 to 128 pooled outputs per plane (13x13, 19x19 here) run the warp-per-plane form (two or
-    four output slots per lane), the other shapes the general one; the former must equal the general scalar
+    four output slots per lane), planes of 33 to 192 elements in aligned tensors with channels in fours the flat
+    vector form, the other shapes the general one; the former two must equal the general scalar
     form bit for bit (pool_variant = PXE_POOL_GENERAL runs that one) and the oracle's separate layers, pooled-only and with the full-resolution output, dense and into channel
     slots of wider buffers, NaNs included."""
     B, C, H, W = shape
@@ -110,14 +113,14 @@ def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding):
     got = {}
     for env, variant in (("1", capi.POOL_AUTO), ("0", capi.POOL_GENERAL)):
         wide = torch.full((B, C + 3, oh, ow), 9.0, device=cuda)
-        wide_full = torch.full((B, C + 2, H, W), 7.0, device=cuda)
+        wide_full = torch.full((B, C + 4, H, W), 7.0, device=cuda)       # slot at four planes: 16-byte aligned
         _, yp = ops.conv_epilogue(dev(x, cuda), y=False, gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], act=act,
                                   pool=(2, 2, padding), pool_variant=variant)
         # the full-resolution output is offered only where the windows cover every input element
-        ops.conv_epilogue(dev(x, cuda), y=wide_full[:, 2:] if covered else False, gamma=dp[0], beta=dp[1], mean=dp[2],
+        ops.conv_epilogue(dev(x, cuda), y=wide_full[:, 4:] if covered else False, gamma=dp[0], beta=dp[1], mean=dp[2],
                           var=dp[3], act=act, pool=(2, 2, padding), y_pool=wide[:, 3:], pool_variant=variant)
-        assert bool((wide[:, :3] == 9.0).all()) and bool((wide_full[:, :2] == 7.0).all())
-        got[env] = (yp.cpu().numpy(), wide[:, 3:].cpu().numpy(), wide_full[:, 2:].cpu().numpy())
+        assert bool((wide[:, :3] == 9.0).all()) and bool((wide_full[:, :4] == 7.0).all())
+        got[env] = (yp.cpu().numpy(), wide[:, 3:].cpu().numpy(), wide_full[:, 4:].cpu().numpy())
     for a, c in zip(got["1"], got["0"]):
         same(a, c)
     yp, yp_slot, full = got["1"]
