@@ -13,7 +13,8 @@ through Runner.predict with a pinned HOST batch in and host detections out.  The
 by image across ranks; there is no collective on the data path.
 
 Other workloads (not run by default): --workload sweep (the isolated fused-epilogue sweep),
---workload centernet (the CenterNet head decode), --workload yolov3-tiny | yolov7.
+--workload centernet (the CenterNet head decode), --workload pools (SPP block and stand-alone max pools),
+--workload yolov3-tiny | yolov7.
 """
 from __future__ import annotations
 
@@ -932,6 +933,85 @@ def run_epilogue_compare(args):
                                  "plan": stats}}), flush=True)
 
 
+def run_pools(args):
+    """The stand-alone pooling kernels on the shapes the preset graphs run them on: the SPP block (with the conv
+    epilogue folded in, as YOLOv7's does, and on its own), the kernel-2 stride-1 pool of YOLOv3-tiny, single
+    stride-1 pools.  Buffers rotate past L2; CUDA events around a CUDA-graph replay of one launch per buffer set."""
+    import torch
+    from pixienn_b200 import ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak, peak_src = measured_peaks()
+    gen = torch.Generator(dev).manual_seed(SEED)
+
+    def graph_time(call, sets):
+        for i in range(max(args.warmup, sets)):
+            call(i)
+        torch.cuda.synchronize()
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            for i in range(sets):
+                call(i)
+        cg.replay()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        torch.cuda.synchronize()
+        for a, z in ev:
+            a.record(); cg.replay(); z.record()
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(z) / sets for a, z in ev)
+        return ts[len(ts) // 2]
+
+    cells = []
+
+    def record(kind, shape, ms, nbytes):
+        cells.append({"kernel": kind, "shape": list(shape), "MB": round(nbytes / 1e6, 1), "us_median": round(ms * 1e3, 2),
+                      "GBps": round(nbytes / ms / 1e6, 1), "frac_measured": round(nbytes / ms / 1e6 / peak, 3)})
+
+    def spp_case(B, C, H, W, fused, act="swish"):
+        n = B * C * H * W
+        sets = max(3, int(500e6 // (n * 20)) + 1)
+        xs = [torch.randn((B, C, H, W), device=dev, generator=gen) for _ in range(sets)]
+        cats = [torch.empty((B, 4 * C, H, W), device=dev) for _ in range(sets)]
+        a, b = torch.rand(C, device=dev, generator=gen) + 0.5, torch.randn(C, device=dev, generator=gen)
+
+        def call(i):
+            cat = cats[i % sets]
+            outs = [cat[:, 0:C], cat[:, C:2 * C], cat[:, 2 * C:3 * C]]
+            if fused:
+                ops.spp(xs[i % sets], [13, 9, 5], outs, a=a, b=b, act=act, y_identity=cat[:, 3 * C:])
+            else:
+                ops.spp(xs[i % sets], [13, 9, 5], outs)
+        record(f"spp 5/9/13{' + epilogue (' + act + ') + pass-through slot' if fused else ''}", (B, C, H, W),
+               graph_time(call, sets), n * 4 * (5 if fused else 4))
+
+    def maxpool_case(B, C, H, W, k, s):
+        n = B * C * H * W
+        sets = max(3, int(500e6 // (n * 8)) + 1)
+        xs = [torch.randn((B, C, H, W), device=dev, generator=gen) for _ in range(sets)]
+        oh, ow = ops.maxpool_out_dim(H, k, s, k - 1), ops.maxpool_out_dim(W, k, s, k - 1)
+        ys = [torch.empty((B, C, oh, ow), device=dev) for _ in range(sets)]
+        record(f"maxpool k{k}/s{s}", (B, C, H, W), graph_time(lambda i: ops.maxpool(xs[i % sets], k, s, out=ys[i % sets]), sets),
+               4 * n + 4 * B * C * oh * ow)
+
+    which = args.pool_cases.split(",")
+    if "spp" in which:
+        spp_case(16, 512, 20, 20, True)               # YOLOv7-640 at 16 images
+        spp_case(16, 512, 20, 20, False)
+        spp_case(64, 512, 19, 19, True, "leaky")      # YOLOv3-SPP / YOLOv4 at 608
+        spp_case(64, 512, 13, 13, False)
+    if "maxpool" in which:
+        maxpool_case(64, 512, 13, 13, 2, 1)           # YOLOv3-tiny-416, layer 11
+        maxpool_case(64, 512, 19, 19, 2, 1)           # the same at 608
+        maxpool_case(16, 512, 20, 20, 5, 1)
+        maxpool_case(64, 256, 26, 26, 3, 2)
+    fr = sorted(c["frac_measured"] for c in cells)
+    print(json.dumps({"metric": "stand-alone pooling kernels, HBM bandwidth", "value": cells[0]["GBps"], "unit": "GB/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "peak": peak, "peak_source": peak_src, "frac_min": fr[0], "frac_max": fr[-1],
+                      "config": {"workload": "SPP block and stand-alone max pools, NCHW", "l2": "rotating buffer sets > 400 MB",
+                                 "timing": "CUDA events around a CUDA-graph replay of one launch per buffer set"},
+                      "cells": cells}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -955,6 +1035,7 @@ def main():
     ap.add_argument("--sweep-pool", default="both", choices=["none", "pool", "both"])
     ap.add_argument("--sweep-residual", action="store_true", help="sweep the epilogue fused with a shortcut add")
     ap.add_argument("--model", default="yolov3-608", help="model graph for --workload epilogue-compare")
+    ap.add_argument("--pool-cases", default="spp,maxpool", help="kernel families for --workload pools")
     ap.add_argument("--nms-boxes", type=int, default=1000, help="candidate boxes per image for --workload nms")
     ap.add_argument("--no-cudnn-benchmark", action="store_true", help="skip cuDNN's algorithm search (profiling runs)")
     ap.add_argument("--layout", default="nchw", choices=["nchw", "nhwc"],
@@ -991,6 +1072,8 @@ def main():
         return run_nms(args)
     if args.workload == "epilogue-compare":
         return run_epilogue_compare(args)
+    if args.workload == "pools":
+        return run_pools(args)
     return run_model(args)
 
 

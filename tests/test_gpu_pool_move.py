@@ -182,6 +182,48 @@ def test_spp_block_nan_infinities_and_signed_zeros(cuda, oracle):
         assert np.array_equal(got[m], ref[m]) and np.array_equal(np.signbit(got[m]), np.signbit(ref[m]))
 
 
+@pytest.mark.parametrize("shape", [(3, 5, 20, 20), (2, 7, 19, 19), (1, 9, 13, 13), (1, 3, 24, 24), (2, 3, 7, 9), (1, 2, 33, 31),
+                                   (1, 2, 40, 40), (2, 3, 1, 1), (1, 4, 3, 50), (1, 130, 20, 20)])
+@pytest.mark.parametrize("kernels", [(5, 9, 13), (13, 9, 5), (5,), (9,), (13, 5), (9, 13), (3, 7), (5, 9, 13, 17)])
+def test_spp_any_subset_and_order_against_the_scan(cuda, oracle, shape, kernels):
+    """Planes that fit three copies per warp in shared memory run the chain of 5-wide row windows for any subset and order of
+    5 / 9 / 13 (dense aligned tensors with 128-bit moves, anything else element by element), other kernel sizes
+    and larger planes the row / column form: every output equals the reference scan bit for bit, into dense
+    tensors and into slots of a wider buffer whose other channels stay untouched."""
+    B, C, H, W = shape
+    x = synth.normal(40, f"sppany{shape}", shape)
+    x[np.abs(x) < 0.3] = 0.0                      # many ties
+    x[(x == 0) & (synth.normal(41, f"sppsign{shape}", shape) < 0)] = -0.0
+    xd = dev(x, cuda)
+    n = len(kernels)
+    outs = [torch.empty((B, C, H, W), device=cuda) for _ in range(n)]
+    ops.spp(xd, list(kernels), outs)
+    wide = torch.full((B, n * C + 1, H, W), 5.0, device=cuda)          # slots start one plane in: unaligned for odd planes
+    ops.spp(xd, list(kernels), [wide[:, 1 + i * C:1 + (i + 1) * C] for i in range(n)])
+    assert bool((wide[:, 0] == 5.0).all())
+    for i, k in enumerate(kernels):
+        ref = oracle.maxpool(x, k, 1)[0]
+        for got in (outs[i].cpu().numpy(), wide[:, 1 + i * C:1 + (i + 1) * C].cpu().numpy()):
+            assert np.array_equal(got, ref) and np.array_equal(np.signbit(got), np.signbit(ref)), (k,)
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 13, 13), (2, 4, 20, 20), (1, 6, 19, 19)])
+def test_spp_planes_with_nans_follow_the_scan(cuda, oracle, shape):
+    """A plane that holds a NaN leaves the chain of windows and is scanned window by window, as the reference does;
+    its neighbours in the same launch are not affected."""
+    B, C, H, W = shape
+    x = synth.normal(42, f"sppn{shape}", shape)
+    x[0, 0, 0, 0] = np.nan
+    x[0, 1, H // 2, W // 2] = np.nan
+    x[0, 2, :, 0] = np.nan
+    x[0, 3, H - 1, :] = np.nan
+    x[-1, -1, 2, 3] = -np.inf
+    outs = [torch.empty((B, C, H, W), device=cuda) for _ in range(3)]
+    ops.spp(dev(x, cuda), [5, 9, 13], outs)
+    for k, o in zip((5, 9, 13), outs):
+        same(o.cpu().numpy(), oracle.maxpool(x, k, 1)[0])
+
+
 @pytest.mark.parametrize("shape", [(2, 4, 16, 16), (2, 3, 13, 13), (1, 5, 38, 38), (2, 2, 19, 19), (1, 3, 5, 7)])
 @pytest.mark.parametrize("stride,scale", [(2, 1.0), (2, 0.5), (3, 1.0)])
 def test_upsample(cuda, oracle, shape, stride, scale):
