@@ -14,6 +14,7 @@ by image across ranks; there is no collective on the data path.
 
 Other workloads (not run by default): --workload sweep (the isolated fused-epilogue sweep),
 --workload centernet (the CenterNet head decode), --workload pools (SPP block and stand-alone max pools),
+--workload bn-train (batch normalisation with batch statistics, forward and backward),
 --workload yolov3-tiny | yolov7.
 """
 from __future__ import annotations
@@ -1012,6 +1013,87 @@ def run_pools(args):
                       "cells": cells}), flush=True)
 
 
+def run_bn_train(args):
+    """Batch normalisation in training mode on the shapes of the epilogue sweep: this library's forward (statistics +
+    one pass that writes the normalised tensor and the activated output) and backward, beside the sequence the
+    reference's CUDA conv layer runs around cuDNN (copy of the conv output, cudnnBatchNormalizationForwardTraining,
+    copy to preActivation_, activation in place: include/cuda/ConvLayer.h:284-307), here through PyTorch's cuDNN
+    batch norm.  Buffers rotate past L2; CUDA events around a CUDA-graph replay of one call per buffer set."""
+    import torch
+    import torch.nn.functional as F
+    from pixienn_b200 import ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak, peak_src = measured_peaks()
+    gen = torch.Generator(dev).manual_seed(SEED)
+    B = args.batch
+    shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
+    if args.sweep_shapes:
+        shapes = shapes[:args.sweep_shapes]
+    cells = []
+    for (Cc, H, W) in shapes:
+        n = B * Cc * H * W
+        sets = max(2, int(400e6 // (n * 4)) + 1)
+        xs = [torch.randn((B, Cc, H, W), device=dev, generator=gen) for _ in range(sets)]
+        dys = [torch.randn((B, Cc, H, W), device=dev, generator=gen) for _ in range(sets)]
+        g, b = torch.rand(Cc, device=dev, generator=gen) + 0.5, torch.randn(Cc, device=dev, generator=gen)
+        rm, rv = torch.zeros(Cc, device=dev), torch.ones(Cc, device=dev)
+        ys = [torch.empty_like(xs[0]) for _ in range(sets)]
+        saved = {}
+
+        def graph_time(call):
+            for i in range(max(args.warmup, sets)):
+                call(i)
+            torch.cuda.synchronize()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                for i in range(sets):
+                    call(i)
+            cg.replay()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+            torch.cuda.synchronize()
+            for a, z in ev:
+                a.record(); cg.replay(); z.record()
+            torch.cuda.synchronize()
+            ts = sorted(a.elapsed_time(z) / sets for a, z in ev)
+            return ts[len(ts) // 2]
+
+        def ours_fwd(i):
+            saved[i % sets] = ops.batchnorm_forward_training(xs[i % sets], g, b, running_mean=rm, running_var=rv, act="leaky",
+                                                            y=ys[i % sets])
+
+        def ours_bwd(i):
+            _, _, sm, ss = saved[i % sets]
+            ops.batchnorm_backward(xs[i % sets], dys[i % sets], g, sm, ss, dx=dys[i % sets])
+
+        def ref_seq(i):
+            x_saved = xs[i % sets].clone()                                       # x_.copy(output_)
+            y = F.batch_norm(x_saved, rm, rv, g, b, training=True, momentum=0.01, eps=1e-5)
+            pre = y.clone()                                                      # preActivation_.copy(output_)
+            F.leaky_relu(y, 0.1, inplace=True)
+            return pre
+
+        with torch.no_grad():
+            t_fwd, t_ref = graph_time(ours_fwd), graph_time(ref_seq)
+            t_bwd = graph_time(ours_bwd)
+        fwd_bytes, bwd_bytes = 16 * n, 20 * n
+        cells.append({"shape": [B, Cc, H, W], "forward_us": round(t_fwd * 1e3, 1), "forward_GBps": round(fwd_bytes / t_fwd / 1e6, 1),
+                      "forward_frac_measured": round(fwd_bytes / t_fwd / 1e6 / peak, 3),
+                      "cudnn_sequence_us": round(t_ref * 1e3, 1), "vs_cudnn_sequence": round(t_ref / t_fwd, 2),
+                      "backward_us": round(t_bwd * 1e3, 1), "backward_GBps": round(bwd_bytes / t_bwd / 1e6, 1),
+                      "backward_frac_measured": round(bwd_bytes / t_bwd / 1e6 / peak, 3)})
+        del xs, dys, ys, saved
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "batch-norm training forward, HBM bandwidth", "value": cells[0]["forward_GBps"], "unit": "GB/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f32",
+                      "data": "synthetic", "peak": peak, "peak_source": peak_src,
+                      "config": {"workload": f"batch norm with batch statistics, {B} images, NCHW; forward = statistics + y + leaky(y) "
+                                             "(16 B per element), backward = sums + dx (20 B per element); cudnn_sequence = copy, "
+                                             "cuDNN batch-norm training, copy, activation in place as the reference's conv layer does",
+                                 "l2": "rotating buffer sets > 400 MB",
+                                 "timing": "CUDA events around a CUDA-graph replay of one call per buffer set"},
+                      "cells": cells}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1074,6 +1156,8 @@ def main():
         return run_epilogue_compare(args)
     if args.workload == "pools":
         return run_pools(args)
+    if args.workload == "bn-train":
+        return run_bn_train(args)
     return run_model(args)
 
 

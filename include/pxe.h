@@ -547,6 +547,59 @@ PXE_API int pxe_centernet_loss(pxe_stream_t stream, const float* output, float* 
                                float* costs, int batch, int classes, int area, float normalizer, float focal_alpha,
                                float focal_beta, float size_weight);
 
+/* ------------------------------------------------------------------------------------------
+ * Batch normalisation in training mode.  Replaces cudnnBatchNormalizationForwardTraining
+ * (include/cuda/ConvLayer.h:285-292, include/cuda/BatchNormLayer.h:59-71, include/cuda/ConnLayer.h:198-203)
+ * together with the copies around it (x_.copy(output_), preActivation_.copy(output_) and the in-place activation,
+ * include/cuda/ConvLayer.h:286, 306-307), and cudnnBatchNormalizationBackward (include/cuda/ConvLayer.h:327-332,
+ * include/cuda/BatchNormLayer.h:108-118, include/cuda/ConnLayer.h:233-238).  CPU twins: batchNormForward /
+ * batchNormBackward, src/BatchNorm.cpp:24-98.  Tensors are dense NCHW; every sum is taken in a fixed order.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pxe_bn_train_desc {
+    const float* x;          /* [batch, channels, height, width]: the convolution output (the reference's x_) */
+    float* y;                /* gamma * xhat + beta (the reference's preActivation_); may be x itself */
+    float* y_act;            /* NULL, or act(y): the layer output; must not alias x or y */
+    int act;                 /* enum pxe_activation, evaluated with the precise math library */
+    int batch, channels, height, width;
+    const float* gamma;      /* [channels] scales */
+    const float* beta;       /* [channels] biases */
+    float* running_mean;     /* [channels] or NULL: (1 - f) * running + f * batch mean */
+    float* running_var;      /* [channels] or NULL: fed the unbiased variance (PXE_BN_EPS_CUDNN, as cuDNN does) or
+                                the population variance (PXE_BN_EPS_CPU, src/BatchNorm.cpp:55-56) */
+    float exp_avg_factor;    /* f: 0.01 in the reference */
+    float eps;               /* 1e-5 in the reference */
+    int eps_mode;            /* enum pxe_bn_eps_mode */
+    float* save_mean;        /* [channels] out: batch mean */
+    float* save_scale;       /* [channels] out: 1 / sqrt(var + eps), cuDNN's saved inverse variance (PXE_BN_EPS_CUDNN),
+                                or the population variance itself (PXE_BN_EPS_CPU: the reference's var) */
+    void* workspace;         /* pxe_batchnorm_workspace_bytes(batch, channels, height, width), 16-byte aligned */
+    size_t workspace_bytes;
+} pxe_bn_train_desc;
+
+typedef struct pxe_bn_backward_desc {
+    const float* x;          /* the x the forward call saw */
+    const float* dy;         /* gradient with respect to y (after px::gradient has been applied) */
+    float* dx;               /* gradient with respect to x; may be dy itself, must not be x */
+    int batch, channels, height, width;
+    const float* gamma;
+    float* dgamma;           /* [channels] or NULL: += sum of dy * xhat */
+    float* dbeta;            /* [channels] or NULL: += sum of dy */
+    const float* save_mean;  /* from the forward call, same eps_mode */
+    const float* save_scale;
+    float eps;
+    int eps_mode;
+    void* workspace;
+    size_t workspace_bytes;
+} pxe_bn_backward_desc;
+
+PXE_API size_t pxe_batchnorm_workspace_bytes(int batch, int channels, int height, int width);
+/* Three launches: per-channel sums, per-channel constants (and the running statistics), one pass that writes y and,
+ * if asked, act(y). */
+PXE_API int pxe_batchnorm_forward_training(pxe_stream_t stream, const pxe_bn_train_desc* desc);
+/* Three launches: per-channel sums of dy and dy * (x - mean), per-channel constants (and the parameter gradients),
+ * dx = k1 * dy + k2 * x + k3. */
+PXE_API int pxe_batchnorm_backward(pxe_stream_t stream, const pxe_bn_backward_desc* desc);
+
 #ifdef __cplusplus
 }
 #endif

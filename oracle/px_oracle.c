@@ -120,6 +120,80 @@ PXO_API void pxo_backward_bias(float* bias_updates, const float* delta, int batc
         }
 }
 
+/* Batch normalisation with batch statistics.
+ * eps_mode 1 follows batchNormForward(training = true), src/BatchNorm.cpp:44-67: meanCpu / varianceCpu
+ * (src/CpuUtil.cpp:248-280: population variance), rolling = 0.99 * rolling + 0.01 * batch value (:52-56, here with the
+ * factor as an argument), normalizeCpu (:282-293: (x - mean) / (sqrt(var) + eps)), scaleBias, addBias; save_scale
+ * receives the variance.  eps_mode 0 is cudnnBatchNormalizationForwardTraining in spatial mode as documented by
+ * cuDNN, which is what the CUDA layers call (include/cuda/ConvLayer.h:285-292): (x - mean) / sqrt(var + eps), the
+ * saved value is 1 / sqrt(var + eps), and the running variance is fed var * n / (n - 1).  Sums in double. */
+PXO_API void pxo_batchnorm_forward_training(const float* x, float* y, int batch, int channels, int spatial,
+                                            const float* gamma, const float* beta, float* running_mean,
+                                            float* running_var, float factor, float eps, int eps_mode,
+                                            float* save_mean, float* save_scale)
+{
+    const double n = (double)batch * spatial;
+    for (int c = 0; c < channels; ++c) {
+        double s = 0.0;
+        for (int b = 0; b < batch; ++b)
+            for (int k = 0; k < spatial; ++k) s += x[((size_t)b * channels + c) * spatial + k];
+        const float mean = (float)(s / n);
+        double v = 0.0;
+        for (int b = 0; b < batch; ++b)
+            for (int k = 0; k < spatial; ++k) {
+                const double d = (double)x[((size_t)b * channels + c) * spatial + k] - (double)mean;
+                v += d * d;
+            }
+        const float var = (float)(v / n);
+        float inv, fed;
+        if (eps_mode == 1) { inv = 1.0f / (sqrtf(var) + eps); fed = var; save_scale[c] = var; }
+        else { inv = 1.0f / sqrtf(var + eps); fed = n > 1.0 ? (float)(v / n * n / (n - 1.0)) : var; save_scale[c] = inv; }
+        save_mean[c] = mean;
+        if (running_mean) running_mean[c] = (1.0f - factor) * running_mean[c] + factor * mean;
+        if (running_var) running_var[c] = (1.0f - factor) * running_var[c] + factor * fed;
+        for (int b = 0; b < batch; ++b)
+            for (int k = 0; k < spatial; ++k) {
+                const size_t i = ((size_t)b * channels + c) * spatial + k;
+                y[i] = gamma[c] * ((x[i] - mean) * inv) + beta[c];
+            }
+    }
+}
+
+/* batchNormBackward, src/BatchNorm.cpp:68-98 (eps_mode 1): biasUpdates += sum delta; scaleUpdates += sum delta * xNorm
+ * with xNorm = (x - mean) / (sqrt(var) + eps); delta *= scale; meanDelta, varianceDelta, normalizeDelta of
+ * src/CpuUtil.cpp:303-343, which use 1 / sqrt(var + eps).  eps_mode 0 is cudnnBatchNormalizationBackward as documented
+ * by cuDNN (include/cuda/ConvLayer.h:327-332): the same sums with xhat = (x - mean) * saved inverse std,
+ * dx = gamma * invstd / n * (n * dy - sum dy - xhat * sum dy * xhat).  Sums in double. */
+PXO_API void pxo_batchnorm_backward(const float* x, const float* dy, float* dx, int batch, int channels, int spatial,
+                                    const float* gamma, float* dgamma, float* dbeta, const float* save_mean,
+                                    const float* save_scale, float eps, int eps_mode)
+{
+    const double n = (double)batch * spatial;
+    for (int c = 0; c < channels; ++c) {
+        const float mean = save_mean[c];
+        float inv_fwd, inv_bwd;
+        if (eps_mode == 1) { inv_fwd = 1.0f / (sqrtf(save_scale[c]) + eps); inv_bwd = 1.0f / sqrtf(save_scale[c] + eps); }
+        else inv_fwd = inv_bwd = save_scale[c];
+        double s1 = 0.0, s2 = 0.0;
+        for (int b = 0; b < batch; ++b)
+            for (int k = 0; k < spatial; ++k) {
+                const size_t i = ((size_t)b * channels + c) * spatial + k;
+                s1 += dy[i];
+                s2 += (double)dy[i] * ((double)x[i] - (double)mean);
+            }
+        if (dbeta) dbeta[c] += (float)s1;
+        if (dgamma) dgamma[c] += (float)(s2 * inv_fwd);
+        const double g = gamma[c];
+        const double mean_delta = -g * s1 * inv_bwd;
+        const double var_delta = -0.5 * g * s2 * (double)inv_bwd * inv_bwd * inv_bwd;
+        for (int b = 0; b < batch; ++b)
+            for (int k = 0; k < spatial; ++k) {
+                const size_t i = ((size_t)b * channels + c) * spatial + k;
+                dx[i] = (float)(g * dy[i] * inv_bwd + var_delta * 2.0 * ((double)x[i] - mean) / n + mean_delta / n);
+            }
+    }
+}
+
 /* MaxPoolLayer::backward, include/MaxPoolLayer.h:138-158. */
 PXO_API void pxo_maxpool_backward(const float* delta, const int* indexes, float* grad, size_t size)
 {

@@ -79,6 +79,9 @@ def lib():
         L.pxo_add_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.pxo_gradient.argtypes = [C.c_int, _f, C.c_size_t, _f]
         L.pxo_backward_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
+        L.pxo_batchnorm_forward_training.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, C.c_float, C.c_float,
+                                                     C.c_int, _f, _f]
+        L.pxo_batchnorm_backward.argtypes = [_f, _f, _f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, _f, C.c_float, C.c_int]
         L.pxo_maxpool_backward.argtypes = [_f, _i, _f, C.c_size_t]
         L.pxo_upsample_backward.argtypes = [_f, _f] + [C.c_int] * 5 + [C.c_float]
         L.pxo_constrain.argtypes = [_f, C.c_size_t, C.c_float]
@@ -150,6 +153,29 @@ def backward_bias(bias_updates, delta):
     B, n = d.shape[0], d.shape[1]
     lib().pxo_backward_bias(_fp(out), _fp(d), B, n, d.size // (B * n))
     return out
+
+
+def batchnorm_forward_training(x, gamma, beta, running_mean, running_var, factor=0.01, eps=1e-5, eps_mode=0):
+    """Returns (y, running_mean, running_var, save_mean, save_scale); see pxo_batchnorm_forward_training."""
+    x = _c(x)
+    B, Cc = x.shape[:2]
+    y = np.empty_like(x)
+    rm, rv = _c(running_mean).copy(), _c(running_var).copy()
+    sm, ss = np.empty(Cc, np.float32), np.empty(Cc, np.float32)
+    lib().pxo_batchnorm_forward_training(_fp(x), _fp(y), B, Cc, x.size // (B * Cc), _fp(_c(gamma)), _fp(_c(beta)), _fp(rm),
+                                         _fp(rv), C.c_float(factor), C.c_float(eps), eps_mode, _fp(sm), _fp(ss))
+    return y, rm, rv, sm, ss
+
+
+def batchnorm_backward(x, dy, gamma, save_mean, save_scale, dgamma, dbeta, eps=1e-5, eps_mode=0):
+    """Returns (dx, dgamma, dbeta); see pxo_batchnorm_backward."""
+    x, dy = _c(x), _c(dy)
+    B, Cc = x.shape[:2]
+    dx = np.empty_like(x)
+    dg, db = _c(dgamma).copy(), _c(dbeta).copy()
+    lib().pxo_batchnorm_backward(_fp(x), _fp(dy), _fp(dx), B, Cc, x.size // (B * Cc), _fp(_c(gamma)), _fp(dg), _fp(db),
+                                 _fp(_c(save_mean)), _fp(_c(save_scale)), C.c_float(eps), eps_mode)
+    return dx, dg, db
 
 
 def maxpool_backward(delta, indexes, grad):
@@ -445,6 +471,8 @@ class RefCpu:
         L.pxref_normalize.argtypes = [_f, _f, _f, C.c_int, C.c_int, C.c_int]
         L.pxref_batchnorm_inference.argtypes = [_f, _f, _f, _f, _f, C.c_int, C.c_int, C.c_int]
         L.pxref_batchnorm_forward_vec.argtypes = [_f, _f, _f, _f, _f] + [C.c_int] * 4
+        L.pxref_batchnorm_forward_training.argtypes = [_f] * 8 + [C.c_int] * 4
+        L.pxref_batchnorm_backward.argtypes = [_f] * 8 + [C.c_int] * 4
         L.pxref_softmax_one.argtypes = [_f, C.c_int, C.c_float, _f, C.c_int]
         L.pxref_softmax.argtypes = [_f] + [C.c_int] * 6 + [C.c_float, _f]
         L.pxref_sigmoid.restype = C.c_float
@@ -487,6 +515,26 @@ class RefCpu:
         y = _c(x).copy()
         self.L.pxref_constrain(y.size, C.c_float(alpha), _fp(y))
         return y
+
+    def batchnorm_forward_training(self, x, gamma, beta, rolling_mean, rolling_var):
+        """batchNormForward(training = true): returns (y, mean, var, rolling_mean, rolling_var, xnorm)."""
+        y = _c(x).copy()
+        B, Cc, H, W = y.shape
+        m, v = np.empty(Cc, np.float32), np.empty(Cc, np.float32)
+        rm, rv = _c(rolling_mean).copy(), _c(rolling_var).copy()
+        xn = np.empty_like(y)
+        self.L.pxref_batchnorm_forward_training(_fp(y), _fp(_c(gamma)), _fp(_c(beta)), _fp(m), _fp(v), _fp(rm), _fp(rv),
+                                                _fp(xn), B, Cc, H, W)
+        return y, m, v, rm, rv, xn
+
+    def batchnorm_backward(self, delta, x, xnorm, mean, var, gamma, scale_updates, bias_updates):
+        """batchNormBackward: returns (dx, scale_updates, bias_updates)."""
+        d = _c(delta).copy()
+        B, Cc, H, W = d.shape
+        su, bu = _c(scale_updates).copy(), _c(bias_updates).copy()
+        self.L.pxref_batchnorm_backward(_fp(d), _fp(_c(x)), _fp(_c(xnorm)), _fp(_c(mean)), _fp(_c(var)), _fp(_c(gamma)),
+                                        _fp(su), _fp(bu), B, Cc, H, W)
+        return d, su, bu
 
     def batchnorm_inference(self, x, gamma, beta, mean, var, via_vector=False):
         y = _c(x).copy()

@@ -109,6 +109,51 @@ API void pxref_batchnorm_forward_vec(float* x, const float* gamma, const float* 
     std::copy(io.begin(), io.end(), x);
 }
 
+/* batchNormForward(training = true), src/BatchNorm.cpp:24-67, through the PxCpuVector interface.  io: x in, y out;
+ * mean / var receive the batch statistics, rolling_mean / rolling_var are updated, xnorm receives the normalised
+ * tensor the backward pass wants. */
+API void pxref_batchnorm_forward_training(float* io, const float* gamma, const float* beta, float* mean, float* var,
+                                          float* rolling_mean, float* rolling_var, float* xnorm, int batch,
+                                          int channels, int height, int width)
+{
+    const std::size_t n = static_cast<std::size_t>(batch) * channels * height * width;
+    PxCpuVector v(n), m(channels), va(channels), rm(channels), rv(channels), s(channels), b(channels), xs(n), xn(n);
+    std::copy(io, io + n, v.begin());
+    std::copy(rolling_mean, rolling_mean + channels, rm.begin());
+    std::copy(rolling_var, rolling_var + channels, rv.begin());
+    std::copy(gamma, gamma + channels, s.begin());
+    std::copy(beta, beta + channels, b.begin());
+    batchNormForward(true, batch, channels, height, width, v, v, m, va, rm, rv, s, b, xs, xn);
+    std::copy(v.begin(), v.end(), io);
+    std::copy(m.begin(), m.end(), mean);
+    std::copy(va.begin(), va.end(), var);
+    std::copy(rm.begin(), rm.end(), rolling_mean);
+    std::copy(rv.begin(), rv.end(), rolling_var);
+    std::copy(xn.begin(), xn.end(), xnorm);
+}
+
+/* batchNormBackward, src/BatchNorm.cpp:68-98.  delta: dy in, dx out; scale_updates / bias_updates are added to. */
+API void pxref_batchnorm_backward(float* delta, const float* x, const float* xnorm, const float* mean, const float* var,
+                                  const float* gamma, float* scale_updates, float* bias_updates, int batch,
+                                  int channels, int height, int width)
+{
+    const std::size_t n = static_cast<std::size_t>(batch) * channels * height * width;
+    PxCpuVector d(n), m(channels), va(channels), md(channels), vd(channels), s(channels), su(channels), bu(channels),
+        xs(n), xn(n);
+    std::copy(delta, delta + n, d.begin());
+    std::copy(x, x + n, xs.begin());
+    std::copy(xnorm, xnorm + n, xn.begin());
+    std::copy(mean, mean + channels, m.begin());
+    std::copy(var, var + channels, va.begin());
+    std::copy(gamma, gamma + channels, s.begin());
+    std::copy(scale_updates, scale_updates + channels, su.begin());
+    std::copy(bias_updates, bias_updates + channels, bu.begin());
+    batchNormBackward(batch, channels, height, width, d, m, va, md, vd, s, su, bu, xs, xn);
+    std::copy(d.begin(), d.end(), delta);
+    std::copy(su.begin(), su.end(), scale_updates);
+    std::copy(bu.begin(), bu.end(), bias_updates);
+}
+
 /* softmax(const float*, int, float, float*, int), src/Math.cpp:77 */
 API void pxref_softmax_one(const float* in, int n, float temp, float* out, int stride)
 {

@@ -19,7 +19,7 @@ OBJDIR = os.path.join(LIBDIR, "obj")
 LIB = os.path.join(LIBDIR, "libpxe.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-CU_SOURCES = ["pxe_api.cu", "pxe_epilogue.cu", "pxe_pool.cu", "pxe_move.cu", "pxe_heads.cu", "pxe_compat.cu", "pxe_nms_gpu.cu", "pxe_nhwc.cu", "pxe_stem.cu", "pxe_backward.cu", "pxe_loss.cu"]
+CU_SOURCES = ["pxe_api.cu", "pxe_epilogue.cu", "pxe_pool.cu", "pxe_move.cu", "pxe_heads.cu", "pxe_compat.cu", "pxe_nms_gpu.cu", "pxe_nhwc.cu", "pxe_stem.cu", "pxe_backward.cu", "pxe_loss.cu", "pxe_bn_train.cu"]
 CXX_SOURCES = ["pxe_nms.cpp", "pxe_plan.cpp"]
 HEADERS = [os.path.join(CSRC, "pxe_common.cuh"), os.path.join(INCLUDE, "pxe.h"),
            os.path.join(INCLUDE, "pxe_compat.hpp"), os.path.join(INCLUDE, "pxe_plan.h")]

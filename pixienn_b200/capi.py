@@ -105,6 +105,25 @@ class YoloLossDesc(C.Structure):
                 ("object_scale", C.c_float), ("no_object_scale", C.c_float), ("class_scale", C.c_float)]
 
 
+class BnTrainDesc(C.Structure):
+    """pxe_bn_train_desc of include/pxe.h."""
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("y_act", C.c_void_p), ("act", C.c_int),
+                ("batch", C.c_int), ("channels", C.c_int), ("height", C.c_int), ("width", C.c_int),
+                ("gamma", C.c_void_p), ("beta", C.c_void_p), ("running_mean", C.c_void_p), ("running_var", C.c_void_p),
+                ("exp_avg_factor", C.c_float), ("eps", C.c_float), ("eps_mode", C.c_int),
+                ("save_mean", C.c_void_p), ("save_scale", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_size_t)]
+
+
+class BnBackwardDesc(C.Structure):
+    """pxe_bn_backward_desc of include/pxe.h."""
+    _fields_ = [("x", C.c_void_p), ("dy", C.c_void_p), ("dx", C.c_void_p),
+                ("batch", C.c_int), ("channels", C.c_int), ("height", C.c_int), ("width", C.c_int),
+                ("gamma", C.c_void_p), ("dgamma", C.c_void_p), ("dbeta", C.c_void_p),
+                ("save_mean", C.c_void_p), ("save_scale", C.c_void_p), ("eps", C.c_float), ("eps_mode", C.c_int),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 PLAN_MAX_SOURCES, PLAN_MAX_DESTS, PLAN_MAX_SPP = 16, 8, 4
 
 
@@ -185,6 +204,9 @@ PROTOTYPES = {
     "pxe_random_normal": (_i, [_vp, _vp, _sz, _f, _f]),
     "pxe_yolo_loss": (_i, [_vp, C.POINTER(YoloLossDesc)]),
     "pxe_centernet_loss": (_i, [_vp] + [_vp] * 7 + [_i] * 3 + [_f] * 4),
+    "pxe_batchnorm_workspace_bytes": (C.c_size_t, [_i] * 4),
+    "pxe_batchnorm_forward_training": (_i, [_vp, C.POINTER(BnTrainDesc)]),
+    "pxe_batchnorm_backward": (_i, [_vp, C.POINTER(BnBackwardDesc)]),
 }
 
 # the planner of include/pxe_plan.h (host code)

@@ -727,3 +727,64 @@ def conv_stem(x: torch.Tensor, weights: torch.Tensor, *, a: Optional[torch.Tenso
     d.batch, d.in_channels, d.out_channels, d.height, d.width, d.act = B, Cin, Cout, H, W, _act(act)
     capi.check(capi.lib().pxe_conv_stem(_stream(), C.byref(d)))
     return out
+
+
+def batchnorm_forward_training(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, *, running_mean=None,
+                               running_var=None, exp_avg_factor: float = 0.01, eps: float = 1e-5,
+                               eps_mode: int = capi.EPS_CUDNN, act=None, y: Optional[torch.Tensor] = None):
+    """Batch normalisation with batch statistics (cudnnBatchNormalizationForwardTraining as the reference's CUDA layers
+    call it, include/cuda/ConvLayer.h:285-292; CPU twin src/BatchNorm.cpp:44-60).  Returns ``(y, y_act, save_mean,
+    save_scale)``: the normalised tensor, its activation (``None`` without ``act``), the batch mean and
+    1 / sqrt(var + eps) (``EPS_CUDNN``) or the population variance (``EPS_CPU``).  The running statistics are updated
+    in place."""
+    _check_f32_cuda(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("batchnorm_forward_training: x must be dense NCHW")
+    B, Cc, H, W = x.shape
+    if y is None:
+        y = torch.empty_like(x)
+    y_act = torch.empty_like(x) if act is not None else None
+    save_mean = torch.empty(Cc, device=x.device, dtype=torch.float32)
+    save_scale = torch.empty(Cc, device=x.device, dtype=torch.float32)
+    nbytes = capi.lib().pxe_batchnorm_workspace_bytes(B, Cc, H, W)
+    ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
+    d = capi.BnTrainDesc()
+    d.x, d.y, d.y_act = x.data_ptr(), y.data_ptr(), (y_act.data_ptr() if y_act is not None else None)
+    d.act = _act(act if act is not None else "linear")
+    d.batch, d.channels, d.height, d.width = B, Cc, H, W
+    d.gamma, d.beta = _vec(gamma, Cc, "gamma"), _vec(beta, Cc, "beta")
+    d.running_mean = _vec(running_mean, Cc, "running_mean") if running_mean is not None else None
+    d.running_var = _vec(running_var, Cc, "running_var") if running_var is not None else None
+    d.exp_avg_factor, d.eps, d.eps_mode = exp_avg_factor, eps, eps_mode
+    d.save_mean, d.save_scale = save_mean.data_ptr(), save_scale.data_ptr()
+    d.workspace, d.workspace_bytes = ws.data_ptr(), nbytes
+    capi.check(capi.lib().pxe_batchnorm_forward_training(_stream(), C.byref(d)))
+    return y, y_act, save_mean, save_scale
+
+
+def batchnorm_backward(x: torch.Tensor, dy: torch.Tensor, gamma: torch.Tensor, save_mean: torch.Tensor,
+                       save_scale: torch.Tensor, *, dgamma: Optional[torch.Tensor] = None,
+                       dbeta: Optional[torch.Tensor] = None, eps: float = 1e-5, eps_mode: int = capi.EPS_CUDNN,
+                       dx: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """cudnnBatchNormalizationBackward as the reference's CUDA layers call it (include/cuda/ConvLayer.h:327-332; CPU twin
+    src/BatchNorm.cpp:68-98): returns dx; ``dgamma`` and ``dbeta`` are added to."""
+    _check_f32_cuda(x, "x")
+    _check_f32_cuda(dy, "dy")
+    if not (x.is_contiguous() and dy.is_contiguous()) or x.shape != dy.shape:
+        raise ValueError("batchnorm_backward: x and dy must be dense NCHW of one shape")
+    B, Cc, H, W = x.shape
+    if dx is None:
+        dx = torch.empty_like(x)
+    nbytes = capi.lib().pxe_batchnorm_workspace_bytes(B, Cc, H, W)
+    ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
+    d = capi.BnBackwardDesc()
+    d.x, d.dy, d.dx = x.data_ptr(), dy.data_ptr(), dx.data_ptr()
+    d.batch, d.channels, d.height, d.width = B, Cc, H, W
+    d.gamma = _vec(gamma, Cc, "gamma")
+    d.dgamma = _vec(dgamma, Cc, "dgamma") if dgamma is not None else None
+    d.dbeta = _vec(dbeta, Cc, "dbeta") if dbeta is not None else None
+    d.save_mean, d.save_scale = _vec(save_mean, Cc, "save_mean"), _vec(save_scale, Cc, "save_scale")
+    d.eps, d.eps_mode = eps, eps_mode
+    d.workspace, d.workspace_bytes = ws.data_ptr(), nbytes
+    capi.check(capi.lib().pxe_batchnorm_backward(_stream(), C.byref(d)))
+    return dx

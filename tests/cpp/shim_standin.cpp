@@ -22,6 +22,12 @@ namespace cv { struct Rect2f { float x, y, width, height; Rect2f(float a, float 
 #include "pxe_plan.h"
 static pxe_epilogue_desc g_last_epilogue;
 static int g_epilogues = 0, g_concats = 0;
+static pxe_bn_train_desc g_last_bn_train;
+static pxe_bn_backward_desc g_last_bn_backward;
+#define pxe_batchnorm_forward_training shim_test_bn_forward
+#define pxe_batchnorm_backward shim_test_bn_backward
+static int shim_test_bn_forward(pxe_stream_t, const pxe_bn_train_desc* d) { g_last_bn_train = *d; return PXE_OK; }
+static int shim_test_bn_backward(pxe_stream_t, const pxe_bn_backward_desc* d) { g_last_bn_backward = *d; return PXE_OK; }
 #define pxe_conv_epilogue shim_test_conv_epilogue
 #define pxe_concat shim_test_concat
 #define pxe_yolo_decode shim_test_yolo_decode
@@ -92,9 +98,19 @@ struct ConvLayer : Layer {
     {
 #include "shim/conv_forward_epilogue.inl"
     }
+    void forwardTraining()
+    {
+#include "shim/conv_forward_training.inl"
+    }
+    void backwardBatchNorm()
+    {
+#include "shim/conv_backward_batchnorm.inl"
+    }
     int filters_;
     bool batchNorm_;
     Vec<float> scales_, biases_, rollingMean_, rollingVar_;
+    Vec<float> x_, preActivation_, delta_, mean_, var_, scaleUpdates_, biasUpdates_;      // the training-side members
+    Vec<char> pxeBnWorkspace_;
 };
 
 struct RouteLayer : Layer {
@@ -178,6 +194,13 @@ int main()
          g_last_epilogue.y2 == nullptr && g_last_epilogue.bias == c3->biases_.data() && g_last_epilogue.gamma == nullptr;
     route->forwardBody();
     ok = ok && g_concats == 0;                         // every producer was redirected: the route runs nothing
+    // training: the batch-norm fragments hand over the saved input, the two outputs and the statistics' homes
+    c1->forwardTraining();
+    c1->backwardBatchNorm();
+    ok = ok && g_last_bn_train.x == c1->x_.data() && g_last_bn_train.y == c1->preActivation_.data() &&
+         g_last_bn_train.y_act == c1->output_.data() && g_last_bn_train.channels == C && g_last_bn_train.save_scale == c1->var_.data() &&
+         g_last_bn_backward.dx == c1->delta_.data() && g_last_bn_backward.dy == c1->delta_.data() &&
+         g_last_bn_backward.dgamma == c1->scaleUpdates_.data() && g_last_bn_backward.save_mean == c1->mean_.data();
     std::printf("%s: epilogues=%d concats=%d\n", ok ? "ok" : "MISMATCH", g_epilogues, g_concats);
     pxe_plan_destroy(m.plan_.plan);
     return ok ? 0 : 1;

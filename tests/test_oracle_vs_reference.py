@@ -79,6 +79,30 @@ def test_backward_bias_and_constrain_bit_identical(oracle, ref):
     assert np.array_equal(ref.constrain(x, 2.5), oracle.constrain(x, 2.5))
 
 
+@pytest.mark.parametrize("shape", [(3, 5, 7, 9), (1, 4, 13, 13), (6, 2, 1, 1), (2, 3, 16, 16)])
+def test_batchnorm_training_forward_and_backward_follow_the_reference(oracle, ref, shape):
+    """batchNormForward(training = true) and batchNormBackward of the reference's own compiled code against the
+    restatement in its CPU mode.  The reference adds in float, in index order (and through cblas_sdot); the
+    restatement adds in double: agreement is to float rounding of sums over batch * spatial terms, not bit for bit."""
+    B, C, H, W = shape
+    x = synth.normal(76, f"bnx{shape}", shape, 0.7, 2.0)
+    g, b, rm, rv = synth.bn_params(77, f"bnp{shape}", C)
+    y_ref, m_ref, v_ref, rm_ref, rv_ref, xn_ref = ref.batchnorm_forward_training(x, g, b, rm, rv)
+    y, rm2, rv2, sm, ss = oracle.batchnorm_forward_training(x, g, b, rm, rv, 0.01, 1e-5, 1)
+    np.testing.assert_allclose(sm, m_ref, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(ss, v_ref, rtol=1e-4, atol=1e-6)
+    np.testing.assert_allclose(rm2, rm_ref, rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(rv2, rv_ref, rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(y, y_ref, rtol=1e-4, atol=1e-5)
+    dy = synth.normal(78, f"bnd{shape}", shape, 0, 1.5)
+    su0, bu0 = synth.normal(79, "su", C), synth.normal(79, "bu", C)
+    dx_ref, su_ref, bu_ref = ref.batchnorm_backward(dy, x, xn_ref, m_ref, v_ref, g, su0, bu0)
+    dx, dg, db = oracle.batchnorm_backward(x, dy, g, m_ref, v_ref, su0, bu0, 1e-5, 1)
+    np.testing.assert_allclose(db, bu_ref, rtol=1e-5, atol=1e-4)
+    np.testing.assert_allclose(dg, su_ref, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(dx, dx_ref, rtol=1e-4, atol=2e-5)
+
+
 def test_launch_grid_of_the_compat_tier_equals_the_reference(oracle):
     """px::cudaGridsize of libpxe.so against the reference's (src/CudaUtils.cu:28-43), through the same glue built
     twice: over the reference's own sources and over libpxe.so.  Host code: no GPU is touched."""
