@@ -547,6 +547,15 @@ PXE_API int pxe_centernet_loss(pxe_stream_t stream, const float* output, float* 
                                float* costs, int batch, int classes, int area, float normalizer, float focal_alpha,
                                float focal_beta, float size_weight);
 
+/* px::adamGpu (include/Adam.cuh:21, src/Adam.cu:26-47): x[i] += rate * mhat / (sqrt(vhat) + eps) with
+ * mhat = m[i] / (1 - beta1^t), vhat = v[i] / (1 - beta2^t); t counts steps from 1. */
+PXE_API int pxe_adam_update(pxe_stream_t stream, size_t n, float* x, const float* m, const float* v, float beta1,
+                            float beta2, float rate, float eps, int t);
+/* px::softmaxCrossEntropy (include/SoftmaxKernel.cuh:21, src/SoftmaxKernel.cu:25-48):
+ * error[i] = truth[i] ? -log(pred[i] + 1e-9) : 0, delta[i] = truth[i] - pred[i]. */
+PXE_API int pxe_softmax_cross_entropy(pxe_stream_t stream, size_t n, const float* pred, const float* truth, float* delta,
+                                      float* error);
+
 /* ------------------------------------------------------------------------------------------
  * Batch normalisation in training mode.  Replaces cudnnBatchNormalizationForwardTraining
  * (include/cuda/ConvLayer.h:285-292, include/cuda/BatchNormLayer.h:59-71, include/cuda/ConnLayer.h:198-203)

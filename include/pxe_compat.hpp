@@ -82,5 +82,9 @@ void yoloLossGpu(const float* output, float* delta, const float* truths, const i
 void centerNetLossGpu(const float* output, float* delta, const float* targetHeatmap, const float* targetSize,
                       const float* targetOffset, const float* targetMask, float* costs, int batch, int classes, int area,
                       float normalizer, float focalAlpha, float focalBeta, float sizeWeight);
+/* include/Adam.cuh:21 */
+void adamGpu(int n, float* x, float* m, float* v, float beta1, float beta2, float rate, float eps, int t);
+/* include/SoftmaxKernel.cuh:21 */
+void softmaxCrossEntropy(int n, const float* pred, const float* truth, float* delta, float* error);
 
 }   // namespace px

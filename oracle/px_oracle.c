@@ -194,6 +194,25 @@ PXO_API void pxo_batchnorm_backward(const float* x, const float* dy, float* dx, 
     }
 }
 
+/* adamKernel, src/Adam.cu:26-38. */
+PXO_API void pxo_adam(size_t n, float* x, const float* m, const float* v, float beta1, float beta2, float rate, float eps, int t)
+{
+    const float c1 = 1.0f - powf(beta1, (float)t), c2 = 1.0f - powf(beta2, (float)t);
+    for (size_t i = 0; i < n; ++i) {
+        const float mhat = m[i] / c1, vhat = v[i] / c2;
+        x[i] += rate * mhat / (sqrtf(vhat) + eps);
+    }
+}
+
+/* softmaxCrossEntropyKernel, src/SoftmaxKernel.cu:25-39. */
+PXO_API void pxo_softmax_cross_entropy(size_t n, const float* pred, const float* truth, float* delta, float* error)
+{
+    for (size_t i = 0; i < n; ++i) {
+        error[i] = truth[i] ? -logf(pred[i] + 1e-9f) : 0.0f;
+        delta[i] = truth[i] - pred[i];
+    }
+}
+
 /* MaxPoolLayer::backward, include/MaxPoolLayer.h:138-158. */
 PXO_API void pxo_maxpool_backward(const float* delta, const int* indexes, float* grad, size_t size)
 {

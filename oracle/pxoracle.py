@@ -79,6 +79,8 @@ def lib():
         L.pxo_add_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.pxo_gradient.argtypes = [C.c_int, _f, C.c_size_t, _f]
         L.pxo_backward_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
+        L.pxo_adam.argtypes = [C.c_size_t, _f, _f, _f, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int]
+        L.pxo_softmax_cross_entropy.argtypes = [C.c_size_t, _f, _f, _f, _f]
         L.pxo_batchnorm_forward_training.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, C.c_float, C.c_float,
                                                      C.c_int, _f, _f]
         L.pxo_batchnorm_backward.argtypes = [_f, _f, _f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, _f, C.c_float, C.c_int]
@@ -176,6 +178,20 @@ def batchnorm_backward(x, dy, gamma, save_mean, save_scale, dgamma, dbeta, eps=1
     lib().pxo_batchnorm_backward(_fp(x), _fp(dy), _fp(dx), B, Cc, x.size // (B * Cc), _fp(_c(gamma)), _fp(dg), _fp(db),
                                  _fp(_c(save_mean)), _fp(_c(save_scale)), C.c_float(eps), eps_mode)
     return dx, dg, db
+
+
+def adam(x, m, v, beta1, beta2, rate, eps, t):
+    y = _c(x).copy()
+    lib().pxo_adam(y.size, _fp(y), _fp(_c(m)), _fp(_c(v)), C.c_float(beta1), C.c_float(beta2), C.c_float(rate), C.c_float(eps), t)
+    return y
+
+
+def softmax_cross_entropy(pred, truth):
+    """Returns (delta, error)."""
+    p, t = _c(pred), _c(truth)
+    delta, error = np.empty_like(p), np.empty_like(p)
+    lib().pxo_softmax_cross_entropy(p.size, _fp(p), _fp(t), _fp(delta), _fp(error))
+    return delta, error
 
 
 def maxpool_backward(delta, indexes, grad):
@@ -665,6 +681,7 @@ class RefCuda:
             "pxrefcu_upsample_backward": [i, i, i, i, i, f, vp, vp],
             "pxrefcu_constrain": [i, f, vp],
             "pxrefcu_mul": [i, vp, vp],
+            "pxrefcu_adam": [i, vp, vp, vp, f, f, f, f, i],
             "pxrefcu_random": [vp, sz, f, f],
             "pxrefcu_random_normal": [vp, sz, f, f],
             "pxrefcu_yolo_loss": [vp] * 12 + [i] * 9 + [f] * 6,

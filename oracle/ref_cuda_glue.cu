@@ -2,7 +2,7 @@
  * ref_cuda_glue.cu -- extern "C" doorway into the reference's own CUDA epilogue kernels.
  *
  * TEST / BASELINE INFRASTRUCTURE ONLY.  Compiled together with the reference's unmodified
- * src/{Activation,BiasKernels,MaxPoolKernels,UpsampleKernels,ShortcutKernel,YoloKernels,
+ * src/{Activation,Adam,BiasKernels,MaxPoolKernels,UpsampleKernels,ShortcutKernel,YoloKernels,
  * CenterNetKernels,CudaUtils}.cu (read in place from the reference tree, never copied) into
  * oracle/_ref/libpxref_cuda.so.  The forwarding functions let tests compare the new kernels with
  * the reference's kernels on the same device; the *_replay functions issue the exact call
@@ -13,6 +13,7 @@
 #include <cudnn.h>
 
 #include "Activation.cuh"
+#include "Adam.cuh"
 #include "BiasKernels.cuh"
 #include "CenterNetKernels.cuh"
 #include "CudaUtils.cuh"
@@ -109,6 +110,11 @@ API int pxrefcu_constrain(int n, float alpha, float* x)
 API int pxrefcu_mul(int n, float* x, float* y)
 {
     return guarded([&] { px::mulGpu(n, x, y); });
+}
+
+API int pxrefcu_adam(int n, float* x, float* m, float* v, float beta1, float beta2, float rate, float eps, int t)
+{
+    return guarded([&] { px::adamGpu(n, x, m, v, beta1, beta2, rate, eps, t); });
 }
 
 API int pxrefcu_random(float* p, std::size_t n, float a, float b)

@@ -204,6 +204,8 @@ PROTOTYPES = {
     "pxe_random_normal": (_i, [_vp, _vp, _sz, _f, _f]),
     "pxe_yolo_loss": (_i, [_vp, C.POINTER(YoloLossDesc)]),
     "pxe_centernet_loss": (_i, [_vp] + [_vp] * 7 + [_i] * 3 + [_f] * 4),
+    "pxe_adam_update": (_i, [_vp, C.c_size_t, _vp, _vp, _vp, _f, _f, _f, _f, _i]),
+    "pxe_softmax_cross_entropy": (_i, [_vp, C.c_size_t, _vp, _vp, _vp, _vp]),
     "pxe_batchnorm_workspace_bytes": (C.c_size_t, [_i] * 4),
     "pxe_batchnorm_forward_training": (_i, [_vp, C.POINTER(BnTrainDesc)]),
     "pxe_batchnorm_backward": (_i, [_vp, C.POINTER(BnBackwardDesc)]),
@@ -242,6 +244,8 @@ COMPAT_SYMBOLS = [
     "_ZN2px15randomNormalGpuEPfmff",
     "_ZN2px11yoloLossGpuEPKfPfS1_PKiiS4_S4_S1_S4_S1_S2_S2_iiiiiiiiffffff",
     "_ZN2px16centerNetLossGpuEPKfPfS1_S1_S1_S1_S2_iiiffff",
+    "_ZN2px7adamGpuEiPfS0_S0_ffffi",
+    "_ZN2px19softmaxCrossEntropyEiPKfS1_PfS2_",
 ]
 
 _lib = None

@@ -203,6 +203,35 @@ random_normal_kernel(float* out, size_t n, float mean, float stddev)
     }
 }
 
+// ---------------------------------------------------------------- Adam step, softmax cross-entropy
+// adamKernel (src/Adam.cu:26-38): x += rate * (m / (1 - beta1^t)) / (sqrt(v / (1 - beta2^t)) + eps), the same
+// expressions in the same order; every thread evaluates the two powers itself, as the reference's does.
+__global__ void __launch_bounds__(256)
+adam_kernel(float* __restrict__ x, const float* __restrict__ m, const float* __restrict__ v, size_t n, float beta1,
+            float beta2, float rate, float eps, int t)
+{
+    const float c1 = 1.0f - powf(beta1, t), c2 = 1.0f - powf(beta2, t);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float mhat = m[i] / c1;
+        const float vhat = v[i] / c2;
+        x[i] += rate * mhat / (sqrtf(vhat) + eps);
+    }
+}
+
+// softmaxCrossEntropyKernel (src/SoftmaxKernel.cu:25-39): error[i] = truth[i] ? -log(pred[i] + 1e-9) : 0,
+// delta[i] = truth[i] - pred[i].  (The reference has every thread loop over all n elements; the values are these.)
+__global__ void __launch_bounds__(256)
+softmax_cross_entropy_kernel(const float* __restrict__ pred, const float* __restrict__ truth, float* __restrict__ delta,
+                             float* __restrict__ error, size_t n)
+{
+    constexpr float epsilon = 1e-9f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float t = truth[i], p = pred[i];
+        error[i] = t ? -logf(p + epsilon) : 0.0f;
+        delta[i] = t - p;
+    }
+}
+
 }  // namespace
 }  // namespace pxe
 
@@ -311,5 +340,32 @@ extern "C" int pxe_random_normal(pxe_stream_t stream, float* out, size_t n, floa
     { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
     random_normal_kernel<<<grid_for((long long)n, 256, di.sm_count, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(out, n, mean, stddev);
     PXE_LAUNCH_OK("random_normal_kernel");
+    return PXE_OK;
+}
+
+extern "C" int pxe_adam_update(pxe_stream_t stream, size_t n, float* x, const float* m, const float* v, float beta1,
+                               float beta2, float rate, float eps, int t)
+{
+    if (n == 0) return PXE_OK;
+    PXE_REQUIRE(x && m && v, "adam_update: null pointer");
+    PXE_REQUIRE(t >= 1, "adam_update: step %d (the first step is 1)", t);
+    DeviceInfo di;
+    { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
+    adam_kernel<<<grid_for((long long)n, 256 * 4, di.sm_count, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, m, v, n, beta1, beta2,
+                                                                                                            rate, eps, t);
+    PXE_LAUNCH_OK("adam_kernel");
+    return PXE_OK;
+}
+
+extern "C" int pxe_softmax_cross_entropy(pxe_stream_t stream, size_t n, const float* pred, const float* truth, float* delta,
+                                         float* error)
+{
+    if (n == 0) return PXE_OK;
+    PXE_REQUIRE(pred && truth && delta && error, "softmax_cross_entropy: null pointer");
+    DeviceInfo di;
+    { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
+    softmax_cross_entropy_kernel<<<grid_for((long long)n, 256 * 4, di.sm_count, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        pred, truth, delta, error, n);
+    PXE_LAUNCH_OK("softmax_cross_entropy_kernel");
     return PXE_OK;
 }

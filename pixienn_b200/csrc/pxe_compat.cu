@@ -157,6 +157,18 @@ PXE_EXPORT void centerNetLossGpu(const float* output, float* delta, const float*
                              classes, area, normalizer, focalAlpha, focalBeta, sizeWeight), "centerNetLossGpu");
 }
 
+PXE_EXPORT void adamGpu(int n, float* x, float* m, float* v, float beta1, float beta2, float rate, float eps, int t)
+{
+    if (n < 0) throw std::runtime_error("adamGpu: negative size");
+    check(pxe_adam_update(nullptr, (std::size_t)n, x, m, v, beta1, beta2, rate, eps, t), "adamGpu");
+}
+
+PXE_EXPORT void softmaxCrossEntropy(int n, const float* pred, const float* truth, float* delta, float* error)
+{
+    if (n < 0) throw std::runtime_error("softmaxCrossEntropy: negative size");
+    check(pxe_softmax_cross_entropy(nullptr, (std::size_t)n, pred, truth, delta, error), "softmaxCrossEntropy");
+}
+
 // Launch grid for n threads in blocks of 512: one row of blocks up to 65535, a near-square arrangement beyond
 // (src/CudaUtils.cu:28-43).  The second dimension is what keeps launches of more than 33.5 M threads legal.
 PXE_EXPORT dim3 cudaGridsize(std::uint32_t n)

@@ -788,3 +788,26 @@ def batchnorm_backward(x: torch.Tensor, dy: torch.Tensor, gamma: torch.Tensor, s
     d.workspace, d.workspace_bytes = ws.data_ptr(), nbytes
     capi.check(capi.lib().pxe_batchnorm_backward(_stream(), C.byref(d)))
     return dx
+
+
+def adam_update(x: torch.Tensor, m: torch.Tensor, v: torch.Tensor, beta1: float, beta2: float, rate: float, eps: float,
+                t: int) -> torch.Tensor:
+    """px::adamGpu (src/Adam.cu:26-47): the parameter step from the moment estimates, in place on ``x``."""
+    for name, tns in (("x", x), ("m", m), ("v", v)):
+        _check_f32_cuda(tns, name)
+        if not tns.is_contiguous() or tns.numel() != x.numel():
+            raise ValueError("adam_update: x, m, v must be contiguous and of one size")
+    capi.check(capi.lib().pxe_adam_update(_stream(), x.numel(), x.data_ptr(), m.data_ptr(), v.data_ptr(), beta1, beta2, rate, eps, t))
+    return x
+
+
+def softmax_cross_entropy(pred: torch.Tensor, truth: torch.Tensor):
+    """px::softmaxCrossEntropy (src/SoftmaxKernel.cu:25-48): returns (delta, error)."""
+    _check_f32_cuda(pred, "pred")
+    _check_f32_cuda(truth, "truth")
+    if not (pred.is_contiguous() and truth.is_contiguous()) or pred.numel() != truth.numel():
+        raise ValueError("softmax_cross_entropy: pred and truth must be contiguous and of one size")
+    delta, error = torch.empty_like(pred), torch.empty_like(pred)
+    capi.check(capi.lib().pxe_softmax_cross_entropy(_stream(), pred.numel(), pred.data_ptr(), truth.data_ptr(), delta.data_ptr(),
+                                                    error.data_ptr()))
+    return delta, error

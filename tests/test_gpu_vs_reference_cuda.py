@@ -231,6 +231,40 @@ def test_constrain_mul_three_way(cuda, oracle, refcu):
     assert np.array_equal(my.cpu().numpy(), ty.cpu().numpy()) and np.array_equal(my.cpu().numpy(), x * y)
 
 
+@pytest.mark.parametrize("t", [1, 2, 10, 1000])
+def test_adam_step_three_way(cuda, oracle, refcu, t):
+    """px::adamGpu: bit-identical to the reference's kernel (same expressions, same device math library); the oracle's
+    host powf / sqrtf may differ in the last place."""
+    n = 100003
+    x, m = synth.normal(97, "ax", n, 0, 1), synth.normal(97, "am", n, 0, 0.1)
+    v = np.abs(synth.normal(97, "av", n, 0, 0.01)).astype(np.float32)
+    args = (0.9, 0.999, -1e-3, 1e-8, t)
+    mine = ops.adam_update(dev(x, cuda), dev(m, cuda), dev(v, cuda), *args)
+    theirs, dm, dv = dev(x, cuda), dev(m, cuda), dev(v, cuda)          # named: the pointers must outlive the call
+    refcu.call("adam", n, theirs.data_ptr(), dm.data_ptr(), dv.data_ptr(), *args)
+    torch.cuda.synchronize()
+    assert np.array_equal(mine.cpu().numpy(), theirs.cpu().numpy())
+    np.testing.assert_allclose(mine.cpu().numpy(), oracle.adam(x, m, v, *args), rtol=2e-6, atol=1e-7)
+
+
+def test_softmax_cross_entropy_equals_the_restatement(cuda, oracle):
+    """px::softmaxCrossEntropy.  The reference's src/SoftmaxKernel.cu cannot be compiled here (its header pulls in
+    OpenCV through GroundTruth.h), so this one is two-way: the kernel against the restatement of its two lines."""
+    n = 64 * 1000
+    logits = synth.normal(98, "sl", (64, 1000), 0, 3)
+    pred = np.exp(logits - logits.max(1, keepdims=True))
+    pred = (pred / pred.sum(1, keepdims=True)).astype(np.float32).ravel()
+    pred[:3] = [0.0, 1.0, 1e-12]
+    truth = np.zeros(n, np.float32)
+    truth[np.arange(64) * 1000 + (np.arange(64) * 37) % 1000] = 1.0
+    truth[:3] = 1.0
+    delta, error = ops.softmax_cross_entropy(dev(pred, cuda), dev(truth, cuda))
+    d_ref, e_ref = oracle.softmax_cross_entropy(pred, truth)
+    assert np.array_equal(delta.cpu().numpy(), d_ref)
+    np.testing.assert_allclose(error.cpu().numpy(), e_ref, rtol=1e-6, atol=1e-7)
+    assert float(error[0]) == pytest.approx(-np.log(np.float32(1e-9)), rel=1e-6) and float(error[1]) == 0.0
+
+
 def test_random_fills_follow_the_reference_engine(cuda, refcu):
     """Element i comes from the minimal-standard generator advanced i steps: uniform values equal the reference's
     (thrust) to the last bit or the one before; normal values have the requested moments and, value by value, sit
