@@ -518,6 +518,21 @@ def run_model(args):
         line["roofline"].update(centernet_ms=round(cn_ms, 4), centernet_batch=256,
                                 centernet_frac=round(4 * 256 * 20 * 128 * 128 / cn_ms / 1e6 / peak, 4),
                                 centernet_note="CenterNet head decode, [256,20,128,128] logits, K=100: heat-map bytes / time / peak")
+        torch.cuda.empty_cache()
+        try:
+            pc = pool_cells(sw_args, ["spp", "maxpool"], compact=True)
+            bc = bn_train_cells(sw_args, [(128, 52, 52)])[0]
+            line["roofline"].update(
+                spp_us=pc[0]["us_median"], spp_frac=pc[0]["frac_measured"], maxpool_k2s1_us=pc[1]["us_median"],
+                maxpool_k2s1_frac=pc[1]["frac_measured"],
+                pools_note="SPP 5/9/13 with its conv epilogue and pass-through slot on [16,512,20,20]; kernel-2 stride-1 pool on "
+                           "[64,512,13,13]: algorithmic bytes / time / peak",
+                bn_train_forward_frac=bc["forward_frac_measured"], bn_train_backward_frac=bc["backward_frac_measured"],
+                bn_train_vs_cudnn_sequence=bc["vs_cudnn_sequence"],
+                bn_train_note="batch norm with batch statistics on [64,128,52,52]: forward 16 B / element (statistics, y, "
+                              "leaky(y)), backward 20 B; cudnn_sequence = copy + cuDNN training batch norm + copy + activation")
+        except Exception as e:
+            line["roofline"]["pools_error"] = f"{type(e).__name__}: {str(e)[:160]}"
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(args, steps=1, warmup=0)
     print(json.dumps(line), flush=True)
@@ -934,7 +949,7 @@ def run_epilogue_compare(args):
                                  "plan": stats}}), flush=True)
 
 
-def run_pools(args):
+def pool_cells(args, which, compact=False):
     """The stand-alone pooling kernels on the shapes the preset graphs run them on: the SPP block (with the conv
     epilogue folded in, as YOLOv7's does, and on its own), the kernel-2 stride-1 pool of YOLOv3-tiny, single
     stride-1 pools.  Buffers rotate past L2; CUDA events around a CUDA-graph replay of one launch per buffer set."""
@@ -993,17 +1008,24 @@ def run_pools(args):
         record(f"maxpool k{k}/s{s}", (B, C, H, W), graph_time(lambda i: ops.maxpool(xs[i % sets], k, s, out=ys[i % sets]), sets),
                4 * n + 4 * B * C * oh * ow)
 
-    which = args.pool_cases.split(",")
     if "spp" in which:
         spp_case(16, 512, 20, 20, True)               # YOLOv7-640 at 16 images
-        spp_case(16, 512, 20, 20, False)
-        spp_case(64, 512, 19, 19, True, "leaky")      # YOLOv3-SPP / YOLOv4 at 608
-        spp_case(64, 512, 13, 13, False)
+        if not compact:
+            spp_case(16, 512, 20, 20, False)
+            spp_case(64, 512, 19, 19, True, "leaky")  # YOLOv3-SPP / YOLOv4 at 608
+            spp_case(64, 512, 13, 13, False)
     if "maxpool" in which:
         maxpool_case(64, 512, 13, 13, 2, 1)           # YOLOv3-tiny-416, layer 11
-        maxpool_case(64, 512, 19, 19, 2, 1)           # the same at 608
-        maxpool_case(16, 512, 20, 20, 5, 1)
-        maxpool_case(64, 256, 26, 26, 3, 2)
+        if not compact:
+            maxpool_case(64, 512, 19, 19, 2, 1)       # the same at 608
+            maxpool_case(16, 512, 20, 20, 5, 1)
+            maxpool_case(64, 256, 26, 26, 3, 2)
+    return cells
+
+
+def run_pools(args):
+    cells = pool_cells(args, args.pool_cases.split(","))
+    peak, peak_src = measured_peaks()
     fr = sorted(c["frac_measured"] for c in cells)
     print(json.dumps({"metric": "stand-alone pooling kernels, HBM bandwidth", "value": cells[0]["GBps"], "unit": "GB/s", "n_gpus": 1,
                       "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
@@ -1013,8 +1035,8 @@ def run_pools(args):
                       "cells": cells}), flush=True)
 
 
-def run_bn_train(args):
-    """Batch normalisation in training mode on the shapes of the epilogue sweep: this library's forward (statistics +
+def bn_train_cells(args, shapes):
+    """Batch normalisation in training mode on shapes of the epilogue sweep: this library's forward (statistics +
     one pass that writes the normalised tensor and the activated output) and backward, beside the sequence the
     reference's CUDA conv layer runs around cuDNN (copy of the conv output, cudnnBatchNormalizationForwardTraining,
     copy to preActivation_, activation in place: include/cuda/ConvLayer.h:284-307), here through PyTorch's cuDNN
@@ -1026,9 +1048,6 @@ def run_bn_train(args):
     peak, peak_src = measured_peaks()
     gen = torch.Generator(dev).manual_seed(SEED)
     B = args.batch
-    shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
-    if args.sweep_shapes:
-        shapes = shapes[:args.sweep_shapes]
     cells = []
     for (Cc, H, W) in shapes:
         n = B * Cc * H * W
@@ -1083,6 +1102,16 @@ def run_bn_train(args):
                       "backward_frac_measured": round(bwd_bytes / t_bwd / 1e6 / peak, 3)})
         del xs, dys, ys, saved
         torch.cuda.empty_cache()
+    return cells
+
+
+def run_bn_train(args):
+    shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
+    if args.sweep_shapes:
+        shapes = shapes[:args.sweep_shapes]
+    cells = bn_train_cells(args, shapes)
+    peak, peak_src = measured_peaks()
+    B = args.batch
     print(json.dumps({"metric": "batch-norm training forward, HBM bandwidth", "value": cells[0]["forward_GBps"], "unit": "GB/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f32",
                       "data": "synthetic", "peak": peak, "peak_source": peak_src,
