@@ -214,7 +214,7 @@ PXE_API int pxe_yolo_activate(pxe_stream_t stream, const float* in, float* out, 
                               int classes, int area);
 
 typedef struct pxe_yolo_decode_desc {
-    const float* head;          /* [batch, masks*(5+classes), height, width] */
+    const float* head;          /* [batch, masks*(5+classes), height, width] (or channels last, see below) */
     long long head_batch_stride;
     int head_is_raw;            /* 0: already activated (YoloLayer output_); 1: raw conv output,
                                    the decode applies `bias` and the head's logistic rule itself */
@@ -230,6 +230,8 @@ typedef struct pxe_yolo_decode_desc {
                                        include/YoloLayer.h:601-635); 0: normalised yoloBox().rect() */
     float threshold;
     int batch_id_offset;        /* added to batch_id (batch-sharded multi-GPU runs) */
+    int head_channels_last;     /* 1: `head` is [batch, height, width, masks*(5+classes)] (the channels-last tier's
+                                   conv output, no transposition first); same records in the same order */
 } pxe_yolo_decode_desc;
 
 /* Bytes of device workspace pxe_yolo_decode needs for this head (12 bytes per 32 cells per image). */

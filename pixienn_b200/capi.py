@@ -76,7 +76,7 @@ class YoloDecodeDesc(C.Structure):
         ("n_anchor_values", C.c_int), ("anchors", C.c_int * 64),
         ("net_width", C.c_int), ("net_height", C.c_int),
         ("image_width", C.c_int), ("image_height", C.c_int),
-        ("threshold", C.c_float), ("batch_id_offset", C.c_int),
+        ("threshold", C.c_float), ("batch_id_offset", C.c_int), ("head_channels_last", C.c_int),
     ]
 
 

@@ -26,7 +26,7 @@ constexpr int kYoloMaxWarps = 32;
 struct YoloParams {
     pxe_yolo_decode_desc d;
     long long hbs;
-    int HW, entries, blocks_per_image;
+    int HW, entries, channels, blocks_per_image;
     int chunks, chunk_len, warps;     // class chunks per mask slot, classes per chunk, warps per block
     pxe_detection* dets;
     long long capacity;
@@ -37,12 +37,18 @@ struct YoloParams {
                                // pass found at or above the threshold; NULL = the emit pass finds them again itself
 };
 
+// position of channel `ch` at `cell` within one image of the head: planes (the reference's layout) or channels last
+__device__ __forceinline__ long long yolo_at(const YoloParams& p, int ch, int cell)
+{
+    return p.d.head_channels_last ? (long long)cell * p.channels + ch : (long long)ch * p.HW + cell;
+}
+
 // value of entry `e` of mask slot `n` at `cell`, activated as YoloLayer::forward leaves it
 // (logistic on x, y, objectness, classes; w, h raw -- src/YoloKernels.cu:63-71)
 __device__ __forceinline__ float yolo_value(const YoloParams& p, const float* img, int n, int e, int cell)
 {
     const int ch = n * p.entries + e;
-    float v = img[(long long)ch * p.HW + cell];
+    float v = img[yolo_at(p, ch, cell)];
     if (p.d.head_is_raw) {
         if (p.d.bias) v += p.d.bias[ch];
         if (e < 2 || e >= 4) v = act_logistic(v);
@@ -79,7 +85,7 @@ __device__ __forceinline__ int yolo_chunk(const YoloParams& p, const float* img,
         const int cls = c0 + j;
         if (cls < cend) {
             const int ch = n * p.entries + 5 + cls;
-            float v = img[(long long)ch * p.HW + cell];
+            float v = img[yolo_at(p, ch, cell)];
             if (p.d.head_is_raw) {
                 if (p.d.bias) v += p.d.bias[ch];
                 if (v < skip_below) continue;
@@ -1581,6 +1587,7 @@ extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* 
     p.d = d;
     p.HW = d.height * d.width;
     p.entries = d.classes + 5;
+    p.channels = d.n_masks * p.entries;
     const long long chw = (long long)d.n_masks * p.entries * p.HW;
     PXE_REQUIRE(d.head_batch_stride == 0 || d.head_batch_stride >= chw, "yolo_decode: head_batch_stride too small");
     p.hbs = d.head_batch_stride ? d.head_batch_stride : chw;

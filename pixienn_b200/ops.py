@@ -296,10 +296,17 @@ class DetectionBuffer:
 def yolo_decode(head: torch.Tensor, mask, anchors, classes: int, net_w: int, net_h: int, threshold: float,
                 buf: DetectionBuffer, *, img_w: int = 0, img_h: int = 0, raw: bool = False,
                 bias: Optional[torch.Tensor] = None, batch_id_offset: int = 0) -> None:
-    """Appends one head's detections to ``buf`` in the reference's emission order."""
-    hp, hbs = _slot(head, "head")
+    """Appends one head's detections to ``buf`` in the reference's emission order.  ``head`` is [B, C, H, W], dense
+    NCHW (or a channel slot of a wider NCHW buffer) or dense channels-last; the latter is read where it lies."""
     B, Cc, H, W = head.shape
     d = capi.YoloDecodeDesc()
+    nhwc = (not head.is_contiguous()) and head.is_contiguous(memory_format=torch.channels_last) and Cc > 1 and H * W > 1
+    if nhwc:
+        _check_f32_cuda(head, "head")
+        hp, hbs = head.data_ptr(), Cc * H * W
+        d.head_channels_last = 1
+    else:
+        hp, hbs = _slot(head, "head")
     d.head, d.head_batch_stride = hp, hbs
     d.head_is_raw = int(raw)
     d.bias = _vec(bias, Cc, "bias")

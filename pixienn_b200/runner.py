@@ -644,7 +644,8 @@ class Runner:
 
     def _yolo(self, st: graph.Step, l: graph.Layer, T) -> None:
         xin = T[st.inputs[0]]
-        if self.nhwc:
+        if self.nhwc and not st.head_raw:
+            # YoloLayer's output() stays NCHW; the raw-head decode below reads the channels-last conv output where it lies
             s = self.timer.begin()
             xin = self._nchw(xin)
             self.timer.end(s, "head->nchw", 8 * xin.numel())

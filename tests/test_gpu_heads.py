@@ -66,6 +66,30 @@ def test_yolo_decode_order_and_values(cuda, oracle, B, classes, H, W, scaled):
         assert np.array_equal(got["prob"], ref["prob"])
 
 
+@pytest.mark.parametrize("B,classes,H,W", [(2, 4, 13, 13), (3, 80, 19, 19), (1, 3, 7, 31), (1, 365, 9, 9), (2, 17, 5, 40)])
+@pytest.mark.parametrize("raw_head", [False, True])
+def test_yolo_decode_reads_a_channels_last_head_where_it_lies(cuda, oracle, B, classes, H, W, raw_head):
+    """The same head stored channels-last ([B, H, W, C] in memory): the records are identical, bit for bit and in the
+    same order, to the decode of the NCHW copy -- the activated head and the raw one with its bias."""
+    mask, net = [3, 4, 5], (416, 416)
+    raw = yolo_case(44, B, classes, H, W)
+    bias = synth.normal(45, f"clb{classes}", raw.shape[1], 0, 0.3)
+    src = raw if raw_head else oracle.yolo_activate(raw, 3, classes)
+    nchw = dev(src, cuda)
+    nhwc = nchw.contiguous(memory_format=torch.channels_last)
+    assert not nhwc.is_contiguous() or H * W == 1
+    kw = dict(raw=True, bias=dev(bias, cuda)) if raw_head else {}
+    bufs = []
+    for head in (nchw, nhwc):
+        buf = ops.DetectionBuffer(1 << 18, cuda)
+        ops.yolo_decode(head, mask, YOLO_ANCHORS, classes, net[0], net[1], 0.2, buf, **kw)
+        bufs.append(buf.to_host())
+    (a, na), (b, nb) = bufs
+    assert na == nb and na > 0
+    for f in a.dtype.names:
+        assert np.array_equal(a[f], b[f]), f
+
+
 def test_yolo_decode_reference_1x1_case(cuda, oracle):
     """The reference's CPU-vs-CUDA decode test: 1x1 head, one anchor (1,1), threshold 0.1."""
     raw = np.array([0.2, -0.4, 0.1, -0.2, 2.0, 1.5], np.float32).reshape(1, 6, 1, 1)
