@@ -145,3 +145,41 @@ def test_decodes_stay_inside_their_record_buffers(cuda):
     heat, size, off = centernet_case(128, 3, 4, 37, 70)
     d, c = ops.centernet_decode(dev(heat, cuda), dev(size, cuda), dev(off, cuda), 0.2, 7, logits=True)
     assert int(c.max().item()) <= 7
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 13, 13), (4, 8, 13, 13), (2, 6, 16, 16), (64, 3, 1, 1), (1, 2, 95, 97)])
+def test_training_side_calls_stay_inside_their_outputs(cuda, shape):
+    """Batch norm with batch statistics (all outputs, both directions), the Adam step and the softmax loss."""
+    import ctypes as C
+    B, Cc, H, W = shape
+    x = dev(synth.normal(128, f"gt{shape}", shape, 0.5, 2.0), cuda)
+    g, b = torch.rand(Cc, device=cuda) + 0.5, torch.randn(Cc, device=cuda)
+    y, ya, dx = Guarded(shape, cuda, lead=1), Guarded(shape, cuda, lead=2), Guarded(shape, cuda, lead=3)
+    sm, ss, rm, rv, dg, db = (Guarded((Cc,), cuda, lead=1, fill=torch.ones(Cc, device=cuda)) for _ in range(6))
+    nbytes = capi.lib().pxe_batchnorm_workspace_bytes(B, Cc, H, W)
+    ws = torch.empty(nbytes + 4096, device=cuda, dtype=torch.uint8)
+    ws[nbytes:] = 0xA5
+    d = capi.BnTrainDesc()
+    d.x, d.y, d.y_act, d.act = x.data_ptr(), y.t.data_ptr(), ya.t.data_ptr(), capi.ACT["mish"]
+    d.batch, d.channels, d.height, d.width = shape
+    d.gamma, d.beta, d.running_mean, d.running_var = g.data_ptr(), b.data_ptr(), rm.t.data_ptr(), rv.t.data_ptr()
+    d.exp_avg_factor, d.eps, d.save_mean, d.save_scale = 0.01, 1e-5, sm.t.data_ptr(), ss.t.data_ptr()
+    d.workspace, d.workspace_bytes = ws.data_ptr(), nbytes
+    capi.check(capi.lib().pxe_batchnorm_forward_training(None, C.byref(d)))
+    e = capi.BnBackwardDesc()
+    dy = dev(synth.normal(129, f"gdy{shape}", shape), cuda)
+    e.x, e.dy, e.dx = x.data_ptr(), dy.data_ptr(), dx.t.data_ptr()
+    e.batch, e.channels, e.height, e.width = shape
+    e.gamma, e.dgamma, e.dbeta = g.data_ptr(), dg.t.data_ptr(), db.t.data_ptr()
+    e.save_mean, e.save_scale, e.eps = sm.t.data_ptr(), ss.t.data_ptr(), 1e-5
+    e.workspace, e.workspace_bytes = ws.data_ptr(), nbytes
+    capi.check(capi.lib().pxe_batchnorm_backward(None, C.byref(e)))
+    n = x.numel()
+    px, pm, pv = Guarded((n,), cuda, lead=1, fill=x.flatten()), torch.randn(n, device=cuda), torch.rand(n, device=cuda)
+    ops.adam_update(px.t, pm, pv, 0.9, 0.999, -1e-3, 1e-8, 3)
+    delta, err = Guarded((n,), cuda, lead=3), Guarded((n,), cuda, lead=1)
+    pred, truth = torch.rand(n, device=cuda), (torch.rand(n, device=cuda) > 0.9).float()
+    capi.check(capi.lib().pxe_softmax_cross_entropy(None, n, pred.data_ptr(), truth.data_ptr(), delta.t.data_ptr(), err.t.data_ptr()))
+    torch.cuda.synchronize()
+    assert all(t.intact() for t in (y, ya, dx, sm, ss, rm, rv, dg, db, px, delta, err))
+    assert bool((ws[nbytes:] == 0xA5).all())
