@@ -93,6 +93,45 @@ def test_maxpool_vs_reference_kernel(cuda, oracle, refcu, shape, k, s, pad):
     assert np.array_equal(idx.cpu().numpy(), ridx.cpu().numpy())
 
 
+@pytest.mark.parametrize("shape", [(16, 512, 20, 20), (8, 256, 19, 19), (8, 512, 13, 13)])
+def test_spp_block_at_model_size_equals_the_reference_kernel(cuda, refcu, shape):
+    """The SPP block of YOLOv7-640 at its configured 16 images per GPU (and the 19x19 / 13x13 planes of the 608 / 416
+    presets): every value of the three pools equals what the reference's own maxPoolForwardGpu writes, bit for bit,
+    with ties (a quarter of the values are zeros of both signs) and the -infinity planes included."""
+    B, C, H, W = shape
+    x = synth.normal(88, f"sppfull{shape}", shape)
+    x[np.abs(x) < 0.3] = 0.0
+    x[(x == 0) & (synth.normal(89, f"sppfs{shape}", shape) < 0)] = -0.0
+    x[0, 1] = -np.inf
+    xd = dev(x, cuda)
+    cat = torch.empty((B, 3 * C, H, W), device=cuda)
+    ops.spp(xd, [5, 9, 13], [cat[:, 0:C], cat[:, C:2 * C], cat[:, 2 * C:]])
+    ridx = torch.empty((B, C, H, W), device=cuda, dtype=torch.int32)
+    ref = torch.empty((B, C, H, W), device=cuda)
+    for i, k in enumerate((5, 9, 13)):
+        refcu.call("maxpool", xd.data_ptr(), ref.data_ptr(), ridx.data_ptr(), B, C, H, W, H, W, k, 1, k - 1)
+        torch.cuda.synchronize()
+        got = cat[:, i * C:(i + 1) * C]
+        assert torch.equal(got.contiguous().view(torch.int32), ref.view(torch.int32)), k      # bit patterns: -0 and +0 differ
+    # one pool alone goes through the same kernel
+    alone = ops.maxpool(xd, 13, 1)
+    assert torch.equal(alone.view(torch.int32), ref.view(torch.int32))
+
+
+def test_kernel2_stride1_pool_at_model_size_equals_the_reference_kernel(cuda, refcu):
+    """YOLOv3-tiny-416, layer 11 at 64 images: values and argmax planes, bit for bit."""
+    B, C, H, W = 64, 512, 13, 13
+    x = synth.normal(90, "k2s1full", (B, C, H, W))
+    x[np.abs(x) < 0.3] = 0.0
+    xd = dev(x, cuda)
+    mine, idx = ops.maxpool(xd, 2, 1, 1, with_indexes=True)
+    out, ridx = torch.empty_like(mine), torch.empty_like(idx)
+    refcu.call("maxpool", xd.data_ptr(), out.data_ptr(), ridx.data_ptr(), B, C, H, W, H, W, 2, 1, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(mine.view(torch.int32), out.view(torch.int32)) and torch.equal(idx, ridx)
+    assert torch.equal(ops.maxpool(xd, 2, 1, 1).view(torch.int32), out.view(torch.int32))
+
+
 def test_upsample_shortcut_heads_vs_reference_kernels(cuda, oracle, refcu):
     B, C, H, W = 2, 6, 13, 13
     x = synth.normal(87, "u", (B, C, H, W))
