@@ -183,3 +183,51 @@ def test_training_side_calls_stay_inside_their_outputs(cuda, shape):
     torch.cuda.synchronize()
     assert all(t.intact() for t in (y, ya, dx, sm, ss, rm, rv, dg, db, px, delta, err))
     assert bool((ws[nbytes:] == 0xA5).all())
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("lead", [0, 1, 2])
+def test_reads_outside_the_inputs_never_reach_the_outputs(cuda, shape, lead):
+    """The reading side of the same question: every input is carved out of a buffer whose surroundings hold NaNs (the
+    pattern above is one), at an offset that breaks 16-byte alignment, and the results must equal, bit for bit, those
+    computed from ordinary tensors.  A tap, a vector or a plane index that strays outside an input would drag a NaN
+    (or a neighbour's value) into some output."""
+    B, C, H, W = shape
+    xh = synth.normal(140, f"rx{shape}", shape)
+    rh = synth.normal(141, f"rr{shape}", shape)
+    _, dp = bn(142, f"rbn{shape}", C, cuda)
+    plain_x, plain_r = dev(xh, cuda), dev(rh, cuda)
+    gx, gr = Guarded(shape, cuda, lead=lead, fill=plain_x), Guarded(shape, cuda, lead=lead, fill=plain_r)
+
+    def both(fn):
+        a, b = fn(plain_x, plain_r), fn(gx.t, gr.t)
+        a, b = (a if isinstance(a, (list, tuple)) else [a]), (b if isinstance(b, (list, tuple)) else [b])
+        for u, v in zip(a, b):
+            if u is not None:
+                assert torch.equal(u.contiguous().view(torch.int32), v.contiguous().view(torch.int32))
+
+    kw = dict(gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3])
+    for act in ("leaky", "swish"):
+        both(lambda x, r: ops.conv_epilogue(x, y=torch.empty(shape, device=cuda), act=act, **kw))
+        both(lambda x, r: ops.conv_epilogue(x, y=torch.empty(shape, device=cuda), act=act, residual=r, res_act="leaky", **kw))
+        for pad in (0, 1):
+            oh, ow = ops.maxpool_out_dim(H, 2, 2, pad), ops.maxpool_out_dim(W, 2, 2, pad)
+            if oh > 0 and ow > 0:
+                for variant in (capi.POOL_AUTO, capi.POOL_GENERAL):
+                    both(lambda x, r: ops.conv_epilogue(x, y=False, act=act, pool=(2, 2, pad), pool_variant=variant, **kw)[1])
+    both(lambda x, r: ops.shortcut(x, r, 0.5, 2.0, "leaky", out=torch.empty(shape, device=cuda)))
+    both(lambda x, r: ops.upsample(x, 2, 0.5))
+    both(lambda x, r: ops.concat([x, r]))
+    both(lambda x, r: ops.avgpool(x))
+    for k, s_ in ((2, 1), (3, 2), (5, 1), (13, 1)):
+        if ops.maxpool_out_dim(H, k, s_, k - 1) > 0 and ops.maxpool_out_dim(W, k, s_, k - 1) > 0:
+            both(lambda x, r: list(ops.maxpool(x, k, s_, with_indexes=True)))
+            both(lambda x, r: ops.maxpool(x, k, s_))
+    both(lambda x, r: list(ops.spp(x, [5, 9, 13], [torch.empty(shape, device=cuda) for _ in range(3)])))
+    # batch-norm statistics are sums whose grouping depends on whether the input allows 128-bit loads: equal to rounding
+    # of the sums, and free of NaNs
+    a = ops.batchnorm_forward_training(plain_x, dp[0], dp[1], act="leaky")
+    b = ops.batchnorm_forward_training(gx.t.contiguous() if not gx.t.is_contiguous() else gx.t, dp[0], dp[1], act="leaky")
+    for u, v in zip(a, b):
+        torch.testing.assert_close(u, v, rtol=1e-5, atol=1e-6)
+    torch.cuda.synchronize()
