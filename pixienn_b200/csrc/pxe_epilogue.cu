@@ -631,13 +631,13 @@ epilogue_pool_smallplane_kernel(const EpiParams p, uint32_t planes, uint32_t pla
 // groups (1024 blocks, seven resident per SM: 56 groups on every SM) 9.5 / 10.9; 1, 3, 4 groups per warp and 2- or
 // 8-warp blocks are all behind.  A launch that only reads the tensor takes 5.1, an empty one 1.2.
 // ---------------------------------------------------------------------------------------------
-constexpr int kFlatPlanes = 4;
 constexpr int kFlatWarps = 4;             // warps per block
 constexpr int kFlatGroups = 2;            // groups per warp
 constexpr int kFlatVectors = 6;           // vectors per lane and group: planes of up to 192 elements
 constexpr int kFlatSlots = 7;             // pooled outputs per lane and group: up to 56 per plane
 
-template <int ACT, bool AFFINE, int NV, int SLOTS, int WARPS, int GPW>
+// G: planes per group (4 for planes of odd size: 4 * HW floats are whole vectors)
+template <int ACT, bool AFFINE, int G, int NV, int SLOTS, int WARPS, int GPW>
 __global__ void __launch_bounds__(WARPS * 32, 7)
 epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
 {
@@ -647,26 +647,27 @@ epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
     const uint32_t HW = (uint32_t)p.HW, W = (uint32_t)p.W;
     const uint32_t ohow = (uint32_t)(p.OH * p.OW);
     // shared memory: staging, HW vectors per warp | the warps' plane entries | tap offsets | component planes
-    float4* stage4 = flat_smem + (size_t)warp * HW;
-    PlaneEntry* tab = reinterpret_cast<PlaneEntry*>(flat_smem + (size_t)WARPS * HW) + warp * GPW * kFlatPlanes;
-    uint2* tap_tab = reinterpret_cast<uint2*>(flat_smem + (size_t)WARPS * HW + WARPS * GPW * kFlatPlanes);
+    const uint32_t V = (uint32_t)G * HW / 4;               // vectors per group
+    float4* stage4 = flat_smem + (size_t)warp * V;
+    PlaneEntry* tab = reinterpret_cast<PlaneEntry*>(flat_smem + (size_t)WARPS * V) + warp * GPW * G;
+    uint2* tap_tab = reinterpret_cast<uint2*>(flat_smem + (size_t)WARPS * V + WARPS * GPW * G);
     uint32_t* comp_tab = reinterpret_cast<uint32_t*>(tap_tab + 32 * SLOTS);
 
     const uint32_t w0 = (blockIdx.x * WARPS + warp) * GPW;                   // the warp's first group
     float4 d[NV];
     auto load_group = [&](uint32_t g) {
         if (g >= groups) return;
-        const uint32_t q0 = g * kFlatPlanes;
+        const uint32_t q0 = g * G;
         const uint32_t img = p.div_c.div(q0);
         const float4* x4 = reinterpret_cast<const float4*>(p.x + (long long)img * p.xbs + (long long)(q0 - img * (uint32_t)p.C) * HW);
 #pragma unroll
         for (int r = 0; r < NV; ++r)
-            if (lane + 32u * r < HW) d[r] = x4[lane + 32u * r];
+            if (lane + 32u * r < V) d[r] = x4[lane + 32u * r];
     };
     load_group(w0);                                        // before anything else
     for (uint32_t o = threadIdx.x; o < 32u * SLOTS; o += kBlock) {
         // pooled output o of a group: byte offsets of its four taps in the group's staging, two per word
-        const uint32_t oo = o < kFlatPlanes * ohow ? o : 0u;
+        const uint32_t oo = o < G * ohow ? o : 0u;
         const uint32_t pl = (oo >= ohow) + (oo >= 2 * ohow) + (oo >= 3 * ohow);
         uint32_t oh, ow;
         p.div_owv.divmod(oo - pl * ohow, oh, ow);                       // OWV == OW in this form
@@ -677,15 +678,15 @@ epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
     for (uint32_t i = threadIdx.x; i < 32u * NV; i += kBlock) {
         // vector i of a group: 16 * (plane of component j) in byte j; HW > 3, so a vector meets one boundary at most
         const uint32_t e = 4u * i;
-        const uint32_t lo = e < kFlatPlanes * HW ? (e >= HW) + (e >= 2 * HW) + (e >= 3 * HW) : 0u;
-        const uint32_t hi = e + 3 < kFlatPlanes * HW ? (e + 3 >= HW) + (e + 3 >= 2 * HW) + (e + 3 >= 3 * HW) : lo;
+        const uint32_t lo = e < G * HW ? (e >= HW) + (e >= 2 * HW) + (e >= 3 * HW) : 0u;
+        const uint32_t hi = e + 3 < G * HW ? (e + 3 >= HW) + (e + 3 >= 2 * HW) + (e + 3 >= 3 * HW) : lo;
         const uint32_t edge = hi * HW;
         const uint32_t p1 = e + 1 >= edge ? hi : lo, p2 = e + 2 >= edge ? hi : lo;
         comp_tab[i] = (lo | (p1 << 8) | (p2 << 16) | (hi << 24)) * (uint32_t)sizeof(PlaneEntry);
     }
     __syncthreads();
-    if (lane < GPW * kFlatPlanes && w0 * kFlatPlanes + lane < groups * kFlatPlanes)
-        tab[lane] = make_entry(p, w0 * kFlatPlanes + lane);
+    if (lane < GPW * G && w0 * G + lane < groups * G)
+        tab[lane] = make_entry(p, w0 * G + lane);
     __syncwarp();
 
     uint32_t straddles = 0;          // bit r: some lane's vector r crosses a plane boundary (the same for every lane)
@@ -694,23 +695,23 @@ epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
         const uint32_t w = comp_tab[lane + 32 * r];
         if (__any_sync(0xffffffffu, (w >> 24) != (w & 0xFFu))) straddles |= 1u << r;
     }
-    const uint32_t n_out = kFlatPlanes * ohow;
+    const uint32_t n_out = G * ohow;
     const char* stage_bytes = reinterpret_cast<const char*>(stage4);
 
 #pragma unroll 1
     for (int k = 0; k < GPW; ++k) {
         const uint32_t g = w0 + k;
         if (g >= groups) break;
-        const uint32_t q0 = g * kFlatPlanes;
+        const uint32_t q0 = g * G;
         const uint32_t img = p.div_c.div(q0);
         const uint32_t c0 = q0 - img * (uint32_t)p.C;
-        const char* tab_bytes = reinterpret_cast<const char*>(tab + k * kFlatPlanes);
+        const char* tab_bytes = reinterpret_cast<const char*>(tab + k * G);
         auto entry = [&](uint32_t off) { return *reinterpret_cast<const PlaneEntry*>(tab_bytes + off); };
         float4* y4 = p.y ? reinterpret_cast<float4*>(p.y + (long long)img * p.ybs + (long long)c0 * HW) : nullptr;
 #pragma unroll
         for (int r = 0; r < NV; ++r) {
             const uint32_t v = lane + 32u * r;
-            if (v >= HW) continue;
+            if (v >= V) continue;
             const uint32_t w = comp_tab[v];
             const PlaneEntry t0 = entry(w & 0xFFu);
             float4 o;
@@ -845,14 +846,18 @@ int launch_pool(cudaStream_t s, EpiParams& p, const DeviceInfo& di, int vo)
     const int slots = ohow <= 64 ? 2 : 4;
     // measured on B200: ahead of the general form with two or four output slots per lane and at least 70 % of the
     // lane slots in use (13x13 -> 7x7, 19x19 -> 10x10); behind it with one slot (tiny planes) or eight (27x27, 31x31)
-    // ahead of the warp-per-plane form wherever it applies (9.5 against 11.1 us at [64,512,13,13] leaky, 10.9 against 13.7 mish)
-    if (vo == 0 && p.flat_ok && !general_only && p.HW > 32 && p.HW <= 32 * kFlatVectors && kFlatPlanes * ohow <= 32 * kFlatSlots) {
-        const uint32_t groups = p.units / per_plane / kFlatPlanes;
+    // ahead of the warp-per-plane form wherever it applies (9.5 against 11.1 us at [64,512,13,13] leaky, 10.9 against 13.7 mish).
+    // Planes that are themselves whole vectors (26x26 = 169 of them) could run it with one plane per group; measured, that
+    // is behind the row-pair form there (15.6 against 13.5 us at [64,256,26,26] leaky), so only odd planes come here.
+    constexpr int flat_g = 4;
+    if (vo == 0 && p.HW % 2 != 0 && p.flat_ok && p.C % flat_g == 0 && !general_only && p.HW > 32
+        && p.HW <= 32 * kFlatVectors && (uint32_t)flat_g * ohow <= 32 * kFlatSlots) {
+        const uint32_t groups = p.units / per_plane / (uint32_t)flat_g;
         constexpr int per_block = kFlatWarps * kFlatGroups;
         const unsigned blocks = (groups + per_block - 1) / per_block;
-        const size_t bytes = (size_t)kFlatWarps * (p.HW * sizeof(float4) + kFlatGroups * kFlatPlanes * sizeof(PlaneEntry))
+        const size_t bytes = (size_t)kFlatWarps * ((size_t)flat_g * p.HW * sizeof(float) + kFlatGroups * flat_g * sizeof(PlaneEntry))
                              + 32 * kFlatSlots * sizeof(uint2) + 32 * kFlatVectors * sizeof(uint32_t);
-        epilogue_pool_flat_kernel<ACT, AFFINE, kFlatVectors, kFlatSlots, kFlatWarps, kFlatGroups>
+        epilogue_pool_flat_kernel<ACT, AFFINE, flat_g, kFlatVectors, kFlatSlots, kFlatWarps, kFlatGroups>
             <<<blocks, kFlatWarps * 32, bytes, s>>>(p, groups);
         PXE_LAUNCH_OK("epilogue_pool_flat_kernel");
         return PXE_OK;
@@ -965,7 +970,7 @@ int run_slice(cudaStream_t s, const pxe_epilogue_desc& d, int b0, int nb, const 
         if (d.width % 8 == 0 && a16 && aligned16(p.ypool) && p.pbs % 4 == 0) vo = 4;
         else if (d.width % 4 == 0 && a16 && aligned8(p.ypool) && p.pbs % 2 == 0) vo = 2;
         else if (d.width % 2 == 0 && a8) vo = 1;
-        p.flat_ok = a16 && d.channels % kFlatPlanes == 0;
+        p.flat_ok = a16;
         const int nv = vo == 0 ? 1 : vo;
         p.units = (uint32_t)((long long)nb * d.channels * p.OH * (p.OW / nv));
         return dispatch(s, p, di, d.act, 0, n, affine, true, vo);

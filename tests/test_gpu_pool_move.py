@@ -94,7 +94,7 @@ def test_epilogue_with_folded_pool(cuda, oracle, shape, act, keep_full, variant)
 
 @pytest.mark.parametrize("shape", [(3, 5, 7, 7), (2, 37, 13, 13), (2, 9, 19, 19), (1, 11, 27, 27), (1, 3, 33, 33),
                                    (1, 70, 5, 9), (2, 130, 13, 13), (1, 4, 3, 31), (2, 8, 13, 13), (1, 132, 13, 13),
-                                   (3, 4, 11, 13), (2, 12, 7, 7), (1, 8, 9, 5)])
+                                   (3, 4, 11, 13), (2, 12, 7, 7), (1, 8, 9, 5), (2, 5, 26, 26), (1, 3, 22, 22), (2, 2, 6, 10), (1, 7, 3, 12), (1, 4, 18, 14)])
 @pytest.mark.parametrize("act", ["leaky", "mish"])
 @pytest.mark.parametrize("padding", [0, 1])
 def test_folded_pool_small_odd_planes(cuda, oracle, shape, act, padding):
