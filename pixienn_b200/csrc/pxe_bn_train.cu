@@ -241,11 +241,12 @@ bn_forward_apply_kernel(const ApplyParams p)
             float4 in[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-                if (u0 + j * stride < p.units) in[j] = reinterpret_cast<const float4*>(p.x)[u0 + j * stride];
+                if (u0 + j * stride < p.units) in[j] = reinterpret_cast<const float4*>(p.x)[p.units - 1 - (u0 + j * stride)];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                const uint32_t u = u0 + j * stride;
-                if (u >= p.units) break;
+                if (u0 + j * stride >= p.units) break;
+                // back to front: the statistics pass went front to back, so the end of x is what L2 still holds
+                const uint32_t u = p.units - 1 - (u0 + j * stride);
                 const uint32_t e = 4u * u;
                 const uint32_t plane = p.div_hw.div(e);
                 const uint32_t c = plane - p.div_c.div(plane) * p.div_c.d;
@@ -283,7 +284,8 @@ template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 bn_backward_apply_kernel(const ApplyParams p)
 {
-    for (uint32_t u = blockIdx.x * kThreads + threadIdx.x; u < p.units; u += gridDim.x * kThreads) {
+    for (uint32_t uf = blockIdx.x * kThreads + threadIdx.x; uf < p.units; uf += gridDim.x * kThreads) {
+        const uint32_t u = p.units - 1 - uf;           // back to front, as in the forward pass
         if (VEC) {
             const uint32_t e = 4u * u;
             const uint32_t plane = p.div_hw.div(e);
