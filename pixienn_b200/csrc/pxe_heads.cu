@@ -27,6 +27,7 @@ struct YoloParams {
     pxe_yolo_decode_desc d;
     long long hbs;
     int HW, entries, channels, blocks_per_image;
+    int groups_per_block;      // consecutive groups of 32 cells one block works through
     int chunks, chunk_len, warps;     // class chunks per mask slot, classes per chunk, warps per block
     pxe_detection* dets;
     long long capacity;
@@ -102,32 +103,31 @@ __device__ __forceinline__ int yolo_chunk(const YoloParams& p, const float* img,
     return cnt;
 }
 
+// A block takes `groups_per_block` consecutive groups of 32 cells of one image (a launch of one block per group spends
+// most of a trained head's decode on starting blocks).  Sums, masks and offsets stay per group.
 __global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
 yolo_count_kernel(const YoloParams p)
 {
-    __shared__ int warp_sums[kYoloMaxWarps];
     const int b = blockIdx.y;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int cell = blockIdx.x * kYoloCells + lane;
     const float* img = p.d.head + (long long)b * p.hbs;
-    int cnt = 0;
-    unsigned mask = 0;
-    if (cell < p.HW) {
-        float prob[kYoloChunk], obj;
-        cnt = yolo_chunk(p, img, w / p.chunks, w % p.chunks, cell, prob, &obj);
-        if (cnt > 0) {                                 // prob[] is only filled when the slot's objectness passed
+    const int g_end = min((int)(blockIdx.x + 1) * p.groups_per_block, p.blocks_per_image);
+    for (int grp = blockIdx.x * p.groups_per_block; grp < g_end; ++grp) {
+        const int cell = grp * kYoloCells + lane;
+        int cnt = 0;
+        unsigned mask = 0;
+        if (cell < p.HW) {
+            float prob[kYoloChunk], obj;
+            cnt = yolo_chunk(p, img, w / p.chunks, w % p.chunks, cell, prob, &obj);
+            if (cnt > 0) {                             // prob[] is only filled when the slot's objectness passed
 #pragma unroll
-            for (int j = 0; j < kYoloChunk; ++j) mask |= prob[j] >= 0.0f ? 1u << j : 0u;
+                for (int j = 0; j < kYoloChunk; ++j) mask |= prob[j] >= 0.0f ? 1u << j : 0u;
+            }
         }
-    }
-    if (p.masks) p.masks[((size_t)b * p.blocks_per_image + blockIdx.x) * blockDim.x + threadIdx.x] = (unsigned short)mask;
-    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
-    if (lane == 0) warp_sums[w] = cnt;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int total = 0;
-        for (int i = 0; i < p.warps; ++i) total += warp_sums[i];
-        p.block_sums[b * p.blocks_per_image + blockIdx.x] = total;
+        if (p.masks) p.masks[((size_t)b * p.blocks_per_image + grp) * blockDim.x + threadIdx.x] = (unsigned short)mask;
+        // the group's total is an integer: each warp adds its share to the (zeroed) sum, and no warp waits for another
+        for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
+        if (lane == 0 && cnt != 0) atomicAdd(&p.block_sums[b * p.blocks_per_image + grp], cnt);
     }
 }
 
@@ -185,54 +185,17 @@ __device__ __forceinline__ int f2i_x86(float v)
     return (int)v;
 }
 
-__global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
-yolo_emit_kernel(const YoloParams p)
+// the records of one thread: box of (cell, mask slot n) and one record per class of its chunk that reached the threshold
+__device__ __forceinline__ void yolo_write_records(const YoloParams& p, const float* img, int b, int cell, int n, int chunk,
+                                                   unsigned mask, float (&prob)[kYoloChunk], float obj, long long pos)
 {
-    __shared__ int ranked[kYoloCells * (kYoloMaxWarps + 1)];   // counts, then exclusive prefixes, in emission order
-    __shared__ int warp_tot[kYoloMaxWarps];
-    const int b = blockIdx.y;
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int cell = blockIdx.x * kYoloCells + lane;
-    const float* img = p.d.head + (long long)b * p.hbs;
-    const int n = w / p.chunks, chunk = w % p.chunks;
-    float prob[kYoloChunk], obj = 0.0f;
-    int cnt = 0;
     if (p.masks) {
-        // the count pass left the classes that reach the threshold: one activation per emitted value, none at all
-        // for the threads (most of them, on a trained head) that emit nothing
-        const unsigned mask = p.masks[((size_t)b * p.blocks_per_image + blockIdx.x) * blockDim.x + threadIdx.x];
-        cnt = __popc(mask);
-        if (cnt) {
-            obj = yolo_value(p, img, n, 4, cell);
-            const int c0 = chunk * p.chunk_len;
+        obj = yolo_value(p, img, n, 4, cell);
+        const int c0m = chunk * p.chunk_len;
 #pragma unroll
-            for (int j = 0; j < kYoloChunk; ++j)
-                prob[j] = (mask >> j) & 1u ? obj * yolo_value(p, img, n, 5 + c0 + j, cell) : -1.0f;
-        }
-    } else if (cell < p.HW) {
-        cnt = yolo_chunk(p, img, n, chunk, cell, prob, &obj);
+        for (int j = 0; j < kYoloChunk; ++j)
+            prob[j] = (mask >> j) & 1u ? obj * yolo_value(p, img, n, 5 + c0m + j, cell) : -1.0f;
     }
-    // exclusive scan over the block in emission order: rank = lane * warps + w
-    const int nthreads = kYoloCells * p.warps;
-    ranked[lane * p.warps + w] = cnt;
-    __syncthreads();
-    {
-        const int v = ranked[threadIdx.x];            // thread t now owns rank t
-        int inc = v;
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, inc, o);
-            if (lane >= o) inc += t;
-        }
-        if (lane == 31) warp_tot[w] = inc;
-        __syncthreads();
-        int before = 0;
-        for (int i = 0; i < w; ++i) before += warp_tot[i];
-        ranked[threadIdx.x] = before + inc - v;
-        (void)nthreads;
-    }
-    __syncthreads();
-    if (cnt == 0) return;
-    long long pos = p.block_offsets[b * p.blocks_per_image + blockIdx.x] + ranked[lane * p.warps + w];
 
     const int W = p.d.width, H = p.d.height;
     const int row = cell / W, col = cell - row * W;
@@ -288,6 +251,56 @@ yolo_emit_kernel(const YoloParams p)
                 store_detection(p.dets + pos, bx, by, bw, bh, pr, cls, b + p.d.batch_id_offset, cell * p.d.n_masks + n);
             ++pos;
         }
+    }
+}
+
+__global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
+yolo_emit_kernel(const YoloParams p)
+{
+    __shared__ int ranked[kYoloCells * (kYoloMaxWarps + 1)];   // counts, then exclusive prefixes, in emission order
+    __shared__ int warp_tot[kYoloMaxWarps];
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const float* img = p.d.head + (long long)b * p.hbs;
+    const int n = w / p.chunks, chunk = w % p.chunks;
+    const int g_end = min((int)(blockIdx.x + 1) * p.groups_per_block, p.blocks_per_image);
+    for (int grp = blockIdx.x * p.groups_per_block; grp < g_end; ++grp) {
+        // nothing to write in this group (most groups of a trained head): the same answer for every thread of the block
+        if (p.block_sums[b * p.blocks_per_image + grp] == 0) continue;
+        const int cell = grp * kYoloCells + lane;
+        float prob[kYoloChunk], obj = 0.0f;
+        int cnt = 0;
+        unsigned mask = 0;
+        if (p.masks) {
+            // the count pass left the classes that reach the threshold: one activation per emitted value, none at all for
+            // the threads that emit nothing; the values are loaded after the scan below, so no barrier waits for them
+            mask = p.masks[((size_t)b * p.blocks_per_image + grp) * blockDim.x + threadIdx.x];
+            cnt = __popc(mask);
+        } else if (cell < p.HW) {
+            cnt = yolo_chunk(p, img, n, chunk, cell, prob, &obj);
+        }
+        // exclusive scan over the block in emission order: rank = lane * warps + w
+        ranked[lane * p.warps + w] = cnt;
+        __syncthreads();
+        {
+            const int v = ranked[threadIdx.x];            // thread t now owns rank t
+            int inc = v;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            if (lane == 31) warp_tot[w] = inc;
+            __syncthreads();
+            int before = 0;
+            for (int i = 0; i < w; ++i) before += warp_tot[i];
+            ranked[threadIdx.x] = before + inc - v;
+        }
+        __syncthreads();
+        if (cnt != 0) {
+            const long long pos = p.block_offsets[b * p.blocks_per_image + grp] + ranked[lane * p.warps + w];
+            yolo_write_records(p, img, b, cell, n, chunk, mask, prob, obj, pos);
+        }
+        __syncthreads();                                  // ranked / warp_tot are reused by the next group
     }
 }
 
@@ -1611,8 +1624,15 @@ extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* 
         p.masks = reinterpret_cast<unsigned short*>(ws);
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid((unsigned)p.blocks_per_image, (unsigned)d.batch);
+    DeviceInfo di;
+    { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
+    // enough blocks to fill the machine sixteen times over, each working through up to eight groups of 32 cells
+    const long long groups_total = (long long)p.blocks_per_image * d.batch;
+    long long gpb = (groups_total + (long long)di.sm_count * 16 - 1) / ((long long)di.sm_count * 16);
+    p.groups_per_block = (int)(gpb < 1 ? 1 : (gpb > 8 ? 8 : gpb));
+    dim3 grid((unsigned)((p.blocks_per_image + p.groups_per_block - 1) / p.groups_per_block), (unsigned)d.batch);
     const unsigned threads = (unsigned)(kYoloCells * p.warps);
+    PXE_CUDA_OK(cudaMemsetAsync(p.block_sums, 0, sizeof(int) * (size_t)d.batch * p.blocks_per_image, s));
     yolo_count_kernel<<<grid, threads, 0, s>>>(p);
     PXE_LAUNCH_OK("yolo_count_kernel");
     yolo_scan_kernel<<<1, 1024, 0, s>>>(p.block_sums, p.block_offsets, d.batch * p.blocks_per_image, count);
