@@ -515,6 +515,7 @@ def run_model(args):
         torch.cuda.empty_cache()
         sw_args = argparse.Namespace(**vars(args))
         sw_args.sweep_shapes, sw_args.sweep_shape_index, sw_args.sweep_residual, sw_args.layout = 0, -1, False, "nchw"
+        sw_args.sweep_folded = True                    # coefficients folded once per layer, as the runner passes them
         sw_args.steps = max(args.steps, 10)
         rows = sweep_rows(sw_args, [(a, k) for a in ("leaky", "mish") for k in ("plain", "pool", "shortcut")])
         worst = min(rows, key=lambda r: r["frac_measured"])
@@ -527,7 +528,8 @@ def run_model(args):
                              f"{'pool' if worst['pool'] else ('shortcut' if worst['residual'] else 'plain')}",
             sweep_worst_cell_copy_frac=round(worst["copy_GBps"] / peak, 3),
             sweep_min_vs_copy=round(min(vs_copy), 3), sweep_median_vs_copy=round(statistics.median(vs_copy), 3),
-            sweep_note="isolated fused epilogue, [64,C,H,W] x {leaky, mish} x {plain, +2x2 pool, +shortcut}: fraction of the "
+            sweep_note="isolated fused epilogue (BN + bias folded once per layer by pxe_fold_bn, as the runner calls it), "
+                       "[64,C,H,W] x {leaky, mish} x {plain, +2x2 pool, +shortcut}: fraction of the "
                        "measured peak on algorithmic bytes; *_vs_copy = against a device copy of the same tensor timed the same way")
         torch.cuda.empty_cache()
         cn_ms, _ = centernet_time(args, 256)
@@ -644,9 +646,12 @@ def sweep_rows(args, variants=None):
         bias = torch.from_numpy(synth.normal(SEED, f"sweepb{C}", C, 0, 0.1)).to(dev)
         base = torch.randn((B, C, H, W), device=dev, generator=torch.Generator(dev).manual_seed(SEED))
         nhwc = args.layout == "nhwc"
+        folded = getattr(args, "sweep_folded", False)
         if nhwc:                      # the same cells on channels-last tensors, coefficients folded once
             base = base.contiguous(memory_format=torch.channels_last)
+        if nhwc or folded:
             fa, fb = ops.fold_bn(C, dev, gamma=g, beta=b, mean=m, var=v, bias=bias)
+        bnkw = dict(a=fa, b=fb) if folded else dict(gamma=g, beta=b, mean=m, var=v, bias=bias)
         xs = [base.clone() for _ in range(sets)]
         want_res = args.sweep_residual or (variants is not None and any(k == "shortcut" for _, k in variants))
         frm_sets = [base.clone() for _ in range(sets)] if want_res else None
@@ -698,13 +703,11 @@ def sweep_rows(args, variants=None):
                     else:
                         ops.conv_epilogue_nhwc(xs[i % sets], a=fa, b=fb, act=act)
                 elif pool:
-                    ops.conv_epilogue(xs[i % sets], y=False, gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
-                                      pool=(2, 2, 1), y_pool=yps[i % sets])
+                    ops.conv_epilogue(xs[i % sets], y=False, act=act, pool=(2, 2, 1), y_pool=yps[i % sets], **bnkw)
                 elif frm is not None:      # conv epilogue + the shortcut layer that follows it: 12 B / element
-                    ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act,
-                                      residual=frm[i % sets], res_act="linear")
+                    ops.conv_epilogue(xs[i % sets], act=act, residual=frm[i % sets], res_act="linear", **bnkw)
                 else:
-                    ops.conv_epilogue(xs[i % sets], gamma=g, beta=b, mean=m, var=v, bias=bias, act=act)
+                    ops.conv_epilogue(xs[i % sets], act=act, **bnkw)
             med, tmin = graph_time(call)
             nbytes = (4 * n + 4 * yps[0].numel()) if pool else (12 * n if frm is not None else 8 * n)
             rows.append({"shape": [B, C, H, W], "act": act, "pool": pool, "residual": frm is not None, "MB": round(nbytes / 1e6, 1),
@@ -1161,6 +1164,8 @@ def main():
     ap.add_argument("--sweep-acts", default="leaky,mish,swish,logistic")
     ap.add_argument("--sweep-pool", default="both", choices=["none", "pool", "both"])
     ap.add_argument("--sweep-residual", action="store_true", help="sweep the epilogue fused with a shortcut add")
+    ap.add_argument("--sweep-folded", action="store_true",
+                    help="sweep with the layer's coefficients folded once (pxe_fold_bn) instead of the raw BN parameters per launch")
     ap.add_argument("--model", default="yolov3-608", help="model graph for --workload epilogue-compare")
     ap.add_argument("--pool-cases", default="spp,maxpool", help="kernel families for --workload pools")
     ap.add_argument("--nms-boxes", type=int, default=1000, help="candidate boxes per image for --workload nms")

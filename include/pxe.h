@@ -138,6 +138,10 @@ typedef struct pxe_epilogue_desc {
                                    PXE_POOL_GENERAL: always the general pooled kernel -- the specialised forms
                                    (even heights, small odd planes) must equal it bit for bit, which is how
                                    the tests hold them to it */
+    const float* folded_a;      /* optional: a[c], b[c] of y = act(a * x + b), folded once per layer by pxe_fold_bn from */
+    const float* folded_b;      /* the same gamma / beta / mean / var / bias (which are then ignored).  Same results bit
+                                   for bit; the kernels then build no per-block coefficient table and meet no barrier,
+                                   which is what tensors under about 200 MB spend a visible share of a launch on */
 } pxe_epilogue_desc;
 
 enum pxe_pool_variant { PXE_POOL_AUTO = 0, PXE_POOL_GENERAL = 1 };

@@ -45,6 +45,7 @@ class EpilogueDesc(C.Structure):
         ("res_alpha", C.c_float), ("res_beta", C.c_float), ("res_act", C.c_int),
         ("pool_kernel", C.c_int), ("pool_stride", C.c_int), ("pool_padding", C.c_int),
         ("y_pool", C.c_void_p), ("y_pool_batch_stride", C.c_longlong), ("pool_variant", C.c_int),
+        ("folded_a", C.c_void_p), ("folded_b", C.c_void_p),
     ]
 
 

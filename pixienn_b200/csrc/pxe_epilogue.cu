@@ -35,6 +35,7 @@ struct EpiParams {
     const float* x; float* y; float* y2; const float* res; float* ypool;
     long long xbs, ybs, y2bs, rbs, pbs;
     const float *gamma, *beta, *mean, *var, *bias;
+    const float *fa, *fb;      // coefficients folded once by the caller (pxe_fold_bn): no per-block table, no barrier
     float eps; int eps_mode;
     int C, H, W, HW;
     int yolo_entries;
@@ -60,13 +61,17 @@ __device__ __forceinline__ PlaneEntry make_entry(const EpiParams& p, uint32_t pl
     const uint32_t img = p.div_c.div(pl);
     const uint32_t c = pl - img * (uint32_t)p.C;
     float a = 1.0f, b = 0.0f;
-    if (p.gamma) {
-        const float v = p.var[c];
-        const float denom = p.eps_mode == PXE_BN_EPS_CPU ? (sqrtf(v) + p.eps) : sqrtf(v + p.eps);
-        a = p.gamma[c] / denom;
-        b = p.beta[c] - p.mean[c] * a;
+    if (p.fa) {
+        a = p.fa[c]; b = p.fb[c];
+    } else {
+        if (p.gamma) {
+            const float v = p.var[c];
+            const float denom = p.eps_mode == PXE_BN_EPS_CPU ? (sqrtf(v) + p.eps) : sqrtf(v + p.eps);
+            a = p.gamma[c] / denom;
+            b = p.beta[c] - p.mean[c] * a;
+        }
+        if (p.bias) b += p.bias[c];
     }
-    if (p.bias) b += p.bias[c];
     int chan = (int)c;
     if (p.yolo_entries > 0) {
         const uint32_t e = c % (uint32_t)p.yolo_entries;
@@ -82,6 +87,25 @@ __device__ __forceinline__ void build_table(const EpiParams& p, PlaneEntry* tab,
 {
     for (uint32_t pl = plane_lo + threadIdx.x; pl <= plane_hi; pl += blockDim.x)
         tab[pl - plane_lo] = make_entry(p, pl);
+}
+
+// The entry of plane `plane_lo + pl`: from the block's table, or, with coefficients the caller folded once per layer,
+// straight from their two arrays (a warp's lanes mostly share a channel: one broadcast load each from L1).  In that
+// form a block builds no table and meets no barrier.
+__device__ __forceinline__ PlaneEntry entry_of(const EpiParams& p, const PlaneEntry* tab, uint32_t plane_lo, uint32_t pl)
+{
+    if (p.fa == nullptr) return tab[pl];
+    const uint32_t q = plane_lo + pl;
+    const uint32_t img = p.div_c.div(q);
+    const uint32_t c = q - img * (uint32_t)p.C;
+    int chan = (int)c;
+    if (p.yolo_entries > 0) {
+        const uint32_t e = c % (uint32_t)p.yolo_entries;
+        if (e == 2 || e == 3) chan |= (1 << 30);
+    }
+    PlaneEntry t;
+    t.a = p.fa[c]; t.b = p.fb[c]; t.image = (int)img; t.chan = chan;
+    return t;
 }
 
 template <int ACT, bool AFFINE>
@@ -155,7 +179,7 @@ epilogue_kernel(const EpiParams p)
                     if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (long long)img[k] * p.rbs + off[k]);
                 }
             }
-            if (rd == 0) {
+            if (rd == 0 && p.fa == nullptr) {
                 build_table(p, tab, plane_lo, plane_hi);
                 __syncthreads();
             }
@@ -163,7 +187,7 @@ epilogue_kernel(const EpiParams p)
             for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
-                    const PlaneEntry t = tab[pl[k]];
+                    const PlaneEntry t = entry_of(p, tab, plane_lo, pl[k]);
                     float4 o;
                     o.x = apply_one<ACT, AFFINE>(v[k].x, t);
                     o.y = apply_one<ACT, AFFINE>(v[k].y, t);
@@ -191,7 +215,7 @@ epilogue_kernel(const EpiParams p)
                     if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (size_t)u * 4);
                 }
             }
-            if (rd == 0) {
+            if (rd == 0 && p.fa == nullptr) {
                 build_table(p, tab, plane_lo, plane_hi);
                 __syncthreads();
             }
@@ -202,8 +226,8 @@ epilogue_kernel(const EpiParams p)
                     uint32_t q, rem;
                     p.div_plane.divmod(u * 4, q, rem);
                     const uint32_t room = (uint32_t)p.HW - rem;      // elements left in plane q
-                    const PlaneEntry t0 = tab[q - plane_lo];
-                    const PlaneEntry t1 = (room < 4) ? tab[q - plane_lo + 1] : t0;
+                    const PlaneEntry t0 = entry_of(p, tab, plane_lo, q - plane_lo);
+                    const PlaneEntry t1 = (room < 4) ? entry_of(p, tab, plane_lo, q - plane_lo + 1) : t0;
                     float4 o;
                     o.x = apply_one<ACT, AFFINE>(v[k].x, t0);
                     o.y = apply_one<ACT, AFFINE>(v[k].y, room > 1 ? t0 : t1);
@@ -236,7 +260,7 @@ epilogue_kernel(const EpiParams p)
                     if (RES) r[k] = p.res[(long long)img[k] * p.rbs + off[k]];
                 }
             }
-            if (rd == 0) {
+            if (rd == 0 && p.fa == nullptr) {
                 build_table(p, tab, plane_lo, plane_hi);
                 __syncthreads();
             }
@@ -244,7 +268,7 @@ epilogue_kernel(const EpiParams p)
             for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
-                    float o = apply_one<ACT, AFFINE>(v[k], tab[pl[k]]);
+                    float o = apply_one<ACT, AFFINE>(v[k], entry_of(p, tab, plane_lo, pl[k]));
                     if (RES) o = residual_one(o, r[k], p);
                     if (p.y) p.y[(long long)img[k] * p.ybs + off[k]] = o;
                     if (p.y2) p.y2[(long long)img[k] * p.y2bs + off[k]] = o;
@@ -347,7 +371,7 @@ epilogue_pool_kernel(const EpiParams p)
                 }
             }
         }
-        if (rd == 0) {
+        if (rd == 0 && p.fa == nullptr) {
             build_table(p, tab, plane_lo, plane_hi);
             __syncthreads();
         }
@@ -355,7 +379,7 @@ epilogue_pool_kernel(const EpiParams p)
         for (int k = 0; k < U; ++k) {
             const uint32_t u = base + k * kThreads;
             if (u >= hi) continue;
-            const PlaneEntry t = tab[pl[k]];
+            const PlaneEntry t = entry_of(p, tab, plane_lo, pl[k]);
             const uint32_t c = (uint32_t)(t.chan & 0xFFFFFF);
 #pragma unroll
             for (int j = 0; j < NI; ++j) {
@@ -468,7 +492,7 @@ epilogue_pool_even_kernel(const EpiParams p)
                 }
             }
         }
-        if (rd == 0) {
+        if (rd == 0 && p.fa == nullptr) {
             build_table(p, tab, plane_lo, plane_hi);
             __syncthreads();
         }
@@ -476,7 +500,7 @@ epilogue_pool_even_kernel(const EpiParams p)
         for (int k = 0; k < U; ++k) {
             const uint32_t u = base + k * kThreads;
             if (u >= hi) continue;
-            const PlaneEntry t = tab[pl[k]];
+            const PlaneEntry t = entry_of(p, tab, plane_lo, pl[k]);
 #pragma unroll
             for (int j = 0; j < NI; ++j) {
                 r0[k][j] = apply_one<ACT, AFFINE>(r0[k][j], t);
@@ -949,13 +973,14 @@ int run_slice(cudaStream_t s, const pxe_epilogue_desc& d, int b0, int nb, const 
     p.y2 = d.y2 ? d.y2 + (long long)b0 * p.y2bs : nullptr;
     p.res = d.residual ? d.residual + (long long)b0 * p.rbs : nullptr;
     p.gamma = d.gamma; p.beta = d.beta; p.mean = d.mean; p.var = d.var; p.bias = d.bias;
+    p.fa = d.folded_a; p.fb = d.folded_b;
     p.eps = d.eps; p.eps_mode = d.eps_mode;
     p.C = d.channels; p.H = d.height; p.W = d.width; p.HW = (int)HW;
     p.yolo_entries = d.act == PXE_ACT_YOLO_HEAD ? d.yolo_classes + 5 : 0;
     p.ralpha = d.res_alpha; p.rbeta = d.res_beta; p.res_act = d.res_act;
     p.div_c = FastDiv((uint32_t)d.channels);
     const long long n = (long long)nb * CHW;
-    const bool affine = d.gamma != nullptr || d.bias != nullptr;
+    const bool affine = d.gamma != nullptr || d.bias != nullptr || d.folded_a != nullptr;
 
     if (d.pool_kernel) {
         PXE_REQUIRE(d.pool_variant == PXE_POOL_AUTO || d.pool_variant == PXE_POOL_GENERAL, "conv_epilogue: unknown pool_variant %d", d.pool_variant);
@@ -1035,6 +1060,7 @@ extern "C" int pxe_conv_epilogue(pxe_stream_t stream, const pxe_epilogue_desc* d
                     "conv_epilogue: channels %d not a multiple of yolo_classes+5 = %d", d.channels, d.yolo_classes + 5);
     if (d.gamma)
         PXE_REQUIRE(d.beta && d.mean && d.var, "conv_epilogue: gamma given but beta/mean/var missing");
+    PXE_REQUIRE((d.folded_a == nullptr) == (d.folded_b == nullptr), "conv_epilogue: folded_a and folded_b go together");
     PXE_REQUIRE(d.eps_mode == PXE_BN_EPS_CUDNN || d.eps_mode == PXE_BN_EPS_CPU, "conv_epilogue: bad eps_mode %d", d.eps_mode);
     const long long HW = (long long)d.height * d.width, CHW = HW * d.channels;
     PXE_REQUIRE(d.x_batch_stride == 0 || d.x_batch_stride >= CHW, "conv_epilogue: x_batch_stride too small");

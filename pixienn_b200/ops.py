@@ -80,12 +80,14 @@ def conv_epilogue(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Opti
                   eps_mode: int = capi.EPS_CUDNN, yolo_classes: int = 0,
                   residual: Optional[torch.Tensor] = None, res_alpha: float = 1.0, res_beta: float = 1.0,
                   res_act="linear", pool: Optional[Sequence[int]] = None,
-                  y_pool: Optional[torch.Tensor] = None, in_place: bool = True, pool_variant: int = 0):
+                  y_pool: Optional[torch.Tensor] = None, in_place: bool = True, pool_variant: int = 0,
+                  a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None):
     """Fused BN / bias / activation (+ residual, + 2x2 pool, + concat-slot stores).
 
     Returns ``y`` (or ``(y, y_pool)`` when pooling).  With ``y=None`` the result overwrites ``x``
     (``in_place=True``) or goes to a new tensor; ``y=False`` with pooling skips the
-    full-resolution output altogether.
+    full-resolution output altogether.  ``a``, ``b``: the layer's coefficients folded once by ``fold_bn`` (then
+    gamma / beta / mean / var / bias are not needed); same results, no per-block coefficient table.
     """
     xp, xbs = _slot(x, "x")
     B, Cc, H, W = x.shape
@@ -111,6 +113,8 @@ def conv_epilogue(x: torch.Tensor, *, y: Optional[torch.Tensor] = None, y2: Opti
         d.mean, d.var = _vec(mean, Cc, "mean"), _vec(var, Cc, "var")
     d.eps, d.eps_mode = eps, eps_mode
     d.bias = _vec(bias, Cc, "bias")
+    if a is not None or b is not None:            # coefficients folded once per layer (fold_bn): no per-block table
+        d.folded_a, d.folded_b = _vec(a, Cc, "a"), _vec(b, Cc, "b")
     d.act, d.yolo_classes = _act(act), yolo_classes
     if residual is not None:
         if tuple(residual.shape) != (B, Cc, H, W):

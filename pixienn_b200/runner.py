@@ -148,17 +148,19 @@ class Runner:
         self.w: Dict[int, Dict[str, torch.Tensor]] = {
             i: {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in d.items()}
             for i, d in weights.items()}
-        if self.nhwc:
-            for l in model.layers:
-                if l.type != "conv":
-                    continue
-                w = self.w[l.index]
+        # every convolution's batch norm / bias folded once to y = a * x + b (pxe_fold_bn): the epilogue kernels then
+        # read two arrays instead of building a coefficient table in every block
+        for l in model.layers:
+            if l.type != "conv":
+                continue
+            w = self.w[l.index]
+            if self.nhwc:
                 w["weights"] = w["weights"].contiguous(memory_format=torch.channels_last)
-                if l.batch_norm:
-                    w["a"], w["b"] = ops.fold_bn(l.filters, device, gamma=w["scales"], beta=w["biases"],
-                                                 mean=w["rolling_mean"], var=w["rolling_var"], eps_mode=eps_mode)
-                else:
-                    w["a"], w["b"] = ops.fold_bn(l.filters, device, bias=w["biases"])
+            if l.batch_norm:
+                w["a"], w["b"] = ops.fold_bn(l.filters, device, gamma=w["scales"], beta=w["biases"],
+                                             mean=w["rolling_mean"], var=w["rolling_var"], eps_mode=eps_mode)
+            else:
+                w["a"], w["b"] = ops.fold_bn(l.filters, device, bias=w["biases"])
         # fused_stem: the first convolution and its epilogue as one launch of the library (pxe_conv_stem) instead of
         # the cuDNN call + epilogue, where the layer and its place in the plan allow it
         self.stem = None
@@ -514,18 +516,11 @@ class Runner:
         if (self.fold_spp and nxt is not None and nxt.op == "spp" and nxt.inputs and nxt.inputs[0] == l.index
                 and st.fused_pool is None and st.fused_shortcut is None and st.dests
                 and 2 * raw.shape[2] * raw.shape[3] * 4 <= 48 * 1024):
-            if "a" not in w:
-                if l.batch_norm:
-                    w["a"], w["b"] = ops.fold_bn(l.filters, self.device, gamma=w["scales"], beta=w["biases"],
-                                                 mean=w["rolling_mean"], var=w["rolling_var"], eps_mode=self.eps_mode)
-                else:
-                    w["a"], w["b"] = ops.fold_bn(l.filters, self.device, bias=w["biases"])
             dests = self._dest_tensors(bufs, st.dests, l)
             self._spp_pending = (raw, dests, w["a"], w["b"], l.activation)
             T[l.index] = dests[0]
             return
-        bn = dict(gamma=w["scales"], beta=w["biases"], mean=w["rolling_mean"], var=w["rolling_var"],
-                  eps_mode=self.eps_mode) if l.batch_norm else dict(bias=w["biases"])
+        bn = dict(a=w["a"], b=w["b"])
         if st.fused_pool is not None:
             pl = self.model.layers[st.fused_pool]
             pd = self._dest_tensors(bufs, st.pool_dests, pl)

@@ -206,3 +206,41 @@ def test_bad_arguments_are_rejected_before_launch(cuda):
     assert capi.lib().pxe_conv_epilogue(None, d) == capi.PXE_ERR_BAD_ARG
     assert b"null" in capi.lib().pxe_last_error_string()
     torch.cuda.synchronize()      # the context is still healthy
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 16, 16), (3, 5, 13, 13), (2, 4, 26, 26), (1, 7, 5, 9), (2, 3, 52, 52), (2, 36, 13, 13),
+                                   (1, 2, 1, 1)])
+@pytest.mark.parametrize("act", ["leaky", "mish", "linear"])
+def test_folded_coefficients_give_the_same_bits(cuda, shape, act):
+    """a, b folded once by pxe_fold_bn instead of gamma / beta / mean / var / bias on every launch: every form of the
+    epilogue (plain, in place, with residual and a second store, both pooled variants with and without the
+    full-resolution output, into channel slots) returns the same bits."""
+    B, C, H, W = shape
+    x = dev(synth.normal(150, f"fx{shape}", shape), cuda)
+    res = dev(synth.normal(151, f"fr{shape}", shape), cuda)
+    _, dp = bn(152, f"fbn{shape}", C, cuda)
+    bias = dev(synth.normal(153, f"fb{shape}", C, 0, 0.1), cuda)
+    raw = dict(gamma=dp[0], beta=dp[1], mean=dp[2], var=dp[3], bias=bias)
+    fa, fb = ops.fold_bn(C, cuda, **raw)
+    fold = dict(a=fa, b=fb)
+
+    def same(call):
+        u, v = call(raw), call(fold)
+        u, v = (u if isinstance(u, tuple) else (u,)), (v if isinstance(v, tuple) else (v,))
+        for s, t in zip(u, v):
+            if s is not None:
+                assert torch.equal(s.contiguous().view(torch.int32), t.contiguous().view(torch.int32))
+
+    same(lambda kw: ops.conv_epilogue(x.clone(), act=act, **kw))
+    same(lambda kw: ops.conv_epilogue(x, y=torch.empty_like(x), y2=torch.empty_like(x), act=act, residual=res, res_act="leaky", **kw))
+    wide = lambda: torch.zeros((B, C + 3, H, W), device=cuda)
+    same(lambda kw: ops.conv_epilogue(x, y=wide()[:, 2:2 + C], act=act, **kw))
+    for pad in (0, 1):
+        if ops.maxpool_out_dim(H, 2, 2, pad) > 0 and ops.maxpool_out_dim(W, 2, 2, pad) > 0:
+            for variant in (capi.POOL_AUTO, capi.POOL_GENERAL):
+                same(lambda kw: ops.conv_epilogue(x, y=False, act=act, pool=(2, 2, pad), pool_variant=variant, **kw))
+                if 2 * ops.maxpool_out_dim(H, 2, 2, pad) >= H and 2 * ops.maxpool_out_dim(W, 2, 2, pad) >= W:
+                    same(lambda kw: ops.conv_epilogue(x, y=torch.empty_like(x), act=act, pool=(2, 2, pad), pool_variant=variant, **kw))
+    # folded coefficients alone (no raw parameters in the call) and a head: the YOLO rule keeps its identity channels
+    if C % 7 == 0:
+        same(lambda kw: ops.conv_epilogue(x.clone(), act="yolo_head", yolo_classes=2, **kw))
