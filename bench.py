@@ -911,8 +911,10 @@ def epilogue_compare(args, model_name, B):
                 x = view(0, l)
                 if st.head_raw:
                     continue
-                bn = dict(gamma=p["scales"], beta=p["biases"], mean=p["rolling_mean"], var=p["rolling_var"]) if l.batch_norm \
-                    else dict(bias=p["biases"])
+                if "a" not in p:                   # folded once per layer, as the runner does at load time
+                    p["a"], p["b"] = ops.fold_bn(l.filters, dev, **(dict(gamma=p["scales"], beta=p["biases"], mean=p["rolling_mean"],
+                                                                       var=p["rolling_var"]) if l.batch_norm else dict(bias=p["biases"])))
+                bn = dict(a=p["a"], b=p["b"])
                 if st.fused_pool is not None:
                     ops.conv_epilogue(x, y=x if st.keep_full else False, act=l.activation, pool=(2, 2, L[st.fused_pool].padding),
                                       y_pool=view(2, L[st.fused_pool]), **bn)
