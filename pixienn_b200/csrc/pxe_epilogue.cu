@@ -793,7 +793,9 @@ int launch_stream_kernel(cudaStream_t s, EpiParams& p, const DeviceInfo& di)
     if (max_chunk < granule) { granule = kThreads; }
     if (max_chunk < granule) { max_chunk = granule; }   // tiny HW: checked below
     unsigned grid;
-    constexpr int rounds = 2;
+    // with folded coefficients a block has no table to amortise: one round per block measured ahead of two for the plain
+    // form at every size below 700 MB (0.95 against 0.91 of peak at 177 MB), level with it for the residual form
+    const int rounds = (p.fa && !RES) ? 1 : 2;
     plan_chunks(p.units, granule, max_chunk, rounds, &p.chunk, &grid);
     long long planes = (long long)p.chunk * vw / p.HW + 2;
     size_t smem = (size_t)planes * sizeof(PlaneEntry);
