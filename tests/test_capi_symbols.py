@@ -62,6 +62,28 @@ def test_host_only_entry_points():
     assert L.pxe_centernet_decode_workspace_bytes(1, 20, 128, 128, 100) >= 20 * 8 * 100 * 8
     assert L.pxe_conv_epilogue(None, None) == capi.PXE_ERR_BAD_ARG
     assert L.pxe_nms_host(None, 0, 0.5, None) == 0
+    # batch norm with batch statistics: workspace = per channel one coefficient slot and one partial sum per block
+    # that shares the channel; refusals come before any launch
+    import ctypes as C
+    small = L.pxe_batchnorm_workspace_bytes(2, 8, 16, 16)
+    large = L.pxe_batchnorm_workspace_bytes(64, 32, 208, 208)
+    assert small >= 8 * 16 and large >= 32 * (16 + 8 * 64) and L.pxe_batchnorm_workspace_bytes(0, 8, 16, 16) == 0
+    assert L.pxe_batchnorm_forward_training(None, None) == capi.PXE_ERR_BAD_ARG
+    assert L.pxe_batchnorm_backward(None, None) == capi.PXE_ERR_BAD_ARG
+    d = capi.BnTrainDesc()
+    d.x = d.y = d.gamma = d.beta = d.save_mean = d.save_scale = 0x10000000
+    d.batch, d.channels, d.height, d.width, d.eps_mode = 2, 8, 16, 16, 7
+    assert L.pxe_batchnorm_forward_training(None, C.byref(d)) == capi.PXE_ERR_BAD_ARG and b"eps_mode" in L.pxe_last_error_string()
+    d.eps_mode = capi.EPS_CUDNN
+    assert L.pxe_batchnorm_forward_training(None, C.byref(d)) == capi.PXE_ERR_BAD_ARG and b"workspace" in L.pxe_last_error_string()
+    assert L.pxe_adam_update(None, 10, None, None, None, 0.9, 0.999, 1e-3, 1e-8, 1) == capi.PXE_ERR_BAD_ARG
+    assert L.pxe_adam_update(None, 0, None, None, None, 0.9, 0.999, 1e-3, 1e-8, 1) == capi.PXE_OK          # nothing to do
+    assert L.pxe_softmax_cross_entropy(None, 5, None, None, None, None) == capi.PXE_ERR_BAD_ARG
+    e = capi.EpilogueDesc()
+    e.x = e.y = 0x10000000
+    e.batch, e.channels, e.height, e.width = 1, 4, 4, 4
+    e.folded_a = 0x20000000                      # one of the two folded arrays only
+    assert L.pxe_conv_epilogue(None, C.byref(e)) == capi.PXE_ERR_BAD_ARG and b"folded" in L.pxe_last_error_string()
 
 
 def test_overlapping_tensors_are_refused_before_any_launch():
