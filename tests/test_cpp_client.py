@@ -22,6 +22,28 @@ def test_headers_compile_as_c99(tmp_path):
     assert r.returncode == 0, r.stderr
 
 
+def test_ctypes_mirrors_have_the_layout_the_c_compiler_gives(tmp_path):
+    """sizeof and a few offsetof values of every descriptor, as gcc lays them out from include/pxe.h, against the ctypes
+    structures the Python binding passes."""
+    import ctypes as C
+    exe = tmp_path / "struct_sizes"
+    r = subprocess.run(["gcc", "-std=c99", "-I", INC, os.path.join(SRC, "struct_sizes.c"), "-o", str(exe)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    out = dict(line.rsplit(" ", 1) for line in subprocess.run([str(exe)], capture_output=True, text=True).stdout.splitlines())
+    mirrors = {"pxe_detection": capi.Detection, "pxe_epilogue_desc": capi.EpilogueDesc,
+               "pxe_epilogue_nhwc_desc": capi.EpilogueNhwcDesc, "pxe_yolo_decode_desc": capi.YoloDecodeDesc,
+               "pxe_centernet_decode_desc": capi.CenterNetDecodeDesc, "pxe_yolo_loss_desc": capi.YoloLossDesc,
+               "pxe_bn_train_desc": capi.BnTrainDesc, "pxe_bn_backward_desc": capi.BnBackwardDesc,
+               "pxe_layer_desc": capi.LayerDesc, "pxe_step": capi.PlanStep}
+    for name, cls in mirrors.items():
+        assert C.sizeof(cls) == int(out[name]), (name, C.sizeof(cls), out[name])
+    for key, value in out.items():
+        if "." in key:
+            name, field = key.split(".")
+            assert getattr(mirrors[name], field).offset == int(value), (key, value)
+
+
 @pytest.mark.skipif(shutil.which("g++") is None, reason="g++ not found")
 def test_cpp_client_links_and_runs(tmp_path):
     capi.lib()                                            # the library exists (raises with build instructions otherwise)
