@@ -43,6 +43,22 @@ def main():
     col = np.empty(3 * 3 * 3 * 4 * 5, np.float32)
     ref.L.pxref_im2col(img[0].ctypes.data_as(po._f), 3, 7, 9, 3, 3, 1, 1, 2, 2, 1, 1, col.ctypes.data_as(po._f))
     out.update(conv_img=img, conv_w=w, im2col_k3_s2_p1=col, conv_y=ref.conv_forward(img, w, 4, 3, 2, 1))
+    # the training side: activation gradients, bias gradient, clip, batch norm with batch statistics both ways
+    gd = synth.normal(17, "golden/grad_delta", len(x), 0, 3)
+    out["grad_delta"] = gd
+    for a in ACTS:
+        out[f"grad_{a}"] = ref.gradient(a, x, gd)
+    bd = synth.normal(18, "golden/bias_delta", (3, 5, 4, 6), 0, 2)
+    bs = synth.normal(18, "golden/bias_start", 5)
+    out.update(bias_delta=bd, bias_start=bs, bias_updates=ref.backward_bias(bs, bd), constrain_y=ref.constrain(gd, 2.5))
+    tx = synth.normal(19, "golden/bnt_x", (3, 5, 7, 9), 0.7, 2.0)
+    tg, tb, trm, trv = synth.bn_params(19, "golden/bnt", 5)
+    ty, tm, tv, trm2, trv2, txn = ref.batchnorm_forward_training(tx, tg, tb, trm, trv)
+    tdy = synth.normal(20, "golden/bnt_dy", tx.shape, 0, 1.5)
+    su0, bu0 = synth.normal(20, "golden/bnt_su", 5), synth.normal(20, "golden/bnt_bu", 5)
+    tdx, tsu, tbu = ref.batchnorm_backward(tdy, tx, txn, tm, tv, tg, su0, bu0)
+    out.update(bnt_x=tx, bnt_gamma=tg, bnt_beta=tb, bnt_rm=trm, bnt_rv=trv, bnt_y=ty, bnt_mean=tm, bnt_var=tv,
+               bnt_rm_out=trm2, bnt_rv_out=trv2, bnt_dy=tdy, bnt_su0=su0, bnt_bu0=bu0, bnt_dx=tdx, bnt_su=tsu, bnt_bu=tbu)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_cpu.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes")
