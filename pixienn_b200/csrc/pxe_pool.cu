@@ -286,8 +286,9 @@ __device__ __forceinline__ void window_x4(const float (&v)[2 * R + 4], float (&o
 // Column maxima over 2*R + 1 rows of S for rows 0..H-1, columns 0..4*nxg-1, straight from the 2*R + 4 rows a strip
 // of four output rows needs (no intermediate planes): into the buffer D (rows past H-1 are left alone) or, with
 // TO_GLOBAL, as vector stores into a dense W-wide plane (W % 4 == 0).  NC columns per lane.
-template <bool EXACT, int R, int NC, bool TO_GLOBAL>
-__device__ __forceinline__ void cascade_cols(const float* S, float* D, int H, int nys, int nxg, int SW, int dw, uint32_t lane)
+template <bool EXACT, int R, int NC, bool TO_GLOBAL, bool SCALAR = false>
+__device__ __forceinline__ void cascade_cols(const float* S, float* D, int H, int nys, int nxg, int SW, int dw, uint32_t lane,
+                                             int W = 0)
 {
     using Vec = typename std::conditional<NC == 4, float4, float2>::type;
     const int ncg = 4 * nxg / NC;
@@ -309,25 +310,21 @@ __device__ __forceinline__ void cascade_cols(const float* S, float* D, int H, in
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             if (4 * ys + j >= H) continue;
-            Vec t;
-            t.x = o[0][j]; t.y = o[1][j];
-            if constexpr (NC == 4) { t.z = o[2][j]; t.w = o[3][j]; }
-            *reinterpret_cast<Vec*>(D + (4 * ys + j) * dw + NC * cg) = t;
+            if constexpr (SCALAR) {
+                // a dense plane whose rows are not vector-aligned: element stores, columns past W - 1 dropped
+                float* row = D + (4 * ys + j) * dw + NC * cg;
+#pragma unroll
+                for (int c = 0; c < NC; ++c)
+                    if (NC * cg + c < W) row[c] = o[c][j];
+            } else {
+                Vec t;
+                t.x = o[0][j]; t.y = o[1][j];
+                if constexpr (NC == 4) { t.z = o[2][j]; t.w = o[3][j]; }
+                *reinterpret_cast<Vec*>(D + (4 * ys + j) * dw + NC * cg) = t;
+            }
         }
         ys += step_y; cg += step_x;
         if (cg >= ncg) { cg -= ncg; ++ys; }
-    }
-}
-
-// the buffer's rows 0..H-1, columns 0..W-1 to a dense plane, coalesced
-__device__ __forceinline__ void cascade_copy_out(const float* S, float* dst, int H, int W, int SW, uint32_t lane)
-{
-    const int step_y = 32 / W, step_x = 32 - step_y * W;
-    int y = (int)lane / W, x = (int)lane - y * W;
-    for (int i = (int)lane; i < H * W; i += 32) {
-        dst[i] = S[y * SW + x];
-        y += step_y; x += step_x;
-        if (x >= W) { x -= W; ++y; }
     }
 }
 
@@ -336,16 +333,14 @@ template <bool VEC, bool EXACT>
 __device__ __forceinline__ void cascade_plane(float* X, float* A, float* B, float* const* out, int levels, int H, int W,
                                               int nxg, int nys, int SW, uint32_t lane)
 {
-    // 5: rows X -> A; 9: rows A -> B; 13: rows B -> A.  Columns go straight out, or through X where the planes
-    // are not aligned for vector stores (X is free once its row maxima exist).
+    // 5: rows X -> A; 9: rows A -> B; 13: rows B -> A.  Columns go straight out: as vectors, or element by element where
+    // the planes are not aligned for them.
     cascade_rows<EXACT>(X, A, H, nxg, lane);
     __syncwarp();
     if (out[0]) {
         if (VEC) cascade_cols<EXACT, 2, 4, true>(A, out[0], H, nys, nxg, SW, W, lane);
         else {
-            cascade_cols<EXACT, 2, 4, false>(A, X, H, nys, nxg, SW, SW, lane);
-            __syncwarp();
-            cascade_copy_out(X, out[0], H, W, SW, lane);
+            cascade_cols<EXACT, 2, 4, true, true>(A, out[0], H, nys, nxg, SW, W, lane, W);
             __syncwarp();
         }
     }
@@ -355,9 +350,7 @@ __device__ __forceinline__ void cascade_plane(float* X, float* A, float* B, floa
         if (out[1]) {
             if (VEC) cascade_cols<EXACT, 4, 2, true>(B, out[1], H, nys, nxg, SW, W, lane);
             else {
-                cascade_cols<EXACT, 4, 2, false>(B, X, H, nys, nxg, SW, SW, lane);
-                __syncwarp();
-                cascade_copy_out(X, out[1], H, W, SW, lane);
+                cascade_cols<EXACT, 4, 2, true, true>(B, out[1], H, nys, nxg, SW, W, lane, W);
                 __syncwarp();
             }
         }
@@ -367,9 +360,7 @@ __device__ __forceinline__ void cascade_plane(float* X, float* A, float* B, floa
         __syncwarp();
         if (VEC) cascade_cols<EXACT, 6, 2, true>(A, out[2], H, nys, nxg, SW, W, lane);
         else {
-            cascade_cols<EXACT, 6, 2, false>(A, X, H, nys, nxg, SW, SW, lane);
-            __syncwarp();
-            cascade_copy_out(X, out[2], H, W, SW, lane);
+            cascade_cols<EXACT, 6, 2, true, true>(A, out[2], H, nys, nxg, SW, W, lane, W);
         }
     }
 }
@@ -419,12 +410,7 @@ spp_cascade_kernel(const CascadeParams cp)
                 if (yid) reinterpret_cast<float4*>(yid)[u] = v;
             }
         } else {
-            // the columns between W and the next multiple of four hold the previous plane's by-products
-            const int extra = 4 * nxg - W;
-            for (int i = (int)lane; i < H * extra; i += 32) {
-                const int y = i / extra;
-                X[y * SW + W + (i - y * extra)] = -INFINITY;
-            }
+            // (columns W .. 4*nxg - 1 of X are never written: they keep the -infinity of the start)
             const int step_y = 32 / W, step_x = 32 - step_y * W;
             int y = (int)lane / W, x = (int)lane - y * W;
             for (int i = (int)lane; i < HW; i += 32) {
