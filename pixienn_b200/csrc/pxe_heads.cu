@@ -105,7 +105,11 @@ __device__ __forceinline__ int yolo_chunk(const YoloParams& p, const float* img,
 
 // A block takes `groups_per_block` consecutive groups of 32 cells of one image (a launch of one block per group spends
 // most of a trained head's decode on starting blocks).  Sums, masks and offsets stay per group.
-__global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
+// MAXW: the most warps a block may have.  Both passes wait on memory, not on registers: with up to 16 warps per block
+// (80 classes: 15) they are compiled for four resident blocks per SM -- 32 registers and a few spills -- which
+// measured 0.88 ms per YOLOv3-608 step at 64 images against 1.03 with three blocks and 1.23 with two.
+template <int MAXW>
+__global__ void __launch_bounds__(kYoloCells * MAXW, MAXW <= 16 ? 4 : 1)
 yolo_count_kernel(const YoloParams p)
 {
     const int b = blockIdx.y;
@@ -254,7 +258,8 @@ __device__ __forceinline__ void yolo_write_records(const YoloParams& p, const fl
     }
 }
 
-__global__ void __launch_bounds__(kYoloCells * kYoloMaxWarps)
+template <int MAXW>
+__global__ void __launch_bounds__(kYoloCells * MAXW, MAXW <= 16 ? 4 : 1)
 yolo_emit_kernel(const YoloParams p)
 {
     __shared__ int ranked[kYoloCells * (kYoloMaxWarps + 1)];   // counts, then exclusive prefixes, in emission order
@@ -1633,11 +1638,13 @@ extern "C" int pxe_yolo_decode(pxe_stream_t stream, const pxe_yolo_decode_desc* 
     dim3 grid((unsigned)((p.blocks_per_image + p.groups_per_block - 1) / p.groups_per_block), (unsigned)d.batch);
     const unsigned threads = (unsigned)(kYoloCells * p.warps);
     PXE_CUDA_OK(cudaMemsetAsync(p.block_sums, 0, sizeof(int) * (size_t)d.batch * p.blocks_per_image, s));
-    yolo_count_kernel<<<grid, threads, 0, s>>>(p);
+    if (p.warps <= 16) yolo_count_kernel<16><<<grid, threads, 0, s>>>(p);
+    else yolo_count_kernel<kYoloMaxWarps><<<grid, threads, 0, s>>>(p);
     PXE_LAUNCH_OK("yolo_count_kernel");
     yolo_scan_kernel<<<1, 1024, 0, s>>>(p.block_sums, p.block_offsets, d.batch * p.blocks_per_image, count);
     PXE_LAUNCH_OK("yolo_scan_kernel");
-    yolo_emit_kernel<<<grid, threads, 0, s>>>(p);
+    if (p.warps <= 16) yolo_emit_kernel<16><<<grid, threads, 0, s>>>(p);
+    else yolo_emit_kernel<kYoloMaxWarps><<<grid, threads, 0, s>>>(p);
     PXE_LAUNCH_OK("yolo_emit_kernel");
     return PXE_OK;
 }
