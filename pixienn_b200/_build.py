@@ -17,12 +17,17 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 LIB = os.path.join(LIBDIR, "libpxe.so")
+# The same sources with every global-memory access of every kernel checked against the caller's allocations
+# (include/pxe_debug.h); slow, for tests on small shapes.
+CHECKED_OBJDIR = os.path.join(LIBDIR, "obj_checked")
+CHECKED_LIB = os.path.join(LIBDIR, "libpxe_checked.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 CU_SOURCES = ["pxe_api.cu", "pxe_epilogue.cu", "pxe_pool.cu", "pxe_move.cu", "pxe_heads.cu", "pxe_compat.cu", "pxe_nms_gpu.cu", "pxe_nhwc.cu", "pxe_stem.cu", "pxe_backward.cu", "pxe_loss.cu", "pxe_bn_train.cu"]
 CXX_SOURCES = ["pxe_nms.cpp", "pxe_plan.cpp"]
 HEADERS = [os.path.join(CSRC, "pxe_common.cuh"), os.path.join(INCLUDE, "pxe.h"),
-           os.path.join(INCLUDE, "pxe_compat.hpp"), os.path.join(INCLUDE, "pxe_plan.h")]
+           os.path.join(INCLUDE, "pxe_compat.hpp"), os.path.join(INCLUDE, "pxe_plan.h"),
+           os.path.join(INCLUDE, "pxe_debug.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC]
@@ -35,26 +40,27 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
 
 
-def _digest(paths) -> str:
+def _digest(paths, extra) -> str:
     h = hashlib.sha256()
     for p in paths:
         with open(p, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + extra).encode())
     return h.hexdigest()
 
 
-def _compile(src: str, verbose: bool) -> str:
+def _compile(src: str, verbose: bool, checked: bool = False) -> str:
     path = os.path.join(CSRC, src)
-    obj = os.path.join(OBJDIR, os.path.splitext(src)[0] + ".o")
+    extra = ["-DPXE_BOUNDS_CHECK"] if checked else []
+    obj = os.path.join(CHECKED_OBJDIR if checked else OBJDIR, os.path.splitext(src)[0] + ".o")
     stamp = obj + ".sha"
-    want = _digest([path] + HEADERS)
+    want = _digest([path] + HEADERS, extra)
     if os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == want:
         return obj
     if src.endswith(".cu"):
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
+        cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
     else:
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", INCLUDE, "-c", path, "-o", obj]
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I", INCLUDE] + extra + ["-c", path, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose and res.stderr:
         sys.stderr.write(res.stderr)
@@ -65,23 +71,24 @@ def _compile(src: str, verbose: bool) -> str:
     return obj
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
-    """Compile whatever changed and link the shared library.  Returns its path."""
-    os.makedirs(OBJDIR, exist_ok=True)
+def build(verbose: bool = False, force: bool = False, checked: bool = False) -> str:
+    """Compile whatever changed and link the shared library (``checked``: the bounds-checked one).  Returns its path."""
+    objdir, lib = (CHECKED_OBJDIR, CHECKED_LIB) if checked else (OBJDIR, LIB)
+    os.makedirs(objdir, exist_ok=True)
     if force:
-        for f in os.listdir(OBJDIR):
-            os.remove(os.path.join(OBJDIR, f))
+        for f in os.listdir(objdir):
+            os.remove(os.path.join(objdir, f))
     srcs = CU_SOURCES + CXX_SOURCES
     with cf.ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 2)) as ex:
-        objs = list(ex.map(lambda s: _compile(s, verbose), srcs))
+        objs = list(ex.map(lambda s: _compile(s, verbose, checked), srcs))
     newest = max(os.path.getmtime(o) for o in objs)
-    if not os.path.exists(LIB) or os.path.getmtime(LIB) < newest:
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]
+    if not os.path.exists(lib) or os.path.getmtime(lib) < newest:
+        cmd = [_nvcc(), "-shared", "-o", lib] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
-            raise RuntimeError(f"linking libpxe.so failed:\n{res.stdout}\n{res.stderr}")
-    return LIB
+            raise RuntimeError(f"linking {os.path.basename(lib)} failed:\n{res.stdout}\n{res.stderr}")
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, checked="--checked" in sys.argv))

@@ -249,6 +249,19 @@ COMPAT_SYMBOLS = [
     "_ZN2px19softmaxCrossEntropyEiPKfS1_PfS2_",
 ]
 
+class BoundsReport(C.Structure):
+    """pxe_bounds_report of include/pxe_debug.h."""
+    _fields_ = [("violations", C.c_uint), ("bytes", C.c_int), ("address", C.c_ulonglong), ("line", C.c_int),
+                ("is_store", C.c_int), ("misaligned", C.c_int), ("reserved", C.c_int), ("file", C.c_char * 48)]
+
+
+# include/pxe_debug.h: present in both builds of the library
+DEBUG_PROTOTYPES = {
+    "pxe_debug_bounds_checked": (C.c_int, []),
+    "pxe_debug_set_allocations": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_int]),
+    "pxe_debug_read_report": (C.c_int, [C.POINTER(BoundsReport), C.c_int]),
+}
+
 _lib = None
 
 
@@ -261,7 +274,7 @@ def lib() -> C.CDLL:
                 f"{LIB_PATH} is missing: build it with `python -m pixienn_b200._build` "
                 "(needs nvcc); there is no fallback implementation")
         L = C.CDLL(LIB_PATH)
-        for name, (res, args) in list(PROTOTYPES.items()) + list(PLAN_PROTOTYPES.items()):
+        for name, (res, args) in list(PROTOTYPES.items()) + list(PLAN_PROTOTYPES.items()) + list(DEBUG_PROTOTYPES.items()):
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args

@@ -62,16 +62,16 @@ gradient_kernel(const float* __restrict__ x, float* __restrict__ delta, size_t n
     if (VEC) {
         const size_t n4 = n >> 2;
         for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
-            const float4 xv = reinterpret_cast<const float4*>(x)[i];
-            float4 d = reinterpret_cast<float4*>(delta)[i];
+            const float4 xv = gld(reinterpret_cast<const float4*>(x) + i);
+            float4 d = gld(reinterpret_cast<float4*>(delta) + i);
             d.x *= act_gradient<ACT>(xv.x); d.y *= act_gradient<ACT>(xv.y);
             d.z *= act_gradient<ACT>(xv.z); d.w *= act_gradient<ACT>(xv.w);
-            reinterpret_cast<float4*>(delta)[i] = d;
+            gst(reinterpret_cast<float4*>(delta) + i, d);
         }
         for (size_t i = (n4 << 2) + (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride)
-            delta[i] *= act_gradient<ACT>(x[i]);
+            gst(delta + i, gld(delta + i) * (act_gradient<ACT>(gld(x + i))));
     } else {
-        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) delta[i] *= act_gradient<ACT>(x[i]);
+        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) gst(delta + i, gld(delta + i) * (act_gradient<ACT>(gld(x + i))));
     }
 }
 
@@ -97,7 +97,7 @@ backward_bias_kernel(float* bias_updates, const float* __restrict__ delta, int b
     float sum = 0.0f;
     for (int b = 0; b < batch; ++b) {
         const float* row = delta + ((size_t)b * n + f) * size;
-        for (int i = threadIdx.x; i < size; i += 256) sum += row[i];
+        for (int i = threadIdx.x; i < size; i += 256) sum += gld(row + i);
     }
     part[threadIdx.x] = sum;
     __syncthreads();
@@ -105,7 +105,7 @@ backward_bias_kernel(float* bias_updates, const float* __restrict__ delta, int b
         if (threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0) bias_updates[f] += part[0];
+    if (threadIdx.x == 0) gst(bias_updates + f, gld(bias_updates + f) + part[0]);
 }
 
 // size == 1 (connected layers): one thread per output, images summed in order (src/BiasKernels.cu:39-53).
@@ -115,8 +115,8 @@ backward_bias_conn_kernel(float* bias_updates, const float* __restrict__ delta, 
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     float sum = 0.0f;
-    for (int b = 0; b < batch; ++b) sum += delta[(size_t)b * n + i];
-    bias_updates[i] += sum;
+    for (int b = 0; b < batch; ++b) sum += gld(delta + ((size_t)b * n + i));
+    gst(bias_updates + i, gld(bias_updates + i) + sum);
 }
 
 // ---------------------------------------------------------------- max-pool backward
@@ -126,8 +126,8 @@ __global__ void __launch_bounds__(256)
 maxpool_backward_kernel(const float* __restrict__ delta, const int* __restrict__ indexes, float* grad, size_t size)
 {
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < size; i += (size_t)gridDim.x * 256) {
-        const int at = indexes[i];
-        if (at >= 0) atomicAdd(grad + at, delta[i]);
+        const int at = gld(indexes + i);
+        if (at >= 0 && gcheck(grad + at)) atomicAdd(grad + at, gld(delta + i));
     }
 }
 
@@ -147,8 +147,8 @@ upsample_backward_kernel(float* acc, const float* __restrict__ out, size_t n_in,
         const float* src = out + (plane * h * stride + (size_t)y * stride) * ow + (size_t)x * stride;
         float sum = 0.0f;
         for (int dy = 0; dy < stride; ++dy)
-            for (int dx = 0; dx < stride; ++dx) sum += scale * src[(size_t)dy * ow + dx];
-        acc[i] += sum;
+            for (int dx = 0; dx < stride; ++dx) sum += scale * gld(src + ((size_t)dy * ow + dx));
+        gst(acc + i, gld(acc + i) + sum);
     }
 }
 
@@ -157,13 +157,13 @@ __global__ void __launch_bounds__(256)
 constrain_kernel(float* x, size_t n, float alpha)
 {
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256)
-        x[i] = fminf(alpha, fmaxf(-alpha, x[i]));                    // src/CudaUtils.cu:122-129
+        gst(x + i, fminf(alpha, fmaxf(-alpha, gld(x + i))));                    // src/CudaUtils.cu:122-129
 }
 
 __global__ void __launch_bounds__(256)
 mul_kernel(const float* __restrict__ x, float* y, size_t n)
 {
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) y[i] = x[i] * y[i];
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) gst(y + i, gld(x + i) * gld(y + i));
 }
 
 // ---------------------------------------------------------------- random fills
@@ -188,7 +188,7 @@ random_uniform_kernel(float* out, size_t n, float a, float b)
 {
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
         const float u = (float)(minstd_after(i + 1) - 1u) / 2147483648.0f;
-        out[i] = u * (b - a) + a;
+        gst(out + i, u * (b - a) + a);
     }
 }
 
@@ -199,7 +199,7 @@ random_normal_kernel(float* out, size_t n, float mean, float stddev)
 {
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
         const float u = ((float)(minstd_after(i + 1) - 1u) + 0.5f) / 2147483648.0f;
-        out[i] = mean + stddev * 1.41421356f * erfinvf(2.0f * u - 1.0f);
+        gst(out + i, mean + stddev * 1.41421356f * erfinvf(2.0f * u - 1.0f));
     }
 }
 
@@ -212,9 +212,9 @@ adam_kernel(float* __restrict__ x, const float* __restrict__ m, const float* __r
 {
     const float c1 = 1.0f - powf(beta1, t), c2 = 1.0f - powf(beta2, t);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const float mhat = m[i] / c1;
-        const float vhat = v[i] / c2;
-        x[i] += rate * mhat / (sqrtf(vhat) + eps);
+        const float mhat = gld(m + i) / c1;
+        const float vhat = gld(v + i) / c2;
+        gst(x + i, gld(x + i) + (rate * mhat / (sqrtf(vhat) + eps)));
     }
 }
 
@@ -226,9 +226,9 @@ softmax_cross_entropy_kernel(const float* __restrict__ pred, const float* __rest
 {
     constexpr float epsilon = 1e-9f;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const float t = truth[i], p = pred[i];
-        error[i] = t ? -logf(p + epsilon) : 0.0f;
-        delta[i] = t - p;
+        const float t = gld(truth + i), p = gld(pred + i);
+        gst(error + i, t ? -logf(p + epsilon) : 0.0f);
+        gst(delta + i, t - p);
     }
 }
 

@@ -73,8 +73,8 @@ __device__ __forceinline__ void bn_piece_sums(const ReduceParams& p, int c, int 
             for (int j = 0; j < U; ++j) {
                 const int i = i0 + j * threads;
                 const bool in = i < hi / 4;
-                v[j] = in ? x4[i] : make_float4(shift, shift, shift, shift);
-                if (BACKWARD) d[j] = in ? d4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                v[j] = in ? gld(x4 + i) : make_float4(shift, shift, shift, shift);
+                if (BACKWARD) d[j] = in ? gld(d4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
 #pragma unroll
             for (int j = 0; j < U; ++j) {
@@ -90,9 +90,9 @@ __device__ __forceinline__ void bn_piece_sums(const ReduceParams& p, int c, int 
         }
     } else {
         for (int i = lo + t; i < hi; i += threads) {
-            const float a = p.x[base + i] - shift;
+            const float a = gld(p.x + (base + i)) - shift;
             if (BACKWARD) {
-                const float d = p.dy[base + i];
+                const float d = gld(p.dy + (base + i));
                 s1 += d;
                 s2 = fmaf(d, a, s2);
             } else {
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kThreads)
 bn_reduce_kernel(const ReduceParams p)
 {
     const int c = blockIdx.x, s = blockIdx.y, splits = gridDim.y;
-    const float shift = BACKWARD ? p.mean[c] : p.x[(long long)c * p.HW];
+    const float shift = BACKWARD ? gld(p.mean + c) : gld(p.x + ((long long)c * p.HW));
     float s1 = 0.0f, s2 = 0.0f;
     if (WARP_PIECES) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +132,7 @@ bn_reduce_kernel(const ReduceParams p)
     if (threadIdx.x == 0) {
         float t1 = 0.0f, t2 = 0.0f;
         for (int w = 0; w < kThreads / 32; ++w) { t1 += warp_sums[w].x; t2 += warp_sums[w].y; }
-        p.partial[(long long)c * splits + s] = make_float2(t1, t2);
+        gst(p.partial + ((long long)c * splits + s), make_float2(t1, t2));
     }
 }
 
@@ -151,11 +151,11 @@ __global__ void bn_forward_final_kernel(const ForwardFinal p)
     if (c >= p.C) return;
     double s1 = 0.0, s2 = 0.0;
     for (int s = 0; s < p.splits; ++s) {
-        const float2 t = p.partial[(long long)c * p.splits + s];
+        const float2 t = gld(p.partial + ((long long)c * p.splits + s));
         s1 += t.x; s2 += t.y;
     }
     const double n = (double)p.n;
-    const float mean = (float)((double)p.x[(long long)c * p.HW] + s1 / n);
+    const float mean = (float)((double)gld(p.x + ((long long)c * p.HW)) + s1 / n);
     double var_d = (s2 - s1 * s1 / n) / n;
     if (var_d < 0.0) var_d = 0.0;
     const float var = (float)var_d;
@@ -163,17 +163,17 @@ __global__ void bn_forward_final_kernel(const ForwardFinal p)
     if (p.eps_mode == PXE_BN_EPS_CPU) {
         inv = 1.0f / (sqrtf(var) + p.eps);
         fed = var;
-        p.save_scale[c] = var;
+        gst(p.save_scale + c, var);
     } else {
         inv = 1.0f / sqrtf(var + p.eps);
         fed = p.n > 1 ? (float)(var_d * n / (n - 1.0)) : var;
-        p.save_scale[c] = inv;
+        gst(p.save_scale + c, inv);
     }
-    p.save_mean[c] = mean;
-    if (p.running_mean) p.running_mean[c] = (1.0f - p.factor) * p.running_mean[c] + p.factor * mean;
-    if (p.running_var) p.running_var[c] = (1.0f - p.factor) * p.running_var[c] + p.factor * fed;
-    const float a = p.gamma[c] * inv;
-    p.coeff[c] = make_float2(a, p.beta[c] - mean * a);
+    gst(p.save_mean + c, mean);
+    if (p.running_mean) gst(p.running_mean + c, (1.0f - p.factor) * gld(p.running_mean + c) + p.factor * mean);
+    if (p.running_var) gst(p.running_var + c, (1.0f - p.factor) * gld(p.running_var + c) + p.factor * fed);
+    const float a = gld(p.gamma + c) * inv;
+    gst(p.coeff + c, make_float2(a, gld(p.beta + c) - mean * a));
 }
 
 struct BackwardFinal {
@@ -191,25 +191,25 @@ __global__ void bn_backward_final_kernel(const BackwardFinal p)
     if (c >= p.C) return;
     double s1 = 0.0, s2 = 0.0;
     for (int s = 0; s < p.splits; ++s) {
-        const float2 t = p.partial[(long long)c * p.splits + s];
+        const float2 t = gld(p.partial + ((long long)c * p.splits + s));
         s1 += t.x; s2 += t.y;
     }
     float inv_fwd, inv_bwd;
     if (p.eps_mode == PXE_BN_EPS_CPU) {
-        const float var = p.save_scale[c];
+        const float var = gld(p.save_scale + c);
         inv_fwd = 1.0f / (sqrtf(var) + p.eps);
         inv_bwd = 1.0f / sqrtf(var + p.eps);
     } else {
-        inv_fwd = inv_bwd = p.save_scale[c];
+        inv_fwd = inv_bwd = gld(p.save_scale + c);
     }
-    if (p.dbeta) p.dbeta[c] += (float)s1;
-    if (p.dgamma) p.dgamma[c] += (float)(s2 * (double)inv_fwd);
+    if (p.dbeta) gst(p.dbeta + c, gld(p.dbeta + c) + (float)s1);
+    if (p.dgamma) gst(p.dgamma + c, gld(p.dgamma + c) + (float)(s2 * (double)inv_fwd));
     const double n = (double)p.n;
-    const float g = p.gamma[c], mean = p.save_mean[c];
+    const float g = gld(p.gamma + c), mean = gld(p.save_mean + c);
     const float k1 = g * inv_bwd;
     const float k2 = (float)(-(double)g * inv_bwd * inv_bwd * inv_bwd * s2 / n);
     const float k3 = (float)(-(double)g * inv_bwd * s1 / n);
-    p.coeff[c] = make_float4(k1, k2, k3 - k2 * mean, 0.0f);
+    gst(p.coeff + c, make_float4(k1, k2, k3 - k2 * mean, 0.0f));
 }
 
 struct ApplyParams {
@@ -241,7 +241,7 @@ bn_forward_apply_kernel(const ApplyParams p)
             float4 in[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-                if (u0 + j * stride < p.units) in[j] = reinterpret_cast<const float4*>(p.x)[p.units - 1 - (u0 + j * stride)];
+                if (u0 + j * stride < p.units) in[j] = gld(reinterpret_cast<const float4*>(p.x) + (p.units - 1 - (u0 + j * stride)));
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 if (u0 + j * stride >= p.units) break;
@@ -251,30 +251,30 @@ bn_forward_apply_kernel(const ApplyParams p)
                 const uint32_t plane = p.div_hw.div(e);
                 const uint32_t c = plane - p.div_c.div(plane) * p.div_c.d;
                 const bool whole = e + 3 < (plane + 1) * p.HW;
-                const float2 k0 = p.coeff2[c];
+                const float2 k0 = gld(p.coeff2 + c);
                 float4 v = in[j];
                 v.x = fmaf(k0.x, v.x, k0.y);
                 if (whole) {
                     v.y = fmaf(k0.x, v.y, k0.y); v.z = fmaf(k0.x, v.z, k0.y); v.w = fmaf(k0.x, v.w, k0.y);
                 } else {
-                    const float2 k1 = p.coeff2[channel_of(p, e + 1)], k2 = p.coeff2[channel_of(p, e + 2)], k3 = p.coeff2[channel_of(p, e + 3)];
+                    const float2 k1 = gld(p.coeff2 + channel_of(p, e + 1)), k2 = gld(p.coeff2 + channel_of(p, e + 2)), k3 = gld(p.coeff2 + channel_of(p, e + 3));
                     v.y = fmaf(k1.x, v.y, k1.y); v.z = fmaf(k2.x, v.z, k2.y); v.w = fmaf(k3.x, v.w, k3.y);
                 }
-                reinterpret_cast<float4*>(p.y)[u] = v;
+                gst(reinterpret_cast<float4*>(p.y) + u, v);
                 if (p.y_act) {
                     v.x = activate_dyn(p.act, v.x); v.y = activate_dyn(p.act, v.y);
                     v.z = activate_dyn(p.act, v.z); v.w = activate_dyn(p.act, v.w);
-                    reinterpret_cast<float4*>(p.y_act)[u] = v;
+                    gst(reinterpret_cast<float4*>(p.y_act) + u, v);
                 }
             }
         }
         return;
     }
     for (uint32_t u = blockIdx.x * kThreads + threadIdx.x; u < p.units; u += gridDim.x * kThreads) {
-        const float2 k = p.coeff2[channel_of(p, u)];
-        const float v = fmaf(k.x, p.x[u], k.y);
-        p.y[u] = v;
-        if (p.y_act) p.y_act[u] = activate_dyn(p.act, v);
+        const float2 k = gld(p.coeff2 + channel_of(p, u));
+        const float v = fmaf(k.x, gld(p.x + u), k.y);
+        gst(p.y + u, v);
+        if (p.y_act) gst(p.y_act + u, activate_dyn(p.act, v));
     }
 }
 
@@ -291,21 +291,21 @@ bn_backward_apply_kernel(const ApplyParams p)
             const uint32_t plane = p.div_hw.div(e);
             const uint32_t c = plane - p.div_c.div(plane) * p.div_c.d;
             const bool whole = e + 3 < (plane + 1) * p.HW;
-            const float4 k0 = p.coeff4[c];
-            const float4 v = reinterpret_cast<const float4*>(p.x)[u];
-            const float4 d = reinterpret_cast<const float4*>(p.dy)[u];
+            const float4 k0 = gld(p.coeff4 + c);
+            const float4 v = gld(reinterpret_cast<const float4*>(p.x) + u);
+            const float4 d = gld(reinterpret_cast<const float4*>(p.dy) + u);
             float4 o;
             o.x = bn_dx(k0, d.x, v.x);
             if (whole) {
                 o.y = bn_dx(k0, d.y, v.y); o.z = bn_dx(k0, d.z, v.z); o.w = bn_dx(k0, d.w, v.w);
             } else {
-                o.y = bn_dx(p.coeff4[channel_of(p, e + 1)], d.y, v.y);
-                o.z = bn_dx(p.coeff4[channel_of(p, e + 2)], d.z, v.z);
-                o.w = bn_dx(p.coeff4[channel_of(p, e + 3)], d.w, v.w);
+                o.y = bn_dx(gld(p.coeff4 + channel_of(p, e + 1)), d.y, v.y);
+                o.z = bn_dx(gld(p.coeff4 + channel_of(p, e + 2)), d.z, v.z);
+                o.w = bn_dx(gld(p.coeff4 + channel_of(p, e + 3)), d.w, v.w);
             }
-            reinterpret_cast<float4*>(p.y)[u] = o;
+            gst(reinterpret_cast<float4*>(p.y) + u, o);
         } else {
-            p.y[u] = bn_dx(p.coeff4[channel_of(p, u)], p.dy[u], p.x[u]);
+            gst(p.y + u, bn_dx(gld(p.coeff4 + channel_of(p, u)), gld(p.dy + u), gld(p.x + u)));
         }
     }
 }

@@ -57,6 +57,88 @@ inline unsigned grid_for(long long work_items, int items_per_block, int sm_count
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
 
+// ---------------------------------------------------------------- global-memory accessors
+// Every access of a kernel to global memory is written with one of these: gld / gst for an element of the pointer's
+// own type, gldv<V> / gstv for a wider vector at an element pointer, gldg / gldgv<V> for the read-only path, and
+// gcheck around an atomic.  In the ordinary build they are the plain dereference.  With -DPXE_BOUNDS_CHECK each
+// one first looks the address up in the table of the caller's allocations (include/pxe_debug.h): an access
+// outside every allocation, across the end of one, or misaligned for its width is skipped (loads give zeros) and
+// recorded with the file and line of the access; the kernel runs to its end, nothing traps.
+#ifdef PXE_BOUNDS_CHECK
+constexpr int kBoundsMaxSpans = 4096;
+struct BoundsTable {
+    unsigned long long start[kBoundsMaxSpans];     // sorted
+    unsigned long long end[kBoundsMaxSpans];
+    int n;                                         // 0 = disarmed
+    unsigned int violations;
+    unsigned long long bad_address;
+    int bad_bytes, bad_line, bad_store, bad_misaligned;
+    char bad_file[48];
+};
+// One pointer per translation unit (the library is linked without relocatable device code); pxe_api.cu calls every
+// unit's attach function when a table is installed.
+static __device__ BoundsTable* tu_bounds_table = nullptr;
+void bounds_register_unit(void (*attach)(BoundsTable*));
+int bounds_add_internal(const void* p, size_t bytes);      // memory the library owns and its kernels reach through a pointer
+namespace {
+inline void bounds_attach_this_unit(BoundsTable* t) { cudaMemcpyToSymbol(tu_bounds_table, &t, sizeof(t)); }
+struct BoundsRegistrar {
+    BoundsRegistrar() { bounds_register_unit(&bounds_attach_this_unit); }
+};
+static BoundsRegistrar bounds_registrar;
+}  // namespace
+
+static __device__ __noinline__ bool bounds_ok(const void* p, unsigned bytes, unsigned align, bool store, int line, const char* file)
+{
+    BoundsTable* t = tu_bounds_table;
+    if (t == nullptr || t->n <= 0 || !__isGlobal(p)) return true;
+    const unsigned long long a = (unsigned long long)p;
+    int lo = 0, hi = t->n;                         // first span that starts after a
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (t->start[mid] <= a) lo = mid + 1; else hi = mid;
+    }
+    const bool inside = lo > 0 && a + bytes <= t->end[lo - 1];
+    const bool aligned = (a % align) == 0;
+    if (inside && aligned) return true;
+    if (atomicAdd(&t->violations, 1u) == 0) {
+        t->bad_address = a; t->bad_bytes = (int)bytes; t->bad_line = line; t->bad_store = store; t->bad_misaligned = inside && !aligned;
+        const char* base = file;
+        for (const char* c = file; *c; ++c) if (*c == '/') base = c + 1;
+        int k = 0;
+        for (; k < 47 && base[k]; ++k) t->bad_file[k] = base[k];
+        t->bad_file[k] = 0;
+    }
+    return false;
+}
+#define PXE_SITE , int line_ = __builtin_LINE(), const char* file_ = __builtin_FILE()
+#define PXE_OK_LD(V) bounds_ok(p, sizeof(V), alignof(V), false, line_, file_)
+#define PXE_OK_ST(V) bounds_ok(p, sizeof(V), alignof(V), true, line_, file_)
+#else
+#define PXE_SITE
+#define PXE_OK_LD(V) true
+#define PXE_OK_ST(V) true
+#endif
+
+template <typename T>
+__device__ __forceinline__ T gld(const T* p PXE_SITE) { return PXE_OK_LD(T) ? *p : T{}; }
+template <typename V, typename T>
+__device__ __forceinline__ V gldv(const T* p PXE_SITE) { return PXE_OK_LD(V) ? *reinterpret_cast<const V*>(p) : V{}; }
+template <typename T>
+__device__ __forceinline__ T gldg(const T* p PXE_SITE) { return PXE_OK_LD(T) ? __ldg(p) : T{}; }
+template <typename V, typename T>
+__device__ __forceinline__ V gldgv(const T* p PXE_SITE) { return PXE_OK_LD(V) ? __ldg(reinterpret_cast<const V*>(p)) : V{}; }
+template <typename T> struct same_type { using type = T; };
+template <typename T>
+__device__ __forceinline__ void gst(T* p, typename same_type<T>::type v PXE_SITE) { if (PXE_OK_ST(T)) *p = v; }
+template <typename V, typename T>
+__device__ __forceinline__ void gstv(T* p, const V& v PXE_SITE) { if (PXE_OK_ST(V)) *reinterpret_cast<V*>(p) = v; }
+// Around an atomic or any other access the helpers above do not cover: true when `bytes` at p may be touched.
+template <typename T>
+__device__ __forceinline__ bool gcheck(T* p PXE_SITE) { return PXE_OK_ST(T); }
+template <typename T>
+__device__ __forceinline__ T gatomic_add(T* p, typename same_type<T>::type v PXE_SITE) { return PXE_OK_ST(T) ? atomicAdd(p, v) : T{}; }
+
 // ---------------------------------------------------------------- exact division
 // Division of a 32-bit unsigned value by a constant fixed at launch time, as a
 // multiply-high and a shift (round-up method; exact for every n < 2^32).

@@ -17,7 +17,7 @@ template <typename T>
 __global__ void fill_kernel(T* ptr, size_t n, T value)
 {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        ptr[i] = value;
+        pxe::gst(ptr + i, value);
 }
 
 template <typename T>

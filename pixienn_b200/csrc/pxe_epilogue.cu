@@ -62,15 +62,15 @@ __device__ __forceinline__ PlaneEntry make_entry(const EpiParams& p, uint32_t pl
     const uint32_t c = pl - img * (uint32_t)p.C;
     float a = 1.0f, b = 0.0f;
     if (p.fa) {
-        a = p.fa[c]; b = p.fb[c];
+        a = gld(p.fa + c); b = gld(p.fb + c);
     } else {
         if (p.gamma) {
-            const float v = p.var[c];
+            const float v = gld(p.var + c);
             const float denom = p.eps_mode == PXE_BN_EPS_CPU ? (sqrtf(v) + p.eps) : sqrtf(v + p.eps);
-            a = p.gamma[c] / denom;
-            b = p.beta[c] - p.mean[c] * a;
+            a = gld(p.gamma + c) / denom;
+            b = gld(p.beta + c) - gld(p.mean + c) * a;
         }
-        if (p.bias) b += p.bias[c];
+        if (p.bias) b += gld(p.bias + c);
     }
     int chan = (int)c;
     if (p.yolo_entries > 0) {
@@ -104,7 +104,7 @@ __device__ __forceinline__ PlaneEntry entry_of(const EpiParams& p, const PlaneEn
         if (e == 2 || e == 3) chan |= (1 << 30);
     }
     PlaneEntry t;
-    t.a = p.fa[c]; t.b = p.fb[c]; t.image = (int)img; t.chan = chan;
+    t.a = gld(p.fa + c); t.b = gld(p.fb + c); t.image = (int)img; t.chan = chan;
     return t;
 }
 
@@ -175,8 +175,8 @@ epilogue_kernel(const EpiParams p)
                     p.div_c.divmod(q, img[k], c);
                     pl[k] = q - plane_lo;
                     off[k] = c * (uint32_t)p.HW + rem * 4;
-                    v[k] = *reinterpret_cast<const float4*>(p.x + (long long)img[k] * p.xbs + off[k]);
-                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (long long)img[k] * p.rbs + off[k]);
+                    v[k] = gldv<float4>(p.x + (long long)img[k] * p.xbs + off[k]);
+                    if (RES) r[k] = gldv<float4>(p.res + (long long)img[k] * p.rbs + off[k]);
                 }
             }
             if (rd == 0 && p.fa == nullptr) {
@@ -199,8 +199,8 @@ epilogue_kernel(const EpiParams p)
                         o.z = residual_one(o.z, r[k].z, p);
                         o.w = residual_one(o.w, r[k].w, p);
                     }
-                    if (p.y) *reinterpret_cast<float4*>(p.y + (long long)img[k] * p.ybs + off[k]) = o;
-                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (long long)img[k] * p.y2bs + off[k]) = o;
+                    if (p.y) gstv(p.y + (long long)img[k] * p.ybs + off[k], o);
+                    if (p.y2) gstv(p.y2 + (long long)img[k] * p.y2bs + off[k], o);
                 }
             }
         } else if (MODE == 1) {
@@ -211,8 +211,8 @@ epilogue_kernel(const EpiParams p)
             for (int k = 0; k < UN; ++k) {
                 const uint32_t u = base + k * kThreads;
                 if (u < hi) {
-                    v[k] = *reinterpret_cast<const float4*>(p.x + (size_t)u * 4);
-                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (size_t)u * 4);
+                    v[k] = gldv<float4>(p.x + (size_t)u * 4);
+                    if (RES) r[k] = gldv<float4>(p.res + (size_t)u * 4);
                 }
             }
             if (rd == 0 && p.fa == nullptr) {
@@ -239,8 +239,8 @@ epilogue_kernel(const EpiParams p)
                         o.z = residual_one(o.z, r[k].z, p);
                         o.w = residual_one(o.w, r[k].w, p);
                     }
-                    if (p.y) *reinterpret_cast<float4*>(p.y + (size_t)u * 4) = o;
-                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (size_t)u * 4) = o;
+                    if (p.y) gstv(p.y + (size_t)u * 4, o);
+                    if (p.y2) gstv(p.y2 + (size_t)u * 4, o);
                 }
             }
         } else {
@@ -256,8 +256,8 @@ epilogue_kernel(const EpiParams p)
                     p.div_c.divmod(q, img[k], c);
                     pl[k] = q - plane_lo;
                     off[k] = c * (uint32_t)p.HW + rem;
-                    v[k] = p.x[(long long)img[k] * p.xbs + off[k]];
-                    if (RES) r[k] = p.res[(long long)img[k] * p.rbs + off[k]];
+                    v[k] = gld(p.x + ((long long)img[k] * p.xbs + off[k]));
+                    if (RES) r[k] = gld(p.res + ((long long)img[k] * p.rbs + off[k]));
                 }
             }
             if (rd == 0 && p.fa == nullptr) {
@@ -270,8 +270,8 @@ epilogue_kernel(const EpiParams p)
                 if (u < hi) {
                     float o = apply_one<ACT, AFFINE>(v[k], entry_of(p, tab, plane_lo, pl[k]));
                     if (RES) o = residual_one(o, r[k], p);
-                    if (p.y) p.y[(long long)img[k] * p.ybs + off[k]] = o;
-                    if (p.y2) p.y2[(long long)img[k] * p.y2bs + off[k]] = o;
+                    if (p.y) gst(p.y + ((long long)img[k] * p.ybs + off[k]), o);
+                    if (p.y2) gst(p.y2 + ((long long)img[k] * p.y2bs + off[k]), o);
                 }
             }
         }
@@ -285,10 +285,10 @@ __global__ void epilogue_tail_kernel(const EpiParams p, uint32_t first, uint32_t
     if (threadIdx.x >= count) return;
     const uint32_t e = first + threadIdx.x;
     const PlaneEntry t = make_entry(p, p.div_plane.div(e));
-    float o = apply_one<ACT, AFFINE>(p.x[e], t);
-    if (RES) o = residual_one(o, p.res[e], p);
-    if (p.y) p.y[e] = o;
-    if (p.y2) p.y2[e] = o;
+    float o = apply_one<ACT, AFFINE>(gld(p.x + e), t);
+    if (RES) o = residual_one(o, gld(p.res + e), p);
+    if (p.y) gst(p.y + e, o);
+    if (p.y2) gst(p.y2 + e, o);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -337,36 +337,36 @@ epilogue_pool_kernel(const EpiParams p)
                 in0[k] = c * (uint32_t)p.HW + (uint32_t)ih * (uint32_t)p.W + (uint32_t)iw;
                 const float* x0 = p.x + (long long)img[k] * p.xbs + in0[k];
                 if (VO == 4) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
-                    const float4 a1 = *reinterpret_cast<const float4*>(x0 + 4);
+                    const float4 a0 = gldv<float4>(x0);
+                    const float4 a1 = gldv<float4>(x0 + 4);
                     r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
                     r0[k][4] = a1.x; r0[k][5] = a1.y; r0[k][6] = a1.z; r0[k][7] = a1.w;
                     if (row1[k]) {
-                        const float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
-                        const float4 b1 = *reinterpret_cast<const float4*>(x0 + p.W + 4);
+                        const float4 b0 = gldv<float4>(x0 + p.W);
+                        const float4 b1 = gldv<float4>(x0 + p.W + 4);
                         r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
                         r1[k][4] = b1.x; r1[k][5] = b1.y; r1[k][6] = b1.z; r1[k][7] = b1.w;
                     }
                 } else if (VO == 2) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
+                    const float4 a0 = gldv<float4>(x0);
                     r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
                     if (row1[k]) {
-                        const float4 b0 = *reinterpret_cast<const float4*>(x0 + p.W);
+                        const float4 b0 = gldv<float4>(x0 + p.W);
                         r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
                     }
                 } else if (VO == 1) {
-                    const float2 a0 = *reinterpret_cast<const float2*>(x0);
+                    const float2 a0 = gldv<float2>(x0);
                     r0[k][0] = a0.x; r0[k][1] = a0.y;
                     if (row1[k]) {
-                        const float2 b0 = *reinterpret_cast<const float2*>(x0 + p.W);
+                        const float2 b0 = gldv<float2>(x0 + p.W);
                         r1[k][0] = b0.x; r1[k][1] = b0.y;
                     }
                 } else {
-                    r0[k][0] = x0[0];
-                    r0[k][1] = col1[k] ? x0[1] : 0.0f;
+                    r0[k][0] = gld(x0);
+                    r0[k][1] = col1[k] ? gld(x0 + 1) : 0.0f;
                     if (row1[k]) {
-                        r1[k][0] = x0[p.W];
-                        r1[k][1] = col1[k] ? x0[p.W + 1] : 0.0f;
+                        r1[k][0] = gld(x0 + p.W);
+                        r1[k][1] = col1[k] ? gld(x0 + (p.W + 1)) : 0.0f;
                     }
                 }
             }
@@ -399,31 +399,31 @@ epilogue_pool_kernel(const EpiParams p)
             }
             float* yp = p.ypool + (long long)img[k] * p.pbs + (long long)c * p.OH * p.OW
                         + (long long)oh_[k] * p.OW + (long long)NV * owv_[k];
-            if (VO == 4) *reinterpret_cast<float4*>(yp) = make_float4(m[0], m[1], m[2], m[3]);
-            else if (VO == 2) *reinterpret_cast<float2*>(yp) = make_float2(m[0], m[1]);
-            else yp[0] = m[0];
+            if (VO == 4) gstv(yp, make_float4(m[0], m[1], m[2], m[3]));
+            else if (VO == 2) gstv(yp, make_float2(m[0], m[1]));
+            else gst(yp, m[0]);
 
             if (p.y) {
                 float* y0 = p.y + (long long)img[k] * p.ybs + in0[k];
                 if (VO == 4) {
-                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
-                    *reinterpret_cast<float4*>(y0 + 4) = make_float4(r0[k][4], r0[k][5], r0[k][6], r0[k][7]);
+                    gstv(y0, make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]));
+                    gstv(y0 + 4, make_float4(r0[k][4], r0[k][5], r0[k][6], r0[k][7]));
                     if (row1[k]) {
-                        *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
-                        *reinterpret_cast<float4*>(y0 + p.W + 4) = make_float4(r1[k][4], r1[k][5], r1[k][6], r1[k][7]);
+                        gstv(y0 + p.W, make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]));
+                        gstv(y0 + p.W + 4, make_float4(r1[k][4], r1[k][5], r1[k][6], r1[k][7]));
                     }
                 } else if (VO == 2) {
-                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
-                    if (row1[k]) *reinterpret_cast<float4*>(y0 + p.W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
+                    gstv(y0, make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]));
+                    if (row1[k]) gstv(y0 + p.W, make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]));
                 } else if (VO == 1) {
-                    *reinterpret_cast<float2*>(y0) = make_float2(r0[k][0], r0[k][1]);
-                    if (row1[k]) *reinterpret_cast<float2*>(y0 + p.W) = make_float2(r1[k][0], r1[k][1]);
+                    gstv(y0, make_float2(r0[k][0], r0[k][1]));
+                    if (row1[k]) gstv(y0 + p.W, make_float2(r1[k][0], r1[k][1]));
                 } else {
-                    y0[0] = r0[k][0];
-                    if (col1[k]) y0[1] = r0[k][1];
+                    gst(y0, r0[k][0]);
+                    if (col1[k]) gst(y0 + 1, r0[k][1]);
                     if (row1[k]) {
-                        y0[p.W] = r1[k][0];
-                        if (col1[k]) y0[p.W + 1] = r1[k][1];
+                        gst(y0 + p.W, r1[k][0]);
+                        if (col1[k]) gst(y0 + (p.W + 1), r1[k][1]);
                     }
                 }
             }
@@ -471,22 +471,22 @@ epilogue_pool_even_kernel(const EpiParams p)
                 pl[k] = p.div_oh.div(rp) - plane_lo;
                 const float* x0 = p.x + off[k];
                 if (VO == 4) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
-                    const float4 a1 = *reinterpret_cast<const float4*>(x0 + 4);
-                    const float4 b0 = *reinterpret_cast<const float4*>(x0 + W);
-                    const float4 b1 = *reinterpret_cast<const float4*>(x0 + W + 4);
+                    const float4 a0 = gldv<float4>(x0);
+                    const float4 a1 = gldv<float4>(x0 + 4);
+                    const float4 b0 = gldv<float4>(x0 + W);
+                    const float4 b1 = gldv<float4>(x0 + W + 4);
                     r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
                     r0[k][4] = a1.x; r0[k][5] = a1.y; r0[k][6] = a1.z; r0[k][7] = a1.w;
                     r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
                     r1[k][4] = b1.x; r1[k][5] = b1.y; r1[k][6] = b1.z; r1[k][7] = b1.w;
                 } else if (VO == 2) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(x0);
-                    const float4 b0 = *reinterpret_cast<const float4*>(x0 + W);
+                    const float4 a0 = gldv<float4>(x0);
+                    const float4 b0 = gldv<float4>(x0 + W);
                     r0[k][0] = a0.x; r0[k][1] = a0.y; r0[k][2] = a0.z; r0[k][3] = a0.w;
                     r1[k][0] = b0.x; r1[k][1] = b0.y; r1[k][2] = b0.z; r1[k][3] = b0.w;
                 } else {
-                    const float2 a0 = *reinterpret_cast<const float2*>(x0);
-                    const float2 b0 = *reinterpret_cast<const float2*>(x0 + W);
+                    const float2 a0 = gldv<float2>(x0);
+                    const float2 b0 = gldv<float2>(x0 + W);
                     r0[k][0] = a0.x; r0[k][1] = a0.y;
                     r1[k][0] = b0.x; r1[k][1] = b0.y;
                 }
@@ -515,9 +515,9 @@ epilogue_pool_even_kernel(const EpiParams p)
                 const uint32_t img = (uint32_t)t.image;
                 yp = p.ypool + (long long)img * p.pbs + (size_t)(u - img * p.units_per_image) * NV;
             }
-            if (VO == 4) *reinterpret_cast<float4*>(yp) = make_float4(m[0], m[1], m[2], m[3]);
-            else if (VO == 2) *reinterpret_cast<float2*>(yp) = make_float2(m[0], m[1]);
-            else yp[0] = m[0];
+            if (VO == 4) gstv(yp, make_float4(m[0], m[1], m[2], m[3]));
+            else if (VO == 2) gstv(yp, make_float2(m[0], m[1]));
+            else gst(yp, m[0]);
 
             if (p.y) {
                 float* y0 = p.y + off[k];
@@ -526,16 +526,16 @@ epilogue_pool_even_kernel(const EpiParams p)
                     y0 = p.y + (long long)img * p.ybs + (off[k] - img * (uint32_t)(p.C * p.HW));
                 }
                 if (VO == 4) {
-                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
-                    *reinterpret_cast<float4*>(y0 + 4) = make_float4(r0[k][4], r0[k][5], r0[k][6], r0[k][7]);
-                    *reinterpret_cast<float4*>(y0 + W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
-                    *reinterpret_cast<float4*>(y0 + W + 4) = make_float4(r1[k][4], r1[k][5], r1[k][6], r1[k][7]);
+                    gstv(y0, make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]));
+                    gstv(y0 + 4, make_float4(r0[k][4], r0[k][5], r0[k][6], r0[k][7]));
+                    gstv(y0 + W, make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]));
+                    gstv(y0 + W + 4, make_float4(r1[k][4], r1[k][5], r1[k][6], r1[k][7]));
                 } else if (VO == 2) {
-                    *reinterpret_cast<float4*>(y0) = make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]);
-                    *reinterpret_cast<float4*>(y0 + W) = make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]);
+                    gstv(y0, make_float4(r0[k][0], r0[k][1], r0[k][2], r0[k][3]));
+                    gstv(y0 + W, make_float4(r1[k][0], r1[k][1], r1[k][2], r1[k][3]));
                 } else {
-                    *reinterpret_cast<float2*>(y0) = make_float2(r0[k][0], r0[k][1]);
-                    *reinterpret_cast<float2*>(y0 + W) = make_float2(r1[k][0], r1[k][1]);
+                    gstv(y0, make_float2(r0[k][0], r0[k][1]));
+                    gstv(y0 + W, make_float2(r1[k][0], r1[k][1]));
                 }
             }
         }
@@ -592,10 +592,10 @@ epilogue_pool_smallplane_kernel(const EpiParams p, uint32_t planes, uint32_t pla
                 for (int s = 0; s < SLOTS; ++s) {
                     if (valid[s]) {
                         const float* x0 = xb + in_off[s];
-                        t00[u][s] = x0[0];
-                        t01[u][s] = col1[s] ? x0[1] : 0.0f;
-                        t10[u][s] = row1[s] ? x0[p.W] : 0.0f;
-                        t11[u][s] = (row1[s] && col1[s]) ? x0[p.W + 1] : 0.0f;
+                        t00[u][s] = gld(x0);
+                        t01[u][s] = col1[s] ? gld(x0 + 1) : 0.0f;
+                        t10[u][s] = row1[s] ? gld(x0 + p.W) : 0.0f;
+                        t11[u][s] = (row1[s] && col1[s]) ? gld(x0 + (p.W + 1)) : 0.0f;
                     }
                 }
             }
@@ -618,14 +618,14 @@ epilogue_pool_smallplane_kernel(const EpiParams p, uint32_t planes, uint32_t pla
                     a10 = apply_one<ACT, AFFINE>(t10[u][s], t); best = pick(best, a10);
                     if (col1[s]) { a11 = apply_one<ACT, AFFINE>(t11[u][s], t); best = pick(best, a11); }
                 }
-                yp[lane + 32u * s] = best;
+                gst(yp + (lane + 32u * s), best);
                 if (yb) {
                     float* y0 = yb + in_off[s];
-                    y0[0] = a00;
-                    if (col1[s]) y0[1] = a01;
+                    gst(y0, a00);
+                    if (col1[s]) gst(y0 + 1, a01);
                     if (row1[s]) {
-                        y0[p.W] = a10;
-                        if (col1[s]) y0[p.W + 1] = a11;
+                        gst(y0 + p.W, a10);
+                        if (col1[s]) gst(y0 + (p.W + 1), a11);
                     }
                 }
             }
@@ -686,7 +686,7 @@ epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
         const float4* x4 = reinterpret_cast<const float4*>(p.x + (long long)img * p.xbs + (long long)(q0 - img * (uint32_t)p.C) * HW);
 #pragma unroll
         for (int r = 0; r < NV; ++r)
-            if (lane + 32u * r < V) d[r] = x4[lane + 32u * r];
+            if (lane + 32u * r < V) d[r] = gld(x4 + (lane + 32u * r));
     };
     load_group(w0);                                        // before anything else
     for (uint32_t o = threadIdx.x; o < 32u * SLOTS; o += kBlock) {
@@ -750,7 +750,7 @@ epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
                 o.w = apply_one<ACT, AFFINE>(d[r].w, entry(w >> 24));
             }
             stage4[v] = o;
-            if (y4) y4[v] = o;
+            if (y4) gst(y4 + v, o);
         }
         if (k + 1 < GPW) load_group(g + 1);
         __syncwarp();
@@ -762,7 +762,7 @@ epilogue_pool_flat_kernel(const EpiParams p, uint32_t groups)
             best = pick(best, *reinterpret_cast<const float*>(stage_bytes + (t.x >> 16)));
             best = pick(best, *reinterpret_cast<const float*>(stage_bytes + (t.y & 0xFFFFu)));
             best = pick(best, *reinterpret_cast<const float*>(stage_bytes + (t.y >> 16)));
-            if (lane + 32u * s < n_out) yp[32 * s] = best;
+            if (lane + 32u * s < n_out) gst(yp + 32 * s, best);
         }
         __syncwarp();
     }

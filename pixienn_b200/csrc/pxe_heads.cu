@@ -49,9 +49,9 @@ __device__ __forceinline__ long long yolo_at(const YoloParams& p, int ch, int ce
 __device__ __forceinline__ float yolo_value(const YoloParams& p, const float* img, int n, int e, int cell)
 {
     const int ch = n * p.entries + e;
-    float v = img[yolo_at(p, ch, cell)];
+    float v = gld(img + yolo_at(p, ch, cell));
     if (p.d.head_is_raw) {
-        if (p.d.bias) v += p.d.bias[ch];
+        if (p.d.bias) v += gld(p.d.bias + ch);
         if (e < 2 || e >= 4) v = act_logistic(v);
     }
     return v;
@@ -86,9 +86,9 @@ __device__ __forceinline__ int yolo_chunk(const YoloParams& p, const float* img,
         const int cls = c0 + j;
         if (cls < cend) {
             const int ch = n * p.entries + 5 + cls;
-            float v = img[yolo_at(p, ch, cell)];
+            float v = gld(img + yolo_at(p, ch, cell));
             if (p.d.head_is_raw) {
-                if (p.d.bias) v += p.d.bias[ch];
+                if (p.d.bias) v += gld(p.d.bias + ch);
                 if (v < skip_below) continue;
                 v = act_logistic(v);
             }
@@ -128,10 +128,11 @@ yolo_count_kernel(const YoloParams p)
                 for (int j = 0; j < kYoloChunk; ++j) mask |= prob[j] >= 0.0f ? 1u << j : 0u;
             }
         }
-        if (p.masks) p.masks[((size_t)b * p.blocks_per_image + grp) * blockDim.x + threadIdx.x] = (unsigned short)mask;
+        if (p.masks) gst(p.masks + (((size_t)b * p.blocks_per_image + grp) * blockDim.x + threadIdx.x), (unsigned short)mask);
         // the group's total is an integer: each warp adds its share to the (zeroed) sum, and no warp waits for another
         for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
-        if (lane == 0 && cnt != 0) atomicAdd(&p.block_sums[b * p.blocks_per_image + grp], cnt);
+        int* sum = p.block_sums + (b * p.blocks_per_image + grp);
+        if (lane == 0 && cnt != 0 && gcheck(sum)) atomicAdd(sum, cnt);
     }
 }
 
@@ -141,11 +142,11 @@ yolo_scan_kernel(const int* block_sums, long long* block_offsets, int n, long lo
 {
     __shared__ long long warp_tot[32];
     __shared__ long long carry;
-    if (threadIdx.x == 0) carry = *count;
+    if (threadIdx.x == 0) carry = gld(count);
     __syncthreads();
     for (int base = 0; base < n; base += 1024) {
         const int i = base + threadIdx.x;
-        long long v = i < n ? block_sums[i] : 0;
+        long long v = i < n ? gld(block_sums + i) : 0;
         long long inc = v;
         for (int o = 1; o < 32; o <<= 1) {
             long long t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -164,21 +165,21 @@ yolo_scan_kernel(const int* block_sums, long long* block_offsets, int n, long lo
         __syncthreads();
         const long long warp_excl = (threadIdx.x >> 5) ? warp_tot[(threadIdx.x >> 5) - 1] : 0;
         const long long c = carry;
-        if (i < n) block_offsets[i] = c + warp_excl + inc - v;
+        if (i < n) gst(block_offsets + i, c + warp_excl + inc - v);
         __syncthreads();
         if (threadIdx.x == 0) carry = c + warp_tot[31];
         __syncthreads();
     }
-    if (threadIdx.x == 0) *count = carry;
+    if (threadIdx.x == 0) gst(count, carry);
 }
 
 // One 32-byte record as two 128-bit stores (records are 16-byte aligned).
 __device__ __forceinline__ void store_detection(pxe_detection* dst, float x, float y, float w, float h, float prob,
                                                 int class_id, int batch_id, int source)
 {
-    float4* q = reinterpret_cast<float4*>(dst);
-    q[0] = make_float4(x, y, w, h);
-    q[1] = make_float4(prob, __int_as_float(class_id), __int_as_float(batch_id), __int_as_float(source));
+    float* q = reinterpret_cast<float*>(dst);
+    gstv(q, make_float4(x, y, w, h));
+    gstv(q + 4, make_float4(prob, __int_as_float(class_id), __int_as_float(batch_id), __int_as_float(source)));
 }
 
 // float -> int the way the reference's host decode converts (x86-64 cvttss2si):
@@ -271,7 +272,7 @@ yolo_emit_kernel(const YoloParams p)
     const int g_end = min((int)(blockIdx.x + 1) * p.groups_per_block, p.blocks_per_image);
     for (int grp = blockIdx.x * p.groups_per_block; grp < g_end; ++grp) {
         // nothing to write in this group (most groups of a trained head): the same answer for every thread of the block
-        if (p.block_sums[b * p.blocks_per_image + grp] == 0) continue;
+        if (gld(p.block_sums + (b * p.blocks_per_image + grp)) == 0) continue;
         const int cell = grp * kYoloCells + lane;
         float prob[kYoloChunk], obj = 0.0f;
         int cnt = 0;
@@ -279,7 +280,7 @@ yolo_emit_kernel(const YoloParams p)
         if (p.masks) {
             // the count pass left the classes that reach the threshold: one activation per emitted value, none at all for
             // the threads that emit nothing; the values are loaded after the scan below, so no barrier waits for them
-            mask = p.masks[((size_t)b * p.blocks_per_image + grp) * blockDim.x + threadIdx.x];
+            mask = gld(p.masks + (((size_t)b * p.blocks_per_image + grp) * blockDim.x + threadIdx.x));
             cnt = __popc(mask);
         } else if (cell < p.HW) {
             cnt = yolo_chunk(p, img, n, chunk, cell, prob, &obj);
@@ -302,7 +303,7 @@ yolo_emit_kernel(const YoloParams p)
         }
         __syncthreads();
         if (cnt != 0) {
-            const long long pos = p.block_offsets[b * p.blocks_per_image + grp] + ranked[lane * p.warps + w];
+            const long long pos = gld(p.block_offsets + (b * p.blocks_per_image + grp)) + ranked[lane * p.warps + w];
             yolo_write_records(p, img, b, cell, n, chunk, mask, prob, obj, pos);
         }
         __syncthreads();                                  // ranked / warp_tot are reused by the next group
@@ -329,16 +330,16 @@ centernet_activate_kernel(const CnActParams p)
         p.div_outputs.divmod(i, q, within);
         const bool heat = within < p.heat;
         if (VEC) {
-            float4 v = reinterpret_cast<const float4*>(p.in)[i];
+            float4 v = gld(reinterpret_cast<const float4*>(p.in) + i);
             if (heat) {
                 v.x = act_logistic(v.x + p.bias); v.y = act_logistic(v.y + p.bias);
                 v.z = act_logistic(v.z + p.bias); v.w = act_logistic(v.w + p.bias);
             }
-            reinterpret_cast<float4*>(p.out)[i] = v;
+            gst(reinterpret_cast<float4*>(p.out) + i, v);
         } else {
-            float v = p.in[i];
+            float v = gld(p.in + i);
             if (heat) v = act_logistic(v + p.bias);
-            p.out[i] = v;
+            gst(p.out + i, v);
         }
     }
 }
@@ -481,8 +482,8 @@ __device__ __forceinline__ float cn_score(const CnParams& p, float v)
 // include/CenterNetLayer.h:217-225: box size and centre offset must be finite and the size positive.
 __device__ __forceinline__ bool cn_valid(const float* size, const float* off, long long idx, long long area, int W, int H)
 {
-    const float bw = size[idx] / W, bh = size[area + idx] / H;
-    const float ox = off[idx], oy = off[area + idx];
+    const float bw = gld(size + idx) / W, bh = gld(size + (area + idx)) / H;
+    const float ox = gld(off + idx), oy = gld(off + (area + idx));
     return isfinite(bw) && isfinite(bh) && isfinite(ox) && isfinite(oy) && bw > 0.0f && bh > 0.0f;
 }
 
@@ -586,7 +587,7 @@ centernet_sample_kernel(const CnParams p)
             for (int x = 4 * lane; x < W; x += 128) {
                 float4 v[kRows];
 #pragma unroll
-                for (int j = 0; j < kRows; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(src[j] + x));
+                for (int j = 0; j < kRows; ++j) v[j] = gldgv<float4>(src[j] + x);
 #pragma unroll
                 for (int j = 0; j < kRows; ++j)
                     if (r0 + j * kWarps < rows) { count(v[j].x); count(v[j].y); count(v[j].z); count(v[j].w); }
@@ -595,7 +596,7 @@ centernet_sample_kernel(const CnParams p)
             for (int x = lane; x < W; x += 32) {
                 float v[kRows];
 #pragma unroll
-                for (int j = 0; j < kRows; ++j) v[j] = __ldg(src[j] + x);
+                for (int j = 0; j < kRows; ++j) v[j] = gldg(src[j] + x);
 #pragma unroll
                 for (int j = 0; j < kRows; ++j)
                     if (r0 + j * kWarps < rows) count(v[j]);
@@ -630,7 +631,7 @@ centernet_sample_kernel(const CnParams p)
     if (threadIdx.x == 0) {
         float bound = lo;
         if (lead_bin >= 2) bound = fmaxf(lo, cn_bin_floor(p, lead_bin));
-        p.bound[b] = bound;
+        gst(p.bound + b, bound);
     }
 }
 
@@ -641,10 +642,10 @@ __device__ __forceinline__ void cn_flush(const unsigned long long* queue, int n,
 {
     const int lane = threadIdx.x & 31;
     int base = 0;
-    if (lane == 0) base = atomicAdd(count, n);
+    if (lane == 0 && gcheck(count)) base = atomicAdd(count, n);
     base = __shfl_sync(0xffffffffu, base, 0);
     for (int i = lane; i < n; i += 32)
-        if (base + i < cap) list[base + i] = queue[i];
+        if (base + i < cap) gst(list + (base + i), queue[i]);
 }
 
 constexpr int kCnFilterWarps = 8;
@@ -673,7 +674,7 @@ centernet_filter_kernel(const CnParams p)
     const uint32_t g_end = min(p.groups, g_begin + (uint32_t)p.groups_per_warp);
     const int H = p.d.height, W = p.d.width;
     const float* heat = p.d.heat + (long long)b * p.hbs;
-    const float lo = p.bound[b], m = p.margin, sat = p.sat_raw;
+    const float lo = gld(p.bound + b), m = p.margin, sat = p.sat_raw;
     // outside the map: never listed (NaN >= x is false), never greater than anything (fmaxf skips NaN)
     const float OUT = __int_as_float(0x7fffffff);
     unsigned long long* key_queue = key_queues[threadIdx.x >> 5];
@@ -683,16 +684,16 @@ centernet_filter_kernel(const CnParams p)
 
     // the four cells of group g (row g / groups_per_row over all classes, columns 4 * (g % groups_per_row) ...)
     auto load_group = [&](uint32_t g) {
-        if (VEC) return __ldg(reinterpret_cast<const float4*>(heat) + g);
+        if (VEC) return gldgv<float4>(heat + 4 * (size_t)g);
         uint32_t row, gx;
         p.div_row.divmod(g, row, gx);
         const int x = 4 * (int)gx;
         const float* src = heat + (size_t)row * W + x;
         float4 v = make_float4(OUT, OUT, OUT, OUT);
-        v.x = __ldg(src);
-        if (x + 1 < W) v.y = __ldg(src + 1);
-        if (x + 2 < W) v.z = __ldg(src + 2);
-        if (x + 3 < W) v.w = __ldg(src + 3);
+        v.x = gldg(src);
+        if (x + 1 < W) v.y = gldg(src + 1);
+        if (x + 2 < W) v.z = gldg(src + 2);
+        if (x + 3 < W) v.w = gldg(src + 3);
         return v;
     };
 
@@ -719,15 +720,15 @@ centernet_filter_kernel(const CnParams p)
                 if (ny >= 0 && ny < H) {
                     const float* src = heat + ((size_t)row + k - 1) * W + x;
                     if (VEC) {
-                        r[k] = __ldg(reinterpret_cast<const float4*>(src));
+                        r[k] = gldgv<float4>(src);
                     } else {
-                        r[k].x = __ldg(src);
-                        if (x + 1 < W) r[k].y = __ldg(src + 1);
-                        if (x + 2 < W) r[k].z = __ldg(src + 2);
-                        if (x + 3 < W) r[k].w = __ldg(src + 3);
+                        r[k].x = gldg(src);
+                        if (x + 1 < W) r[k].y = gldg(src + 1);
+                        if (x + 2 < W) r[k].z = gldg(src + 2);
+                        if (x + 3 < W) r[k].w = gldg(src + 3);
                     }
-                    if (x > 0) l[k] = __ldg(src - 1);
-                    if (x + 4 < W) rt[k] = __ldg(src + 4);
+                    if (x > 0) l[k] = gldg(src - 1);
+                    if (x + 4 < W) rt[k] = gldg(src + 4);
                 }
             }
             c = r[1];
@@ -831,7 +832,7 @@ __device__ __forceinline__ unsigned long long cn_exact(const CnParams& p, const 
             const int dy = (k < 3) ? -1 : (k < 5 ? 0 : 1);
             const int dx = (k < 3) ? k - 1 : (k == 3 ? -1 : (k == 4 ? 1 : k - 6));
             const int ny = gy + dy, nx = gx + dx;
-            nv[k] = (ny >= 0 && ny < H && nx >= 0 && nx < W) ? __ldg(plane + (size_t)ny * W + nx) : NONE;
+            nv[k] = (ny >= 0 && ny < H && nx >= 0 && nx < W) ? gldg(plane + (size_t)ny * W + nx) : NONE;
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -881,10 +882,10 @@ centernet_peaks_kernel(const CnParams p, const int* todo)
     const float bias = logit ? p.d.heatmap_bias : 0.0f;
     const float lo_list = p.lo_list;
     constexpr float NEG = -INFINITY;                  // outside the map: never greater than a score
-    const int n_over = min(todo[0], p.d.batch);
+    const int n_over = min(gld(todo), p.d.batch);
 
     for (int oi = blockIdx.z; oi < n_over; oi += gridDim.z) {
-    const int b = todo[1 + oi];
+    const int b = gld(todo + (1 + oi));
     const float* heat = p.d.heat + (long long)b * p.hbs + (long long)cls * area;
     __syncthreads();                                  // the previous image's shared state is dead
     if (threadIdx.x == 0) { n_keys = 0; n_out = 0; n_work = 0; }
@@ -900,12 +901,12 @@ centernet_peaks_kernel(const CnParams p, const int* todo)
             if (gy >= 0 && gy < H && gx < W) {
                 const float* src = heat + (long long)gy * W + gx;
                 if (gx + 3 < W) {
-                    v = *reinterpret_cast<const float4*>(src);
+                    v = gldv<float4>(src);
                     v.x += bias; v.y += bias; v.z += bias; v.w += bias;
                 } else {
-                    v.x = src[0] + bias;
-                    if (gx + 1 < W) v.y = src[1] + bias;
-                    if (gx + 2 < W) v.z = src[2] + bias;
+                    v.x = gld(src) + bias;
+                    if (gx + 1 < W) v.y = gld(src + 1) + bias;
+                    if (gx + 2 < W) v.z = gld(src + 2) + bias;
                 }
             }
             const int si = row * kCnRowStride + 4 + 4 * vx;
@@ -926,7 +927,7 @@ centernet_peaks_kernel(const CnParams p, const int* todo)
             const int row = i >> 1, side = i & 1;
             const int gy = y0 + row - 1, gx = side ? x0 + kCnTileW : x0 - 1;
             float v = NEG;
-            if (gy >= 0 && gy < H && gx >= 0 && gx < W) v = heat[(long long)gy * W + gx] + bias;
+            if (gy >= 0 && gy < H && gx >= 0 && gx < W) v = gld(heat + ((long long)gy * W + gx)) + bias;
             const int si = row * kCnRowStride + (side ? 4 + kCnTileW : 3);
             tile[si] = v;
             score[si] = NEG;
@@ -937,7 +938,7 @@ centernet_peaks_kernel(const CnParams p, const int* todo)
             const int row = i / (kCnTileW + 2), lx = i - row * (kCnTileW + 2);
             const int gy = y0 + row - 1, gx = x0 + lx - 1;
             float v = NEG;
-            if (gy >= 0 && gy < H && gx >= 0 && gx < W) v = heat[(long long)gy * W + gx] + bias;
+            if (gy >= 0 && gy < H && gx >= 0 && gx < W) v = gld(heat + ((long long)gy * W + gx)) + bias;
             const int si = row * kCnRowStride + 3 + lx;
             tile[si] = v;
             score[si] = NEG;
@@ -975,9 +976,9 @@ centernet_peaks_kernel(const CnParams p, const int* todo)
     const int n = n_keys;
     unsigned long long* out = p.list + (long long)b * p.cap;
     if (n <= p.K) {
-        if (threadIdx.x == 0) base = n ? atomicAdd(&p.count2[b], n) : 0;
+        if (threadIdx.x == 0) base = n && gcheck(p.count2 + b) ? atomicAdd(p.count2 + b, n) : 0;
         __syncthreads();
-        for (int i = threadIdx.x; i < n; i += kCnThreads) out[base + i] = keys[i];
+        for (int i = threadIdx.x; i < n; i += kCnThreads) gst(out + (base + i), keys[i]);
         continue;
     }
     // More candidates than an image keeps: the tile's K best are enough -- but only valid candidates may
@@ -998,10 +999,10 @@ centernet_peaks_kernel(const CnParams p, const int* todo)
     unsigned long long kth = 1ULL;                     // every valid key
     if (n_valid > p.K) kth = block_select_kth([&](int i) { return keys[i]; }, n, p.K, hist, sel);
     const int n_pass = n_valid > p.K ? p.K : n_valid;
-    if (threadIdx.x == 0) base = n_pass ? atomicAdd(&p.count2[b], n_pass) : 0;
+    if (threadIdx.x == 0) base = n_pass && gcheck(p.count2 + b) ? atomicAdd(p.count2 + b, n_pass) : 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += kCnThreads)
-        if (keys[i] >= kth) out[base + atomicAdd(&n_out, 1)] = keys[i];
+        if (keys[i] >= kth) gst(out + (base + atomicAdd(&n_out, 1)), keys[i]);
     }
 }
 
@@ -1036,27 +1037,27 @@ centernet_select_kernel(const CnParams p, const int* only)
     const int H = p.d.height, W = p.d.width;
     const long long area = (long long)H * W;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n_items = only ? min(only[0], p.d.batch) : p.d.batch;
+    const int n_items = only ? min(gld(only), p.d.batch) : p.d.batch;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int b = only ? only[1 + item] : item;
+    const int b = only ? gld(only + (1 + item)) : item;
     const float* heat = p.d.heat + (long long)b * p.hbs;
     const float* size = p.d.size + (long long)b * p.sbs;
     const float* off = p.d.offset + (long long)b * p.obs;
     const unsigned long long* cand = p.list + (long long)b * p.cap;
-    const int found = p.count[b];
+    const int found = gld(p.count + b);
     if (only == nullptr && found > p.cap) {
         // the filter found more keys than the list holds (a plateau): the tile pass redoes this image
         if (threadIdx.x == 0) {
-            p.redo[1 + atomicAdd(&p.redo[0], 1)] = b;
-            p.counts[b] = 0;
+            if (gcheck(p.redo)) gst(p.redo + (1 + atomicAdd(p.redo, 1)), b);
+            gst(p.counts + b, 0);
         }
         continue;
     }
     // an image on the list was redone by the tile pass, which stored count2 final keys (at most cap)
     const bool redone = only != nullptr;
-    const int n_total = redone ? min(p.count2[b], p.cap) : found;
-    const float bound = p.bound[b];
+    const int n_total = redone ? min(gld(p.count2 + b), p.cap) : found;
+    const float bound = gld(p.bound + b);
     const bool raised = !redone && bound > p.lo_raw;
     const float clear = bound + p.margin;              // a detection at or above this beats every cell below the bound
     __syncthreads();                                   // the previous image's shared state is dead
@@ -1073,7 +1074,7 @@ centernet_select_kernel(const CnParams p, const int* only)
             for (int i = threadIdx.x; i < kCnBins; i += kCnSelThreads) bins[i] = 0;
             __syncthreads();
             for (int i = threadIdx.x; i < n_total; i += kCnSelThreads)
-                atomicAdd(&bins[cn_bin(p, order_float((uint32_t)(cand[i] >> 32)))], 1);
+                atomicAdd(&bins[cn_bin(p, order_float((uint32_t)(gld(cand + i) >> 32)))], 1);
             __syncthreads();
             const int want = p.K + p.K / 4 + 32;
             const int top = kCnBins - 1 - 2 * (int)threadIdx.x;
@@ -1097,7 +1098,7 @@ centernet_select_kernel(const CnParams p, const int* only)
         // 2. stage, then the exact treatment
 #pragma unroll 4
         for (int i = threadIdx.x; i < n_total; i += kCnSelThreads) {
-            const unsigned long long key = cand[i];
+            const unsigned long long key = gld(cand + i);
             if (lead_staged == 0 || cn_bin(p, order_float((uint32_t)(key >> 32))) >= lead_staged) {
                 const int at = atomicAdd(&n_best, 1);
                 if (at < kCnStageKeys) stage[at] = key;
@@ -1164,7 +1165,7 @@ centernet_select_kernel(const CnParams p, const int* only)
         const bool staged = n_total <= kCnStageKeys;
         unsigned long long* list = staged ? stage : p.list2 + (long long)b * p.cap;
         for (int i = threadIdx.x; i < n_total; i += kCnSelThreads) {
-            unsigned long long key = cand[i];
+            unsigned long long key = gld(cand + i);
             if (redone) {                                  // final keys of the tile pass: only validity is open
                 const uint32_t flat = 0xffffffffu - (uint32_t)(key & 0xffffffffu);
                 const uint32_t cls = flat / (uint32_t)area;
@@ -1174,7 +1175,7 @@ centernet_select_kernel(const CnParams p, const int* only)
                 key = cn_exact(p, heat, size, off, key);
                 if (key != 0ULL && value >= clear) atomicAdd(&n_above, 1);
             }
-            if (key != 0ULL) list[atomicAdd(&n_valid, 1)] = key;
+            if (key != 0ULL) gst(list + (atomicAdd(&n_valid, 1)), key);
         }
         __syncthreads();
         const int n = n_valid;
@@ -1194,12 +1195,12 @@ centernet_select_kernel(const CnParams p, const int* only)
             int m_sort = 0;
             if (n > p.K) {
                 int want = 0;
-                const unsigned long long lead16 = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel, 2, &want) >> 48;
+                const unsigned long long lead16 = block_select_kth([&](int i) { return gld(list + i); }, n, p.K, hist, sel, 2, &want) >> 48;
                 const int winners = p.K - want;
                 if (threadIdx.x == 0) { n_best = 0; n_valid = 0; }      // n_valid is reused as the tie counter
                 __syncthreads();
                 for (int i = threadIdx.x; i < n; i += kCnSelThreads) {
-                    const unsigned long long key = list[i];
+                    const unsigned long long key = gld(list + i);
                     const unsigned long long top = key >> 48;
                     if (top > lead16) stage[atomicAdd(&n_best, 1)] = key;
                     else if (top == lead16) {
@@ -1211,18 +1212,18 @@ centernet_select_kernel(const CnParams p, const int* only)
                 if (winners + n_valid <= kCnStageKeys) {
                     m_sort = winners + n_valid;
                 } else {
-                    const unsigned long long kth = block_select_kth([&](int i) { return list[i]; }, n, p.K, hist, sel);
+                    const unsigned long long kth = block_select_kth([&](int i) { return gld(list + i); }, n, p.K, hist, sel);
                     if (threadIdx.x == 0) n_best = 0;
                     __syncthreads();
                     for (int i = threadIdx.x; i < n; i += kCnSelThreads) {
-                        const unsigned long long key = list[i];
+                        const unsigned long long key = gld(list + i);
                         if (key >= kth) stage[atomicAdd(&n_best, 1)] = key;
                     }
                     __syncthreads();
                     m_sort = n_best;
                 }
             } else {
-                for (int i = threadIdx.x; i < n; i += kCnSelThreads) stage[i] = list[i];
+                for (int i = threadIdx.x; i < n; i += kCnSelThreads) stage[i] = gld(list + i);
                 m_sort = n;
             }
             __syncthreads();
@@ -1238,8 +1239,8 @@ centernet_select_kernel(const CnParams p, const int* only)
     if (raised && n_above < p.K) {
         // the raised bound may have kept some of the K best off the list: the tile pass redoes this image
         if (threadIdx.x == 0) {
-            p.redo[1 + atomicAdd(&p.redo[0], 1)] = b;
-            p.counts[b] = 0;
+            if (gcheck(p.redo)) gst(p.redo + (1 + atomicAdd(p.redo, 1)), b);
+            gst(p.counts + b, 0);
         }
         continue;
     }
@@ -1253,13 +1254,13 @@ centernet_select_kernel(const CnParams p, const int* only)
         const uint32_t idx = flat - (uint32_t)cls * (uint32_t)area;
         const int y = (int)(idx / (uint32_t)W), x = (int)(idx - (uint32_t)y * (uint32_t)W);
         // include/CenterNetLayer.h:217-237, each product and sum rounded separately as on the host
-        const float bw = size[idx] / W, bh = size[area + idx] / H;
-        const float cx = (x + off[idx]) / W, cy = (y + off[area + idx]) / H;
+        const float bw = gld(size + idx) / W, bh = gld(size + (area + idx)) / H;
+        const float cx = (x + gld(off + idx)) / W, cy = (y + gld(off + (area + idx))) / H;
         store_detection(p.dets + (long long)b * p.K + i, __fmul_rn(__fsub_rn(cx, bw / 2.0f), image_w),
                         __fmul_rn(__fsub_rn(cy, bh / 2.0f), image_h), __fmul_rn(bw, image_w), __fmul_rn(bh, image_h),
                         score, cls, b + p.d.batch_id_offset, (int)flat);
     }
-    if (threadIdx.x == 0) p.counts[b] = m;
+    if (threadIdx.x == 0) gst(p.counts + b, m);
     }
 }
 
@@ -1275,7 +1276,7 @@ softmax_rows_kernel(const float* in, float* out, int n, float temp)
     const float* x = in + (long long)blockIdx.x * n;
     float* y = out + (long long)blockIdx.x * n;
     float m = -FLT_MAX;
-    for (int i = threadIdx.x; i < n; i += 128) m = x[i] > m ? x[i] : m;
+    for (int i = threadIdx.x; i < n; i += 128) m = gld(x + i) > m ? gld(x + i) : m;
     for (int o = 16; o > 0; o >>= 1) { float t = __shfl_xor_sync(0xffffffffu, m, o); m = t > m ? t : m; }
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
     __syncthreads();
@@ -1284,8 +1285,8 @@ softmax_rows_kernel(const float* in, float* out, int n, float temp)
     const float largest = bcast;
     float sum = 0.0f;
     for (int i = threadIdx.x; i < n; i += 128) {
-        const float e = expf(x[i] / temp - largest / temp);
-        y[i] = e;
+        const float e = expf(gld(x + i) / temp - largest / temp);
+        gst(y + i, e);
         sum += e;
     }
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -1295,7 +1296,7 @@ softmax_rows_kernel(const float* in, float* out, int n, float temp)
     if (threadIdx.x == 0) bcast = red[0] + red[1] + red[2] + red[3];
     __syncthreads();
     const float total = bcast;
-    for (int i = threadIdx.x; i < n; i += 128) y[i] = y[i] / total;
+    for (int i = threadIdx.x; i < n; i += 128) gst(y + i, gld(y + i) / total);
 }
 
 struct RegionParams {
@@ -1318,16 +1319,16 @@ region_forward_kernel(const RegionParams p)
         const float* src = p.in + b * outputs + (long long)n * p.size * p.HW + cell;
         float* dst = p.out + b * outputs + ((long long)cell * p.num + n) * p.size;
         for (int e = 0; e < p.size; ++e) {
-            float v = src[(long long)e * p.HW];
+            float v = gld(src + ((long long)e * p.HW));
             if (e == 4) v = act_logistic(v);
-            dst[e] = v;
+            gst(dst + e, v);
         }
         if (p.softmax) {
             float* cls = dst + p.coords + 1;
             float largest = -FLT_MAX, sum = 0.0f;
-            for (int j = 0; j < p.classes; ++j) largest = cls[j] > largest ? cls[j] : largest;
-            for (int j = 0; j < p.classes; ++j) { const float e = expf(cls[j] - largest); sum += e; cls[j] = e; }
-            for (int j = 0; j < p.classes; ++j) cls[j] = cls[j] / sum;
+            for (int j = 0; j < p.classes; ++j) largest = gld(cls + j) > largest ? gld(cls + j) : largest;
+            for (int j = 0; j < p.classes; ++j) { const float e = expf(gld(cls + j) - largest); sum += e; gst(cls + j, e); }
+            for (int j = 0; j < p.classes; ++j) gst(cls + j, gld(cls + j) / sum);
         }
     }
 }
@@ -1352,7 +1353,7 @@ detect_decode_kernel(const DetectParams p)
 {
     __shared__ int warp_tot[32];
     __shared__ long long carry;
-    if (threadIdx.x == 0) carry = *p.count;
+    if (threadIdx.x == 0) carry = gld(p.count);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int locations = p.side * p.side;
@@ -1369,18 +1370,18 @@ detect_decode_kernel(const DetectParams p)
             const int i = slot / p.num;
             const int row = i / p.side, col = i - row * p.side;
             const float* pred = p.pred + (long long)b * p.pbs;
-            const float scale = pred[locations * p.classes + slot];
+            const float scale = gld(pred + (locations * p.classes + slot));
             if (isfinite(scale) && scale > 0.0f) {
                 const float* box = pred + (long long)locations * (p.classes + p.num) + (long long)slot * p.coords;
-                const float x = __fmul_rn((box[0] + col) / p.side, p.width);
-                const float y = __fmul_rn((box[1] + row) / p.side, p.height);
+                const float x = __fmul_rn((gld(box) + col) / p.side, p.width);
+                const float y = __fmul_rn((gld(box + 1) + row) / p.side, p.height);
                 // the host squares with std::pow(v, 2), glibc's powf: within one ulp of v*v, equal to it for
                 // all but ~0.06 % of inputs; one multiplication here
-                const float w = __fmul_rn(p.squared ? __fmul_rn(box[2], box[2]) : box[2], p.width);
-                const float h = __fmul_rn(p.squared ? __fmul_rn(box[3], box[3]) : box[3], p.height);
+                const float w = __fmul_rn(p.squared ? __fmul_rn(gld(box + 2), gld(box + 2)) : gld(box + 2), p.width);
+                const float h = __fmul_rn(p.squared ? __fmul_rn(gld(box + 3), gld(box + 3)) : gld(box + 3), p.height);
                 best_prob = -FLT_MAX;
                 for (int j = 0; j < p.classes; ++j) {
-                    const float pr = __fmul_rn(scale, pred[i * p.classes + j]);
+                    const float pr = __fmul_rn(scale, gld(pred + (i * p.classes + j)));
                     if (pr > best_prob) { best = j; best_prob = pr; }
                 }
                 if (best_prob >= p.threshold) {
@@ -1408,7 +1409,7 @@ detect_decode_kernel(const DetectParams p)
         if (threadIdx.x == 1023) carry = before + inc;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *p.count = carry;
+    if (threadIdx.x == 0) gst(p.count, carry);
 }
 
 // ============================================================================================
@@ -1433,7 +1434,7 @@ region_decode_kernel(const RegionDecodeParams p)
 {
     __shared__ int warp_tot[32];
     __shared__ long long carry;
-    if (threadIdx.x == 0) carry = *p.count;
+    if (threadIdx.x == 0) carry = gld(p.count);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int size = p.coords + 1 + p.classes;
@@ -1450,9 +1451,9 @@ region_decode_kernel(const RegionDecodeParams p)
             // RegionLayer.h:363-369 indexes the predictions without the image's offset: every image decodes
             // image 0's boxes.  per_image = 0 keeps that; 1 gives every image its own.
             box = p.pred + ((long long)(p.per_image ? b : 0) * per_image + index) * size;
-            scale = box[p.coords];
+            scale = gld(box + p.coords);
             for (int j = 0; j < p.classes; ++j)
-                if (__fmul_rn(scale, box[p.coords + 1 + j]) >= p.threshold) ++cnt;
+                if (__fmul_rn(scale, gld(box + (p.coords + 1 + j))) >= p.threshold) ++cnt;
         }
         int inc = cnt;
         for (int o = 1; o < 32; o <<= 1) {
@@ -1467,14 +1468,14 @@ region_decode_kernel(const RegionDecodeParams p)
             long long pos = before + inc - cnt;
             const int i = index / p.num, n = index - i * p.num;
             const int row = i / p.W, col = i - row * p.W;
-            const float x = (col + 1.0f / (1.0f + expf(-box[0]))) / p.W;
-            const float y = (row + 1.0f / (1.0f + expf(-box[1]))) / p.H;
-            const float bw = expf(box[2]) * p.biases[2 * n] / p.W;
-            const float bh = expf(box[3]) * p.biases[2 * n + 1] / p.H;
+            const float x = (col + 1.0f / (1.0f + expf(-gld(box)))) / p.W;
+            const float y = (row + 1.0f / (1.0f + expf(-gld(box + 1)))) / p.H;
+            const float bw = expf(gld(box + 2)) * p.biases[2 * n] / p.W;
+            const float bh = expf(gld(box + 3)) * p.biases[2 * n + 1] / p.H;
             const float x1 = __fmul_rn(x, p.img_w), y1 = __fmul_rn(y, p.img_h);
             const float ww = __fmul_rn(bw, p.img_w), hh = __fmul_rn(bh, p.img_h);
             for (int j = 0; j < p.classes; ++j) {
-                const float pr = __fmul_rn(scale, box[p.coords + 1 + j]);
+                const float pr = __fmul_rn(scale, gld(box + (p.coords + 1 + j)));
                 if (pr >= p.threshold) {
                     if (pos < p.capacity)
                         store_detection(p.dets + pos, __fsub_rn(x1, ww / 2.0f), __fsub_rn(y1, hh / 2.0f), ww, hh, pr, j,
@@ -1487,7 +1488,7 @@ region_decode_kernel(const RegionDecodeParams p)
         if (threadIdx.x == 1023) carry = before + inc;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *p.count = carry;
+    if (threadIdx.x == 0) gst(p.count, carry);
 }
 
 // Softmax (classifier) head: SoftmaxLayer::addDetects, include/SoftmaxLayer.h:182-196.  One record per image
@@ -1499,7 +1500,7 @@ softmax_decode_kernel(const float* probs, long long pbs, int batch, int classes,
 {
     __shared__ int flags[32];
     __shared__ long long carry;
-    if (threadIdx.x == 0) carry = *count;
+    if (threadIdx.x == 0) carry = gld(count);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int base = 0; base < batch; base += 32) {
@@ -1512,9 +1513,9 @@ softmax_decode_kernel(const float* probs, long long pbs, int batch, int classes,
         bool first_is_nan = false;
         if (b < batch) {
             const float* p = probs + (long long)b * pbs;
-            first_is_nan = !(p[0] == p[0]);
+            first_is_nan = !(gld(p) == gld(p));
             for (int j = lane; j < classes; j += 32) {
-                const float v = p[j];
+                const float v = gld(p + j);
                 if (v > best || (v == best && j < arg)) { best = v; arg = j; }
             }
         }
@@ -1539,7 +1540,7 @@ softmax_decode_kernel(const float* probs, long long pbs, int batch, int classes,
         if (threadIdx.x == 0) carry += total;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *count = carry;
+    if (threadIdx.x == 0) gst(count, carry);
 }
 
 }  // namespace
@@ -1682,6 +1683,9 @@ extern "C" int pxe_yolo_decode_static(pxe_stream_t stream, const pxe_yolo_decode
             void* p = nullptr;
             PXE_CUDA_OK(cudaGetSymbolAddress(&p, g_yolo_static_scratch));
             g_static_scratch_ptr[dev] = p;
+#ifdef PXE_BOUNDS_CHECK
+            if (const int rc = pxe::bounds_add_internal(p, sizeof(g_yolo_static_scratch))) return rc;
+#endif
         }
         scratch = g_static_scratch_ptr[dev];
     }

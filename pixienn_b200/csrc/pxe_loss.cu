@@ -40,10 +40,10 @@ __device__ __forceinline__ float overlap(float x1, float w1, float x2, float w2)
 
 __device__ __forceinline__ float box_iou(const float* a, const float* b)
 {
-    const float w = overlap(a[0], a[2], b[0], b[2]);
-    const float h = overlap(a[1], a[3], b[1], b[3]);
+    const float w = overlap(gld(a), gld(a + 2), gld(b), gld(b + 2));
+    const float h = overlap(gld(a + 1), gld(a + 3), gld(b + 1), gld(b + 3));
     const float intersection = w > 0.0f && h > 0.0f ? w * h : 0.0f;
-    const float union_area = fmaxf(0.0f, a[2] * a[3] + b[2] * b[3] - intersection);
+    const float union_area = fmaxf(0.0f, gld(a + 2) * gld(a + 3) + gld(b + 2) * gld(b + 3) - intersection);
     return union_area > 0.0f ? intersection / union_area : 0.0f;
 }
 
@@ -78,26 +78,26 @@ yolo_loss_kernel(const YoloLossParams p)
         const int base = batch * p.mask_count * entries * area + mask_slot * entries * area + cell;   // entry 0
         const float* out = p.output + base;
         float* del = p.delta + base;
-        const float o0 = out[0], o1 = out[area], o2 = out[2 * area], o3 = out[3 * area];
-        const float objectness = out[4 * area];
+        const float o0 = gld(out), o1 = gld(out + area), o2 = gld(out + (2 * area)), o3 = gld(out + (3 * area));
+        const float objectness = gld(out + (4 * area));
 
         // what the slot's deltas end up as; entries not decided below keep what delta holds
         float d_box[4];
-        float d_obj = del[4 * area];
+        float d_obj = gld(del + (4 * area));
         bool write_box = false, write_obj = false, write_cls = false;
         int cls_truth = -1;
 
         // ---- region part: the prediction against every truth of the image (:73-124)
         {
-            const int a = p.masks[mask_slot];
+            const int a = gld(p.masks + mask_slot);
             float pred[4];
             pred[0] = (x + o0) / p.width;
             pred[1] = (y + o1) / p.height;
-            pred[2] = expf(o2) * p.anchors[2 * a] / p.net_width;
-            pred[3] = expf(o3) * p.anchors[2 * a + 1] / p.net_height;
+            pred[2] = expf(o2) * gld(p.anchors + (2 * a)) / p.net_width;
+            pred[3] = expf(o3) * gld(p.anchors + (2 * a + 1)) / p.net_height;
             float best_iou = -FLT_MAX;
             int best = -1;
-            const int n_truth = p.truth_counts[batch];
+            const int n_truth = gld(p.truth_counts + batch);
             for (int t = 0; t < n_truth; ++t) {
                 const int ti = (batch * p.max_truth + t) * 5;
                 const float iou = box_iou(pred, p.truths + ti);
@@ -108,36 +108,36 @@ yolo_loss_kernel(const YoloLossParams p)
             if (best >= 0 && best_iou > p.truth_threshold) {
                 d_obj = p.object_scale * (1.0f - objectness);
                 write_obj = true;
-                cls_truth = (int)p.truths[best + 4];
+                cls_truth = (int)gld(p.truths + (best + 4));
                 write_cls = true;
                 const float* truth = p.truths + best;
-                const float scale = p.coord_scale * (2.0f - truth[2] * truth[3]);
-                const float tx = truth[0] * p.width - x;
-                const float ty = truth[1] * p.height - y;
-                const float tw = logf(fmaxf(1e-9f, truth[2] * p.net_width / p.anchors[2 * a]));
-                const float th = logf(fmaxf(1e-9f, truth[3] * p.net_height / p.anchors[2 * a + 1]));
+                const float scale = p.coord_scale * (2.0f - gld(truth + 2) * gld(truth + 3));
+                const float tx = gld(truth) * p.width - x;
+                const float ty = gld(truth + 1) * p.height - y;
+                const float tw = logf(fmaxf(1e-9f, gld(truth + 2) * p.net_width / gld(p.anchors + (2 * a))));
+                const float th = logf(fmaxf(1e-9f, gld(truth + 3) * p.net_height / gld(p.anchors + (2 * a + 1))));
                 d_box[0] = scale * (tx - o0); d_box[1] = scale * (ty - o1);
                 d_box[2] = scale * (tw - o2); d_box[3] = scale * (th - o3);
                 write_box = true;
             }
         }
         // ---- object part: a slot a truth was assigned to (:126-168); overrides the region part
-        const int assigned = p.assigned_classes[slot];
+        const int assigned = gld(p.assigned_classes + slot);
         float cat_score = 0.0f;
         if (assigned >= 0) {
             const float* truth = p.assigned_boxes + (size_t)slot * 4;
-            const int a = p.assigned_anchors[slot];
+            const int a = gld(p.assigned_anchors + slot);
             float pred[4];
             pred[0] = (x + o0) / p.width;
             pred[1] = (y + o1) / p.height;
-            pred[2] = expf(o2) * p.anchors[2 * a] / p.net_width;
-            pred[3] = expf(o3) * p.anchors[2 * a + 1] / p.net_height;
+            pred[2] = expf(o2) * gld(p.anchors + (2 * a)) / p.net_width;
+            pred[3] = expf(o3) * gld(p.anchors + (2 * a + 1)) / p.net_height;
             const float iou = box_iou(pred, truth);
-            const float scale = p.coord_scale * (2.0f - truth[2] * truth[3]);
-            const float tx = truth[0] * p.width - x;
-            const float ty = truth[1] * p.height - y;
-            const float tw = logf(fmaxf(1e-9f, truth[2] * p.net_width / p.anchors[2 * a]));
-            const float th = logf(fmaxf(1e-9f, truth[3] * p.net_height / p.anchors[2 * a + 1]));
+            const float scale = p.coord_scale * (2.0f - gld(truth + 2) * gld(truth + 3));
+            const float tx = gld(truth) * p.width - x;
+            const float ty = gld(truth + 1) * p.height - y;
+            const float tw = logf(fmaxf(1e-9f, gld(truth + 2) * p.net_width / gld(p.anchors + (2 * a))));
+            const float th = logf(fmaxf(1e-9f, gld(truth + 3) * p.net_height / gld(p.anchors + (2 * a + 1))));
             d_box[0] = scale * (tx - o0); d_box[1] = scale * (ty - o1);
             d_box[2] = scale * (tw - o2); d_box[3] = scale * (th - o3);
             write_box = true;
@@ -150,7 +150,7 @@ yolo_loss_kernel(const YoloLossParams p)
             s_r50 = iou > 0.5f ? 1.0f : 0.0f;
             s_r75 = iou > 0.75f ? 1.0f : 0.0f;
             s_n = 1.0f;
-            if (assigned < p.classes) cat_score = fminf(1.0f, out[(5 + assigned) * area]);
+            if (assigned < p.classes) cat_score = fminf(1.0f, gld(out + ((5 + assigned) * area)));
         }
         s_cat = cat_score;
 
@@ -158,38 +158,38 @@ yolo_loss_kernel(const YoloLossParams p)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             float v;
-            if (write_box) { v = d_box[k]; del[k * area] = v; } else { v = del[k * area]; }
+            if (write_box) { v = d_box[k]; gst(del + (k * area), v); } else { v = gld(del + (k * area)); }
             l_box += v * v;
         }
-        if (write_obj) del[4 * area] = d_obj;
+        if (write_obj) gst(del + (4 * area), d_obj);
         const float o_sq = d_obj * d_obj;
         if (d_obj >= 0.0f) l_pos = o_sq; else l_neg = o_sq;
         for (int c = 0; c < p.classes; ++c) {
             float v;
             if (write_cls) {
                 const float truth_class = c == cls_truth ? 1.0f : 0.0f;
-                v = p.class_scale * (truth_class - out[(5 + c) * area]);
-                del[(5 + c) * area] = v;
+                v = p.class_scale * (truth_class - gld(out + ((5 + c) * area)));
+                gst(del + ((5 + c) * area), v);
             } else {
-                v = del[(5 + c) * area];
+                v = gld(del + ((5 + c) * area));
             }
             l_cls += v * v;
         }
         l_all = l_box + o_sq + l_cls;
     }
     float t;
-    t = block_sum(s_iou, red); if (threadIdx.x == 0 && t != 0.0f) atomicAdd(p.stats + 0, t);
-    t = block_sum(s_r50, red); if (threadIdx.x == 0 && t != 0.0f) atomicAdd(p.stats + 1, t);
-    t = block_sum(s_r75, red); if (threadIdx.x == 0 && t != 0.0f) atomicAdd(p.stats + 2, t);
-    t = block_sum(s_cat, red); if (threadIdx.x == 0 && t != 0.0f) atomicAdd(p.stats + 3, t);
-    t = block_sum(s_obj, red); if (threadIdx.x == 0 && t != 0.0f) atomicAdd(p.stats + 4, t);
-    t = block_sum(s_any, red); if (threadIdx.x == 0) atomicAdd(p.stats + 5, t);
-    t = block_sum(s_n, red);   if (threadIdx.x == 0 && t != 0.0f) { atomicAdd(p.stats + 6, t); atomicAdd(p.stats + 7, t); }
-    t = block_sum(l_box, red); if (threadIdx.x == 0) atomicAdd(p.stats + 8, t);
-    t = block_sum(l_pos, red); if (threadIdx.x == 0) atomicAdd(p.stats + 9, t);
-    t = block_sum(l_neg, red); if (threadIdx.x == 0) atomicAdd(p.stats + 10, t);
-    t = block_sum(l_cls, red); if (threadIdx.x == 0) atomicAdd(p.stats + 11, t);
-    t = block_sum(l_all, red); if (threadIdx.x == 0) atomicAdd(p.cost, t);
+    t = block_sum(s_iou, red); if (threadIdx.x == 0 && t != 0.0f) gatomic_add(p.stats + 0, t);
+    t = block_sum(s_r50, red); if (threadIdx.x == 0 && t != 0.0f) gatomic_add(p.stats + 1, t);
+    t = block_sum(s_r75, red); if (threadIdx.x == 0 && t != 0.0f) gatomic_add(p.stats + 2, t);
+    t = block_sum(s_cat, red); if (threadIdx.x == 0 && t != 0.0f) gatomic_add(p.stats + 3, t);
+    t = block_sum(s_obj, red); if (threadIdx.x == 0 && t != 0.0f) gatomic_add(p.stats + 4, t);
+    t = block_sum(s_any, red); if (threadIdx.x == 0) gatomic_add(p.stats + 5, t);
+    t = block_sum(s_n, red);   if (threadIdx.x == 0 && t != 0.0f) { gatomic_add(p.stats + 6, t); gatomic_add(p.stats + 7, t); }
+    t = block_sum(l_box, red); if (threadIdx.x == 0) gatomic_add(p.stats + 8, t);
+    t = block_sum(l_pos, red); if (threadIdx.x == 0) gatomic_add(p.stats + 9, t);
+    t = block_sum(l_neg, red); if (threadIdx.x == 0) gatomic_add(p.stats + 10, t);
+    t = block_sum(l_cls, red); if (threadIdx.x == 0) gatomic_add(p.stats + 11, t);
+    t = block_sum(l_all, red); if (threadIdx.x == 0) gatomic_add(p.cost, t);
 }
 
 // ---------------------------------------------------------------- CenterNet
@@ -213,22 +213,22 @@ centernet_heat_loss_kernel(const CnLossParams p)
     for (size_t i = (size_t)blockIdx.x * kLossThreads + threadIdx.x; i < p.heat_elements; i += (size_t)gridDim.x * kLossThreads) {
         const size_t batch = i / heat;
         const size_t at = batch * outputs + (i - batch * heat);
-        const float prediction = fminf(fmaxf(p.output[at], 1e-4f), 1.0f - 1e-4f);
-        const float truth = p.target_heat[i];
+        const float prediction = fminf(fmaxf(gld(p.output + at), 1e-4f), 1.0f - 1e-4f);
+        const float truth = gld(p.target_heat + i);
         if (truth >= 1.0f - 1e-6f) {
             const float one_minus = 1.0f - prediction;
             loss += -powf(one_minus, p.alpha) * logf(prediction);
-            p.delta[at] = p.normalizer * (powf(one_minus, p.alpha + 1.0f)
-                                          - p.alpha * prediction * powf(one_minus, p.alpha) * logf(prediction));
+            gst(p.delta + at, p.normalizer * (powf(one_minus, p.alpha + 1.0f)
+                                          - p.alpha * prediction * powf(one_minus, p.alpha) * logf(prediction)));
         } else {
             const float weight = powf(1.0f - truth, p.beta);
             loss += -weight * powf(prediction, p.alpha) * logf(1.0f - prediction);
-            p.delta[at] = p.normalizer * weight * (p.alpha * powf(prediction, p.alpha) * (1.0f - prediction)
-                                                   * logf(1.0f - prediction) - powf(prediction, p.alpha + 1.0f));
+            gst(p.delta + at, p.normalizer * weight * (p.alpha * powf(prediction, p.alpha) * (1.0f - prediction)
+                                                   * logf(1.0f - prediction) - powf(prediction, p.alpha + 1.0f)));
         }
     }
     const float t = block_sum(loss, red);
-    if (threadIdx.x == 0) atomicAdd(p.costs, t);
+    if (threadIdx.x == 0) gatomic_add(p.costs, t);
 }
 
 // L1 loss on size and offset at the cells a target marks (src/CenterNetKernels.cu:63-122): costs[1], costs[2].
@@ -239,24 +239,24 @@ centernet_regression_loss_kernel(const CnLossParams p)
     const int outputs = (p.classes + 4) * p.area, heat = p.classes * p.area;
     float size_loss = 0.0f, offset_loss = 0.0f;
     for (size_t i = (size_t)blockIdx.x * kLossThreads + threadIdx.x; i < p.cells; i += (size_t)gridDim.x * kLossThreads) {
-        if (p.target_mask[i] == 0.0f) continue;
+        if (gld(p.target_mask + i) == 0.0f) continue;
         const size_t batch = i / p.area, cell = i - batch * p.area;
         const size_t tbase = batch * 2 * p.area, obase = batch * outputs;
         for (int channel = 0; channel < 2; ++channel) {
             const size_t map = (size_t)channel * p.area + cell;
             const size_t si = obase + heat + map, oi = obase + heat + 2 * (size_t)p.area + map;
-            const float size_error = p.target_size[tbase + map] - p.output[si];
-            const float offset_error = p.target_offset[tbase + map] - p.output[oi];
+            const float size_error = gld(p.target_size + (tbase + map)) - gld(p.output + si);
+            const float offset_error = gld(p.target_offset + (tbase + map)) - gld(p.output + oi);
             size_loss += fabsf(size_error);
             offset_loss += fabsf(offset_error);
-            p.delta[si] = p.size_weight * p.normalizer * ((size_error > 0.0f) - (size_error < 0.0f));
-            p.delta[oi] = p.normalizer * ((offset_error > 0.0f) - (offset_error < 0.0f));
+            gst(p.delta + si, p.size_weight * p.normalizer * ((size_error > 0.0f) - (size_error < 0.0f)));
+            gst(p.delta + oi, p.normalizer * ((offset_error > 0.0f) - (offset_error < 0.0f)));
         }
     }
     float t = block_sum(size_loss, red);
-    if (threadIdx.x == 0) atomicAdd(p.costs + 1, t);
+    if (threadIdx.x == 0) gatomic_add(p.costs + 1, t);
     t = block_sum(offset_loss, red);
-    if (threadIdx.x == 0) atomicAdd(p.costs + 2, t);
+    if (threadIdx.x == 0) gatomic_add(p.costs + 2, t);
 }
 
 }  // namespace

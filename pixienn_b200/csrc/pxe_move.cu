@@ -37,25 +37,25 @@ upsample2_vec_kernel(const UpParams p)
         float* dst = p.y + (long long)b * p.ybs + ((long long)c * p.H * 2 + 2 * h) * (p.W * 2) + (long long)wv * VI * 2;
         const int ow = p.W * 2;
         if (VI == 4) {
-            float4 v = *reinterpret_cast<const float4*>(src);
+            float4 v = gldv<float4>(src);
             v.x *= p.scale; v.y *= p.scale; v.z *= p.scale; v.w *= p.scale;
             const float4 lo = make_float4(v.x, v.x, v.y, v.y), hi = make_float4(v.z, v.z, v.w, v.w);
-            *reinterpret_cast<float4*>(dst) = lo;
-            *reinterpret_cast<float4*>(dst + 4) = hi;
-            *reinterpret_cast<float4*>(dst + ow) = lo;
-            *reinterpret_cast<float4*>(dst + ow + 4) = hi;
+            gstv(dst, lo);
+            gstv(dst + 4, hi);
+            gstv(dst + ow, lo);
+            gstv(dst + ow + 4, hi);
         } else if (VI == 2) {
-            float2 v = *reinterpret_cast<const float2*>(src);
+            float2 v = gldv<float2>(src);
             v.x *= p.scale; v.y *= p.scale;
             const float4 o = make_float4(v.x, v.x, v.y, v.y);
-            *reinterpret_cast<float4*>(dst) = o;
-            *reinterpret_cast<float4*>(dst + ow) = o;
+            gstv(dst, o);
+            gstv(dst + ow, o);
         } else {
             // odd widths (13, 19): one input element per thread, the output rows are still 8-byte aligned
-            const float v = src[0] * p.scale;
+            const float v = gld(src) * p.scale;
             const float2 o = make_float2(v, v);
-            *reinterpret_cast<float2*>(dst) = o;
-            *reinterpret_cast<float2*>(dst + ow) = o;
+            gstv(dst, o);
+            gstv(dst + ow, o);
         }
     }
 }
@@ -71,8 +71,8 @@ upsample_scalar_kernel(const UpParams p)
         p.div_h.divmod(t, t, oh);
         p.div_c.divmod(t, b, c);
         const int ih = (int)oh / p.stride, iw = (int)ow / p.stride;
-        const float v = p.x[(long long)b * p.xbs + ((long long)c * p.H + ih) * p.W + iw];
-        p.y[(long long)b * p.ybs + ((long long)c * p.H * p.stride + oh) * OW + ow] = p.scale * v;
+        const float v = gld(p.x + ((long long)b * p.xbs + ((long long)c * p.H + ih) * p.W + iw));
+        gst(p.y + ((long long)b * p.ybs + ((long long)c * p.H * p.stride + oh) * OW + ow), p.scale * v);
     }
 }
 
@@ -96,7 +96,7 @@ shortcut_general_kernel(const ScParams p)
         const int b = id % p.batch;
         const long long oi = i * p.sample + (long long)p.w2 * (j * p.sample + (long long)p.h2 * (k + (long long)p.c2 * b));
         const long long ai = i * p.stride + (long long)p.w1 * (j * p.stride + (long long)p.h1 * (k + (long long)p.c1 * b));
-        p.out[oi] = fmaf(p.s1, p.out[oi], p.s2 * p.add[ai]);
+        gst(p.out + oi, fmaf(p.s1, gld(p.out + oi), p.s2 * gld(p.add + ai)));
     }
 }
 
@@ -123,14 +123,14 @@ concat_kernel(const CatParams p)
         const long long total = nv * p.batch;
         for (long long u = (long long)blockIdx.x * kThreads + threadIdx.x; u < total; u += (long long)gridDim.x * kThreads) {
             const long long b = u / nv, r = u - b * nv;
-            const float4 v = *reinterpret_cast<const float4*>(p.src[s] + b * p.sbs[s] + r * 4);
-            *reinterpret_cast<float4*>(p.y + b * p.ybs + p.dst_off[s] + r * 4) = v;
+            const float4 v = gldv<float4>(p.src[s] + b * p.sbs[s] + r * 4);
+            gstv(p.y + b * p.ybs + p.dst_off[s] + r * 4, v);
         }
     } else {
         const long long total = len * p.batch;
         for (long long u = (long long)blockIdx.x * kThreads + threadIdx.x; u < total; u += (long long)gridDim.x * kThreads) {
             const long long b = u / len, r = u - b * len;
-            p.y[b * p.ybs + p.dst_off[s] + r] = p.src[s][b * p.sbs[s] + r];
+            gst(p.y + (b * p.ybs + p.dst_off[s] + r), gld(p.src[s] + (b * p.sbs[s] + r)));
         }
     }
 }

@@ -31,14 +31,14 @@ __global__ void fold_bn_kernel(const float* gamma, const float* beta, const floa
     if (c >= channels) return;
     float fa = 1.0f, fb = 0.0f;
     if (gamma) {
-        const float v = var[c];
+        const float v = gld(var + c);
         const float denom = eps_mode == PXE_BN_EPS_CPU ? (sqrtf(v) + eps) : sqrtf(v + eps);
-        fa = gamma[c] / denom;
-        fb = beta[c] - mean[c] * fa;
+        fa = gld(gamma + c) / denom;
+        fb = gld(beta + c) - gld(mean + c) * fa;
     }
-    if (bias) fb += bias[c];
-    a[c] = fa;
-    b[c] = fb;
+    if (bias) fb += gld(bias + c);
+    gst(a + c, fa);
+    gst(b + c, fb);
 }
 
 struct NhwcParams {
@@ -79,8 +79,8 @@ epilogue_nhwc_kernel(const NhwcParams p)
     float4 fa = make_float4(1.f, 1.f, 1.f, 1.f), fb = make_float4(0.f, 0.f, 0.f, 0.f);
     if (fixed) {
         const uint32_t c4 = threadIdx.x & (p.div_cv.d - 1);
-        fa = *reinterpret_cast<const float4*>(p.a + 4 * c4);
-        fb = *reinterpret_cast<const float4*>(p.b + 4 * c4);
+        fa = gldv<float4>(p.a + 4 * c4);
+        fb = gldv<float4>(p.b + 4 * c4);
     }
     for (uint32_t r0 = lo; r0 < hi; r0 += step) {
         if (VW == 4) {
@@ -93,8 +93,8 @@ epilogue_nhwc_kernel(const NhwcParams p)
                     uint32_t cv;
                     p.div_cv.divmod(u, pix[k], cv);
                     ch[k] = cv * 4;
-                    v[k] = *reinterpret_cast<const float4*>(p.x + (long long)pix[k] * p.xps + ch[k]);
-                    if (RES) r[k] = *reinterpret_cast<const float4*>(p.res + (long long)pix[k] * p.rps + ch[k]);
+                    v[k] = gldv<float4>(p.x + (long long)pix[k] * p.xps + ch[k]);
+                    if (RES) r[k] = gldv<float4>(p.res + (long long)pix[k] * p.rps + ch[k]);
                 }
             }
 #pragma unroll
@@ -103,8 +103,8 @@ epilogue_nhwc_kernel(const NhwcParams p)
                 if (u < hi) {
                     float4 ca = fa, cb = fb;
                     if (AFFINE && !fixed) {                      // cache hits: the table is a few KB
-                        ca = *reinterpret_cast<const float4*>(p.a + ch[k]);
-                        cb = *reinterpret_cast<const float4*>(p.b + ch[k]);
+                        ca = gldv<float4>(p.a + ch[k]);
+                        cb = gldv<float4>(p.b + ch[k]);
                     }
                     float4 o;
                     o.x = nhwc_apply<ACT, AFFINE>(v[k].x, ca.x, cb.x);
@@ -118,8 +118,8 @@ epilogue_nhwc_kernel(const NhwcParams p)
                         o.z = activate_dyn(p.res_act, fmaf(p.ralpha, o.z, p.rbeta * r[k].z));
                         o.w = activate_dyn(p.res_act, fmaf(p.ralpha, o.w, p.rbeta * r[k].w));
                     }
-                    if (p.y) *reinterpret_cast<float4*>(p.y + (long long)pix[k] * p.yps + ch[k]) = o;
-                    if (p.y2) *reinterpret_cast<float4*>(p.y2 + (long long)pix[k] * p.y2ps + ch[k]) = o;
+                    if (p.y) gstv(p.y + (long long)pix[k] * p.yps + ch[k], o);
+                    if (p.y2) gstv(p.y2 + (long long)pix[k] * p.y2ps + ch[k], o);
                 }
             }
         } else {
@@ -129,10 +129,10 @@ epilogue_nhwc_kernel(const NhwcParams p)
                 if (u < hi) {
                     uint32_t pix, c;
                     p.div_cv.divmod(u, pix, c);
-                    float o = nhwc_apply<ACT, AFFINE>(p.x[(long long)pix * p.xps + c], AFFINE ? p.a[c] : 1.0f, AFFINE ? p.b[c] : 0.0f);
-                    if (RES) o = activate_dyn(p.res_act, fmaf(p.ralpha, o, p.rbeta * p.res[(long long)pix * p.rps + c]));
-                    if (p.y) p.y[(long long)pix * p.yps + c] = o;
-                    if (p.y2) p.y2[(long long)pix * p.y2ps + c] = o;
+                    float o = nhwc_apply<ACT, AFFINE>(gld(p.x + ((long long)pix * p.xps + c)), AFFINE ? gld(p.a + c) : 1.0f, AFFINE ? gld(p.b + c) : 0.0f);
+                    if (RES) o = activate_dyn(p.res_act, fmaf(p.ralpha, o, p.rbeta * gld(p.res + ((long long)pix * p.rps + c))));
+                    if (p.y) gst(p.y + ((long long)pix * p.yps + c), o);
+                    if (p.y2) gst(p.y2 + ((long long)pix * p.y2ps + c), o);
                 }
             }
         }
@@ -196,15 +196,15 @@ epilogue_pool_nhwc_kernel(const NhwcPoolParams q)
             if (!on[t]) continue;
             const float* src = p.x + tap[t] * p.xps + c;
             if (VW == 4) {
-                const float4 f = *reinterpret_cast<const float4*>(src);
+                const float4 f = gldv<float4>(src);
                 v[t][0] = f.x; v[t][1] = f.y; v[t][2] = f.z; v[t][3] = f.w;
             } else {
-                v[t][0] = src[0];
+                v[t][0] = gld(src);
             }
         }
         float ca[VW], cb[VW];
 #pragma unroll
-        for (int j = 0; j < VW; ++j) { ca[j] = AFFINE ? p.a[c + j] : 1.0f; cb[j] = AFFINE ? p.b[c + j] : 0.0f; }
+        for (int j = 0; j < VW; ++j) { ca[j] = AFFINE ? gld(p.a + (c + j)) : 1.0f; cb[j] = AFFINE ? gld(p.b + (c + j)) : 0.0f; }
         float m[VW];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -216,13 +216,13 @@ epilogue_pool_nhwc_kernel(const NhwcPoolParams q)
             }
             if (p.y) {
                 float* dst = p.y + tap[t] * p.yps + c;
-                if (VW == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[t][0], v[t][1], v[t][2], v[t][3]);
-                else dst[0] = v[t][0];
+                if (VW == 4) gstv(dst, make_float4(v[t][0], v[t][1], v[t][2], v[t][3]));
+                else gst(dst, v[t][0]);
             }
         }
         float* dst = q.ypool + (long long)opix * q.pps + c;
-        if (VW == 4) *reinterpret_cast<float4*>(dst) = make_float4(m[0], m[1], m[2], m[3]);
-        else dst[0] = m[0];
+        if (VW == 4) gstv(dst, make_float4(m[0], m[1], m[2], m[3]));
+        else gst(dst, m[0]);
     }
 }
 
@@ -257,15 +257,15 @@ upsample_nhwc_kernel(const float* in, long long ips, float* out, long long ops, 
         const long long OW = (long long)W * stride;
         const long long obase = ((long long)b * H * stride + (long long)row * stride) * OW + (long long)col * stride;
         if (VW == 4) {
-            float4 v = *reinterpret_cast<const float4*>(in + (long long)pix * ips + c);
+            float4 v = gldv<float4>(in + (long long)pix * ips + c);
             v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
             for (int dy = 0; dy < stride; ++dy)
                 for (int dx = 0; dx < stride; ++dx)
-                    *reinterpret_cast<float4*>(out + (obase + dy * OW + dx) * ops + c) = v;
+                    gstv(out + (obase + dy * OW + dx) * ops + c, v);
         } else {
-            const float v = in[(long long)pix * ips + c] * scale;
+            const float v = gld(in + ((long long)pix * ips + c)) * scale;
             for (int dy = 0; dy < stride; ++dy)
-                for (int dx = 0; dx < stride; ++dx) out[(obase + dy * OW + dx) * ops + c] = v;
+                for (int dx = 0; dx < stride; ++dx) gst(out + ((obase + dy * OW + dx) * ops + c), v);
         }
     }
 }
@@ -295,17 +295,17 @@ maxpool_nhwc_kernel(const float* in, long long ips, float* out, long long ops, u
                 if (ix < 0 || ix >= W) continue;
                 const float* src = in + (((long long)b * H + iy) * W + ix) * ips + c;
                 if (VW == 4) {
-                    const float4 v = *reinterpret_cast<const float4*>(src);
+                    const float4 v = gldv<float4>(src);
                     m[0] = v.x > m[0] ? v.x : m[0]; m[1] = v.y > m[1] ? v.y : m[1];
                     m[2] = v.z > m[2] ? v.z : m[2]; m[3] = v.w > m[3] ? v.w : m[3];
                 } else {
-                    m[0] = src[0] > m[0] ? src[0] : m[0];
+                    m[0] = gld(src) > m[0] ? gld(src) : m[0];
                 }
             }
         }
         float* dst = out + (long long)opix * ops + c;
-        if (VW == 4) *reinterpret_cast<float4*>(dst) = make_float4(m[0], m[1], m[2], m[3]);
-        else dst[0] = m[0];
+        if (VW == 4) gstv(dst, make_float4(m[0], m[1], m[2], m[3]));
+        else gst(dst, m[0]);
     }
 }
 
@@ -319,12 +319,12 @@ nhwc_to_nchw_kernel(const float* in, long long ips, float* out, long long obs, i
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;       // 32 x 8
     for (int j = ty; j < 32; j += 8) {
         const int pix = p0 + j, c = c0 + tx;
-        if (pix < HW && c < C) tile[j][tx] = in[((long long)b * HW + pix) * ips + c];
+        if (pix < HW && c < C) tile[j][tx] = gld(in + (((long long)b * HW + pix) * ips + c));
     }
     __syncthreads();
     for (int j = ty; j < 32; j += 8) {
         const int c = c0 + j, pix = p0 + tx;
-        if (pix < HW && c < C) out[(long long)b * obs + (long long)c * HW + pix] = tile[tx][j];
+        if (pix < HW && c < C) gst(out + ((long long)b * obs + (long long)c * HW + pix), tile[tx][j]);
     }
 }
 

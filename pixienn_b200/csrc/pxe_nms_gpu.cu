@@ -68,13 +68,13 @@ __global__ void nms_prepare_kernel(const pxe_detection* dets, int n, unsigned lo
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const pxe_detection d = dets[i];
-    key[i] = ((unsigned long long)(~prob_order(d.prob)) << 32) | (unsigned)i;
+    const pxe_detection d = gld(dets + i);
+    gst(key + i, ((unsigned long long)(~prob_order(d.prob)) << 32) | (unsigned)i);
     const float x2 = __fadd_rn(d.x, d.w), y2 = __fadd_rn(d.y, d.h);
     const float xa = fminf(d.x, x2), ya = fminf(d.y, y2), xb = fmaxf(d.x, x2), yb = fmaxf(d.y, y2);
-    rect[i] = Rect{xa, ya, fmaxf(0.0f, __fsub_rn(xb, xa)), fmaxf(0.0f, __fsub_rn(yb, ya))};
-    image[i] = (unsigned)d.batch_id;
-    cls[i] = (unsigned)d.class_id;
+    gst(rect + i, Rect{xa, ya, fmaxf(0.0f, __fsub_rn(xb, xa)), fmaxf(0.0f, __fsub_rn(yb, ya))});
+    gst(image + i, (unsigned)d.batch_id);
+    gst(cls + i, (unsigned)d.class_id);
 }
 
 // after the first sort: order[r] = input index of the r-th record; keys for the two segment sorts
@@ -83,10 +83,10 @@ __global__ void nms_segment_keys_kernel(const unsigned long long* sorted_key, co
 {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
-    const int i = (int)(unsigned)sorted_key[r];
-    order[r] = i;
-    image_key[r] = image[i];
-    group_key[r] = ((unsigned long long)image[i] << 32) | cls[i];
+    const int i = (int)(unsigned)gld(sorted_key + r);
+    gst(order + r, i);
+    gst(image_key + r, gld(image + i));
+    gst(group_key + r, ((unsigned long long)gld(image + i) << 32) | gld(cls + i));
 }
 
 // starts[s] = first position of segment s in a sorted key array; *count = number of segments
@@ -101,7 +101,7 @@ __global__ void nms_segment_starts_kernel(const K* sorted, int n, int* starts, i
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int base = 0; base < n; base += blockDim.x) {
         const int i = base + threadIdx.x;
-        const int flag = (i < n && (i == 0 || sorted[i] != sorted[i - 1])) ? 1 : 0;
+        const int flag = (i < n && (i == 0 || gld(sorted + i) != gld(sorted + (i - 1)))) ? 1 : 0;
         int inc = flag;
         for (int o = 1; o < 32; o <<= 1) {
             const int t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -111,12 +111,12 @@ __global__ void nms_segment_starts_kernel(const K* sorted, int n, int* starts, i
         __syncthreads();
         int before = carry;
         for (int w = 0; w < warp; ++w) before += warp_tot[w];
-        if (flag) starts[before + inc - 1] = i;
+        if (flag) gst(starts + (before + inc - 1), i);
         __syncthreads();
         if (threadIdx.x == blockDim.x - 1) carry = before + inc;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *count = carry;
+    if (threadIdx.x == 0) gst(count, carry);
 }
 
 // Step 2.  members[start..end) = input indices of one image's records in probability order.  An image with at
@@ -133,15 +133,15 @@ nms_cross_class_kernel(const int* members, const int* starts, const int* nseg, i
     Rect* sbox = reinterpret_cast<Rect*>(stage_raw);
     unsigned* scls = reinterpret_cast<unsigned*>(sbox + kImageStage);
     unsigned char* sdead = reinterpret_cast<unsigned char*>(scls + kImageStage);
-    const int segs = *nseg;
+    const int segs = gld(nseg);
     for (int s = blockIdx.x; s < segs; s += gridDim.x) {
-        const int lo = starts[s], hi = s + 1 < segs ? starts[s + 1] : n;
+        const int lo = gld(starts + s), hi = s + 1 < segs ? gld(starts + (s + 1)) : n;
         const int cnt = hi - lo;
         if (cnt <= kImageStage) {
             for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
-                const int j = members[lo + t];
-                sbox[t] = rect[j];
-                scls[t] = cls[j];
+                const int j = gld(members + (lo + t));
+                sbox[t] = gld(rect + j);
+                scls[t] = gld(cls + j);
                 sdead[t] = 0;                              // nothing has been discarded before this step
             }
             __syncthreads();
@@ -154,18 +154,18 @@ nms_cross_class_kernel(const int* members, const int* starts, const int* nseg, i
                 __syncthreads();
             }
             for (int t = threadIdx.x; t < cnt; t += blockDim.x)
-                if (sdead[t]) discard[members[lo + t]] = 1;
+                if (sdead[t]) gst(discard + (gld(members + (lo + t))), 1);
             __syncthreads();
             continue;
         }
         for (int p = lo; p < hi; ++p) {
-            const int i = members[p];
-            if (discard[i]) continue;                      // block-uniform: written before the last barrier
-            const Rect ri = rect[i];
-            const unsigned ci = cls[i];
+            const int i = gld(members + p);
+            if (gld(discard + i)) continue;                      // block-uniform: written before the last barrier
+            const Rect ri = gld(rect + i);
+            const unsigned ci = gld(cls + i);
             for (int q = p + 1 + (int)threadIdx.x; q < hi; q += blockDim.x) {
-                const int j = members[q];
-                if (cls[j] != ci && !discard[j] && rect_iou(rect[j], ri) > 0.9f) discard[j] = 1;
+                const int j = gld(members + q);
+                if (gld(cls + j) != ci && !gld(discard + j) && rect_iou(gld(rect + j), ri) > 0.9f) gst(discard + j, 1);
             }
             __syncthreads();
         }
@@ -183,16 +183,16 @@ nms_group_kernel(const int* members, const int* starts, const int* nseg, int n, 
 {
     __shared__ Rect box[kGroupCap];
     __shared__ unsigned char dead[kGroupCap];
-    const int segs = *nseg;
+    const int segs = gld(nseg);
     for (int s = blockIdx.x; s < segs; s += gridDim.x) {
-        const int lo = starts[s], hi = s + 1 < segs ? starts[s + 1] : n;
+        const int lo = gld(starts + s), hi = s + 1 < segs ? gld(starts + (s + 1)) : n;
         const int count = min(hi - lo, kGroupCap);
         const int t = threadIdx.x;
         int mine = -1;
         if (t < count) {
-            mine = members[lo + t];
-            box[t] = rect[mine];
-            dead[t] = discard[mine];
+            mine = gld(members + (lo + t));
+            box[t] = gld(rect + mine);
+            dead[t] = gld(discard + mine);
         }
         __syncthreads();
         for (int p = 0; p < count; ++p) {
@@ -200,7 +200,7 @@ nms_group_kernel(const int* members, const int* starts, const int* nseg, int n, 
             if (t > p && t < count && !dead[t] && rect_iou(box[t], box[p]) > threshold) dead[t] = 1;
             __syncthreads();
         }
-        if (t < count && dead[t]) discard[mine] = 1;
+        if (t < count && dead[t]) gst(discard + mine, 1);
         __syncthreads();
     }
 }
@@ -209,19 +209,19 @@ nms_group_kernel(const int* members, const int* starts, const int* nseg, int n, 
 __global__ void nms_keep_flags_kernel(const int* order, const unsigned char* discard, int n, unsigned char* keep)
 {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r < n) keep[r] = discard[order[r]] ? 0 : 1;
+    if (r < n) gst(keep + r, gld(discard + (gld(order + r))) ? 0 : 1);
 }
 
 __global__ void nms_gather_kernel(const pxe_detection* dets, const int* kept_order, const int* kept_count,
                                   pxe_detection* out, long long* out_count)
 {
-    const int m = *kept_count;
-    if (blockIdx.x == 0 && threadIdx.x == 0) *out_count = m;
+    const int m = gld(kept_count);
+    if (blockIdx.x == 0 && threadIdx.x == 0) gst(out_count, m);
     for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < m; k += gridDim.x * blockDim.x) {
-        const float4* src = reinterpret_cast<const float4*>(dets + kept_order[k]);
+        const float4* src = reinterpret_cast<const float4*>(dets + gld(kept_order + k));
         float4* dst = reinterpret_cast<float4*>(out + k);
-        dst[0] = src[0];
-        dst[1] = src[1];
+        gst(dst, gld(src));
+        gst(dst + 1, gld(src + 1));
     }
 }
 

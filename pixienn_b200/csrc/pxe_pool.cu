@@ -44,15 +44,15 @@ maxpool_kernel(const PoolParams p)
             for (int kx = 0; kx < p.kernel; ++kx) {
                 const int ix = x0 + kx;
                 if (ix < 0 || ix >= p.W) continue;
-                const float v = plane[iy * p.W + ix];
+                const float v = gld(plane + (iy * p.W + ix));
                 if (best_idx < 0 || v > best) {
                     best = v;
                     best_idx = ix + p.W * (iy + p.H * ((int)c + p.C * (int)b));
                 }
             }
         }
-        p.y[(long long)b * p.ybs + ((long long)c * p.OH + oh) * p.OW + ow] = best;
-        if (WITH_INDEX) p.idx[((long long)b * p.C + c) * p.OH * p.OW + (long long)oh * p.OW + ow] = best_idx;
+        gst(p.y + ((long long)b * p.ybs + ((long long)c * p.OH + oh) * p.OW + ow), best);
+        if (WITH_INDEX) gst(p.idx + (((long long)b * p.C + c) * p.OH * p.OW + (long long)oh * p.OW + ow), best_idx);
     }
 }
 
@@ -78,14 +78,14 @@ maxpool_k2s1_kernel(const PoolParams p, uint32_t planes)
         for (int i = (int)lane; i < n_out; i += 32) {
             const int at = y * W + x;
             const int dx = x + 1 < W ? 1 : 0, dy = y + 1 < H ? W : 0;
-            const float v00 = src[at], v01 = src[at + dx], v10 = src[at + dy], v11 = src[at + dy + dx];
+            const float v00 = gld(src + at), v01 = gld(src + (at + dx)), v10 = gld(src + (at + dy)), v11 = gld(src + (at + dy + dx));
             float best = v00;
             int where = at;
             if (v01 > best) { best = v01; where = at + dx; }
             if (v10 > best) { best = v10; where = at + dy; }
             if (v11 > best) { best = v11; where = at + dy + dx; }
-            dst[i] = best;
-            if (WITH_INDEX) idx[i] = plane_base + where;
+            gst(dst + i, best);
+            if (WITH_INDEX) gst(idx + i, plane_base + where);
             y += step_y; x += step_x;
             if (x >= OW) { x -= OW; ++y; }
         }
@@ -144,17 +144,17 @@ spp_kernel(const SppParams p)
     float* rowmax = tile + HW;
     const float* src = p.x + (long long)b * p.xbs + (long long)c * HW;
     if (p.a || p.act != PXE_ACT_LINEAR || p.yid) {
-        const float ca = p.a ? p.a[c] : 1.0f, cb = p.a ? p.b[c] : 0.0f;
+        const float ca = p.a ? gld(p.a + c) : 1.0f, cb = p.a ? gld(p.b + c) : 0.0f;
         float* yid = p.yid ? p.yid + (long long)b * p.yidbs + (long long)c * HW : nullptr;
         for (int i = threadIdx.x; i < HW; i += kThreads) {
-            float v = src[i];
+            float v = gld(src + i);
             if (p.a) v = fmaf(ca, v, cb);
             v = activate_fast_dyn(p.act, v);
             tile[i] = v;
-            if (yid) yid[i] = v;
+            if (yid) gst(yid + i, v);
         }
     } else {
-        for (int i = threadIdx.x; i < HW; i += kThreads) tile[i] = src[i];
+        for (int i = threadIdx.x; i < HW; i += kThreads) tile[i] = gld(src + i);
     }
     __syncthreads();
     for (int k = 0; k < p.n_pools; ++k) {
@@ -183,7 +183,7 @@ spp_kernel(const SppParams p)
             }
             const float first = tile[ya * p.W + xa];
             if (first != first) m = first;
-            p.y[k][(long long)b * p.ybs[k] + (long long)c * HW + i] = m;
+            gst(p.y[k] + ((long long)b * p.ybs[k] + (long long)c * HW + i), m);
         }
         __syncthreads();
     }
@@ -315,12 +315,12 @@ __device__ __forceinline__ void cascade_cols(const float* S, float* D, int H, in
                 float* row = D + (4 * ys + j) * dw + NC * cg;
 #pragma unroll
                 for (int c = 0; c < NC; ++c)
-                    if (NC * cg + c < W) row[c] = o[c][j];
+                    if (NC * cg + c < W) gst(row + c, o[c][j]);
             } else {
                 Vec t;
                 t.x = o[0][j]; t.y = o[1][j];
                 if constexpr (NC == 4) { t.z = o[2][j]; t.w = o[3][j]; }
-                *reinterpret_cast<Vec*>(D + (4 * ys + j) * dw + NC * cg) = t;
+                gstv(D + (4 * ys + j) * dw + NC * cg, t);        // D: an output plane, or shared memory
             }
         }
         ys += step_y; cg += step_x;
@@ -393,11 +393,11 @@ spp_cascade_kernel(const CascadeParams cp)
         cp.div_c.divmod(plane, b, c);
         const float* src = p.x + (long long)b * p.xbs + (long long)c * HW;
         float* yid = p.yid ? p.yid + (long long)b * p.yidbs + (long long)c * HW : nullptr;
-        const float ca = p.a ? p.a[c] : 1.0f, cb = p.a ? p.b[c] : 0.0f;
+        const float ca = p.a ? gld(p.a + c) : 1.0f, cb = p.a ? gld(p.b + c) : 0.0f;
         bool nan = false, negzero = false;
         if (VEC) {
             for (int u = (int)lane; u < HW / 4; u += 32) {
-                float4 v = reinterpret_cast<const float4*>(src)[u];
+                float4 v = gldv<float4>(src + 4 * u);
                 if (epilogue) {
                     if (p.a) { v.x = fmaf(ca, v.x, cb); v.y = fmaf(ca, v.y, cb); v.z = fmaf(ca, v.z, cb); v.w = fmaf(ca, v.w, cb); }
                     v.x = activate_fast_dyn(p.act, v.x); v.y = activate_fast_dyn(p.act, v.y);
@@ -407,14 +407,14 @@ spp_cascade_kernel(const CascadeParams cp)
                 negzero |= (__float_as_uint(v.x) == 0x80000000u) | (__float_as_uint(v.y) == 0x80000000u)
                            | (__float_as_uint(v.z) == 0x80000000u) | (__float_as_uint(v.w) == 0x80000000u);
                 reinterpret_cast<float4*>(X)[u] = v;             // W == 4*nxg: the plane as it lies in memory
-                if (yid) reinterpret_cast<float4*>(yid)[u] = v;
+                if (yid) gstv(yid + 4 * u, v);
             }
         } else {
             // (columns W .. 4*nxg - 1 of X are never written: they keep the -infinity of the start)
             const int step_y = 32 / W, step_x = 32 - step_y * W;
             int y = (int)lane / W, x = (int)lane - y * W;
             for (int i = (int)lane; i < HW; i += 32) {
-                float v = src[i];
+                float v = gld(src + i);
                 if (epilogue) {
                     if (p.a) v = fmaf(ca, v, cb);
                     v = activate_fast_dyn(p.act, v);
@@ -422,7 +422,7 @@ spp_cascade_kernel(const CascadeParams cp)
                 nan |= v != v;
                 negzero |= __float_as_uint(v) == 0x80000000u;
                 X[y * SW + x] = v;
-                if (yid) yid[i] = v;
+                if (yid) gst(yid + i, v);
                 y += step_y; x += step_x;
                 if (x >= W) { x -= W; ++y; }
             }
@@ -450,7 +450,7 @@ spp_cascade_kernel(const CascadeParams cp)
                     float best = X[ya * SW + xa];
                     for (int iy = ya; iy < yb; ++iy)
                         for (int ix = xa; ix < xb; ++ix) best = keep_first(best, X[iy * SW + ix]);
-                    out[l][i] = best;
+                    gst(out[l] + i, best);
                 }
             }
             __syncwarp();
@@ -476,9 +476,9 @@ avgpool_kernel(const float* x, long long xbs, float* y, long long ybs, int batch
     const int b = (int)(plane / channels), c = (int)(plane - (long long)b * channels);
     const float* src = x + (long long)b * xbs + (long long)c * area;
     float sum = 0.0f;
-    for (int i = lane; i < area; i += 32) sum += src[i];
+    for (int i = lane; i < area; i += 32) sum += gld(src + i);
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) y[(long long)b * ybs + c] = sum / (float)(area > 1 ? area : 1);
+    if (lane == 0) gst(y + ((long long)b * ybs + c), sum / (float)(area > 1 ? area : 1));
 }
 
 }  // namespace

@@ -67,11 +67,11 @@ stem_conv_kernel(const StemParams p)
     // filters (transposed so that 4 output channels are one 128-bit shared-memory read) and coefficients
     for (int i = threadIdx.x; i < CIN * 9 * p.cout; i += kStemThreads) {
         const int k = i / (CIN * 9), r = i - k * (CIN * 9);
-        wsm[r][k] = p.w[i];
+        wsm[r][k] = gld(p.w + i);
     }
     for (int i = threadIdx.x; i < p.cout; i += kStemThreads) {
-        asm_[i] = p.a ? p.a[i] : 1.0f;
-        bsm[i] = p.b ? p.b[i] : 0.0f;
+        asm_[i] = p.a ? gld(p.a + i) : 1.0f;
+        bsm[i] = p.b ? gld(p.b + i) : 0.0f;
     }
     // input patch rows y0-1 .. y0+8, columns x0-1 .. x0+128; zero outside the image
     const float* xin = p.x + (long long)b * p.xbs;
@@ -82,7 +82,7 @@ stem_conv_kernel(const StemParams p)
         const float* src = xin + ((long long)ci * H + gy) * W + x0 - 1;
         for (int px = threadIdx.x & 31; px < kStemTW + 2; px += 32) {
             const int gx = x0 + px - 1;
-            patch[ci][py][px] = (row_in && gx >= 0 && gx < W) ? src[px] : 0.0f;
+            patch[ci][py][px] = (row_in && gx >= 0 && gx < W) ? gld(src + px) : 0.0f;
         }
     }
     __syncthreads();
@@ -146,12 +146,13 @@ stem_conv_kernel(const StemParams p)
                 float* dst = p.y + (((long long)b * H + gy) * W + gx + px) * p.yps + k0;
                 if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
                     // one 256-bit store: the pixel's 8 channels are exactly one 32-byte sector
+                    if (gcheck(dst) && gcheck(dst + 7))
                     asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                                  :: "l"(dst), "f"(acc[px][0]), "f"(acc[px][1]), "f"(acc[px][2]), "f"(acc[px][3]),
                                     "f"(acc[px][4]), "f"(acc[px][5]), "f"(acc[px][6]), "f"(acc[px][7]) : "memory");
                 } else {
-                    *reinterpret_cast<float4*>(dst) = make_float4(acc[px][0], acc[px][1], acc[px][2], acc[px][3]);
-                    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[px][4], acc[px][5], acc[px][6], acc[px][7]);
+                    gstv(dst, make_float4(acc[px][0], acc[px][1], acc[px][2], acc[px][3]));
+                    gstv(dst + 4, make_float4(acc[px][4], acc[px][5], acc[px][6], acc[px][7]));
                 }
             }
         } else {
@@ -159,11 +160,11 @@ stem_conv_kernel(const StemParams p)
             for (int k = 0; k < 8; ++k) {
                 float* dst = p.y + (long long)b * p.ybs + ((long long)(k0 + k) * H + gy) * W + gx;
                 if (gx + 3 < W && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                    *reinterpret_cast<float4*>(dst) = make_float4(acc[0][k], acc[1][k], acc[2][k], acc[3][k]);
+                    gstv(dst, make_float4(acc[0][k], acc[1][k], acc[2][k], acc[3][k]));
                 } else {
 #pragma unroll
                     for (int px = 0; px < 4; ++px)
-                        if (gx + px < W) dst[px] = acc[px][k];
+                        if (gx + px < W) gst(dst + px, acc[px][k]);
                 }
             }
         }

@@ -32,6 +32,20 @@ def test_planner_symbols_exported_and_bound():
     assert sorted(capi.PLAN_PROTOTYPES) == names
 
 
+def test_debug_symbols_exported_and_answer_unsupported():
+    import ctypes as C
+    names = declared_in_header("pxe_debug.h")
+    assert sorted(capi.DEBUG_PROTOTYPES) == names and len(names) == 3
+    L = capi.lib()
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in pxe_debug.h but not exported by libpxe.so"
+    assert L.pxe_debug_bounds_checked() == 0                  # the ordinary build
+    rep = capi.BoundsReport()
+    assert L.pxe_debug_read_report(C.byref(rep), 0) == capi.PXE_ERR_UNSUPPORTED
+    assert L.pxe_debug_set_allocations(None, None, 0) == capi.PXE_ERR_UNSUPPORTED
+    assert C.sizeof(capi.BoundsReport) == 80
+
+
 def test_compat_tier_symbols_exported():
     L = capi.lib()
     for n in capi.COMPAT_SYMBOLS:
