@@ -5,6 +5,7 @@
 
 #include "pxe.h"
 #include "pxe_plan.h"
+#include "pxe_debug.h"
 
 #define SIZE(t) printf(#t " %zu\n", sizeof(t))
 #define OFF(t, f) printf(#t "." #f " %zu\n", offsetof(t, f))
@@ -21,5 +22,6 @@ int main(void)
     SIZE(pxe_bn_backward_desc); OFF(pxe_bn_backward_desc, save_scale);
     SIZE(pxe_layer_desc);
     SIZE(pxe_step);
+    SIZE(pxe_bounds_report); OFF(pxe_bounds_report, address); OFF(pxe_bounds_report, file);
     return 0;
 }

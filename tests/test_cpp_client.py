@@ -35,7 +35,7 @@ def test_ctypes_mirrors_have_the_layout_the_c_compiler_gives(tmp_path):
                "pxe_epilogue_nhwc_desc": capi.EpilogueNhwcDesc, "pxe_yolo_decode_desc": capi.YoloDecodeDesc,
                "pxe_centernet_decode_desc": capi.CenterNetDecodeDesc, "pxe_yolo_loss_desc": capi.YoloLossDesc,
                "pxe_bn_train_desc": capi.BnTrainDesc, "pxe_bn_backward_desc": capi.BnBackwardDesc,
-               "pxe_layer_desc": capi.LayerDesc, "pxe_step": capi.PlanStep}
+               "pxe_layer_desc": capi.LayerDesc, "pxe_step": capi.PlanStep, "pxe_bounds_report": capi.BoundsReport}
     for name, cls in mirrors.items():
         assert C.sizeof(cls) == int(out[name]), (name, C.sizeof(cls), out[name])
     for key, value in out.items():
