@@ -18,7 +18,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SUITES = ["test_gpu_epilogue.py", "test_gpu_pool_move.py", "test_gpu_heads.py", "test_gpu_nhwc.py", "test_gpu_guard_zones.py",
-          "test_gpu_bn_train.py", "test_gpu_model.py", "test_gpu_graph_parity.py", "test_zz_no_alloc.py"]
+          "test_gpu_bn_train.py", "test_gpu_model.py", "test_gpu_graph_parity.py", "test_gpu_vs_reference_cuda.py",
+          "test_gpu_torch_spec.py", "test_zz_no_alloc.py"]
 
 
 def checked_python(code: str) -> subprocess.CompletedProcess:

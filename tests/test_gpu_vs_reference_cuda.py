@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from pixienn_b200 import ops, synth
+from pixienn_b200 import capi, ops, synth
 from test_gpu_epilogue import bn, close, dev
 
 pytestmark = pytest.mark.gpu
@@ -375,7 +375,10 @@ def test_yolo_loss_three_way(cuda, oracle, refcu, prior):
                ref_c.data_ptr(), None, truths.shape[1], B, len(masks), 6, ch // len(masks) - 5, W, H, 416, 416,
                kw["ignore_thr"], kw["truth_thr"], kw["coord_scale"], kw["object_scale"], kw["no_object_scale"], kw["class_scale"])
     torch.cuda.synchronize()
-    assert torch.equal(mine_d, ref_d)                      # the same expressions: identical deltas
+    if capi.lib().pxe_debug_bounds_checked():              # the bounds-checked build: the compiler contracts some
+        close(mine_d.cpu().numpy(), ref_d.cpu().numpy(), atol=2e-6)      # multiply-adds differently (last-bit differences)
+    else:
+        assert torch.equal(mine_d, ref_d)                  # the same expressions: identical deltas
     close(mine_d.cpu().numpy(), want_delta, atol=2e-6)
     assert np.count_nonzero(want_delta != delta0) > 500
     for got in (mine_s.cpu().numpy(), ref_s.cpu().numpy()):
