@@ -46,6 +46,20 @@ def test_debug_symbols_exported_and_answer_unsupported():
     assert C.sizeof(capi.BoundsReport) == 80
 
 
+def test_checked_build_exports_the_same_symbols():
+    """libpxe_checked.so (the sources with -DPXE_BOUNDS_CHECK) is the same ABI; only pxe_debug_bounds_checked differs."""
+    import ctypes as C
+    from pixienn_b200 import debug
+    L = C.CDLL(debug.CHECKED_LIB_PATH)
+    for header in ("pxe.h", "pxe_plan.h", "pxe_debug.h"):
+        for n in declared_in_header(header):
+            assert hasattr(L, n), f"{n} declared in {header} but not exported by libpxe_checked.so"
+    for n in capi.COMPAT_SYMBOLS:
+        assert hasattr(L, n), n
+    assert L.pxe_debug_bounds_checked() == 1
+    assert L.pxe_debug_read_report(None, 0) == capi.PXE_ERR_BAD_ARG       # argument check comes before any CUDA call
+
+
 def test_compat_tier_symbols_exported():
     L = capi.lib()
     for n in capi.COMPAT_SYMBOLS:

@@ -4,9 +4,8 @@
 of every kernel is looked up in the table of live device allocations first; one that is outside them, crosses the end
 of one or is misaligned is skipped and recorded -- nothing traps.  The suites run in a child pytest process (the
 library is loaded once per process); tests/conftest.py re-arms the table before every library call and fails a test
-whose kernels had an access refused.  Left out: the full-size cases (a binary search per access), the C++ client and
-the comparison with the reference's CUDA kernels (both link libpxe.so itself and allocate outside PyTorch), and the
-CUDA-graph cases (a table cannot be installed while a stream is being captured).
+whose kernels had an access refused.  Left out: the full-size cases (a binary search per access), the C++ client
+(it links libpxe.so itself and allocates outside PyTorch), and the CUDA-graph cases (a table cannot be installed while a stream is being captured).
 """
 import ctypes as C
 import os
