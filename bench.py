@@ -1130,6 +1130,8 @@ def run_bn_train(args):
     shapes = [(32, 208, 208), (64, 104, 104), (128, 52, 52), (256, 26, 26), (512, 13, 13)]
     if args.sweep_shapes:
         shapes = shapes[:args.sweep_shapes]
+    if args.bn_shapes:
+        shapes = [tuple(int(v) for v in s.split("x")) for s in args.bn_shapes.split(",")]
     cells = bn_train_cells(args, shapes)
     peak, peak_src = measured_peaks()
     B = args.batch
@@ -1170,6 +1172,7 @@ def main():
                     help="sweep with the layer's coefficients folded once (pxe_fold_bn) instead of the raw BN parameters per launch")
     ap.add_argument("--model", default="yolov3-608", help="model graph for --workload epilogue-compare")
     ap.add_argument("--pool-cases", default="spp,maxpool", help="kernel families for --workload pools")
+    ap.add_argument("--bn-shapes", default="", help="--workload bn-train: CxHxW[,CxHxW...] instead of the sweep's five shapes")
     ap.add_argument("--nms-boxes", type=int, default=1000, help="candidate boxes per image for --workload nms")
     ap.add_argument("--no-cudnn-benchmark", action="store_true", help="skip cuDNN's algorithm search (profiling runs)")
     ap.add_argument("--layout", default="nchw", choices=["nchw", "nhwc"],

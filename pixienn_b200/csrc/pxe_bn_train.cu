@@ -147,13 +147,20 @@ struct ForwardFinal {
 
 __global__ void bn_forward_final_kernel(const ForwardFinal p)
 {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    // a warp per channel: the lanes take the channel's partial sums side by side (a single thread walking them pays one
+    // memory latency per partial: 10 us for 43 of them), then one shuffle tree in double precision
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= p.C) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int s = 0; s < p.splits; ++s) {
+    for (int s = lane; s < p.splits; s += 32) {
         const float2 t = gld(p.partial + ((long long)c * p.splits + s));
         s1 += t.x; s2 += t.y;
     }
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane != 0) return;
     const double n = (double)p.n;
     const float mean = (float)((double)gld(p.x + ((long long)c * p.HW)) + s1 / n);
     double var_d = (s2 - s1 * s1 / n) / n;
@@ -187,13 +194,20 @@ struct BackwardFinal {
 
 __global__ void bn_backward_final_kernel(const BackwardFinal p)
 {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    // a warp per channel: the lanes take the channel's partial sums side by side (a single thread walking them pays one
+    // memory latency per partial: 10 us for 43 of them), then one shuffle tree in double precision
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= p.C) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int s = 0; s < p.splits; ++s) {
+    for (int s = lane; s < p.splits; s += 32) {
         const float2 t = gld(p.partial + ((long long)c * p.splits + s));
         s1 += t.x; s2 += t.y;
     }
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane != 0) return;
     float inv_fwd, inv_bwd;
     if (p.eps_mode == PXE_BN_EPS_CPU) {
         const float var = gld(p.save_scale + c);
@@ -400,7 +414,7 @@ extern "C" int pxe_batchnorm_forward_training(pxe_stream_t stream, const pxe_bn_
     ff.coeff = reinterpret_cast<float2*>(coeff4);
     ff.factor = d.exp_avg_factor; ff.eps = d.eps; ff.eps_mode = d.eps_mode;
     ff.C = d.channels; ff.HW = (int)sh.hw; ff.splits = sh.splits; ff.n = (long long)d.batch * sh.hw;
-    bn_forward_final_kernel<<<(d.channels + 127) / 128, 128, 0, s>>>(ff);
+    bn_forward_final_kernel<<<(d.channels + 3) / 4, 128, 0, s>>>(ff);
     PXE_LAUNCH_OK("bn_forward_final_kernel");
 
     ApplyParams ap{};
@@ -456,7 +470,7 @@ extern "C" int pxe_batchnorm_backward(pxe_stream_t stream, const pxe_bn_backward
     bf.partial = partial; bf.gamma = d.gamma; bf.save_mean = d.save_mean; bf.save_scale = d.save_scale;
     bf.dgamma = d.dgamma; bf.dbeta = d.dbeta; bf.coeff = coeff4;
     bf.eps = d.eps; bf.eps_mode = d.eps_mode; bf.C = d.channels; bf.splits = sh.splits; bf.n = (long long)d.batch * sh.hw;
-    bn_backward_final_kernel<<<(d.channels + 127) / 128, 128, 0, s>>>(bf);
+    bn_backward_final_kernel<<<(d.channels + 3) / 4, 128, 0, s>>>(bf);
     PXE_LAUNCH_OK("bn_backward_final_kernel");
 
     ApplyParams ap{};
