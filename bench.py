@@ -15,6 +15,7 @@ by image across ranks; there is no collective on the data path.
 Other workloads (not run by default): --workload sweep (the isolated fused-epilogue sweep),
 --workload centernet (the CenterNet head decode), --workload pools (SPP block and stand-alone max pools),
 --workload bn-train (batch normalisation with batch statistics, forward and backward),
+--workload aux (the kernels no model run or sweep times: generic pools and moves, small heads, NMS, training-side),
 --workload yolov3-tiny | yolov7.
 """
 from __future__ import annotations
@@ -1146,6 +1147,148 @@ def run_bn_train(args):
                       "cells": cells}), flush=True)
 
 
+def run_aux(args):
+    """The kernels no model benchmark and no sweep times: the generic pools and moves, the small heads, device NMS and the
+    training-side kernels, each at a model-size shape.  Two buffer sets alternate (every set is larger than L2 or the
+    pair is); CUDA events around bursts of eight calls, median of `steps` bursts; algorithmic bytes per call as stated in
+    each cell."""
+    import torch
+    from pixienn_b200 import capi, ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak, peak_src = measured_peaks()
+    gen = torch.Generator(dev).manual_seed(SEED)
+    B = args.batch
+    rnd = lambda *shape: torch.randn(shape, device=dev, generator=gen)
+    cells = []
+
+    def timed(name, shape, nbytes, make, call, note=""):
+        sets = [make() for _ in range(2)]
+        for i in range(max(args.warmup, 2)):
+            call(sets[i % 2])
+        torch.cuda.synchronize()
+        burst = 8                                          # calls per event pair: launch gaps do not count as kernel time
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, z in ev:
+            a.record()
+            for i in range(burst):
+                call(sets[i % 2])
+            z.record()
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(z) / burst for a, z in ev)
+        ms = ts[len(ts) // 2]
+        cell = {"kernel": name, "shape": shape, "us": round(ms * 1e3, 1)}
+        if nbytes:
+            cell.update(MB=round(nbytes / 1e6, 1), GBps=round(nbytes / ms / 1e6, 1), frac_measured=round(nbytes / ms / 1e6 / peak, 3))
+        if note:
+            cell["note"] = note
+        cells.append(cell)
+        del sets
+        torch.cuda.empty_cache()
+
+    C1, H1 = 64, 104                                    # [B, 64, 104, 104]: 177 MB at 64 images
+    n1 = B * C1 * H1 * H1
+    big = [B, C1, H1, H1]
+    for act in ("leaky", "mish"):
+        timed(f"activation gradient ({act})", big, 12 * n1, lambda: (rnd(*big), rnd(*big)),
+              lambda t, act=act: ops.activation_gradient(act, t[0], t[1]), "x and delta read, delta written")
+    timed("bias gradient", big, 4 * n1, lambda: (torch.zeros(C1, device=dev), rnd(*big)), lambda t: ops.backward_bias(t[0], t[1]),
+          "delta read once")
+    timed("connected-layer bias gradient", [4096, 1000], 4 * 4096 * 1000, lambda: (torch.zeros(1000, device=dev), rnd(4096, 1000)),
+          lambda t: ops.backward_bias(t[0], t[1]))
+
+    def pool_case():
+        x = rnd(*big)
+        y, idx = ops.maxpool(x, 2, 2, 1, with_indexes=True)
+        return rnd(*y.shape), idx, torch.zeros_like(x)
+    half = [B, C1, H1 // 2, H1 // 2]
+    timed("max-pool backward (2x2 / 2)", half, 16 * (n1 // 4), pool_case, lambda t: ops.maxpool_backward(t[0], t[1], t[2]),
+          "delta and index read, one float added in place per output")
+    timed("upsample backward (x2)", half, 4 * n1 + 8 * (n1 // 4), lambda: (rnd(*half), rnd(*big)),
+          lambda t: ops.upsample_backward(t[0], t[1], 2, 1.0), "four outputs read, one input updated")
+    timed("clip", big, 8 * n1, lambda: (rnd(*big),), lambda t: ops.constrain(t[0], 1.0))
+    timed("product", big, 12 * n1, lambda: (rnd(*big), rnd(*big)), lambda t: ops.mul(t[0], t[1]))
+    timed("Adam step", big, 16 * n1, lambda: (rnd(*big), rnd(*big), rnd(*big).abs_()),
+          lambda t: ops.adam_update(t[0], t[1], t[2], 0.9, 0.999, 1e-3, 1e-8, 10))
+    timed("uniform fill", big, 4 * n1, lambda: (torch.empty(big, device=dev),), lambda t: ops.random_uniform(t[0], 0.0, 1.0))
+    timed("normal fill", big, 4 * n1, lambda: (torch.empty(big, device=dev),), lambda t: ops.random_normal(t[0], 0.0, 1.0))
+    timed("softmax cross entropy", [n1], 16 * n1, lambda: (torch.rand(n1, device=dev, generator=gen), (rnd(n1) > 1.5).float()),
+          lambda t: ops.softmax_cross_entropy(t[0], t[1]), "prediction and truth read, delta and error written (allocated per call)")
+
+    # YOLO loss on the three heads of YOLOv3-608 and CenterNet loss on a 128x128 head
+    def yolo_case(hw):
+        out = torch.rand((B, 255, hw, hw), device=dev, generator=gen)
+        slots = B * 3 * hw * hw
+        truths = torch.rand((B, 30, 5), device=dev, generator=gen) * 0.8 + 0.1
+        truths[:, :, 4] = torch.randint(0, 80, (B, 30), device=dev, generator=gen).float()
+        cls = torch.full((slots,), -1, device=dev, dtype=torch.int32)
+        pick = torch.randint(0, slots, (B * 10,), device=dev, generator=gen)
+        cls[pick] = torch.randint(0, 80, (B * 10,), device=dev, generator=gen).int()
+        return (out, torch.zeros_like(out), truths, torch.full((B,), 10, device=dev, dtype=torch.int32), cls,
+                torch.randint(0, 9, (slots,), device=dev, generator=gen).int(), torch.rand((slots, 4), device=dev, generator=gen) * 0.8 + 0.1,
+                torch.tensor([0, 1, 2], device=dev, dtype=torch.int32),
+                torch.tensor([10, 13, 16, 30, 33, 23, 30, 61, 62, 45, 59, 119, 116, 90, 156, 198, 373, 326], device=dev, dtype=torch.float32),
+                torch.zeros(12, device=dev), torch.zeros(1, device=dev))
+    for hw in (76, 38):
+        timed("YOLO loss", [B, 255, hw, hw], 8 * B * 255 * hw * hw, lambda hw=hw: yolo_case(hw),
+              lambda t: ops.yolo_loss(*t, 608, 608, ignore_thr=0.7, truth_thr=1.0), "head read, delta written; 10 truths per image")
+
+    def cn_case():
+        out = torch.rand((B, 24, 128, 128), device=dev, generator=gen)
+        return (out, torch.zeros_like(out), torch.rand((B, 20, 128, 128), device=dev, generator=gen) ** 8,
+                torch.rand((B, 2, 128, 128), device=dev, generator=gen), torch.rand((B, 2, 128, 128), device=dev, generator=gen),
+                (torch.rand((B, 128, 128), device=dev, generator=gen) > 0.999).float(), torch.zeros(3, device=dev))
+    ncn = B * 128 * 128
+    timed("CenterNet loss", [B, 24, 128, 128], 4 * ncn * (20 * 3 + 1), cn_case, lambda t: ops.centernet_loss(*t, 1.0 / B),
+          "heat map, target and delta of the 20 classes; the mask; size / offset terms only where the mask is set")
+
+    # generic pools and moves
+    for k, st in ((3, 2), (3, 1)):
+        pad = k - 1
+        oh = ops.maxpool_out_dim(H1, k, st, pad)
+        for widx in (False, True):
+            timed(f"generic max pool {k}x{k} / {st}" + (" with indexes" if widx else ""), big, 4 * n1 + (8 if widx else 4) * B * C1 * oh * oh,
+                  lambda: (rnd(*big),), lambda t, k=k, st=st, pad=pad, widx=widx: ops.maxpool(t[0], k, st, pad, with_indexes=widx),
+                  "output allocated per call")
+    timed("global average pool", [B, 1024, 19, 19], 4 * B * 1024 * 361, lambda: (rnd(B, 1024, 19, 19),), lambda t: ops.avgpool(t[0]))
+    q = [B, C1, 52, 52]
+    nq = B * C1 * 52 * 52
+    timed("upsample x3 (scalar form)", q, 4 * nq * 10, lambda: (rnd(*q), torch.empty((B, C1, 156, 156), device=dev)),
+          lambda t: ops.upsample(t[0], 3, 1.0, out=t[1]))
+    timed("shortcut across shapes", [B, 128, 52, 52], 12 * B * 64 * 52 * 52, lambda: (rnd(*big), rnd(B, 128, 52, 52)),
+          lambda t: ops.shortcut_general(B, H1, H1, C1, t[0], 52, 52, 128, 1.0, 1.0, t[1]),
+          "[B,64,104,104] sampled with stride 2 into the first 64 channels of [B,128,52,52]")
+    timed("route copy (two sources)", [B, 384, 52, 52], 8 * B * 384 * 52 * 52,
+          lambda: ([rnd(B, 128, 52, 52), rnd(B, 256, 52, 52)], torch.empty((B, 384, 52, 52), device=dev)),
+          lambda t: ops.concat(t[0], out=t[1]))
+    timed("CenterNet head activation", [B, 24, 128, 128], 8 * B * 24 * 128 * 128, lambda: (rnd(B, 24, 128, 128), torch.empty((B, 24, 128, 128), device=dev)),
+          lambda t: ops.centernet_activate(t[0], 20, -2.19, out=t[1]))
+    timed("softmax layer", [B * 64, 1000], 8 * B * 64 * 1000, lambda: (rnd(B * 64, 1000), torch.empty((B * 64, 1000), device=dev)),
+          lambda t: ops.softmax(t[0], out=t[1]), "rows of 1000; the row is read three times, twice from L1 / L2")
+    timed("Region head forward", [B, 425, 19, 19], 8 * B * 425 * 361, lambda: (rnd(B, 425, 19, 19),),
+          lambda t: ops.region_forward(t[0], 5, 4, 80), "NCHW in, per-box records out (allocated per call)")
+
+    # device NMS: 1000 candidates per image
+    def nms_case():
+        n = B * 1000
+        d = torch.zeros((n, 8), device=dev, dtype=torch.float32)
+        d[:, 0:2] = torch.rand((n, 2), device=dev, generator=gen) * 500
+        d[:, 2:4] = torch.rand((n, 2), device=dev, generator=gen) * 100 + 10
+        d[:, 4] = torch.rand(n, device=dev, generator=gen)
+        di = d.view(torch.int32).clone()
+        di[:, 5] = torch.randint(0, 80, (n,), device=dev, generator=gen).int()
+        di[:, 6] = torch.arange(n, device=dev, dtype=torch.int32) // 1000
+        ws = torch.empty(max(int(capi.lib().pxe_nms_workspace_bytes(n)), 256), device=dev, dtype=torch.uint8)
+        return di, torch.empty((n, 8), device=dev, dtype=torch.int32), ws
+    timed("device NMS", [B, 1000], 0, nms_case, lambda t: ops.nms_device(t[0], t[0].shape[0], 0.4, out=t[1], workspace=t[2]),
+          "1000 candidates per image, 80 classes: every launch of pxe_nms")
+    print(json.dumps({"metric": "auxiliary kernels, HBM bandwidth", "value": cells[0]["GBps"], "unit": "GB/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "peak": peak, "peak_source": peak_src,
+                      "config": {"workload": f"kernels outside the model benchmarks and the sweeps, {B} images", "l2": "two buffer sets alternate",
+                                 "timing": "CUDA events around bursts of 8 calls, median of steps"},
+                      "cells": cells}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1213,6 +1356,8 @@ def main():
         return run_pools(args)
     if args.workload == "bn-train":
         return run_bn_train(args)
+    if args.workload == "aux":
+        return run_aux(args)
     return run_model(args)
 
 

@@ -12,6 +12,7 @@
 // Sums: the reference accumulates with atomicAdd (max-pool and upsample backward) or in a fixed 512-way split
 // (bias gradient), so its own results depend on thread timing in the last bits.  Here every sum is taken in a
 // fixed order -- the same call gives the same bits every time -- and agrees with the reference to rounding.
+#include <cooperative_groups.h>
 #include <stdint.h>
 
 #include "pxe_common.cuh"
@@ -87,36 +88,90 @@ int launch_gradient(cudaStream_t s, const float* x, float* delta, size_t n, int 
 }
 
 // ---------------------------------------------------------------- bias gradient
-// bias_updates[f] += sum over images and positions of delta[b, f, :].  One block per filter; every thread sums
-// its strided share image by image, the block combines the 256 partial sums in a fixed tree.
+// bias_updates[f] += sum over images and positions of delta[b, f, :].  A thread-block cluster per filter: its blocks
+// take consecutive segments of the filter's planes, every thread sums its strided share image by image, a block
+// combines its 256 partial sums in a fixed tree, and the cluster's first block adds the blocks' sums in rank order out
+// of their shared memory (distributed shared memory: no scratch buffer, no atomics, the same bits every run).  One
+// block per filter, as the reference launches it, leaves a 64-filter layer on 64 of the machine's 148 SMs.
+namespace cg = cooperative_groups;
+
+template <bool VEC>
 __global__ void __launch_bounds__(256)
-backward_bias_kernel(float* bias_updates, const float* __restrict__ delta, int batch, int n, int size)
+backward_bias_kernel(float* bias_updates, const float* __restrict__ delta, int batch, int n, int size, int segment)
 {
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned ranks = cluster.num_blocks(), rank = cluster.block_rank();
     __shared__ float part[256];
-    const int f = blockIdx.x;
-    float sum = 0.0f;
-    for (int b = 0; b < batch; ++b) {
-        const float* row = delta + ((size_t)b * n + f) * size;
-        for (int i = threadIdx.x; i < size; i += 256) sum += gld(row + i);
+    __shared__ float block_sum;
+    const int f = blockIdx.x / ranks;
+    const int lo = (int)rank * segment, hi = min(size, lo + segment);
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    // the segment of every image as one index space, four loads in flight per thread
+    const int per_image = hi > lo ? (VEC ? (hi - lo) / 4 : hi - lo) : 0;
+    const int total = batch * per_image;                       // the host checks that batch * size fits an int
+    const float* base = delta + (size_t)f * size + lo;
+    const size_t image_stride = (size_t)n * size;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * 256) {
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int id = i0 + k * 256;
+            v[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (id < total) {
+                const int b = id / per_image, i = id - b * per_image;
+                if (VEC) v[k] = gld(reinterpret_cast<const float4*>(base + b * image_stride) + i);
+                else v[k].x = gld(base + b * image_stride + i);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { s0 += v[k].x; s1 += v[k].y; s2 += v[k].z; s3 += v[k].w; }
     }
-    part[threadIdx.x] = sum;
+    part[threadIdx.x] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1) {
         if (threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0) gst(bias_updates + f, gld(bias_updates + f) + part[0]);
+    if (threadIdx.x == 0) block_sum = part[0];
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        float total = 0.0f;
+        for (unsigned r = 0; r < ranks; ++r) total += *cluster.map_shared_rank(&block_sum, r);
+        gst(bias_updates + f, gld(bias_updates + f) + total);
+    }
+    cluster.sync();                                    // the other blocks' shared memory stays until it has been read
 }
 
-// size == 1 (connected layers): one thread per output, images summed in order (src/BiasKernels.cu:39-53).
+// size == 1 (connected layers; the reference: one thread per output, src/BiasKernels.cu:39-53).  A block is 32
+// outputs x 8 phases of the batch, a cluster's blocks take consecutive parts of the batch; phases, then blocks, are
+// added in a fixed order.
 __global__ void __launch_bounds__(256)
-backward_bias_conn_kernel(float* bias_updates, const float* __restrict__ delta, int batch, int n)
+backward_bias_conn_kernel(float* bias_updates, const float* __restrict__ delta, int batch, int n, int segment)
 {
-    const int i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= n) return;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned ranks = cluster.num_blocks(), rank = cluster.block_rank();
+    __shared__ float part[8][32];
+    __shared__ float block_sum[32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int i = (int)(blockIdx.x / ranks) * 32 + tx;
+    const int lo = (int)rank * segment, hi = min(batch, lo + segment);
     float sum = 0.0f;
-    for (int b = 0; b < batch; ++b) sum += gld(delta + ((size_t)b * n + i));
-    gst(bias_updates + i, gld(bias_updates + i) + sum);
+    if (i < n)
+        for (int b = lo + ty; b < hi; b += 8) sum += gld(delta + ((size_t)b * n + i));
+    part[ty][tx] = sum;
+    __syncthreads();
+    if (ty == 0) {
+        float t = part[0][tx];
+        for (int k = 1; k < 8; ++k) t += part[k][tx];
+        block_sum[tx] = t;
+    }
+    cluster.sync();
+    if (rank == 0 && ty == 0 && i < n) {
+        float total = 0.0f;
+        for (unsigned r = 0; r < ranks; ++r) total += *cluster.map_shared_rank(&block_sum[tx], r);
+        gst(bias_updates + i, gld(bias_updates + i) + total);
+    }
+    cluster.sync();
 }
 
 // ---------------------------------------------------------------- max-pool backward
@@ -153,42 +208,78 @@ upsample_backward_kernel(float* acc, const float* __restrict__ out, size_t n_in,
 }
 
 // ---------------------------------------------------------------- clip / product
+// VEC: the tensors are 16-byte aligned, so four elements move per access; the last n % 4 go one by one.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 constrain_kernel(float* x, size_t n, float alpha)
 {
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256)
+    const size_t stride = (size_t)gridDim.x * 256, first = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t n4 = VEC ? n >> 2 : 0;
+    for (size_t i = first; i < n4; i += stride) {
+        float4 v = gld(reinterpret_cast<const float4*>(x) + i);
+        v.x = fminf(alpha, fmaxf(-alpha, v.x)); v.y = fminf(alpha, fmaxf(-alpha, v.y));
+        v.z = fminf(alpha, fmaxf(-alpha, v.z)); v.w = fminf(alpha, fmaxf(-alpha, v.w));
+        gst(reinterpret_cast<float4*>(x) + i, v);
+    }
+    for (size_t i = (n4 << 2) + first; i < n; i += stride)
         gst(x + i, fminf(alpha, fmaxf(-alpha, gld(x + i))));                    // src/CudaUtils.cu:122-129
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 mul_kernel(const float* __restrict__ x, float* y, size_t n)
 {
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) gst(y + i, gld(x + i) * gld(y + i));
+    const size_t stride = (size_t)gridDim.x * 256, first = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t n4 = VEC ? n >> 2 : 0;
+    for (size_t i = first; i < n4; i += stride) {
+        const float4 a = gld(reinterpret_cast<const float4*>(x) + i);
+        float4 b = gld(reinterpret_cast<const float4*>(y) + i);
+        b.x = a.x * b.x; b.y = a.y * b.y; b.z = a.z * b.z; b.w = a.w * b.w;
+        gst(reinterpret_cast<float4*>(y) + i, b);
+    }
+    for (size_t i = (n4 << 2) + first; i < n; i += stride) gst(y + i, gld(x + i) * gld(y + i));
 }
 
 // ---------------------------------------------------------------- random fills
 // The reference draws element i from thrust::default_random_engine (the minimal-standard generator,
 // x <- 48271 x mod 2^31-1, seed 1) advanced i steps (src/CudaUtils.cu:53-60, 103-109).  The state after i + 1
 // steps is 48271^(i+1) mod (2^31-1): a modular power, so every element is independent of the others, as there.
-__device__ __forceinline__ uint32_t minstd_after(uint64_t steps)
+// a * b mod 2^31-1 for a, b below the modulus: 2^31 = 1 (mod 2^31-1), so the high part of the product folds onto the low
+__device__ __forceinline__ uint32_t minstd_mul(uint32_t a, uint32_t b)
 {
     const uint64_t M = 2147483647ull;
-    uint64_t result = 1, base = 48271ull;
+    const uint64_t p = (uint64_t)a * b;
+    uint64_t r = (p & M) + (p >> 31);
+    r = (r & M) + (r >> 31);
+    return (uint32_t)(r >= M ? r - M : r);
+}
+
+__device__ __forceinline__ uint32_t minstd_after(uint64_t steps)
+{
+    uint32_t result = 1, base = 48271u;
     while (steps) {
-        if (steps & 1ull) result = result * base % M;
-        base = base * base % M;
+        if (steps & 1ull) result = minstd_mul(result, base);
+        base = minstd_mul(base, base);
         steps >>= 1;
     }
-    return (uint32_t)result;
+    return result;
 }
+
+// A thread's elements are a whole grid apart: it raises the generator to its first element's power once and then
+// jumps from one element to the next with one multiplication by 48271^(grid stride).
 
 // Uniform on [a, b): the engine's value mapped to [0, 1) as (x - 1) / 2^31 (its range is 1 .. 2^31-2).
 __global__ void __launch_bounds__(256)
 random_uniform_kernel(float* out, size_t n, float a, float b)
 {
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
-        const float u = (float)(minstd_after(i + 1) - 1u) / 2147483648.0f;
+    const size_t first = (size_t)blockIdx.x * 256 + threadIdx.x, stride = (size_t)gridDim.x * 256;
+    if (first >= n) return;
+    uint32_t state = minstd_after(first + 1);
+    const uint32_t jump = minstd_after(stride);
+    for (size_t i = first; i < n; i += stride) {
+        const float u = (float)(state - 1u) / 2147483648.0f;
         gst(out + i, u * (b - a) + a);
+        state = minstd_mul(state, jump);
     }
 }
 
@@ -197,25 +288,40 @@ random_uniform_kernel(float* out, size_t n, float a, float b)
 __global__ void __launch_bounds__(256)
 random_normal_kernel(float* out, size_t n, float mean, float stddev)
 {
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
-        const float u = ((float)(minstd_after(i + 1) - 1u) + 0.5f) / 2147483648.0f;
+    const size_t first = (size_t)blockIdx.x * 256 + threadIdx.x, stride = (size_t)gridDim.x * 256;
+    if (first >= n) return;
+    uint32_t state = minstd_after(first + 1);
+    const uint32_t jump = minstd_after(stride);
+    for (size_t i = first; i < n; i += stride) {
+        const float u = ((float)(state - 1u) + 0.5f) / 2147483648.0f;
         gst(out + i, mean + stddev * 1.41421356f * erfinvf(2.0f * u - 1.0f));
+        state = minstd_mul(state, jump);
     }
 }
 
 // ---------------------------------------------------------------- Adam step, softmax cross-entropy
 // adamKernel (src/Adam.cu:26-38): x += rate * (m / (1 - beta1^t)) / (sqrt(v / (1 - beta2^t)) + eps), the same
 // expressions in the same order; every thread evaluates the two powers itself, as the reference's does.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ x, const float* __restrict__ m, const float* __restrict__ v, size_t n, float beta1,
             float beta2, float rate, float eps, int t)
 {
     const float c1 = 1.0f - powf(beta1, t), c2 = 1.0f - powf(beta2, t);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const float mhat = gld(m + i) / c1;
-        const float vhat = gld(v + i) / c2;
-        gst(x + i, gld(x + i) + (rate * mhat / (sqrtf(vhat) + eps)));
+    const size_t stride = (size_t)gridDim.x * blockDim.x, first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t n4 = VEC ? n >> 2 : 0;
+    auto step = [&](float xv, float mv, float vv) {
+        const float mhat = mv / c1;
+        const float vhat = vv / c2;
+        return xv + (rate * mhat / (sqrtf(vhat) + eps));
+    };
+    for (size_t i = first; i < n4; i += stride) {
+        const float4 mv = gld(reinterpret_cast<const float4*>(m) + i), vv = gld(reinterpret_cast<const float4*>(v) + i);
+        float4 xv = gld(reinterpret_cast<const float4*>(x) + i);
+        xv.x = step(xv.x, mv.x, vv.x); xv.y = step(xv.y, mv.y, vv.y); xv.z = step(xv.z, mv.z, vv.z); xv.w = step(xv.w, mv.w, vv.w);
+        gst(reinterpret_cast<float4*>(x) + i, xv);
     }
+    for (size_t i = (n4 << 2) + first; i < n; i += stride) gst(x + i, step(gld(x + i), gld(m + i), gld(v + i)));
 }
 
 // softmaxCrossEntropyKernel (src/SoftmaxKernel.cu:25-39): error[i] = truth[i] ? -log(pred[i] + 1e-9) : 0,
@@ -262,13 +368,28 @@ extern "C" int pxe_backward_bias(pxe_stream_t stream, float* bias_updates, const
 {
     PXE_REQUIRE(bias_updates && delta, "backward_bias: null pointer");
     PXE_REQUIRE(batch > 0 && n > 0 && size > 0, "backward_bias: non-positive shape");
+    PXE_REQUIRE((long long)batch * size < (1LL << 31), "backward_bias: batch * size = %lld does not fit 31 bits", (long long)batch * size);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // blocks per filter (a cluster, at most 8): enough to put a few blocks on every SM, each with 8192 terms or more
+    const long long work = size == 1 ? (long long)batch * 32 : (long long)batch * size;
+    const long long groups = size == 1 ? (n + 31) / 32 : n;
+    int ranks = 1;
+    while (ranks < 8 && groups * ranks < 592 && work / (ranks * 2) >= 8192) ranks *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ranks; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)(groups * ranks)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+    cfg.attrs = attr; cfg.numAttrs = 1;
     if (size == 1) {
-        backward_bias_conn_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(bias_updates, delta, batch, n);
-        PXE_LAUNCH_OK("backward_bias_conn_kernel");
+        const int segment = (batch + ranks - 1) / ranks;
+        PXE_CUDA_OK(cudaLaunchKernelEx(&cfg, backward_bias_conn_kernel, bias_updates, delta, batch, n, segment));
     } else {
-        backward_bias_kernel<<<(unsigned)n, 256, 0, s>>>(bias_updates, delta, batch, n, size);
-        PXE_LAUNCH_OK("backward_bias_kernel");
+        int segment = (size + ranks - 1) / ranks;
+        segment = (segment + 3) & ~3;
+        const bool vec = size % 4 == 0 && aligned16(delta);
+        if (vec) PXE_CUDA_OK(cudaLaunchKernelEx(&cfg, backward_bias_kernel<true>, bias_updates, delta, batch, n, size, segment));
+        else PXE_CUDA_OK(cudaLaunchKernelEx(&cfg, backward_bias_kernel<false>, bias_updates, delta, batch, n, size, segment));
     }
     return PXE_OK;
 }
@@ -305,7 +426,9 @@ extern "C" int pxe_constrain(pxe_stream_t stream, float* x, size_t n, float alph
     PXE_REQUIRE(x != nullptr, "constrain: null pointer");
     DeviceInfo di;
     { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
-    constrain_kernel<<<grid_for((long long)n, 256, di.sm_count, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, n, alpha);
+    const unsigned grid = grid_for((long long)n, 256 * 4, di.sm_count, 16);
+    if (aligned16(x)) constrain_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, n, alpha);
+    else constrain_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, n, alpha);
     PXE_LAUNCH_OK("constrain_kernel");
     return PXE_OK;
 }
@@ -316,7 +439,9 @@ extern "C" int pxe_mul(pxe_stream_t stream, const float* x, float* y, size_t n)
     PXE_REQUIRE(x && y, "mul: null pointer");
     DeviceInfo di;
     { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
-    mul_kernel<<<grid_for((long long)n, 256, di.sm_count, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n);
+    const unsigned grid = grid_for((long long)n, 256 * 4, di.sm_count, 16);
+    if (aligned16(x) && aligned16(y)) mul_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n);
+    else mul_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n);
     PXE_LAUNCH_OK("mul_kernel");
     return PXE_OK;
 }
@@ -351,8 +476,11 @@ extern "C" int pxe_adam_update(pxe_stream_t stream, size_t n, float* x, const fl
     PXE_REQUIRE(t >= 1, "adam_update: step %d (the first step is 1)", t);
     DeviceInfo di;
     { const int rc = device_info(&di); if (rc != PXE_OK) return rc; }
-    adam_kernel<<<grid_for((long long)n, 256 * 4, di.sm_count, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, m, v, n, beta1, beta2,
-                                                                                                            rate, eps, t);
+    const unsigned grid = grid_for((long long)n, 256 * 4, di.sm_count, 16);
+    if (aligned16(x) && aligned16(m) && aligned16(v))
+        adam_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, m, v, n, beta1, beta2, rate, eps, t);
+    else
+        adam_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, m, v, n, beta1, beta2, rate, eps, t);
     PXE_LAUNCH_OK("adam_kernel");
     return PXE_OK;
 }

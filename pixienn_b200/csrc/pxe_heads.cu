@@ -1268,6 +1268,9 @@ centernet_select_kernel(const CnParams p, const int* only)
 // Softmax / Region
 // ============================================================================================
 // One block per row of n contiguous values: out = exp(x/temp - max/temp) / sum (src/Math.cpp:77-97).
+// PER > 0: rows of up to 128 * PER values stay in registers between the three passes (same operations in the same
+// order as the form that re-reads the row, so the same bits); PER == 0: any length.
+template <int PER>
 __global__ void __launch_bounds__(128)
 softmax_rows_kernel(const float* in, float* out, int n, float temp)
 {
@@ -1275,8 +1278,19 @@ softmax_rows_kernel(const float* in, float* out, int n, float temp)
     __shared__ float bcast;
     const float* x = in + (long long)blockIdx.x * n;
     float* y = out + (long long)blockIdx.x * n;
+    constexpr int R = PER > 0 ? PER : 1;
+    float xv[R];
     float m = -FLT_MAX;
-    for (int i = threadIdx.x; i < n; i += 128) m = gld(x + i) > m ? gld(x + i) : m;
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const int i = threadIdx.x + 128 * k;
+            xv[k] = i < n ? gld(x + i) : -FLT_MAX;
+            m = xv[k] > m ? xv[k] : m;
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += 128) m = gld(x + i) > m ? gld(x + i) : m;
+    }
     for (int o = 16; o > 0; o >>= 1) { float t = __shfl_xor_sync(0xffffffffu, m, o); m = t > m ? t : m; }
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
     __syncthreads();
@@ -1284,10 +1298,20 @@ softmax_rows_kernel(const float* in, float* out, int n, float temp)
     __syncthreads();
     const float largest = bcast;
     float sum = 0.0f;
-    for (int i = threadIdx.x; i < n; i += 128) {
-        const float e = expf(gld(x + i) / temp - largest / temp);
-        gst(y + i, e);
-        sum += e;
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            if (threadIdx.x + 128 * k < n) {
+                xv[k] = expf(xv[k] / temp - largest / temp);
+                sum += xv[k];
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += 128) {
+            const float e = expf(gld(x + i) / temp - largest / temp);
+            gst(y + i, e);
+            sum += e;
+        }
     }
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     __syncthreads();
@@ -1296,7 +1320,13 @@ softmax_rows_kernel(const float* in, float* out, int n, float temp)
     if (threadIdx.x == 0) bcast = red[0] + red[1] + red[2] + red[3];
     __syncthreads();
     const float total = bcast;
-    for (int i = threadIdx.x; i < n; i += 128) gst(y + i, gld(y + i) / total);
+    if (PER > 0) {
+#pragma unroll
+        for (int k = 0; k < R; ++k)
+            if (threadIdx.x + 128 * k < n) gst(y + (threadIdx.x + 128 * k), xv[k] / total);
+    } else {
+        for (int i = threadIdx.x; i < n; i += 128) gst(y + i, gld(y + i) / total);
+    }
 }
 
 struct RegionParams {
@@ -1330,6 +1360,57 @@ region_forward_kernel(const RegionParams p)
             for (int j = 0; j < p.classes; ++j) { const float e = expf(gld(cls + j) - largest); sum += e; gst(cls + j, e); }
             for (int j = 0; j < p.classes; ++j) gst(cls + j, gld(cls + j) / sum);
         }
+    }
+}
+
+// The same result from coalesced traffic: a warp takes 32 consecutive cells of one (image, box slot).  It reads the
+// slot's `size` planes row by row (32 consecutive cells = one 128-byte request) into a shared-memory tile, each lane
+// then does its own cell's objectness and softmax on its column of the tile (the operations and their order are the
+// thread-per-box kernel's, so the bits are), and the warp writes the 32 records out, each as consecutive floats.  The
+// thread-per-box form reads with a stride of HW floats and writes with a stride of `size` floats per lane, and runs
+// its three softmax passes over global memory.  Rows are 33 floats apart: no bank conflicts in any of the phases.
+constexpr int kRegionWarps = 4;
+
+__global__ void __launch_bounds__(kRegionWarps * 32)
+region_forward_tile_kernel(const RegionParams p, int tiles_per_plane, long long tiles)
+{
+    extern __shared__ float region_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* tile = region_smem + (size_t)warp * p.size * 33;
+    const long long outputs = (long long)p.HW * p.num * p.size;
+    for (long long t = (long long)blockIdx.x * kRegionWarps + warp; t < tiles; t += (long long)gridDim.x * kRegionWarps) {
+        const int tp = (int)(t % tiles_per_plane);
+        const long long r = t / tiles_per_plane;
+        const int n = (int)(r % p.num), b = (int)(r / p.num);
+        const int cell0 = tp * 32, cell = cell0 + lane;
+        const bool live = cell < p.HW;
+        const float* src = p.in + b * outputs + (long long)n * p.size * p.HW + cell;
+        for (int e0 = 0; e0 < p.size; e0 += 16) {              // sixteen rows in flight per lane
+            float r[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) r[k] = (live && e0 + k < p.size) ? gld(src + (long long)(e0 + k) * p.HW) : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                if (e0 + k < p.size) tile[(e0 + k) * 33 + lane] = r[k];
+        }
+        if (live) {
+            float* col = tile + lane;
+            col[4 * 33] = act_logistic(col[4 * 33]);
+            if (p.softmax) {
+                float* cls = col + (p.coords + 1) * 33;
+                float largest = -FLT_MAX, sum = 0.0f;
+                for (int j = 0; j < p.classes; ++j) largest = cls[j * 33] > largest ? cls[j * 33] : largest;
+                for (int j = 0; j < p.classes; ++j) { const float e = expf(cls[j * 33] - largest); sum += e; cls[j * 33] = e; }
+                for (int j = 0; j < p.classes; ++j) cls[j * 33] = cls[j * 33] / sum;
+            }
+        }
+        __syncwarp();
+        const int live_cells = min(32, p.HW - cell0);
+        for (int c = 0; c < live_cells; ++c) {
+            float* dst = p.out + b * outputs + ((long long)(cell0 + c) * p.num + n) * p.size;
+            for (int e = lane; e < p.size; e += 32) gst(dst + e, tile[e * 33 + c]);
+        }
+        __syncwarp();
     }
 }
 
@@ -1907,7 +1988,14 @@ extern "C" int pxe_softmax(pxe_stream_t stream, const float* in, float* out, int
     PXE_REQUIRE(temperature != 0.0f, "softmax: temperature is zero");
     const long long rows = (long long)batch * groups;
     PXE_REQUIRE(rows <= 0x7fffffffLL, "softmax: too many rows");
-    softmax_rows_kernel<<<(unsigned)rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(in, out, inputs / groups, temperature);
+    const int row = inputs / groups;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (row <= 128) softmax_rows_kernel<1><<<(unsigned)rows, 128, 0, s>>>(in, out, row, temperature);
+    else if (row <= 256) softmax_rows_kernel<2><<<(unsigned)rows, 128, 0, s>>>(in, out, row, temperature);
+    else if (row <= 512) softmax_rows_kernel<4><<<(unsigned)rows, 128, 0, s>>>(in, out, row, temperature);
+    else if (row <= 1024) softmax_rows_kernel<8><<<(unsigned)rows, 128, 0, s>>>(in, out, row, temperature);
+    else if (row <= 2048) softmax_rows_kernel<16><<<(unsigned)rows, 128, 0, s>>>(in, out, row, temperature);
+    else softmax_rows_kernel<0><<<(unsigned)rows, 128, 0, s>>>(in, out, row, temperature);
     PXE_LAUNCH_OK("softmax_rows_kernel");
     return PXE_OK;
 }
@@ -1924,6 +2012,19 @@ extern "C" int pxe_region_forward(pxe_stream_t stream, const float* in, float* o
     p.in = in; p.out = out; p.batch = batch; p.HW = width * height; p.num = num;
     p.size = coords + 1 + classes; p.coords = coords; p.classes = classes; p.softmax = softmax;
     const long long boxes = (long long)batch * p.HW * num;
+    const size_t tile_bytes = (size_t)kRegionWarps * p.size * 33 * sizeof(float);
+    if (tile_bytes <= (size_t)di.max_smem_optin) {
+        if (tile_bytes > 48 * 1024)
+            PXE_CUDA_OK(cudaFuncSetAttribute(region_forward_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_bytes));
+        const int tiles_per_plane = (p.HW + 31) / 32;
+        const long long tiles = (long long)batch * num * tiles_per_plane;
+        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(200 * 1024) / tile_bytes));
+        region_forward_tile_kernel<<<grid_for(tiles, kRegionWarps, di.sm_count, per_sm), kRegionWarps * 32, tile_bytes,
+                                     static_cast<cudaStream_t>(stream)>>>(p, tiles_per_plane, tiles);
+        PXE_LAUNCH_OK("region_forward_tile_kernel");
+        return PXE_OK;
+    }
+    // records too long for a shared-memory tile: a thread per box
     region_forward_kernel<<<grid_for(boxes, 128, di.sm_count, 16), 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
     PXE_LAUNCH_OK("region_forward_kernel");
     return PXE_OK;
