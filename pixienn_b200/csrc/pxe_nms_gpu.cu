@@ -123,7 +123,10 @@ __global__ void nms_segment_starts_kernel(const K* sorted, int n, int* starts, i
 // most kImageStage records is staged in shared memory first, so that a pivot step costs a barrier and a few
 // shared-memory reads instead of a chain of dependent global loads; longer segments run from global memory.
 constexpr int kImageStage = 4096;
-constexpr size_t kImageStageBytes = (size_t)kImageStage * (sizeof(Rect) + sizeof(unsigned) + 1);
+constexpr int kPairCap = 1024;
+constexpr size_t kPairBytes = (size_t)kPairCap * (sizeof(Rect) + sizeof(unsigned) + 32 * sizeof(unsigned) + sizeof(float) + 1) + 32 * sizeof(unsigned);
+constexpr size_t kImageStageBytes = (size_t)kImageStage * (sizeof(Rect) + sizeof(unsigned) + 1) > kPairBytes
+                                        ? (size_t)kImageStage * (sizeof(Rect) + sizeof(unsigned) + 1) : kPairBytes;
 
 __global__ void __launch_bounds__(1024)
 nms_cross_class_kernel(const int* members, const int* starts, const int* nseg, int n, const Rect* rect,
@@ -137,6 +140,74 @@ nms_cross_class_kernel(const int* members, const int* starts, const int* nseg, i
     for (int s = blockIdx.x; s < segs; s += gridDim.x) {
         const int lo = gld(starts + s), hi = s + 1 < segs ? gld(starts + (s + 1)) : n;
         const int cnt = hi - lo;
+        if (cnt <= kPairCap) {
+            // Up to 1024 boxes: every "q would fall to p" (p before q, other class, IoU above 0.9) is found first, by all
+            // warps at once, as one bit of row q of a triangular matrix in shared memory; one warp then walks the rows
+            // that have a bit set, in order, and discards q when one of its p is still standing.  That is the loop below
+            // -- p discards q only while p stands -- without a barrier per box.
+            Rect* pbox = reinterpret_cast<Rect*>(stage_raw);
+            unsigned* pcls = reinterpret_cast<unsigned*>(pbox + kPairCap);
+            unsigned* mask = pcls + kPairCap;                              // [kPairCap][32] words, row q: bits p < q
+            unsigned* deadw = mask + kPairCap * 32;                        // [32]
+            float* parea = reinterpret_cast<float*>(deadw + 32);              // [kPairCap]
+            unsigned char* rowflag = reinterpret_cast<unsigned char*>(parea + kPairCap);
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+            for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
+                const int j = gld(members + (lo + t));
+                pbox[t] = gld(rect + j);
+                pcls[t] = gld(cls + j);
+                // the area, or a NaN (which sends every pair of this box to the exact expression) when the box is so
+                // small against its coordinates that the rounding of x + w could change an intersection by a per cent
+                const Rect bx = pbox[t];
+                const bool plain = fabsf(bx.x) + bx.w <= 16384.0f * bx.w && fabsf(bx.y) + bx.h <= 16384.0f * bx.h;
+                parea[t] = plain ? rect_area(bx) : __int_as_float(0x7fc00000);
+            }
+            __syncthreads();
+            for (int q = warp; q < cnt; q += warps) {
+                const Rect rq = pbox[q];
+                const unsigned cq = pcls[q];
+                const float aq = parea[q];
+                unsigned any = 0;
+                for (int w = 0; 32 * w < q; ++w) {
+                    const int pp = 32 * w + lane;
+                    bool hit = false;
+                    if (pp < q && pcls[pp] != cq) {
+                        // Two bounds spare most pairs the exact expression.  IoU <= smaller area / larger area, and
+                        // IoU <= (width of the intersection) / (width of q), likewise for the heights: a pair that is
+                        // below 0.8 on one of them cannot reach 0.9, with a margin many times the rounding of the exact
+                        // expression.  An area that is a NaN (see above) sends the pair to the exact expression.
+                        const float ap = parea[pp];
+                        const Rect rp = pbox[pp];
+                        bool maybe = !(aq < 0.8f * ap || ap < 0.8f * aq);
+                        if (maybe && aq == aq && ap == ap) {
+                            const float wi = fminf(rq.x + rq.w, rp.x + rp.w) - fmaxf(rq.x, rp.x);
+                            const float hi = fminf(rq.y + rq.h, rp.y + rp.h) - fmaxf(rq.y, rp.y);
+                            maybe = !(wi < 0.8f * rq.w || hi < 0.8f * rq.h);
+                        }
+                        if (maybe) hit = rect_iou(rq, rp) > 0.9f;
+                    }
+                    const unsigned word = __ballot_sync(0xffffffffu, hit);
+                    if (lane == 0) mask[q * 32 + w] = word;
+                    any |= word;
+                }
+                if (lane == 0) rowflag[q] = any != 0;
+            }
+            __syncthreads();
+            if (warp == 0) {
+                unsigned dead = 0;                                         // lane w: boxes 32w .. 32w + 31
+                for (int q = 1; q < cnt; ++q) {
+                    if (!rowflag[q]) continue;                             // the same for every lane
+                    const unsigned m = 32 * lane < q ? mask[q * 32 + lane] : 0u;
+                    if (__any_sync(0xffffffffu, (m & ~dead) != 0u) && lane == (q >> 5)) dead |= 1u << (q & 31);
+                }
+                deadw[lane] = dead;
+            }
+            __syncthreads();
+            for (int t = threadIdx.x; t < cnt; t += blockDim.x)
+                if ((deadw[t >> 5] >> (t & 31)) & 1u) gst(discard + (gld(members + (lo + t))), 1);
+            __syncthreads();
+            continue;
+        }
         if (cnt <= kImageStage) {
             for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
                 const int j = gld(members + (lo + t));
