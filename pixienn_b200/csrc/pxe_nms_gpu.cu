@@ -93,16 +93,26 @@ __global__ void nms_segment_keys_kernel(const unsigned long long* sorted_key, co
 template <typename K>
 __global__ void nms_segment_starts_kernel(const K* sorted, int n, int* starts, int* count)
 {
-    // one block; segments are listed in ascending position so that a segment's end is the next start
+    // one block; segments are listed in ascending position so that a segment's end is the next start.  A thread takes
+    // eight consecutive positions per turn, so a turn's three barriers cover 8192 positions.
+    constexpr int U = 8;
     __shared__ int warp_tot[32];
     __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int base = 0; base < n; base += blockDim.x) {
-        const int i = base + threadIdx.x;
-        const int flag = (i < n && (i == 0 || gld(sorted + i) != gld(sorted + (i - 1)))) ? 1 : 0;
-        int inc = flag;
+    for (int base = 0; base < n; base += U * blockDim.x) {
+        const int i0 = base + U * threadIdx.x;
+        K key[U + 1];
+        key[0] = (i0 > 0 && i0 - 1 < n) ? gld(sorted + (i0 - 1)) : K(0);
+#pragma unroll
+        for (int k = 0; k < U; ++k) key[k + 1] = i0 + k < n ? gld(sorted + (i0 + k)) : K(0);
+        unsigned flags = 0;
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+            if (i0 + k < n && (i0 + k == 0 || key[k + 1] != key[k])) flags |= 1u << k;
+        const int mine = __popc(flags);
+        int inc = mine;
         for (int o = 1; o < 32; o <<= 1) {
             const int t = __shfl_up_sync(0xffffffffu, inc, o);
             if (lane >= o) inc += t;
@@ -111,7 +121,10 @@ __global__ void nms_segment_starts_kernel(const K* sorted, int n, int* starts, i
         __syncthreads();
         int before = carry;
         for (int w = 0; w < warp; ++w) before += warp_tot[w];
-        if (flag) gst(starts + (before + inc - 1), i);
+        int at = before + inc - mine;
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+            if ((flags >> k) & 1u) gst(starts + at++, i0 + k);
         __syncthreads();
         if (threadIdx.x == blockDim.x - 1) carry = before + inc;
         __syncthreads();
@@ -257,6 +270,7 @@ nms_group_kernel(const int* members, const int* starts, const int* nseg, int n, 
     const int segs = gld(nseg);
     for (int s = blockIdx.x; s < segs; s += gridDim.x) {
         const int lo = gld(starts + s), hi = s + 1 < segs ? gld(starts + (s + 1)) : n;
+        if (hi - lo <= 32) continue;                       // nms_small_group_kernel's
         const int count = min(hi - lo, kGroupCap);
         const int t = threadIdx.x;
         int mine = -1;
@@ -273,6 +287,39 @@ nms_group_kernel(const int* members, const int* starts, const int* nseg, int n, 
         }
         if (t < count && dead[t]) gst(discard + mine, 1);
         __syncthreads();
+    }
+}
+
+// The same rule for groups of up to 32 members (a head with 80 classes leaves a dozen candidates per image and class):
+// a warp per group, a lane per member, the pivot's box handed round by shuffles -- no shared memory, no barrier.
+__global__ void __launch_bounds__(256)
+nms_small_group_kernel(const int* members, const int* starts, const int* nseg, int n, const Rect* rect, float threshold,
+                       unsigned char* discard)
+{
+    const int segs = gld(nseg);
+    const int lane = threadIdx.x & 31;
+    const int first = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), step = (int)((gridDim.x * blockDim.x) >> 5);
+    for (int s = first; s < segs; s += step) {
+        const int lo = gld(starts + s), hi = s + 1 < segs ? gld(starts + (s + 1)) : n;
+        const int count = hi - lo;
+        if (count > 32 || count < 2) continue;             // the same for the whole warp
+        int mine = -1;
+        Rect b{0.0f, 0.0f, 0.0f, 0.0f};
+        bool dead = true;
+        if (lane < count) {
+            mine = gld(members + (lo + lane));
+            b = gld(rect + mine);
+            dead = gld(discard + mine) != 0;
+        }
+        bool fell = false;
+        for (int p = 0; p + 1 < count; ++p) {
+            if (__shfl_sync(0xffffffffu, (int)dead, p)) continue;          // a discarded member discards nobody
+            Rect bp;
+            bp.x = __shfl_sync(0xffffffffu, b.x, p); bp.y = __shfl_sync(0xffffffffu, b.y, p);
+            bp.w = __shfl_sync(0xffffffffu, b.w, p); bp.h = __shfl_sync(0xffffffffu, b.h, p);
+            if (lane > p && lane < count && !dead && rect_iou(b, bp) > threshold) { dead = true; fell = true; }
+        }
+        if (fell) gst(discard + mine, 1);
     }
 }
 
@@ -411,6 +458,9 @@ extern "C" int pxe_nms(pxe_stream_t stream, const pxe_detection* dets, long long
     PXE_LAUNCH_OK("nms_cross_class_kernel");
     nms_group_kernel<<<seg_blocks, kGroupCap, 0, s>>>(by_group, starts_grp, counts + 1, N, rect, threshold, discard);
     PXE_LAUNCH_OK("nms_group_kernel");
+    const unsigned small_blocks = (unsigned)std::min<long long>(((long long)N + 7) / 8, 8LL * di.sm_count);
+    nms_small_group_kernel<<<small_blocks, 256, 0, s>>>(by_group, starts_grp, counts + 1, N, rect, threshold, discard);
+    PXE_LAUNCH_OK("nms_small_group_kernel");
     nms_keep_flags_kernel<<<blocks, 256, 0, s>>>(order, discard, N, keep);
     PXE_LAUNCH_OK("nms_keep_flags_kernel");
     PXE_CUDA_OK(cub::DeviceSelect::Flagged(cub_ws, cub_n, order, keep, kept, counts + 2, N, s));
