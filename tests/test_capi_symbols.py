@@ -107,6 +107,10 @@ def test_host_only_entry_points():
     assert L.pxe_adam_update(None, 10, None, None, None, 0.9, 0.999, 1e-3, 1e-8, 1) == capi.PXE_ERR_BAD_ARG
     assert L.pxe_adam_update(None, 0, None, None, None, 0.9, 0.999, 1e-3, 1e-8, 1) == capi.PXE_OK          # nothing to do
     assert L.pxe_softmax_cross_entropy(None, 5, None, None, None, None) == capi.PXE_ERR_BAD_ARG
+    assert L.pxe_backward_bias(None, None, None, 4, 4, 4) == capi.PXE_ERR_BAD_ARG
+    # the bias gradient indexes one filter's terms with an int: batch * size must fit 31 bits (addresses are never touched)
+    assert L.pxe_backward_bias(None, 0x10000000, 0x20000000, 70000, 8, 70000) == capi.PXE_ERR_BAD_ARG
+    assert b"31 bits" in L.pxe_last_error_string()
     e = capi.EpilogueDesc()
     e.x = e.y = 0x10000000
     e.batch, e.channels, e.height, e.width = 1, 4, 4, 4
