@@ -202,7 +202,8 @@ def test_activation_gradient_three_way(cuda, oracle, refcu, act):
     close(ops.activation_gradient(act, xs.contiguous(), ds).cpu().numpy(), oracle.gradient(act, x[1:1001], delta[1:1001]), atol=4e-6)
 
 
-@pytest.mark.parametrize("shape", [(4, 16, 26, 26), (2, 255, 19, 19), (3, 7, 1, 1), (5, 300, 1, 1), (2, 3, 50, 70)])
+@pytest.mark.parametrize("shape", [(4, 16, 26, 26), (2, 255, 19, 19), (3, 7, 1, 1), (5, 300, 1, 1), (2, 3, 50, 70),
+                                   (8, 16, 104, 104), (8, 16, 51, 53), (2048, 100, 1, 1)])   # the last three: clusters of 8, 2, 8 blocks
 def test_backward_bias_three_way(cuda, oracle, refcu, shape):
     """Sums of up to tens of thousands of terms: the reference's kernel, this library's and the CPU loop add in
     different orders; they agree to the rounding of such a sum."""
