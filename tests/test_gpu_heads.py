@@ -409,7 +409,8 @@ def test_centernet_plateau_larger_than_the_default_list(cuda):
 
 
 @pytest.mark.parametrize("shape,groups,temp", [((4, 1000, 1, 1), 1, 1.0), ((2, 30, 1, 1), 3, 0.7), ((3, 5, 2, 2), 1, 2.0),
-                                               ((1, 3000, 1, 1), 1, 1.0)])
+                                               ((1, 3000, 1, 1), 1, 1.0), ((2, 200, 1, 1), 1, 1.0), ((2, 400, 1, 1), 1, 0.5),
+                                               ((2, 1500, 1, 1), 1, 1.0), ((3, 128, 1, 1), 1, 1.0), ((2, 2049, 1, 1), 1, 1.0)])
 def test_softmax(cuda, oracle, shape, groups, temp):
     x = synth.normal(60, f"sm{shape}", shape, 0, 3)
     ref = oracle.softmax(x, groups, temp)
