@@ -269,6 +269,12 @@ def test_constrain_mul_three_way(cuda, oracle, refcu):
     refcu.call("mul", len(x), dev(x, cuda).data_ptr(), ty.data_ptr())
     torch.cuda.synchronize()
     assert np.array_equal(my.cpu().numpy(), ty.cpu().numpy()) and np.array_equal(my.cpu().numpy(), x * y)
+    # tensors that start 4 bytes past a 16-byte boundary take the element-wise form of the kernels
+    ux, uy = dev(x, cuda)[1:], dev(y, cuda)[1:]
+    assert ux.data_ptr() % 16 == 4
+    assert np.array_equal(ops.constrain(ux, 1.5).cpu().numpy(), oracle.constrain(x[1:], 1.5))
+    ux = dev(x, cuda)[1:]
+    assert np.array_equal(ops.mul(ux, uy).cpu().numpy(), x[1:] * y[1:])
 
 
 @pytest.mark.parametrize("t", [1, 2, 10, 1000])
@@ -285,6 +291,9 @@ def test_adam_step_three_way(cuda, oracle, refcu, t):
     torch.cuda.synchronize()
     assert np.array_equal(mine.cpu().numpy(), theirs.cpu().numpy())
     np.testing.assert_allclose(mine.cpu().numpy(), oracle.adam(x, m, v, *args), rtol=2e-6, atol=1e-7)
+    # off a 16-byte boundary (the element-wise form): the same values
+    again = ops.adam_update(dev(x, cuda)[1:], dev(m, cuda)[1:], dev(v, cuda)[1:], *args)
+    assert np.array_equal(again.cpu().numpy(), mine.cpu().numpy()[1:])
 
 
 def test_softmax_cross_entropy_equals_the_restatement(cuda, oracle):
