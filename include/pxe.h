@@ -492,7 +492,8 @@ PXE_API int pxe_nms(pxe_stream_t stream, const pxe_detection* dets, long long n,
  * gradient() of the functor for `act` (include/Activation.h:54-228). */
 PXE_API int pxe_activation_gradient(pxe_stream_t stream, int act, const float* x, size_t n, float* delta);
 /* px::backwardBiasGpu (include/BiasKernels.cuh:22, src/BiasKernels.cu:39-111): bias_updates[f] += the sum of
- * delta[b, f, 0..size) over the images; size == 1 is the connected-layer form. */
+ * delta[b, f, 0..size) over the images; size == 1 is the connected-layer form.  batch * size < 2^31.  The sum is
+ * taken in a fixed order (the same bits on every call); it needs no scratch memory. */
 PXE_API int pxe_backward_bias(pxe_stream_t stream, float* bias_updates, const float* delta, int batch, int n,
                               int size);
 /* px::maxPoolBackwardGpu (include/MaxPoolKernels.cuh:7, src/MaxPoolKernels.cu:45-49, 61-65):
