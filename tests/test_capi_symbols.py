@@ -60,6 +60,28 @@ def test_checked_build_exports_the_same_symbols():
     assert L.pxe_debug_read_report(None, 0) == capi.PXE_ERR_BAD_ARG       # argument check comes before any CUDA call
 
 
+def test_checked_library_is_chosen_before_the_first_load_only():
+    """pixienn_b200.debug swaps the library for the bounds-checked one in a fresh process and refuses once libpxe.so is
+    loaded; without a CUDA context nothing is armed, and the report reads through the same binding."""
+    import subprocess
+    import sys
+    code = ("from pixienn_b200 import capi, debug\n"
+            "debug.use_checked_library()\n"
+            "L = capi.lib()\n"
+            "assert L.pxe_debug_bounds_checked() == 1 and L.pxe_version() >= 100\n"
+            "assert capi.LIB_PATH.endswith('libpxe_checked.so')\n"
+            "r = capi.BoundsReport(); r.violations = 3; r.bytes = 16; r.address = 0x7f00; r.line = 96; r.file = b'pxe_nhwc.cu'\n"
+            "assert debug.describe(r) == '3 refused accesses; first: 16-byte load at 0x7f00 (outside every allocation), pxe_nhwc.cu:96'\n"
+            "print('ok')\n")
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
+    code = ("from pixienn_b200 import capi, debug\n"
+            "capi.lib()\n"
+            "try:\n    debug.use_checked_library()\nexcept RuntimeError as e:\n    print('refused:', e)\n")
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True)
+    assert res.returncode == 0 and "refused: use_checked_library() must run before" in res.stdout, res.stdout + res.stderr[-2000:]
+
+
 def test_compat_tier_symbols_exported():
     L = capi.lib()
     for n in capi.COMPAT_SYMBOLS:
