@@ -91,3 +91,25 @@ def test_cpp_program_drives_the_c_abi_on_the_gpu(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
     assert run.stdout.startswith("ok:")
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    return None
+
+
+@pytest.mark.skipif(_nvcc() is None, reason="nvcc not found")
+def test_index_division_is_exact(tmp_path):
+    """FastDiv (csrc/pxe_common.cuh), the multiply-high division every kernel's index arithmetic uses: the device
+    formula with the constructor's constants equals n / d for 7109 divisors (every one up to 5000, powers of two and
+    their neighbours, the model shapes, random odd 32-bit values) over 31.7 M values of n -- small ones, the ends of the
+    32-bit range, the neighbours of multiples of d, random ones.  A host program; no GPU."""
+    exe = tmp_path / "fastdiv_check"
+    r = subprocess.run([_nvcc(), "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I", INC, "-I",
+                        os.path.join(ROOT, "pixienn_b200", "csrc"), os.path.join(SRC, "fastdiv_check.cu"), "-o", str(exe)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.startswith("ok: 7109 divisors"), run.stdout + run.stderr
