@@ -64,5 +64,21 @@
             d.y_pool_batch_stride = s.batch_stride;
         }
         PXE_CHECK(pxe_conv_epilogue(nullptr, &d));
+        for (int k = 1; st->fused_pool >= 0 && k < st->n_pool_dests; ++k) {   /* the pooled tensor, stored more than once */
+            auto& pool = this->model().layerAt(st->fused_pool);
+            const pxe_dest& pd = st->pool_dests[k];
+            auto& route = this->model().layerAt(pd.kind == 1 ? pd.route : st->fused_pool);
+            PXE_CHECK(pxe_shim::copy_to(d.y_pool, d.y_pool_batch_stride, filters_,
+                                        pxe_shim::resolve(pd, pool.pxeOutput(), pool.outputs(), route.pxeOutput(), route.outputs(),
+                                                          (long long)pool.outHeight() * pool.outWidth()),
+                                        this->batch(), pool.outHeight(), pool.outWidth()));
+        }
+        for (int k = 2; k < st->n_dests && d.y != nullptr; ++k) {          /* read by more than two routes: copies */
+            const pxe_dest& pd = st->dests[k];
+            auto& route = this->model().layerAt(pd.kind == 1 ? pd.route : out_layer);
+            PXE_CHECK(pxe_shim::copy_to(d.y, d.y_batch_stride, filters_,
+                                        pxe_shim::resolve(pd, out.pxeOutput(), out.outputs(), route.pxeOutput(), route.outputs(), plane),
+                                        this->batch(), this->outHeight(), this->outWidth()));
+        }
     }
 }

@@ -7,6 +7,9 @@
  *
  *   conv_forward_epilogue.inl    ConvLayer<Device::CUDA>::forward, in place of include/cuda/ConvLayer.h:284-307
  *   route_forward.inl            RouteLayer<Device::CUDA>::forward, in place of include/cuda/RouteLayer.h:25-43
+ *   maxpool_forward.inl          MaxPoolLayer<Device::CUDA>::forward, in place of include/cuda/MaxPoolLayer.h:39-41
+ *   upsample_forward.inl         UpsampleLayer<Device::CUDA>::forward, in place of include/cuda/UpsampleLayer.h:37-38
+ *   shortcut_forward.inl         ShortcutLayer<Device::CUDA>::forward, in place of include/cuda/ShortcutLayer.h:27-33
  *   yolo_add_detects.inl         YoloLayer<Device::CUDA>::addDetects, in place of include/cuda/YoloLayer.h:171-176
  *   centernet_add_detects.inl    CenterNetLayer<Device::CUDA>::addDetects, in place of include/cuda/CenterNetLayer.h:92-95
  *
@@ -84,6 +87,13 @@ inline Slot resolve(const pxe_dest& d, float* own_output, long long own_outputs,
 {
     if (d.kind == 0) return Slot{own_output, own_outputs};
     return Slot{route_output + (long long)d.channel_offset * plane, route_outputs};
+}
+
+/* One tensor copied into a further destination (a step stores up to two destinations itself; a tensor that still more
+ * routes read is copied from the first). */
+inline int copy_to(const float* src, long long src_batch_stride, int channels, const Slot& dst, int batch, int height, int width)
+{
+    return pxe_concat(nullptr, 1, &src, &src_batch_stride, &channels, dst.ptr, dst.batch_stride, batch, height, width);
 }
 
 }   // namespace pxe_shim

@@ -28,12 +28,39 @@ static pxe_bn_backward_desc g_last_bn_backward;
 #define pxe_batchnorm_backward shim_test_bn_backward
 static int shim_test_bn_forward(pxe_stream_t, const pxe_bn_train_desc* d) { g_last_bn_train = *d; return PXE_OK; }
 static int shim_test_bn_backward(pxe_stream_t, const pxe_bn_backward_desc* d) { g_last_bn_backward = *d; return PXE_OK; }
+struct PoolCall { const float* x; float* y; long long ybs; int* indexes; int kernel, stride, padding; };
+struct SppCall { const float* x; int n; int kernels[4]; float* ys[4]; long long strides[4]; };
+struct UpCall { const float* x; float* y; long long ybs; int stride; };
+struct ShortcutCall { const float* x; const float* from; float* y; long long ybs; float* y2; long long y2bs; int act; };
+static std::vector<PoolCall> g_pools;
+static std::vector<SppCall> g_spps;
+static std::vector<UpCall> g_ups;
+static std::vector<ShortcutCall> g_shortcuts;
+static int g_general_shortcuts = 0, g_activations = 0;
+static std::vector<float*> g_copy_dsts;
+#define pxe_maxpool shim_test_maxpool
+#define pxe_spp shim_test_spp
+#define pxe_upsample shim_test_upsample
+#define pxe_shortcut shim_test_shortcut
+#define pxe_shortcut_general shim_test_shortcut_general
+#define pxe_activate shim_test_activate
+static int shim_test_maxpool(pxe_stream_t, const float* x, long long, float* y, long long ybs, int* idx, int, int, int, int, int k, int s, int p)
+{ g_pools.push_back({x, y, ybs, idx, k, s, p}); return PXE_OK; }
+static int shim_test_spp(pxe_stream_t, const float* x, long long, int, int, int, int, int n, const int* kernels, float* const* ys, const long long* strides)
+{ SppCall c{}; c.x = x; c.n = n; for (int i = 0; i < n && i < 4; ++i) { c.kernels[i] = kernels[i]; c.ys[i] = ys[i]; c.strides[i] = strides[i]; } g_spps.push_back(c); return PXE_OK; }
+static int shim_test_upsample(pxe_stream_t, const float* x, long long, float* y, long long ybs, int, int, int, int, int stride, float)
+{ g_ups.push_back({x, y, ybs, stride}); return PXE_OK; }
+static int shim_test_shortcut(pxe_stream_t, const float* x, long long, const float* from, long long, float* y, long long ybs, float* y2, long long y2bs,
+                              int, int, int, int, float, float, int act)
+{ g_shortcuts.push_back({x, from, y, ybs, y2, y2bs, act}); return PXE_OK; }
+static int shim_test_shortcut_general(pxe_stream_t, int, int, int, int, const float*, int, int, int, float, float, float*) { ++g_general_shortcuts; return PXE_OK; }
+static int shim_test_activate(pxe_stream_t, int, float*, size_t) { ++g_activations; return PXE_OK; }
 #define pxe_conv_epilogue shim_test_conv_epilogue
 #define pxe_concat shim_test_concat
 #define pxe_yolo_decode shim_test_yolo_decode
 #define pxe_centernet_decode shim_test_centernet_decode
 static int shim_test_conv_epilogue(pxe_stream_t, const pxe_epilogue_desc* d) { g_last_epilogue = *d; ++g_epilogues; return PXE_OK; }
-static int shim_test_concat(pxe_stream_t, int, const float* const*, const long long*, const int*, float*, long long, int, int, int) { ++g_concats; return PXE_OK; }
+static int shim_test_concat(pxe_stream_t, int, const float* const*, const long long*, const int*, float* dst, long long, int, int, int) { ++g_concats; g_copy_dsts.push_back(dst); return PXE_OK; }
 static int shim_test_yolo_decode(pxe_stream_t, const pxe_yolo_decode_desc*, pxe_detection*, long long, long long*, void*, size_t) { return PXE_OK; }
 static int shim_test_centernet_decode(pxe_stream_t, const pxe_centernet_decode_desc*, pxe_detection*, int*, void*, size_t) { return PXE_OK; }
 
@@ -50,6 +77,7 @@ struct Vec {                                        // PxCudaVectorT: data() and
     T* data() { return v.data(); }
     const T* data() const { return v.data(); }
     std::size_t size() const { return v.size(); }
+    void copy(const Vec<T>& o) { v = o.v; }                // PxCudaVectorT::copy
 };
 
 struct Model;
@@ -73,6 +101,13 @@ struct Layer {
     float beta() const { return 1.0f; }
     int pxeActivation() const { return pxeActivation_; }
     int padding() const { return 1; }
+    int pxeKernel() const { return pxeKernel_; }
+    bool training() const { return false; }
+    // input geometry (the stand-in's layers keep their input's shape unless set otherwise)
+    int channels() const { return in_c_ ? in_c_ : c_; }
+    int height() const { return in_h_ ? in_h_ : h_; }
+    int width() const { return in_w_ ? in_w_ : w_; }
+    int in_c_ = 0, in_h_ = 0, in_w_ = 0, pxeKernel_ = 2;
     Model& model_;
     int index_, c_, h_, w_, batch_;
     Vec<float> output_;
@@ -119,6 +154,41 @@ struct RouteLayer : Layer {
     void forwardBody()
     {
 #include "shim/route_forward.inl"
+    }
+};
+
+struct MaxPoolLayer : Layer {
+    using V = Vec<float>;
+    MaxPoolLayer(Model& m, int index, int c, int h, int w, int batch, int kernel, int stride, int padding)
+        : Layer(m, index, c, h, w, batch), kernel_(kernel), stride_(stride), padding_(padding) { pxeKernel_ = kernel; }
+    int kernel_, stride_, padding_;
+    Vec<int> indexes_;
+    void forward(const V& input)
+    {
+#include "shim/maxpool_forward.inl"
+    }
+};
+
+struct UpsampleLayer : Layer {
+    using V = Vec<float>;
+    UpsampleLayer(Model& m, int index, int c, int h, int w, int batch, int stride) : Layer(m, index, c, h * stride, w * stride, batch), stride_(stride)
+    { in_c_ = c; in_h_ = h; in_w_ = w; }
+    int stride_;
+    float scale_ = 1.0f;
+    void forward(const V& input)
+    {
+#include "shim/upsample_forward.inl"
+    }
+};
+
+struct ShortcutLayer : Layer {
+    using V = Vec<float>;
+    ShortcutLayer(Model& m, int index, int c, int h, int w, int batch, Layer* from) : Layer(m, index, c, h, w, batch), from_(from) {}
+    Layer* from_;
+    float alpha_ = 1.0f, beta_ = 1.0f;
+    void forward(const V& input)
+    {
+#include "shim/shortcut_forward.inl"
     }
 };
 
@@ -203,5 +273,89 @@ int main()
          g_last_bn_backward.dgamma == c1->scaleUpdates_.data() && g_last_bn_backward.save_mean == c1->mean_.data();
     std::printf("%s: epilogues=%d concats=%d\n", ok ? "ok" : "MISMATCH", g_epilogues, g_concats);
     pxe_plan_destroy(m.plan_.plan);
-    return ok ? 0 : 1;
+    if (!ok) return 1;
+
+    // ---- pools, SPP block, upsample into a route slot, shortcuts that stand alone ------------------------------
+    //  0 conv 16x16          1 maxpool 2/2 (folded into 0)   2 conv 8x8            3 maxpool 5/1 of 2
+    //  4 route(2)            5 maxpool 9/1                   6 route(2)            7 maxpool 13/1
+    //  8 route(7, 5, 3, 2)   9 conv 8x8                     10 upsample x2        11 route(10, 0)
+    // 12 conv 16x16         13 maxpool 2/1                  14 shortcut(13, from 12)   15 conv 16x16
+    // 16 shortcut(15, from 9): 16x16 with an 8x8 partner
+    px::Model n;
+    const int S = 16, Hh = 8;
+    auto add = [&](px::Layer* l) { n.layers_.emplace_back(l); return l; };
+    add(new px::ConvLayer(n, 0, C, S, S, B, true));
+    auto* p1 = new px::MaxPoolLayer(n, 1, C, Hh, Hh, B, 2, 2, 1); p1->in_c_ = C; p1->in_h_ = S; p1->in_w_ = S; add(p1);
+    add(new px::ConvLayer(n, 2, C, Hh, Hh, B, true));
+    auto* p3 = static_cast<px::MaxPoolLayer*>(add(new px::MaxPoolLayer(n, 3, C, Hh, Hh, B, 5, 1, 4)));
+    add(new px::RouteLayer(n, 4, C, Hh, Hh, B));
+    auto* p5 = static_cast<px::MaxPoolLayer*>(add(new px::MaxPoolLayer(n, 5, C, Hh, Hh, B, 9, 1, 8)));
+    add(new px::RouteLayer(n, 6, C, Hh, Hh, B));
+    auto* p7 = static_cast<px::MaxPoolLayer*>(add(new px::MaxPoolLayer(n, 7, C, Hh, Hh, B, 13, 1, 12)));
+    auto* r8 = add(new px::RouteLayer(n, 8, 4 * C, Hh, Hh, B));
+    add(new px::ConvLayer(n, 9, C, Hh, Hh, B, true));
+    auto* u10 = static_cast<px::UpsampleLayer*>(add(new px::UpsampleLayer(n, 10, C, Hh, Hh, B, 2)));
+    auto* r11 = add(new px::RouteLayer(n, 11, 2 * C, S, S, B));
+    add(new px::ConvLayer(n, 12, C, S, S, B, true));
+    auto* p13 = static_cast<px::MaxPoolLayer*>(add(new px::MaxPoolLayer(n, 13, C, S, S, B, 2, 1, 1)));
+    auto* s14 = static_cast<px::ShortcutLayer*>(add(new px::ShortcutLayer(n, 14, C, S, S, B, n.layers_[12].get())));
+    add(new px::ConvLayer(n, 15, C, S, S, B, true));
+    auto* s16 = static_cast<px::ShortcutLayer*>(add(new px::ShortcutLayer(n, 16, C, S, S, B, n.layers_[9].get())));
+    auto pool = [](int c, int hw, int k, int st, int pad, int src) {
+        pxe_layer_desc d = desc(PXE_LAYER_MAXPOOL, c, hw, hw, src);
+        d.kernel = k; d.stride = st; d.padding = pad;
+        return d;
+    };
+    auto route_of = [](int c, int hw, std::initializer_list<int> srcs) {
+        pxe_layer_desc d = desc(PXE_LAYER_ROUTE, c, hw, hw, -1);
+        d.n_sources = 0;
+        for (int v : srcs) d.sources[d.n_sources++] = v;
+        return d;
+    };
+    pxe_layer_desc up = desc(PXE_LAYER_UPSAMPLE, C, S, S, 9);
+    up.stride = 2;
+    std::vector<pxe_layer_desc> nd = {
+        desc(PXE_LAYER_CONV, C, S, S, -1), pool(C, Hh, 2, 2, 1, 0), desc(PXE_LAYER_CONV, C, Hh, Hh, 1), pool(C, Hh, 5, 1, 4, 2),
+        route_of(C, Hh, {2}), pool(C, Hh, 9, 1, 8, 4), route_of(C, Hh, {2}), pool(C, Hh, 13, 1, 12, 6), route_of(4 * C, Hh, {7, 5, 3, 2}),
+        desc(PXE_LAYER_CONV, C, Hh, Hh, 8), up, route_of(2 * C, S, {10, 0}), desc(PXE_LAYER_CONV, C, S, S, 11), pool(C, S, 2, 1, 1, 12),
+        desc(PXE_LAYER_SHORTCUT, C, S, S, 13, 12), desc(PXE_LAYER_CONV, C, S, S, 14), desc(PXE_LAYER_SHORTCUT, C, S, S, 15, 9)};
+    if (pxe_shim::build_plan(nd, true, &n.plan_) != PXE_OK) { std::printf("plan 2 failed: %s\n", pxe_last_error_string()); return 1; }
+    const long long small = (long long)Hh * Hh, big = (long long)S * S;
+    // the folded pool and the later pools of the SPP block run nothing
+    p1->forward(n.layers_[0]->output_);
+    p5->forward(n.layers_[4]->output_);
+    p7->forward(n.layers_[6]->output_);
+    bool ok2 = g_pools.empty() && g_spps.empty();
+    // the first pool of the block: one call, kernels 5 / 9 / 13, each into its slot of route 8 = (13, 9, 5, identity)
+    p3->forward(n.layers_[2]->output_);
+    ok2 = ok2 && g_spps.size() == 1 && g_spps[0].n == 3 && g_spps[0].x == n.layers_[2]->output_.data() &&
+          g_spps[0].kernels[0] == 5 && g_spps[0].kernels[1] == 9 && g_spps[0].kernels[2] == 13 &&
+          g_spps[0].ys[0] == r8->output_.data() + 2 * C * small && g_spps[0].ys[1] == r8->output_.data() + 1 * C * small &&
+          g_spps[0].ys[2] == r8->output_.data() && g_spps[0].strides[0] == 4 * C * small && g_pools.empty();
+    // the upsampled tensor goes straight into channels [0, C) of route 11
+    u10->forward(n.layers_[9]->output_);
+    ok2 = ok2 && g_ups.size() == 1 && g_ups[0].x == n.layers_[9]->output_.data() && g_ups[0].y == r11->output_.data() &&
+          g_ups[0].ybs == 2 * C * big && g_ups[0].stride == 2;
+    // conv 0: full-resolution output into channels [C, 2C) of route 11, pooled output into layer 1's own tensor
+    static_cast<px::ConvLayer*>(n.layers_[0].get())->forwardEpilogue();
+    ok2 = ok2 && g_last_epilogue.y == r11->output_.data() + C * big && g_last_epilogue.y_batch_stride == 2 * C * big &&
+          g_last_epilogue.y_pool == p1->output_.data() && g_last_epilogue.pool_kernel == 2;
+    // a pool that stands alone, with the layer's own kernel / stride / padding
+    p13->forward(n.layers_[12]->output_);
+    ok2 = ok2 && g_pools.size() == 1 && g_pools[0].x == n.layers_[12]->output_.data() && g_pools[0].y == p13->output_.data() &&
+          g_pools[0].kernel == 2 && g_pools[0].stride == 1 && g_pools[0].padding == 1 && g_pools[0].indexes == nullptr;
+    // a shortcut behind a pool cannot be folded into a convolution: one pass
+    s14->pxeActivation_ = PXE_ACT_LEAKY;
+    s14->forward(p13->output_);
+    ok2 = ok2 && g_shortcuts.size() == 1 && g_shortcuts[0].x == p13->output_.data() && g_shortcuts[0].from == n.layers_[12]->output_.data() &&
+          g_shortcuts[0].y == s14->output_.data() && g_shortcuts[0].y2 == nullptr && g_shortcuts[0].act == PXE_ACT_LEAKY;
+    // partner of another shape: the reference's three steps (conv 15 keeps its epilogue: the plan does not fold this one)
+    const pxe_step* st15 = n.plan_.step(15);
+    ok2 = ok2 && st15 != nullptr && st15->fused_shortcut < 0;
+    s16->forward(n.layers_[15]->output_);
+    ok2 = ok2 && g_general_shortcuts == 1 && g_activations == 1 && g_shortcuts.size() == 1;
+    std::printf("%s: pools=%zu spp=%zu upsamples=%zu shortcuts=%zu general=%d\n", ok2 ? "ok" : "MISMATCH", g_pools.size(), g_spps.size(),
+                g_ups.size(), g_shortcuts.size(), g_general_shortcuts);
+    pxe_plan_destroy(n.plan_.plan);
+    return ok2 ? 0 : 1;
 }

@@ -73,6 +73,9 @@ def test_shim_fragments_compile_inside_stand_in_layers(tmp_path):
     assert r.returncode == 0, r.stderr
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0 and run.stdout.startswith("ok: epilogues=2 concats=0"), (run.stdout, run.stderr)
+    # second graph: a folded pool and the later pools of an SPP block run nothing, the block's first pool makes one pxe_spp
+    # call into the route's slots, the upsample writes its route slot, a stand-alone pool and two kinds of shortcut
+    assert "ok: pools=1 spp=1 upsamples=1 shortcuts=1 general=1" in run.stdout, run.stdout
 
 
 @pytest.mark.gpu
