@@ -12,6 +12,10 @@
  *   shortcut_forward.inl         ShortcutLayer<Device::CUDA>::forward, in place of include/cuda/ShortcutLayer.h:27-33
  *   yolo_add_detects.inl         YoloLayer<Device::CUDA>::addDetects, in place of include/cuda/YoloLayer.h:171-176
  *   centernet_add_detects.inl    CenterNetLayer<Device::CUDA>::addDetects, in place of include/cuda/CenterNetLayer.h:92-95
+ *   region_forward.inl           RegionLayer<Device::CUDA>::forward (inferring), in place of include/cuda/RegionLayer.h:43-53
+ *   region_add_detects.inl       RegionLayer<Device::CUDA>::addDetects, in place of include/cuda/RegionLayer.h:76-82
+ *   softmax_forward.inl          SoftmaxLayer<Device::CUDA>::forward, in place of include/cuda/SoftmaxLayer.h:72-74
+ *   avgpool_forward.inl          AvgPoolLayer<Device::CUDA>::forward, in place of include/cuda/AvgPoolLayer.h:71-73
  *
  * What the fragments expect from the surrounding class beyond the reference's own members is listed at the top of
  * each; it comes to: a `const pxe_shim::PlanView& pxePlan()` on the model (built once after parseModel, see

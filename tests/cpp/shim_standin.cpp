@@ -55,6 +55,27 @@ static int shim_test_shortcut(pxe_stream_t, const float* x, long long, const flo
 { g_shortcuts.push_back({x, from, y, ybs, y2, y2bs, act}); return PXE_OK; }
 static int shim_test_shortcut_general(pxe_stream_t, int, int, int, int, const float*, int, int, int, float, float, float*) { ++g_general_shortcuts; return PXE_OK; }
 static int shim_test_activate(pxe_stream_t, int, float*, size_t) { ++g_activations; return PXE_OK; }
+struct RegionCall { const float* in; float* out; int num, coords, classes, softmax; };
+struct RegionDecodeCall { const float* pred; const float* anchors; int per_image; float w, h, thr; long long capacity; };
+struct SoftmaxCall { const float* in; float* out; int inputs, groups; float temp; };
+struct AvgCall { const float* x; float* y; long long ybs; int c, h, w; };
+static std::vector<RegionCall> g_regions;
+static std::vector<RegionDecodeCall> g_region_decodes;
+static std::vector<SoftmaxCall> g_softmaxes;
+static std::vector<AvgCall> g_avgs;
+#define pxe_region_forward shim_test_region_forward
+#define pxe_region_decode shim_test_region_decode
+#define pxe_softmax shim_test_softmax
+#define pxe_avgpool shim_test_avgpool
+static int shim_test_region_forward(pxe_stream_t, const float* in, float* out, int, int, int, int num, int coords, int classes, int softmax)
+{ g_regions.push_back({in, out, num, coords, classes, softmax}); return PXE_OK; }
+static int shim_test_region_decode(pxe_stream_t, const float* pred, int, int, int, int, int, int, const float* anchors, int per_image, float w, float h,
+                                   float thr, pxe_detection*, long long capacity, long long*, int)
+{ g_region_decodes.push_back({pred, anchors, per_image, w, h, thr, capacity}); return PXE_OK; }
+static int shim_test_softmax(pxe_stream_t, const float* in, float* out, int, int inputs, int groups, float temp)
+{ g_softmaxes.push_back({in, out, inputs, groups, temp}); return PXE_OK; }
+static int shim_test_avgpool(pxe_stream_t, const float* x, long long, float* y, long long ybs, int, int c, int h, int w)
+{ g_avgs.push_back({x, y, ybs, c, h, w}); return PXE_OK; }
 #define pxe_conv_epilogue shim_test_conv_epilogue
 #define pxe_concat shim_test_concat
 #define pxe_yolo_decode shim_test_yolo_decode
@@ -189,6 +210,47 @@ struct ShortcutLayer : Layer {
     void forward(const V& input)
     {
 #include "shim/shortcut_forward.inl"
+    }
+};
+
+struct RegionLayer : Layer {
+    using V = Vec<float>;
+    using Layer::Layer;
+    int classes() const { return 3; }
+    int num_ = 2, coords_ = 4;
+    bool softmax_ = true;
+    std::vector<float> anchors_{1.0f, 2.0f, 3.0f, 4.0f};
+    Vec<char> pxeDets_;
+    Vec<long long> pxeCount_;
+    long long pxeCapacity_ = 64;
+    void forward(const V& input)
+    {
+#include "shim/region_forward.inl"
+    }
+    void addDetects(Detections& detects, int width, int height, float threshold)
+    {
+#include "shim/region_add_detects.inl"
+    }
+};
+
+struct SoftmaxLayer : Layer {
+    using V = Vec<float>;
+    using Layer::Layer;
+    int inputs() const { return c_ * h_ * w_; }
+    int groups_ = 2;
+    float temperature_ = 0.5f;
+    void forward(const V& input)
+    {
+#include "shim/softmax_forward.inl"
+    }
+};
+
+struct AvgPoolLayer : Layer {
+    using V = Vec<float>;
+    AvgPoolLayer(Model& m, int index, int c, int h, int w, int batch) : Layer(m, index, c, 1, 1, batch) { in_c_ = c; in_h_ = h; in_w_ = w; }
+    void forward(const V& input)
+    {
+#include "shim/avgpool_forward.inl"
     }
 };
 
@@ -357,5 +419,35 @@ int main()
     std::printf("%s: pools=%zu spp=%zu upsamples=%zu shortcuts=%zu general=%d\n", ok2 ? "ok" : "MISMATCH", g_pools.size(), g_spps.size(),
                 g_ups.size(), g_shortcuts.size(), g_general_shortcuts);
     pxe_plan_destroy(n.plan_.plan);
-    return ok2 ? 0 : 1;
+    if (!ok2) return 1;
+
+    // ---- heads that need no plan: Region forward / addDetects, softmax, global average pool -----------------------
+    px::Model h;
+    px::RegionLayer region(h, 0, 2 * (4 + 1 + 3), 5, 5, B);
+    px::Vec<float> head_in;
+    head_in.v.resize(region.output_.size());
+    region.pxeDets_.v.resize(64 * sizeof(pxe_detection));
+    region.pxeCount_.v.resize(1);
+    region.forward(head_in);
+    px::Detections found;
+    region.addDetects(found, 416, 320, 0.25f);
+    px::SoftmaxLayer soft(h, 1, 10, 1, 1, B);
+    px::Vec<float> soft_in;
+    soft_in.v.resize(soft.output_.size());
+    soft.forward(soft_in);
+    px::AvgPoolLayer avg(h, 2, 6, 7, 7, B);
+    px::Vec<float> avg_in;
+    avg_in.v.resize((std::size_t)B * 6 * 7 * 7);
+    avg.forward(avg_in);
+    const bool ok3 = g_regions.size() == 1 && g_regions[0].in == head_in.data() && g_regions[0].out == region.output_.data() &&
+                     g_regions[0].num == 2 && g_regions[0].coords == 4 && g_regions[0].classes == 3 && g_regions[0].softmax == 1 &&
+                     g_region_decodes.size() == 1 && g_region_decodes[0].pred == region.output_.data() &&
+                     g_region_decodes[0].anchors == region.anchors_.data() && g_region_decodes[0].per_image == 0 &&
+                     g_region_decodes[0].w == 416.0f && g_region_decodes[0].h == 320.0f && g_region_decodes[0].capacity == 64 &&
+                     found.empty() && g_softmaxes.size() == 1 && g_softmaxes[0].in == soft_in.data() && g_softmaxes[0].inputs == 10 &&
+                     g_softmaxes[0].groups == 2 && g_softmaxes[0].temp == 0.5f && g_avgs.size() == 1 && g_avgs[0].x == avg_in.data() &&
+                     g_avgs[0].y == avg.output_.data() && g_avgs[0].ybs == 6 && g_avgs[0].c == 6 && g_avgs[0].h == 7 && g_avgs[0].w == 7;
+    std::printf("%s: region=%zu region_decode=%zu softmax=%zu avgpool=%zu\n", ok3 ? "ok" : "MISMATCH", g_regions.size(),
+                g_region_decodes.size(), g_softmaxes.size(), g_avgs.size());
+    return ok3 ? 0 : 1;
 }

@@ -76,6 +76,9 @@ def test_shim_fragments_compile_inside_stand_in_layers(tmp_path):
     # second graph: a folded pool and the later pools of an SPP block run nothing, the block's first pool makes one pxe_spp
     # call into the route's slots, the upsample writes its route slot, a stand-alone pool and two kinds of shortcut
     assert "ok: pools=1 spp=1 upsamples=1 shortcuts=1 general=1" in run.stdout, run.stdout
+    # heads that need no plan: Region forward and addDetects (the reference's image-0 indexing kept), softmax with groups and
+    # temperature, the global average pool
+    assert "ok: region=1 region_decode=1 softmax=1 avgpool=1" in run.stdout, run.stdout
 
 
 @pytest.mark.gpu
