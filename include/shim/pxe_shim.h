@@ -63,10 +63,14 @@ struct PlanView {
     }
 };
 
-/* Built once at the end of Model<D>::parseModel (include/Model.h:1596-1641) from one pxe_layer_desc per layer. */
+/* Built once at the end of Model<D>::parseModel (include/Model.h:1596-1641) from one pxe_layer_desc per layer.
+ * raw_heads = 0: the convolution in front of a YOLO layer keeps its epilogue (bias, linear), YoloLayer<CUDA>::forward
+ * activates into output_ as in the reference -- output() is public -- and yolo_add_detects.inl decodes that tensor.
+ * (With raw_heads = 1 the plan marks those convolutions head_raw: no epilogue, and the decode must then be given the
+ * raw convolution output, the bias and head_is_raw = 1 instead; the fragments here do not take that route.) */
 inline int build_plan(const std::vector<pxe_layer_desc>& descs, bool inferring, PlanView* out)
 {
-    const int rc = pxe_plan_build(descs.data(), (int)descs.size(), inferring ? 1 : 0, /*raw_heads=*/1, &out->plan);
+    const int rc = pxe_plan_build(descs.data(), (int)descs.size(), inferring ? 1 : 0, /*raw_heads=*/0, &out->plan);
     if (rc != PXE_OK) return rc;
     out->step_of.assign(descs.size(), -1);
     for (int s = 0; s < pxe_plan_step_count(out->plan); ++s) {
