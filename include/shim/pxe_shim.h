@@ -16,6 +16,8 @@
  *   region_add_detects.inl       RegionLayer<Device::CUDA>::addDetects, in place of include/cuda/RegionLayer.h:76-82
  *   softmax_forward.inl          SoftmaxLayer<Device::CUDA>::forward, in place of include/cuda/SoftmaxLayer.h:72-74
  *   avgpool_forward.inl          AvgPoolLayer<Device::CUDA>::forward, in place of include/cuda/AvgPoolLayer.h:71-73
+ *   conn_forward_epilogue.inl    ConnLayer<Device::CUDA>::forward (inferring), in place of include/cuda/ConnLayer.h:187-216
+ *   detect_add_detects.inl       DetectLayer<Device::CUDA>::addDetects, in place of include/cuda/DetectLayer.h:81-86
  *
  * What the fragments expect from the surrounding class beyond the reference's own members is listed at the top of
  * each; it comes to: a `const pxe_shim::PlanView& pxePlan()` on the model (built once after parseModel, see

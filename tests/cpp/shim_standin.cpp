@@ -63,6 +63,12 @@ static std::vector<RegionCall> g_regions;
 static std::vector<RegionDecodeCall> g_region_decodes;
 static std::vector<SoftmaxCall> g_softmaxes;
 static std::vector<AvgCall> g_avgs;
+struct DetectCall { const float* pred; long long pbs; int side, num, classes, coords, squared; float w, h; long long capacity; };
+static std::vector<DetectCall> g_detects;
+#define pxe_detect_decode shim_test_detect_decode
+static int shim_test_detect_decode(pxe_stream_t, const float* pred, long long pbs, int, int side, int num, int classes, int coords, int squared,
+                                   float w, float h, float, pxe_detection*, long long capacity, long long*, int)
+{ g_detects.push_back({pred, pbs, side, num, classes, coords, squared, w, h, capacity}); return PXE_OK; }
 #define pxe_region_forward shim_test_region_forward
 #define pxe_region_decode shim_test_region_decode
 #define pxe_softmax shim_test_softmax
@@ -251,6 +257,34 @@ struct AvgPoolLayer : Layer {
     void forward(const V& input)
     {
 #include "shim/avgpool_forward.inl"
+    }
+};
+
+struct ConnLayer : Layer {
+    ConnLayer(Model& m, int index, int outputs, int batch, bool bn) : Layer(m, index, outputs, 1, 1, batch), batchNorm_(bn)
+    {
+        for (auto* p : {&scales_, &biases_, &rollingMean_, &rollingVar_}) p->v.resize((std::size_t)outputs);
+        pxeActivation_ = pxe_shim::activation_from_name("relu");
+    }
+    bool batchNorm_;
+    Vec<float> scales_, biases_, rollingMean_, rollingVar_;
+    void forwardEpilogue()
+    {
+#include "shim/conn_forward_epilogue.inl"
+    }
+};
+
+struct DetectLayer : Layer {
+    using Layer::Layer;
+    int classes() const { return 20; }
+    int coords_ = 4, num_ = 2, side_ = 7;
+    bool sqrt_ = true;
+    Vec<char> pxeDets_;
+    Vec<long long> pxeCount_;
+    long long pxeCapacity_ = 0;
+    void addDetects(Detections& detects, int width, int height, float threshold)
+    {
+#include "shim/detect_add_detects.inl"
     }
 };
 
@@ -449,5 +483,23 @@ int main()
                      g_avgs[0].y == avg.output_.data() && g_avgs[0].ybs == 6 && g_avgs[0].c == 6 && g_avgs[0].h == 7 && g_avgs[0].w == 7;
     std::printf("%s: region=%zu region_decode=%zu softmax=%zu avgpool=%zu\n", ok3 ? "ok" : "MISMATCH", g_regions.size(),
                 g_region_decodes.size(), g_softmaxes.size(), g_avgs.size());
-    return ok3 ? 0 : 1;
+    if (!ok3) return 1;
+
+    // connected layer: the conv epilogue on a 1x1 map, in place; YOLOv1 head decode
+    const int before = g_epilogues;
+    px::ConnLayer conn(h, 3, 1470, B, false);
+    conn.forwardEpilogue();
+    px::DetectLayer det(h, 4, 1470, 1, 1, B);
+    det.pxeCapacity_ = (long long)B * 7 * 7 * 2;
+    det.pxeDets_.v.resize((std::size_t)det.pxeCapacity_ * sizeof(pxe_detection));
+    det.pxeCount_.v.resize(1);
+    det.addDetects(found, 448, 448, 0.2f);
+    const pxe_epilogue_desc& ce = g_last_epilogue;
+    const bool ok4 = g_epilogues == before + 1 && ce.x == conn.output_.data() && ce.y == conn.output_.data() && ce.channels == 1470 &&
+                     ce.height == 1 && ce.width == 1 && ce.bias == conn.biases_.data() && ce.gamma == nullptr && ce.act == PXE_ACT_RELU &&
+                     g_detects.size() == 1 && g_detects[0].pred == det.output_.data() && g_detects[0].pbs == 1470 && g_detects[0].side == 7 &&
+                     g_detects[0].num == 2 && g_detects[0].classes == 20 && g_detects[0].coords == 4 && g_detects[0].squared == 1 &&
+                     g_detects[0].w == 448.0f && g_detects[0].capacity == (long long)B * 98;
+    std::printf("%s: connected=%d detect=%zu\n", ok4 ? "ok" : "MISMATCH", g_epilogues - before, g_detects.size());
+    return ok4 ? 0 : 1;
 }

@@ -79,6 +79,8 @@ def test_shim_fragments_compile_inside_stand_in_layers(tmp_path):
     # heads that need no plan: Region forward and addDetects (the reference's image-0 indexing kept), softmax with groups and
     # temperature, the global average pool
     assert "ok: region=1 region_decode=1 softmax=1 avgpool=1" in run.stdout, run.stdout
+    # the connected layer's epilogue (a 1x1 map, in place) and the YOLOv1 head decode
+    assert "ok: connected=1 detect=1" in run.stdout, run.stdout
 
 
 @pytest.mark.gpu
